@@ -1,0 +1,62 @@
+"""Builds the CUDA library in-tree with nvcc for sm_100a (no GPU needed to compile).
+
+`python -m heirloom_b200.build` compiles every `csrc/*.cu` to an object file in parallel and
+links `heirloom_b200/lib/libheirloom_b200.so`.  Objects are rebuilt only when their source or a
+header is newer.
+"""
+from __future__ import annotations
+
+import os
+import subprocess
+import sys
+from concurrent.futures import ThreadPoolExecutor
+from pathlib import Path
+
+PKG = Path(__file__).resolve().parent
+CSRC = PKG / "csrc"
+OUT = PKG / "lib"
+LIB = OUT / "libheirloom_b200.so"
+NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
+FLAGS = [
+    "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
+    "--extended-lambda", "--expt-relaxed-constexpr", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=default",
+]
+
+
+def _newest_header() -> float:
+    headers = list(CSRC.glob("*.cuh")) + list(CSRC.glob("*.h")) + list((PKG.parent / "include").glob("*.h"))
+    return max(h.stat().st_mtime for h in headers)
+
+
+def _compile(src: Path, verbose: bool) -> Path:
+    obj = OUT / (src.stem + ".o")
+    stamp = max(src.stat().st_mtime, _newest_header())
+    if obj.exists() and obj.stat().st_mtime >= stamp:
+        return obj
+    cmd = [NVCC, *FLAGS, "-c", str(src), "-o", str(obj)]
+    if verbose:
+        cmd.insert(1, "-Xptxas=-v")
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    if res.returncode != 0:
+        raise RuntimeError(f"nvcc failed for {src.name}:\n{res.stdout}\n{res.stderr}")
+    if verbose:
+        sys.stderr.write(res.stderr)
+    return obj
+
+
+def build(verbose: bool = False) -> Path:
+    OUT.mkdir(exist_ok=True)
+    sources = sorted(CSRC.glob("*.cu"))
+    with ThreadPoolExecutor(max_workers=min(8, len(sources))) as pool:
+        objs = list(pool.map(lambda s: _compile(s, verbose), sources))
+    if LIB.exists() and all(LIB.stat().st_mtime >= o.stat().st_mtime for o in objs):
+        return LIB
+    cmd = [NVCC, "-shared", "-o", str(LIB), *map(str, objs), "-lcudart", "-ldl"]
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    if res.returncode != 0:
+        raise RuntimeError(f"link failed:\n{res.stdout}\n{res.stderr}")
+    return LIB
+
+
+if __name__ == "__main__":
+    print(build(verbose="-v" in sys.argv))

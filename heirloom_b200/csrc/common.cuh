@@ -1,0 +1,168 @@
+// Shared declarations for the sm_100a backend: context, error channel, dtype tags,
+// vector helpers.  Everything here is internal; the public surface is include/heirloom_b200.h.
+#pragma once
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <cuda.h>
+#include <stdint.h>
+#include <stddef.h>
+#include <string>
+#include "../../include/heirloom_b200.h"
+
+namespace hl {
+
+// Thread-local UTF-8 message behind hl_last_error(); mirrors the reference's
+// CudaError{message} channel (heirloom-kernels/src/cuda.rs:259-280).
+void set_error(const std::string& msg);
+int fail(const std::string& msg);                      // sets the message, returns HL_ERR_*
+int fail_cuda(cudaError_t e, const char* what);
+
+#define HL_CUDA(expr)                                                     \
+  do {                                                                    \
+    cudaError_t _e = (expr);                                              \
+    if (_e != cudaSuccess) return ::hl::fail_cuda(_e, #expr);             \
+  } while (0)
+
+#define HL_REQUIRE(cond, msg)                                             \
+  do {                                                                    \
+    if (!(cond)) return ::hl::fail(std::string(msg));                     \
+  } while (0)
+
+#define HL_LAUNCH_CHECK(name)                                             \
+  do {                                                                    \
+    cudaError_t _e = cudaGetLastError();                                  \
+    if (_e != cudaSuccess) return ::hl::fail_cuda(_e, name);              \
+  } while (0)
+
+// Device status words.  Kernels never trap: a bad index or an expired wait writes a code
+// here and the host folds it into the error channel at the next hl_ctx_sync/hl_status_check
+// (the reference reads a status word after each launch, cuda.rs:7184-7193).
+enum StatusSlot : int {
+  ST_BAD_INDEX = 0,      // out-of-range gather/scatter/target index
+  ST_WAIT_EXPIRED = 1,   // a bounded mbarrier wait ran out
+  ST_BAD_ARGUMENT = 2,
+  ST_SLOTS = 8
+};
+
+struct Counters {
+  unsigned long long launches, gemm_tcgen05_launches, attention_launches, h2d_bytes, d2h_bytes,
+      allocations, allocated_bytes, nccl_calls, nccl_bytes;
+};
+
+}  // namespace hl
+
+struct hl_ctx {
+  int device = 0;
+  int sm_count = 0;
+  cudaStream_t stream = nullptr;       // compute stream
+  cudaStream_t comm_stream = nullptr;  // collective stream
+  int* status_dev = nullptr;           // hl::ST_SLOTS ints
+  int* status_host = nullptr;          // pinned mirror
+  void* workspace = nullptr;           // grow-only scratch (split-K partials, reductions)
+  size_t workspace_bytes = 0;
+  hl::Counters counters{};
+  void* nccl = nullptr;                // hl::NcclState*
+};
+
+namespace hl {
+int ensure_workspace(hl_ctx* ctx, size_t bytes);
+inline void count_launch(hl_ctx* ctx, unsigned long long n = 1) { ctx->counters.launches += n; }
+
+inline size_t dtype_size(int dtype) {
+  switch (dtype) {
+    case HL_F32: return 4;
+    case HL_BF16: return 2;
+    case HL_F64: return 8;
+    case HL_I64: return 8;
+    case HL_U8: return 1;
+    default: return 0;
+  }
+}
+
+__host__ __device__ inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
+__host__ __device__ inline long long ceil_div_ll(long long a, long long b) { return (a + b - 1) / b; }
+
+// f32 -> bf16 round-to-nearest-even (same rounding as the reference's storage.rs:440-445).
+__device__ __forceinline__ __nv_bfloat16 to_bf16(float x) { return __float2bfloat16_rn(x); }
+__device__ __forceinline__ float from_bf16(__nv_bfloat16 x) { return __bfloat162float(x); }
+__device__ __forceinline__ float bf16_round(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
+
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+__device__ __forceinline__ float2 unpack_bf16x2(uint32_t u) {
+  __nv_bfloat162 v = *reinterpret_cast<__nv_bfloat162*>(&u);
+  return __bfloat1622float2(v);
+}
+
+// tanh-approximate GELU and its derivative (reference: src/tensor.rs:5152-5154,
+// src/tensor/autograd.rs:2891-2897).
+template <typename T>
+__device__ __forceinline__ T gelu_fwd(T x) {
+  const T c = T(0.7978845608028654);
+  T inner = c * (x + T(0.044715) * x * x * x);
+  return T(0.5) * x * (T(1) + tanh(inner));
+}
+template <typename T>
+__device__ __forceinline__ T gelu_grad(T x) {
+  const T c = T(0.7978845608028654);
+  T inner = c * (x + T(0.044715) * x * x * x);
+  T t = tanh(inner);
+  T sech2 = T(1) - t * t;
+  T dinner = c * (T(1) + T(3.0 * 0.044715) * x * x);
+  return T(0.5) * (T(1) + t) + T(0.5) * x * sech2 * dinner;
+}
+__device__ __forceinline__ float gelu_fwd_f(float x) {
+  float inner = 0.7978845608028654f * (x + 0.044715f * x * x * x);
+  return 0.5f * x * (1.0f + tanhf(inner));
+}
+__device__ __forceinline__ float gelu_grad_f(float x) {
+  float inner = 0.7978845608028654f * (x + 0.044715f * x * x * x);
+  float t = tanhf(inner);
+  float sech2 = 1.0f - t * t;
+  float dinner = 0.7978845608028654f * (1.0f + 3.0f * 0.044715f * x * x);
+  return 0.5f * (1.0f + t) + 0.5f * x * sech2 * dinner;
+}
+
+template <typename T>
+__device__ __forceinline__ T warp_sum(T v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+template <typename T>
+__device__ __forceinline__ T warp_max(T v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    T other = __shfl_xor_sync(0xffffffffu, v, o);
+    v = other > v ? other : v;
+  }
+  return v;
+}
+
+// Block-wide sum for blockDim.x <= 1024 (multiple of 32); result valid in every thread.
+template <typename T>
+__device__ __forceinline__ T block_sum(T v, T* smem /* >= 32 entries */) {
+  int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+  v = warp_sum(v);
+  __syncthreads();
+  if (lane == 0) smem[warp] = v;
+  __syncthreads();
+  T r = (lane < nw) ? smem[lane] : T(0);
+  r = warp_sum(r);
+  return r;
+}
+template <typename T>
+__device__ __forceinline__ T block_max(T v, T* smem, T lowest) {
+  int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+  v = warp_max(v);
+  __syncthreads();
+  if (lane == 0) smem[warp] = v;
+  __syncthreads();
+  T r = (lane < nw) ? smem[lane] : lowest;
+  r = warp_max(r);
+  return r;
+}
+
+}  // namespace hl

@@ -1,0 +1,277 @@
+"""Host-side wrappers over the C ABI, one function per device op.
+
+The names follow the safe wrappers of the reference's kernel crate
+(`heirloom_kernels::cuda::*`, heirloom-kernels/src/cuda.rs:1001-6847): value-style functions that
+validate, launch and return the result buffer.  Device memory is held in torch tensors (torch
+is the allocator here, nothing more); every computation goes through `libheirloom_b200.so`.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import byref, c_float, c_int, c_longlong, c_size_t, c_void_p
+from typing import Optional
+
+import torch
+
+from . import _lib
+from ._lib import AdamWParams, AdamWTensor, Counters, DeviceInfo, GemmDesc, HeirloomError, MatrixLayout, check
+
+F32, BF16, F64, I64, U8 = 0, 1, 2, 3, 4
+ADD, SUB, MUL, DIV = 0, 1, 2, 3
+K_MAJOR, MN_MAJOR = 0, 1
+EPI_NONE, EPI_BIAS, EPI_BIAS_GELU, EPI_BIAS_RESIDUAL, EPI_DGELU = 0, 1, 2, 3, 4
+
+_DT = {torch.float32: F32, torch.bfloat16: BF16, torch.float64: F64, torch.int64: I64, torch.uint8: U8}
+
+
+def _p(t: Optional[torch.Tensor]) -> c_void_p:
+    return c_void_p(0 if t is None else t.data_ptr())
+
+
+def _dt(t: torch.Tensor) -> int:
+    return _DT[t.dtype]
+
+
+class Context:
+    """One compute stream + one collective stream on one device (`hl_ctx`)."""
+
+    def __init__(self, device: int = 0):
+        self.lib = _lib.load()
+        self.device = device
+        h = c_void_p()
+        check(self.lib.hl_ctx_create(c_int(device), byref(h)))
+        self.handle = h
+        self.torch_device = torch.device("cuda", device)
+        self.stream = torch.cuda.ExternalStream(self.lib.hl_ctx_stream(self.handle), device=self.torch_device)
+        # torch allocations, copies and fills issued by this thread now share the compute stream,
+        # so buffers handed to the library are always ordered with the kernels that use them.
+        torch.cuda.set_stream(self.stream)
+
+    def close(self) -> None:
+        if self.handle:
+            self.lib.hl_ctx_destroy(self.handle)
+            self.handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def sync(self) -> None:
+        check(self.lib.hl_ctx_sync(self.handle))
+
+    def device_info(self) -> DeviceInfo:
+        info = DeviceInfo()
+        check(self.lib.hl_device_info(self.handle, byref(info)))
+        return info
+
+    def counters(self) -> Counters:
+        c = Counters()
+        check(self.lib.hl_counters_get(self.handle, byref(c)))
+        return c
+
+    def reset_counters(self) -> None:
+        check(self.lib.hl_counters_reset(self.handle))
+
+    def empty(self, shape, dtype=torch.float32) -> torch.Tensor:
+        return torch.empty(shape, dtype=dtype, device=self.torch_device)
+
+    def zeros(self, shape, dtype=torch.float32) -> torch.Tensor:
+        return torch.zeros(shape, dtype=dtype, device=self.torch_device)
+
+
+# ---- elementwise ------------------------------------------------------------------------------
+def binary_f32(ctx: Context, op: int, a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    out = torch.empty_like(a)
+    check(ctx.lib.hl_binary_f32(ctx.handle, c_int(op), _p(a), _p(b), _p(out), c_size_t(a.numel())))
+    return out
+
+
+def scale_f32(ctx: Context, a: torch.Tensor, s: float) -> torch.Tensor:
+    out = torch.empty_like(a)
+    check(ctx.lib.hl_scale_f32(ctx.handle, _p(a), c_float(s), _p(out), c_size_t(a.numel())))
+    return out
+
+
+def fill_f32(ctx: Context, out: torch.Tensor, value: float) -> None:
+    check(ctx.lib.hl_fill_f32(ctx.handle, _p(out), c_float(value), c_size_t(out.numel())))
+
+
+def relu_f32(ctx: Context, x: torch.Tensor) -> torch.Tensor:
+    out = torch.empty_like(x)
+    check(ctx.lib.hl_relu_f32(ctx.handle, _p(x), _p(out), c_size_t(x.numel())))
+    return out
+
+
+def relu_backward_f32(ctx: Context, x: torch.Tensor, grad_out: torch.Tensor) -> torch.Tensor:
+    out = torch.empty_like(x)
+    check(ctx.lib.hl_relu_backward_f32(ctx.handle, _p(x), _p(grad_out), _p(out), c_size_t(x.numel())))
+    return out
+
+
+def cast(ctx: Context, src: torch.Tensor, dst_dtype: torch.dtype) -> torch.Tensor:
+    dst = torch.empty(src.shape, dtype=dst_dtype, device=src.device)
+    check(ctx.lib.hl_cast(ctx.handle, _p(src), c_int(_dt(src)), _p(dst), c_int(_DT[dst_dtype]), c_size_t(src.numel())))
+    return dst
+
+
+def gelu(ctx: Context, x: torch.Tensor) -> torch.Tensor:
+    out = torch.empty_like(x)
+    check(ctx.lib.hl_gelu(ctx.handle, _p(x), _p(out), c_int(_dt(x)), c_size_t(x.numel())))
+    return out
+
+
+def gelu_backward(ctx: Context, x: torch.Tensor, grad_out: torch.Tensor) -> torch.Tensor:
+    out = torch.empty_like(x)
+    check(ctx.lib.hl_gelu_backward(ctx.handle, _p(x), _p(grad_out), _p(out), c_int(_dt(x)), c_size_t(x.numel())))
+    return out
+
+
+def bias_add_f32(ctx: Context, x: torch.Tensor, bias: torch.Tensor) -> torch.Tensor:
+    out = torch.empty_like(x)
+    rows, cols = x.numel() // bias.numel(), bias.numel()
+    check(ctx.lib.hl_bias_add_f32(ctx.handle, _p(x), _p(bias), _p(out), c_int(rows), c_int(cols)))
+    return out
+
+
+def bias_grad(ctx: Context, grad_out: torch.Tensor) -> torch.Tensor:
+    rows, cols = grad_out.shape
+    out = torch.empty(cols, dtype=torch.float32, device=grad_out.device)
+    check(ctx.lib.hl_bias_grad(ctx.handle, _p(grad_out), c_int(_dt(grad_out)), _p(out), c_int(rows), c_int(cols)))
+    return out
+
+
+def _reduce(ctx: Context, fn, x: torch.Tensor) -> torch.Tensor:
+    out = torch.empty(1, dtype=torch.float32, device=x.device)
+    check(fn(ctx.handle, _p(x), c_size_t(x.numel()), _p(out)))
+    return out
+
+
+def sum_f32(ctx, x):
+    return _reduce(ctx, ctx.lib.hl_sum_f32, x)
+
+
+def mean_f32(ctx, x):
+    return _reduce(ctx, ctx.lib.hl_mean_f32, x)
+
+
+def sum_squares_f32(ctx, x):
+    return _reduce(ctx, ctx.lib.hl_sum_squares_f32, x)
+
+
+# ---- layer norm / embedding / loss ---------------------------------------------------------------
+def layer_norm_forward(ctx: Context, x, gamma, beta, eps: float = 1e-5, out_dtype=None):
+    rows, feat = x.numel() // x.shape[-1], x.shape[-1]
+    y = torch.empty(x.shape, dtype=out_dtype or x.dtype, device=x.device)
+    mean = torch.empty(rows, dtype=torch.float32, device=x.device)
+    rstd = torch.empty(rows, dtype=torch.float32, device=x.device)
+    check(ctx.lib.hl_layer_norm_forward(ctx.handle, _p(x), c_int(_dt(x)), _p(gamma), _p(beta), _p(y), c_int(_dt(y)),
+                                        _p(mean), _p(rstd), c_int(rows), c_int(feat), c_float(eps)))
+    return y, mean, rstd
+
+
+def layer_norm_backward(ctx: Context, x, gamma, dy, mean=None, rstd=None, residual_grad=None, want_bf16=False):
+    rows, feat = x.numel() // x.shape[-1], x.shape[-1]
+    dx = torch.empty(x.shape, dtype=torch.float32, device=x.device)
+    dxb = torch.empty(x.shape, dtype=torch.bfloat16, device=x.device) if want_bf16 else None
+    dg = torch.empty(feat, dtype=torch.float32, device=x.device)
+    db = torch.empty(feat, dtype=torch.float32, device=x.device)
+    check(ctx.lib.hl_layer_norm_backward(ctx.handle, _p(x), c_int(_dt(x)), _p(gamma), _p(dy), _p(mean), _p(rstd),
+                                         _p(residual_grad), _p(dx), _p(dxb), _p(dg), _p(db), c_int(rows), c_int(feat)))
+    return (dx, dxb, dg, db) if want_bf16 else (dx, dg, db)
+
+
+def embedding_forward(ctx: Context, table, idx, pos_table=None, out_dtype=torch.float32):
+    n, dim = idx.numel(), table.shape[1]
+    period = idx.shape[-1] if pos_table is not None else 0
+    out = torch.empty(tuple(idx.shape) + (dim,), dtype=out_dtype, device=table.device)
+    check(ctx.lib.hl_embedding_forward(ctx.handle, _p(table), c_int(table.shape[0]), _p(idx), _p(pos_table),
+                                       c_int(period), _p(out), c_int(_DT[out_dtype]), c_int(n), c_int(dim)))
+    return out
+
+
+def embedding_backward(ctx: Context, grad_out, idx, table_rows: int, pos_rows: int = 0):
+    n, dim = idx.numel(), grad_out.shape[-1]
+    gt = torch.zeros(table_rows, dim, dtype=torch.float32, device=grad_out.device)
+    gp = torch.zeros(pos_rows, dim, dtype=torch.float32, device=grad_out.device) if pos_rows else None
+    check(ctx.lib.hl_embedding_backward(ctx.handle, _p(grad_out), _p(idx), _p(gt), c_int(table_rows), _p(gp),
+                                        c_int(pos_rows), c_int(n), c_int(dim)))
+    return (gt, gp) if pos_rows else gt
+
+
+def cross_entropy(ctx: Context, logits, targets, grad_scale: float = 1.0, dlogits_dtype=torch.float32,
+                  want_grad: bool = True):
+    rows, classes = logits.shape
+    loss = torch.empty(1, dtype=torch.float32, device=logits.device)
+    d = torch.empty(rows, classes, dtype=dlogits_dtype, device=logits.device) if want_grad else None
+    check(ctx.lib.hl_cross_entropy(ctx.handle, _p(logits), c_longlong(logits.stride(0)), _p(targets), c_int(rows),
+                                   c_int(classes), c_float(grad_scale), _p(loss), c_void_p(0), _p(d),
+                                   c_int(_DT[dlogits_dtype]), c_longlong(classes)))
+    return loss, d
+
+
+# ---- optimizer -------------------------------------------------------------------------------------
+def adamw_params(lr, beta1, beta2, eps, weight_decay, clip_scale, step) -> AdamWParams:
+    """Bias corrections are computed on the host in f64 and narrowed to f32, as
+    `AdamW::step_mut` does (src/nn.rs:2196-2198)."""
+    return AdamWParams(lr, beta1, beta2, eps, weight_decay, clip_scale, 1.0 - beta1 ** step, 1.0 - beta2 ** step)
+
+
+def adamw_update_f32(ctx: Context, param, grad, m, v, hp: AdamWParams) -> None:
+    check(ctx.lib.hl_adamw_f32(ctx.handle, _p(param), _p(grad), _p(m), _p(v), c_size_t(param.numel()), byref(hp)))
+
+
+def adamw_update_multi(ctx: Context, params, grads, ms, vs, hp: AdamWParams, shadows=None) -> None:
+    arr = (AdamWTensor * len(params))()
+    for i, (p, g, m, v) in enumerate(zip(params, grads, ms, vs)):
+        arr[i] = AdamWTensor(p.data_ptr(), g.data_ptr(), m.data_ptr(), v.data_ptr(),
+                             shadows[i].data_ptr() if shadows is not None else 0, p.numel())
+    check(ctx.lib.hl_adamw_multi(ctx.handle, arr, c_int(len(params)), byref(hp)))
+
+
+# ---- matmul ------------------------------------------------------------------------------------------
+def _layout(t: torch.Tensor) -> MatrixLayout:
+    return MatrixLayout(t.shape[0], t.shape[1], t.stride(0), t.stride(1), 0)
+
+
+def matmul_f32_strided(ctx: Context, a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None,
+                       accumulate: bool = False) -> torch.Tensor:
+    """Rank-2 f32 matmul over arbitrary strided views (e.g. `weight.t()`), f64 accumulation."""
+    if out is None:
+        out = torch.empty(a.shape[0], b.shape[1], dtype=torch.float32, device=a.device)
+    la, lb, lo = _layout(a), _layout(b), _layout(out)
+    check(ctx.lib.hl_matmul_f32_strided(ctx.handle, _p(a), byref(la), _p(b), byref(lb), _p(out), byref(lo),
+                                        c_int(1 if accumulate else 0)))
+    return out
+
+
+def gemm_bf16(ctx: Context, a: torch.Tensor, b: torch.Tensor, m: int, n: int, k: int, a_layout=K_MAJOR,
+              b_layout=K_MAJOR, epilogue=EPI_NONE, out_dtype=torch.bfloat16, bias=None, aux_in=None,
+              want_aux_out=False, split_k=0, out=None):
+    """C[m,n] = A·B with per-operand storage order; see `hl_gemm_bf16` in the C header."""
+    if out is None:
+        out = torch.empty(m, n, dtype=out_dtype, device=a.device)
+    aux_out = torch.empty(m, n, dtype=torch.bfloat16, device=a.device) if want_aux_out else None
+    desc = GemmDesc(m, n, k, a_layout, b_layout, a.stride(0), b.stride(0), out.stride(0), epilogue, _DT[out.dtype],
+                    split_k, aux_in.stride(0) if aux_in is not None else 0, n if want_aux_out else 0)
+    check(ctx.lib.hl_gemm_bf16(ctx.handle, byref(desc), _p(a), _p(b), _p(out), _p(bias), _p(aux_in), _p(aux_out)))
+    return (out, aux_out) if want_aux_out else out
+
+
+# ---- attention, f32 route ----------------------------------------------------------------------------
+def causal_attention_f32_forward(ctx: Context, q, k, v, n_heads: int):
+    B, T, C = q.shape
+    out = torch.empty_like(q)
+    probs = torch.empty(B, n_heads, T, T, dtype=torch.float32, device=q.device)
+    check(ctx.lib.hl_causal_attention_f32_forward(ctx.handle, _p(q), _p(k), _p(v), _p(out), _p(probs), c_int(B),
+                                                  c_int(T), c_int(C), c_int(n_heads)))
+    return out, probs
+
+
+def causal_attention_f32_backward(ctx: Context, q, k, v, probs, grad_out, n_heads: int):
+    B, T, C = q.shape
+    dq, dk, dv = torch.empty_like(q), torch.empty_like(q), torch.empty_like(q)
+    check(ctx.lib.hl_causal_attention_f32_backward(ctx.handle, _p(q), _p(k), _p(v), _p(probs), _p(grad_out), _p(dq),
+                                                   _p(dk), _p(dv), c_int(B), c_int(T), c_int(C), c_int(n_heads)))
+    return dq, dk, dv

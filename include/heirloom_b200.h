@@ -1,0 +1,221 @@
+/*
+ * heirloom_b200 — C ABI of the sm_100a backend for Heirloom's transformer training step.
+ *
+ * Every entry point returns 0 (HL_OK) or a negative HL_ERR_* code; the message is available
+ * from hl_last_error() (thread local).  Nothing throws or aborts across this boundary.
+ * Pointers named `*_dev` / documented as device pointers are plain CUDA device addresses;
+ * sizes are element counts unless they say bytes.  No kernel traps on bad data: device-side
+ * problems (out-of-range index, expired wait) are written to status words that
+ * hl_ctx_sync()/hl_status_check() fold into the same error channel.
+ *
+ * File:line citations name the reference interface each entry point replaces, by path inside
+ * the Heirloom repository.
+ */
+#ifndef HEIRLOOM_B200_H
+#define HEIRLOOM_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define HL_OK 0
+#define HL_ERR_INVALID (-1) /* argument validation failed before any launch */
+#define HL_ERR_CUDA (-2)    /* a CUDA runtime/driver call failed */
+#define HL_ERR_DEVICE (-3)  /* a kernel reported a problem through the status words */
+#define HL_ERR_NCCL (-4)
+
+/* Element types (reference: DType, src/storage.rs:14-20; device bool is one byte). */
+enum { HL_F32 = 0, HL_BF16 = 1, HL_F64 = 2, HL_I64 = 3, HL_U8 = 4 };
+
+typedef struct hl_ctx hl_ctx;
+typedef struct hl_buffer hl_buffer;
+
+/* ---- runtime -------------------------------------------------------------------------------
+ * One context per (thread, device): one compute stream and one collective stream, a status
+ * buffer and a grow-only scratch arena.  Replaces the per-thread context/stream cache of
+ * heirloom-kernels/src/cuda.rs:7517-7521, :7653-7681.  Not thread-safe by contract. */
+int hl_ctx_create(int device_ordinal, hl_ctx** out);
+void hl_ctx_destroy(hl_ctx* ctx);
+/* Waits for the compute stream, then reports any device status word as an error. */
+int hl_ctx_sync(hl_ctx* ctx);
+/* The compute stream as a cudaStream_t, for callers that time with their own events. */
+void* hl_ctx_stream(hl_ctx* ctx);
+const char* hl_last_error(void);
+
+/* Device facts (reference: device_supports_bf16_tensor_cores, cuda.rs:8290-8296). */
+typedef struct {
+  int sm_major, sm_minor, sm_count;
+  size_t total_bytes, free_bytes;
+  int supports_tcgen05; /* 1 only on compute capability 10.x */
+} hl_device_info_t;
+int hl_device_info(hl_ctx* ctx, hl_device_info_t* out);
+
+/* Counters (reference: cuda_runtime_counters / tensor_core_counters, cuda.rs:1589-2014). */
+typedef struct {
+  uint64_t launches, gemm_tcgen05_launches, attention_launches, h2d_bytes, d2h_bytes, allocations,
+      allocated_bytes, nccl_calls, nccl_bytes;
+} hl_counters_t;
+int hl_counters_get(hl_ctx* ctx, hl_counters_t* out);
+int hl_counters_reset(hl_ctx* ctx);
+
+/* Reference-counted device buffers (reference: CudaBuffer, cuda.rs:652-656; frees are
+ * stream-ordered as in :7870-7922).  hl_memcpy_d2h waits for the compute stream first
+ * (cuda.rs:836). */
+int hl_buffer_alloc(hl_ctx* ctx, size_t bytes, hl_buffer** out);
+int hl_buffer_retain(hl_buffer* buf);
+int hl_buffer_release(hl_buffer* buf);
+void* hl_buffer_ptr(hl_buffer* buf);
+size_t hl_buffer_bytes(hl_buffer* buf);
+int hl_memcpy_h2d(hl_ctx* ctx, void* dst_dev, const void* src_host, size_t bytes);
+int hl_memcpy_d2h(hl_ctx* ctx, void* dst_host, const void* src_dev, size_t bytes);
+int hl_memset_zero(hl_ctx* ctx, void* dst_dev, size_t bytes);
+
+/* ---- elementwise ---------------------------------------------------------------------------
+ * f32 add/sub/mul/div (reference: heirloom_add/sub/mul/div_f32, kernels.ptx:6-141). */
+enum { HL_ADD = 0, HL_SUB = 1, HL_MUL = 2, HL_DIV = 3 };
+int hl_binary_f32(hl_ctx* ctx, int op, const float* a, const float* b, float* out, size_t n);
+/* out = a * s (kernels.ptx:142). */
+int hl_scale_f32(hl_ctx* ctx, const float* a, float s, float* out, size_t n);
+/* kernels.ptx:1131. */
+int hl_fill_f32(hl_ctx* ctx, float* out, float value, size_t n);
+/* ReLU and its gradient (kernels.ptx:4724, :4755). */
+int hl_relu_f32(hl_ctx* ctx, const float* x, float* out, size_t n);
+int hl_relu_backward_f32(hl_ctx* ctx, const float* x, const float* grad_out, float* grad_in, size_t n);
+/* Casts with round-to-nearest-even (kernels.ptx:174, :208, :238; src/storage.rs:440-449).
+ * src_dtype/dst_dtype in {HL_F32, HL_BF16}; equal f32 types perform the bf16 round trip. */
+int hl_cast(hl_ctx* ctx, const void* src, int src_dtype, void* dst, int dst_dtype, size_t n);
+/* tanh-GELU and its gradient (kernels.ptx:4791, :4842; src/tensor.rs:5152-5154,
+ * src/tensor/autograd.rs:2891-2897).  dtype in {HL_F32, HL_BF16} applies to x/out/grads. */
+int hl_gelu(hl_ctx* ctx, const void* x, void* out, int dtype, size_t n);
+int hl_gelu_backward(hl_ctx* ctx, const void* x, const void* grad_out, void* grad_in, int dtype, size_t n);
+/* out[r,c] = x[r,c] + bias[c] (kernels.ptx:272). */
+int hl_bias_add_f32(hl_ctx* ctx, const float* x, const float* bias, float* out, int rows, int cols);
+/* Column sums: grad_bias[c] = sum_r grad_out[r,c] (kernels.ptx:312).  grad_out dtype f32 or
+ * bf16, f32 result; a two-stage reduction instead of one serial thread per column. */
+int hl_bias_grad(hl_ctx* ctx, const void* grad_out, int dtype, float* grad_bias, int rows, int cols);
+
+/* ---- reductions (kernels.ptx:4610, :4647, :4685): result is one f32 on the device ---------- */
+int hl_sum_f32(hl_ctx* ctx, const float* x, size_t n, float* out_dev);
+int hl_mean_f32(hl_ctx* ctx, const float* x, size_t n, float* out_dev);
+int hl_sum_squares_f32(hl_ctx* ctx, const float* x, size_t n, float* out_dev);
+
+/* ---- layer norm over the last dimension ----------------------------------------------------
+ * Forward (reference: src/tensor.rs:3175-3256, kernels.ptx:3260): biased variance,
+ * rstd = 1/sqrt(var+eps).  x/y dtypes in {HL_F32, HL_BF16}; gamma/beta f32; saves per-row
+ * mean and rstd (f32, may be NULL). */
+int hl_layer_norm_forward(hl_ctx* ctx, const void* x, int x_dtype, const float* gamma, const float* beta,
+                          void* y, int y_dtype, float* mean, float* rstd, int rows, int features, float eps);
+/* Backward (src/tensor/autograd.rs:2158-2232, kernels.ptx:3347, :3463):
+ *   dx = rstd*(F*dxhat - sum(dxhat) - xhat*sum(dxhat*xhat))/F  [+ residual_grad if given]
+ *   dgamma = sum_rows dy*xhat, dbeta = sum_rows dy.
+ * dy and residual_grad are f32; dx is written as f32 (dx_f32) and/or bf16 (dx_bf16), either
+ * may be NULL.  mean/rstd as saved by the forward. */
+int hl_layer_norm_backward(hl_ctx* ctx, const void* x, int x_dtype, const float* gamma, const float* dy,
+                           const float* mean, const float* rstd, const float* residual_grad, float* dx_f32,
+                           void* dx_bf16, float* dgamma, float* dbeta, int rows, int features);
+
+/* ---- embedding -----------------------------------------------------------------------------
+ * out[n,:] = table[idx[n],:] (+ pos_table[n % period,:] when pos_table != NULL, each term and
+ * the sum rounded to out_dtype as the reference's AMP route does, memory_transformer.rs:1636-1648).
+ * (reference: src/tensor.rs:3337-3395, kernels.ptx:1660).  Out-of-range ids set a status word. */
+int hl_embedding_forward(hl_ctx* ctx, const float* table, int table_rows, const int64_t* idx,
+                         const float* pos_table, int period, void* out, int out_dtype, int n, int dim);
+/* grad_table[idx[n],:] += grad_out[n,:]; repeats accumulate (src/tensor/autograd.rs:2234-2261,
+ * kernels.ptx:1720).  grad_table must be zeroed by the caller when it starts a new step.
+ * When pos_grad != NULL also pos_grad[n % period,:] += grad_out[n,:]. */
+int hl_embedding_backward(hl_ctx* ctx, const float* grad_out, const int64_t* idx, float* grad_table,
+                          int table_rows, float* pos_grad, int period, int n, int dim);
+
+/* ---- softmax cross-entropy with fused logits gradient --------------------------------------
+ * loss = mean_rows(-z[y] + max + ln sum exp(z - max)) (src/tensor.rs:4816-4882,
+ * kernels.ptx:3558); dlogits = (softmax - onehot) * grad_scale / rows
+ * (src/tensor/autograd.rs:2591-2621, kernels.ptx:3658).  logits f32 `[rows, classes]` with row
+ * stride `ld`; dlogits (may be NULL) f32 or bf16, may alias logits when f32.  row_loss (may be
+ * NULL) receives per-row losses; loss_dev receives the mean. */
+int hl_cross_entropy(hl_ctx* ctx, const float* logits, long long ld, const int64_t* targets, int rows,
+                     int classes, float grad_scale, float* loss_dev, float* row_loss, void* dlogits,
+                     int dlogits_dtype, long long ld_dlogits);
+
+/* ---- coupled-decay AdamW -------------------------------------------------------------------
+ * Arithmetic and operation order of the reference kernel (kernels.ptx:441-467; host side
+ * src/nn.rs:2156-2220): g' = g*clip + wd*p; m = b1*m + (1-b1)*g'; v = b2*v + (1-b2)*g'*g';
+ * p -= lr * (m/bc1) / (sqrt(v/bc2) + eps), every product and sum rounded separately. */
+typedef struct {
+  float lr, beta1, beta2, eps, weight_decay, clip_scale, bias_correction1, bias_correction2;
+} hl_adamw_params;
+int hl_adamw_f32(hl_ctx* ctx, float* param, const float* grad, float* m, float* v, size_t n,
+                 const hl_adamw_params* hp);
+/* One launch over many tensors (replaces one launch per parameter, src/nn.rs:2467-2505).
+ * Each entry is a 16-byte aligned chunk of one tensor; `shadow_bf16` (may be NULL) receives
+ * the updated parameter rounded to bf16 for the next step's GEMM operands. */
+typedef struct {
+  float* param;
+  const float* grad;
+  float* m;
+  float* v;
+  void* shadow_bf16;
+  uint64_t n;
+} hl_adamw_tensor;
+int hl_adamw_multi(hl_ctx* ctx, const hl_adamw_tensor* tensors_host, int count, const hl_adamw_params* hp);
+
+/* ---- GEMM ----------------------------------------------------------------------------------
+ * f32 strided matmul with f64 accumulation: out[i,j] = sum_k A[i,k]*B[k,j] with arbitrary
+ * element strides and offsets (reference: heirloom_matmul_f32_strided, kernels.ptx:1455-1659;
+ * MatrixLayout, cuda.rs:536-560).  Used by the f32 parity mode; not a throughput path. */
+typedef struct {
+  long long rows, cols, row_stride, col_stride, offset;
+} hl_matrix_layout;
+int hl_matmul_f32_strided(hl_ctx* ctx, const float* a, const hl_matrix_layout* la, const float* b,
+                          const hl_matrix_layout* lb, float* out, const hl_matrix_layout* lo, int accumulate);
+
+/* ---- causal self-attention, f32 route -------------------------------------------------------
+ * q, k, v, out: [batch, time, channels] with heads interleaved along channels
+ * (index b*T*C + t*C + h*hd + j, src/tensor.rs:5156-5177); scale 1/sqrt(hd); probs
+ * [batch, heads, time, time] is saved for the backward like the reference's f32 CUDA route
+ * (src/tensor.rs:3980-4098, :4404-4494; kernels.ptx:3760-4609).  f64 accumulation. */
+int hl_causal_attention_f32_forward(hl_ctx* ctx, const float* q, const float* k, const float* v, float* out,
+                                    float* probs, int batch, int time, int channels, int n_heads);
+/* dQ, dK, dV from the saved probabilities (src/tensor/autograd.rs:2623-2712); sums run in a
+ * fixed order (no atomics). */
+int hl_causal_attention_f32_backward(hl_ctx* ctx, const float* q, const float* k, const float* v,
+                                     const float* probs, const float* grad_out, float* dq, float* dk, float* dv,
+                                     int batch, int time, int channels, int n_heads);
+
+/* bf16 x bf16 -> f32-accumulate GEMM on tcgen05 tensor cores:
+ *   C[m,n] = A[m,k] * B[k,n] with operand storage chosen per side,
+ *   a_layout: HL_K_MAJOR  A stored [m][k] (k contiguous, row stride lda)
+ *             HL_MN_MAJOR A stored [k][m] (m contiguous, row stride lda)
+ *   b_layout: HL_K_MAJOR  B stored [n][k] (k contiguous, row stride ldb)  -- "rhs_t"
+ *             HL_MN_MAJOR B stored [k][n] (n contiguous, row stride ldb)  -- "normal rhs"
+ * so forward (X*W^T), dgrad (dY*W) and wgrad (dY^T*X) need no transpose or pad kernels.
+ * Replaces matmul_bf16_tensor_core_* (cuda.rs:4215-4386; tensor_core.ptx:42-1527) and the
+ * bias / cast / gelu kernels around them.  Epilogues act on the f32 accumulator:
+ *   HL_EPI_NONE           C = acc
+ *   HL_EPI_BIAS           C = acc + bias[n]
+ *   HL_EPI_BIAS_GELU      C = bf16(acc + bias) and aux_out = bf16(gelu(C))
+ *   HL_EPI_BIAS_RESIDUAL  C = bf16(aux_in + bf16(acc + bias))
+ *   HL_EPI_DGELU          C = acc * gelu'(aux_in)
+ * Requirements: n, lda, ldb, ldc multiples of 8; 16-byte aligned pointers.  split_k = 0 lets
+ * the library split the contraction for small outputs (plain f32 output only; partial sums go
+ * through the context's scratch arena and are reduced in a fixed order). */
+enum { HL_K_MAJOR = 0, HL_MN_MAJOR = 1 };
+enum { HL_EPI_NONE = 0, HL_EPI_BIAS = 1, HL_EPI_BIAS_GELU = 2, HL_EPI_BIAS_RESIDUAL = 3, HL_EPI_DGELU = 4 };
+typedef struct {
+  int m, n, k;
+  int a_layout, b_layout;
+  long long lda, ldb, ldc;
+  int epilogue;
+  int out_dtype; /* HL_BF16 or HL_F32 */
+  int split_k;
+  long long ld_aux_in, ld_aux_out; /* 0 = same as ldc */
+} hl_gemm_desc;
+int hl_gemm_bf16(hl_ctx* ctx, const hl_gemm_desc* desc, const void* a, const void* b, void* c,
+                 const float* bias, const void* aux_in, void* aux_out);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* HEIRLOOM_B200_H */
