@@ -326,8 +326,9 @@ size_t gemm_splitk_workspace_bytes(const hl_gemm_desc* d, int sm_count, int* spl
 
 int gemm_bf16_run(hl_ctx* ctx, const hl_gemm_desc* d, const void* a, const void* b, void* c, const float* bias,
                   const void* aux_in, void* aux_out, float* workspace, size_t workspace_bytes) {
-  HL_REQUIRE(ctx && d && a && b && c, "hl_gemm_bf16: null argument");
+  HL_REQUIRE(ctx && d, "hl_gemm_bf16: null argument");
   HL_REQUIRE(d->m > 0 && d->n > 0 && d->k > 0, "hl_gemm_bf16: m, n, k must be positive");
+  HL_REQUIRE(a && b && c, "hl_gemm_bf16: null operand pointer");
   HL_REQUIRE(d->n % 8 == 0 && d->ldc % 8 == 0, "hl_gemm_bf16: n and ldc must be multiples of 8");
   HL_REQUIRE(d->lda % 8 == 0 && d->ldb % 8 == 0, "hl_gemm_bf16: lda and ldb must be multiples of 8 elements");
   HL_REQUIRE(d->out_dtype == HL_BF16 || d->out_dtype == HL_F32, "hl_gemm_bf16: output dtype must be bf16 or f32");

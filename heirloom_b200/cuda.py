@@ -275,3 +275,16 @@ def causal_attention_f32_backward(ctx: Context, q, k, v, probs, grad_out, n_head
     check(ctx.lib.hl_causal_attention_f32_backward(ctx.handle, _p(q), _p(k), _p(v), _p(probs), _p(grad_out), _p(dq),
                                                    _p(dk), _p(dv), c_int(B), c_int(T), c_int(C), c_int(n_heads)))
     return dq, dk, dv
+
+
+# ---- attention, bf16 flash route ----------------------------------------------------------------------
+def flash_attention_forward(ctx: Context, q, k, v, batch: int, time: int, n_heads: int):
+    """q, k, v: bf16 `[batch*time, C]` views (possibly column slices of one fused buffer with the
+    same row stride).  Returns (out bf16 `[batch*time, C]`, lse f32 `[batch, heads, time]`)."""
+    C = q.shape[1]
+    out = torch.empty(batch * time, C, dtype=torch.bfloat16, device=q.device)
+    lse = torch.empty(batch, n_heads, time, dtype=torch.float32, device=q.device)
+    check(ctx.lib.hl_flash_attention_forward(ctx.handle, _p(q), _p(k), _p(v), c_longlong(q.stride(0)), _p(out),
+                                             c_longlong(out.stride(0)), _p(lse), c_int(batch), c_int(time),
+                                             c_int(n_heads), c_int(C // n_heads)))
+    return out, lse

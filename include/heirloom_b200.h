@@ -215,6 +215,19 @@ typedef struct {
 int hl_gemm_bf16(hl_ctx* ctx, const hl_gemm_desc* desc, const void* a, const void* b, void* c,
                  const float* bias, const void* aux_in, void* aux_out);
 
+/* ---- causal flash attention, bf16 route ----------------------------------------------------
+ * q, k, v: bf16 row-major views of [batch*time, *] with row stride ld_qkv and heads interleaved
+ * along the channel dimension (column h*head_dim + j, src/tensor.rs:5156-5177), so the three
+ * may be column slices of one fused projection buffer.  out: bf16 [batch*time, heads*head_dim]
+ * with row stride ld_out.  lse: f32 [batch, heads, time], natural-log log-sum-exp of the scaled
+ * scores, saved for the backward (the reference saves row_max and row_denom instead,
+ * src/tensor.rs:4164-4358).  P enters the PV product rounded to bf16, accumulation is f32.
+ * Replaces causal_attention_bf16_flash_tensor_core_forward_f32_buffers (cuda.rs:5283-5420,
+ * tensor_core.ptx:2284-2981).  head_dim must be 64. */
+int hl_flash_attention_forward(hl_ctx* ctx, const void* q, const void* k, const void* v, long long ld_qkv,
+                               void* out, long long ld_out, float* lse, int batch, int time, int n_heads,
+                               int head_dim);
+
 #ifdef __cplusplus
 }
 #endif
