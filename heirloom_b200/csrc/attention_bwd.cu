@@ -1,0 +1,404 @@
+// Causal flash attention backward on tcgen05.  One CTA owns 128 keys of one (batch, head) and
+// walks the query tiles at or below the diagonal.  Per query tile five tensor-core products
+// run against tensor memory:
+//     S  = Q·Kᵀ          dP = dO·Vᵀ                      (recomputed scores, f32)
+//     dV += Pᵀ·dO        dK += dSᵀ·Q        dQ_tile = dS·K
+// P = exp(S·scale − lse) and dS = P∘(dP − D)·scale are formed in registers by eight warps (two
+// per tensor-memory lane group, each taking half of the key columns) and handed back through
+// swizzled shared memory as bf16 operands.  dK and dV stay in tensor memory for the whole
+// walk; dQ tiles are added into an f32 accumulator with 128-bit reductions.
+//
+// Replaces the reference's recompute-based backward with scalar f32 atomics
+// (tensor_core.ptx:3111-4407, heirloom-kernels/src/cuda.rs:9256-9294) and, for the values it
+// computes, follows src/tensor/autograd.rs:1626-1914 (bf16 operands, f32 accumulation).
+#include "common.cuh"
+#include "tc05.cuh"
+
+namespace hl {
+namespace {
+
+constexpr int FB_BM = 128;  // queries per tile
+constexpr int FB_BN = 128;  // keys per CTA
+constexpr int FB_HD = 64;
+constexpr int FB_Q_STAGES = 2;
+constexpr int FB_TILE_BYTES = 128 * FB_HD * 2;  // 16 KB
+constexpr int FB_PS_BYTES = FB_BM * FB_BN * 2;  // 32 KB
+constexpr int FB_SOFTMAX_WARPS = 8;
+constexpr int FB_THREADS = (FB_SOFTMAX_WARPS + 2) * 32;  // + TMA warp + MMA warp
+constexpr int FB_TMEM_COLS = 512;
+constexpr int FB_SMEM_DATA = FB_TILE_BYTES * (2 + 2 * FB_Q_STAGES) + 2 * FB_PS_BYTES;  // 160 KB
+constexpr int FB_SMEM_BYTES = FB_SMEM_DATA + 1024;
+
+struct FbBarriers {
+  uint64_t kv_full;
+  uint64_t q_full[FB_Q_STAGES], q_empty[FB_Q_STAGES];
+  uint64_t sdp_full, p_full, dq_full;
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+struct FbParams {
+  int B, T, H;
+  const float* lse;    // [B,H,T]
+  const float* delta;  // [B,H,T] rowsum(dO * O)
+  float* dq_accum;     // f32 [B*T, H*hd], zeroed by the caller
+  long long ld_dq;
+  __nv_bfloat16* dk;
+  __nv_bfloat16* dv;
+  long long ld_dkv;
+  float scale, scale_log2;
+  int* status;
+};
+
+__device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
+  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
+
+__global__ void __launch_bounds__(FB_THREADS, 1)
+flash_attention_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                           const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do,
+                           const FbParams p) {
+  extern __shared__ uint8_t fb_smem_raw[];
+  const uintptr_t raw = reinterpret_cast<uintptr_t>(fb_smem_raw);
+  uint8_t* tiles = reinterpret_cast<uint8_t*>((raw + sizeof(FbBarriers) + 1023) & ~uintptr_t(1023));
+  FbBarriers* bars = reinterpret_cast<FbBarriers*>(fb_smem_raw);
+  const bool layout_ok = (tiles + FB_SMEM_DATA) <= (fb_smem_raw + FB_SMEM_BYTES);
+  uint8_t* sk = tiles;
+  uint8_t* sv = sk + FB_TILE_BYTES;
+  uint8_t* sq = sv + FB_TILE_BYTES;                    // [stage] Q tiles
+  uint8_t* sdo = sq + FB_Q_STAGES * FB_TILE_BYTES;     // [stage] dO tiles
+  uint8_t* sp = sdo + FB_Q_STAGES * FB_TILE_BYTES;     // P  (bf16, [query][key], two 64-key blocks)
+  uint8_t* sds = sp + FB_PS_BYTES;                     // dS (same layout)
+  volatile int* abort_flag = &bars->abort_flag;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nq = (p.T + FB_BM - 1) / FB_BM;
+  const int bh = blockIdx.x % (p.B * p.H);
+  const int kj = blockIdx.x / (p.B * p.H);  // key tile; low tiles have the longest walks and start first
+  const int b = bh / p.H, h = bh % p.H;
+  const int row_base = b * p.T;
+  const int key0 = kj * FB_BN;
+  const int n_tiles = nq - kj;  // query tiles kj .. nq-1
+
+  if (threadIdx.x == 0) {
+    tc05::mbar_init(&bars->kv_full, 1);
+    for (int s = 0; s < FB_Q_STAGES; ++s) {
+      tc05::mbar_init(&bars->q_full[s], 1);
+      tc05::mbar_init(&bars->q_empty[s], 1);
+    }
+    tc05::mbar_init(&bars->sdp_full, 1);
+    tc05::mbar_init(&bars->p_full, FB_SOFTMAX_WARPS);
+    tc05::mbar_init(&bars->dq_full, 1);
+    bars->abort_flag = layout_ok ? 0 : 1;
+    tc05::fence_barrier_init();
+  }
+  if (warp == FB_SOFTMAX_WARPS + 1) {
+    tc05::tmem_alloc(&bars->tmem_base, FB_TMEM_COLS);
+    tc05::tmem_relinquish();
+  }
+  tc05::tc_fence_before_sync();
+  __syncthreads();
+  tc05::tc_fence_after_sync();
+  const uint32_t tmem_s = bars->tmem_base;  // 128 columns
+  const uint32_t tmem_dp = tmem_s + 128;    // 128 columns
+  const uint32_t tmem_dv = tmem_s + 256;    // 64 columns
+  const uint32_t tmem_dk = tmem_s + 320;    // 64 columns
+  const uint32_t tmem_dq = tmem_s + 384;    // 64 columns
+
+  if (warp == FB_SOFTMAX_WARPS) {
+    // -------------------------------------------------------------------------- TMA producer
+    if (tc05::elect_one() && !*abort_flag) {
+      tc05::tma_prefetch_desc(&map_q);
+      tc05::tma_prefetch_desc(&map_k);
+      tc05::tma_prefetch_desc(&map_v);
+      tc05::tma_prefetch_desc(&map_do);
+      tc05::mbar_arrive_expect_tx(&bars->kv_full, 2 * FB_TILE_BYTES);
+      tc05::tma_load_2d(sk, &map_k, &bars->kv_full, h * FB_HD, row_base + key0);
+      tc05::tma_load_2d(sv, &map_v, &bars->kv_full, h * FB_HD, row_base + key0);
+      for (int it = 0; it < n_tiles; ++it) {
+        const int s = it % FB_Q_STAGES;
+        if (!tc05::mbar_wait(&bars->q_empty[s], ((uint32_t)(it / FB_Q_STAGES) & 1u) ^ 1u, abort_flag)) break;
+        const int qrow = row_base + (kj + it) * FB_BM;
+        tc05::mbar_arrive_expect_tx(&bars->q_full[s], 2 * FB_TILE_BYTES);
+        tc05::tma_load_2d(sq + s * FB_TILE_BYTES, &map_q, &bars->q_full[s], h * FB_HD, qrow);
+        tc05::tma_load_2d(sdo + s * FB_TILE_BYTES, &map_do, &bars->q_full[s], h * FB_HD, qrow);
+      }
+    }
+  } else if (warp == FB_SOFTMAX_WARPS + 1) {
+    // -------------------------------------------------------------------------- MMA issuer
+    if (tc05::elect_one() && !*abort_flag) {
+      constexpr uint32_t idesc_sdp = tc05::instr_desc_bf16_f32(128, 128, false, false);
+      constexpr uint32_t idesc_dkv = tc05::instr_desc_bf16_f32(128, FB_HD, true, true);
+      constexpr uint32_t idesc_dq = tc05::instr_desc_bf16_f32(128, FB_HD, false, true);
+      const uint32_t ak = tc05::smem_u32(sk), av = tc05::smem_u32(sv);
+      const uint32_t ap = tc05::smem_u32(sp), ads = tc05::smem_u32(sds);
+      auto issue_scores = [&](int it) -> bool {
+        const int s = it % FB_Q_STAGES;
+        if (!tc05::mbar_wait(&bars->q_full[s], (uint32_t)(it / FB_Q_STAGES) & 1u, abort_flag)) return false;
+        tc05::tc_fence_after_sync();
+        const uint32_t aq = tc05::smem_u32(sq + s * FB_TILE_BYTES), ado = tc05::smem_u32(sdo + s * FB_TILE_BYTES);
+#pragma unroll
+        for (int ks = 0; ks < FB_HD / 16; ++ks)
+          tc05::umma_ss(tmem_s, tc05::smem_desc_sw128(aq + ks * 32, 16, 1024),
+                        tc05::smem_desc_sw128(ak + ks * 32, 16, 1024), idesc_sdp, ks > 0 ? 1u : 0u);
+#pragma unroll
+        for (int ks = 0; ks < FB_HD / 16; ++ks)
+          tc05::umma_ss(tmem_dp, tc05::smem_desc_sw128(ado + ks * 32, 16, 1024),
+                        tc05::smem_desc_sw128(av + ks * 32, 16, 1024), idesc_sdp, ks > 0 ? 1u : 0u);
+        tc05::umma_commit(&bars->sdp_full);
+        return true;
+      };
+      bool ok = tc05::mbar_wait(&bars->kv_full, 0, abort_flag);
+      if (ok) ok = issue_scores(0);
+      for (int it = 0; it < n_tiles && ok; ++it) {
+        if (!tc05::mbar_wait(&bars->p_full, (uint32_t)it & 1u, abort_flag)) break;
+        tc05::tc_fence_after_sync();
+        if (it + 1 < n_tiles && !issue_scores(it + 1)) break;
+        const int s = it % FB_Q_STAGES;
+        const uint32_t aq = tc05::smem_u32(sq + s * FB_TILE_BYTES), ado = tc05::smem_u32(sdo + s * FB_TILE_BYTES);
+#pragma unroll
+        for (int ks = 0; ks < FB_BM / 16; ++ks) {
+          // contraction over the 128 queries of this tile: 16 query rows = 2048 bytes per step
+          const uint64_t a_pt = tc05::smem_desc_sw128(ap + ks * 2048, FB_BM * 128, 1024);    // Pᵀ  (keys x queries)
+          const uint64_t a_dst = tc05::smem_desc_sw128(ads + ks * 2048, FB_BM * 128, 1024);  // dSᵀ
+          const uint64_t b_do = tc05::smem_desc_sw128(ado + ks * 2048, FB_BM * 128, 1024);
+          const uint64_t b_q = tc05::smem_desc_sw128(aq + ks * 2048, FB_BM * 128, 1024);
+          const uint32_t acc = (it > 0 || ks > 0) ? 1u : 0u;
+          tc05::umma_ss(tmem_dv, a_pt, b_do, idesc_dkv, acc);
+          tc05::umma_ss(tmem_dk, a_dst, b_q, idesc_dkv, acc);
+        }
+#pragma unroll
+        for (int ks = 0; ks < FB_BN / 16; ++ks) {
+          // dQ_tile = dS·K: contraction over the 128 keys; dS is K-major in two 64-key blocks
+          const uint64_t a_ds = tc05::smem_desc_sw128(ads + (ks / 4) * (FB_BM * 128) + (ks % 4) * 32, 16, 1024);
+          const uint64_t b_k = tc05::smem_desc_sw128(ak + ks * 2048, FB_BN * 128, 1024);
+          tc05::umma_ss(tmem_dq, a_ds, b_k, idesc_dq, ks > 0 ? 1u : 0u);
+        }
+        tc05::umma_commit(&bars->q_empty[s]);
+        tc05::umma_commit(&bars->dq_full);
+      }
+    }
+  } else {
+    // -------------------------------------------------------------------------- softmax warps
+    const int lg = warp & 3;          // tensor-memory lane group
+    const int half = warp >> 2;       // which 64 key columns / which 32 dQ columns
+    const int r = lg * 32 + lane;     // row within the tile
+    const uint32_t lane_sel = (uint32_t)(lg * 32) << 16;
+    bool ok = !*abort_flag;
+    for (int it = 0; it < n_tiles && ok; ++it) {
+      const int t = (kj + it) * FB_BM + r;  // query position
+      const bool t_ok = t < p.T;
+      const size_t stat = ((size_t)b * p.H + h) * p.T + (t_ok ? t : 0);
+      const float lse2 = t_ok ? p.lse[stat] * 1.4426950408889634f : 0.f;
+      const float dlt = t_ok ? p.delta[stat] : 0.f;
+      if (!tc05::mbar_wait(&bars->sdp_full, (uint32_t)it & 1u, abort_flag)) { ok = false; break; }
+      tc05::tc_fence_after_sync();
+      const bool diag = (it == 0);
+#pragma unroll 1
+      for (int c = 0; c < 2; ++c) {
+        const int col0 = half * 64 + c * 32;  // key column within the tile
+        uint32_t sb[32], db[32];
+        tc05::tmem_ld_32x32b_x32(tmem_s + lane_sel + col0, sb);
+        tc05::tmem_ld_32x32b_x32(tmem_dp + lane_sel + col0, db);
+        tc05::tmem_ld_wait();
+        uint32_t pp[16], dd[16];
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          float pr[2], dsv[2];
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const int key = key0 + col0 + i + e;
+            const bool live = t_ok && !(diag && key > t);
+            const float pv = live ? exp2f(__uint_as_float(sb[i + e]) * p.scale_log2 - lse2) : 0.f;
+            pr[e] = pv;
+            dsv[e] = pv * (__uint_as_float(db[i + e]) - dlt) * p.scale;
+          }
+          pp[i / 2] = pack_bf16x2(pr[0], pr[1]);
+          dd[i / 2] = pack_bf16x2(dsv[0], dsv[1]);
+        }
+        uint8_t* pline = sp + half * (FB_BM * 128) + r * 128;
+        uint8_t* dline = sds + half * (FB_BM * 128) + r * 128;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const int chunk = c * 4 + q;
+          const int off = (chunk ^ (r & 7)) << 4;
+          *reinterpret_cast<uint4*>(pline + off) = make_uint4(pp[q * 4], pp[q * 4 + 1], pp[q * 4 + 2], pp[q * 4 + 3]);
+          *reinterpret_cast<uint4*>(dline + off) = make_uint4(dd[q * 4], dd[q * 4 + 1], dd[q * 4 + 2], dd[q * 4 + 3]);
+        }
+      }
+      tc05::fence_proxy_async_smem();
+      tc05::tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) tc05::mbar_arrive(&bars->p_full);
+      // dQ tile -> global accumulator
+      if (!tc05::mbar_wait(&bars->dq_full, (uint32_t)it & 1u, abort_flag)) { ok = false; break; }
+      tc05::tc_fence_after_sync();
+      {
+        uint32_t qb[32];
+        tc05::tmem_ld_32x32b_x32(tmem_dq + lane_sel + half * 32, qb);
+        tc05::tmem_ld_wait();
+        if (t_ok) {
+          float* dst = p.dq_accum + (size_t)(row_base + t) * p.ld_dq + (size_t)h * FB_HD + half * 32;
+#pragma unroll
+          for (int i = 0; i < 32; i += 4)
+            red_add_v4(dst + i, __uint_as_float(qb[i]), __uint_as_float(qb[i + 1]), __uint_as_float(qb[i + 2]),
+                       __uint_as_float(qb[i + 3]));
+        }
+      }
+      tc05::tc_fence_before_sync();
+    }
+    // dK, dV for this key tile (row r = key)
+    if (ok) {
+      const int key = key0 + r;
+      uint32_t vb[32], kb[32];
+      tc05::tmem_ld_32x32b_x32(tmem_dv + lane_sel + half * 32, vb);
+      tc05::tmem_ld_32x32b_x32(tmem_dk + lane_sel + half * 32, kb);
+      tc05::tmem_ld_wait();
+      if (key < p.T) {
+        const size_t off = (size_t)(row_base + key) * p.ld_dkv + (size_t)h * FB_HD + half * 32;
+#pragma unroll
+        for (int i = 0; i < 32; i += 8) {
+          uint4 o;
+          o.x = pack_bf16x2(__uint_as_float(vb[i]), __uint_as_float(vb[i + 1]));
+          o.y = pack_bf16x2(__uint_as_float(vb[i + 2]), __uint_as_float(vb[i + 3]));
+          o.z = pack_bf16x2(__uint_as_float(vb[i + 4]), __uint_as_float(vb[i + 5]));
+          o.w = pack_bf16x2(__uint_as_float(vb[i + 6]), __uint_as_float(vb[i + 7]));
+          *reinterpret_cast<uint4*>(p.dv + off + i) = o;
+          o.x = pack_bf16x2(__uint_as_float(kb[i]), __uint_as_float(kb[i + 1]));
+          o.y = pack_bf16x2(__uint_as_float(kb[i + 2]), __uint_as_float(kb[i + 3]));
+          o.z = pack_bf16x2(__uint_as_float(kb[i + 4]), __uint_as_float(kb[i + 5]));
+          o.w = pack_bf16x2(__uint_as_float(kb[i + 6]), __uint_as_float(kb[i + 7]));
+          *reinterpret_cast<uint4*>(p.dk + off + i) = o;
+        }
+      }
+    }
+  }
+
+  tc05::tc_fence_before_sync();
+  __syncthreads();
+  if (*abort_flag) {
+    for (int i = 0; i < 2000; ++i) __nanosleep(100);
+    if (threadIdx.x == 0) atomicExch(p.status + (layout_ok ? ST_WAIT_EXPIRED : ST_BAD_ARGUMENT), 1);
+  }
+  if (warp == FB_SOFTMAX_WARPS + 1) {
+    tc05::tc_fence_after_sync();
+    tc05::tmem_dealloc(tmem_s, FB_TMEM_COLS);
+  }
+}
+
+// delta[b,h,t] = sum_j dO[b,t,h,j] * O[b,t,h,j]; one warp per (row, head).
+__global__ void attention_delta_kernel(const __nv_bfloat16* __restrict__ out, long long ld_out,
+                                       const __nv_bfloat16* __restrict__ dout, long long ld_dout,
+                                       float* __restrict__ delta, int B, int T, int H) {
+  const int lane = threadIdx.x & 31;
+  const long long w = blockIdx.x * (long long)(blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (w >= (long long)B * T * H) return;
+  const int h = (int)(w % H);
+  const long long row = w / H;  // b*T + t
+  const uint32_t o2 = *reinterpret_cast<const uint32_t*>(out + row * ld_out + h * FB_HD + lane * 2);
+  const uint32_t d2 = *reinterpret_cast<const uint32_t*>(dout + row * ld_dout + h * FB_HD + lane * 2);
+  const float2 of = unpack_bf16x2(o2), df = unpack_bf16x2(d2);
+  const float s = warp_sum(of.x * df.x + of.y * df.y);
+  if (lane == 0) {
+    const int b = (int)(row / T), t = (int)(row % T);
+    delta[((size_t)b * H + h) * T + t] = s;
+  }
+}
+
+__global__ void dq_to_bf16_kernel(const float* __restrict__ acc, long long ld_acc, __nv_bfloat16* __restrict__ dq,
+                                  long long ld_dq, long long rows, int cols) {
+  const long long quads = rows * (cols / 4);
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < quads; i += (long long)gridDim.x * blockDim.x) {
+    const long long row = i / (cols / 4);
+    const int c = (int)(i % (cols / 4)) * 4;
+    const float4 v = *reinterpret_cast<const float4*>(acc + row * ld_acc + c);
+    *reinterpret_cast<uint2*>(dq + row * ld_dq + c) = make_uint2(pack_bf16x2(v.x, v.y), pack_bf16x2(v.z, v.w));
+  }
+}
+
+}  // namespace
+
+size_t flash_attention_backward_scratch_bytes(int batch, int time, int n_heads, int head_dim) {
+  const size_t rows = (size_t)batch * time;
+  return sizeof(float) * rows * n_heads * head_dim + sizeof(float) * rows * n_heads + 256;
+}
+
+int flash_attention_backward_impl(hl_ctx* ctx, const void* q, const void* k, const void* v, long long ld_qkv,
+                                  const void* out, long long ld_out, const void* dout, long long ld_dout,
+                                  const float* lse, void* dq, void* dk, void* dv, long long ld_dqkv, int batch, int time,
+                                  int n_heads, int head_dim, void* scratch, size_t scratch_bytes) {
+  HL_REQUIRE(ctx && q && k && v && out && dout && lse && dq && dk && dv, "hl_flash_attention_backward: null argument");
+  HL_REQUIRE(n_heads > 0 && batch > 0 && time > 0, "hl_flash_attention_backward: sizes must be positive");
+  HL_REQUIRE(head_dim == FB_HD, "hl_flash_attention_backward: head_dim must be 64");
+  const long long C = (long long)n_heads * head_dim;
+  HL_REQUIRE(ld_qkv % 8 == 0 && ld_out % 8 == 0 && ld_dout % 8 == 0 && ld_dqkv % 8 == 0 && ld_qkv >= C && ld_out >= C &&
+                 ld_dout >= C && ld_dqkv >= C,
+             "hl_flash_attention_backward: row strides must be multiples of 8 and cover all heads");
+  HL_REQUIRE(((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v) |
+               reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(dout) | reinterpret_cast<uintptr_t>(dq) |
+               reinterpret_cast<uintptr_t>(dk) | reinterpret_cast<uintptr_t>(dv)) & 15) == 0,
+             "hl_flash_attention_backward: pointers must be 16-byte aligned");
+  const size_t rows = (size_t)batch * time;
+  HL_REQUIRE(scratch && scratch_bytes >= flash_attention_backward_scratch_bytes(batch, time, n_heads, head_dim),
+             "hl_flash_attention_backward: scratch is too small");
+  float* dq_accum = reinterpret_cast<float*>(scratch);
+  float* delta = dq_accum + rows * C;
+  HL_CUDA(cudaMemsetAsync(dq_accum, 0, sizeof(float) * rows * C, ctx->stream));
+  {
+    const long long warps = (long long)rows * n_heads;
+    attention_delta_kernel<<<(unsigned)ceil_div_ll(warps, 8), 256, 0, ctx->stream>>>(
+        reinterpret_cast<const __nv_bfloat16*>(out), ld_out, reinterpret_cast<const __nv_bfloat16*>(dout), ld_dout,
+        delta, batch, time, n_heads);
+    HL_LAUNCH_CHECK("attention_delta_kernel");
+  }
+  CUtensorMap mq, mk, mv, mdo;
+  int rc;
+  if ((rc = make_tensor_map_bf16_2d(&mq, q, (uint64_t)C, rows, (uint64_t)ld_qkv, FB_HD, FB_BM)) != HL_OK) return rc;
+  if ((rc = make_tensor_map_bf16_2d(&mk, k, (uint64_t)C, rows, (uint64_t)ld_qkv, FB_HD, FB_BN)) != HL_OK) return rc;
+  if ((rc = make_tensor_map_bf16_2d(&mv, v, (uint64_t)C, rows, (uint64_t)ld_qkv, FB_HD, FB_BN)) != HL_OK) return rc;
+  if ((rc = make_tensor_map_bf16_2d(&mdo, dout, (uint64_t)C, rows, (uint64_t)ld_dout, FB_HD, FB_BM)) != HL_OK) return rc;
+  FbParams p{};
+  p.B = batch; p.T = time; p.H = n_heads;
+  p.lse = lse; p.delta = delta;
+  p.dq_accum = dq_accum; p.ld_dq = C;
+  p.dk = reinterpret_cast<__nv_bfloat16*>(dk);
+  p.dv = reinterpret_cast<__nv_bfloat16*>(dv);
+  p.ld_dkv = ld_dqkv;
+  p.scale = 1.0f / sqrtf((float)head_dim);
+  p.scale_log2 = p.scale * 1.4426950408889634f;
+  p.status = ctx->status_dev;
+  static bool configured = false;
+  if (!configured) {
+    HL_CUDA(cudaFuncSetAttribute(flash_attention_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, FB_SMEM_BYTES));
+    configured = true;
+  }
+  const int nq = ceil_div(time, FB_BM);
+  flash_attention_bwd_kernel<<<nq * batch * n_heads, FB_THREADS, FB_SMEM_BYTES, ctx->stream>>>(mq, mk, mv, mdo, p);
+  HL_LAUNCH_CHECK("flash_attention_bwd_kernel");
+  {
+    const long long quads = (long long)rows * (C / 4);
+    const long long want = ceil_div_ll(quads, 256), cap = (long long)ctx->sm_count * 8;
+    dq_to_bf16_kernel<<<(unsigned)(want < cap ? want : cap), 256, 0, ctx->stream>>>(
+        dq_accum, C, reinterpret_cast<__nv_bfloat16*>(dq), ld_dqkv, (long long)rows, (int)C);
+    HL_LAUNCH_CHECK("dq_to_bf16_kernel");
+  }
+  count_launch(ctx, 3);
+  ctx->counters.attention_launches += 1;
+  return HL_OK;
+}
+
+}  // namespace hl
+
+extern "C" int hl_flash_attention_backward(hl_ctx* ctx, const void* q, const void* k, const void* v, long long ld_qkv,
+                                           const void* out, long long ld_out, const void* dout, long long ld_dout,
+                                           const float* lse, void* dq, void* dk, void* dv, long long ld_dqkv, int batch,
+                                           int time, int n_heads, int head_dim) {
+  if (!ctx) return hl::fail("hl_flash_attention_backward: null context");
+  if (batch <= 0 || time <= 0 || n_heads <= 0 || head_dim <= 0)
+    return hl::fail("hl_flash_attention_backward: sizes must be positive");
+  const size_t need = hl::flash_attention_backward_scratch_bytes(batch, time, n_heads, head_dim);
+  int rc = hl::ensure_workspace(ctx, need);
+  if (rc != HL_OK) return rc;
+  return hl::flash_attention_backward_impl(ctx, q, k, v, ld_qkv, out, ld_out, dout, ld_dout, lse, dq, dk, dv, ld_dqkv,
+                                           batch, time, n_heads, head_dim, ctx->workspace, ctx->workspace_bytes);
+}

@@ -288,3 +288,15 @@ def flash_attention_forward(ctx: Context, q, k, v, batch: int, time: int, n_head
                                              c_longlong(out.stride(0)), _p(lse), c_int(batch), c_int(time),
                                              c_int(n_heads), c_int(C // n_heads)))
     return out, lse
+
+
+def flash_attention_backward(ctx: Context, q, k, v, out, dout, lse, batch: int, time: int, n_heads: int):
+    """Returns one fused bf16 gradient buffer `[batch*time, 3C]` holding dq | dk | dv."""
+    C = q.shape[1]
+    dqkv = torch.empty(batch * time, 3 * C, dtype=torch.bfloat16, device=q.device)
+    dq, dk, dv = dqkv[:, :C], dqkv[:, C:2 * C], dqkv[:, 2 * C:]
+    check(ctx.lib.hl_flash_attention_backward(
+        ctx.handle, _p(q), _p(k), _p(v), c_longlong(q.stride(0)), _p(out), c_longlong(out.stride(0)), _p(dout),
+        c_longlong(dout.stride(0)), _p(lse), _p(dq), _p(dk), _p(dv), c_longlong(dqkv.stride(0)), c_int(batch),
+        c_int(time), c_int(n_heads), c_int(C // n_heads)))
+    return dqkv

@@ -228,6 +228,18 @@ int hl_flash_attention_forward(hl_ctx* ctx, const void* q, const void* k, const 
                                void* out, long long ld_out, float* lse, int batch, int time, int n_heads,
                                int head_dim);
 
+/* Backward of hl_flash_attention_forward: recomputes P from q, k and lse, then
+ *   dV = P^T dO, dP = dO V^T, dS = P*(dP - rowsum(dO*O))*scale, dQ = dS K, dK = dS^T Q
+ * with bf16 operands and f32 accumulation (src/tensor/autograd.rs:1626-1914,
+ * tensor_core.ptx:3111-4407).  out/dout: bf16 [batch*time, C]; dq, dk, dv: bf16 views with row
+ * stride ld_dqkv (may be column slices of one fused gradient buffer).  dK and dV are summed in
+ * tensor memory in a fixed order; dQ tiles are summed with f32 reductions whose order is not
+ * fixed.  Uses the context's scratch arena (f32 dQ accumulator and row sums). */
+int hl_flash_attention_backward(hl_ctx* ctx, const void* q, const void* k, const void* v, long long ld_qkv,
+                                const void* out, long long ld_out, const void* dout, long long ld_dout,
+                                const float* lse, void* dq, void* dk, void* dv, long long ld_dqkv, int batch,
+                                int time, int n_heads, int head_dim);
+
 #ifdef __cplusplus
 }
 #endif

@@ -45,3 +45,28 @@ def test_flash_forward_rejects_unsupported_shapes():
     x = c.zeros((128, 96), torch.bfloat16)
     with pytest.raises(HeirloomError, match="head_dim must be 64"):
         cuda.flash_attention_forward(c, x, x, x, 1, 128, 3)
+
+
+@pytest.mark.parametrize("B,T,H", [(1, 128, 1), (2, 256, 2), (1, 200, 2), (1, 1024, 2), (2, 72, 3)])
+def test_flash_backward_matches_oracle(B, T, H):
+    from heirloom_b200 import cuda
+    c = ctx()
+    C = 64 * H
+    rng = np.random.default_rng(B * 77 + T + H)
+    qkv = ho.bf16_round(rng.standard_normal((B * T, 3 * C)))
+    go = ho.bf16_round(rng.standard_normal((B * T, C)))
+    fused = dev(qkv, torch.bfloat16)
+    q, k, v = fused[:, :C], fused[:, C:2 * C], fused[:, 2 * C:]
+    out, lse = cuda.flash_attention_forward(c, q, k, v, B, T, H)
+    dqkv = cuda.flash_attention_backward(c, q, k, v, out, dev(go, torch.bfloat16), lse, B, T, H)
+    got = host(dqkv)
+    qn, kn, vn = (qkv[:, i * C:(i + 1) * C].reshape(B, T, C) for i in range(3))
+    want = ho.causal_attention_backward(qn, kn, vn, H, go.reshape(B, T, C), bf16_operands=True)
+    for i, name in enumerate(("dq", "dk", "dv")):
+        w = want[i].reshape(B * T, C)
+        g = got[:, i * C:(i + 1) * C]
+        scale = np.abs(w).max()
+        # bf16 operands on both sides; rounding of P/dS happens against slightly different f32
+        # values, so compare at a few bf16 ulps of the tensor's scale
+        assert_close("flash " + name, g, w, atol=scale * 2 ** -6, rtol=2 ** -5)
+        assert np.abs(g - w).mean() <= scale * 2 ** -9
