@@ -1,0 +1,41 @@
+// Internal entry points shared between translation units: the same kernels the C ABI exposes,
+// with scratch memory passed explicitly so the step executor can plan it once.
+#pragma once
+#include "common.cuh"
+
+namespace hl {
+
+size_t gemm_splitk_workspace_bytes(const hl_gemm_desc* d, int sm_count, int* splits_out);
+int gemm_bf16_run(hl_ctx* ctx, const hl_gemm_desc* d, const void* a, const void* b, void* c, const float* bias,
+                  const void* aux_in, void* aux_out, float* workspace, size_t workspace_bytes);
+
+int bias_grad_impl(hl_ctx* ctx, const void* grad_out, int dtype, float* grad_bias, int rows, int cols);
+
+int layer_norm_forward_impl(hl_ctx* ctx, const void* x, int x_dtype, const float* gamma, const float* beta, void* y,
+                            int y_dtype, float* mean, float* rstd, int rows, int features, float eps);
+int layer_norm_backward_impl(hl_ctx* ctx, const void* x, int x_dtype, const float* gamma, const float* dy,
+                             const float* mean, const float* rstd, const float* residual_grad, float* dx_f32,
+                             void* dx_bf16, float* dgamma, float* dbeta, int rows, int features);
+int cross_entropy_impl(hl_ctx* ctx, const float* logits, long long ld, const int64_t* targets, int rows, int classes,
+                       float grad_scale, float* loss_dev, float* row_loss, void* dlogits, int dlogits_dtype,
+                       long long ld_dlogits);
+
+int flash_attention_forward_impl(hl_ctx* ctx, const void* q, const void* k, const void* v, long long ld_qkv, void* out,
+                                 long long ld_out, float* lse, int batch, int time, int n_heads, int head_dim);
+size_t flash_attention_backward_scratch_bytes(int batch, int time, int n_heads, int head_dim);
+int flash_attention_backward_impl(hl_ctx* ctx, const void* q, const void* k, const void* v, long long ld_qkv,
+                                  const void* out, long long ld_out, const void* dout, long long ld_dout,
+                                  const float* lse, void* dq, void* dk, void* dv, long long ld_dqkv, int batch, int time,
+                                  int n_heads, int head_dim, void* scratch, size_t scratch_bytes);
+
+struct AdamPlan;
+int adam_plan_create(hl_ctx* ctx, const hl_adamw_tensor* tensors, int count, AdamPlan** out);
+void adam_plan_destroy(AdamPlan* plan);
+int adam_plan_step(hl_ctx* ctx, AdamPlan* plan, const hl_adamw_params* hp);
+
+// NCCL (loaded at run time); see nccl_ddp.cu.
+int nccl_allreduce_sum_f32(hl_ctx* ctx, float* buf, size_t count, cudaStream_t stream);
+bool nccl_active(const hl_ctx* ctx);
+int nccl_world(const hl_ctx* ctx);
+
+}  // namespace hl

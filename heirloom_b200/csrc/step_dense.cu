@@ -1,0 +1,565 @@
+// Training-step executor for the dense pre-LayerNorm decoder LM: forward, backward, bucketed
+// gradient all-reduce overlapped with backward, and the fused AdamW update, on preplanned
+// arenas.  It reproduces the reference's AMP-bf16 dataflow
+//   MemoryTransformerLm::forward_amp_bf16 / loss_amp_bf16 (src/memory_transformer.rs:1636-1670),
+//   block (src/memory_transformer.rs:1153-1172), attention (src/nn.rs:718-788),
+//   feed-forward (src/nn.rs:873-884), Linear (src/nn.rs:338-450),
+//   backward operand rounding (src/tensor/autograd.rs:593-851),
+//   AdamW::step_mut (src/nn.rs:2156-2220) and the data-parallel exchange
+//   AdamW::all_reduce_cuda_gradients_nccl (src/nn.rs:2083-2138)
+// with every bf16 round trip of that path realised as "store the activation in bf16".
+//
+// Parameters live in one flat f32 arena (plus f32 gradients, AdamW moments and a bf16 shadow
+// used as GEMM operands), ordered by the time their gradient becomes final in backward
+// (lm_head first, embeddings last) so that fixed-size buckets of the gradient arena can be
+// all-reduced on the collective stream while backward is still running.
+#include <cstring>
+#include <string>
+#include <vector>
+
+#include "kernels.h"
+
+namespace hl {
+namespace {
+
+constexpr size_t kAlignElems = 64;
+inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+struct Slot {
+  std::string name;
+  size_t offset, numel;
+  int rank;
+  long long shape[2];
+};
+
+struct LayerOffsets {
+  size_t w2, b2, w1, b1, ln2g, ln2b, wo, bo, wqkv, bqkv, ln1g, ln1b;
+};
+
+struct LayerActs {
+  __nv_bfloat16 *a, *qkv, *o, *r, *c, *h, *g;
+  float *lse, *mean1, *rstd1, *mean2, *rstd2;
+};
+
+}  // namespace
+}  // namespace hl
+
+using namespace hl;
+
+struct hl_decoder {
+  hl_ctx* ctx = nullptr;
+  hl_decoder_config cfg{};
+  int N = 0;
+  // parameter arenas
+  size_t arena = 0;
+  float *params = nullptr, *grads = nullptr, *m = nullptr, *v = nullptr;
+  __nv_bfloat16* shadow = nullptr;
+  std::vector<Slot> slots;  // state-dict order
+  size_t off_head_w = 0, off_head_b = 0, off_lnf_g = 0, off_lnf_b = 0, off_pos = 0, off_tok = 0;
+  std::vector<LayerOffsets> lo;
+  // activations
+  uint8_t* act_arena = nullptr;
+  size_t act_bytes = 0;
+  std::vector<__nv_bfloat16*> x;  // x[l] is the input of block l; x[L] the final residual stream
+  std::vector<LayerActs> la;
+  __nv_bfloat16 *z = nullptr, *dlogits = nullptr, *dxb = nullptr, *dh = nullptr, *dob = nullptr, *dqkv = nullptr;
+  float *logits = nullptr, *meanf = nullptr, *rstdf = nullptr, *dx0 = nullptr, *dx1 = nullptr, *dtmp = nullptr;
+  int64_t *tokens = nullptr, *targets = nullptr;
+  float* loss_dev = nullptr;
+  float* loss_host = nullptr;  // pinned
+  float* norm_dev = nullptr;
+  float* norm_host = nullptr;  // pinned
+  // optimizer
+  bool has_opt = false;
+  hl_adamw_config opt{};
+  long long step = 0;
+  AdamPlan* plan = nullptr;
+  // data-parallel buckets over the gradient arena
+  size_t bucket_elems = 6553600;  // 25 MiB of f32
+  size_t next_bucket = 0, n_buckets = 0;
+  std::vector<cudaEvent_t> bucket_ready;
+  cudaEvent_t comm_done = nullptr;
+  unsigned long long launches_last_step = 0;
+};
+
+namespace hl {
+namespace {
+
+// Lays the parameters out in gradient-completion order and records the name -> slice map in
+// the reference's state-dict order (src/memory_transformer.rs:2098-2117).
+void plan_parameters(hl_decoder* m) {
+  const hl_decoder_config& c = m->cfg;
+  const long long d = c.d_model, F = c.d_ff, V = c.vocab, T = c.context;
+  size_t cur = 0;
+  std::vector<Slot> tmp;
+  auto add = [&](const std::string& name, size_t numel, int rank, long long s0, long long s1) {
+    const size_t off = cur;
+    cur = align_up(cur + numel, kAlignElems);
+    tmp.push_back(Slot{name, off, numel, rank, {s0, s1}});
+    return off;
+  };
+  m->off_head_w = add("lm_head.weight", (size_t)V * d, 2, V, d);
+  m->off_head_b = add("lm_head.bias", (size_t)V, 1, V, 0);
+  m->off_lnf_g = add("ln_f.weight", (size_t)d, 1, d, 0);
+  m->off_lnf_b = add("ln_f.bias", (size_t)d, 1, d, 0);
+  m->lo.resize(c.n_layers);
+  for (int l = c.n_layers - 1; l >= 0; --l) {
+    const std::string b = "block." + std::to_string(l) + ".";
+    LayerOffsets& o = m->lo[l];
+    o.w2 = add(b + "feed_forward.dense.fc2.weight", (size_t)d * F, 2, d, F);
+    o.b2 = add(b + "feed_forward.dense.fc2.bias", (size_t)d, 1, d, 0);
+    o.w1 = add(b + "feed_forward.dense.fc1.weight", (size_t)F * d, 2, F, d);
+    o.b1 = add(b + "feed_forward.dense.fc1.bias", (size_t)F, 1, F, 0);
+    o.ln2g = add(b + "ln2.weight", (size_t)d, 1, d, 0);
+    o.ln2b = add(b + "ln2.bias", (size_t)d, 1, d, 0);
+    o.wo = add(b + "attention.out_proj.weight", (size_t)d * d, 2, d, d);
+    o.bo = add(b + "attention.out_proj.bias", (size_t)d, 1, d, 0);
+    // q, k, v are three reference Linears stored back to back so one [3d, d] GEMM serves them
+    o.wqkv = cur;
+    add(b + "attention.q_proj.weight", (size_t)d * d, 2, d, d);
+    cur = o.wqkv + (size_t)d * d;
+    add(b + "attention.k_proj.weight", (size_t)d * d, 2, d, d);
+    cur = o.wqkv + 2 * (size_t)d * d;
+    add(b + "attention.v_proj.weight", (size_t)d * d, 2, d, d);
+    o.bqkv = cur;
+    add(b + "attention.q_proj.bias", (size_t)d, 1, d, 0);
+    cur = o.bqkv + d;
+    add(b + "attention.k_proj.bias", (size_t)d, 1, d, 0);
+    cur = o.bqkv + 2 * d;
+    add(b + "attention.v_proj.bias", (size_t)d, 1, d, 0);
+    o.ln1g = add(b + "ln1.weight", (size_t)d, 1, d, 0);
+    o.ln1b = add(b + "ln1.bias", (size_t)d, 1, d, 0);
+  }
+  m->off_pos = add("position_embedding.weight", (size_t)T * d, 2, T, d);
+  m->off_tok = add("token_embedding.weight", (size_t)V * d, 2, V, d);
+  m->arena = cur;
+  // state-dict order
+  auto find = [&](const std::string& n) -> Slot {
+    for (const Slot& s : tmp) if (s.name == n) return s;
+    return Slot{};
+  };
+  m->slots.push_back(find("token_embedding.weight"));
+  m->slots.push_back(find("position_embedding.weight"));
+  for (int l = 0; l < c.n_layers; ++l) {
+    const std::string b = "block." + std::to_string(l) + ".";
+    for (const char* n : {"ln1.weight", "ln1.bias", "attention.q_proj.weight", "attention.q_proj.bias",
+                          "attention.k_proj.weight", "attention.k_proj.bias", "attention.v_proj.weight",
+                          "attention.v_proj.bias", "attention.out_proj.weight", "attention.out_proj.bias", "ln2.weight",
+                          "ln2.bias", "feed_forward.dense.fc1.weight", "feed_forward.dense.fc1.bias",
+                          "feed_forward.dense.fc2.weight", "feed_forward.dense.fc2.bias"})
+      m->slots.push_back(find(b + n));
+  }
+  for (const char* n : {"ln_f.weight", "ln_f.bias", "lm_head.weight", "lm_head.bias"}) m->slots.push_back(find(n));
+}
+
+template <typename T>
+T* carve(uint8_t*& cursor, size_t count) {
+  T* p = reinterpret_cast<T*>(cursor);
+  cursor += align_up(count * sizeof(T), 256);
+  return p;
+}
+
+int plan_activations(hl_decoder* m, bool measure_only, size_t* bytes_out) {
+  const hl_decoder_config& c = m->cfg;
+  const size_t N = (size_t)m->N, d = c.d_model, F = c.d_ff, V = c.vocab, L = c.n_layers;
+  uint8_t* cur = measure_only ? nullptr : m->act_arena;
+  uint8_t* base = cur;
+  m->x.resize(L + 1);
+  m->la.resize(L);
+  for (size_t l = 0; l <= L; ++l) m->x[l] = carve<__nv_bfloat16>(cur, N * d);
+  for (size_t l = 0; l < L; ++l) {
+    LayerActs& a = m->la[l];
+    a.a = carve<__nv_bfloat16>(cur, N * d);
+    a.qkv = carve<__nv_bfloat16>(cur, N * 3 * d);
+    a.o = carve<__nv_bfloat16>(cur, N * d);
+    a.r = carve<__nv_bfloat16>(cur, N * d);
+    a.c = carve<__nv_bfloat16>(cur, N * d);
+    a.h = carve<__nv_bfloat16>(cur, N * F);
+    a.g = carve<__nv_bfloat16>(cur, N * F);
+    a.lse = carve<float>(cur, N * c.n_heads);
+    a.mean1 = carve<float>(cur, N);
+    a.rstd1 = carve<float>(cur, N);
+    a.mean2 = carve<float>(cur, N);
+    a.rstd2 = carve<float>(cur, N);
+  }
+  m->z = carve<__nv_bfloat16>(cur, N * d);
+  m->meanf = carve<float>(cur, N);
+  m->rstdf = carve<float>(cur, N);
+  m->logits = carve<float>(cur, N * V);
+  m->dlogits = carve<__nv_bfloat16>(cur, N * V);
+  m->dx0 = carve<float>(cur, N * d);
+  m->dx1 = carve<float>(cur, N * d);
+  m->dtmp = carve<float>(cur, N * d);
+  m->dxb = carve<__nv_bfloat16>(cur, N * d);
+  m->dh = carve<__nv_bfloat16>(cur, N * F);
+  m->dob = carve<__nv_bfloat16>(cur, N * d);
+  m->dqkv = carve<__nv_bfloat16>(cur, N * 3 * d);
+  m->tokens = carve<int64_t>(cur, N);
+  m->targets = carve<int64_t>(cur, N);
+  m->loss_dev = carve<float>(cur, 4);
+  m->norm_dev = carve<float>(cur, 4);
+  *bytes_out = (size_t)(cur - base);
+  return HL_OK;
+}
+
+struct Gemm {
+  hl_decoder* m;
+  int run(int M, int N, int K, const void* a, long long lda, int al, const void* b, long long ldb, int bl, void* c,
+          long long ldc, int out_dtype, int epi = HL_EPI_NONE, const float* bias = nullptr, const void* aux_in = nullptr,
+          long long ld_aux_in = 0, void* aux_out = nullptr, long long ld_aux_out = 0) const {
+    hl_gemm_desc d{};
+    d.m = M; d.n = N; d.k = K;
+    d.a_layout = al; d.b_layout = bl;
+    d.lda = lda; d.ldb = ldb; d.ldc = ldc;
+    d.epilogue = epi; d.out_dtype = out_dtype; d.split_k = 0;
+    d.ld_aux_in = ld_aux_in; d.ld_aux_out = ld_aux_out;
+    const size_t need = gemm_splitk_workspace_bytes(&d, m->ctx->sm_count, nullptr);
+    if (need > m->ctx->workspace_bytes) {
+      int rc = ensure_workspace(m->ctx, need);
+      if (rc != HL_OK) return rc;
+    }
+    return gemm_bf16_run(m->ctx, &d, a, b, c, bias, aux_in, aux_out, reinterpret_cast<float*>(m->ctx->workspace),
+                         m->ctx->workspace_bytes);
+  }
+};
+
+#define HL_TRY(expr)            \
+  do {                          \
+    int _rc = (expr);           \
+    if (_rc != HL_OK) return _rc; \
+  } while (0)
+
+int forward(hl_decoder* m) {
+  hl_ctx* ctx = m->ctx;
+  const hl_decoder_config& c = m->cfg;
+  const int N = m->N, d = c.d_model, F = c.d_ff, V = c.vocab, B = c.batch, T = c.context, H = c.n_heads;
+  const Gemm g{m};
+  const float* P = m->params;
+  const __nv_bfloat16* W = m->shadow;
+  HL_TRY(hl_embedding_forward(ctx, P + m->off_tok, V, m->tokens, P + m->off_pos, T, m->x[0], HL_BF16, N, d));
+  for (int l = 0; l < c.n_layers; ++l) {
+    const LayerOffsets& o = m->lo[l];
+    LayerActs& a = m->la[l];
+    HL_TRY(layer_norm_forward_impl(ctx, m->x[l], HL_BF16, P + o.ln1g, P + o.ln1b, a.a, HL_BF16, a.mean1, a.rstd1, N, d, 1e-5f));
+    HL_TRY(g.run(N, 3 * d, d, a.a, d, HL_K_MAJOR, W + o.wqkv, d, HL_K_MAJOR, a.qkv, 3 * d, HL_BF16, HL_EPI_BIAS, P + o.bqkv));
+    HL_TRY(flash_attention_forward_impl(ctx, a.qkv, a.qkv + d, a.qkv + 2 * d, 3 * d, a.o, d, a.lse, B, T, H, d / H));
+    HL_TRY(g.run(N, d, d, a.o, d, HL_K_MAJOR, W + o.wo, d, HL_K_MAJOR, a.r, d, HL_BF16, HL_EPI_BIAS_RESIDUAL, P + o.bo,
+                 m->x[l], d));
+    HL_TRY(layer_norm_forward_impl(ctx, a.r, HL_BF16, P + o.ln2g, P + o.ln2b, a.c, HL_BF16, a.mean2, a.rstd2, N, d, 1e-5f));
+    HL_TRY(g.run(N, F, d, a.c, d, HL_K_MAJOR, W + o.w1, d, HL_K_MAJOR, a.h, F, HL_BF16, HL_EPI_BIAS_GELU, P + o.b1, nullptr,
+                 0, a.g, F));
+    HL_TRY(g.run(N, d, F, a.g, F, HL_K_MAJOR, W + o.w2, F, HL_K_MAJOR, m->x[l + 1], d, HL_BF16, HL_EPI_BIAS_RESIDUAL,
+                 P + o.b2, a.r, d));
+  }
+  HL_TRY(layer_norm_forward_impl(ctx, m->x[c.n_layers], HL_BF16, P + m->off_lnf_g, P + m->off_lnf_b, m->z, HL_BF16, m->meanf,
+                                 m->rstdf, N, d, 1e-5f));
+  HL_TRY(g.run(N, V, d, m->z, d, HL_K_MAJOR, W + m->off_head_w, d, HL_K_MAJOR, m->logits, V, HL_F32, HL_EPI_BIAS,
+               P + m->off_head_b));
+  return HL_OK;
+}
+
+// Queue the all-reduce of every bucket whose gradients are final.
+int flush_buckets(hl_decoder* m, size_t done_elems) {
+  if (!nccl_active(m->ctx)) return HL_OK;
+  while (m->next_bucket < m->n_buckets) {
+    const size_t start = m->next_bucket * m->bucket_elems;
+    const size_t end = std::min(start + m->bucket_elems, m->arena);
+    if (end > done_elems) break;
+    HL_CUDA(cudaEventRecord(m->bucket_ready[m->next_bucket], m->ctx->stream));
+    HL_CUDA(cudaStreamWaitEvent(m->ctx->comm_stream, m->bucket_ready[m->next_bucket], 0));
+    HL_TRY(nccl_allreduce_sum_f32(m->ctx, m->grads + start, end - start, m->ctx->comm_stream));
+    m->next_bucket += 1;
+  }
+  return HL_OK;
+}
+
+int backward(hl_decoder* m) {
+  hl_ctx* ctx = m->ctx;
+  const hl_decoder_config& c = m->cfg;
+  const int N = m->N, d = c.d_model, F = c.d_ff, V = c.vocab, B = c.batch, T = c.context, H = c.n_heads;
+  const Gemm g{m};
+  const float* P = m->params;
+  const __nv_bfloat16* W = m->shadow;
+  float* G = m->grads;
+  m->next_bucket = 0;
+  // loss and dlogits = (softmax - onehot)/N in bf16, the operand precision of the next GEMMs
+  HL_TRY(cross_entropy_impl(ctx, m->logits, V, m->targets, N, V, 1.0f, m->loss_dev, nullptr, m->dlogits, HL_BF16, V));
+  // lm_head
+  HL_TRY(g.run(V, d, N, m->dlogits, V, HL_MN_MAJOR, m->z, d, HL_MN_MAJOR, G + m->off_head_w, d, HL_F32));
+  HL_TRY(bias_grad_impl(ctx, m->dlogits, HL_BF16, G + m->off_head_b, N, V));
+  HL_TRY(g.run(N, d, V, m->dlogits, V, HL_K_MAJOR, W + m->off_head_w, d, HL_MN_MAJOR, m->dtmp, d, HL_F32));
+  float* dx = m->dx0;
+  float* dx_next = m->dx1;
+  HL_TRY(layer_norm_backward_impl(ctx, m->x[c.n_layers], HL_BF16, P + m->off_lnf_g, m->dtmp, m->meanf, m->rstdf, nullptr, dx,
+                                  m->dxb, G + m->off_lnf_g, G + m->off_lnf_b, N, d));
+  HL_TRY(flush_buckets(m, m->off_lnf_b + d));
+  for (int l = c.n_layers - 1; l >= 0; --l) {
+    const LayerOffsets& o = m->lo[l];
+    LayerActs& a = m->la[l];
+    // y = r + fc2(gelu(fc1(c)));   dx is dL/dy (f32), dxb its bf16 operand copy
+    HL_TRY(g.run(d, F, N, m->dxb, d, HL_MN_MAJOR, a.g, F, HL_MN_MAJOR, G + o.w2, F, HL_F32));
+    HL_TRY(bias_grad_impl(ctx, dx, HL_F32, G + o.b2, N, d));
+    HL_TRY(g.run(N, F, d, m->dxb, d, HL_K_MAJOR, W + o.w2, F, HL_MN_MAJOR, m->dh, F, HL_BF16, HL_EPI_DGELU, nullptr, a.h, F));
+    HL_TRY(g.run(F, d, N, m->dh, F, HL_MN_MAJOR, a.c, d, HL_MN_MAJOR, G + o.w1, d, HL_F32));
+    HL_TRY(bias_grad_impl(ctx, m->dh, HL_BF16, G + o.b1, N, F));
+    HL_TRY(g.run(N, d, F, m->dh, F, HL_K_MAJOR, W + o.w1, d, HL_MN_MAJOR, m->dtmp, d, HL_F32));
+    // dr = dx + LN2'(dc)
+    HL_TRY(layer_norm_backward_impl(ctx, a.r, HL_BF16, P + o.ln2g, m->dtmp, a.mean2, a.rstd2, dx, dx_next, m->dxb,
+                                    G + o.ln2g, G + o.ln2b, N, d));
+    std::swap(dx, dx_next);  // dx is now dL/dr
+    HL_TRY(g.run(d, d, N, m->dxb, d, HL_MN_MAJOR, a.o, d, HL_MN_MAJOR, G + o.wo, d, HL_F32));
+    HL_TRY(bias_grad_impl(ctx, dx, HL_F32, G + o.bo, N, d));
+    HL_TRY(g.run(N, d, d, m->dxb, d, HL_K_MAJOR, W + o.wo, d, HL_MN_MAJOR, m->dob, d, HL_BF16));
+    {
+      const size_t need = flash_attention_backward_scratch_bytes(B, T, H, d / H);
+      if (need > ctx->workspace_bytes) HL_TRY(ensure_workspace(ctx, need));
+      HL_TRY(flash_attention_backward_impl(ctx, a.qkv, a.qkv + d, a.qkv + 2 * d, 3 * d, a.o, d, m->dob, d, a.lse, m->dqkv,
+                                           m->dqkv + d, m->dqkv + 2 * d, 3 * d, B, T, H, d / H, ctx->workspace,
+                                           ctx->workspace_bytes));
+    }
+    HL_TRY(g.run(3 * d, d, N, m->dqkv, 3 * d, HL_MN_MAJOR, a.a, d, HL_MN_MAJOR, G + o.wqkv, d, HL_F32));
+    HL_TRY(bias_grad_impl(ctx, m->dqkv, HL_BF16, G + o.bqkv, N, 3 * d));
+    HL_TRY(g.run(N, d, 3 * d, m->dqkv, 3 * d, HL_K_MAJOR, W + o.wqkv, d, HL_MN_MAJOR, m->dtmp, d, HL_F32));
+    // dx_in = dr + LN1'(da)
+    HL_TRY(layer_norm_backward_impl(ctx, m->x[l], HL_BF16, P + o.ln1g, m->dtmp, a.mean1, a.rstd1, dx, dx_next, m->dxb,
+                                    G + o.ln1g, G + o.ln1b, N, d));
+    std::swap(dx, dx_next);
+    HL_TRY(flush_buckets(m, o.ln1b + d));
+  }
+  // embeddings: scatter-add into zeroed tables
+  HL_CUDA(cudaMemsetAsync(G + m->off_pos, 0, sizeof(float) * (m->arena - m->off_pos), ctx->stream));
+  HL_TRY(hl_embedding_backward(ctx, dx, m->tokens, G + m->off_tok, V, G + m->off_pos, T, N, d));
+  HL_TRY(flush_buckets(m, m->arena));
+  if (nccl_active(ctx)) {
+    HL_CUDA(cudaEventRecord(m->comm_done, ctx->comm_stream));
+    HL_CUDA(cudaStreamWaitEvent(ctx->stream, m->comm_done, 0));
+  }
+  return HL_OK;
+}
+
+int optimizer_step(hl_decoder* m) {
+  HL_REQUIRE(m->has_opt, "hl_decoder: no optimizer configured (call hl_decoder_set_optimizer)");
+  hl_ctx* ctx = m->ctx;
+  const int world = nccl_world(ctx);
+  const float inv_world = 1.0f / (float)world;  // sum then scale by 1/world (src/nn.rs:2100-2117)
+  double clip = 1.0;
+  if (m->opt.clip_norm > 0.f) {
+    // global gradient norm after averaging; forces one device-to-host read like the reference
+    HL_TRY(hl_sum_squares_f32(ctx, m->grads, m->arena, m->norm_dev));
+    HL_CUDA(cudaMemcpyAsync(m->norm_host, m->norm_dev, sizeof(float), cudaMemcpyDeviceToHost, ctx->stream));
+    HL_CUDA(cudaStreamSynchronize(ctx->stream));
+    const double sum_sq = (double)m->norm_host[0] * (double)inv_world * (double)inv_world;
+    if (!(sum_sq >= 0.0) || sum_sq > 1e300) return fail("non-finite or negative global gradient sum-of-squares");
+    const double norm = sqrt(sum_sq);
+    if (norm > (double)m->opt.clip_norm) clip = (double)m->opt.clip_norm / (norm + 1e-12);
+  }
+  m->step += 1;
+  hl_adamw_params hp{};
+  hp.lr = m->opt.lr; hp.beta1 = m->opt.beta1; hp.beta2 = m->opt.beta2; hp.eps = m->opt.eps;
+  hp.weight_decay = m->opt.weight_decay;
+  hp.clip_scale = (float)clip * inv_world;
+  hp.bias_correction1 = (float)(1.0 - pow((double)m->opt.beta1, (double)m->step));
+  hp.bias_correction2 = (float)(1.0 - pow((double)m->opt.beta2, (double)m->step));
+  return adam_plan_step(ctx, m->plan, &hp);
+}
+
+int refresh_shadow(hl_decoder* m, size_t offset, size_t numel) {
+  return hl_cast(m->ctx, m->params + offset, HL_F32, m->shadow + offset, HL_BF16, numel);
+}
+
+}  // namespace
+}  // namespace hl
+
+extern "C" {
+
+int hl_decoder_create(hl_ctx* ctx, const hl_decoder_config* cfg, hl_decoder** out) {
+  HL_REQUIRE(ctx && cfg && out, "hl_decoder_create: null argument");
+  *out = nullptr;
+  HL_REQUIRE(cfg->vocab > 0 && cfg->d_model > 0 && cfg->n_layers > 0 && cfg->n_heads > 0 && cfg->d_ff > 0 &&
+                 cfg->context > 0 && cfg->batch > 0,
+             "hl_decoder_create: every size must be positive");
+  HL_REQUIRE(cfg->d_model % cfg->n_heads == 0, "hl_decoder_create: d_model must be divisible by n_heads");
+  HL_REQUIRE(cfg->precision == HL_PRECISION_AMP_BF16, "hl_decoder_create: only the amp-bf16 route is available here");
+  HL_REQUIRE(cfg->d_model / cfg->n_heads == 64, "hl_decoder_create: the bf16 route needs head_dim 64");
+  HL_REQUIRE(cfg->d_model % 8 == 0 && cfg->d_ff % 8 == 0 && cfg->vocab % 8 == 0 && cfg->d_model <= 1024,
+             "hl_decoder_create: d_model (<= 1024), d_ff and vocab must be multiples of 8");
+  hl_decoder* m = new hl_decoder();
+  m->ctx = ctx;
+  m->cfg = *cfg;
+  m->N = cfg->batch * cfg->context;
+  plan_parameters(m);
+  auto cleanup = [&](int rc) { hl_decoder_destroy(m); return rc; };
+  cudaError_t e;
+  const size_t fb = sizeof(float) * m->arena;
+#define HL_ALLOC(ptr, bytes)                                              \
+  e = cudaMalloc(reinterpret_cast<void**>(&(ptr)), (bytes));               \
+  if (e != cudaSuccess) return cleanup(fail_cuda(e, "cudaMalloc(" #ptr ")"));
+  HL_ALLOC(m->params, fb)
+  HL_ALLOC(m->grads, fb)
+  HL_ALLOC(m->m, fb)
+  HL_ALLOC(m->v, fb)
+  HL_ALLOC(m->shadow, sizeof(__nv_bfloat16) * m->arena)
+  size_t act = 0;
+  plan_activations(m, true, &act);
+  m->act_bytes = act;
+  HL_ALLOC(m->act_arena, act)
+#undef HL_ALLOC
+  plan_activations(m, false, &act);
+  cudaMemsetAsync(m->params, 0, fb, ctx->stream);
+  cudaMemsetAsync(m->grads, 0, fb, ctx->stream);
+  cudaMemsetAsync(m->m, 0, fb, ctx->stream);
+  cudaMemsetAsync(m->v, 0, fb, ctx->stream);
+  cudaMemsetAsync(m->shadow, 0, sizeof(__nv_bfloat16) * m->arena, ctx->stream);
+  e = cudaMallocHost(reinterpret_cast<void**>(&m->loss_host), 64);
+  if (e != cudaSuccess) return cleanup(fail_cuda(e, "cudaMallocHost"));
+  m->norm_host = m->loss_host + 8;
+  hl_adamw_tensor whole{m->params, m->grads, m->m, m->v, m->shadow, (uint64_t)m->arena};
+  int rc = adam_plan_create(ctx, &whole, 1, &m->plan);
+  if (rc != HL_OK) return cleanup(rc);
+  m->n_buckets = (m->arena + m->bucket_elems - 1) / m->bucket_elems;
+  m->bucket_ready.resize(m->n_buckets);
+  for (auto& ev : m->bucket_ready) {
+    e = cudaEventCreateWithFlags(&ev, cudaEventDisableTiming);
+    if (e != cudaSuccess) return cleanup(fail_cuda(e, "cudaEventCreate"));
+  }
+  e = cudaEventCreateWithFlags(&m->comm_done, cudaEventDisableTiming);
+  if (e != cudaSuccess) return cleanup(fail_cuda(e, "cudaEventCreate"));
+  e = cudaStreamSynchronize(ctx->stream);
+  if (e != cudaSuccess) return cleanup(fail_cuda(e, "cudaStreamSynchronize"));
+  ctx->counters.allocations += 6;
+  ctx->counters.allocated_bytes += 4 * fb + sizeof(__nv_bfloat16) * m->arena + act;
+  *out = m;
+  return HL_OK;
+}
+
+void hl_decoder_destroy(hl_decoder* m) {
+  if (!m) return;
+  if (m->ctx) {
+    cudaStreamSynchronize(m->ctx->stream);
+    cudaStreamSynchronize(m->ctx->comm_stream);
+  }
+  for (auto ev : m->bucket_ready) if (ev) cudaEventDestroy(ev);
+  if (m->comm_done) cudaEventDestroy(m->comm_done);
+  adam_plan_destroy(m->plan);
+  cudaFree(m->params); cudaFree(m->grads); cudaFree(m->m); cudaFree(m->v); cudaFree(m->shadow); cudaFree(m->act_arena);
+  if (m->loss_host) cudaFreeHost(m->loss_host);
+  delete m;
+}
+
+int hl_decoder_param_count(hl_decoder* m) { return m ? (int)m->slots.size() : 0; }
+
+int hl_decoder_param_info(hl_decoder* m, int index, char* name_out, size_t name_cap, long long* numel, int* rank,
+                          long long shape_out[2]) {
+  HL_REQUIRE(m, "hl_decoder_param_info: null model");
+  HL_REQUIRE(index >= 0 && index < (int)m->slots.size(), "hl_decoder_param_info: parameter index out of range");
+  const Slot& s = m->slots[index];
+  if (name_out && name_cap > 0) {
+    strncpy(name_out, s.name.c_str(), name_cap - 1);
+    name_out[name_cap - 1] = 0;
+  }
+  if (numel) *numel = (long long)s.numel;
+  if (rank) *rank = s.rank;
+  if (shape_out) { shape_out[0] = s.shape[0]; shape_out[1] = s.shape[1]; }
+  return HL_OK;
+}
+
+static int slot_io(hl_decoder* m, int index, long long numel, const Slot** out, const char* who) {
+  HL_REQUIRE(m, std::string(who) + ": null model");
+  HL_REQUIRE(index >= 0 && index < (int)m->slots.size(), std::string(who) + ": parameter index out of range");
+  const Slot& s = m->slots[index];
+  HL_REQUIRE(numel == (long long)s.numel, std::string(who) + ": parameter " + s.name + " has " + std::to_string(s.numel) +
+                                              " elements, got " + std::to_string(numel));
+  *out = &s;
+  return HL_OK;
+}
+
+int hl_decoder_set_param(hl_decoder* m, int index, const float* host, long long numel) {
+  const Slot* s;
+  HL_TRY(slot_io(m, index, numel, &s, "hl_decoder_set_param"));
+  HL_TRY(hl_memcpy_h2d(m->ctx, m->params + s->offset, host, sizeof(float) * s->numel));
+  return refresh_shadow(m, s->offset, s->numel);
+}
+
+int hl_decoder_get_param(hl_decoder* m, int index, float* host, long long numel) {
+  const Slot* s;
+  HL_TRY(slot_io(m, index, numel, &s, "hl_decoder_get_param"));
+  return hl_memcpy_d2h(m->ctx, host, m->params + s->offset, sizeof(float) * s->numel);
+}
+
+int hl_decoder_get_grad(hl_decoder* m, int index, float* host, long long numel) {
+  const Slot* s;
+  HL_TRY(slot_io(m, index, numel, &s, "hl_decoder_get_grad"));
+  return hl_memcpy_d2h(m->ctx, host, m->grads + s->offset, sizeof(float) * s->numel);
+}
+
+int hl_decoder_get_moments(hl_decoder* m, int index, float* m_host, float* v_host, long long numel) {
+  const Slot* s;
+  HL_TRY(slot_io(m, index, numel, &s, "hl_decoder_get_moments"));
+  HL_TRY(hl_memcpy_d2h(m->ctx, m_host, m->m + s->offset, sizeof(float) * s->numel));
+  return hl_memcpy_d2h(m->ctx, v_host, m->v + s->offset, sizeof(float) * s->numel);
+}
+
+int hl_decoder_set_optimizer(hl_decoder* m, const hl_adamw_config* opt) {
+  HL_REQUIRE(m && opt, "hl_decoder_set_optimizer: null argument");
+  HL_REQUIRE(opt->lr >= 0.f && opt->beta1 >= 0.f && opt->beta1 < 1.f && opt->beta2 >= 0.f && opt->beta2 < 1.f &&
+                 opt->eps > 0.f && opt->weight_decay >= 0.f,
+             "hl_decoder_set_optimizer: invalid AdamW hyper-parameters");
+  m->opt = *opt;
+  m->has_opt = true;
+  m->step = 0;
+  HL_CUDA(cudaMemsetAsync(m->m, 0, sizeof(float) * m->arena, m->ctx->stream));
+  HL_CUDA(cudaMemsetAsync(m->v, 0, sizeof(float) * m->arena, m->ctx->stream));
+  return HL_OK;
+}
+
+long long hl_decoder_optimizer_steps(hl_decoder* m) { return m ? m->step : 0; }
+
+int hl_decoder_forward_backward(hl_decoder* m, const int64_t* tokens_dev, const int64_t* targets_dev) {
+  HL_REQUIRE(m && tokens_dev && targets_dev, "hl_decoder_forward_backward: null argument");
+  const unsigned long long before = m->ctx->counters.launches;
+  if (tokens_dev != m->tokens)
+    HL_CUDA(cudaMemcpyAsync(m->tokens, tokens_dev, sizeof(int64_t) * m->N, cudaMemcpyDeviceToDevice, m->ctx->stream));
+  if (targets_dev != m->targets)
+    HL_CUDA(cudaMemcpyAsync(m->targets, targets_dev, sizeof(int64_t) * m->N, cudaMemcpyDeviceToDevice, m->ctx->stream));
+  HL_TRY(forward(m));
+  HL_TRY(backward(m));
+  m->launches_last_step = m->ctx->counters.launches - before;
+  return HL_OK;
+}
+
+int hl_decoder_optimizer_step(hl_decoder* m) {
+  HL_REQUIRE(m, "hl_decoder_optimizer_step: null model");
+  const unsigned long long before = m->ctx->counters.launches;
+  HL_TRY(optimizer_step(m));
+  m->launches_last_step += m->ctx->counters.launches - before;
+  return HL_OK;
+}
+
+int hl_decoder_train_step_device(hl_decoder* m, const int64_t* tokens_dev, const int64_t* targets_dev) {
+  HL_TRY(hl_decoder_forward_backward(m, tokens_dev, targets_dev));
+  return hl_decoder_optimizer_step(m);
+}
+
+int hl_decoder_train_step(hl_decoder* m, const int64_t* tokens_host, const int64_t* targets_host, float* loss_host) {
+  HL_REQUIRE(m && tokens_host && targets_host, "hl_decoder_train_step: null argument");
+  hl_ctx* ctx = m->ctx;
+  HL_CUDA(cudaMemcpyAsync(m->tokens, tokens_host, sizeof(int64_t) * m->N, cudaMemcpyHostToDevice, ctx->stream));
+  HL_CUDA(cudaMemcpyAsync(m->targets, targets_host, sizeof(int64_t) * m->N, cudaMemcpyHostToDevice, ctx->stream));
+  ctx->counters.h2d_bytes += 2 * sizeof(int64_t) * (size_t)m->N;
+  HL_TRY(hl_decoder_forward_backward(m, m->tokens, m->targets));
+  HL_TRY(hl_decoder_optimizer_step(m));
+  HL_CUDA(cudaMemcpyAsync(m->loss_host, m->loss_dev, sizeof(float), cudaMemcpyDeviceToHost, ctx->stream));
+  ctx->counters.d2h_bytes += sizeof(float);
+  HL_TRY(hl_ctx_sync(ctx));
+  if (loss_host) *loss_host = m->loss_host[0];
+  return HL_OK;
+}
+
+int hl_decoder_loss(hl_decoder* m, float* loss_host) {
+  HL_REQUIRE(m && loss_host, "hl_decoder_loss: null argument");
+  return hl_memcpy_d2h(m->ctx, loss_host, m->loss_dev, sizeof(float));
+}
+
+unsigned long long hl_decoder_launches_last_step(hl_decoder* m) { return m ? m->launches_last_step : 0; }
+
+}  // extern "C"

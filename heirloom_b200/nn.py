@@ -1,0 +1,161 @@
+"""Host-side mirror of the reference's model/optimizer surface for the training-step path.
+
+`DecoderLm` stands where the reference has `MemoryTransformerLm` with no memory layers plus
+its `AdamW` (src/memory_transformer.rs:1217-1261, src/nn.rs:1941-2220): named parameters in
+state-dict order, `loss`/`backward`/`step`, and a one-call `train_step`.  All arithmetic runs in
+`libheirloom_b200.so`; this file only moves bytes and names.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import POINTER, Structure, byref, c_char_p, c_float, c_int, c_longlong, c_size_t, c_void_p
+from dataclasses import dataclass
+from typing import Dict, List, Optional, Tuple
+
+import numpy as np
+import torch
+
+from ._lib import HeirloomError, check
+from .cuda import Context
+
+PRECISION_F32, PRECISION_AMP_BF16 = 0, 1
+
+
+class _DecoderConfig(Structure):
+    _fields_ = [(n, c_int) for n in ("vocab", "d_model", "n_layers", "n_heads", "d_ff", "context", "batch", "precision")]
+
+
+class _AdamWConfig(Structure):
+    _fields_ = [(n, c_float) for n in ("lr", "beta1", "beta2", "eps", "weight_decay", "clip_norm")]
+
+
+@dataclass
+class DecoderConfig:
+    vocab: int
+    d_model: int
+    n_layers: int
+    n_heads: int
+    d_ff: int
+    context: int
+    batch: int
+    precision: int = PRECISION_AMP_BF16
+
+
+class DecoderLm:
+    """N-layer pre-LayerNorm decoder LM living on one GPU (`hl_decoder`)."""
+
+    def __init__(self, ctx: Context, cfg: DecoderConfig):
+        self.ctx, self.cfg = ctx, cfg
+        self._lib = ctx.lib
+        self._lib.hl_decoder_launches_last_step.restype = ctypes.c_ulonglong
+        self._lib.hl_decoder_optimizer_steps.restype = c_longlong
+        self._lib.hl_decoder_destroy.restype = None
+        c = _DecoderConfig(cfg.vocab, cfg.d_model, cfg.n_layers, cfg.n_heads, cfg.d_ff, cfg.context, cfg.batch,
+                           cfg.precision)
+        h = c_void_p()
+        check(self._lib.hl_decoder_create(ctx.handle, byref(c), byref(h)))
+        self.handle = h
+        self._index: Dict[str, Tuple[int, Tuple[int, ...]]] = {}
+        for i in range(self._lib.hl_decoder_param_count(self.handle)):
+            name = ctypes.create_string_buffer(160)
+            numel, rank = c_longlong(), c_int()
+            shape = (c_longlong * 2)()
+            check(self._lib.hl_decoder_param_info(self.handle, c_int(i), name, c_size_t(160), byref(numel), byref(rank),
+                                                  shape))
+            self._index[name.value.decode()] = (i, tuple(int(shape[j]) for j in range(rank.value)))
+        self._pinned = None
+
+    def close(self) -> None:
+        if self.handle:
+            self._lib.hl_decoder_destroy(self.handle)
+            self.handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    # ---- parameters (Module::named_parameters, src/nn.rs:16-29) -----------------------------------
+    def parameter_names(self) -> List[str]:
+        return list(self._index)
+
+    def parameter_shapes(self) -> Dict[str, Tuple[int, ...]]:
+        return {n: s for n, (_, s) in self._index.items()}
+
+    def _slot(self, name: str):
+        if name not in self._index:
+            raise HeirloomError(f"no parameter named {name}")
+        return self._index[name]
+
+    def load_state_dict(self, state: Dict[str, np.ndarray]) -> None:
+        """Loads by name and shape like `load_state_dict` (src/nn.rs:2997-3038)."""
+        for name, (idx, shape) in self._index.items():
+            if name not in state:
+                raise HeirloomError(f"state dict is missing {name}")
+            arr = np.ascontiguousarray(state[name], dtype=np.float32)
+            if tuple(arr.shape) != shape:
+                raise HeirloomError(f"shape mismatch for {name}: expected {shape}, got {tuple(arr.shape)}")
+            check(self._lib.hl_decoder_set_param(self.handle, c_int(idx), arr.ctypes.data_as(c_void_p),
+                                                 c_longlong(arr.size)))
+
+    def _fetch(self, fn, name: str) -> np.ndarray:
+        idx, shape = self._slot(name)
+        out = np.empty(shape, np.float32)
+        check(fn(self.handle, c_int(idx), out.ctypes.data_as(c_void_p), c_longlong(out.size)))
+        return out
+
+    def parameter(self, name: str) -> np.ndarray:
+        return self._fetch(self._lib.hl_decoder_get_param, name)
+
+    def grad(self, name: str) -> np.ndarray:
+        return self._fetch(self._lib.hl_decoder_get_grad, name)
+
+    def moments(self, name: str) -> Tuple[np.ndarray, np.ndarray]:
+        idx, shape = self._slot(name)
+        m, v = np.empty(shape, np.float32), np.empty(shape, np.float32)
+        check(self._lib.hl_decoder_get_moments(self.handle, c_int(idx), m.ctypes.data_as(c_void_p),
+                                               v.ctypes.data_as(c_void_p), c_longlong(m.size)))
+        return m, v
+
+    def state_dict(self) -> Dict[str, np.ndarray]:
+        return {n: self.parameter(n) for n in self._index}
+
+    # ---- optimizer (AdamW, src/nn.rs:1941-2220) ----------------------------------------------------
+    def set_optimizer(self, lr=1e-3, beta1=0.9, beta2=0.999, eps=1e-8, weight_decay=0.01, clip_norm=None) -> None:
+        cfg = _AdamWConfig(lr, beta1, beta2, eps, weight_decay, clip_norm if clip_norm else 0.0)
+        check(self._lib.hl_decoder_set_optimizer(self.handle, byref(cfg)))
+
+    @property
+    def optimizer_steps(self) -> int:
+        return int(self._lib.hl_decoder_optimizer_steps(self.handle))
+
+    # ---- the step ----------------------------------------------------------------------------------
+    def forward_backward(self, tokens: torch.Tensor, targets: torch.Tensor) -> None:
+        """tokens/targets: int64 CUDA tensors `[batch, context]`."""
+        check(self._lib.hl_decoder_forward_backward(self.handle, c_void_p(tokens.data_ptr()),
+                                                    c_void_p(targets.data_ptr())))
+
+    def optimizer_step(self) -> None:
+        check(self._lib.hl_decoder_optimizer_step(self.handle))
+
+    def train_step_device(self, tokens: torch.Tensor, targets: torch.Tensor) -> None:
+        check(self._lib.hl_decoder_train_step_device(self.handle, c_void_p(tokens.data_ptr()),
+                                                     c_void_p(targets.data_ptr())))
+
+    def train_step(self, tokens_host: torch.Tensor, targets_host: torch.Tensor) -> float:
+        """The call a user makes: host int64 `[batch, context]` tensors (pinned for speed) in,
+        loss out."""
+        loss = c_float()
+        check(self._lib.hl_decoder_train_step(self.handle, c_void_p(tokens_host.data_ptr()),
+                                              c_void_p(targets_host.data_ptr()), byref(loss)))
+        return float(loss.value)
+
+    def loss(self) -> float:
+        out = c_float()
+        check(self._lib.hl_decoder_loss(self.handle, byref(out)))
+        return float(out.value)
+
+    @property
+    def launches_last_step(self) -> int:
+        return int(self._lib.hl_decoder_launches_last_step(self.handle))

@@ -240,6 +240,66 @@ int hl_flash_attention_backward(hl_ctx* ctx, const void* q, const void* k, const
                                 const float* lse, void* dq, void* dk, void* dv, long long ld_dqkv, int batch,
                                 int time, int n_heads, int head_dim);
 
+/* ---- NCCL data-parallel plumbing ------------------------------------------------------------
+ * Same surface as the reference's NcclUniqueId / NcclCommunicator (cuda.rs:305-349,
+ * :8049-8233): a 128-byte unique id made on one rank and handed to the others by the caller,
+ * init_rank, in-place f32 sum all-reduce, abort.  NCCL is opened at run time. */
+int hl_nccl_version(int* out);
+int hl_nccl_unique_id(unsigned char out[128]);
+int hl_nccl_init(hl_ctx* ctx, int rank, int world, const unsigned char id[128]);
+int hl_nccl_allreduce_f32(hl_ctx* ctx, float* buf_dev, size_t count);
+int hl_nccl_abort(hl_ctx* ctx);
+int hl_nccl_destroy(hl_ctx* ctx);
+
+/* ---- training step of the dense decoder LM --------------------------------------------------
+ * The reference's N-layer pre-LayerNorm decoder (MemoryTransformerLm without memory layers,
+ * src/memory_transformer.rs:1217-1261): learned positions, separate q/k/v/out projections with
+ * biases, GELU MLP, untied lm_head with bias, mean next-token cross-entropy, coupled AdamW.
+ * Parameter indices follow named_parameters order (src/memory_transformer.rs:2098-2117);
+ * hl_decoder_param_info returns the reference's names, so a state dict moves across unchanged. */
+enum { HL_PRECISION_F32 = 0, HL_PRECISION_AMP_BF16 = 1 };
+typedef struct {
+  int vocab, d_model, n_layers, n_heads, d_ff, context;
+  int batch;     /* sequences per step on this rank; tokens per step = batch * context */
+  int precision; /* HL_PRECISION_AMP_BF16: AmpBf16Policy::cuda_training (src/amp.rs:24-41) */
+} hl_decoder_config;
+typedef struct {
+  float lr, beta1, beta2, eps, weight_decay;
+  float clip_norm; /* <= 0: no clipping (AdamW::new default, src/nn.rs:1941-2005) */
+} hl_adamw_config;
+typedef struct hl_decoder hl_decoder;
+
+int hl_decoder_create(hl_ctx* ctx, const hl_decoder_config* cfg, hl_decoder** out);
+void hl_decoder_destroy(hl_decoder* model);
+int hl_decoder_param_count(hl_decoder* model);
+int hl_decoder_param_info(hl_decoder* model, int index, char* name_out, size_t name_cap, long long* numel,
+                          int* rank, long long shape_out[2]);
+/* Host <-> device copies of one parameter / its gradient / its AdamW moments (f32, C order). */
+int hl_decoder_set_param(hl_decoder* model, int index, const float* host, long long numel);
+int hl_decoder_get_param(hl_decoder* model, int index, float* host, long long numel);
+int hl_decoder_get_grad(hl_decoder* model, int index, float* host, long long numel);
+int hl_decoder_get_moments(hl_decoder* model, int index, float* m_host, float* v_host, long long numel);
+/* AdamW::new + with_* (src/nn.rs:1941-2005): resets the step counter and the moments. */
+int hl_decoder_set_optimizer(hl_decoder* model, const hl_adamw_config* opt);
+long long hl_decoder_optimizer_steps(hl_decoder* model);
+/* zero_grad + loss + backward (src/bin/heirloom/commands/training.rs:125-167) on device-resident
+ * i64 tokens/targets of shape [batch, context].  With an NCCL communicator on the context,
+ * 25 MiB gradient buckets are all-reduced on the collective stream as backward produces them. */
+int hl_decoder_forward_backward(hl_decoder* model, const int64_t* tokens_dev, const int64_t* targets_dev);
+/* AdamW::step_mut (src/nn.rs:2156-2220); with world > 1 the summed gradients are scaled by
+ * 1/world inside the update (src/nn.rs:2100-2117). */
+int hl_decoder_optimizer_step(hl_decoder* model);
+/* forward_backward + optimizer_step, nothing leaves the device. */
+int hl_decoder_train_step_device(hl_decoder* model, const int64_t* tokens_dev, const int64_t* targets_dev);
+/* The whole step from host memory: copies tokens/targets in, runs the step, copies the loss out
+ * and waits for it (the reference reads the loss every step too, reports.rs:285-308). */
+int hl_decoder_train_step(hl_decoder* model, const int64_t* tokens_host, const int64_t* targets_host,
+                          float* loss_host);
+/* Loss of the last forward (waits for the compute stream). */
+int hl_decoder_loss(hl_decoder* model, float* loss_host);
+/* Kernels launched by the last forward_backward + optimizer_step. */
+unsigned long long hl_decoder_launches_last_step(hl_decoder* model);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,0 +1,95 @@
+"""Step-level parity of the decoder executor (amp-bf16 route) against the oracle's AMP restatement."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import heirloom_oracle as ho
+from tests.gpu_util import ctx
+
+pytestmark = pytest.mark.gpu
+
+# parameters whose true gradient is identically zero (a constant added to every key leaves the
+# softmax unchanged), so what reaches AdamW is rounding noise on both sides
+NULL_GRADIENT = ("attention.k_proj.bias",)
+
+
+def make(cfg_kwargs, batch, seed=0):
+    from heirloom_b200 import nn
+    c = ctx()
+    cfg = nn.DecoderConfig(batch=batch, **cfg_kwargs)
+    model = nn.DecoderLm(c, cfg)
+    ocfg = ho.DecoderConfig(**cfg_kwargs)
+    params = ho.init_parameters(ocfg, seed)
+    model.load_state_dict(params)
+    return c, model, ocfg, params
+
+
+def test_parameter_names_follow_state_dict_order():
+    kw = dict(vocab=512, d_model=128, n_layers=2, n_heads=2, d_ff=256, context=128)
+    _, model, ocfg, _ = make(kw, 2)
+    assert model.parameter_names() == ho.parameter_names(ocfg)
+    assert model.parameter_shapes() == ho.parameter_shapes(ocfg)
+    model.close()
+
+
+def test_one_step_loss_and_gradients_match_the_amp_oracle():
+    kw = dict(vocab=512, d_model=128, n_layers=2, n_heads=2, d_ff=256, context=128)
+    c, model, ocfg, params = make(kw, 2)
+    rng = np.random.default_rng(3)
+    tok = ho.zipf_tokens(rng, ocfg.vocab, (2, 129))
+    x, y = tok[:, :-1].copy(), tok[:, 1:].copy()
+    model.forward_backward(torch.tensor(x, device="cuda"), torch.tensor(y, device="cuda"))
+    loss = model.loss()
+    oloss, ograds = ho.decoder_loss_and_grads(ocfg, params, x, y, amp_bf16=True)
+    assert abs(loss - oloss) <= 2e-3 * abs(oloss), (loss, oloss)
+    for name in ho.parameter_names(ocfg):
+        g, w = model.grad(name).astype(np.float64), ograds[name]
+        scale = np.abs(w).max() + 1e-12
+        if any(name.endswith(s) for s in NULL_GRADIENT):
+            assert np.abs(g).max() <= 2e-2 * max(np.abs(ograds[name.replace("k_proj", "q_proj")]).max(), 1e-12)
+            continue
+        # bf16 operands: compare against the tensor's scale, elementwise and on average
+        assert np.abs(g - w).max() <= 0.06 * scale, (name, np.abs(g - w).max(), scale)
+        assert np.abs(g - w).mean() <= 0.01 * scale, (name, np.abs(g - w).mean(), scale)
+    model.close()
+
+
+def test_ten_steps_parameters_and_losses_track_the_amp_oracle():
+    kw = dict(vocab=512, d_model=128, n_layers=2, n_heads=2, d_ff=256, context=128)
+    c, model, ocfg, params = make(kw, 2, seed=1)
+    model.set_optimizer(lr=1e-3, weight_decay=0.01)
+    state = ho.AdamWState(lr=1e-3, weight_decay=0.01)
+    rng = np.random.default_rng(4)
+    losses, olosses = [], []
+    for _ in range(10):
+        tok = ho.zipf_tokens(rng, ocfg.vocab, (2, 129))
+        x, y = tok[:, :-1].copy(), tok[:, 1:].copy()
+        losses.append(model.train_step(torch.tensor(x).pin_memory(), torch.tensor(y).pin_memory()))
+        olosses += ho.train_steps(ocfg, params, [(x, y)], state, amp_bf16=True)
+    assert model.optimizer_steps == 10
+    assert np.max(np.abs(np.array(losses) - np.array(olosses)) / np.array(olosses)) <= 0.01
+    # parameters after 10 steps: |a-b| <= 2e-2 * max(|b|, floor); the floor covers elements whose
+    # value is comparable to the 10*lr an Adam update can move them when the gradient sign is noise
+    floor = 10 * 1e-3
+    worst = 0.0
+    for name in ho.parameter_names(ocfg):
+        if any(name.endswith(s) for s in NULL_GRADIENT):
+            continue
+        got, want = model.parameter(name).astype(np.float64), params[name]
+        viol = np.abs(got - want) / np.maximum(np.abs(want), floor)
+        frac_bad = np.mean(viol > 2e-2)
+        worst = max(worst, frac_bad)
+        assert frac_bad <= 0.02, (name, frac_bad, viol.max())
+    model.close()
+
+
+def test_launch_count_is_reported_and_nonzero():
+    kw = dict(vocab=512, d_model=128, n_layers=1, n_heads=2, d_ff=256, context=128)
+    c, model, ocfg, _ = make(kw, 1)
+    model.set_optimizer()
+    tok = torch.zeros(1, 128, dtype=torch.int64, device="cuda")
+    model.train_step_device(tok, tok)
+    c.sync()
+    assert model.launches_last_step > 20
+    assert c.counters().gemm_tcgen05_launches >= 13
+    model.close()
