@@ -22,6 +22,10 @@ class Counters(Structure):
                                         "d2h_bytes", "allocations", "allocated_bytes", "nccl_calls", "nccl_bytes")]
 
 
+class Profile(Structure):
+    _fields_ = [("ms", ctypes.c_double * 9), ("work", ctypes.c_double * 9), ("scopes", c_uint64 * 9)]
+
+
 class AdamWParams(Structure):
     _fields_ = [(n, c_float) for n in ("lr", "beta1", "beta2", "eps", "weight_decay", "clip_scale",
                                        "bias_correction1", "bias_correction2")]

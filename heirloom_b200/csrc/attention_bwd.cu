@@ -343,6 +343,8 @@ int flash_attention_backward_impl(hl_ctx* ctx, const void* q, const void* k, con
              "hl_flash_attention_backward: scratch is too small");
   float* dq_accum = reinterpret_cast<float*>(scratch);
   float* delta = dq_accum + rows * C;
+  // five causal products against the forward's two
+  ProfileScope prof(ctx, HL_PROF_ATTENTION_BWD, 5.0 * batch * n_heads * (double)time * time * head_dim);
   HL_CUDA(cudaMemsetAsync(dq_accum, 0, sizeof(float) * rows * C, ctx->stream));
   {
     const long long warps = (long long)rows * n_heads;

@@ -292,6 +292,8 @@ int flash_attention_forward_impl(hl_ctx* ctx, const void* q, const void* k, cons
     configured = true;
   }
   const int nq = ceil_div(time, FA_BM);
+  // causal algorithmic work: QK^T and PV over the lower triangle
+  ProfileScope prof(ctx, HL_PROF_ATTENTION_FWD, 2.0 * batch * n_heads * (double)time * time * head_dim);
   flash_attention_fwd_kernel<<<nq * batch * n_heads, FA_THREADS, FA_SMEM_BYTES, ctx->stream>>>(mq, mk, mv, p);
   HL_LAUNCH_CHECK("flash_attention_fwd_kernel");
   count_launch(ctx);

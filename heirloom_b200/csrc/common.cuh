@@ -62,11 +62,24 @@ struct hl_ctx {
   size_t workspace_bytes = 0;
   hl::Counters counters{};
   void* nccl = nullptr;                // hl::NcclState*
+  void* profiler = nullptr;            // hl::Profiler*, present while per-kernel timing is on
 };
 
 namespace hl {
 int ensure_workspace(hl_ctx* ctx, size_t bytes);
 inline void count_launch(hl_ctx* ctx, unsigned long long n = 1) { ctx->counters.launches += n; }
+
+// Opt-in per-kernel timing: a scope brackets the launches of one op with two events on the
+// compute stream; hl_profile_read folds them by category after a stream sync (the reference's
+// opt-in launch-family timing, heirloom-kernels/src/cuda.rs:8574-8611, forces a sync per
+// launch instead).  `work` is the algorithmic flops (GEMM, attention) or bytes (the rest).
+void profile_begin(hl_ctx* ctx, int category, double work);
+void profile_end(hl_ctx* ctx);
+struct ProfileScope {
+  hl_ctx* ctx;
+  ProfileScope(hl_ctx* c, int category, double work) : ctx(c) { if (c->profiler) profile_begin(c, category, work); }
+  ~ProfileScope() { if (ctx->profiler) profile_end(ctx); }
+};
 
 inline size_t dtype_size(int dtype) {
   switch (dtype) {

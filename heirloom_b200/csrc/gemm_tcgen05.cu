@@ -387,6 +387,7 @@ int gemm_bf16_run(hl_ctx* ctx, const hl_gemm_desc* d, const void* a, const void*
 
   const int total = p.m_tiles * p.n_tiles * p.splits;
   const int grid = min(total, ctx->sm_count);
+  ProfileScope prof(ctx, HL_PROF_GEMM, 2.0 * (double)d->m * (double)d->n * (double)d->k);
   if (a_mn && b_mn) rc = launch_variant<true, true>(ctx, ma, mb, p, grid);
   else if (a_mn)    rc = launch_variant<true, false>(ctx, ma, mb, p, grid);
   else if (b_mn)    rc = launch_variant<false, true>(ctx, ma, mb, p, grid);

@@ -362,6 +362,7 @@ int layer_norm_forward_impl(hl_ctx* ctx, const void* x, int x_dtype, const float
   HL_REQUIRE(ctx && x && gamma && beta && y, "hl_layer_norm_forward: null argument");
   HL_REQUIRE(rows > 0 && features > 0, "hl_layer_norm_forward: rows and features must be positive");
   HL_REQUIRE(eps > 0.f, "hl_layer_norm_forward: eps must be positive");
+  ProfileScope prof(ctx, HL_PROF_LAYER_NORM, (double)rows * features * (double)(dtype_size(x_dtype) + dtype_size(y_dtype)));
   const int warps = 4;
   const int grid = ceil_div(rows, warps);
   const bool vec = (features % 4 == 0) && ((reinterpret_cast<uintptr_t>(x) & 15) == 0) &&
@@ -395,6 +396,8 @@ int layer_norm_backward_impl(hl_ctx* ctx, const void* x, int x_dtype, const floa
   HL_REQUIRE(features % 4 == 0 && features <= LNB_MAXJ * 128,
              "hl_layer_norm_backward: features must be a multiple of 4 and at most 1024");
   HL_REQUIRE(x_dtype == HL_F32 || x_dtype == HL_BF16, "hl_layer_norm_backward: x dtype must be f32 or bf16");
+  ProfileScope prof(ctx, HL_PROF_LAYER_NORM,
+                    (double)rows * features * (double)(dtype_size(x_dtype) + 4 + (residual_grad ? 4 : 0) + (dx_f32 ? 4 : 0) + (dx_bf16 ? 2 : 0)));
   int blocks = std::min(ctx->sm_count * 2, ceil_div(rows, LNB_WARPS));
   const int rows_per_block = ceil_div(rows, blocks);
   blocks = ceil_div(rows, rows_per_block);
@@ -443,6 +446,7 @@ int cross_entropy_impl(hl_ctx* ctx, const float* logits, long long ld, const int
     rl = reinterpret_cast<float*>(ctx->workspace);
   }
   const float scale = grad_scale / (float)rows;
+  ProfileScope prof(ctx, HL_PROF_LOSS, (double)rows * classes * (4.0 + (dlogits ? (double)dtype_size(dlogits_dtype) : 0.0)));
   const int threads = classes >= 4096 ? 512 : 256;
   if (dlogits && dlogits_dtype == HL_BF16)
     cross_entropy_kernel<float, __nv_bfloat16><<<rows, threads, 0, ctx->stream>>>(
@@ -483,6 +487,7 @@ int hl_embedding_forward(hl_ctx* ctx, const float* table, int table_rows, const 
   HL_REQUIRE(ctx && table && idx && out, "hl_embedding_forward: null argument");
   HL_REQUIRE(n > 0 && dim > 0 && table_rows > 0, "hl_embedding_forward: sizes must be positive");
   HL_REQUIRE(!pos_table || period > 0, "hl_embedding_forward: period must be positive with a position table");
+  ProfileScope prof(ctx, HL_PROF_EMBEDDING, (double)n * dim * (4.0 + (pos_table ? 4.0 : 0.0) + (double)dtype_size(out_dtype)));
   const int warps = 4;
   if (out_dtype == HL_BF16)
     embedding_fwd_kernel<__nv_bfloat16><<<ceil_div(n, warps), warps * 32, 0, ctx->stream>>>(
@@ -501,6 +506,7 @@ int hl_embedding_backward(hl_ctx* ctx, const float* grad_out, const int64_t* idx
                           float* pos_grad, int period, int n, int dim) {
   HL_REQUIRE(ctx && grad_out && idx && grad_table, "hl_embedding_backward: null argument");
   HL_REQUIRE(n > 0 && dim > 0 && table_rows > 0, "hl_embedding_backward: sizes must be positive");
+  ProfileScope prof(ctx, HL_PROF_EMBEDDING, (double)n * dim * 12.0);
   const int warps = 4;
   embedding_bwd_kernel<<<ceil_div(n, warps), warps * 32, 0, ctx->stream>>>(grad_out, idx, grad_table, table_rows, n,
                                                                            dim, ctx->status_dev);

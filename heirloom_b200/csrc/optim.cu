@@ -85,11 +85,13 @@ int validate(const hl_adamw_params* hp, const char* who) {
 struct AdamPlan {
   AdamChunk* chunks_dev = nullptr;
   int count = 0;
+  unsigned long long elements = 0;
 };
 
 int adam_plan_create(hl_ctx* ctx, const hl_adamw_tensor* tensors, int count, AdamPlan** out) {
   HL_REQUIRE(ctx && tensors && out && count > 0, "adamw plan: null or empty argument");
   std::vector<AdamChunk> chunks;
+  unsigned long long elements_total = 0;
   for (int t = 0; t < count; ++t) {
     const hl_adamw_tensor& x = tensors[t];
     HL_REQUIRE(x.param && x.grad && x.m && x.v, "adamw plan: null tensor pointer");
@@ -105,9 +107,11 @@ int adam_plan_create(hl_ctx* ctx, const hl_adamw_tensor* tensors, int count, Ada
       c.n = (unsigned int)std::min<uint64_t>(ADAM_CHUNK, x.n - off);
       chunks.push_back(c);
     }
+    elements_total += x.n;
   }
   AdamPlan* plan = new AdamPlan();
   plan->count = (int)chunks.size();
+  plan->elements = elements_total;
   if (plan->count > 0) {
     cudaError_t e = cudaMalloc(&plan->chunks_dev, sizeof(AdamChunk) * chunks.size());
     if (e != cudaSuccess) { delete plan; return fail_cuda(e, "cudaMalloc(adamw chunk table)"); }
@@ -130,6 +134,8 @@ int adam_plan_step(hl_ctx* ctx, AdamPlan* plan, const hl_adamw_params* hp) {
   int rc = validate(hp, "hl_adamw_multi");
   if (rc != HL_OK) return rc;
   if (plan->count == 0) return HL_OK;
+  // 28 bytes per parameter (read p, g, m, v; write p, m, v) plus 2 for the bf16 shadow
+  ProfileScope prof(ctx, HL_PROF_OPTIMIZER, 30.0 * (double)plan->elements);
   adamw_chunks_kernel<<<plan->count, ADAM_THREADS, 0, ctx->stream>>>(plan->chunks_dev, *hp);
   HL_LAUNCH_CHECK("adamw_chunks_kernel");
   count_launch(ctx);

@@ -5,6 +5,7 @@
 #include <cstdio>
 #include <cstring>
 #include <mutex>
+#include <vector>
 
 #include "common.cuh"
 #include "tc05.cuh"
@@ -98,6 +99,32 @@ int make_tensor_map_bf16_3d(CUtensorMap* out, const void* base, uint64_t d0, uin
   return HL_OK;
 }
 
+struct ProfRecord { cudaEvent_t a, b; int category; double work; };
+struct Profiler {
+  std::vector<ProfRecord> records;
+  std::vector<cudaEvent_t> pool;
+  size_t used = 0;
+  cudaEvent_t take() {
+    if (used == pool.size()) {
+      cudaEvent_t e;
+      cudaEventCreate(&e);
+      pool.push_back(e);
+    }
+    return pool[used++];
+  }
+};
+
+void profile_begin(hl_ctx* ctx, int category, double work) {
+  Profiler* p = static_cast<Profiler*>(ctx->profiler);
+  ProfRecord r{p->take(), p->take(), category, work};
+  cudaEventRecord(r.a, ctx->stream);
+  p->records.push_back(r);
+}
+void profile_end(hl_ctx* ctx) {
+  Profiler* p = static_cast<Profiler*>(ctx->profiler);
+  if (!p->records.empty()) cudaEventRecord(p->records.back().b, ctx->stream);
+}
+
 }  // namespace hl
 
 struct hl_buffer {
@@ -143,6 +170,7 @@ void hl_ctx_destroy(hl_ctx* ctx) {
   cudaSetDevice(ctx->device);
   cudaStreamSynchronize(ctx->stream);
   cudaStreamSynchronize(ctx->comm_stream);
+  if (ctx->profiler) hl_profile_enable(ctx, 0);
   if (ctx->workspace) cudaFree(ctx->workspace);
   if (ctx->status_dev) cudaFree(ctx->status_dev);
   if (ctx->status_host) cudaFreeHost(ctx->status_host);
@@ -202,6 +230,42 @@ int hl_counters_get(hl_ctx* ctx, hl_counters_t* out) {
 int hl_counters_reset(hl_ctx* ctx) {
   if (!ctx) return hl::fail("hl_counters_reset: null context");
   ctx->counters = hl::Counters{};
+  return HL_OK;
+}
+
+int hl_profile_enable(hl_ctx* ctx, int on) {
+  if (!ctx) return hl::fail("hl_profile_enable: null context");
+  hl::Profiler* p = static_cast<hl::Profiler*>(ctx->profiler);
+  if (on) {
+    if (!p) ctx->profiler = p = new hl::Profiler();
+    p->records.clear();
+    p->used = 0;
+  } else if (p) {
+    HL_CUDA(cudaStreamSynchronize(ctx->stream));
+    for (cudaEvent_t e : p->pool) cudaEventDestroy(e);
+    delete p;
+    ctx->profiler = nullptr;
+  }
+  return HL_OK;
+}
+
+int hl_profile_read(hl_ctx* ctx, hl_profile_t* out) {
+  if (!ctx || !out) return hl::fail("hl_profile_read: null argument");
+  memset(out, 0, sizeof(*out));
+  hl::Profiler* p = static_cast<hl::Profiler*>(ctx->profiler);
+  if (!p) return hl::fail("hl_profile_read: profiling is not enabled");
+  HL_CUDA(cudaStreamSynchronize(ctx->stream));
+  for (const hl::ProfRecord& r : p->records) {
+    float ms = 0.f;
+    HL_CUDA(cudaEventElapsedTime(&ms, r.a, r.b));
+    if (r.category >= 0 && r.category < HL_PROF_CATEGORIES) {
+      out->ms[r.category] += ms;
+      out->work[r.category] += r.work;
+      out->scopes[r.category] += 1;
+    }
+  }
+  p->records.clear();
+  p->used = 0;
   return HL_OK;
 }
 

@@ -61,6 +61,21 @@ typedef struct {
 int hl_counters_get(hl_ctx* ctx, hl_counters_t* out);
 int hl_counters_reset(hl_ctx* ctx);
 
+/* Opt-in per-kernel timing with CUDA events on the compute stream, folded by category
+ * (reference: launch-family timing, cuda.rs:8574-8611, and CudaEventTimer, :853-949).
+ * `work` is algorithmic flops for GEMM/attention categories and bytes for the others. */
+enum {
+  HL_PROF_GEMM = 0, HL_PROF_ATTENTION_FWD = 1, HL_PROF_ATTENTION_BWD = 2, HL_PROF_LAYER_NORM = 3, HL_PROF_LOSS = 4,
+  HL_PROF_OPTIMIZER = 5, HL_PROF_BIAS_GRAD = 6, HL_PROF_EMBEDDING = 7, HL_PROF_OTHER = 8, HL_PROF_CATEGORIES = 9
+};
+typedef struct {
+  double ms[HL_PROF_CATEGORIES];
+  double work[HL_PROF_CATEGORIES];
+  uint64_t scopes[HL_PROF_CATEGORIES];
+} hl_profile_t;
+int hl_profile_enable(hl_ctx* ctx, int on);
+int hl_profile_read(hl_ctx* ctx, hl_profile_t* out);
+
 /* Reference-counted device buffers (reference: CudaBuffer, cuda.rs:652-656; frees are
  * stream-ordered as in :7870-7922).  hl_memcpy_d2h waits for the compute stream first
  * (cuda.rs:836). */
