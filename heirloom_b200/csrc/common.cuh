@@ -138,6 +138,24 @@ __device__ __forceinline__ float gelu_grad_f(float x) {
   return 0.5f * (1.0f + t) + 0.5f * x * sech2 * dinner;
 }
 
+// Hardware tanh (one MUFU op, relative error about 2^-11): enough for values that are rounded
+// to bf16 right after, as in the GEMM epilogues.
+__device__ __forceinline__ float tanh_fast(float x) {
+  float y;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ float gelu_fwd_fast(float x) {
+  const float inner = 0.7978845608028654f * (x + 0.044715f * x * x * x);
+  return 0.5f * x * (1.0f + tanh_fast(inner));
+}
+__device__ __forceinline__ float gelu_grad_fast(float x) {
+  const float x2 = x * x;
+  const float t = tanh_fast(0.7978845608028654f * (x + 0.044715f * x * x2));
+  const float dinner = 0.7978845608028654f * (1.0f + 3.0f * 0.044715f * x2);
+  return 0.5f * (1.0f + t) + 0.5f * x * (1.0f - t * t) * dinner;
+}
+
 template <typename T>
 __device__ __forceinline__ T warp_sum(T v) {
 #pragma unroll

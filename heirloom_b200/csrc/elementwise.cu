@@ -1,7 +1,7 @@
 // 128-bit vectorised elementwise kernels, casts, bias add / bias gradient and grid reductions.
 // Reference counterparts are one-thread-per-element scalar PTX entries
 // (heirloom-kernels/src/ptx/kernels.ptx:6-312, :4610-4907).
-#include "common.cuh"
+#include "kernels.h"
 
 namespace hl {
 namespace {
@@ -203,6 +203,7 @@ int bias_grad_impl(hl_ctx* ctx, const void* grad_out, int dtype, float* grad_bia
   HL_REQUIRE(rows > 0 && cols > 0, "hl_bias_grad: rows and cols must be positive");
   HL_REQUIRE(dtype == HL_F32 || dtype == HL_BF16, "hl_bias_grad: dtype must be f32 or bf16");
   ProfileScope prof(ctx, HL_PROF_BIAS_GRAD, (double)rows * cols * (double)dtype_size(dtype));
+  if (colsum_fast_applicable(dtype, cols, grad_out)) return colsum_fast(ctx, grad_out, dtype, grad_bias, rows, cols);
   int slabs = std::min(std::max(rows / 256, 1), 64);
   const int rows_per_block = ceil_div(rows, slabs);
   slabs = ceil_div(rows, rows_per_block);

@@ -1,0 +1,315 @@
+// Bandwidth-bound row kernels of the bf16 route: layer norm forward/backward with the whole
+// row held in registers (one global read per operand, 128-bit accesses) and a vectorised
+// column-sum for bias gradients.  The backward also returns the column sums of the dx it
+// writes, which is the bias gradient of the linear layer that produced that activation, so the
+// f32 bias gradients of the step cost no extra pass over memory.
+// Arithmetic: src/tensor.rs:3175-3256 (forward), src/tensor/autograd.rs:2158-2232 (backward),
+// kernels.ptx:312 (bias gradient), in f32 as the reference's CUDA route.
+#include "kernels.h"
+
+namespace hl {
+namespace {
+
+constexpr int ROW_WARPS = 8;
+
+__device__ __forceinline__ void load8_bf16(const __nv_bfloat16* p, float (&v)[8]) {
+  const uint4 t = *reinterpret_cast<const uint4*>(p);
+  const float2 a = unpack_bf16x2(t.x), b = unpack_bf16x2(t.y), c = unpack_bf16x2(t.z), d = unpack_bf16x2(t.w);
+  v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y; v[4] = c.x; v[5] = c.y; v[6] = d.x; v[7] = d.y;
+}
+__device__ __forceinline__ void load8_f32(const float* p, float (&v)[8]) {
+  const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+  v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+__device__ __forceinline__ void store8_bf16(__nv_bfloat16* p, const float (&v)[8]) {
+  *reinterpret_cast<uint4*>(p) =
+      make_uint4(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]), pack_bf16x2(v[4], v[5]), pack_bf16x2(v[6], v[7]));
+}
+__device__ __forceinline__ void store8_f32(float* p, const float (&v)[8]) {
+  *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+  *reinterpret_cast<float4*>(p + 4) = make_float4(v[4], v[5], v[6], v[7]);
+}
+
+// One warp per row; lane owns columns (j*32 + lane)*8 .. +7 for j < J.
+template <int J>
+__global__ void __launch_bounds__(ROW_WARPS * 32)
+ln_fwd_bf16_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ gamma, const float* __restrict__ beta,
+                   __nv_bfloat16* __restrict__ y, float* __restrict__ mean_out, float* __restrict__ rstd_out, int rows,
+                   int features, float eps) {
+  const int lane = threadIdx.x & 31;
+  const int row = blockIdx.x * ROW_WARPS + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const __nv_bfloat16* xr = x + (size_t)row * features;
+  float v[J][8];
+  float sum = 0.f;
+#pragma unroll
+  for (int j = 0; j < J; ++j) {
+    const int c = (j * 32 + lane) * 8;
+    if (c < features) {
+      load8_bf16(xr + c, v[j]);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) sum += v[j][e];
+    }
+  }
+  const float mean = warp_sum(sum) / (float)features;
+  float sq = 0.f;
+#pragma unroll
+  for (int j = 0; j < J; ++j) {
+    const int c = (j * 32 + lane) * 8;
+    if (c < features) {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) { const float d = v[j][e] - mean; sq += d * d; }
+    }
+  }
+  const float rstd = 1.0f / sqrtf(warp_sum(sq) / (float)features + eps);
+  if (lane == 0) {
+    if (mean_out) mean_out[row] = mean;
+    if (rstd_out) rstd_out[row] = rstd;
+  }
+  __nv_bfloat16* yr = y + (size_t)row * features;
+#pragma unroll
+  for (int j = 0; j < J; ++j) {
+    const int c = (j * 32 + lane) * 8;
+    if (c < features) {
+      float g[8], b[8], o[8];
+      load8_f32(gamma + c, g);
+      load8_f32(beta + c, b);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) o[e] = (v[j][e] - mean) * rstd * g[e] + b[e];
+      store8_bf16(yr + c, o);
+    }
+  }
+}
+
+// Each warp walks rows of its block's slab; partial[block][3][features] receives the block's
+// sums of dy*xhat, dy and of the dx written (the last only when want_colsum).
+template <int J>
+__global__ void __launch_bounds__(ROW_WARPS * 32, 1)
+ln_bwd_bf16_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ gamma, const float* __restrict__ dy,
+                   const float* __restrict__ mean_in, const float* __restrict__ rstd_in,
+                   const float* __restrict__ residual, float* __restrict__ dx_f32, __nv_bfloat16* __restrict__ dx_bf16,
+                   float* __restrict__ partial, int rows, int features, int rows_per_block) {
+  extern __shared__ float fold_smem[];  // [ROW_WARPS][3][features]
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int r0 = blockIdx.x * rows_per_block, r1 = min(rows, r0 + rows_per_block);
+  float g[J][8], dg[J][8], db[J][8], ds[J][8];
+#pragma unroll
+  for (int j = 0; j < J; ++j) {
+    const int c = (j * 32 + lane) * 8;
+    if (c < features) load8_f32(gamma + c, g[j]);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) { dg[j][e] = 0.f; db[j][e] = 0.f; ds[j][e] = 0.f; }
+  }
+  const float inv_f = 1.0f / (float)features;
+  for (int row = r0 + warp; row < r1; row += ROW_WARPS) {
+    const size_t base = (size_t)row * features;
+    const float mean = mean_in[row], rstd = rstd_in[row];
+    float xh[J][8], d[J][8];
+    float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+    for (int j = 0; j < J; ++j) {
+      const int c = (j * 32 + lane) * 8;
+      if (c < features) {
+        load8_bf16(x + base + c, xh[j]);
+        load8_f32(dy + base + c, d[j]);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          xh[j][e] = (xh[j][e] - mean) * rstd;
+          const float dxhat = d[j][e] * g[j][e];
+          s1 += dxhat;
+          s2 += dxhat * xh[j][e];
+          dg[j][e] += d[j][e] * xh[j][e];
+          db[j][e] += d[j][e];
+        }
+      }
+    }
+    s1 = warp_sum(s1);
+    s2 = warp_sum(s2);
+#pragma unroll
+    for (int j = 0; j < J; ++j) {
+      const int c = (j * 32 + lane) * 8;
+      if (c < features) {
+        float o[8];
+        if (residual) load8_f32(residual + base + c, o);
+        else {
+#pragma unroll
+          for (int e = 0; e < 8; ++e) o[e] = 0.f;
+        }
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          const float dxhat = d[j][e] * g[j][e];
+          o[e] += rstd * ((float)features * dxhat - s1 - xh[j][e] * s2) * inv_f;
+          ds[j][e] += o[e];
+        }
+        if (dx_f32) store8_f32(dx_f32 + base + c, o);
+        if (dx_bf16) store8_bf16(dx_bf16 + base + c, o);
+      }
+    }
+  }
+  float* mine = fold_smem + (size_t)warp * 3 * features;
+#pragma unroll
+  for (int j = 0; j < J; ++j) {
+    const int c = (j * 32 + lane) * 8;
+    if (c < features) {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        mine[c + e] = dg[j][e];
+        mine[features + c + e] = db[j][e];
+        mine[2 * features + c + e] = ds[j][e];
+      }
+    }
+  }
+  __syncthreads();
+  for (int c = threadIdx.x; c < 3 * features; c += blockDim.x) {
+    float s = 0.f;
+#pragma unroll
+    for (int w = 0; w < ROW_WARPS; ++w) s += fold_smem[(size_t)w * 3 * features + c];
+    partial[(size_t)blockIdx.x * 3 * features + c] = s;
+  }
+}
+
+__global__ void fold3_kernel(const float* __restrict__ partial, float* __restrict__ o0, float* __restrict__ o1,
+                             float* __restrict__ o2, int features, int blocks) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= 3 * features) return;
+  double s = 0.0;
+  for (int b = 0; b < blocks; ++b) s += (double)partial[(size_t)b * 3 * features + c];
+  float* dst = c < features ? o0 : (c < 2 * features ? o1 : o2);
+  if (dst) dst[c % features] = (float)s;
+}
+
+// Column sums with 16-byte loads: a warp covers 32*VEC consecutive columns, the block's eight
+// warps take different rows of the slab.
+template <typename T, int VEC>
+__global__ void __launch_bounds__(ROW_WARPS * 32)
+colsum_vec_kernel(const T* __restrict__ g, float* __restrict__ partial, int rows, int cols, int rows_per_block) {
+  __shared__ float fold[ROW_WARPS][32 * VEC + 1];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int c = (blockIdx.x * 32 + lane) * VEC;
+  const int r0 = blockIdx.y * rows_per_block, r1 = min(rows, r0 + rows_per_block);
+  float acc[VEC];
+#pragma unroll
+  for (int e = 0; e < VEC; ++e) acc[e] = 0.f;
+  if (c < cols) {
+#pragma unroll 4
+    for (int r = r0 + warp; r < r1; r += ROW_WARPS) {
+      float v[8];
+      if constexpr (VEC == 8) load8_bf16(reinterpret_cast<const __nv_bfloat16*>(g) + (size_t)r * cols + c, v);
+      else {
+        const float4 t = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(g) + (size_t)r * cols + c);
+        v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+      }
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) acc[e] += v[e];
+    }
+  }
+#pragma unroll
+  for (int e = 0; e < VEC; ++e) fold[warp][lane * VEC + e] = acc[e];
+  __syncthreads();
+  for (int i = threadIdx.x; i < 32 * VEC; i += blockDim.x) {
+    const int col = blockIdx.x * 32 * VEC + i;
+    if (col < cols) {
+      float s = 0.f;
+#pragma unroll
+      for (int w = 0; w < ROW_WARPS; ++w) s += fold[w][i];
+      partial[(size_t)blockIdx.y * cols + col] = s;
+    }
+  }
+}
+
+__global__ void colsum_fold_kernel(const float* __restrict__ partial, float* __restrict__ out, int cols, int slabs) {
+  const int col = blockIdx.x * blockDim.x + threadIdx.x;
+  if (col >= cols) return;
+  double s = 0.0;
+  for (int j = 0; j < slabs; ++j) s += (double)partial[(size_t)j * cols + col];
+  out[col] = (float)s;
+}
+
+}  // namespace
+
+bool layer_norm_fast_applicable(int x_dtype, int y_dtype, int features, const void* x, const void* y) {
+  return x_dtype == HL_BF16 && y_dtype == HL_BF16 && features % 8 == 0 && features <= 1024 &&
+         ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y)) & 15) == 0;
+}
+
+int layer_norm_forward_fast(hl_ctx* ctx, const void* x, const float* gamma, const float* beta, void* y, float* mean,
+                            float* rstd, int rows, int features, float eps) {
+  const int grid = ceil_div(rows, ROW_WARPS);
+  const int J = ceil_div(features, 256);
+#define HL_LAUNCH(JJ)                                                                                          \
+  ln_fwd_bf16_kernel<JJ><<<grid, ROW_WARPS * 32, 0, ctx->stream>>>((const __nv_bfloat16*)x, gamma, beta,       \
+                                                                    (__nv_bfloat16*)y, mean, rstd, rows, features, eps)
+  switch (J) {
+    case 1: HL_LAUNCH(1); break;
+    case 2: HL_LAUNCH(2); break;
+    case 3: HL_LAUNCH(3); break;
+    default: HL_LAUNCH(4); break;
+  }
+#undef HL_LAUNCH
+  HL_LAUNCH_CHECK("ln_fwd_bf16_kernel");
+  count_launch(ctx);
+  return HL_OK;
+}
+
+int layer_norm_backward_fast(hl_ctx* ctx, const void* x, const float* gamma, const float* dy, const float* mean,
+                             const float* rstd, const float* residual, float* dx_f32, void* dx_bf16, float* dgamma,
+                             float* dbeta, float* dx_colsum, int rows, int features) {
+  int blocks = std::min(ctx->sm_count, ceil_div(rows, ROW_WARPS));
+  const int rows_per_block = ceil_div(rows, blocks);
+  blocks = ceil_div(rows, rows_per_block);
+  int rc = ensure_workspace(ctx, sizeof(float) * (size_t)blocks * 3 * features);
+  if (rc != HL_OK) return rc;
+  float* partial = reinterpret_cast<float*>(ctx->workspace);
+  const size_t smem = sizeof(float) * ROW_WARPS * 3 * (size_t)features;
+  const int J = ceil_div(features, 256);
+#define HL_LAUNCH(JJ)                                                                                             \
+  do {                                                                                                            \
+    auto k = ln_bwd_bf16_kernel<JJ>;                                                                              \
+    HL_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));                     \
+    k<<<blocks, ROW_WARPS * 32, smem, ctx->stream>>>((const __nv_bfloat16*)x, gamma, dy, mean, rstd, residual,    \
+                                                      dx_f32, (__nv_bfloat16*)dx_bf16, partial, rows, features,   \
+                                                      rows_per_block);                                            \
+  } while (0)
+  switch (J) {
+    case 1: HL_LAUNCH(1); break;
+    case 2: HL_LAUNCH(2); break;
+    case 3: HL_LAUNCH(3); break;
+    default: HL_LAUNCH(4); break;
+  }
+#undef HL_LAUNCH
+  HL_LAUNCH_CHECK("ln_bwd_bf16_kernel");
+  fold3_kernel<<<ceil_div(3 * features, 256), 256, 0, ctx->stream>>>(partial, dgamma, dbeta, dx_colsum, features, blocks);
+  HL_LAUNCH_CHECK("fold3_kernel");
+  count_launch(ctx, 2);
+  return HL_OK;
+}
+
+bool colsum_fast_applicable(int dtype, int cols, const void* g) {
+  const int vec = dtype == HL_BF16 ? 8 : 4;
+  return (dtype == HL_BF16 || dtype == HL_F32) && cols % vec == 0 && (reinterpret_cast<uintptr_t>(g) & 15) == 0;
+}
+
+int colsum_fast(hl_ctx* ctx, const void* g, int dtype, float* out, int rows, int cols) {
+  const int vec = dtype == HL_BF16 ? 8 : 4;
+  const int col_blocks = ceil_div(cols, 32 * vec);
+  int slabs = std::max(1, std::min(std::min(64, ceil_div(rows, ROW_WARPS * 4)), (ctx->sm_count * 4) / col_blocks));
+  const int rows_per_block = ceil_div(rows, slabs);
+  slabs = ceil_div(rows, rows_per_block);
+  int rc = ensure_workspace(ctx, sizeof(float) * (size_t)slabs * cols);
+  if (rc != HL_OK) return rc;
+  float* partial = reinterpret_cast<float*>(ctx->workspace);
+  dim3 grid(col_blocks, slabs);
+  if (dtype == HL_BF16)
+    colsum_vec_kernel<__nv_bfloat16, 8><<<grid, ROW_WARPS * 32, 0, ctx->stream>>>((const __nv_bfloat16*)g, partial, rows,
+                                                                                   cols, rows_per_block);
+  else
+    colsum_vec_kernel<float, 4><<<grid, ROW_WARPS * 32, 0, ctx->stream>>>((const float*)g, partial, rows, cols,
+                                                                           rows_per_block);
+  HL_LAUNCH_CHECK("colsum_vec_kernel");
+  colsum_fold_kernel<<<ceil_div(cols, 256), 256, 0, ctx->stream>>>(partial, out, cols, slabs);
+  HL_LAUNCH_CHECK("colsum_fold_kernel");
+  count_launch(ctx, 2);
+  return HL_OK;
+}
+
+}  // namespace hl

@@ -5,14 +5,16 @@
 // wrappers heirloom-kernels/src/cuda.rs:4215-4386) together with the cast / transpose / pad /
 // crop / bias kernels it launches around every matmul (src/nn.rs:432-446,
 // src/tensor/autograd.rs:795-850): operand majors are expressed in the TMA descriptors, ragged
-// edges by TMA zero fill plus a predicated epilogue, and bias / GELU / residual / dGELU run
+// edges by TMA zero fill on loads and clipping on stores, and bias / GELU / residual / dGELU run
 // in the epilogue on the f32 accumulators.
 //
 // Tile: 128 (M) x 256 (N) x 64 (K) per stage, 4 stages (192 KB shared memory), two
 // accumulator buffers of 256 tensor-memory columns so the epilogue of tile i overlaps the
 // main loop of tile i+1.  Warp roles: warp 0 TMA producer, warp 1 MMA issuer (one elected
-// thread), warps 2-5 epilogue (each owns the 32 tensor-memory lanes its warp id maps to).
-#include "common.cuh"
+// thread), warps 2-9 epilogue: two warps per tensor-memory lane group, each taking 128 of the
+// 256 columns.  An epilogue warp moves its 32 rows through a 4 KB swizzled staging tile and
+// writes them with TMA stores, so global writes are full 128-byte lines.
+#include "kernels.h"
 #include "tc05.cuh"
 
 namespace hl {
@@ -27,23 +29,22 @@ constexpr int UMMA_K = 16;
 constexpr int A_STAGE_BYTES = BM * BK * 2;  // 16 KB
 constexpr int B_STAGE_BYTES = BN * BK * 2;  // 32 KB
 constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
-constexpr int GEMM_THREADS = 192;
+constexpr int EPI_WARPS = 8;
+constexpr int GEMM_THREADS = (2 + EPI_WARPS) * 32;
 constexpr int TMEM_COLS = 512;
-constexpr size_t GEMM_SMEM_BYTES = size_t(STAGES) * STAGE_BYTES + 1024 /*align slack*/ + 256 /*barriers*/;
+constexpr int STAGING_BYTES = 4096;  // per epilogue warp: 32 rows x 128 bytes
+constexpr size_t GEMM_SMEM_BYTES =
+    size_t(STAGES) * STAGE_BYTES + size_t(EPI_WARPS) * STAGING_BYTES + 1024 /*align slack*/ + 256 /*barriers*/;
 
 struct GemmParams {
   int m, n, k;
   int m_tiles, n_tiles, splits, k_blocks, k_blocks_per_split;
   int epilogue;
   int out_dtype;
-  long long ldc;
+  int partial_out;  // split-K: raw accumulators go to the [splits][m][n] scratch through map_c
   long long ld_aux_in;
-  long long ld_aux_out;
-  void* c;
   const float* bias;
   const void* aux_in;
-  void* aux_out;
-  float* partials;  // split-K workspace [splits][m][n]
   int* status;
 };
 
@@ -56,13 +57,20 @@ struct SharedTail {
   int abort_flag;
 };
 
+// Write 8 consecutive 32-bit words pairs ... helper: one 16-byte chunk of a staging row.
+__device__ __forceinline__ void stage_chunk(uint8_t* staging, int r, int chunk, uint4 v) {
+  *reinterpret_cast<uint4*>(staging + r * 128 + ((chunk ^ (r & 7)) << 4)) = v;
+}
+
 template <bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                         const __grid_constant__ CUtensorMap map_c, const __grid_constant__ CUtensorMap map_aux,
                          const GemmParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  SharedTail* tail = reinterpret_cast<SharedTail*>(smem + size_t(STAGES) * STAGE_BYTES);
+  uint8_t* staging_base = smem + size_t(STAGES) * STAGE_BYTES;
+  SharedTail* tail = reinterpret_cast<SharedTail*>(staging_base + size_t(EPI_WARPS) * STAGING_BYTES);
   volatile int* abort_flag = &tail->abort_flag;
 
   const int warp = threadIdx.x >> 5;
@@ -76,7 +84,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
     }
     for (int b = 0; b < 2; ++b) {
       tc05::mbar_init(&tail->tmem_full[b], 1);
-      tc05::mbar_init(&tail->tmem_empty[b], 4);
+      tc05::mbar_init(&tail->tmem_empty[b], EPI_WARPS);
     }
     tail->abort_flag = 0;
     tc05::fence_barrier_init();
@@ -165,8 +173,14 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
       }
     }
   } else {
-    // ------------------------------------------------------------------ epilogue warps 2..5
+    // ------------------------------------------------------------------ epilogue warps 2..9
+    const int ew = warp - 2;
     const int lane_group = warp & 3;  // tensor-memory lanes this warp may read
+    const int half = ew >> 2;         // which 128 of the tile's 256 columns
+    uint8_t* staging = staging_base + size_t(ew) * STAGING_BYTES;
+    const bool out_bf16 = !p.partial_out && p.out_dtype == HL_BF16;
+    const int group_cols = out_bf16 ? 64 : 32;  // columns per 128-byte staging row
+    const int groups = 128 / group_cols;
     int local = 0;
     bool ok = true;
     for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x, ++local) {
@@ -178,77 +192,96 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
       const uint32_t buf_phase = (uint32_t)(local >> 1) & 1u;
       if (!tc05::mbar_wait(&tail->tmem_full[buf], buf_phase, abort_flag)) { ok = false; break; }
       tc05::tc_fence_after_sync();
-      const int row = m_tile * BM + lane_group * 32 + lane;
+      const int row0 = m_tile * BM + lane_group * 32;
+      const int row = row0 + lane;
       const bool row_ok = row < p.m;
       const uint32_t taddr_row = tmem_base + (uint32_t)(buf * BN) + ((uint32_t)(lane_group * 32) << 16);
 #pragma unroll 1
-      for (int chunk = 0; chunk < BN / 32; ++chunk) {
-        const int col0 = n_tile * BN + chunk * 32;
-        if (col0 >= p.n) break;  // uniform across the CTA
-        uint32_t acc_bits[32];
-        tc05::tmem_ld_32x32b_x32(taddr_row + (uint32_t)(chunk * 32), acc_bits);
-        tc05::tmem_ld_wait();
-        if (!row_ok) continue;
-        float acc[32];
+      for (int grp = 0; grp < groups; ++grp) {
+        const int gcol0 = n_tile * BN + half * 128 + grp * group_cols;
+        if (gcol0 >= p.n) break;  // uniform across the warp
+        uint32_t gelu_packed[32];  // second output of the bias+gelu epilogue (64 bf16)
+        // the staging tile may still be read by the previous store
+        if (lane == 0) tc05::tma_store_wait_read();
+        __syncwarp();
 #pragma unroll
-        for (int i = 0; i < 32; ++i) acc[i] = __uint_as_float(acc_bits[i]);
-
-        if (p.partials != nullptr) {
-          float* dst = p.partials + ((size_t)split * p.m + row) * (size_t)p.n + col0;
+        for (int sub = 0; sub < 2; ++sub) {
+          if (sub * 32 >= group_cols) break;
+          const int col0 = gcol0 + sub * 32;
+          uint32_t acc_bits[32];
+          tc05::tmem_ld_32x32b_x32(taddr_row + (uint32_t)(half * 128 + grp * group_cols + sub * 32), acc_bits);
+          tc05::tmem_ld_wait();
 #pragma unroll
-          for (int g = 0; g < 8; ++g)
-            if (col0 + g * 4 < p.n)
-              *reinterpret_cast<float4*>(dst + g * 4) = make_float4(acc[g * 4], acc[g * 4 + 1], acc[g * 4 + 2], acc[g * 4 + 3]);
-          continue;
+          for (int g = 0; g < 4; ++g) {  // groups of 8 columns
+            const int col = col0 + g * 8;
+            float v[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(acc_bits[g * 8 + i]);
+            const bool col_ok = col < p.n;
+            if (!p.partial_out) {
+              if (p.bias != nullptr && col_ok) {
+                const float4 b0 = __ldg(reinterpret_cast<const float4*>(p.bias + col));
+                const float4 b1 = __ldg(reinterpret_cast<const float4*>(p.bias + col + 4));
+                v[0] += b0.x; v[1] += b0.y; v[2] += b0.z; v[3] += b0.w;
+                v[4] += b1.x; v[5] += b1.y; v[6] += b1.z; v[7] += b1.w;
+              }
+              if (p.epilogue == HL_EPI_BIAS_GELU) {
+                // h = bf16(acc + bias) is the main output; g = bf16(gelu(h)) the second one
+                float gl[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) { v[i] = bf16_round(v[i]); gl[i] = gelu_fwd_fast(v[i]); }
+                const int w = (sub * 4 + g) * 4;
+                gelu_packed[w] = pack_bf16x2(gl[0], gl[1]); gelu_packed[w + 1] = pack_bf16x2(gl[2], gl[3]);
+                gelu_packed[w + 2] = pack_bf16x2(gl[4], gl[5]); gelu_packed[w + 3] = pack_bf16x2(gl[6], gl[7]);
+              } else if (p.epilogue == HL_EPI_BIAS_RESIDUAL || p.epilogue == HL_EPI_DGELU) {
+                uint4 r = make_uint4(0, 0, 0, 0);
+                if (row_ok && col_ok)
+                  r = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(p.aux_in) +
+                                                           (size_t)row * p.ld_aux_in + col));
+                const float2 r0 = unpack_bf16x2(r.x), r1 = unpack_bf16x2(r.y), r2 = unpack_bf16x2(r.z), r3 = unpack_bf16x2(r.w);
+                const float rr[8] = {r0.x, r0.y, r1.x, r1.y, r2.x, r2.y, r3.x, r3.y};
+                if (p.epilogue == HL_EPI_BIAS_RESIDUAL) {
+                  // out = bf16(residual + bf16(acc + bias)): the two round trips of the block
+#pragma unroll
+                  for (int i = 0; i < 8; ++i) v[i] = rr[i] + bf16_round(v[i]);
+                } else {
+                  // out = acc * gelu'(h), h read from aux_in
+#pragma unroll
+                  for (int i = 0; i < 8; ++i) v[i] = v[i] * gelu_grad_fast(rr[i]);
+                }
+              }
+            }
+            if (out_bf16) {
+              stage_chunk(staging, lane, sub * 4 + g,
+                          make_uint4(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]), pack_bf16x2(v[4], v[5]),
+                                     pack_bf16x2(v[6], v[7])));
+            } else {
+              stage_chunk(staging, lane, g * 2, make_uint4(__float_as_uint(v[0]), __float_as_uint(v[1]),
+                                                           __float_as_uint(v[2]), __float_as_uint(v[3])));
+              stage_chunk(staging, lane, g * 2 + 1, make_uint4(__float_as_uint(v[4]), __float_as_uint(v[5]),
+                                                               __float_as_uint(v[6]), __float_as_uint(v[7])));
+            }
+          }
         }
+        tc05::fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          if (p.partial_out) tc05::tma_store_3d(&map_c, staging, gcol0, row0, split);
+          else tc05::tma_store_2d(&map_c, staging, gcol0, row0);
+          tc05::tma_store_commit();
+        }
+        if (p.epilogue == HL_EPI_BIAS_GELU && !p.partial_out) {
+          if (lane == 0) tc05::tma_store_wait_read();
+          __syncwarp();
 #pragma unroll
-        for (int g = 0; g < 4; ++g) {  // groups of 8 columns
-          const int col = col0 + g * 8;
-          if (col >= p.n) break;
-          float v[8];
-#pragma unroll
-          for (int i = 0; i < 8; ++i) v[i] = acc[g * 8 + i];
-          if (p.bias != nullptr) {
-            const float4 b0 = __ldg(reinterpret_cast<const float4*>(p.bias + col));
-            const float4 b1 = __ldg(reinterpret_cast<const float4*>(p.bias + col + 4));
-            v[0] += b0.x; v[1] += b0.y; v[2] += b0.z; v[3] += b0.w;
-            v[4] += b1.x; v[5] += b1.y; v[6] += b1.z; v[7] += b1.w;
-          }
-          if (p.epilogue == HL_EPI_BIAS_GELU) {
-            // h = bf16(acc + bias) is stored; g = bf16(gelu(h)) goes to aux_out.
-            float gl[8];
-#pragma unroll
-            for (int i = 0; i < 8; ++i) { v[i] = bf16_round(v[i]); gl[i] = gelu_fwd_f(v[i]); }
-            uint4 o;
-            o.x = pack_bf16x2(gl[0], gl[1]); o.y = pack_bf16x2(gl[2], gl[3]);
-            o.z = pack_bf16x2(gl[4], gl[5]); o.w = pack_bf16x2(gl[6], gl[7]);
-            *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.aux_out) + (size_t)row * p.ld_aux_out + col) = o;
-          } else if (p.epilogue == HL_EPI_BIAS_RESIDUAL) {
-            // out = bf16(residual + bf16(acc + bias)): the two round trips of the block.
-            const uint4 r = *reinterpret_cast<const uint4*>(
-                reinterpret_cast<const __nv_bfloat16*>(p.aux_in) + (size_t)row * p.ld_aux_in + col);
-            const float2 r0 = unpack_bf16x2(r.x), r1 = unpack_bf16x2(r.y), r2 = unpack_bf16x2(r.z), r3 = unpack_bf16x2(r.w);
-            const float rr[8] = {r0.x, r0.y, r1.x, r1.y, r2.x, r2.y, r3.x, r3.y};
-#pragma unroll
-            for (int i = 0; i < 8; ++i) v[i] = rr[i] + bf16_round(v[i]);
-          } else if (p.epilogue == HL_EPI_DGELU) {
-            // out = acc * gelu'(h), h read from aux_in.
-            const uint4 r = *reinterpret_cast<const uint4*>(
-                reinterpret_cast<const __nv_bfloat16*>(p.aux_in) + (size_t)row * p.ld_aux_in + col);
-            const float2 r0 = unpack_bf16x2(r.x), r1 = unpack_bf16x2(r.y), r2 = unpack_bf16x2(r.z), r3 = unpack_bf16x2(r.w);
-            const float hh[8] = {r0.x, r0.y, r1.x, r1.y, r2.x, r2.y, r3.x, r3.y};
-#pragma unroll
-            for (int i = 0; i < 8; ++i) v[i] = v[i] * gelu_grad_f(hh[i]);
-          }
-          if (p.out_dtype == HL_BF16) {
-            uint4 o;
-            o.x = pack_bf16x2(v[0], v[1]); o.y = pack_bf16x2(v[2], v[3]);
-            o.z = pack_bf16x2(v[4], v[5]); o.w = pack_bf16x2(v[6], v[7]);
-            *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.c) + (size_t)row * p.ldc + col) = o;
-          } else {
-            float* dst = reinterpret_cast<float*>(p.c) + (size_t)row * p.ldc + col;
-            *reinterpret_cast<float4*>(dst) = make_float4(v[0], v[1], v[2], v[3]);
-            *reinterpret_cast<float4*>(dst + 4) = make_float4(v[4], v[5], v[6], v[7]);
+          for (int q = 0; q < 8; ++q)
+            stage_chunk(staging, lane, q,
+                        make_uint4(gelu_packed[q * 4], gelu_packed[q * 4 + 1], gelu_packed[q * 4 + 2], gelu_packed[q * 4 + 3]));
+          tc05::fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            tc05::tma_store_2d(&map_aux, staging, gcol0, row0);
+            tc05::tma_store_commit();
           }
         }
       }
@@ -256,6 +289,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
       __syncwarp();
       if (lane == 0) tc05::mbar_arrive(&tail->tmem_empty[buf]);
     }
+    if (lane == 0) tc05::tma_store_wait_all();  // global writes are complete before the kernel ends
   }
 
   // ---------------------------------------------------------------------- teardown
@@ -288,14 +322,15 @@ __global__ void splitk_reduce_kernel(const float* __restrict__ partials, float* 
 }
 
 template <bool A_MN, bool B_MN>
-int launch_variant(hl_ctx* ctx, const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, int grid) {
+int launch_variant(hl_ctx* ctx, const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc,
+                   const CUtensorMap& maux, const GemmParams& p, int grid) {
   auto kern = gemm_bf16_tcgen05_kernel<A_MN, B_MN>;
   static bool configured = false;
   if (!configured) {
     HL_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GEMM_SMEM_BYTES));
     configured = true;
   }
-  kern<<<grid, GEMM_THREADS, GEMM_SMEM_BYTES, ctx->stream>>>(ma, mb, p);
+  kern<<<grid, GEMM_THREADS, GEMM_SMEM_BYTES, ctx->stream>>>(ma, mb, mc, maux, p);
   HL_LAUNCH_CHECK("gemm_bf16_tcgen05_kernel");
   count_launch(ctx);
   ctx->counters.gemm_tcgen05_launches += 1;
@@ -311,14 +346,20 @@ size_t gemm_splitk_workspace_bytes(const hl_gemm_desc* d, int sm_count, int* spl
   if (splits <= 0) {
     splits = 1;
     if (d->epilogue == HL_EPI_NONE && d->out_dtype == HL_F32) {
-      // Fill the machine when the output has few tiles and the contraction is long.
+      // Few output tiles and a long contraction: pick the split that fills whole waves best.
       const int tiles = m_tiles * n_tiles;
-      if (tiles < sm_count && k_blocks >= 16) splits = min(min(sm_count / tiles, k_blocks / 8), 32);
-      if (splits < 1) splits = 1;
+      if (tiles < sm_count && k_blocks >= 16) {
+        double best = (double)tiles / (double)(ceil_div(tiles, sm_count) * sm_count);
+        for (int s = 2; s <= 16 && k_blocks / s >= 8; ++s) {
+          const int items = tiles * s;
+          const double eff = (double)items / (double)(ceil_div(items, sm_count) * sm_count);
+          if (eff > best + 0.02) { best = eff; splits = s; }
+        }
+      }
     }
   }
-  splits = min(splits, k_blocks);
-  int per = ceil_div(k_blocks, splits);
+  splits = std::max(1, std::min(splits, k_blocks));
+  const int per = ceil_div(k_blocks, splits);
   splits = ceil_div(k_blocks, per);  // every split owns at least one k block
   if (splits_out) *splits_out = splits;
   return splits > 1 ? (size_t)splits * d->m * (size_t)d->n * sizeof(float) : 0;
@@ -338,11 +379,15 @@ int gemm_bf16_run(hl_ctx* ctx, const hl_gemm_desc* d, const void* a, const void*
   const bool a_mn = d->a_layout == HL_MN_MAJOR, b_mn = d->b_layout == HL_MN_MAJOR;
   HL_REQUIRE(d->lda >= (a_mn ? d->m : d->k) && d->ldb >= (b_mn ? d->n : d->k) && d->ldc >= d->n,
              "hl_gemm_bf16: leading dimension smaller than the row length");
+  const long long ld_aux_in = d->ld_aux_in > 0 ? d->ld_aux_in : d->ldc;
+  const long long ld_aux_out = d->ld_aux_out > 0 ? d->ld_aux_out : d->ldc;
   switch (d->epilogue) {
     case HL_EPI_NONE: break;
     case HL_EPI_BIAS: HL_REQUIRE(bias, "hl_gemm_bf16: bias epilogue needs a bias"); break;
     case HL_EPI_BIAS_GELU:
       HL_REQUIRE(bias && aux_out && d->out_dtype == HL_BF16, "hl_gemm_bf16: bias+gelu needs bias, aux_out and bf16 output");
+      HL_REQUIRE(ld_aux_out % 8 == 0 && ld_aux_out >= d->n && (reinterpret_cast<uintptr_t>(aux_out) & 15) == 0,
+                 "hl_gemm_bf16: aux_out must be 16-byte aligned with a row stride that is a multiple of 8");
       break;
     case HL_EPI_BIAS_RESIDUAL:
       HL_REQUIRE(bias && aux_in && d->out_dtype == HL_BF16, "hl_gemm_bf16: bias+residual needs bias, aux_in and bf16 output");
@@ -350,6 +395,9 @@ int gemm_bf16_run(hl_ctx* ctx, const hl_gemm_desc* d, const void* a, const void*
     case HL_EPI_DGELU: HL_REQUIRE(aux_in, "hl_gemm_bf16: dgelu epilogue needs aux_in"); break;
     default: return fail("hl_gemm_bf16: unknown epilogue");
   }
+  if (aux_in)
+    HL_REQUIRE(ld_aux_in % 8 == 0 && ld_aux_in >= d->n && (reinterpret_cast<uintptr_t>(aux_in) & 15) == 0,
+               "hl_gemm_bf16: aux_in must be 16-byte aligned with a row stride that is a multiple of 8");
   if (bias) HL_REQUIRE((reinterpret_cast<uintptr_t>(bias) & 15) == 0, "hl_gemm_bf16: bias must be 16-byte aligned");
 
   GemmParams p{};
@@ -363,20 +411,18 @@ int gemm_bf16_run(hl_ctx* ctx, const hl_gemm_desc* d, const void* a, const void*
   p.k_blocks_per_split = ceil_div(p.k_blocks, splits);
   p.epilogue = d->epilogue;
   p.out_dtype = d->out_dtype;
-  p.ldc = d->ldc;
-  p.ld_aux_in = d->ld_aux_in > 0 ? d->ld_aux_in : d->ldc;
-  p.ld_aux_out = d->ld_aux_out > 0 ? d->ld_aux_out : d->ldc;
-  p.c = c; p.bias = bias; p.aux_in = aux_in; p.aux_out = aux_out;
+  p.ld_aux_in = ld_aux_in;
+  p.bias = bias; p.aux_in = aux_in;
   p.status = ctx->status_dev;
-  p.partials = nullptr;
+  p.partial_out = 0;
   if (splits > 1) {
     HL_REQUIRE(d->epilogue == HL_EPI_NONE && d->out_dtype == HL_F32, "hl_gemm_bf16: split-K needs a plain f32 output");
-    HL_REQUIRE(d->n % 4 == 0, "hl_gemm_bf16: split-K needs n % 4 == 0");
     HL_REQUIRE(workspace != nullptr && workspace_bytes >= need, "hl_gemm_bf16: split-K scratch is too small");
-    p.partials = workspace;
+    HL_REQUIRE((reinterpret_cast<uintptr_t>(workspace) & 15) == 0, "hl_gemm_bf16: split-K scratch must be 16-byte aligned");
+    p.partial_out = 1;
   }
 
-  CUtensorMap ma, mb;
+  CUtensorMap ma, mb, mc, maux;
   int rc;
   if (a_mn) rc = make_tensor_map_bf16_2d(&ma, a, (uint64_t)d->m, (uint64_t)d->k, (uint64_t)d->lda, 64, BK);
   else      rc = make_tensor_map_bf16_2d(&ma, a, (uint64_t)d->k, (uint64_t)d->m, (uint64_t)d->lda, BK, BM);
@@ -384,14 +430,35 @@ int gemm_bf16_run(hl_ctx* ctx, const hl_gemm_desc* d, const void* a, const void*
   if (b_mn) rc = make_tensor_map_bf16_2d(&mb, b, (uint64_t)d->n, (uint64_t)d->k, (uint64_t)d->ldb, 64, BK);
   else      rc = make_tensor_map_bf16_2d(&mb, b, (uint64_t)d->k, (uint64_t)d->n, (uint64_t)d->ldb, BK, BN);
   if (rc != HL_OK) return rc;
+  if (p.partial_out) {
+    const uint64_t dims[3] = {(uint64_t)d->n, (uint64_t)d->m, (uint64_t)splits};
+    const uint64_t strides[2] = {(uint64_t)d->n * 4, (uint64_t)d->n * (uint64_t)d->m * 4};
+    const uint32_t box[3] = {32, 32, 1};
+    rc = make_tensor_map(&mc, HL_F32, 3, workspace, dims, strides, box);
+  } else {
+    const uint64_t dims[2] = {(uint64_t)d->n, (uint64_t)d->m};
+    const uint64_t strides[1] = {(uint64_t)d->ldc * (d->out_dtype == HL_BF16 ? 2u : 4u)};
+    const uint32_t box[2] = {d->out_dtype == HL_BF16 ? 64u : 32u, 32u};
+    rc = make_tensor_map(&mc, d->out_dtype, 2, c, dims, strides, box);
+  }
+  if (rc != HL_OK) return rc;
+  if (d->epilogue == HL_EPI_BIAS_GELU) {
+    const uint64_t dims[2] = {(uint64_t)d->n, (uint64_t)d->m};
+    const uint64_t strides[1] = {(uint64_t)ld_aux_out * 2};
+    const uint32_t box[2] = {64, 32};
+    rc = make_tensor_map(&maux, HL_BF16, 2, aux_out, dims, strides, box);
+    if (rc != HL_OK) return rc;
+  } else {
+    maux = mc;
+  }
 
   const int total = p.m_tiles * p.n_tiles * p.splits;
   const int grid = min(total, ctx->sm_count);
   ProfileScope prof(ctx, HL_PROF_GEMM, 2.0 * (double)d->m * (double)d->n * (double)d->k);
-  if (a_mn && b_mn) rc = launch_variant<true, true>(ctx, ma, mb, p, grid);
-  else if (a_mn)    rc = launch_variant<true, false>(ctx, ma, mb, p, grid);
-  else if (b_mn)    rc = launch_variant<false, true>(ctx, ma, mb, p, grid);
-  else              rc = launch_variant<false, false>(ctx, ma, mb, p, grid);
+  if (a_mn && b_mn) rc = launch_variant<true, true>(ctx, ma, mb, mc, maux, p, grid);
+  else if (a_mn)    rc = launch_variant<true, false>(ctx, ma, mb, mc, maux, p, grid);
+  else if (b_mn)    rc = launch_variant<false, true>(ctx, ma, mb, mc, maux, p, grid);
+  else              rc = launch_variant<false, false>(ctx, ma, mb, mc, maux, p, grid);
   if (rc != HL_OK) return rc;
   if (splits > 1) {
     const long long quads = (long long)d->m * (d->n / 4);

@@ -15,7 +15,15 @@ int layer_norm_forward_impl(hl_ctx* ctx, const void* x, int x_dtype, const float
                             int y_dtype, float* mean, float* rstd, int rows, int features, float eps);
 int layer_norm_backward_impl(hl_ctx* ctx, const void* x, int x_dtype, const float* gamma, const float* dy,
                              const float* mean, const float* rstd, const float* residual_grad, float* dx_f32,
-                             void* dx_bf16, float* dgamma, float* dbeta, int rows, int features);
+                             void* dx_bf16, float* dgamma, float* dbeta, float* dx_colsum, int rows, int features);
+bool layer_norm_fast_applicable(int x_dtype, int y_dtype, int features, const void* x, const void* y);
+int layer_norm_forward_fast(hl_ctx* ctx, const void* x, const float* gamma, const float* beta, void* y, float* mean,
+                            float* rstd, int rows, int features, float eps);
+int layer_norm_backward_fast(hl_ctx* ctx, const void* x, const float* gamma, const float* dy, const float* mean,
+                             const float* rstd, const float* residual, float* dx_f32, void* dx_bf16, float* dgamma,
+                             float* dbeta, float* dx_colsum, int rows, int features);
+bool colsum_fast_applicable(int dtype, int cols, const void* g);
+int colsum_fast(hl_ctx* ctx, const void* g, int dtype, float* out, int rows, int cols);
 int cross_entropy_impl(hl_ctx* ctx, const float* logits, long long ld, const int64_t* targets, int rows, int classes,
                        float grad_scale, float* loss_dev, float* row_loss, void* dlogits, int dlogits_dtype,
                        long long ld_dlogits);

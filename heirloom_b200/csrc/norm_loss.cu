@@ -3,7 +3,7 @@
 // kernels are one thread per element with per-element row re-reduction (layer norm,
 // heirloom-kernels/src/ptx/kernels.ptx:3296-3322) or a single thread for the whole loss
 // (heirloom-kernels/src/cuda.rs:10328-10339).
-#include "common.cuh"
+#include "kernels.h"
 
 namespace hl {
 namespace {
@@ -363,6 +363,9 @@ int layer_norm_forward_impl(hl_ctx* ctx, const void* x, int x_dtype, const float
   HL_REQUIRE(rows > 0 && features > 0, "hl_layer_norm_forward: rows and features must be positive");
   HL_REQUIRE(eps > 0.f, "hl_layer_norm_forward: eps must be positive");
   ProfileScope prof(ctx, HL_PROF_LAYER_NORM, (double)rows * features * (double)(dtype_size(x_dtype) + dtype_size(y_dtype)));
+  if (layer_norm_fast_applicable(x_dtype, y_dtype, features, x, y) &&
+      ((reinterpret_cast<uintptr_t>(gamma) | reinterpret_cast<uintptr_t>(beta)) & 15) == 0)
+    return layer_norm_forward_fast(ctx, x, gamma, beta, y, mean, rstd, rows, features, eps);
   const int warps = 4;
   const int grid = ceil_div(rows, warps);
   const bool vec = (features % 4 == 0) && ((reinterpret_cast<uintptr_t>(x) & 15) == 0) &&
@@ -390,7 +393,7 @@ int layer_norm_forward_impl(hl_ctx* ctx, const void* x, int x_dtype, const float
 
 int layer_norm_backward_impl(hl_ctx* ctx, const void* x, int x_dtype, const float* gamma, const float* dy,
                              const float* mean, const float* rstd, const float* residual_grad, float* dx_f32,
-                             void* dx_bf16, float* dgamma, float* dbeta, int rows, int features) {
+                             void* dx_bf16, float* dgamma, float* dbeta, float* dx_colsum, int rows, int features) {
   HL_REQUIRE(ctx && x && gamma && dy, "hl_layer_norm_backward: null argument");
   HL_REQUIRE(rows > 0 && features > 0, "hl_layer_norm_backward: rows and features must be positive");
   HL_REQUIRE(features % 4 == 0 && features <= LNB_MAXJ * 128,
@@ -398,6 +401,13 @@ int layer_norm_backward_impl(hl_ctx* ctx, const void* x, int x_dtype, const floa
   HL_REQUIRE(x_dtype == HL_F32 || x_dtype == HL_BF16, "hl_layer_norm_backward: x dtype must be f32 or bf16");
   ProfileScope prof(ctx, HL_PROF_LAYER_NORM,
                     (double)rows * features * (double)(dtype_size(x_dtype) + 4 + (residual_grad ? 4 : 0) + (dx_f32 ? 4 : 0) + (dx_bf16 ? 2 : 0)));
+  const uintptr_t align_bits = reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(gamma) |
+                               reinterpret_cast<uintptr_t>(dy) | reinterpret_cast<uintptr_t>(residual_grad) |
+                               reinterpret_cast<uintptr_t>(dx_f32) | reinterpret_cast<uintptr_t>(dx_bf16);
+  if (x_dtype == HL_BF16 && mean && rstd && features % 8 == 0 && (align_bits & 15) == 0)
+    return layer_norm_backward_fast(ctx, x, gamma, dy, mean, rstd, residual_grad, dx_f32, dx_bf16, dgamma, dbeta,
+                                    dx_colsum, rows, features);
+  HL_REQUIRE(!dx_colsum || dx_f32, "hl_layer_norm_backward: dx_colsum needs dx_f32 on this route");
   int blocks = std::min(ctx->sm_count * 2, ceil_div(rows, LNB_WARPS));
   const int rows_per_block = ceil_div(rows, blocks);
   blocks = ceil_div(rows, rows_per_block);
@@ -426,6 +436,7 @@ int layer_norm_backward_impl(hl_ctx* ctx, const void* x, int x_dtype, const floa
     count_launch(ctx);
   }
   count_launch(ctx);
+  if (dx_colsum) return bias_grad_impl(ctx, dx_f32, HL_F32, dx_colsum, rows, features);
   return HL_OK;
 }
 
@@ -477,9 +488,9 @@ int hl_layer_norm_forward(hl_ctx* ctx, const void* x, int x_dtype, const float* 
 
 int hl_layer_norm_backward(hl_ctx* ctx, const void* x, int x_dtype, const float* gamma, const float* dy,
                            const float* mean, const float* rstd, const float* residual_grad, float* dx_f32,
-                           void* dx_bf16, float* dgamma, float* dbeta, int rows, int features) {
+                           void* dx_bf16, float* dgamma, float* dbeta, float* dx_colsum, int rows, int features) {
   return layer_norm_backward_impl(ctx, x, x_dtype, gamma, dy, mean, rstd, residual_grad, dx_f32, dx_bf16, dgamma,
-                                  dbeta, rows, features);
+                                  dbeta, dx_colsum, rows, features);
 }
 
 int hl_embedding_forward(hl_ctx* ctx, const float* table, int table_rows, const int64_t* idx, const float* pos_table,

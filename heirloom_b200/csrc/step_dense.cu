@@ -290,25 +290,25 @@ int backward(hl_decoder* m) {
   HL_TRY(g.run(N, d, V, m->dlogits, V, HL_K_MAJOR, W + m->off_head_w, d, HL_MN_MAJOR, m->dtmp, d, HL_F32));
   float* dx = m->dx0;
   float* dx_next = m->dx1;
+  // every layer-norm backward also returns the column sums of the gradient it writes: the bias
+  // gradient of the projection that produced that residual-stream value (fc2 or out_proj)
   HL_TRY(layer_norm_backward_impl(ctx, m->x[c.n_layers], HL_BF16, P + m->off_lnf_g, m->dtmp, m->meanf, m->rstdf, nullptr, dx,
-                                  m->dxb, G + m->off_lnf_g, G + m->off_lnf_b, N, d));
+                                  m->dxb, G + m->off_lnf_g, G + m->off_lnf_b, G + m->lo[c.n_layers - 1].b2, N, d));
   HL_TRY(flush_buckets(m, m->off_lnf_b + d));
   for (int l = c.n_layers - 1; l >= 0; --l) {
     const LayerOffsets& o = m->lo[l];
     LayerActs& a = m->la[l];
     // y = r + fc2(gelu(fc1(c)));   dx is dL/dy (f32), dxb its bf16 operand copy
     HL_TRY(g.run(d, F, N, m->dxb, d, HL_MN_MAJOR, a.g, F, HL_MN_MAJOR, G + o.w2, F, HL_F32));
-    HL_TRY(bias_grad_impl(ctx, dx, HL_F32, G + o.b2, N, d));
     HL_TRY(g.run(N, F, d, m->dxb, d, HL_K_MAJOR, W + o.w2, F, HL_MN_MAJOR, m->dh, F, HL_BF16, HL_EPI_DGELU, nullptr, a.h, F));
     HL_TRY(g.run(F, d, N, m->dh, F, HL_MN_MAJOR, a.c, d, HL_MN_MAJOR, G + o.w1, d, HL_F32));
     HL_TRY(bias_grad_impl(ctx, m->dh, HL_BF16, G + o.b1, N, F));
     HL_TRY(g.run(N, d, F, m->dh, F, HL_K_MAJOR, W + o.w1, d, HL_MN_MAJOR, m->dtmp, d, HL_F32));
     // dr = dx + LN2'(dc)
     HL_TRY(layer_norm_backward_impl(ctx, a.r, HL_BF16, P + o.ln2g, m->dtmp, a.mean2, a.rstd2, dx, dx_next, m->dxb,
-                                    G + o.ln2g, G + o.ln2b, N, d));
+                                    G + o.ln2g, G + o.ln2b, G + o.bo, N, d));
     std::swap(dx, dx_next);  // dx is now dL/dr
     HL_TRY(g.run(d, d, N, m->dxb, d, HL_MN_MAJOR, a.o, d, HL_MN_MAJOR, G + o.wo, d, HL_F32));
-    HL_TRY(bias_grad_impl(ctx, dx, HL_F32, G + o.bo, N, d));
     HL_TRY(g.run(N, d, d, m->dxb, d, HL_K_MAJOR, W + o.wo, d, HL_MN_MAJOR, m->dob, d, HL_BF16));
     {
       const size_t need = flash_attention_backward_scratch_bytes(B, T, H, d / H);
@@ -322,7 +322,7 @@ int backward(hl_decoder* m) {
     HL_TRY(g.run(N, d, 3 * d, m->dqkv, 3 * d, HL_K_MAJOR, W + o.wqkv, d, HL_MN_MAJOR, m->dtmp, d, HL_F32));
     // dx_in = dr + LN1'(da)
     HL_TRY(layer_norm_backward_impl(ctx, m->x[l], HL_BF16, P + o.ln1g, m->dtmp, a.mean1, a.rstd1, dx, dx_next, m->dxb,
-                                    G + o.ln1g, G + o.ln1b, N, d));
+                                    G + o.ln1g, G + o.ln1b, l > 0 ? G + m->lo[l - 1].b2 : nullptr, N, d));
     std::swap(dx, dx_next);
     HL_TRY(flush_buckets(m, o.ln1b + d));
   }

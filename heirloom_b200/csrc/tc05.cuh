@@ -82,6 +82,24 @@ __device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* m
       ::"r"(smem_u32(smem_dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2)
       : "memory");
 }
+// TMA tile stores (shared -> global), tracked by bulk async-groups of the issuing thread.
+// Elements outside the tensor's extent are not written.
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, const void* smem_src, int c0, int c1) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(map),
+               "r"(smem_u32(smem_src)), "r"(c0), "r"(c1)
+               : "memory");
+}
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, const void* smem_src, int c0, int c1, int c2) {
+  asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(map),
+               "r"(smem_u32(smem_src)), "r"(c0), "r"(c1), "r"(c2)
+               : "memory");
+}
+__device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// The shared-memory sources of all committed stores have been read (safe to overwrite them).
+__device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+// All committed stores are complete.
+__device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* map) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
 }
@@ -182,6 +200,10 @@ __device__ __forceinline__ bool elect_one() {
 // time so the library does not link against libcuda.
 int make_tensor_map_bf16_2d(CUtensorMap* out, const void* base, uint64_t inner, uint64_t outer,
                             uint64_t row_stride_elems, uint32_t box_inner, uint32_t box_outer);
+// General form: `rank` dims (innermost first), byte strides for dims 1.., box extents, element
+// type HL_BF16 or HL_F32, 128-byte swizzle (the box's inner extent must span 128 bytes or less).
+int make_tensor_map(CUtensorMap* out, int dtype, int rank, const void* base, const uint64_t* dims,
+                    const uint64_t* strides_bytes, const uint32_t* box);
 int make_tensor_map_bf16_3d(CUtensorMap* out, const void* base, uint64_t d0, uint64_t d1, uint64_t d2,
                             uint64_t stride1_elems, uint64_t stride2_elems, uint32_t box0, uint32_t box1,
                             uint32_t box2);

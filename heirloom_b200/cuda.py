@@ -171,15 +171,19 @@ def layer_norm_forward(ctx: Context, x, gamma, beta, eps: float = 1e-5, out_dtyp
     return y, mean, rstd
 
 
-def layer_norm_backward(ctx: Context, x, gamma, dy, mean=None, rstd=None, residual_grad=None, want_bf16=False):
+def layer_norm_backward(ctx: Context, x, gamma, dy, mean=None, rstd=None, residual_grad=None, want_bf16=False,
+                        want_colsum=False):
     rows, feat = x.numel() // x.shape[-1], x.shape[-1]
     dx = torch.empty(x.shape, dtype=torch.float32, device=x.device)
     dxb = torch.empty(x.shape, dtype=torch.bfloat16, device=x.device) if want_bf16 else None
     dg = torch.empty(feat, dtype=torch.float32, device=x.device)
     db = torch.empty(feat, dtype=torch.float32, device=x.device)
+    cs = torch.empty(feat, dtype=torch.float32, device=x.device) if want_colsum else None
     check(ctx.lib.hl_layer_norm_backward(ctx.handle, _p(x), c_int(_dt(x)), _p(gamma), _p(dy), _p(mean), _p(rstd),
-                                         _p(residual_grad), _p(dx), _p(dxb), _p(dg), _p(db), c_int(rows), c_int(feat)))
-    return (dx, dxb, dg, db) if want_bf16 else (dx, dg, db)
+                                         _p(residual_grad), _p(dx), _p(dxb), _p(dg), _p(db), _p(cs), c_int(rows),
+                                         c_int(feat)))
+    out = (dx, dxb, dg, db) if want_bf16 else (dx, dg, db)
+    return out + (cs,) if want_colsum else out
 
 
 def embedding_forward(ctx: Context, table, idx, pos_table=None, out_dtype=torch.float32):

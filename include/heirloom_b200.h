@@ -127,10 +127,12 @@ int hl_layer_norm_forward(hl_ctx* ctx, const void* x, int x_dtype, const float* 
  *   dx = rstd*(F*dxhat - sum(dxhat) - xhat*sum(dxhat*xhat))/F  [+ residual_grad if given]
  *   dgamma = sum_rows dy*xhat, dbeta = sum_rows dy.
  * dy and residual_grad are f32; dx is written as f32 (dx_f32) and/or bf16 (dx_bf16), either
- * may be NULL.  mean/rstd as saved by the forward. */
+ * may be NULL.  mean/rstd as saved by the forward.  dx_colsum (may be NULL) receives the column
+ * sums of the dx written, i.e. the bias gradient of the linear layer whose output this layer
+ * norm consumed (the reference computes it with a separate kernel, kernels.ptx:312). */
 int hl_layer_norm_backward(hl_ctx* ctx, const void* x, int x_dtype, const float* gamma, const float* dy,
                            const float* mean, const float* rstd, const float* residual_grad, float* dx_f32,
-                           void* dx_bf16, float* dgamma, float* dbeta, int rows, int features);
+                           void* dx_bf16, float* dgamma, float* dbeta, float* dx_colsum, int rows, int features);
 
 /* ---- embedding -----------------------------------------------------------------------------
  * out[n,:] = table[idx[n],:] (+ pos_table[n % period,:] when pos_table != NULL, each term and

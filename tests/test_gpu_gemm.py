@@ -54,7 +54,8 @@ def test_gemm_epilogues_match_the_amp_rounding_points():
     h, g = cuda.gemm_bf16(c, da, db, m, n, k, epilogue=cuda.EPI_BIAS_GELU, bias=dev(bias), want_aux_out=True)
     hh = host(h)
     assert_close("h", hh, acc + bias, atol=1e-2, rtol=2 ** -7)
-    assert_close("g", host(g), ho.bf16_round(ho.gelu_value(hh)), atol=1e-6, rtol=2 ** -7)
+    # the epilogue uses the hardware tanh (relative error ~2^-11) before rounding to bf16
+    assert_close("g", host(g), ho.bf16_round(ho.gelu_value(hh)), atol=2e-3, rtol=2 ** -7)
     # bias + residual: bf16(res + bf16(acc + bias))
     res = ho.bf16_round(rng.standard_normal((m, n)))
     out = cuda.gemm_bf16(c, da, db, m, n, k, epilogue=cuda.EPI_BIAS_RESIDUAL, bias=dev(bias),
@@ -65,7 +66,7 @@ def test_gemm_epilogues_match_the_amp_rounding_points():
     hin = ho.bf16_round(rng.standard_normal((m, n)))
     out = cuda.gemm_bf16(c, da, db, m, n, k, epilogue=cuda.EPI_DGELU, aux_in=dev(hin, torch.bfloat16),
                          out_dtype=torch.float32)
-    assert_close("dgelu", host(out), acc * ho.gelu_backward(hin, np.ones_like(hin)), atol=2e-3, rtol=1e-4)
+    assert_close("dgelu", host(out), acc * ho.gelu_backward(hin, np.ones_like(hin)), atol=2e-2, rtol=2e-3)
 
 
 def test_gemm_split_k_is_deterministic_and_matches():
