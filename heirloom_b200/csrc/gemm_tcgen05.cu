@@ -57,7 +57,8 @@ struct SharedTail {
   int abort_flag;
 };
 
-// Write 8 consecutive 32-bit words pairs ... helper: one 16-byte chunk of a staging row.
+// One 16-byte chunk of row r of a [32 rows x 128 bytes] staging tile in the 128-byte swizzle
+// pattern the TMA store expects.
 __device__ __forceinline__ void stage_chunk(uint8_t* staging, int r, int chunk, uint4 v) {
   *reinterpret_cast<uint4*>(staging + r * 128 + ((chunk ^ (r & 7)) << 4)) = v;
 }
@@ -483,4 +484,61 @@ extern "C" int hl_gemm_bf16(hl_ctx* ctx, const hl_gemm_desc* desc, const void* a
   }
   return hl::gemm_bf16_run(ctx, desc, a, b, c, bias, aux_in, aux_out, reinterpret_cast<float*>(ctx->workspace),
                            ctx->workspace_bytes);
+}
+
+// ---- split-K GEMM for callers that must not allocate ----------------------------------------
+// hl_gemm_bf16 takes its split-K partial sums from the context's scratch arena and grows that
+// arena with the CUDA allocator when a call needs more.  Two kinds of callers of this library
+// cannot afford that: a host runtime that has already handed all free device memory to its own
+// caching pool (an allocator call there can fail, or succeed only by fragmenting the pool), and
+// a step loop whose compute and collective streams are running overlapped, where an allocator
+// call may wait for the whole device.  For them the same kernel runs here with its partial sums
+// in a fixed array that is part of the library image: every GPU that loads the library holds
+// these 32 MiB until the process exits.
+namespace hl {
+namespace {
+
+constexpr size_t kStaticScratchBytes = size_t(32) << 20;
+static __device__ __align__(256) unsigned char g_gemm_static_scratch[kStaticScratchBytes];
+
+constexpr int kMaxDevices = 64;
+void* g_static_scratch_addr[kMaxDevices] = {};  // device address of the array, per device ordinal
+
+// The array's name is only a host-side handle; the address a kernel can use has to be asked for,
+// once per device, with that device current.
+int static_scratch_address(hl_ctx* ctx, void** out) {
+  HL_REQUIRE(ctx->device >= 0 && ctx->device < kMaxDevices, "hl_gemm_bf16_static_scratch: device ordinal out of range");
+  if (g_static_scratch_addr[ctx->device] == nullptr) {
+    int current = -1;
+    HL_CUDA(cudaGetDevice(&current));
+    if (current != ctx->device) HL_CUDA(cudaSetDevice(ctx->device));
+    void* ptr = nullptr;
+    HL_CUDA(cudaGetSymbolAddress(&ptr, g_gemm_static_scratch));
+    HL_REQUIRE(ptr != nullptr, "hl_gemm_bf16_static_scratch: the static scratch array has no device address");
+    g_static_scratch_addr[ctx->device] = ptr;
+  }
+  *out = g_static_scratch_addr[ctx->device];
+  return HL_OK;
+}
+
+}  // namespace
+}  // namespace hl
+
+extern "C" int hl_gemm_bf16_static_scratch(hl_ctx* ctx, const hl_gemm_desc* desc, const void* a, const void* b, void* c,
+                                           const float* bias, const void* aux_in, void* aux_out) {
+  if (!ctx || !desc) return hl::fail("hl_gemm_bf16_static_scratch: null argument");
+  if (ctx->profiler)
+    return hl::fail("hl_gemm_bf16_static_scratch: per-kernel timing creates events; turn it off for calls that must not allocate");
+  const size_t need = hl::gemm_splitk_workspace_bytes(desc, ctx->sm_count, nullptr);
+  if (need > hl::kStaticScratchBytes)
+    return hl::fail("hl_gemm_bf16_static_scratch: this shape needs " + std::to_string(need) +
+                    " bytes of split-K scratch, more than the fixed " + std::to_string(hl::kStaticScratchBytes) +
+                    " bytes; lower split_k or use hl_gemm_bf16");
+  void* scratch = nullptr;
+  int rc = hl::static_scratch_address(ctx, &scratch);
+  if (rc != HL_OK) return rc;
+  // Nothing in the array has to start at zero: a split-K launch writes every partial sum that
+  // its reduction reads, so the previous call's contents are simply overwritten.
+  return hl::gemm_bf16_run(ctx, desc, a, b, c, bias, aux_in, aux_out, reinterpret_cast<float*>(scratch),
+                           hl::kStaticScratchBytes);
 }

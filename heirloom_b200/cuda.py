@@ -263,6 +263,18 @@ def gemm_bf16(ctx: Context, a: torch.Tensor, b: torch.Tensor, m: int, n: int, k:
     return (out, aux_out) if want_aux_out else out
 
 
+def gemm_bf16_static_scratch(ctx: Context, a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, m: int, n: int,
+                             k: int, a_layout=K_MAJOR, b_layout=K_MAJOR, split_k=0) -> torch.Tensor:
+    """`hl_gemm_bf16_static_scratch`: the split-K GEMM with its partial sums in the library's fixed
+    32 MiB array, for callers that must not reach the CUDA allocator.  `out` is supplied by the
+    caller (this wrapper allocates nothing either)."""
+    desc = GemmDesc(m, n, k, a_layout, b_layout, a.stride(0), b.stride(0), out.stride(0), EPI_NONE, _DT[out.dtype],
+                    split_k, 0, 0)
+    check(ctx.lib.hl_gemm_bf16_static_scratch(ctx.handle, byref(desc), _p(a), _p(b), _p(out), _p(None), _p(None),
+                                              _p(None)))
+    return out
+
+
 # ---- attention, f32 route ----------------------------------------------------------------------------
 def causal_attention_f32_forward(ctx: Context, q, k, v, n_heads: int):
     B, T, C = q.shape

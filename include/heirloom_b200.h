@@ -232,6 +232,22 @@ typedef struct {
 int hl_gemm_bf16(hl_ctx* ctx, const hl_gemm_desc* desc, const void* a, const void* b, void* c,
                  const float* bias, const void* aux_in, void* aux_out);
 
+/* The same GEMM for callers that must not allocate.  It has no counterpart in the reference.
+ * hl_gemm_bf16 keeps split-K partial sums in the context's scratch arena and grows that arena
+ * with the CUDA allocator when needed; a host runtime that has given all free device memory to
+ * its own pool, or a step loop whose compute and collective streams are overlapped (an allocator
+ * call may wait for the whole device), cannot afford that.  Here the partial sums live in a
+ * fixed 32 MiB array inside the library image, held by every GPU that loads the library until
+ * the process exits.  Shapes whose split-K scratch (splits * m * n * 4 bytes) exceeds 32 MiB are
+ * rejected with an error; nothing is allocated, freed or resized by this call.  The first call
+ * on a device looks up the array's device address (make that call before starting any stream
+ * capture).  All calls share the array and it keeps the previous call's contents (a split-K
+ * launch overwrites everything it later reads, so nothing needs clearing); two calls that
+ * overlap on the GPU, e.g. from two contexts on one device, race on it.  Per-kernel timing must
+ * be off.  Arguments and results are those of hl_gemm_bf16. */
+int hl_gemm_bf16_static_scratch(hl_ctx* ctx, const hl_gemm_desc* desc, const void* a, const void* b, void* c,
+                                const float* bias, const void* aux_in, void* aux_out);
+
 /* ---- causal flash attention, bf16 route ----------------------------------------------------
  * q, k, v: bf16 row-major views of [batch*time, *] with row stride ld_qkv and heads interleaved
  * along the channel dimension (column h*head_dim + j, src/tensor.rs:5156-5177), so the three
