@@ -89,37 +89,47 @@ ln_bwd_bf16_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict_
                    const float* __restrict__ mean_in, const float* __restrict__ rstd_in,
                    const float* __restrict__ residual, float* __restrict__ dx_f32, __nv_bfloat16* __restrict__ dx_bf16,
                    float* __restrict__ partial, int rows, int features, int rows_per_block) {
-  extern __shared__ float fold_smem[];  // [ROW_WARPS][3][features]
+  extern __shared__ float fold_smem[];  // [ROW_WARPS][3][features] then gamma[features]
+  float* gamma_s = fold_smem + (size_t)ROW_WARPS * 3 * features;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int r0 = blockIdx.x * rows_per_block, r1 = min(rows, r0 + rows_per_block);
-  float g[J][8], dg[J][8], db[J][8], ds[J][8];
+  for (int c = threadIdx.x; c < features; c += blockDim.x) gamma_s[c] = gamma[c];
+  __syncthreads();
+  float dg[J][8], db[J][8], ds[J][8];
 #pragma unroll
-  for (int j = 0; j < J; ++j) {
-    const int c = (j * 32 + lane) * 8;
-    if (c < features) load8_f32(gamma + c, g[j]);
+  for (int j = 0; j < J; ++j)
 #pragma unroll
     for (int e = 0; e < 8; ++e) { dg[j][e] = 0.f; db[j][e] = 0.f; ds[j][e] = 0.f; }
-  }
   const float inv_f = 1.0f / (float)features;
   for (int row = r0 + warp; row < r1; row += ROW_WARPS) {
     const size_t base = (size_t)row * features;
-    const float mean = mean_in[row], rstd = rstd_in[row];
-    float xh[J][8], d[J][8];
-    float s1 = 0.f, s2 = 0.f;
+    // every global read of the row is issued before anything is consumed
+    float xh[J][8], d[J][8], o[J][8];
 #pragma unroll
     for (int j = 0; j < J; ++j) {
       const int c = (j * 32 + lane) * 8;
       if (c < features) {
         load8_bf16(x + base + c, xh[j]);
         load8_f32(dy + base + c, d[j]);
+        if (residual) load8_f32(residual + base + c, o[j]);
+      }
+    }
+    const float mean = mean_in[row], rstd = rstd_in[row];
+    float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+    for (int j = 0; j < J; ++j) {
+      const int c = (j * 32 + lane) * 8;
+      if (c < features) {
+        float g[8];
+        load8_f32(gamma_s + c, g);
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
           xh[j][e] = (xh[j][e] - mean) * rstd;
-          const float dxhat = d[j][e] * g[j][e];
-          s1 += dxhat;
-          s2 += dxhat * xh[j][e];
           dg[j][e] += d[j][e] * xh[j][e];
           db[j][e] += d[j][e];
+          d[j][e] *= g[e];  // dxhat
+          s1 += d[j][e];
+          s2 += d[j][e] * xh[j][e];
         }
       }
     }
@@ -129,20 +139,14 @@ ln_bwd_bf16_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict_
     for (int j = 0; j < J; ++j) {
       const int c = (j * 32 + lane) * 8;
       if (c < features) {
-        float o[8];
-        if (residual) load8_f32(residual + base + c, o);
-        else {
-#pragma unroll
-          for (int e = 0; e < 8; ++e) o[e] = 0.f;
-        }
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
-          const float dxhat = d[j][e] * g[j][e];
-          o[e] += rstd * ((float)features * dxhat - s1 - xh[j][e] * s2) * inv_f;
-          ds[j][e] += o[e];
+          const float dxv = rstd * ((float)features * d[j][e] - s1 - xh[j][e] * s2) * inv_f;
+          o[j][e] = residual ? o[j][e] + dxv : dxv;
+          ds[j][e] += o[j][e];
         }
-        if (dx_f32) store8_f32(dx_f32 + base + c, o);
-        if (dx_bf16) store8_bf16(dx_bf16 + base + c, o);
+        if (dx_f32) store8_f32(dx_f32 + base + c, o[j]);
+        if (dx_bf16) store8_bf16(dx_bf16 + base + c, o[j]);
       }
     }
   }
@@ -260,7 +264,7 @@ int layer_norm_backward_fast(hl_ctx* ctx, const void* x, const float* gamma, con
   int rc = ensure_workspace(ctx, sizeof(float) * (size_t)blocks * 3 * features);
   if (rc != HL_OK) return rc;
   float* partial = reinterpret_cast<float*>(ctx->workspace);
-  const size_t smem = sizeof(float) * ROW_WARPS * 3 * (size_t)features;
+  const size_t smem = sizeof(float) * (ROW_WARPS * 3 + 1) * (size_t)features;
   const int J = ceil_div(features, 256);
 #define HL_LAUNCH(JJ)                                                                                             \
   do {                                                                                                            \

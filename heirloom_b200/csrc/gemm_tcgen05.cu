@@ -182,6 +182,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
     const bool out_bf16 = !p.partial_out && p.out_dtype == HL_BF16;
     const int group_cols = out_bf16 ? 64 : 32;  // columns per 128-byte staging row
     const int groups = 128 / group_cols;
+    const bool need_aux = !p.partial_out && (p.epilogue == HL_EPI_BIAS_RESIDUAL || p.epilogue == HL_EPI_DGELU);
     int local = 0;
     bool ok = true;
     for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x, ++local) {
@@ -202,6 +203,19 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
         const int gcol0 = n_tile * BN + half * 128 + grp * group_cols;
         if (gcol0 >= p.n) break;  // uniform across the warp
         uint32_t gelu_packed[32];  // second output of the bias+gelu epilogue (64 bf16)
+        // All residual / pre-activation reads of this group are issued up front so their
+        // latencies overlap each other and the tensor-memory loads.
+        uint4 aux_pref[8];
+        if (need_aux) {
+#pragma unroll
+          for (int q = 0; q < 8; ++q) {
+            const int col = gcol0 + q * 8;
+            aux_pref[q] = make_uint4(0, 0, 0, 0);
+            if (q * 8 < group_cols && row_ok && col < p.n)
+              aux_pref[q] = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(p.aux_in) +
+                                                                 (size_t)row * p.ld_aux_in + col));
+          }
+        }
         // the staging tile may still be read by the previous store
         if (lane == 0) tc05::tma_store_wait_read();
         __syncwarp();
@@ -235,10 +249,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
                 gelu_packed[w] = pack_bf16x2(gl[0], gl[1]); gelu_packed[w + 1] = pack_bf16x2(gl[2], gl[3]);
                 gelu_packed[w + 2] = pack_bf16x2(gl[4], gl[5]); gelu_packed[w + 3] = pack_bf16x2(gl[6], gl[7]);
               } else if (p.epilogue == HL_EPI_BIAS_RESIDUAL || p.epilogue == HL_EPI_DGELU) {
-                uint4 r = make_uint4(0, 0, 0, 0);
-                if (row_ok && col_ok)
-                  r = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(p.aux_in) +
-                                                           (size_t)row * p.ld_aux_in + col));
+                const uint4 r = aux_pref[sub * 4 + g];
                 const float2 r0 = unpack_bf16x2(r.x), r1 = unpack_bf16x2(r.y), r2 = unpack_bf16x2(r.z), r3 = unpack_bf16x2(r.w);
                 const float rr[8] = {r0.x, r0.y, r1.x, r1.y, r2.x, r2.y, r3.x, r3.y};
                 if (p.epilogue == HL_EPI_BIAS_RESIDUAL) {

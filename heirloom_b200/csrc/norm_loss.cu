@@ -347,6 +347,49 @@ __global__ void cross_entropy_kernel(const float* __restrict__ logits, long long
   }
 }
 
+// bf16-gradient route: persistent blocks walk rows, so only a few hundred rows (tens of MB)
+// are in flight and the second read of a row is served by L2.  Pass 1 is an online
+// max / sum-of-exponentials (one read), pass 2 writes dlogits = (softmax - onehot) * scale.
+__global__ void __launch_bounds__(1024)
+cross_entropy_online_kernel(const float* __restrict__ logits, long long ld, const int64_t* __restrict__ targets,
+                            int rows, int classes, float scale, float* __restrict__ row_loss,
+                            __nv_bfloat16* __restrict__ dlogits, long long ld_d, int* __restrict__ status) {
+  __shared__ float sm[32];
+  constexpr float kLog2e = 1.4426950408889634f;
+  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+    const float* z = logits + (size_t)row * ld;
+    const long long target = targets[row];
+    if (target < 0 || target >= classes) {
+      if (threadIdx.x == 0) { atomicExch(status + ST_BAD_INDEX, 1); if (row_loss) row_loss[row] = 0.f; }
+      continue;
+    }
+    float m = -INFINITY, s = 0.f;
+    for (int c = threadIdx.x * 4; c < classes; c += blockDim.x * 4) {
+      const float4 v = *reinterpret_cast<const float4*>(z + c);
+      const float mx = fmaxf(fmaxf(v.x, v.y), fmaxf(v.z, v.w));
+      if (mx > m) { s *= exp2f((m - mx) * kLog2e); m = mx; }
+      s += exp2f((v.x - m) * kLog2e) + exp2f((v.y - m) * kLog2e) + exp2f((v.z - m) * kLog2e) + exp2f((v.w - m) * kLog2e);
+    }
+    const float big = block_max(m, sm, -INFINITY);
+    const float total = block_sum(s * exp2f((m - big) * kLog2e), sm);
+    if (threadIdx.x == 0 && row_loss) row_loss[row] = -z[target] + big + logf(total);
+    if (dlogits != nullptr) {
+      const float inv = scale / total;
+      __nv_bfloat16* d = dlogits + (size_t)row * ld_d;
+      for (int c = threadIdx.x * 4; c < classes; c += blockDim.x * 4) {
+        const float4 v = *reinterpret_cast<const float4*>(z + c);
+        float o[4] = {exp2f((v.x - big) * kLog2e) * inv, exp2f((v.y - big) * kLog2e) * inv,
+                      exp2f((v.z - big) * kLog2e) * inv, exp2f((v.w - big) * kLog2e) * inv};
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+          if (c + e == target) o[e] -= scale;
+        Vec<__nv_bfloat16>::store(d + c, o);
+      }
+    }
+    __syncthreads();  // sm is reused by the next row
+  }
+}
+
 __global__ void mean_rows_kernel(const float* __restrict__ row_loss, int rows, float* __restrict__ out) {
   __shared__ double sm[32];
   double acc = 0.0;
@@ -459,7 +502,13 @@ int cross_entropy_impl(hl_ctx* ctx, const float* logits, long long ld, const int
   const float scale = grad_scale / (float)rows;
   ProfileScope prof(ctx, HL_PROF_LOSS, (double)rows * classes * (4.0 + (dlogits ? (double)dtype_size(dlogits_dtype) : 0.0)));
   const int threads = classes >= 4096 ? 512 : 256;
-  if (dlogits && dlogits_dtype == HL_BF16)
+  const bool online_ok = (!dlogits || dlogits_dtype == HL_BF16) && classes % 4 == 0 && ld % 4 == 0 && ld_dlogits % 4 == 0 &&
+                         (reinterpret_cast<uintptr_t>(logits) & 15) == 0 && (reinterpret_cast<uintptr_t>(dlogits) & 7) == 0 &&
+                         classes >= 1024;
+  if (online_ok && (dlogits || dlogits_dtype == HL_BF16))
+    cross_entropy_online_kernel<<<std::min(rows, ctx->sm_count * 2), 1024, 0, ctx->stream>>>(
+        logits, ld, targets, rows, classes, scale, rl, (__nv_bfloat16*)dlogits, ld_dlogits, ctx->status_dev);
+  else if (dlogits && dlogits_dtype == HL_BF16)
     cross_entropy_kernel<float, __nv_bfloat16><<<rows, threads, 0, ctx->stream>>>(
         logits, ld, targets, rows, classes, scale, rl, (__nv_bfloat16*)dlogits, ld_dlogits, ctx->status_dev);
   else

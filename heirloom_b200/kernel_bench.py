@@ -1,0 +1,163 @@
+"""Kernel-level sweep of the training step's pieces, one JSON line per case.
+
+    python -m heirloom_b200.kernel_bench                      # everything
+    python -m heirloom_b200.kernel_bench --only gemm          # cases whose name contains "gemm"
+    python -m heirloom_b200.kernel_bench --only fc1_fwd --iters 3 --warmup 1   # small run for a profiler
+
+Cases: the bf16 GEMM shapes of the GPT-124M-shaped step (forward, input gradient, weight gradient),
+causal attention forward/backward (batch 16, 12 heads, head_dim 64, T 1024), layer norm and GELU
+over 16384 x 768 / 16384 x 3072, fused cross-entropy over 16384 x 50304, bias column sums and the
+fused AdamW over 124 M parameters.  Inputs are N(0,1) from torch's generator with seed 0.
+Each case reports time from CUDA events on the library's compute stream, the algorithmic work
+(flop or bytes) and the fraction of the measured peak (MEASURED_PEAKS.json when present).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import sys
+from pathlib import Path
+
+import torch
+
+ROOT = Path(__file__).resolve().parents[1]
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+from heirloom_b200 import cuda  # noqa: E402
+
+N, D, F, V, B, T, H = 16384, 768, 3072, 50304, 16, 1024, 12
+K_, MN = cuda.K_MAJOR, cuda.MN_MAJOR
+
+
+def peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return d["hbm_gbs"], d["bf16_tflops"], "measured"
+    return 6650.0, 1590.0, "fallback"
+
+
+def timed(ctx, fn, iters, warmup):
+    for _ in range(warmup):
+        fn()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ctx.sync()
+    e0.record(ctx.stream)
+    for _ in range(iters):
+        fn()
+    e1.record(ctx.stream)
+    ctx.sync()
+    return e0.elapsed_time(e1) / iters
+
+
+def bf16(*shape):
+    return torch.randn(*shape, device="cuda").to(torch.bfloat16)
+
+
+def gemm_case(ctx, m, n, k, al, bl, out_dtype=torch.bfloat16, epi=cuda.EPI_NONE):
+    a = bf16(*((m, k) if al == K_ else (k, m)))
+    b = bf16(*((n, k) if bl == K_ else (k, n)))
+    out = torch.empty(m, n, dtype=out_dtype, device="cuda")
+    bias = torch.zeros(n, device="cuda") if epi in (cuda.EPI_BIAS, cuda.EPI_BIAS_GELU, cuda.EPI_BIAS_RESIDUAL) else None
+    aux = bf16(m, n) if epi in (cuda.EPI_BIAS_RESIDUAL, cuda.EPI_DGELU) else None
+    want_aux = epi == cuda.EPI_BIAS_GELU
+    fn = lambda: cuda.gemm_bf16(ctx, a, b, m, n, k, al, bl, epi, out_dtype, bias, aux, want_aux, out=out)
+    return fn, 2.0 * m * n * k, "flop"
+
+
+def build_cases(ctx):
+    cases = {}
+    g = lambda *a, **kw: (lambda: gemm_case(ctx, *a, **kw))
+    cases["gemm_qkv_fwd"] = g(N, 3 * D, D, K_, K_, epi=cuda.EPI_BIAS)
+    cases["gemm_out_proj_fwd"] = g(N, D, D, K_, K_, epi=cuda.EPI_BIAS_RESIDUAL)
+    cases["gemm_fc1_fwd"] = g(N, F, D, K_, K_, epi=cuda.EPI_BIAS_GELU)
+    cases["gemm_fc2_fwd"] = g(N, D, F, K_, K_, epi=cuda.EPI_BIAS_RESIDUAL)
+    cases["gemm_lm_head_fwd"] = g(N, V, D, K_, K_, torch.float32, cuda.EPI_BIAS)
+    cases["gemm_lm_head_wgrad"] = g(V, D, N, MN, MN, torch.float32)
+    cases["gemm_lm_head_dgrad"] = g(N, D, V, K_, MN, torch.float32)
+    cases["gemm_fc2_wgrad"] = g(D, F, N, MN, MN, torch.float32)
+    cases["gemm_fc2_dgrad_dgelu"] = g(N, F, D, K_, MN, epi=cuda.EPI_DGELU)
+    cases["gemm_fc1_wgrad"] = g(F, D, N, MN, MN, torch.float32)
+    cases["gemm_fc1_dgrad"] = g(N, D, F, K_, MN, torch.float32)
+    cases["gemm_out_proj_wgrad"] = g(D, D, N, MN, MN, torch.float32)
+    cases["gemm_out_proj_dgrad"] = g(N, D, D, K_, MN)
+    cases["gemm_qkv_wgrad"] = g(3 * D, D, N, MN, MN, torch.float32)
+    cases["gemm_qkv_dgrad"] = g(N, D, 3 * D, K_, MN, torch.float32)
+    cases["gemm_4096_768_768"] = g(4096, D, D, K_, K_)
+
+    def attn_fwd():
+        qkv = bf16(N, 3 * D)
+        q, k, v = qkv[:, :D], qkv[:, D:2 * D], qkv[:, 2 * D:]
+        return (lambda: cuda.flash_attention_forward(ctx, q, k, v, B, T, H)), 2.0 * B * H * T * T * 64, "flop"
+
+    def attn_bwd():
+        qkv = bf16(N, 3 * D)
+        q, k, v = qkv[:, :D], qkv[:, D:2 * D], qkv[:, 2 * D:]
+        out, lse = cuda.flash_attention_forward(ctx, q, k, v, B, T, H)
+        do = bf16(N, D)
+        return (lambda: cuda.flash_attention_backward(ctx, q, k, v, out, do, lse, B, T, H)), 5.0 * B * H * T * T * 64, "flop"
+
+    def ln_fwd():
+        x, w, b = bf16(N, D), torch.ones(D, device="cuda"), torch.zeros(D, device="cuda")
+        return (lambda: cuda.layer_norm_forward(ctx, x, w, b)), N * D * 4.0, "bytes"
+
+    def ln_bwd():
+        x, w, b = bf16(N, D), torch.ones(D, device="cuda"), torch.zeros(D, device="cuda")
+        _, mean, rstd = cuda.layer_norm_forward(ctx, x, w, b)
+        dy, res = torch.randn(N, D, device="cuda"), torch.randn(N, D, device="cuda")
+        return (lambda: cuda.layer_norm_backward(ctx, x, w, dy, mean, rstd, res, want_bf16=True, want_colsum=True)), \
+            N * D * 16.0, "bytes"
+
+    def gelu_fwd():
+        x = bf16(N, F)
+        return (lambda: cuda.gelu(ctx, x)), N * F * 4.0, "bytes"
+
+    def ce():
+        z = torch.randn(N, V, device="cuda")
+        t = torch.randint(0, V, (N,), device="cuda")
+        return (lambda: cuda.cross_entropy(ctx, z, t, dlogits_dtype=torch.bfloat16)), N * V * 6.0, "bytes"
+
+    def colsum():
+        x = bf16(N, V)
+        return (lambda: cuda.bias_grad(ctx, x)), N * V * 2.0, "bytes"
+
+    def adamw():
+        n = 124_000_000
+        p, g_, m, v = (torch.randn(n, device="cuda") for _ in range(4))
+        v.abs_()
+        hp = cuda.adamw_params(1e-3, 0.9, 0.999, 1e-8, 0.01, 1.0, 1)
+        return (lambda: cuda.adamw_update_multi(ctx, [p], [g_], [m], [v], hp)), n * 28.0, "bytes"
+
+    cases.update(attention_fwd_t1024=attn_fwd, attention_bwd_t1024=attn_bwd, layer_norm_fwd=ln_fwd, layer_norm_bwd=ln_bwd,
+                 gelu_fwd_16384x3072=gelu_fwd, cross_entropy_16384x50304=ce, bias_colsum_16384x50304=colsum,
+                 adamw_124m=adamw)
+    return cases
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--only", default="")
+    ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    args = ap.parse_args()
+    torch.manual_seed(0)
+    ctx = cuda.Context(0)
+    hbm, tf, src = peaks()
+    for name, make in build_cases(ctx).items():
+        if args.only and args.only not in name:
+            continue
+        fn, work, unit = make()
+        ms = timed(ctx, fn, args.iters, args.warmup)
+        if unit == "flop":
+            rate, peak, runit = work / ms / 1e9, tf, "TFLOP/s"
+        else:
+            rate, peak, runit = work / ms / 1e6, hbm, "GB/s"
+        print(json.dumps({"case": name, "us": round(ms * 1e3, 2), "achieved": round(rate, 1), "unit": runit,
+                          "peak": peak, "frac": round(rate / peak, 4), "peak_source": src}), flush=True)
+        del fn
+        torch.cuda.empty_cache()
+
+
+if __name__ == "__main__":
+    main()
