@@ -80,6 +80,14 @@ struct hl_decoder {
   std::vector<cudaEvent_t> bucket_ready;
   cudaEvent_t comm_done = nullptr;
   unsigned long long launches_last_step = 0;
+  // f32 route (reference f32 semantics: f32 tensors, f64 accumulation inside every op)
+  struct F32Layer {
+    float *a, *q, *k, *v, *probs, *o, *pr, *r, *c, *h, *g, *f;
+  };
+  std::vector<float*> xf;  // residual stream per block input, f32
+  std::vector<F32Layer> lf;
+  float *zf = nullptr, *tmp_f = nullptr, *tmp2_f = nullptr, *dlogits_f = nullptr, *d_a = nullptr, *d_b = nullptr,
+        *d_c = nullptr, *d_q = nullptr, *d_k = nullptr, *d_v = nullptr, *d_wide = nullptr, *d_wide2 = nullptr;
 };
 
 namespace hl {
@@ -194,6 +202,51 @@ int plan_activations(hl_decoder* m, bool measure_only, size_t* bytes_out) {
   m->dh = carve<__nv_bfloat16>(cur, N * F);
   m->dob = carve<__nv_bfloat16>(cur, N * d);
   m->dqkv = carve<__nv_bfloat16>(cur, N * 3 * d);
+  m->tokens = carve<int64_t>(cur, N);
+  m->targets = carve<int64_t>(cur, N);
+  m->loss_dev = carve<float>(cur, 4);
+  m->norm_dev = carve<float>(cur, 4);
+  *bytes_out = (size_t)(cur - base);
+  return HL_OK;
+}
+
+int plan_activations_f32(hl_decoder* m, bool measure_only, size_t* bytes_out) {
+  const hl_decoder_config& c = m->cfg;
+  const size_t N = (size_t)m->N, d = c.d_model, F = c.d_ff, V = c.vocab, L = c.n_layers;
+  const size_t BHTT = (size_t)c.batch * c.n_heads * c.context * c.context;
+  uint8_t* cur = measure_only ? nullptr : m->act_arena;
+  uint8_t* base = cur;
+  m->xf.resize(L + 1);
+  m->lf.resize(L);
+  for (size_t l = 0; l <= L; ++l) m->xf[l] = carve<float>(cur, N * d);
+  for (size_t l = 0; l < L; ++l) {
+    hl_decoder::F32Layer& a = m->lf[l];
+    a.a = carve<float>(cur, N * d);
+    a.q = carve<float>(cur, N * d);
+    a.k = carve<float>(cur, N * d);
+    a.v = carve<float>(cur, N * d);
+    a.probs = carve<float>(cur, BHTT);
+    a.o = carve<float>(cur, N * d);
+    a.pr = carve<float>(cur, N * d);
+    a.r = carve<float>(cur, N * d);
+    a.c = carve<float>(cur, N * d);
+    a.h = carve<float>(cur, N * F);
+    a.g = carve<float>(cur, N * F);
+    a.f = carve<float>(cur, N * d);
+  }
+  m->zf = carve<float>(cur, N * d);
+  m->logits = carve<float>(cur, N * V);
+  m->dlogits_f = carve<float>(cur, N * V);
+  m->tmp_f = carve<float>(cur, N * std::max(std::max(d, F), V));
+  m->tmp2_f = carve<float>(cur, N * d);
+  m->d_a = carve<float>(cur, N * d);
+  m->d_b = carve<float>(cur, N * d);
+  m->d_c = carve<float>(cur, N * d);
+  m->d_q = carve<float>(cur, N * d);
+  m->d_k = carve<float>(cur, N * d);
+  m->d_v = carve<float>(cur, N * d);
+  m->d_wide = carve<float>(cur, N * F);
+  m->d_wide2 = carve<float>(cur, N * F);
   m->tokens = carve<int64_t>(cur, N);
   m->targets = carve<int64_t>(cur, N);
   m->loss_dev = carve<float>(cur, 4);
@@ -337,6 +390,104 @@ int backward(hl_decoder* m) {
   return HL_OK;
 }
 
+// ---- f32 route ---------------------------------------------------------------------------------
+// Op by op what the reference's f32 path does (MemoryTransformerLm::forward / loss,
+// src/memory_transformer.rs:2069-2081, :1604-1610; Linear = matmul(weight.transpose()) then
+// add(bias), src/nn.rs:454-475), every op rounding its f32 result from an f64 accumulation.
+hl_matrix_layout dense(long long rows, long long cols) { return hl_matrix_layout{rows, cols, cols, 1, 0}; }
+hl_matrix_layout transposed(long long rows, long long cols) { return hl_matrix_layout{cols, rows, 1, cols, 0}; }  // view of [rows, cols] storage
+
+int linear_f32(hl_decoder* m, const float* x, const float* w, const float* b, float* y, int rows, int in, int out) {
+  // y = x · Wᵀ (rounded), then + b (rounded)
+  const hl_matrix_layout lx = dense(rows, in), lw = transposed(out, in), ly = dense(rows, out);
+  HL_TRY(hl_matmul_f32_strided(m->ctx, x, &lx, w, &lw, m->tmp_f, &ly, 0));
+  return hl_bias_add_f32(m->ctx, m->tmp_f, b, y, rows, out);
+}
+
+int linear_backward_f32(hl_decoder* m, const float* x, const float* w, const float* dy, float* dx, int accumulate_dx,
+                        float* dw, float* db, int rows, int in, int out) {
+  const hl_matrix_layout ldy = dense(rows, out), lw = dense(out, in), ldx = dense(rows, in);
+  if (dx) HL_TRY(hl_matmul_f32_strided(m->ctx, dy, &ldy, w, &lw, dx, &ldx, accumulate_dx));
+  const hl_matrix_layout ldyt = transposed(rows, out), lx = dense(rows, in), ldw = dense(out, in);
+  HL_TRY(hl_matmul_f32_strided(m->ctx, dy, &ldyt, x, &lx, dw, &ldw, 0));
+  return bias_grad_impl(m->ctx, dy, HL_F32, db, rows, out);
+}
+
+int forward_f32(hl_decoder* m) {
+  hl_ctx* ctx = m->ctx;
+  const hl_decoder_config& c = m->cfg;
+  const int N = m->N, d = c.d_model, F = c.d_ff, V = c.vocab, B = c.batch, T = c.context, H = c.n_heads;
+  const float* P = m->params;
+  HL_TRY(hl_embedding_forward(ctx, P + m->off_tok, V, m->tokens, P + m->off_pos, T, m->xf[0], HL_F32, N, d));
+  for (int l = 0; l < c.n_layers; ++l) {
+    const LayerOffsets& o = m->lo[l];
+    hl_decoder::F32Layer& a = m->lf[l];
+    HL_TRY(layer_norm_forward_impl(ctx, m->xf[l], HL_F32, P + o.ln1g, P + o.ln1b, a.a, HL_F32, nullptr, nullptr, N, d, 1e-5f));
+    HL_TRY(linear_f32(m, a.a, P + o.wqkv, P + o.bqkv, a.q, N, d, d));
+    HL_TRY(linear_f32(m, a.a, P + o.wqkv + (size_t)d * d, P + o.bqkv + d, a.k, N, d, d));
+    HL_TRY(linear_f32(m, a.a, P + o.wqkv + 2 * (size_t)d * d, P + o.bqkv + 2 * d, a.v, N, d, d));
+    HL_TRY(hl_causal_attention_f32_forward(ctx, a.q, a.k, a.v, a.o, a.probs, B, T, d, H));
+    HL_TRY(linear_f32(m, a.o, P + o.wo, P + o.bo, a.pr, N, d, d));
+    HL_TRY(hl_binary_f32(ctx, HL_ADD, m->xf[l], a.pr, a.r, (size_t)N * d));
+    HL_TRY(layer_norm_forward_impl(ctx, a.r, HL_F32, P + o.ln2g, P + o.ln2b, a.c, HL_F32, nullptr, nullptr, N, d, 1e-5f));
+    HL_TRY(linear_f32(m, a.c, P + o.w1, P + o.b1, a.h, N, d, F));
+    HL_TRY(hl_gelu(ctx, a.h, a.g, HL_F32, (size_t)N * F));
+    HL_TRY(linear_f32(m, a.g, P + o.w2, P + o.b2, a.f, N, F, d));
+    HL_TRY(hl_binary_f32(ctx, HL_ADD, a.r, a.f, m->xf[l + 1], (size_t)N * d));
+  }
+  HL_TRY(layer_norm_forward_impl(ctx, m->xf[c.n_layers], HL_F32, P + m->off_lnf_g, P + m->off_lnf_b, m->zf, HL_F32, nullptr,
+                                 nullptr, N, d, 1e-5f));
+  return linear_f32(m, m->zf, P + m->off_head_w, P + m->off_head_b, m->logits, N, d, V);
+}
+
+int backward_f32(hl_decoder* m) {
+  hl_ctx* ctx = m->ctx;
+  const hl_decoder_config& c = m->cfg;
+  const int N = m->N, d = c.d_model, F = c.d_ff, V = c.vocab, B = c.batch, T = c.context, H = c.n_heads;
+  const float* P = m->params;
+  float* G = m->grads;
+  m->next_bucket = 0;
+  HL_TRY(cross_entropy_impl(ctx, m->logits, V, m->targets, N, V, 1.0f, m->loss_dev, nullptr, m->dlogits_f, HL_F32, V));
+  float* dx = m->d_a;       // gradient of the residual stream
+  float* dx_next = m->d_b;
+  HL_TRY(linear_backward_f32(m, m->zf, P + m->off_head_w, m->dlogits_f, m->d_c, 0, G + m->off_head_w, G + m->off_head_b, N,
+                             d, V));
+  HL_TRY(layer_norm_backward_impl(ctx, m->xf[c.n_layers], HL_F32, P + m->off_lnf_g, m->d_c, nullptr, nullptr, nullptr, dx,
+                                  nullptr, G + m->off_lnf_g, G + m->off_lnf_b, nullptr, N, d));
+  HL_TRY(flush_buckets(m, m->off_lnf_b + d));
+  for (int l = c.n_layers - 1; l >= 0; --l) {
+    const LayerOffsets& o = m->lo[l];
+    hl_decoder::F32Layer& a = m->lf[l];
+    // y = r + fc2(gelu(fc1(ln2 r)))
+    HL_TRY(linear_backward_f32(m, a.g, P + o.w2, dx, m->d_wide, 0, G + o.w2, G + o.b2, N, F, d));
+    HL_TRY(hl_gelu_backward(ctx, a.h, m->d_wide, m->d_wide2, HL_F32, (size_t)N * F));
+    HL_TRY(linear_backward_f32(m, a.c, P + o.w1, m->d_wide2, m->d_c, 0, G + o.w1, G + o.b1, N, d, F));
+    HL_TRY(layer_norm_backward_impl(ctx, a.r, HL_F32, P + o.ln2g, m->d_c, nullptr, nullptr, dx, dx_next, nullptr, G + o.ln2g,
+                                    G + o.ln2b, nullptr, N, d));
+    std::swap(dx, dx_next);  // dL/dr
+    // r = x + out_proj(attention(q, k, v))
+    HL_TRY(linear_backward_f32(m, a.o, P + o.wo, dx, m->d_c, 0, G + o.wo, G + o.bo, N, d, d));
+    HL_TRY(hl_causal_attention_f32_backward(ctx, a.q, a.k, a.v, a.probs, m->d_c, m->d_q, m->d_k, m->d_v, B, T, d, H));
+    HL_TRY(linear_backward_f32(m, a.a, P + o.wqkv, m->d_q, m->tmp2_f, 0, G + o.wqkv, G + o.bqkv, N, d, d));
+    HL_TRY(linear_backward_f32(m, a.a, P + o.wqkv + (size_t)d * d, m->d_k, m->tmp2_f, 1, G + o.wqkv + (size_t)d * d,
+                               G + o.bqkv + d, N, d, d));
+    HL_TRY(linear_backward_f32(m, a.a, P + o.wqkv + 2 * (size_t)d * d, m->d_v, m->tmp2_f, 1,
+                               G + o.wqkv + 2 * (size_t)d * d, G + o.bqkv + 2 * d, N, d, d));
+    HL_TRY(layer_norm_backward_impl(ctx, m->xf[l], HL_F32, P + o.ln1g, m->tmp2_f, nullptr, nullptr, dx, dx_next, nullptr,
+                                    G + o.ln1g, G + o.ln1b, nullptr, N, d));
+    std::swap(dx, dx_next);
+    HL_TRY(flush_buckets(m, o.ln1b + d));
+  }
+  HL_CUDA(cudaMemsetAsync(G + m->off_pos, 0, sizeof(float) * (m->arena - m->off_pos), ctx->stream));
+  HL_TRY(hl_embedding_backward(ctx, dx, m->tokens, G + m->off_tok, V, G + m->off_pos, T, N, d));
+  HL_TRY(flush_buckets(m, m->arena));
+  if (nccl_active(ctx)) {
+    HL_CUDA(cudaEventRecord(m->comm_done, ctx->comm_stream));
+    HL_CUDA(cudaStreamWaitEvent(ctx->stream, m->comm_done, 0));
+  }
+  return HL_OK;
+}
+
 int optimizer_step(hl_decoder* m) {
   HL_REQUIRE(m->has_opt, "hl_decoder: no optimizer configured (call hl_decoder_set_optimizer)");
   hl_ctx* ctx = m->ctx;
@@ -379,10 +530,17 @@ int hl_decoder_create(hl_ctx* ctx, const hl_decoder_config* cfg, hl_decoder** ou
                  cfg->context > 0 && cfg->batch > 0,
              "hl_decoder_create: every size must be positive");
   HL_REQUIRE(cfg->d_model % cfg->n_heads == 0, "hl_decoder_create: d_model must be divisible by n_heads");
-  HL_REQUIRE(cfg->precision == HL_PRECISION_AMP_BF16, "hl_decoder_create: only the amp-bf16 route is available here");
-  HL_REQUIRE(cfg->d_model / cfg->n_heads == 64, "hl_decoder_create: the bf16 route needs head_dim 64");
-  HL_REQUIRE(cfg->d_model % 8 == 0 && cfg->d_ff % 8 == 0 && cfg->vocab % 8 == 0 && cfg->d_model <= 1024,
-             "hl_decoder_create: d_model (<= 1024), d_ff and vocab must be multiples of 8");
+  HL_REQUIRE(cfg->precision == HL_PRECISION_AMP_BF16 || cfg->precision == HL_PRECISION_F32,
+             "hl_decoder_create: precision must be HL_PRECISION_F32 or HL_PRECISION_AMP_BF16");
+  const bool amp = cfg->precision == HL_PRECISION_AMP_BF16;
+  if (amp) {
+    HL_REQUIRE(cfg->d_model / cfg->n_heads == 64, "hl_decoder_create: the bf16 route needs head_dim 64");
+    HL_REQUIRE(cfg->d_model % 8 == 0 && cfg->d_ff % 8 == 0 && cfg->vocab % 8 == 0 && cfg->d_model <= 1024,
+               "hl_decoder_create: d_model (<= 1024), d_ff and vocab must be multiples of 8");
+  } else {
+    HL_REQUIRE(cfg->d_model % 4 == 0 && cfg->d_model <= 1024,
+               "hl_decoder_create: the f32 route needs d_model to be a multiple of 4 and at most 1024");
+  }
   hl_decoder* m = new hl_decoder();
   m->ctx = ctx;
   m->cfg = *cfg;
@@ -400,11 +558,11 @@ int hl_decoder_create(hl_ctx* ctx, const hl_decoder_config* cfg, hl_decoder** ou
   HL_ALLOC(m->v, fb)
   HL_ALLOC(m->shadow, sizeof(__nv_bfloat16) * m->arena)
   size_t act = 0;
-  plan_activations(m, true, &act);
+  if (amp) plan_activations(m, true, &act); else plan_activations_f32(m, true, &act);
   m->act_bytes = act;
   HL_ALLOC(m->act_arena, act)
 #undef HL_ALLOC
-  plan_activations(m, false, &act);
+  if (amp) plan_activations(m, false, &act); else plan_activations_f32(m, false, &act);
   cudaMemsetAsync(m->params, 0, fb, ctx->stream);
   cudaMemsetAsync(m->grads, 0, fb, ctx->stream);
   cudaMemsetAsync(m->m, 0, fb, ctx->stream);
@@ -521,8 +679,13 @@ int hl_decoder_forward_backward(hl_decoder* m, const int64_t* tokens_dev, const 
     HL_CUDA(cudaMemcpyAsync(m->tokens, tokens_dev, sizeof(int64_t) * m->N, cudaMemcpyDeviceToDevice, m->ctx->stream));
   if (targets_dev != m->targets)
     HL_CUDA(cudaMemcpyAsync(m->targets, targets_dev, sizeof(int64_t) * m->N, cudaMemcpyDeviceToDevice, m->ctx->stream));
-  HL_TRY(forward(m));
-  HL_TRY(backward(m));
+  if (m->cfg.precision == HL_PRECISION_AMP_BF16) {
+    HL_TRY(forward(m));
+    HL_TRY(backward(m));
+  } else {
+    HL_TRY(forward_f32(m));
+    HL_TRY(backward_f32(m));
+  }
   m->launches_last_step = m->ctx->counters.launches - before;
   return HL_OK;
 }

@@ -93,3 +93,51 @@ def test_launch_count_is_reported_and_nonzero():
     assert model.launches_last_step > 20
     assert c.counters().gemm_tcgen05_launches >= 13
     model.close()
+
+
+def test_f32_route_one_step_matches_the_f64_oracle_tightly():
+    from heirloom_b200 import nn
+    kw = dict(vocab=96, d_model=64, n_layers=2, n_heads=2, d_ff=128, context=24)
+    c = ctx()
+    model = nn.DecoderLm(c, nn.DecoderConfig(batch=3, precision=nn.PRECISION_F32, **kw))
+    ocfg = ho.DecoderConfig(**kw)
+    params = ho.init_parameters(ocfg, 5)
+    rng = np.random.default_rng(6)
+    for n in params:  # larger weights: gradients well above rounding noise everywhere
+        if params[n].ndim == 2:
+            params[n] = ho.f32_round(rng.standard_normal(params[n].shape) * 0.2)
+    model.load_state_dict(params)
+    tok = rng.integers(0, ocfg.vocab, (3, 25))
+    x, y = tok[:, :-1].copy(), tok[:, 1:].copy()
+    model.forward_backward(torch.tensor(x, device="cuda"), torch.tensor(y, device="cuda"))
+    oloss, ograds = ho.decoder_loss_and_grads(ocfg, params, x, y)
+    assert abs(model.loss() - oloss) <= 1e-6 * abs(oloss)
+    for name in ho.parameter_names(ocfg):
+        g, w = model.grad(name).astype(np.float64), ograds[name]
+        scale = np.abs(w).max()
+        if name.endswith("attention.k_proj.bias"):
+            assert np.abs(g).max() <= 1e-5 * np.abs(ograds[name.replace("k_proj", "q_proj")]).max()
+            continue
+        assert np.abs(g - w).max() <= 2e-6 * scale + 1e-9, (name, np.abs(g - w).max(), scale)
+    model.close()
+
+
+def test_f32_route_tracks_the_reference_loss_trace_for_200_steps():
+    """north_star gate: f32 per-step loss within 1e-5 relative on the tiny byte-level decoder."""
+    import json
+    from pathlib import Path
+    from heirloom_b200 import nn
+    from tests.golden.make_tiny_trace import BATCH, CONFIG, STEPS, WEIGHT_SEED, batches
+    trace = json.loads((Path(__file__).parent / "golden" / "tiny_decoder_trace.json").read_text())
+    assert trace["config"] == CONFIG and trace["steps"] == STEPS
+    c = ctx()
+    model = nn.DecoderLm(c, nn.DecoderConfig(batch=BATCH, precision=nn.PRECISION_F32, **CONFIG))
+    model.load_state_dict(ho.init_parameters(ho.DecoderConfig(**CONFIG), WEIGHT_SEED))
+    model.set_optimizer(lr=1e-3, beta1=0.9, beta2=0.999, eps=1e-8, weight_decay=0.01, clip_norm=None)
+    losses = [model.train_step(torch.tensor(x).pin_memory(), torch.tensor(y).pin_memory()) for x, y in batches(STEPS)]
+    rel = np.abs(np.array(losses) - np.array(trace["losses"])) / np.array(trace["losses"])
+    assert rel.max() <= 1e-5, (rel.max(), int(rel.argmax()))
+    for name, (want_sum, want_sumsq) in trace["final_parameter_sum_and_sumsq"].items():
+        p = model.parameter(name).astype(np.float64)
+        assert abs((p * p).sum() - want_sumsq) <= 1e-4 * want_sumsq, name
+    model.close()
