@@ -138,6 +138,20 @@ __device__ __forceinline__ float gelu_grad_f(float x) {
   return 0.5f * (1.0f + t) + 0.5f * x * sech2 * dinner;
 }
 
+// Round-to-nearest-even to bf16 precision with integer ops (same result as the conversion
+// instruction for every finite input and infinities).  The GEMM epilogues use it because the
+// conversion instructions share the 16-lane special-function pipe with tanh.
+__device__ __forceinline__ uint32_t bf16_rne_bits(float x) {
+  uint32_t u = __float_as_uint(x);
+  u += 0x7FFFu + ((u >> 16) & 1u);
+  return u & 0xFFFF0000u;
+}
+__device__ __forceinline__ float bf16_round_alu(float x) { return __uint_as_float(bf16_rne_bits(x)); }
+// Packs two floats that are already bf16-representable (low 16 bits zero).
+__device__ __forceinline__ uint32_t pack_rounded_bf16x2(float lo, float hi) {
+  return __byte_perm(__float_as_uint(lo), __float_as_uint(hi), 0x7632);
+}
+
 // Hardware tanh (one MUFU op, relative error about 2^-11): enough for values that are rounded
 // to bf16 right after, as in the GEMM epilogues.
 __device__ __forceinline__ float tanh_fast(float x) {

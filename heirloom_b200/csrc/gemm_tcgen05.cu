@@ -12,8 +12,8 @@
 // accumulator buffers of 256 tensor-memory columns so the epilogue of tile i overlaps the
 // main loop of tile i+1.  Warp roles: warp 0 TMA producer, warp 1 MMA issuer (one elected
 // thread), warps 2-9 epilogue: two warps per tensor-memory lane group, each taking 128 of the
-// 256 columns.  An epilogue warp moves its 32 rows through a 4 KB swizzled staging tile and
-// writes them with TMA stores, so global writes are full 128-byte lines.
+// 256 columns.  An epilogue warp moves its 32 rows through two alternating 2 KB swizzled staging
+// tiles and writes them with TMA stores (64-byte row segments, clipped at the tensor edge).
 #include "kernels.h"
 #include "tc05.cuh"
 
@@ -32,7 +32,7 @@ constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
 constexpr int EPI_WARPS = 8;
 constexpr int GEMM_THREADS = (2 + EPI_WARPS) * 32;
 constexpr int TMEM_COLS = 512;
-constexpr int STAGING_BYTES = 4096;  // per epilogue warp: 32 rows x 128 bytes
+constexpr int STAGING_BYTES = 4096;  // per epilogue warp: two tiles of 32 rows x 64 bytes
 constexpr size_t GEMM_SMEM_BYTES =
     size_t(STAGES) * STAGE_BYTES + size_t(EPI_WARPS) * STAGING_BYTES + 1024 /*align slack*/ + 256 /*barriers*/;
 
@@ -56,12 +56,6 @@ struct SharedTail {
   uint32_t tmem_base;
   int abort_flag;
 };
-
-// One 16-byte chunk of row r of a [32 rows x 128 bytes] staging tile in the 128-byte swizzle
-// pattern the TMA store expects.
-__device__ __forceinline__ void stage_chunk(uint8_t* staging, int r, int chunk, uint4 v) {
-  *reinterpret_cast<uint4*>(staging + r * 128 + ((chunk ^ (r & 7)) << 4)) = v;
-}
 
 template <bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
@@ -178,11 +172,13 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
     const int ew = warp - 2;
     const int lane_group = warp & 3;  // tensor-memory lanes this warp may read
     const int half = ew >> 2;         // which 128 of the tile's 256 columns
+    // Two 2 KB staging tiles per warp ([32 rows x 64 bytes], 64-byte swizzle), used in turn, so
+    // a TMA store is still reading one tile while the next columns are written into the other.
     uint8_t* staging = staging_base + size_t(ew) * STAGING_BYTES;
+    int stage_sel = 0;
     const bool out_bf16 = !p.partial_out && p.out_dtype == HL_BF16;
-    const int group_cols = out_bf16 ? 64 : 32;  // columns per 128-byte staging row
-    const int groups = 128 / group_cols;
     const bool need_aux = !p.partial_out && (p.epilogue == HL_EPI_BIAS_RESIDUAL || p.epilogue == HL_EPI_DGELU);
+    const bool need_bias = !p.partial_out && p.bias != nullptr;
     int local = 0;
     bool ok = true;
     for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x, ++local) {
@@ -192,110 +188,122 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
       const int m_tile = rem - n_tile * p.m_tiles;
       const int buf = local & 1;
       const uint32_t buf_phase = (uint32_t)(local >> 1) & 1u;
-      if (!tc05::mbar_wait(&tail->tmem_full[buf], buf_phase, abort_flag)) { ok = false; break; }
-      tc05::tc_fence_after_sync();
       const int row0 = m_tile * BM + lane_group * 32;
       const int row = row0 + lane;
       const bool row_ok = row < p.m;
+      const int half_col0 = n_tile * BN + half * 128;
+      // Global reads of the epilogue are issued ahead of their use so that their latency hides
+      // behind the wait for the accumulator and behind the previous chunk's arithmetic:
+      // the warp's 128 bias values sit four per lane and are handed around by shuffles, and the
+      // residual / pre-activation rows are fetched one 32-column chunk ahead.
+      float4 bias_reg = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (need_bias && half_col0 + lane * 4 < p.n) bias_reg = __ldg(reinterpret_cast<const float4*>(p.bias + half_col0 + lane * 4));
+      auto fetch_aux = [&](int chunk, uint4 (&dst)[4]) {
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const int col = half_col0 + chunk * 32 + q * 8;
+          dst[q] = make_uint4(0, 0, 0, 0);
+          if (need_aux && row_ok && col < p.n)
+            dst[q] = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(p.aux_in) +
+                                                          (size_t)row * p.ld_aux_in + col));
+        }
+      };
+      uint4 aux_a[4], aux_b[4];
+      fetch_aux(0, aux_a);
+      if (!tc05::mbar_wait(&tail->tmem_full[buf], buf_phase, abort_flag)) { ok = false; break; }
+      tc05::tc_fence_after_sync();
       const uint32_t taddr_row = tmem_base + (uint32_t)(buf * BN) + ((uint32_t)(lane_group * 32) << 16);
-#pragma unroll 1
-      for (int grp = 0; grp < groups; ++grp) {
-        const int gcol0 = n_tile * BN + half * 128 + grp * group_cols;
-        if (gcol0 >= p.n) break;  // uniform across the warp
-        uint32_t gelu_packed[32];  // second output of the bias+gelu epilogue (64 bf16)
-        // All residual / pre-activation reads of this group are issued up front so their
-        // latencies overlap each other and the tensor-memory loads.
-        uint4 aux_pref[8];
-        if (need_aux) {
-#pragma unroll
-          for (int q = 0; q < 8; ++q) {
-            const int col = gcol0 + q * 8;
-            aux_pref[q] = make_uint4(0, 0, 0, 0);
-            if (q * 8 < group_cols && row_ok && col < p.n)
-              aux_pref[q] = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(p.aux_in) +
-                                                                 (size_t)row * p.ld_aux_in + col));
-          }
-        }
-        // the staging tile may still be read by the previous store
-        if (lane == 0) tc05::tma_store_wait_read();
+      // Sixteen 32-bit words of this lane's row (32 bf16 or 16 f32) go to the free staging tile
+      // and out through one TMA store; at most one earlier store may still be reading.
+      auto emit = [&](const CUtensorMap* map, const uint32_t* w, int col) {
+        if (lane == 0) tc05::tma_store_wait_read1();
         __syncwarp();
+        uint8_t* tile = staging + stage_sel * (STAGING_BYTES / 2);
 #pragma unroll
-        for (int sub = 0; sub < 2; ++sub) {
-          if (sub * 32 >= group_cols) break;
-          const int col0 = gcol0 + sub * 32;
-          uint32_t acc_bits[32];
-          tc05::tmem_ld_32x32b_x32(taddr_row + (uint32_t)(half * 128 + grp * group_cols + sub * 32), acc_bits);
-          tc05::tmem_ld_wait();
-#pragma unroll
-          for (int g = 0; g < 4; ++g) {  // groups of 8 columns
-            const int col = col0 + g * 8;
-            float v[8];
-#pragma unroll
-            for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(acc_bits[g * 8 + i]);
-            const bool col_ok = col < p.n;
-            if (!p.partial_out) {
-              if (p.bias != nullptr && col_ok) {
-                const float4 b0 = __ldg(reinterpret_cast<const float4*>(p.bias + col));
-                const float4 b1 = __ldg(reinterpret_cast<const float4*>(p.bias + col + 4));
-                v[0] += b0.x; v[1] += b0.y; v[2] += b0.z; v[3] += b0.w;
-                v[4] += b1.x; v[5] += b1.y; v[6] += b1.z; v[7] += b1.w;
-              }
-              if (p.epilogue == HL_EPI_BIAS_GELU) {
-                // h = bf16(acc + bias) is the main output; g = bf16(gelu(h)) the second one
-                float gl[8];
-#pragma unroll
-                for (int i = 0; i < 8; ++i) { v[i] = bf16_round(v[i]); gl[i] = gelu_fwd_fast(v[i]); }
-                const int w = (sub * 4 + g) * 4;
-                gelu_packed[w] = pack_bf16x2(gl[0], gl[1]); gelu_packed[w + 1] = pack_bf16x2(gl[2], gl[3]);
-                gelu_packed[w + 2] = pack_bf16x2(gl[4], gl[5]); gelu_packed[w + 3] = pack_bf16x2(gl[6], gl[7]);
-              } else if (p.epilogue == HL_EPI_BIAS_RESIDUAL || p.epilogue == HL_EPI_DGELU) {
-                const uint4 r = aux_pref[sub * 4 + g];
-                const float2 r0 = unpack_bf16x2(r.x), r1 = unpack_bf16x2(r.y), r2 = unpack_bf16x2(r.z), r3 = unpack_bf16x2(r.w);
-                const float rr[8] = {r0.x, r0.y, r1.x, r1.y, r2.x, r2.y, r3.x, r3.y};
-                if (p.epilogue == HL_EPI_BIAS_RESIDUAL) {
-                  // out = bf16(residual + bf16(acc + bias)): the two round trips of the block
-#pragma unroll
-                  for (int i = 0; i < 8; ++i) v[i] = rr[i] + bf16_round(v[i]);
-                } else {
-                  // out = acc * gelu'(h), h read from aux_in
-#pragma unroll
-                  for (int i = 0; i < 8; ++i) v[i] = v[i] * gelu_grad_fast(rr[i]);
-                }
-              }
-            }
-            if (out_bf16) {
-              stage_chunk(staging, lane, sub * 4 + g,
-                          make_uint4(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]), pack_bf16x2(v[4], v[5]),
-                                     pack_bf16x2(v[6], v[7])));
-            } else {
-              stage_chunk(staging, lane, g * 2, make_uint4(__float_as_uint(v[0]), __float_as_uint(v[1]),
-                                                           __float_as_uint(v[2]), __float_as_uint(v[3])));
-              stage_chunk(staging, lane, g * 2 + 1, make_uint4(__float_as_uint(v[4]), __float_as_uint(v[5]),
-                                                               __float_as_uint(v[6]), __float_as_uint(v[7])));
-            }
-          }
-        }
+        for (int q = 0; q < 4; ++q)
+          *reinterpret_cast<uint4*>(tile + lane * 64 + ((q ^ ((lane >> 1) & 3)) << 4)) =
+              make_uint4(w[q * 4], w[q * 4 + 1], w[q * 4 + 2], w[q * 4 + 3]);
         tc05::fence_proxy_async_smem();
         __syncwarp();
         if (lane == 0) {
-          if (p.partial_out) tc05::tma_store_3d(&map_c, staging, gcol0, row0, split);
-          else tc05::tma_store_2d(&map_c, staging, gcol0, row0);
+          if (p.partial_out) tc05::tma_store_3d(map, tile, col, row0, split);
+          else tc05::tma_store_2d(map, tile, col, row0);
           tc05::tma_store_commit();
         }
-        if (p.epilogue == HL_EPI_BIAS_GELU && !p.partial_out) {
-          if (lane == 0) tc05::tma_store_wait_read();
-          __syncwarp();
+        stage_sel ^= 1;
+      };
+      auto process = [&](int chunk, const uint4 (&aux)[4]) {
+        const int col0 = half_col0 + chunk * 32;
+        uint32_t acc_bits[32];
+        tc05::tmem_ld_32x32b_x32(taddr_row + (uint32_t)(half * 128 + chunk * 32), acc_bits);
+        tc05::tmem_ld_wait();
+        uint32_t packed[16], gelu_packed[16], hi_words[16];  // f32 output: packed = columns 0-15, hi_words = 16-31
 #pragma unroll
-          for (int q = 0; q < 8; ++q)
-            stage_chunk(staging, lane, q,
-                        make_uint4(gelu_packed[q * 4], gelu_packed[q * 4 + 1], gelu_packed[q * 4 + 2], gelu_packed[q * 4 + 3]));
-          tc05::fence_proxy_async_smem();
-          __syncwarp();
-          if (lane == 0) {
-            tc05::tma_store_2d(&map_aux, staging, gcol0, row0);
-            tc05::tma_store_commit();
+        for (int g = 0; g < 4; ++g) {  // groups of 8 columns
+          float v[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(acc_bits[g * 8 + i]);
+          if (!p.partial_out) {
+            if (need_bias) {
+              // columns chunk*32 + g*8 + i of this half live in lane chunk*8 + g*2 + i/4
+              const int src = chunk * 8 + g * 2;
+              v[0] += __shfl_sync(0xffffffffu, bias_reg.x, src); v[1] += __shfl_sync(0xffffffffu, bias_reg.y, src);
+              v[2] += __shfl_sync(0xffffffffu, bias_reg.z, src); v[3] += __shfl_sync(0xffffffffu, bias_reg.w, src);
+              v[4] += __shfl_sync(0xffffffffu, bias_reg.x, src + 1); v[5] += __shfl_sync(0xffffffffu, bias_reg.y, src + 1);
+              v[6] += __shfl_sync(0xffffffffu, bias_reg.z, src + 1); v[7] += __shfl_sync(0xffffffffu, bias_reg.w, src + 1);
+            }
+            if (p.epilogue == HL_EPI_BIAS_GELU) {
+              // h = bf16(acc + bias) is the main output; g = bf16(gelu(h)) the second one
+              float gl[8];
+#pragma unroll
+              for (int i = 0; i < 8; ++i) { v[i] = bf16_round_alu(v[i]); gl[i] = gelu_fwd_fast(v[i]); }
+              gelu_packed[g * 4] = pack_bf16x2(gl[0], gl[1]); gelu_packed[g * 4 + 1] = pack_bf16x2(gl[2], gl[3]);
+              gelu_packed[g * 4 + 2] = pack_bf16x2(gl[4], gl[5]); gelu_packed[g * 4 + 3] = pack_bf16x2(gl[6], gl[7]);
+            } else if (p.epilogue == HL_EPI_BIAS_RESIDUAL || p.epilogue == HL_EPI_DGELU) {
+              const uint4 r = aux[g];
+              const float2 r0 = unpack_bf16x2(r.x), r1 = unpack_bf16x2(r.y), r2 = unpack_bf16x2(r.z), r3 = unpack_bf16x2(r.w);
+              const float rr[8] = {r0.x, r0.y, r1.x, r1.y, r2.x, r2.y, r3.x, r3.y};
+              if (p.epilogue == HL_EPI_BIAS_RESIDUAL) {
+                // out = bf16(residual + bf16(acc + bias)): the two round trips of the block
+#pragma unroll
+                for (int i = 0; i < 8; ++i) v[i] = rr[i] + bf16_round_alu(v[i]);
+              } else {
+                // out = acc * gelu'(h), h read from aux_in
+#pragma unroll
+                for (int i = 0; i < 8; ++i) v[i] = v[i] * gelu_grad_fast(rr[i]);
+              }
+            }
+          }
+          if (out_bf16 && p.epilogue == HL_EPI_BIAS_GELU) {  // h is already rounded
+            packed[g * 4] = pack_rounded_bf16x2(v[0], v[1]); packed[g * 4 + 1] = pack_rounded_bf16x2(v[2], v[3]);
+            packed[g * 4 + 2] = pack_rounded_bf16x2(v[4], v[5]); packed[g * 4 + 3] = pack_rounded_bf16x2(v[6], v[7]);
+          } else if (out_bf16) {
+            packed[g * 4] = pack_bf16x2(v[0], v[1]); packed[g * 4 + 1] = pack_bf16x2(v[2], v[3]);
+            packed[g * 4 + 2] = pack_bf16x2(v[4], v[5]); packed[g * 4 + 3] = pack_bf16x2(v[6], v[7]);
+          } else {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              if (g < 2) packed[g * 8 + i] = __float_as_uint(v[i]);
+              else hi_words[(g - 2) * 8 + i] = __float_as_uint(v[i]);
+            }
           }
         }
+        if (out_bf16) {
+          emit(&map_c, packed, col0);
+          if (p.epilogue == HL_EPI_BIAS_GELU) emit(&map_aux, gelu_packed, col0);
+        } else {
+          emit(&map_c, packed, col0);
+          if (col0 + 16 < p.n) emit(&map_c, hi_words, col0 + 16);
+        }
+      };
+      // chunks beyond the matrix edge are skipped (the test is uniform across the warp)
+#pragma unroll 1
+      for (int chunk = 0; chunk < 4; ++chunk) {
+        if (half_col0 + chunk * 32 >= p.n) break;
+        if (chunk < 3) fetch_aux(chunk + 1, aux_b);
+        process(chunk, aux_a);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) aux_a[q] = aux_b[q];
       }
       tc05::tc_fence_before_sync();
       __syncwarp();
@@ -445,20 +453,20 @@ int gemm_bf16_run(hl_ctx* ctx, const hl_gemm_desc* d, const void* a, const void*
   if (p.partial_out) {
     const uint64_t dims[3] = {(uint64_t)d->n, (uint64_t)d->m, (uint64_t)splits};
     const uint64_t strides[2] = {(uint64_t)d->n * 4, (uint64_t)d->n * (uint64_t)d->m * 4};
-    const uint32_t box[3] = {32, 32, 1};
-    rc = make_tensor_map(&mc, HL_F32, 3, workspace, dims, strides, box);
+    const uint32_t box[3] = {16, 32, 1};
+    rc = make_tensor_map(&mc, HL_F32, 3, workspace, dims, strides, box, 64);
   } else {
     const uint64_t dims[2] = {(uint64_t)d->n, (uint64_t)d->m};
     const uint64_t strides[1] = {(uint64_t)d->ldc * (d->out_dtype == HL_BF16 ? 2u : 4u)};
-    const uint32_t box[2] = {d->out_dtype == HL_BF16 ? 64u : 32u, 32u};
-    rc = make_tensor_map(&mc, d->out_dtype, 2, c, dims, strides, box);
+    const uint32_t box[2] = {d->out_dtype == HL_BF16 ? 32u : 16u, 32u};  // 64-byte rows
+    rc = make_tensor_map(&mc, d->out_dtype, 2, c, dims, strides, box, 64);
   }
   if (rc != HL_OK) return rc;
   if (d->epilogue == HL_EPI_BIAS_GELU) {
     const uint64_t dims[2] = {(uint64_t)d->n, (uint64_t)d->m};
     const uint64_t strides[1] = {(uint64_t)ld_aux_out * 2};
-    const uint32_t box[2] = {64, 32};
-    rc = make_tensor_map(&maux, HL_BF16, 2, aux_out, dims, strides, box);
+    const uint32_t box[2] = {32, 32};
+    rc = make_tensor_map(&maux, HL_BF16, 2, aux_out, dims, strides, box, 64);
     if (rc != HL_OK) return rc;
   } else {
     maux = mc;

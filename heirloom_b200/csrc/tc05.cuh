@@ -97,6 +97,8 @@ __device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, const void*
 __device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 // The shared-memory sources of all committed stores have been read (safe to overwrite them).
 __device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+// Same, but the most recently committed store may still be reading.
+__device__ __forceinline__ void tma_store_wait_read1() { asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); }
 // All committed stores are complete.
 __device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 
@@ -201,9 +203,10 @@ __device__ __forceinline__ bool elect_one() {
 int make_tensor_map_bf16_2d(CUtensorMap* out, const void* base, uint64_t inner, uint64_t outer,
                             uint64_t row_stride_elems, uint32_t box_inner, uint32_t box_outer);
 // General form: `rank` dims (innermost first), byte strides for dims 1.., box extents, element
-// type HL_BF16 or HL_F32, 128-byte swizzle (the box's inner extent must span 128 bytes or less).
+// type HL_BF16 or HL_F32, 128- or 64-byte swizzle (the box's inner extent must span no more
+// bytes than the swizzle width).
 int make_tensor_map(CUtensorMap* out, int dtype, int rank, const void* base, const uint64_t* dims,
-                    const uint64_t* strides_bytes, const uint32_t* box);
+                    const uint64_t* strides_bytes, const uint32_t* box, int swizzle_bytes = 128);
 int make_tensor_map_bf16_3d(CUtensorMap* out, const void* base, uint64_t d0, uint64_t d1, uint64_t d2,
                             uint64_t stride1_elems, uint64_t stride2_elems, uint32_t box0, uint32_t box1,
                             uint32_t box2);
