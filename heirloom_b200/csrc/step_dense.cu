@@ -311,12 +311,19 @@ int forward(hl_decoder* m) {
   return HL_OK;
 }
 
+// Bucket b covers gradient-arena elements [b*bucket, min((b+1)*bucket, arena)); it may be reduced
+// once every gradient below its end is final.  Pure host arithmetic, shared with hl_ddp_ready_buckets.
+inline void bucket_range(size_t arena, size_t bucket, size_t b, size_t* start, size_t* end) {
+  *start = b * bucket;
+  *end = std::min(*start + bucket, arena);
+}
+
 // Queue the all-reduce of every bucket whose gradients are final.
 int flush_buckets(hl_decoder* m, size_t done_elems) {
   if (!nccl_active(m->ctx)) return HL_OK;
   while (m->next_bucket < m->n_buckets) {
-    const size_t start = m->next_bucket * m->bucket_elems;
-    const size_t end = std::min(start + m->bucket_elems, m->arena);
+    size_t start, end;
+    bucket_range(m->arena, m->bucket_elems, m->next_bucket, &start, &end);
     if (end > done_elems) break;
     HL_CUDA(cudaEventRecord(m->bucket_ready[m->next_bucket], m->ctx->stream));
     HL_CUDA(cudaStreamWaitEvent(m->ctx->comm_stream, m->bucket_ready[m->next_bucket], 0));
@@ -724,5 +731,29 @@ int hl_decoder_loss(hl_decoder* m, float* loss_host) {
 }
 
 unsigned long long hl_decoder_launches_last_step(hl_decoder* m) { return m ? m->launches_last_step : 0; }
+
+long long hl_ddp_bucket_count(long long arena_elems, long long bucket_elems) {
+  if (arena_elems <= 0 || bucket_elems <= 0) return 0;
+  return (arena_elems + bucket_elems - 1) / bucket_elems;
+}
+
+int hl_ddp_ready_buckets(long long arena_elems, long long bucket_elems, long long next_bucket, long long done_elems,
+                         long long* starts, long long* counts, int capacity) {
+  if (arena_elems <= 0 || bucket_elems <= 0 || next_bucket < 0 || !starts || !counts || capacity < 0) {
+    hl::fail("hl_ddp_ready_buckets: invalid argument");
+    return -1;
+  }
+  const long long total = hl_ddp_bucket_count(arena_elems, bucket_elems);
+  int n = 0;
+  for (long long b = next_bucket; b < total && n < capacity; ++b) {
+    size_t start, end;
+    hl::bucket_range((size_t)arena_elems, (size_t)bucket_elems, (size_t)b, &start, &end);
+    if ((long long)end > done_elems) break;
+    starts[n] = (long long)start;
+    counts[n] = (long long)(end - start);
+    ++n;
+  }
+  return n;
+}
 
 }  // extern "C"

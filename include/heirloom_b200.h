@@ -284,6 +284,16 @@ int hl_nccl_allreduce_f32(hl_ctx* ctx, float* buf_dev, size_t count);
 int hl_nccl_abort(hl_ctx* ctx);
 int hl_nccl_destroy(hl_ctx* ctx);
 
+/* Bucket arithmetic of the gradient exchange (host only, no GPU needed): the gradient arena of
+ * `arena_elems` f32 values is cut into consecutive buckets of `bucket_elems` (25 MiB = 6,553,600 by
+ * default; the last one is shorter).  hl_ddp_ready_buckets lists, from `next_bucket` on, the
+ * buckets that lie wholly below `done_elems` (every gradient before that offset is final) and
+ * returns how many it wrote (-1 on bad arguments).  The reference reduces one tensor at a time
+ * after backward (src/nn.rs:2083-2138); this is the schedule that replaces it. */
+long long hl_ddp_bucket_count(long long arena_elems, long long bucket_elems);
+int hl_ddp_ready_buckets(long long arena_elems, long long bucket_elems, long long next_bucket, long long done_elems,
+                         long long* starts, long long* counts, int capacity);
+
 /* ---- training step of the dense decoder LM --------------------------------------------------
  * The reference's N-layer pre-LayerNorm decoder (MemoryTransformerLm without memory layers,
  * src/memory_transformer.rs:1217-1261): learned positions, separate q/k/v/out projections with
