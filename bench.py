@@ -251,13 +251,16 @@ def run_ours(args):
     e2e_ms = max_over_ranks((time.perf_counter() - t0) * 1e3)
 
     # ---- per-kernel timing of one more pass, for the roofline of the dominant kernel --------------
+    # Every rank runs these steps (the gradient exchange needs all of them); only rank 0 times them.
     prof = None
+    prof_steps = min(args.steps, 5)
+    if rank == 0:
+        cuda.check(ctx.lib.hl_profile_enable(ctx.handle, 1))
+    for i in range(prof_steps):
+        model.train_step_device(*dev_pool[i % n_pool])
+    ctx.sync()
     if rank == 0:
         from heirloom_b200._lib import Profile
-        cuda.check(ctx.lib.hl_profile_enable(ctx.handle, 1))
-        prof_steps = min(args.steps, 5)
-        for i in range(prof_steps):
-            model.train_step_device(*dev_pool[i % n_pool])
         p = Profile()
         cuda.check(ctx.lib.hl_profile_read(ctx.handle, ctypes.byref(p)))
         cuda.check(ctx.lib.hl_profile_enable(ctx.handle, 0))
@@ -266,6 +269,10 @@ def run_ours(args):
         prof = {n: {"ms_per_step": p.ms[i] / prof_steps, "work_per_step": p.work[i] / prof_steps,
                     "scopes_per_step": p.scopes[i] / prof_steps} for i, n in enumerate(names)}
     barrier()
+    model.close()
+    if world > 1:
+        cuda.check(ctx.lib.hl_nccl_destroy(ctx.handle))
+        dist.destroy_process_group()
 
     if rank != 0:
         return
