@@ -316,3 +316,106 @@ def flash_attention_backward(ctx: Context, q, k, v, out, dout, lse, batch: int, 
         c_longlong(dout.stride(0)), _p(lse), _p(dq), _p(dk), _p(dv), c_longlong(dqkv.stride(0)), c_int(batch),
         c_int(time), c_int(n_heads), c_int(C // n_heads)))
     return dqkv
+
+
+# ---- product-key memory layer -------------------------------------------------------------------------
+def topk_rows(ctx: Context, scores: torch.Tensor, k: int) -> torch.Tensor:
+    rows, cols = scores.shape
+    out = torch.empty(rows, k, dtype=torch.int64, device=scores.device)
+    check(ctx.lib.hl_topk_rows_f32(ctx.handle, _p(scores), _p(out), c_int(rows), c_int(cols), c_int(k)))
+    return out
+
+
+def product_key_side_scores(ctx: Context, query, left_keys, right_keys):
+    tokens, key_dim = query.shape
+    side = left_keys.shape[0]
+    ls = torch.empty(tokens, side, dtype=torch.float32, device=query.device)
+    rs = torch.empty(tokens, side, dtype=torch.float32, device=query.device)
+    check(ctx.lib.hl_product_key_side_scores_f32(ctx.handle, _p(query), c_longlong(query.stride(0)), _p(left_keys),
+                                                 _p(right_keys), _p(ls), _p(rs), c_int(tokens), c_int(side),
+                                                 c_int(key_dim)))
+    return ls, rs
+
+
+def product_key_topk_from_side_scores(ctx: Context, left_scores, right_scores, top_k: int, beam: int):
+    tokens, side = left_scores.shape
+    out = torch.empty(tokens, top_k, dtype=torch.int64, device=left_scores.device)
+    check(ctx.lib.hl_product_key_topk_from_side_scores(ctx.handle, _p(left_scores), _p(right_scores), _p(out),
+                                                       c_int(tokens), c_int(side), c_int(top_k), c_int(beam)))
+    return out
+
+
+def product_key_split_rows(ctx: Context, rows: torch.Tensor, side: int):
+    left, right = torch.empty_like(rows), torch.empty_like(rows)
+    check(ctx.lib.hl_product_key_split_rows(ctx.handle, _p(rows), _p(left), _p(right), c_longlong(rows.numel()),
+                                            c_int(side)))
+    return left, right
+
+
+def memory_selected_scores_forward(ctx: Context, indices, query, left_or_keys, right_keys=None):
+    tokens, top_k = indices.shape
+    key_dim = query.shape[1]
+    side = left_or_keys.shape[0] if right_keys is not None else 0
+    slots = side * side if side else left_or_keys.shape[0]
+    out = torch.empty(tokens, top_k, dtype=torch.float32, device=query.device)
+    check(ctx.lib.hl_memory_selected_scores_forward(ctx.handle, _p(indices), _p(query), c_longlong(query.stride(0)),
+                                                    _p(left_or_keys), _p(right_keys), _p(out), c_int(tokens),
+                                                    c_int(top_k), c_int(side), c_int(key_dim), c_int(slots)))
+    return out
+
+
+def memory_selected_scores_backward(ctx: Context, indices, query, left_or_keys, right_keys, grad_scores):
+    tokens, top_k = indices.shape
+    key_dim = query.shape[1]
+    side = left_or_keys.shape[0] if right_keys is not None else 0
+    slots = side * side if side else left_or_keys.shape[0]
+    dq = torch.empty_like(query)
+    dl = torch.zeros_like(left_or_keys)
+    dr = torch.zeros_like(right_keys) if right_keys is not None else None
+    check(ctx.lib.hl_memory_selected_scores_backward(
+        ctx.handle, _p(indices), _p(query), c_longlong(query.stride(0)), _p(left_or_keys), _p(right_keys),
+        _p(grad_scores), _p(dq), c_longlong(dq.stride(0)), _p(dl), _p(dr), c_int(tokens), c_int(top_k), c_int(side),
+        c_int(key_dim), c_int(slots)))
+    return dq, dl, dr
+
+
+def softmax_rows(ctx: Context, x):
+    y = torch.empty_like(x)
+    check(ctx.lib.hl_softmax_rows_f32(ctx.handle, _p(x), _p(y), c_int(x.shape[0]), c_int(x.shape[1])))
+    return y
+
+
+def softmax_rows_backward(ctx: Context, y, grad_y):
+    gx = torch.empty_like(y)
+    check(ctx.lib.hl_softmax_rows_backward_f32(ctx.handle, _p(y), _p(grad_y), _p(gx), c_int(y.shape[0]),
+                                               c_int(y.shape[1])))
+    return gx
+
+
+def memory_weighted_value_forward(ctx: Context, indices, weights, values):
+    tokens, top_k = indices.shape
+    rows, dim = values.shape
+    out = torch.empty(tokens, dim, dtype=torch.float32, device=values.device)
+    check(ctx.lib.hl_memory_weighted_value_forward(ctx.handle, _p(indices), _p(weights), _p(values), _p(out),
+                                                   c_int(tokens), c_int(top_k), c_int(rows), c_int(dim)))
+    return out
+
+
+def memory_weighted_value_backward(ctx: Context, indices, weights, values, grad_out):
+    tokens, top_k = indices.shape
+    rows, dim = values.shape
+    dw = torch.empty_like(weights)
+    dv = torch.zeros_like(values)
+    check(ctx.lib.hl_memory_weighted_value_backward(ctx.handle, _p(indices), _p(weights), _p(values), _p(grad_out),
+                                                    _p(dw), _p(dv), c_int(tokens), c_int(top_k), c_int(rows),
+                                                    c_int(dim)))
+    return dw, dv
+
+
+def sparse_adamw_rows(ctx: Context, param, grad, m, v, selected_rows, hp: AdamWParams, row_mask=None,
+                      zero_grad_rows: bool = False) -> None:
+    rows, row_dim = param.shape
+    flags = torch.zeros(rows, dtype=torch.uint8, device=param.device)
+    check(ctx.lib.hl_sparse_adamw_rows_f32(ctx.handle, _p(param), _p(grad), _p(m), _p(v), _p(selected_rows),
+                                           c_longlong(selected_rows.numel()), _p(row_mask), _p(flags), c_int(rows),
+                                           c_int(row_dim), byref(hp), c_int(1 if zero_grad_rows else 0)))

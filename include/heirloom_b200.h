@@ -273,6 +273,55 @@ int hl_flash_attention_backward(hl_ctx* ctx, const void* q, const void* k, const
                                 const float* lse, void* dq, void* dk, void* dv, long long ld_dqkv, int batch,
                                 int time, int n_heads, int head_dim);
 
+/* ---- product-key memory layer ----------------------------------------------------------------
+ * Per-row top-k of stored f32 scores: descending score, ties to the lower index
+ * (Tensor::topk_indices_dim1, src/tensor.rs:641-702; kernels.ptx:1780).  cols <= 2048. */
+int hl_topk_rows_f32(hl_ctx* ctx, const float* scores, int64_t* out, int rows, int cols, int k);
+/* Side scores of the product-key lookup: left[t,s] = q[t,:half] . K_L[s], right[t,s] = q[t,half:] . K_R[s]
+ * with the reference's f32 dot order (acc = acc + q[j]*k[j], multiply and add rounded separately,
+ * src/memory_transformer.rs:2029-2034; kernels.ptx:1873), so that equal inputs give equal score
+ * bits and therefore equal indices. */
+int hl_product_key_side_scores_f32(hl_ctx* ctx, const float* query, long long ld_query, const float* left_keys,
+                                   const float* right_keys, float* left_scores, float* right_scores, int tokens,
+                                   int side, int key_dim);
+/* Top-`beam` per side (desc score, asc index), beam^2 f32 sums, top_k by (desc sum, asc slot);
+ * slot = left*side + right (src/memory_transformer.rs:847-924; kernels.ptx:2121).  beam <= 32. */
+int hl_product_key_topk_from_side_scores(hl_ctx* ctx, const float* left_scores, const float* right_scores,
+                                         int64_t* out, int tokens, int side, int top_k, int beam);
+/* row / side and row % side (src/tensor.rs:1654-1719; kernels.ptx:2263). */
+int hl_product_key_split_rows(hl_ctx* ctx, const int64_t* rows, int64_t* left, int64_t* right, long long n, int side);
+/* Differentiable re-scoring of the chosen slots.  side > 0: product-key tables
+ * (score = q_L . K_L[slot/side] + q_R . K_R[slot%side], src/tensor.rs:3593-3769; kernels.ptx:2317);
+ * side == 0: exact lookup over one [slots, key_dim] table (src/tensor.rs:3465-3548; kernels.ptx:3028). */
+int hl_memory_selected_scores_forward(hl_ctx* ctx, const int64_t* indices, const float* query, long long ld_query,
+                                      const float* left_or_keys, const float* right_keys, float* scores, int tokens,
+                                      int top_k, int side, int key_dim, int slots);
+/* dq and the key-table gradients (added into zero-initialised or running tables with f32 atomics,
+ * repeats accumulate; src/tensor/autograd.rs:2325-2494; kernels.ptx:2417-2624, :3110-3259). */
+int hl_memory_selected_scores_backward(hl_ctx* ctx, const int64_t* indices, const float* query, long long ld_query,
+                                       const float* left_or_keys, const float* right_keys, const float* grad_scores,
+                                       float* grad_query, long long ld_grad_query, float* grad_left_or_keys,
+                                       float* grad_right_keys, int tokens, int top_k, int side, int key_dim,
+                                       int slots);
+/* Row softmax and its gradient (Tensor::softmax_dim(1), src/tensor.rs:4521-4602; kernels.ptx:2625, :2697). */
+int hl_softmax_rows_f32(hl_ctx* ctx, const float* x, float* y, int rows, int cols);
+int hl_softmax_rows_backward_f32(hl_ctx* ctx, const float* y, const float* grad_y, float* grad_x, int rows, int cols);
+/* out[t,:] = sum_k w[t,k] V[idx[t,k],:] and its gradients (dw = dout . V row; dV scatter-add with f32
+ * atomics) (src/tensor.rs:3771-3900, src/tensor/autograd.rs:2263-2323; kernels.ptx:2796-3027). */
+int hl_memory_weighted_value_forward(hl_ctx* ctx, const int64_t* indices, const float* weights, const float* values,
+                                     float* out, int tokens, int top_k, int rows, int dim);
+int hl_memory_weighted_value_backward(hl_ctx* ctx, const int64_t* indices, const float* weights, const float* values,
+                                      const float* grad_out, float* grad_weights, float* grad_values, int tokens,
+                                      int top_k, int rows, int dim);
+/* AdamW on the set of selected rows: duplicates update once, an optional byte mask filters rows
+ * (AdamW::step_sparse_rows_mut, src/nn.rs:2256-2323, :2899-2939; kernels.ptx:537-811).  row_flags is a
+ * caller-owned zeroed byte per row; it is left zeroed.  zero_grad_rows != 0 also clears the gradient
+ * rows that were consumed.  The caller advances the step counter and passes the bias corrections. */
+int hl_sparse_adamw_rows_f32(hl_ctx* ctx, float* param, float* grad, float* m, float* v,
+                             const int64_t* selected_rows, long long n_selected, const unsigned char* row_mask,
+                             unsigned char* row_flags, int rows, int row_dim, const hl_adamw_params* hp,
+                             int zero_grad_rows);
+
 /* ---- NCCL data-parallel plumbing ------------------------------------------------------------
  * Same surface as the reference's NcclUniqueId / NcclCommunicator (cuda.rs:305-349,
  * :8049-8233): a 128-byte unique id made on one rank and handed to the others by the caller,
