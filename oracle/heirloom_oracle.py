@@ -716,3 +716,212 @@ def train_steps(cfg: DecoderConfig, params: Dict[str, np.ndarray], batches, stat
         adamw_step(params, grads, state)
         losses.append(loss)
     return losses
+
+
+# --------------------------------------------------------------------------------------
+# memory transformer: the same decoder with product-key memory feed-forward blocks
+# --------------------------------------------------------------------------------------
+@dataclass
+class MemoryConfig:
+    """`MemoryTransformerConfig` restricted to what the training step uses
+    (`src/memory_transformer.rs:1217-1261`): one shared table set, one memory head, product-key
+    lookup, gated value path (`memory_plus`)."""
+    memory_layers: Tuple[int, ...] = ()
+    slots: int = 0
+    key_dim: int = 0
+    value_dim: int = 0
+    top_k: int = 0
+
+
+def memory_parameter_names(cfg: DecoderConfig, mem: MemoryConfig) -> List[str]:
+    """State-dict order with shared tables (`src/memory_transformer.rs:2098-2117`, `:632-642`,
+    `:1015-1032`)."""
+    names = ["token_embedding.weight", "position_embedding.weight"]
+    if mem.memory_layers:
+        names += ["shared_memory.product_key_left", "shared_memory.product_key_right", "shared_memory.value"]
+    for i in range(cfg.n_layers):
+        b = f"block.{i}."
+        names += [b + "ln1.weight", b + "ln1.bias"]
+        for proj in ("q_proj", "k_proj", "v_proj", "out_proj"):
+            names += [b + f"attention.{proj}.weight", b + f"attention.{proj}.bias"]
+        names += [b + "ln2.weight", b + "ln2.bias"]
+        if i in mem.memory_layers:
+            for proj in ("query_proj", "gate_proj", "out_proj"):
+                names += [b + f"feed_forward.memory.{proj}.weight", b + f"feed_forward.memory.{proj}.bias"]
+        else:
+            names += [b + "feed_forward.dense.fc1.weight", b + "feed_forward.dense.fc1.bias",
+                      b + "feed_forward.dense.fc2.weight", b + "feed_forward.dense.fc2.bias"]
+    names += ["ln_f.weight", "ln_f.bias", "lm_head.weight", "lm_head.bias"]
+    return names
+
+
+def memory_parameter_shapes(cfg: DecoderConfig, mem: MemoryConfig) -> Dict[str, Tuple[int, ...]]:
+    base = parameter_shapes(cfg)
+    d = cfg.d_model
+    side = int(round(math.sqrt(mem.slots))) if mem.slots else 0
+    shapes: Dict[str, Tuple[int, ...]] = {}
+    for name in memory_parameter_names(cfg, mem):
+        if name in base:
+            shapes[name] = base[name]
+        elif name.endswith("product_key_left") or name.endswith("product_key_right"):
+            shapes[name] = (side, mem.key_dim // 2)
+        elif name.endswith("shared_memory.value"):
+            shapes[name] = (mem.slots, mem.value_dim)
+        elif "query_proj" in name:
+            shapes[name] = (mem.key_dim, d) if name.endswith("weight") else (mem.key_dim,)
+        elif "gate_proj" in name:
+            shapes[name] = (mem.value_dim, d) if name.endswith("weight") else (mem.value_dim,)
+        elif "memory.out_proj" in name:
+            shapes[name] = (d, mem.value_dim) if name.endswith("weight") else (d,)
+    return shapes
+
+
+def init_memory_parameters(cfg: DecoderConfig, mem: MemoryConfig, seed: int) -> Dict[str, np.ndarray]:
+    """Harness-side generator: N(0, 0.02) weights (residual projections scaled), half-key tables
+    N(0, 1/sqrt(half_dim)) and value table N(0, 0.02) as in `MemoryTables::new`
+    (`src/memory_transformer.rs:568-601`)."""
+    rng = np.random.default_rng(seed)
+    res_scale = 1.0 / math.sqrt(2.0 * cfg.n_layers)
+    params: Dict[str, np.ndarray] = {}
+    for name, shape in memory_parameter_shapes(cfg, mem).items():
+        if name.endswith(".bias"):
+            params[name] = np.zeros(shape, F64)
+        elif ".ln" in name or name.startswith("ln_f"):
+            params[name] = np.ones(shape, F64)
+        elif "product_key" in name:
+            params[name] = f32_round(rng.standard_normal(shape) / math.sqrt(shape[1]))
+        else:
+            w = rng.standard_normal(shape) * 0.02
+            if "out_proj" in name or "fc2" in name:
+                w = w * res_scale
+            params[name] = f32_round(w)
+    return params
+
+
+def memory_feed_forward(x, p: Dict[str, np.ndarray], prefix: str, mem: MemoryConfig):
+    """`MemoryFeedForward::forward_named` (`src/memory_transformer.rs:742-781`): every internal op is an
+    f32 tensor op, also under AMP (`:787-789`).  Returns the output and what backward needs."""
+    side = int(round(math.sqrt(mem.slots)))
+    half = mem.key_dim // 2
+    kl, kr, val = p["shared_memory.product_key_left"], p["shared_memory.product_key_right"], p["shared_memory.value"]
+    q = _linear(x, p[prefix + "query_proj.weight"], p[prefix + "query_proj.bias"], False)
+    ls = side_scores_f32(q[:, :half], kl)
+    rs = side_scores_f32(q[:, half:], kr)
+    idx = product_key_indices_from_side_scores(ls, rs, mem.top_k, product_key_beam(side, mem.top_k))
+    scores = product_key_selected_scores(idx, q, kl, kr)
+    w = softmax(scores, 1)
+    weighted = memory_weighted_value(idx, w, val)
+    gpre = _linear(x, p[prefix + "gate_proj.weight"], p[prefix + "gate_proj.bias"], False)
+    gate = gelu(gpre)
+    mv = f32_round(weighted * gate)
+    out = _linear(mv, p[prefix + "out_proj.weight"], p[prefix + "out_proj.bias"], False)
+    return out, (x, q, idx, w, weighted, gpre, gate, mv)
+
+
+def memory_feed_forward_backward(saved, p, prefix: str, mem: MemoryConfig, gout, grads, gr):
+    """Gradients of the memory feed-forward; indices are not differentiable
+    (`src/tensor/autograd.rs:2263-2494`).  Table gradients are added into `grads`."""
+    x, q, idx, w, weighted, gpre, gate, mv = saved
+    kl, kr, val = p["shared_memory.product_key_left"], p["shared_memory.product_key_right"], p["shared_memory.value"]
+    dmv, grads[prefix + "out_proj.weight"], grads[prefix + "out_proj.bias"] = \
+        _linear_backward(mv, p[prefix + "out_proj.weight"], gout, False)
+    dmv = gr(dmv)
+    dweighted = gr(dmv * gate)
+    dgate = gr(dmv * weighted)
+    dgpre = gr(gelu_backward(gpre, dgate))
+    dx_gate, grads[prefix + "gate_proj.weight"], grads[prefix + "gate_proj.bias"] = \
+        _linear_backward(x, p[prefix + "gate_proj.weight"], dgpre, False)
+    dw, dval = memory_weighted_value_backward(idx, w, val, dweighted)
+    dscores = gr(softmax_backward(w, gr(dw), 1))
+    dq, dkl, dkr = product_key_selected_scores_backward(idx, q, kl, kr, dscores)
+    dx_q, grads[prefix + "query_proj.weight"], grads[prefix + "query_proj.bias"] = \
+        _linear_backward(x, p[prefix + "query_proj.weight"], gr(dq), False)
+    for name, g in (("shared_memory.value", dval), ("shared_memory.product_key_left", dkl),
+                    ("shared_memory.product_key_right", dkr)):
+        grads[name] = g if name not in grads else gr(grads[name] + g)
+    # gradient accumulation on the shared input follows the order the graph is walked: gate path
+    # first, then the query path (`src/tensor.rs:1721-1846`)
+    return gr(gr(dx_gate) + gr(dx_q))
+
+
+def memory_decoder_loss_and_grads(cfg: DecoderConfig, mem: MemoryConfig, params, tokens, targets,
+                                  amp_bf16: bool = False, grad_f32: bool = False, return_indices: bool = False):
+    """The decoder of `decoder_loss_and_grads` with memory feed-forward blocks at `mem.memory_layers`
+    (`MemoryTransformerBlock`, `src/memory_transformer.rs:1092-1183`)."""
+    amp = amp_bf16
+    rt = bf16_round if amp else (lambda a: a)
+    gr = f32_round if (grad_f32 or amp) else (lambda a: np.asarray(a, F64))
+    B, T = tokens.shape
+    N, d, H = B * T, cfg.d_model, cfg.n_heads
+    p = params
+    pos_ids = np.tile(np.arange(T, dtype=np.int64), (B, 1))
+    tok = rt(embedding(p["token_embedding.weight"], tokens))
+    pos = rt(embedding(p["position_embedding.weight"], pos_ids))
+    x = rt(add(tok, pos)).reshape(N, d)
+    saved = []
+    all_indices = {}
+    for i in range(cfg.n_layers):
+        b = f"block.{i}."
+        a = rt(layer_norm(x, p[b + "ln1.weight"], p[b + "ln1.bias"]))
+        q = rt(_linear(a, p[b + "attention.q_proj.weight"], p[b + "attention.q_proj.bias"], amp))
+        k = rt(_linear(a, p[b + "attention.k_proj.weight"], p[b + "attention.k_proj.bias"], amp))
+        v = rt(_linear(a, p[b + "attention.v_proj.weight"], p[b + "attention.v_proj.bias"], amp))
+        o, probs = causal_attention(q.reshape(B, T, d), k.reshape(B, T, d), v.reshape(B, T, d), H,
+                                    return_probs=True, round_probs_bf16=amp)
+        o = rt(o).reshape(N, d)
+        pr = rt(_linear(o, p[b + "attention.out_proj.weight"], p[b + "attention.out_proj.bias"], amp))
+        r = rt(add(x, pr))
+        c = rt(layer_norm(r, p[b + "ln2.weight"], p[b + "ln2.bias"]))
+        if i in mem.memory_layers:
+            f_raw, ff_saved = memory_feed_forward(c, p, b + "feed_forward.memory.", mem)
+            all_indices[i] = ff_saved[2]
+            f = rt(f_raw)
+            saved.append((x, a, q, k, v, probs, o, r, c, None, None, ff_saved))
+        else:
+            h = rt(_linear(c, p[b + "feed_forward.dense.fc1.weight"], p[b + "feed_forward.dense.fc1.bias"], amp))
+            g = rt(gelu(h))
+            f = rt(_linear(g, p[b + "feed_forward.dense.fc2.weight"], p[b + "feed_forward.dense.fc2.bias"], amp))
+            saved.append((x, a, q, k, v, probs, o, r, c, h, g, None))
+        x = rt(add(r, f))
+    z = rt(layer_norm(x, p["ln_f.weight"], p["ln_f.bias"]))
+    logits = _linear(z, p["lm_head.weight"], p["lm_head.bias"], amp)
+    flat_targets = targets.reshape(N)
+    loss = float(cross_entropy(logits, flat_targets))
+
+    grads: Dict[str, np.ndarray] = {}
+    dlogits = gr(cross_entropy_backward(logits, flat_targets))
+    dz, grads["lm_head.weight"], grads["lm_head.bias"] = _linear_backward(z, p["lm_head.weight"], dlogits, amp)
+    dx, grads["ln_f.weight"], grads["ln_f.bias"] = layer_norm_backward(x, p["ln_f.weight"], gr(dz))
+    dx = gr(dx)
+    for i in reversed(range(cfg.n_layers)):
+        b = f"block.{i}."
+        x_in, a, q, k, v, probs, o, r, c, h, g, ff_saved = saved[i]
+        if ff_saved is not None:
+            dc = memory_feed_forward_backward(ff_saved, p, b + "feed_forward.memory.", mem, dx, grads, gr)
+        else:
+            dg, grads[b + "feed_forward.dense.fc2.weight"], grads[b + "feed_forward.dense.fc2.bias"] = \
+                _linear_backward(g, p[b + "feed_forward.dense.fc2.weight"], dx, amp)
+            dh = gr(gelu_backward(h, gr(dg)))
+            dc, grads[b + "feed_forward.dense.fc1.weight"], grads[b + "feed_forward.dense.fc1.bias"] = \
+                _linear_backward(c, p[b + "feed_forward.dense.fc1.weight"], dh, amp)
+        dr_ln, grads[b + "ln2.weight"], grads[b + "ln2.bias"] = layer_norm_backward(r, p[b + "ln2.weight"], gr(dc))
+        dr = gr(dx + gr(dr_ln))
+        do, grads[b + "attention.out_proj.weight"], grads[b + "attention.out_proj.bias"] = \
+            _linear_backward(o, p[b + "attention.out_proj.weight"], dr, amp)
+        dq, dk, dv = causal_attention_backward(q.reshape(B, T, d), k.reshape(B, T, d), v.reshape(B, T, d), H,
+                                               gr(do).reshape(B, T, d), probs=probs, bf16_operands=amp)
+        da = np.zeros((N, d), F64)
+        for name, dproj in (("q_proj", dq), ("k_proj", dk), ("v_proj", dv)):
+            dai, grads[b + f"attention.{name}.weight"], grads[b + f"attention.{name}.bias"] = \
+                _linear_backward(a, p[b + f"attention.{name}.weight"], gr(dproj).reshape(N, d), amp)
+            da = gr(da + dai)
+        dx_ln, grads[b + "ln1.weight"], grads[b + "ln1.bias"] = layer_norm_backward(x_in, p[b + "ln1.weight"], da)
+        dx = gr(dr + gr(dx_ln))
+    dx3 = dx.reshape(B, T, d)
+    grads["token_embedding.weight"] = embedding_backward(p["token_embedding.weight"].shape, tokens, dx3)
+    grads["position_embedding.weight"] = embedding_backward(p["position_embedding.weight"].shape, pos_ids, dx3)
+    if grad_f32 or amp:
+        grads = {n: f32_round(g_) for n, g_ in grads.items()}
+    if return_indices:
+        return loss, grads, all_indices
+    return loss, grads

@@ -188,3 +188,43 @@ def test_decoder_gradients_match_finite_differences():
         dn = loss64(pp)
         fd = (up - dn) / (2 * eps)
         assert abs(fd - grads[name][idx]) <= 1e-5 + 1e-3 * abs(fd), (name, fd, grads[name][idx])
+
+
+def test_memory_decoder_gradients_match_finite_differences():
+    cfg = ho.DecoderConfig(vocab=13, d_model=8, n_layers=2, n_heads=2, d_ff=16, context=5)
+    mem = ho.MemoryConfig(memory_layers=(1,), slots=16, key_dim=8, value_dim=8, top_k=3)
+    assert ho.memory_parameter_names(cfg, mem)[2:5] == ["shared_memory.product_key_left",
+                                                        "shared_memory.product_key_right", "shared_memory.value"]
+    params = ho.init_memory_parameters(cfg, mem, 4)
+    rng = np.random.default_rng(2)
+    for n in params:
+        if params[n].ndim == 2 and "product_key" not in n:
+            params[n] = ho.f32_round(rng.standard_normal(params[n].shape) * 0.3)
+    tok = rng.integers(0, cfg.vocab, (2, 5))
+    tgt = rng.integers(0, cfg.vocab, (2, 5))
+    _, grads, indices = ho.memory_decoder_loss_and_grads(cfg, mem, params, tok, tgt, return_indices=True)
+    assert indices[1].shape == (10, 3)
+
+    def loss64(pp):
+        saved = ho.f32_round
+        ho.f32_round = lambda a: np.asarray(a, np.float64)
+        try:
+            return ho.memory_decoder_loss_and_grads(cfg, mem, pp, tok, tgt)[0]
+        finally:
+            ho.f32_round = saved
+
+    touched_row = int(indices[1][0, 0])
+    probes = [("block.1.feed_forward.memory.query_proj.weight", 5), ("block.1.feed_forward.memory.gate_proj.weight", 3),
+              ("block.1.feed_forward.memory.out_proj.weight", 7), ("shared_memory.value", touched_row * 8 + 2),
+              ("shared_memory.product_key_left", (touched_row // 4) * 4 + 1), ("block.0.feed_forward.dense.fc1.weight", 9),
+              ("block.1.ln2.weight", 2)]
+    for name, flat_idx in probes:
+        idx = np.unravel_index(flat_idx % params[name].size, params[name].shape)
+        eps = 1e-6
+        pp = {k: v.copy() for k, v in params.items()}
+        pp[name][idx] += eps
+        up = loss64(pp)
+        pp[name][idx] -= 2 * eps
+        dn = loss64(pp)
+        fd = (up - dn) / (2 * eps)
+        assert abs(fd - grads[name][idx]) <= 2e-5 + 2e-3 * abs(fd), (name, fd, grads[name][idx])
