@@ -41,6 +41,8 @@ int adam_plan_create(hl_ctx* ctx, const hl_adamw_tensor* tensors, int count, Ada
 void adam_plan_destroy(AdamPlan* plan);
 int adam_plan_step(hl_ctx* ctx, AdamPlan* plan, const hl_adamw_params* hp);
 
+extern "C" int hl_memory_copy_indices(hl_ctx* ctx, int64_t* host, const int64_t* dev, long long count);
+
 // NCCL (loaded at run time); see nccl_ddp.cu.
 int nccl_allreduce_sum_f32(hl_ctx* ctx, float* buf, size_t count, cudaStream_t stream);
 bool nccl_active(const hl_ctx* ctx);

@@ -339,6 +339,10 @@ int hl_memcpy_d2h(hl_ctx* ctx, void* dst_host, const void* src_dev, size_t bytes
   return HL_OK;
 }
 
+int hl_memory_copy_indices(hl_ctx* ctx, int64_t* host, const int64_t* dev, long long count) {
+  return hl_memcpy_d2h(ctx, host, dev, sizeof(int64_t) * (size_t)count);
+}
+
 int hl_memset_zero(hl_ctx* ctx, void* dst_dev, size_t bytes) {
   if (!ctx || (bytes && !dst_dev)) return hl::fail("hl_memset_zero: null argument");
   HL_CUDA(cudaMemsetAsync(dst_dev, 0, bytes, ctx->stream));

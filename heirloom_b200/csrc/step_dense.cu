@@ -34,6 +34,19 @@ struct Slot {
 
 struct LayerOffsets {
   size_t w2, b2, w1, b1, ln2g, ln2b, wo, bo, wqkv, bqkv, ln1g, ln1b;
+  // memory feed-forward blocks use these instead of w1/b1/w2/b2
+  bool is_memory = false;
+  size_t wq_m = 0, bq_m = 0, wg_m = 0, bg_m = 0, wout_m = 0, bout_m = 0;
+  // bias of the projection that writes the block output (fc2 or the memory out_proj)
+  size_t out_bias() const { return is_memory ? bout_m : b2; }
+};
+
+// Per memory layer: everything the backward needs (all f32, as in the reference the memory
+// feed-forward runs in f32 also under AMP, src/memory_transformer.rs:787-789).
+struct MemoryActs {
+  float *query = nullptr, *weights = nullptr, *weighted = nullptr, *gpre = nullptr, *gate = nullptr, *mv = nullptr;
+  int64_t* idx = nullptr;
+  __nv_bfloat16* mv_b = nullptr;
 };
 
 struct LayerActs {
@@ -80,6 +93,16 @@ struct hl_decoder {
   std::vector<cudaEvent_t> bucket_ready;
   cudaEvent_t comm_done = nullptr;
   unsigned long long launches_last_step = 0;
+  // product-key memory (shared tables, MemoryTransformerLm with memory layers)
+  bool has_memory = false;
+  hl_memory_config mem{};
+  int side = 0;
+  size_t off_kl = 0, off_kr = 0, off_val = 0;
+  std::vector<MemoryActs> ma;  // indexed by layer; empty entries for dense layers
+  float *m_ls = nullptr, *m_rs = nullptr, *m_scores = nullptr, *m_dmv = nullptr, *m_dweighted = nullptr, *m_dgate = nullptr,
+        *m_dgpre = nullptr, *m_dw = nullptr, *m_dscores = nullptr, *m_dq = nullptr, *m_dc2 = nullptr;
+  __nv_bfloat16 *m_dgpre_b = nullptr, *m_dq_b = nullptr;
+  unsigned char* m_row_flags = nullptr;
   // f32 route (reference f32 semantics: f32 tensors, f64 accumulation inside every op)
   struct F32Layer {
     float *a, *q, *k, *v, *probs, *o, *pr, *r, *c, *h, *g, *f;
@@ -114,10 +137,24 @@ void plan_parameters(hl_decoder* m) {
   for (int l = c.n_layers - 1; l >= 0; --l) {
     const std::string b = "block." + std::to_string(l) + ".";
     LayerOffsets& o = m->lo[l];
+    o.is_memory = false;
+    for (int i = 0; m->has_memory && i < m->mem.n_memory_layers; ++i) o.is_memory |= m->mem.memory_layers[i] == l;
+    if (o.is_memory) {
+      const long long kd = m->mem.key_dim, vd = m->mem.value_dim;
+      const std::string f = b + "feed_forward.memory.";
+      o.wout_m = add(f + "out_proj.weight", (size_t)d * vd, 2, d, vd);
+      o.bout_m = add(f + "out_proj.bias", (size_t)d, 1, d, 0);
+      o.wg_m = add(f + "gate_proj.weight", (size_t)vd * d, 2, vd, d);
+      o.bg_m = add(f + "gate_proj.bias", (size_t)vd, 1, vd, 0);
+      o.wq_m = add(f + "query_proj.weight", (size_t)kd * d, 2, kd, d);
+      o.bq_m = add(f + "query_proj.bias", (size_t)kd, 1, kd, 0);
+      o.w2 = o.b2 = o.w1 = o.b1 = 0;
+    } else {
     o.w2 = add(b + "feed_forward.dense.fc2.weight", (size_t)d * F, 2, d, F);
     o.b2 = add(b + "feed_forward.dense.fc2.bias", (size_t)d, 1, d, 0);
     o.w1 = add(b + "feed_forward.dense.fc1.weight", (size_t)F * d, 2, F, d);
     o.b1 = add(b + "feed_forward.dense.fc1.bias", (size_t)F, 1, F, 0);
+    }
     o.ln2g = add(b + "ln2.weight", (size_t)d, 1, d, 0);
     o.ln2b = add(b + "ln2.bias", (size_t)d, 1, d, 0);
     o.wo = add(b + "attention.out_proj.weight", (size_t)d * d, 2, d, d);
@@ -138,6 +175,12 @@ void plan_parameters(hl_decoder* m) {
     o.ln1g = add(b + "ln1.weight", (size_t)d, 1, d, 0);
     o.ln1b = add(b + "ln1.bias", (size_t)d, 1, d, 0);
   }
+  if (m->has_memory) {
+    const long long half = m->mem.key_dim / 2;
+    m->off_kl = add("shared_memory.product_key_left", (size_t)m->side * half, 2, m->side, half);
+    m->off_kr = add("shared_memory.product_key_right", (size_t)m->side * half, 2, m->side, half);
+    m->off_val = add("shared_memory.value", (size_t)m->mem.slots * m->mem.value_dim, 2, m->mem.slots, m->mem.value_dim);
+  }
   m->off_pos = add("position_embedding.weight", (size_t)T * d, 2, T, d);
   m->off_tok = add("token_embedding.weight", (size_t)V * d, 2, V, d);
   m->arena = cur;
@@ -148,14 +191,26 @@ void plan_parameters(hl_decoder* m) {
   };
   m->slots.push_back(find("token_embedding.weight"));
   m->slots.push_back(find("position_embedding.weight"));
+  if (m->has_memory)
+    for (const char* n : {"shared_memory.product_key_left", "shared_memory.product_key_right", "shared_memory.value"})
+      m->slots.push_back(find(n));
   for (int l = 0; l < c.n_layers; ++l) {
     const std::string b = "block." + std::to_string(l) + ".";
     for (const char* n : {"ln1.weight", "ln1.bias", "attention.q_proj.weight", "attention.q_proj.bias",
                           "attention.k_proj.weight", "attention.k_proj.bias", "attention.v_proj.weight",
                           "attention.v_proj.bias", "attention.out_proj.weight", "attention.out_proj.bias", "ln2.weight",
-                          "ln2.bias", "feed_forward.dense.fc1.weight", "feed_forward.dense.fc1.bias",
-                          "feed_forward.dense.fc2.weight", "feed_forward.dense.fc2.bias"})
+                          "ln2.bias"})
       m->slots.push_back(find(b + n));
+    if (m->lo[l].is_memory) {
+      for (const char* n : {"feed_forward.memory.query_proj.weight", "feed_forward.memory.query_proj.bias",
+                            "feed_forward.memory.gate_proj.weight", "feed_forward.memory.gate_proj.bias",
+                            "feed_forward.memory.out_proj.weight", "feed_forward.memory.out_proj.bias"})
+        m->slots.push_back(find(b + n));
+    } else {
+      for (const char* n : {"feed_forward.dense.fc1.weight", "feed_forward.dense.fc1.bias", "feed_forward.dense.fc2.weight",
+                            "feed_forward.dense.fc2.bias"})
+        m->slots.push_back(find(b + n));
+    }
   }
   for (const char* n : {"ln_f.weight", "ln_f.bias", "lm_head.weight", "lm_head.bias"}) m->slots.push_back(find(n));
 }
@@ -165,6 +220,39 @@ T* carve(uint8_t*& cursor, size_t count) {
   T* p = reinterpret_cast<T*>(cursor);
   cursor += align_up(count * sizeof(T), 256);
   return p;
+}
+
+// Buffers of the memory feed-forward blocks; appended to either route's arena.
+void plan_memory_buffers(hl_decoder* m, uint8_t*& cur) {
+  if (!m->has_memory) return;
+  const size_t N = (size_t)m->N, kd = m->mem.key_dim, vd = m->mem.value_dim, k = m->mem.top_k, d = m->cfg.d_model;
+  m->ma.assign(m->cfg.n_layers, MemoryActs{});
+  for (int l = 0; l < m->cfg.n_layers; ++l) {
+    if (!m->lo[l].is_memory) continue;
+    MemoryActs& a = m->ma[l];
+    a.query = carve<float>(cur, N * kd);
+    a.weights = carve<float>(cur, N * k);
+    a.weighted = carve<float>(cur, N * vd);
+    a.gpre = carve<float>(cur, N * vd);
+    a.gate = carve<float>(cur, N * vd);
+    a.mv = carve<float>(cur, N * vd);
+    a.idx = carve<int64_t>(cur, N * k);
+    a.mv_b = carve<__nv_bfloat16>(cur, N * vd);
+  }
+  m->m_ls = carve<float>(cur, N * m->side);
+  m->m_rs = carve<float>(cur, N * m->side);
+  m->m_scores = carve<float>(cur, N * k);
+  m->m_dmv = carve<float>(cur, N * vd);
+  m->m_dweighted = carve<float>(cur, N * vd);
+  m->m_dgate = carve<float>(cur, N * vd);
+  m->m_dgpre = carve<float>(cur, N * vd);
+  m->m_dw = carve<float>(cur, N * k);
+  m->m_dscores = carve<float>(cur, N * k);
+  m->m_dq = carve<float>(cur, N * kd);
+  m->m_dc2 = carve<float>(cur, N * d);
+  m->m_dgpre_b = carve<__nv_bfloat16>(cur, N * vd);
+  m->m_dq_b = carve<__nv_bfloat16>(cur, N * kd);
+  m->m_row_flags = carve<unsigned char>(cur, (size_t)m->mem.slots);
 }
 
 int plan_activations(hl_decoder* m, bool measure_only, size_t* bytes_out) {
@@ -202,6 +290,7 @@ int plan_activations(hl_decoder* m, bool measure_only, size_t* bytes_out) {
   m->dh = carve<__nv_bfloat16>(cur, N * F);
   m->dob = carve<__nv_bfloat16>(cur, N * d);
   m->dqkv = carve<__nv_bfloat16>(cur, N * 3 * d);
+  plan_memory_buffers(m, cur);
   m->tokens = carve<int64_t>(cur, N);
   m->targets = carve<int64_t>(cur, N);
   m->loss_dev = carve<float>(cur, 4);
@@ -237,7 +326,8 @@ int plan_activations_f32(hl_decoder* m, bool measure_only, size_t* bytes_out) {
   m->zf = carve<float>(cur, N * d);
   m->logits = carve<float>(cur, N * V);
   m->dlogits_f = carve<float>(cur, N * V);
-  m->tmp_f = carve<float>(cur, N * std::max(std::max(d, F), V));
+  m->tmp_f = carve<float>(cur, N * std::max(std::max(std::max(d, F), V),
+                                            m->has_memory ? (size_t)std::max(m->mem.key_dim, m->mem.value_dim) : (size_t)1));
   m->tmp2_f = carve<float>(cur, N * d);
   m->d_a = carve<float>(cur, N * d);
   m->d_b = carve<float>(cur, N * d);
@@ -247,6 +337,7 @@ int plan_activations_f32(hl_decoder* m, bool measure_only, size_t* bytes_out) {
   m->d_v = carve<float>(cur, N * d);
   m->d_wide = carve<float>(cur, N * F);
   m->d_wide2 = carve<float>(cur, N * F);
+  plan_memory_buffers(m, cur);
   m->tokens = carve<int64_t>(cur, N);
   m->targets = carve<int64_t>(cur, N);
   m->loss_dev = carve<float>(cur, 4);
@@ -282,6 +373,45 @@ struct Gemm {
     if (_rc != HL_OK) return _rc; \
   } while (0)
 
+// ---- memory feed-forward core (both routes): lookup, re-scoring, softmax, weighted value -----------
+// query [N, key_dim] f32 is already in ma[l].query (MemoryFeedForward::forward_named,
+// src/memory_transformer.rs:742-781).
+int memory_core_forward(hl_decoder* m, int l) {
+  hl_ctx* ctx = m->ctx;
+  MemoryActs& a = m->ma[l];
+  const float* P = m->params;
+  const int N = m->N, kd = m->mem.key_dim, vd = m->mem.value_dim, k = m->mem.top_k, side = m->side;
+  const int beam = std::min(side, std::max(k, (int)ceil(sqrt((double)k))));  // product_key_beam, :2014-2016
+  HL_TRY(hl_product_key_side_scores_f32(ctx, a.query, kd, P + m->off_kl, P + m->off_kr, m->m_ls, m->m_rs, N, side, kd));
+  HL_TRY(hl_product_key_topk_from_side_scores(ctx, m->m_ls, m->m_rs, a.idx, N, side, k, beam));
+  HL_TRY(hl_memory_selected_scores_forward(ctx, a.idx, a.query, kd, P + m->off_kl, P + m->off_kr, m->m_scores, N, k, side, kd,
+                                           m->mem.slots));
+  HL_TRY(hl_softmax_rows_f32(ctx, m->m_scores, a.weights, N, k));
+  return hl_memory_weighted_value_forward(ctx, a.idx, a.weights, P + m->off_val, a.weighted, N, k, m->mem.slots, vd);
+}
+
+// dweighted -> m_dq (gradient of the query) and the table gradients (added into the arena).
+int memory_core_backward(hl_decoder* m, int l, const float* dweighted) {
+  hl_ctx* ctx = m->ctx;
+  MemoryActs& a = m->ma[l];
+  const float* P = m->params;
+  float* G = m->grads;
+  const int N = m->N, kd = m->mem.key_dim, vd = m->mem.value_dim, k = m->mem.top_k, side = m->side;
+  HL_TRY(hl_memory_weighted_value_backward(ctx, a.idx, a.weights, P + m->off_val, dweighted, m->m_dw, G + m->off_val, N, k,
+                                           m->mem.slots, vd));
+  HL_TRY(hl_softmax_rows_backward_f32(ctx, a.weights, m->m_dw, m->m_dscores, N, k));
+  return hl_memory_selected_scores_backward(ctx, a.idx, a.query, kd, P + m->off_kl, P + m->off_kr, m->m_dscores, m->m_dq, kd,
+                                            G + m->off_kl, G + m->off_kr, N, k, side, kd, m->mem.slots);
+}
+
+// Table gradients are sums over scattered rows: they start every backward at zero.
+int zero_memory_table_grads(hl_decoder* m) {
+  if (!m->has_memory) return HL_OK;
+  const size_t count = m->off_val + (size_t)m->mem.slots * m->mem.value_dim - m->off_kl;
+  HL_CUDA(cudaMemsetAsync(m->grads + m->off_kl, 0, sizeof(float) * count, m->ctx->stream));
+  return HL_OK;
+}
+
 int forward(hl_decoder* m) {
   hl_ctx* ctx = m->ctx;
   const hl_decoder_config& c = m->cfg;
@@ -299,6 +429,21 @@ int forward(hl_decoder* m) {
     HL_TRY(g.run(N, d, d, a.o, d, HL_K_MAJOR, W + o.wo, d, HL_K_MAJOR, a.r, d, HL_BF16, HL_EPI_BIAS_RESIDUAL, P + o.bo,
                  m->x[l], d));
     HL_TRY(layer_norm_forward_impl(ctx, a.r, HL_BF16, P + o.ln2g, P + o.ln2b, a.c, HL_BF16, a.mean2, a.rstd2, N, d, 1e-5f));
+    if (o.is_memory) {
+      // The three projections run on the tensor cores with bf16 operands and f32 results; the
+      // lookup, scores, softmax, gather and gate stay in f32.
+      MemoryActs& ma = m->ma[l];
+      const int kd = m->mem.key_dim, vd = m->mem.value_dim;
+      HL_TRY(g.run(N, kd, d, a.c, d, HL_K_MAJOR, W + o.wq_m, d, HL_K_MAJOR, ma.query, kd, HL_F32, HL_EPI_BIAS, P + o.bq_m));
+      HL_TRY(memory_core_forward(m, l));
+      HL_TRY(g.run(N, vd, d, a.c, d, HL_K_MAJOR, W + o.wg_m, d, HL_K_MAJOR, ma.gpre, vd, HL_F32, HL_EPI_BIAS, P + o.bg_m));
+      HL_TRY(hl_gelu(ctx, ma.gpre, ma.gate, HL_F32, (size_t)N * vd));
+      HL_TRY(hl_binary_f32(ctx, HL_MUL, ma.weighted, ma.gate, ma.mv, (size_t)N * vd));
+      HL_TRY(hl_cast(ctx, ma.mv, HL_F32, ma.mv_b, HL_BF16, (size_t)N * vd));
+      HL_TRY(g.run(N, d, vd, ma.mv_b, vd, HL_K_MAJOR, W + o.wout_m, vd, HL_K_MAJOR, m->x[l + 1], d, HL_BF16,
+                   HL_EPI_BIAS_RESIDUAL, P + o.bout_m, a.r, d));
+      continue;
+    }
     HL_TRY(g.run(N, F, d, a.c, d, HL_K_MAJOR, W + o.w1, d, HL_K_MAJOR, a.h, F, HL_BF16, HL_EPI_BIAS_GELU, P + o.b1, nullptr,
                  0, a.g, F));
     HL_TRY(g.run(N, d, F, a.g, F, HL_K_MAJOR, W + o.w2, F, HL_K_MAJOR, m->x[l + 1], d, HL_BF16, HL_EPI_BIAS_RESIDUAL,
@@ -342,6 +487,7 @@ int backward(hl_decoder* m) {
   const __nv_bfloat16* W = m->shadow;
   float* G = m->grads;
   m->next_bucket = 0;
+  HL_TRY(zero_memory_table_grads(m));
   // loss and dlogits = (softmax - onehot)/N in bf16, the operand precision of the next GEMMs
   HL_TRY(cross_entropy_impl(ctx, m->logits, V, m->targets, N, V, 1.0f, m->loss_dev, nullptr, m->dlogits, HL_BF16, V));
   // lm_head
@@ -353,17 +499,39 @@ int backward(hl_decoder* m) {
   // every layer-norm backward also returns the column sums of the gradient it writes: the bias
   // gradient of the projection that produced that residual-stream value (fc2 or out_proj)
   HL_TRY(layer_norm_backward_impl(ctx, m->x[c.n_layers], HL_BF16, P + m->off_lnf_g, m->dtmp, m->meanf, m->rstdf, nullptr, dx,
-                                  m->dxb, G + m->off_lnf_g, G + m->off_lnf_b, G + m->lo[c.n_layers - 1].b2, N, d));
+                                  m->dxb, G + m->off_lnf_g, G + m->off_lnf_b, G + m->lo[c.n_layers - 1].out_bias(), N, d));
   HL_TRY(flush_buckets(m, m->off_lnf_b + d));
   for (int l = c.n_layers - 1; l >= 0; --l) {
     const LayerOffsets& o = m->lo[l];
     LayerActs& a = m->la[l];
+    if (o.is_memory) {
+      // y = r + out_proj(weighted * gelu(gate_proj(c))), weighted from the lookup on query_proj(c)
+      MemoryActs& ma = m->ma[l];
+      const int kd = m->mem.key_dim, vd = m->mem.value_dim;
+      const size_t nv = (size_t)N * vd;
+      HL_TRY(g.run(d, vd, N, m->dxb, d, HL_MN_MAJOR, ma.mv_b, vd, HL_MN_MAJOR, G + o.wout_m, vd, HL_F32));
+      HL_TRY(g.run(N, vd, d, m->dxb, d, HL_K_MAJOR, W + o.wout_m, vd, HL_MN_MAJOR, m->m_dmv, vd, HL_F32));
+      HL_TRY(hl_binary_f32(ctx, HL_MUL, m->m_dmv, ma.gate, m->m_dweighted, nv));
+      HL_TRY(hl_binary_f32(ctx, HL_MUL, m->m_dmv, ma.weighted, m->m_dgate, nv));
+      HL_TRY(hl_gelu_backward(ctx, ma.gpre, m->m_dgate, m->m_dgpre, HL_F32, nv));
+      HL_TRY(hl_cast(ctx, m->m_dgpre, HL_F32, m->m_dgpre_b, HL_BF16, nv));
+      HL_TRY(g.run(vd, d, N, m->m_dgpre_b, vd, HL_MN_MAJOR, a.c, d, HL_MN_MAJOR, G + o.wg_m, d, HL_F32));
+      HL_TRY(bias_grad_impl(ctx, m->m_dgpre, HL_F32, G + o.bg_m, N, vd));
+      HL_TRY(g.run(N, d, vd, m->m_dgpre_b, vd, HL_K_MAJOR, W + o.wg_m, d, HL_MN_MAJOR, m->dtmp, d, HL_F32));
+      HL_TRY(memory_core_backward(m, l, m->m_dweighted));
+      HL_TRY(hl_cast(ctx, m->m_dq, HL_F32, m->m_dq_b, HL_BF16, (size_t)N * kd));
+      HL_TRY(g.run(kd, d, N, m->m_dq_b, kd, HL_MN_MAJOR, a.c, d, HL_MN_MAJOR, G + o.wq_m, d, HL_F32));
+      HL_TRY(bias_grad_impl(ctx, m->m_dq, HL_F32, G + o.bq_m, N, kd));
+      HL_TRY(g.run(N, d, kd, m->m_dq_b, kd, HL_K_MAJOR, W + o.wq_m, d, HL_MN_MAJOR, m->m_dc2, d, HL_F32));
+      HL_TRY(hl_binary_f32(ctx, HL_ADD, m->dtmp, m->m_dc2, m->dtmp, (size_t)N * d));
+    } else {
     // y = r + fc2(gelu(fc1(c)));   dx is dL/dy (f32), dxb its bf16 operand copy
     HL_TRY(g.run(d, F, N, m->dxb, d, HL_MN_MAJOR, a.g, F, HL_MN_MAJOR, G + o.w2, F, HL_F32));
     HL_TRY(g.run(N, F, d, m->dxb, d, HL_K_MAJOR, W + o.w2, F, HL_MN_MAJOR, m->dh, F, HL_BF16, HL_EPI_DGELU, nullptr, a.h, F));
     HL_TRY(g.run(F, d, N, m->dh, F, HL_MN_MAJOR, a.c, d, HL_MN_MAJOR, G + o.w1, d, HL_F32));
     HL_TRY(bias_grad_impl(ctx, m->dh, HL_BF16, G + o.b1, N, F));
     HL_TRY(g.run(N, d, F, m->dh, F, HL_K_MAJOR, W + o.w1, d, HL_MN_MAJOR, m->dtmp, d, HL_F32));
+    }
     // dr = dx + LN2'(dc)
     HL_TRY(layer_norm_backward_impl(ctx, a.r, HL_BF16, P + o.ln2g, m->dtmp, a.mean2, a.rstd2, dx, dx_next, m->dxb,
                                     G + o.ln2g, G + o.ln2b, G + o.bo, N, d));
@@ -382,7 +550,7 @@ int backward(hl_decoder* m) {
     HL_TRY(g.run(N, d, 3 * d, m->dqkv, 3 * d, HL_K_MAJOR, W + o.wqkv, d, HL_MN_MAJOR, m->dtmp, d, HL_F32));
     // dx_in = dr + LN1'(da)
     HL_TRY(layer_norm_backward_impl(ctx, m->x[l], HL_BF16, P + o.ln1g, m->dtmp, a.mean1, a.rstd1, dx, dx_next, m->dxb,
-                                    G + o.ln1g, G + o.ln1b, l > 0 ? G + m->lo[l - 1].b2 : nullptr, N, d));
+                                    G + o.ln1g, G + o.ln1b, l > 0 ? G + m->lo[l - 1].out_bias() : nullptr, N, d));
     std::swap(dx, dx_next);
     HL_TRY(flush_buckets(m, o.ln1b + d));
   }
@@ -437,9 +605,20 @@ int forward_f32(hl_decoder* m) {
     HL_TRY(linear_f32(m, a.o, P + o.wo, P + o.bo, a.pr, N, d, d));
     HL_TRY(hl_binary_f32(ctx, HL_ADD, m->xf[l], a.pr, a.r, (size_t)N * d));
     HL_TRY(layer_norm_forward_impl(ctx, a.r, HL_F32, P + o.ln2g, P + o.ln2b, a.c, HL_F32, nullptr, nullptr, N, d, 1e-5f));
+    if (o.is_memory) {
+      MemoryActs& ma = m->ma[l];
+      const int kd = m->mem.key_dim, vd = m->mem.value_dim;
+      HL_TRY(linear_f32(m, a.c, P + o.wq_m, P + o.bq_m, ma.query, N, d, kd));
+      HL_TRY(memory_core_forward(m, l));
+      HL_TRY(linear_f32(m, a.c, P + o.wg_m, P + o.bg_m, ma.gpre, N, d, vd));
+      HL_TRY(hl_gelu(ctx, ma.gpre, ma.gate, HL_F32, (size_t)N * vd));
+      HL_TRY(hl_binary_f32(ctx, HL_MUL, ma.weighted, ma.gate, ma.mv, (size_t)N * vd));
+      HL_TRY(linear_f32(m, ma.mv, P + o.wout_m, P + o.bout_m, a.f, N, vd, d));
+    } else {
     HL_TRY(linear_f32(m, a.c, P + o.w1, P + o.b1, a.h, N, d, F));
     HL_TRY(hl_gelu(ctx, a.h, a.g, HL_F32, (size_t)N * F));
     HL_TRY(linear_f32(m, a.g, P + o.w2, P + o.b2, a.f, N, F, d));
+    }
     HL_TRY(hl_binary_f32(ctx, HL_ADD, a.r, a.f, m->xf[l + 1], (size_t)N * d));
   }
   HL_TRY(layer_norm_forward_impl(ctx, m->xf[c.n_layers], HL_F32, P + m->off_lnf_g, P + m->off_lnf_b, m->zf, HL_F32, nullptr,
@@ -455,6 +634,7 @@ int backward_f32(hl_decoder* m) {
   float* G = m->grads;
   m->next_bucket = 0;
   HL_TRY(cross_entropy_impl(ctx, m->logits, V, m->targets, N, V, 1.0f, m->loss_dev, nullptr, m->dlogits_f, HL_F32, V));
+  HL_TRY(zero_memory_table_grads(m));
   float* dx = m->d_a;       // gradient of the residual stream
   float* dx_next = m->d_b;
   HL_TRY(linear_backward_f32(m, m->zf, P + m->off_head_w, m->dlogits_f, m->d_c, 0, G + m->off_head_w, G + m->off_head_b, N,
@@ -465,10 +645,25 @@ int backward_f32(hl_decoder* m) {
   for (int l = c.n_layers - 1; l >= 0; --l) {
     const LayerOffsets& o = m->lo[l];
     hl_decoder::F32Layer& a = m->lf[l];
+    if (o.is_memory) {
+      MemoryActs& ma = m->ma[l];
+      const int kd = m->mem.key_dim, vd = m->mem.value_dim;
+      const size_t nv = (size_t)N * vd;
+      HL_TRY(linear_backward_f32(m, ma.mv, P + o.wout_m, dx, m->m_dmv, 0, G + o.wout_m, G + o.bout_m, N, vd, d));
+      HL_TRY(hl_binary_f32(ctx, HL_MUL, m->m_dmv, ma.gate, m->m_dweighted, nv));
+      HL_TRY(hl_binary_f32(ctx, HL_MUL, m->m_dmv, ma.weighted, m->m_dgate, nv));
+      HL_TRY(hl_gelu_backward(ctx, ma.gpre, m->m_dgate, m->m_dgpre, HL_F32, nv));
+      HL_TRY(linear_backward_f32(m, a.c, P + o.wg_m, m->m_dgpre, m->d_c, 0, G + o.wg_m, G + o.bg_m, N, d, vd));
+      HL_TRY(memory_core_backward(m, l, m->m_dweighted));
+      // the query path's input gradient is added to the gate path's (rounded sum of two rounded terms)
+      HL_TRY(linear_backward_f32(m, a.c, P + o.wq_m, m->m_dq, m->m_dc2, 0, G + o.wq_m, G + o.bq_m, N, d, kd));
+      HL_TRY(hl_binary_f32(ctx, HL_ADD, m->d_c, m->m_dc2, m->d_c, (size_t)N * d));
+    } else {
     // y = r + fc2(gelu(fc1(ln2 r)))
     HL_TRY(linear_backward_f32(m, a.g, P + o.w2, dx, m->d_wide, 0, G + o.w2, G + o.b2, N, F, d));
     HL_TRY(hl_gelu_backward(ctx, a.h, m->d_wide, m->d_wide2, HL_F32, (size_t)N * F));
     HL_TRY(linear_backward_f32(m, a.c, P + o.w1, m->d_wide2, m->d_c, 0, G + o.w1, G + o.b1, N, d, F));
+    }
     HL_TRY(layer_norm_backward_impl(ctx, a.r, HL_F32, P + o.ln2g, m->d_c, nullptr, nullptr, dx, dx_next, nullptr, G + o.ln2g,
                                     G + o.ln2b, nullptr, N, d));
     std::swap(dx, dx_next);  // dL/dr
@@ -530,9 +725,45 @@ int refresh_shadow(hl_decoder* m, size_t offset, size_t numel) {
 
 extern "C" {
 
+static int decoder_create_impl(hl_ctx* ctx, const hl_decoder_config* cfg, const hl_memory_config* mem, hl_decoder** out);
+
 int hl_decoder_create(hl_ctx* ctx, const hl_decoder_config* cfg, hl_decoder** out) {
+  return decoder_create_impl(ctx, cfg, nullptr, out);
+}
+
+int hl_memory_decoder_create(hl_ctx* ctx, const hl_decoder_config* cfg, const hl_memory_config* mem, hl_decoder** out) {
+  HL_REQUIRE(mem, "hl_memory_decoder_create: null memory configuration");
+  return decoder_create_impl(ctx, cfg, mem, out);
+}
+
+int hl_decoder_selected_indices(hl_decoder* m, int layer, int64_t* host, long long count) {
+  HL_REQUIRE(m && host, "hl_decoder_selected_indices: null argument");
+  HL_REQUIRE(m->has_memory && layer >= 0 && layer < m->cfg.n_layers && m->lo[layer].is_memory,
+             "hl_decoder_selected_indices: block " + std::to_string(layer) + " has no memory feed-forward");
+  HL_REQUIRE(count == (long long)m->N * m->mem.top_k, "hl_decoder_selected_indices: expected tokens * top_k entries");
+  return hl_memory_copy_indices(m->ctx, host, m->ma[layer].idx, count);
+}
+
+static int decoder_create_impl(hl_ctx* ctx, const hl_decoder_config* cfg, const hl_memory_config* mem, hl_decoder** out) {
   HL_REQUIRE(ctx && cfg && out, "hl_decoder_create: null argument");
   *out = nullptr;
+  int side = 0;
+  if (mem && mem->n_memory_layers > 0) {
+    HL_REQUIRE(mem->n_memory_layers <= 16, "hl_memory_decoder_create: at most 16 memory layers");
+    for (int i = 0; i < mem->n_memory_layers; ++i)
+      HL_REQUIRE(mem->memory_layers[i] >= 0 && mem->memory_layers[i] < cfg->n_layers,
+                 "hl_memory_decoder_create: memory layer index out of range");
+    HL_REQUIRE(mem->slots > 0 && mem->key_dim > 0 && mem->value_dim > 0 && mem->top_k > 0,
+               "hl_memory_decoder_create: memory sizes must be positive");
+    side = (int)sqrt((double)mem->slots);
+    HL_REQUIRE((long long)side * side == mem->slots,
+               "product-key memory lookup requires square memory_slots, got " + std::to_string(mem->slots));
+    HL_REQUIRE(mem->key_dim % 2 == 0, "product-key memory lookup requires even memory_key_dim, got " + std::to_string(mem->key_dim));
+    HL_REQUIRE(mem->memory_heads == 1, "memory_heads=" + std::to_string(mem->memory_heads) +
+                                           " requested, but the memory feed-forward supports one memory head");
+    HL_REQUIRE(mem->value_dim % 8 == 0 && mem->key_dim % 8 == 0, "hl_memory_decoder_create: key_dim and value_dim must be multiples of 8");
+    HL_REQUIRE(side <= 2048 && mem->top_k <= 1024, "hl_memory_decoder_create: side <= 2048 and top_k <= 1024");
+  }
   HL_REQUIRE(cfg->vocab > 0 && cfg->d_model > 0 && cfg->n_layers > 0 && cfg->n_heads > 0 && cfg->d_ff > 0 &&
                  cfg->context > 0 && cfg->batch > 0,
              "hl_decoder_create: every size must be positive");
@@ -552,6 +783,11 @@ int hl_decoder_create(hl_ctx* ctx, const hl_decoder_config* cfg, hl_decoder** ou
   m->ctx = ctx;
   m->cfg = *cfg;
   m->N = cfg->batch * cfg->context;
+  if (mem && mem->n_memory_layers > 0) {
+    m->has_memory = true;
+    m->mem = *mem;
+    m->side = side;
+  }
   plan_parameters(m);
   auto cleanup = [&](int rc) { hl_decoder_destroy(m); return rc; };
   cudaError_t e;

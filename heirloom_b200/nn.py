@@ -25,6 +25,11 @@ class _DecoderConfig(Structure):
     _fields_ = [(n, c_int) for n in ("vocab", "d_model", "n_layers", "n_heads", "d_ff", "context", "batch", "precision")]
 
 
+class _MemoryConfig(Structure):
+    _fields_ = [("n_memory_layers", c_int), ("memory_layers", c_int * 16), ("slots", c_int), ("key_dim", c_int),
+                ("value_dim", c_int), ("top_k", c_int), ("memory_heads", c_int)]
+
+
 class _AdamWConfig(Structure):
     _fields_ = [(n, c_float) for n in ("lr", "beta1", "beta2", "eps", "weight_decay", "clip_norm")]
 
@@ -41,11 +46,24 @@ class DecoderConfig:
     precision: int = PRECISION_AMP_BF16
 
 
-class DecoderLm:
-    """N-layer pre-LayerNorm decoder LM living on one GPU (`hl_decoder`)."""
+@dataclass
+class MemoryConfig:
+    """Product-key memory feed-forward blocks with one shared table set
+    (`MemoryTransformerConfig`, src/memory_transformer.rs:1217-1261)."""
+    memory_layers: Tuple[int, ...]
+    slots: int
+    key_dim: int
+    value_dim: int
+    top_k: int
+    memory_heads: int = 1
 
-    def __init__(self, ctx: Context, cfg: DecoderConfig):
-        self.ctx, self.cfg = ctx, cfg
+
+class DecoderLm:
+    """N-layer pre-LayerNorm decoder LM living on one GPU (`hl_decoder`); with `memory` the
+    listed blocks use the product-key memory feed-forward."""
+
+    def __init__(self, ctx: Context, cfg: DecoderConfig, memory: Optional[MemoryConfig] = None):
+        self.ctx, self.cfg, self.memory = ctx, cfg, memory
         self._lib = ctx.lib
         self._lib.hl_decoder_launches_last_step.restype = ctypes.c_ulonglong
         self._lib.hl_decoder_optimizer_steps.restype = c_longlong
@@ -53,7 +71,13 @@ class DecoderLm:
         c = _DecoderConfig(cfg.vocab, cfg.d_model, cfg.n_layers, cfg.n_heads, cfg.d_ff, cfg.context, cfg.batch,
                            cfg.precision)
         h = c_void_p()
-        check(self._lib.hl_decoder_create(ctx.handle, byref(c), byref(h)))
+        if memory is None:
+            check(self._lib.hl_decoder_create(ctx.handle, byref(c), byref(h)))
+        else:
+            layers = (c_int * 16)(*memory.memory_layers)
+            mc = _MemoryConfig(len(memory.memory_layers), layers, memory.slots, memory.key_dim, memory.value_dim,
+                               memory.top_k, memory.memory_heads)
+            check(self._lib.hl_memory_decoder_create(ctx.handle, byref(c), byref(mc), byref(h)))
         self.handle = h
         self._index: Dict[str, Tuple[int, Tuple[int, ...]]] = {}
         for i in range(self._lib.hl_decoder_param_count(self.handle)):
@@ -155,6 +179,15 @@ class DecoderLm:
         out = c_float()
         check(self._lib.hl_decoder_loss(self.handle, byref(out)))
         return float(out.value)
+
+    def selected_indices(self, layer: int) -> np.ndarray:
+        """Memory slots chosen by block `layer` in the last forward: int64 `[batch*context, top_k]`
+        (`MemoryFeedForward::last_selected_indices`, src/memory_transformer.rs:734-736)."""
+        n = self.cfg.batch * self.cfg.context
+        out = np.empty((n, self.memory.top_k), np.int64)
+        check(self._lib.hl_decoder_selected_indices(self.handle, c_int(layer), out.ctypes.data_as(c_void_p),
+                                                    c_longlong(out.size)))
+        return out
 
     @property
     def launches_last_step(self) -> int:

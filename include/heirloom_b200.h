@@ -362,6 +362,26 @@ typedef struct {
 typedef struct hl_decoder hl_decoder;
 
 int hl_decoder_create(hl_ctx* ctx, const hl_decoder_config* cfg, hl_decoder** out);
+/* The same decoder with product-key memory feed-forward blocks at the listed block indices and
+ * one shared table set (MemoryTransformerLm with memory layers, src/memory_transformer.rs:1217-1261,
+ * :1101-1125; memory feed-forward :742-781; gated value path = memory_plus).  Extra parameters,
+ * in state-dict order after the embeddings: shared_memory.product_key_left/right
+ * [sqrt(slots), key_dim/2], shared_memory.value [slots, value_dim]; per memory block
+ * feed_forward.memory.{query_proj,gate_proj,out_proj}.  memory_heads must be 1 like the reference
+ * (src/memory_transformer.rs:683-688).  The optimizer step is the reference's `Full` policy: dense
+ * AdamW over every parameter, tables included (runtime.rs:2416-2453).  Under
+ * HL_PRECISION_AMP_BF16 the three projections use bf16 operands on the tensor cores (the
+ * reference keeps them f32, :787-789); lookup, scores, softmax, gather and gate stay f32. */
+typedef struct {
+  int n_memory_layers;
+  int memory_layers[16];
+  int slots, key_dim, value_dim, top_k;
+  int memory_heads;
+} hl_memory_config;
+int hl_memory_decoder_create(hl_ctx* ctx, const hl_decoder_config* cfg, const hl_memory_config* mem,
+                             hl_decoder** out);
+/* Slots chosen by the last forward of one memory block: int64 [batch*context, top_k]. */
+int hl_decoder_selected_indices(hl_decoder* model, int layer, int64_t* host, long long count);
 void hl_decoder_destroy(hl_decoder* model);
 int hl_decoder_param_count(hl_decoder* model);
 int hl_decoder_param_info(hl_decoder* model, int index, char* name_out, size_t name_cap, long long* numel,

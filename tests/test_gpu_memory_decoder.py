@@ -1,0 +1,98 @@
+"""Step-level parity of the memory transformer (product-key memory feed-forward blocks)."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import heirloom_oracle as ho
+from tests.gpu_util import ctx
+
+pytestmark = pytest.mark.gpu
+
+KW = dict(vocab=512, d_model=128, n_layers=3, n_heads=2, d_ff=256, context=128)
+MEM = dict(memory_layers=(1, 2), slots=1024, key_dim=64, value_dim=64, top_k=8)
+
+
+def build(precision, batch, seed=0):
+    from heirloom_b200 import nn
+    c = ctx()
+    model = nn.DecoderLm(c, nn.DecoderConfig(batch=batch, precision=precision, **KW), nn.MemoryConfig(**MEM))
+    ocfg, omem = ho.DecoderConfig(**KW), ho.MemoryConfig(**MEM)
+    params = ho.init_memory_parameters(ocfg, omem, seed)
+    model.load_state_dict(params)
+    return model, ocfg, omem, params
+
+
+def test_parameter_names_and_shapes_follow_the_reference_state_dict():
+    from heirloom_b200 import nn
+    model, ocfg, omem, _ = build(nn.PRECISION_F32, 1)
+    assert model.parameter_names() == ho.memory_parameter_names(ocfg, omem)
+    assert model.parameter_shapes() == ho.memory_parameter_shapes(ocfg, omem)
+    model.close()
+
+
+def test_f32_route_matches_the_oracle_with_identical_indices():
+    from heirloom_b200 import nn
+    model, ocfg, omem, params = build(nn.PRECISION_F32, 2)
+    rng = np.random.default_rng(11)
+    tok = ho.zipf_tokens(rng, ocfg.vocab, (2, 129))
+    x, y = tok[:, :-1].copy(), tok[:, 1:].copy()
+    model.forward_backward(torch.tensor(x, device="cuda"), torch.tensor(y, device="cuda"))
+    oloss, ograds, oidx = ho.memory_decoder_loss_and_grads(ocfg, omem, params, x, y, return_indices=True)
+    assert abs(model.loss() - oloss) <= 1e-6 * abs(oloss)
+    for layer in MEM["memory_layers"]:
+        assert np.array_equal(model.selected_indices(layer), oidx[layer]), layer   # bit-exact top-k routing
+    for name in ho.memory_parameter_names(ocfg, omem):
+        if name.endswith("attention.k_proj.bias"):
+            continue
+        g, w = model.grad(name).astype(np.float64), ograds[name]
+        scale = np.abs(w).max() + 1e-30
+        assert np.abs(g - w).max() <= 5e-6 * scale + 1e-10, (name, np.abs(g - w).max(), scale)
+    model.close()
+
+
+def test_amp_route_tracks_the_oracle_and_routes_almost_identically():
+    from heirloom_b200 import nn
+    model, ocfg, omem, params = build(nn.PRECISION_AMP_BF16, 2, seed=1)
+    model.set_optimizer(lr=1e-3, weight_decay=0.01)
+    state = ho.AdamWState(lr=1e-3, weight_decay=0.01)
+    rng = np.random.default_rng(12)
+    agree = []
+    for step in range(5):
+        tok = ho.zipf_tokens(rng, ocfg.vocab, (2, 129))
+        x, y = tok[:, :-1].copy(), tok[:, 1:].copy()
+        loss = model.train_step(torch.tensor(x).pin_memory(), torch.tensor(y).pin_memory())
+        oloss, ograds, oidx = ho.memory_decoder_loss_and_grads(ocfg, omem, params, x, y, amp_bf16=True, return_indices=True)
+        ho.adamw_step(params, ograds, state)
+        assert abs(loss - oloss) <= 1e-2 * abs(oloss), (step, loss, oloss)
+        for layer in MEM["memory_layers"]:
+            got = model.selected_indices(layer)
+            agree.append(np.mean([len(set(a) & set(b)) / len(a) for a, b in zip(got, oidx[layer])]))
+    # projections run with bf16 operands here and in f32 in the reference: a few near-tie slots differ
+    assert min(agree) >= 0.9, agree
+    floor = 5 * 1e-3
+    report = {}
+    for name in ho.memory_parameter_names(ocfg, omem):
+        if name.endswith("attention.k_proj.bias"):
+            continue
+        got, want = model.parameter(name).astype(np.float64), params[name]
+        bad = np.abs(got - want) > 2e-2 * np.maximum(np.abs(want), floor)
+        # Small vectors that start at zero (biases) move by about lr per step whatever the gradient's
+        # size, so a handful of sign flips already is several per cent of their elements.  Parameters
+        # of the memory blocks also see the few slots that are routed differently (bf16 projections
+        # here, f32 in the reference).
+        limit = 0.25 if "memory" in name else (0.03 if got.size >= 1024 else 0.10)
+        if bad.mean() > limit:
+            report[name] = float(bad.mean())
+    assert not report, report
+    model.close()
+
+
+def test_memory_configuration_errors_read_like_the_reference():
+    from heirloom_b200 import nn
+    from heirloom_b200._lib import HeirloomError
+    c = ctx()
+    cfg = nn.DecoderConfig(batch=1, precision=nn.PRECISION_F32, **KW)
+    with pytest.raises(HeirloomError, match="supports one memory head"):
+        nn.DecoderLm(c, cfg, nn.MemoryConfig(**{**MEM, "memory_heads": 4}))
+    with pytest.raises(HeirloomError, match="square memory_slots"):
+        nn.DecoderLm(c, cfg, nn.MemoryConfig(**{**MEM, "slots": 1000}))
