@@ -103,6 +103,7 @@ struct hl_decoder {
         *m_dgpre = nullptr, *m_dw = nullptr, *m_dscores = nullptr, *m_dq = nullptr, *m_dc2 = nullptr;
   __nv_bfloat16 *m_dgpre_b = nullptr, *m_dq_b = nullptr;
   unsigned char* m_row_flags = nullptr;
+  int64_t *m_sel_all = nullptr, *m_sel_left = nullptr, *m_sel_right = nullptr;  // concatenated selections of all memory blocks
   // f32 route (reference f32 semantics: f32 tensors, f64 accumulation inside every op)
   struct F32Layer {
     float *a, *q, *k, *v, *probs, *o, *pr, *r, *c, *h, *g, *f;
@@ -253,6 +254,10 @@ void plan_memory_buffers(hl_decoder* m, uint8_t*& cur) {
   m->m_dgpre_b = carve<__nv_bfloat16>(cur, N * vd);
   m->m_dq_b = carve<__nv_bfloat16>(cur, N * kd);
   m->m_row_flags = carve<unsigned char>(cur, (size_t)m->mem.slots);
+  const size_t all = N * k * (size_t)m->mem.n_memory_layers;
+  m->m_sel_all = carve<int64_t>(cur, all);
+  m->m_sel_left = carve<int64_t>(cur, all);
+  m->m_sel_right = carve<int64_t>(cur, all);
 }
 
 int plan_activations(hl_decoder* m, bool measure_only, size_t* bytes_out) {
@@ -939,6 +944,43 @@ int hl_decoder_optimizer_step(hl_decoder* m) {
   HL_TRY(optimizer_step(m));
   m->launches_last_step += m->ctx->counters.launches - before;
   return HL_OK;
+}
+
+int hl_decoder_optimizer_step_sparse_rows(hl_decoder* m) {
+  HL_REQUIRE(m, "hl_decoder_optimizer_step_sparse_rows: null model");
+  HL_REQUIRE(m->has_memory, "hl_decoder_optimizer_step_sparse_rows: the model has no memory layers");
+  HL_REQUIRE(m->has_opt, "hl_decoder: no optimizer configured (call hl_decoder_set_optimizer)");
+  HL_REQUIRE(m->opt.clip_norm <= 0.f, "hl_decoder_optimizer_step_sparse_rows: gradient clipping over active rows is not built");
+  HL_REQUIRE(!nccl_active(m->ctx),
+             "hl_decoder_optimizer_step_sparse_rows: with more than one rank the row-union exchange is needed (not built)");
+  hl_ctx* ctx = m->ctx;
+  const size_t per_layer = (size_t)m->N * m->mem.top_k;
+  size_t total = 0;
+  // one list for all memory blocks: a row chosen by several blocks (or tokens) is updated once
+  // (memory_sparse_adamw_updates, src/memory_transformer.rs:1293-1424)
+  for (int l = 0; l < m->cfg.n_layers; ++l) {
+    if (!m->lo[l].is_memory) continue;
+    HL_CUDA(cudaMemcpyAsync(m->m_sel_all + total, m->ma[l].idx, sizeof(int64_t) * per_layer, cudaMemcpyDeviceToDevice,
+                            ctx->stream));
+    total += per_layer;
+  }
+  HL_TRY(hl_product_key_split_rows(ctx, m->m_sel_all, m->m_sel_left, m->m_sel_right, (long long)total, m->side));
+  m->step += 1;  // every sparse call advances the step counter (src/nn.rs:2262)
+  hl_adamw_params hp{};
+  hp.lr = m->opt.lr; hp.beta1 = m->opt.beta1; hp.beta2 = m->opt.beta2; hp.eps = m->opt.eps;
+  hp.weight_decay = m->opt.weight_decay;
+  hp.clip_scale = 1.0f;
+  hp.bias_correction1 = (float)(1.0 - pow((double)m->opt.beta1, (double)m->step));
+  hp.bias_correction2 = (float)(1.0 - pow((double)m->opt.beta2, (double)m->step));
+  const int half = m->mem.key_dim / 2;
+  HL_CUDA(cudaMemsetAsync(m->m_row_flags, 0, (size_t)m->mem.slots, ctx->stream));
+  HL_TRY(hl_sparse_adamw_rows_f32(ctx, m->params + m->off_kl, m->grads + m->off_kl, m->m + m->off_kl, m->v + m->off_kl,
+                                  m->m_sel_left, (long long)total, nullptr, m->m_row_flags, m->side, half, &hp, 0));
+  HL_TRY(hl_sparse_adamw_rows_f32(ctx, m->params + m->off_kr, m->grads + m->off_kr, m->m + m->off_kr, m->v + m->off_kr,
+                                  m->m_sel_right, (long long)total, nullptr, m->m_row_flags, m->side, half, &hp, 0));
+  return hl_sparse_adamw_rows_f32(ctx, m->params + m->off_val, m->grads + m->off_val, m->m + m->off_val, m->v + m->off_val,
+                                  m->m_sel_all, (long long)total, nullptr, m->m_row_flags, m->mem.slots, m->mem.value_dim, &hp,
+                                  0);
 }
 
 int hl_decoder_train_step_device(hl_decoder* m, const int64_t* tokens_dev, const int64_t* targets_dev) {

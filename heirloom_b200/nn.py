@@ -163,6 +163,12 @@ class DecoderLm:
     def optimizer_step(self) -> None:
         check(self._lib.hl_decoder_optimizer_step(self.handle))
 
+    def optimizer_step_sparse_rows(self) -> None:
+        """The reference's `SparseRows` policy (runtime.rs:2424-2435): row-set AdamW on the two
+        half-key tables and the value table over the rows the memory blocks chose in the last
+        forward, no dense update in this call."""
+        check(self._lib.hl_decoder_optimizer_step_sparse_rows(self.handle))
+
     def train_step_device(self, tokens: torch.Tensor, targets: torch.Tensor) -> None:
         check(self._lib.hl_decoder_train_step_device(self.handle, c_void_p(tokens.data_ptr()),
                                                      c_void_p(targets.data_ptr())))

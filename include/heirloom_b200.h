@@ -380,6 +380,13 @@ typedef struct {
 } hl_memory_config;
 int hl_memory_decoder_create(hl_ctx* ctx, const hl_decoder_config* cfg, const hl_memory_config* mem,
                              hl_decoder** out);
+/* The reference's `SparseRows` optimizer policy for the memory model (runtime.rs:2424-2435;
+ * descriptors memory_sparse_adamw_updates, src/memory_transformer.rs:1293-1424; step
+ * AdamW::step_sparse_rows_mut, src/nn.rs:2256-2323): row-set AdamW on product_key_left,
+ * product_key_right (rows slot/side and slot%side of every selected slot) and the value table
+ * (selected slots), rows chosen by several blocks or tokens updated once; nothing else is
+ * updated and the step counter advances by one.  Single rank, no clipping. */
+int hl_decoder_optimizer_step_sparse_rows(hl_decoder* model);
 /* Slots chosen by the last forward of one memory block: int64 [batch*context, top_k]. */
 int hl_decoder_selected_indices(hl_decoder* model, int layer, int64_t* host, long long count);
 void hl_decoder_destroy(hl_decoder* model);

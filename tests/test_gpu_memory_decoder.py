@@ -96,3 +96,32 @@ def test_memory_configuration_errors_read_like_the_reference():
         nn.DecoderLm(c, cfg, nn.MemoryConfig(**{**MEM, "memory_heads": 4}))
     with pytest.raises(HeirloomError, match="square memory_slots"):
         nn.DecoderLm(c, cfg, nn.MemoryConfig(**{**MEM, "slots": 1000}))
+
+
+def test_sparse_rows_policy_updates_only_the_selected_table_rows():
+    from heirloom_b200 import nn
+    model, ocfg, omem, params = build(nn.PRECISION_F32, 2, seed=3)
+    model.set_optimizer(lr=1e-2, weight_decay=0.01)
+    rng = np.random.default_rng(13)
+    tok = ho.zipf_tokens(rng, ocfg.vocab, (2, 129))
+    x, y = tok[:, :-1].copy(), tok[:, 1:].copy()
+    model.forward_backward(torch.tensor(x, device="cuda"), torch.tensor(y, device="cuda"))
+    _, ograds, oidx = ho.memory_decoder_loss_and_grads(ocfg, omem, params, x, y, return_indices=True)
+    model.optimizer_step_sparse_rows()
+    assert model.optimizer_steps == 1
+    selected = np.concatenate([oidx[l].reshape(-1) for l in MEM["memory_layers"]])
+    side = int(np.sqrt(MEM["slots"]))
+    state = ho.AdamWState(lr=1e-2, weight_decay=0.01)
+    for name, rows in (("shared_memory.product_key_left", selected // side), ("shared_memory.product_key_right", selected % side),
+                       ("shared_memory.value", selected)):
+        state.step = 0
+        p = params[name]
+        want = ho.adamw_sparse_rows_step(p, ograds[name], np.zeros_like(p), np.zeros_like(p), rows, state)
+        got = model.parameter(name).astype(np.float64)
+        touched = np.zeros(p.shape[0], bool); touched[rows] = True
+        assert np.array_equal(got[~touched], p[~touched])                 # untouched rows keep their bits
+        assert np.abs(got[touched] - want[touched]).max() <= 2e-4         # CPU-vs-CUDA AdamW tolerance of the reference
+        assert np.abs(got[touched] - p[touched]).max() > 1e-3             # and they did move
+    for name in ("lm_head.weight", "block.1.feed_forward.memory.query_proj.weight", "token_embedding.weight"):
+        assert np.array_equal(model.parameter(name).astype(np.float64), params[name])   # no dense update in this policy
+    model.close()
