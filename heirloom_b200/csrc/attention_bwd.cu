@@ -32,7 +32,7 @@ constexpr int FB_SMEM_BYTES = FB_SMEM_DATA + 1024;
 struct FbBarriers {
   uint64_t kv_full;
   uint64_t q_full[FB_Q_STAGES], q_empty[FB_Q_STAGES];
-  uint64_t sdp_full, p_full, dq_full;
+  uint64_t sdp_full, sdp_free, p_full, dq_full;
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -87,6 +87,7 @@ flash_attention_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
       tc05::mbar_init(&bars->q_empty[s], 1);
     }
     tc05::mbar_init(&bars->sdp_full, 1);
+    tc05::mbar_init(&bars->sdp_free, FB_SOFTMAX_WARPS);
     tc05::mbar_init(&bars->p_full, FB_SOFTMAX_WARPS);
     tc05::mbar_init(&bars->dq_full, 1);
     bars->abort_flag = layout_ok ? 0 : 1;
@@ -103,7 +104,7 @@ flash_attention_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
   const uint32_t tmem_dp = tmem_s + 128;    // 128 columns
   const uint32_t tmem_dv = tmem_s + 256;    // 64 columns
   const uint32_t tmem_dk = tmem_s + 320;    // 64 columns
-  const uint32_t tmem_dq = tmem_s + 384;    // 64 columns
+  const uint32_t tmem_dq = tmem_s + 384;    // two buffers of 64 columns, alternating by query tile
 
   if (warp == FB_SOFTMAX_WARPS) {
     // -------------------------------------------------------------------------- TMA producer
@@ -151,16 +152,22 @@ flash_attention_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
       bool ok = tc05::mbar_wait(&bars->kv_full, 0, abort_flag);
       if (ok) ok = issue_scores(0);
       for (int it = 0; it < n_tiles && ok; ++it) {
+        // S/dP of the next query tile are issued as soon as this tile's have been read out, so the
+        // softmax warps find them ready when they come back
+        if (it + 1 < n_tiles) {
+          if (!tc05::mbar_wait(&bars->sdp_free, (uint32_t)it & 1u, abort_flag)) break;
+          tc05::tc_fence_after_sync();
+          if (!issue_scores(it + 1)) break;
+        }
         if (!tc05::mbar_wait(&bars->p_full, (uint32_t)it & 1u, abort_flag)) break;
         tc05::tc_fence_after_sync();
-        if (it + 1 < n_tiles && !issue_scores(it + 1)) break;
         const int s = it % FB_Q_STAGES;
         const uint32_t aq = tc05::smem_u32(sq + s * FB_TILE_BYTES), ado = tc05::smem_u32(sdo + s * FB_TILE_BYTES);
 #pragma unroll
         for (int ks = 0; ks < FB_BM / 16; ++ks) {
           // contraction over the 128 queries of this tile: 16 query rows = 2048 bytes per step
-          const uint64_t a_pt = tc05::smem_desc_sw128(ap + ks * 2048, FB_BM * 128, 1024);    // Pᵀ  (keys x queries)
-          const uint64_t a_dst = tc05::smem_desc_sw128(ads + ks * 2048, FB_BM * 128, 1024);  // dSᵀ
+          const uint64_t a_pt = tc05::smem_desc_sw128(ap + ks * 2048, FB_BM * 128, 1024);    // P^T  (keys x queries)
+          const uint64_t a_dst = tc05::smem_desc_sw128(ads + ks * 2048, FB_BM * 128, 1024);  // dS^T
           const uint64_t b_do = tc05::smem_desc_sw128(ado + ks * 2048, FB_BM * 128, 1024);
           const uint64_t b_q = tc05::smem_desc_sw128(aq + ks * 2048, FB_BM * 128, 1024);
           const uint32_t acc = (it > 0 || ks > 0) ? 1u : 0u;
@@ -172,7 +179,7 @@ flash_attention_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
           // dQ_tile = dS·K: contraction over the 128 keys; dS is K-major in two 64-key blocks
           const uint64_t a_ds = tc05::smem_desc_sw128(ads + (ks / 4) * (FB_BM * 128) + (ks % 4) * 32, 16, 1024);
           const uint64_t b_k = tc05::smem_desc_sw128(ak + ks * 2048, FB_BN * 128, 1024);
-          tc05::umma_ss(tmem_dq, a_ds, b_k, idesc_dq, ks > 0 ? 1u : 0u);
+          tc05::umma_ss(tmem_dq + (uint32_t)((it & 1) * FB_HD), a_ds, b_k, idesc_dq, ks > 0 ? 1u : 0u);
         }
         tc05::umma_commit(&bars->q_empty[s]);
         tc05::umma_commit(&bars->dq_full);
@@ -180,72 +187,111 @@ flash_attention_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
     }
   } else {
     // -------------------------------------------------------------------------- softmax warps
+    // Per query tile: read S and dP, release them, form P and dS in registers while the tensor
+    // cores still work on the previous tile's dV/dK/dQ; then take the previous dQ tile out of
+    // tensor memory, hand P/dS over through shared memory and add the dQ tile to global memory.
     const int lg = warp & 3;          // tensor-memory lane group
     const int half = warp >> 2;       // which 64 key columns / which 32 dQ columns
     const int r = lg * 32 + lane;     // row within the tile
     const uint32_t lane_sel = (uint32_t)(lg * 32) << 16;
     bool ok = !*abort_flag;
+    // dQ tile of query tile `i`: out of tensor memory and into the f32 accumulator in global memory
+    auto add_dq = [&](int i, int t) {
+      uint32_t qb[32];
+      tc05::tmem_ld_32x32b_x32(tmem_dq + (uint32_t)((i & 1) * FB_HD) + lane_sel + half * 32, qb);
+      tc05::tmem_ld_wait();
+      if (t < p.T) {
+        float* dst = p.dq_accum + (size_t)(row_base + t) * p.ld_dq + (size_t)h * FB_HD + half * 32;
+#pragma unroll
+        for (int i = 0; i < 32; i += 4)
+          red_add_v4(dst + i, __uint_as_float(qb[i]), __uint_as_float(qb[i + 1]), __uint_as_float(qb[i + 2]),
+                     __uint_as_float(qb[i + 3]));
+      }
+    };
+    // per-row statistics of the first query tile; later tiles' are fetched one tile ahead
+    auto row_stats = [&](int it, float* neg_lse2, float* dlt) {
+      const int tt = (kj + it) * FB_BM + r;
+      const bool in = it < n_tiles && tt < p.T;
+      const size_t stat = ((size_t)b * p.H + h) * p.T + (in ? tt : 0);
+      *neg_lse2 = in ? -p.lse[stat] * 1.4426950408889634f : 0.f;
+      *dlt = in ? p.delta[stat] : 0.f;
+    };
+    float neg_lse2, dlt;
+    row_stats(0, &neg_lse2, &dlt);
     for (int it = 0; it < n_tiles && ok; ++it) {
       const int t = (kj + it) * FB_BM + r;  // query position
       const bool t_ok = t < p.T;
-      const size_t stat = ((size_t)b * p.H + h) * p.T + (t_ok ? t : 0);
-      const float lse2 = t_ok ? p.lse[stat] * 1.4426950408889634f : 0.f;
-      const float dlt = t_ok ? p.delta[stat] : 0.f;
+      float next_neg_lse2, next_dlt;
+      row_stats(it + 1, &next_neg_lse2, &next_dlt);
       if (!tc05::mbar_wait(&bars->sdp_full, (uint32_t)it & 1u, abort_flag)) { ok = false; break; }
       tc05::tc_fence_after_sync();
       const bool diag = (it == 0);
-#pragma unroll 1
-      for (int c = 0; c < 2; ++c) {
-        const int col0 = half * 64 + c * 32;  // key column within the tile
-        uint32_t sb[32], db[32];
-        tc05::tmem_ld_32x32b_x32(tmem_s + lane_sel + col0, sb);
-        tc05::tmem_ld_32x32b_x32(tmem_dp + lane_sel + col0, db);
-        tc05::tmem_ld_wait();
-        uint32_t pp[16], dd[16];
+      uint32_t pp[4][8], dd[4][8];  // P and dS of this thread's 64 key columns, bf16 pairs
+      uint32_t sb[2][16], db[2][16];
+      tc05::tmem_ld_32x32b_x16(tmem_s + lane_sel + half * 64, sb[0]);
+      tc05::tmem_ld_32x32b_x16(tmem_dp + lane_sel + half * 64, db[0]);
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
+      for (int c = 0; c < 4; ++c) {
+        const int col0 = half * 64 + c * 16;  // key column within the tile
+        tc05::tmem_ld_wait();
+        tc05::tmem_ld_fence(sb[c & 1]);
+        tc05::tmem_ld_fence(db[c & 1]);
+        if (c < 3) {  // the next 16 columns travel while these are worked on
+          tc05::tmem_ld_32x32b_x16(tmem_s + lane_sel + col0 + 16, sb[(c + 1) & 1]);
+          tc05::tmem_ld_32x32b_x16(tmem_dp + lane_sel + col0 + 16, db[(c + 1) & 1]);
+        } else {  // all of S and dP is in registers: the next tile's may overwrite them
+          tc05::tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) tc05::mbar_arrive(&bars->sdp_free);
+        }
+#pragma unroll
+        for (int i = 0; i < 16; i += 2) {
           float pr[2], dsv[2];
 #pragma unroll
           for (int e = 0; e < 2; ++e) {
             const int key = key0 + col0 + i + e;
             const bool live = t_ok && !(diag && key > t);
-            const float pv = live ? exp2f(__uint_as_float(sb[i + e]) * p.scale_log2 - lse2) : 0.f;
+            const float pv = live ? ex2_fast(fmaf(__uint_as_float(sb[c & 1][i + e]), p.scale_log2, neg_lse2)) : 0.f;
             pr[e] = pv;
-            dsv[e] = pv * (__uint_as_float(db[i + e]) - dlt) * p.scale;
+            dsv[e] = pv * (__uint_as_float(db[c & 1][i + e]) - dlt) * p.scale;
           }
-          pp[i / 2] = pack_bf16x2(pr[0], pr[1]);
-          dd[i / 2] = pack_bf16x2(dsv[0], dsv[1]);
+          pp[c][i / 2] = pack_bf16x2(pr[0], pr[1]);
+          dd[c][i / 2] = pack_bf16x2(dsv[0], dsv[1]);
         }
-        uint8_t* pline = sp + half * (FB_BM * 128) + r * 128;
-        uint8_t* dline = sds + half * (FB_BM * 128) + r * 128;
+      }
+      neg_lse2 = next_neg_lse2;
+      dlt = next_dlt;
+      // the previous tile's products have finished: its dQ is ready and P/dS may be overwritten
+      if (it > 0) {
+        if (!tc05::mbar_wait(&bars->dq_full, (uint32_t)(it - 1) & 1u, abort_flag)) { ok = false; break; }
+        tc05::tc_fence_after_sync();
+      }
+      uint8_t* pline = sp + half * (FB_BM * 128) + r * 128;
+      uint8_t* dline = sds + half * (FB_BM * 128) + r * 128;
 #pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          const int chunk = c * 4 + q;
+      for (int c = 0; c < 4; ++c) {
+#pragma unroll
+        for (int q = 0; q < 2; ++q) {
+          const int chunk = c * 2 + q;  // 16-byte chunk = 8 keys
           const int off = (chunk ^ (r & 7)) << 4;
-          *reinterpret_cast<uint4*>(pline + off) = make_uint4(pp[q * 4], pp[q * 4 + 1], pp[q * 4 + 2], pp[q * 4 + 3]);
-          *reinterpret_cast<uint4*>(dline + off) = make_uint4(dd[q * 4], dd[q * 4 + 1], dd[q * 4 + 2], dd[q * 4 + 3]);
+          *reinterpret_cast<uint4*>(pline + off) = make_uint4(pp[c][q * 4], pp[c][q * 4 + 1], pp[c][q * 4 + 2], pp[c][q * 4 + 3]);
+          *reinterpret_cast<uint4*>(dline + off) = make_uint4(dd[c][q * 4], dd[c][q * 4 + 1], dd[c][q * 4 + 2], dd[c][q * 4 + 3]);
         }
       }
       tc05::fence_proxy_async_smem();
       tc05::tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) tc05::mbar_arrive(&bars->p_full);
-      // dQ tile -> global accumulator
-      if (!tc05::mbar_wait(&bars->dq_full, (uint32_t)it & 1u, abort_flag)) { ok = false; break; }
-      tc05::tc_fence_after_sync();
-      {
-        uint32_t qb[32];
-        tc05::tmem_ld_32x32b_x32(tmem_dq + lane_sel + half * 32, qb);
-        tc05::tmem_ld_wait();
-        if (t_ok) {
-          float* dst = p.dq_accum + (size_t)(row_base + t) * p.ld_dq + (size_t)h * FB_HD + half * 32;
-#pragma unroll
-          for (int i = 0; i < 32; i += 4)
-            red_add_v4(dst + i, __uint_as_float(qb[i]), __uint_as_float(qb[i + 1]), __uint_as_float(qb[i + 2]),
-                       __uint_as_float(qb[i + 3]));
-        }
+      // the other dQ buffer is not written again before this warp's next arrival on p_full
+      if (it > 0) add_dq(it - 1, t - FB_BM);
+    }
+    if (ok) {  // dQ of the last query tile
+      if (tc05::mbar_wait(&bars->dq_full, (uint32_t)(n_tiles - 1) & 1u, abort_flag)) {
+        tc05::tc_fence_after_sync();
+        add_dq(n_tiles - 1, (kj + n_tiles - 1) * FB_BM + r);
+      } else {
+        ok = false;
       }
-      tc05::tc_fence_before_sync();
     }
     // dK, dV for this key tile (row r = key)
     if (ok) {

@@ -1,6 +1,6 @@
 // Causal flash attention forward on tcgen05: S = Q·Kᵀ and O_tile = P·V are tensor-memory
-// accumulators, K/V tiles stream in by TMA, the online softmax runs in registers (one thread
-// per query row) and P goes back to the tensor cores through swizzled shared memory.
+// accumulators, K/V tiles stream in by TMA, the online softmax runs in registers and P goes
+// back to the tensor cores through swizzled shared memory.
 //
 // Replaces the reference's attention forward family — materialised [B,H,T,T] scores
 // (src/tensor.rs:4459-4472, tensor_core.ptx:1785-2283) and the mma.sync flash forward that
@@ -11,6 +11,13 @@
 // Layout: q, k, v are bf16 row-major [B*T, *] views with heads interleaved along the channel
 // dimension (column h*hd + j, as src/tensor.rs:5156-5177), so they may live side by side in
 // one fused [B*T, 3C] projection buffer.  One CTA owns 128 query rows of one (batch, head).
+//
+// Pipeline: key tiles of 64; two S buffers and two O_tile buffers in tensor memory and two P
+// buffers in shared memory.  Four softmax warps (one per tensor-memory lane group, a thread per
+// query row) work on tile j while the tensor cores run P·V of tile j-1 and Q·Kᵀ of tile j+1; an
+// O_tile is folded into the running output two tiles later, rescaled by the maximum recorded when
+// it was produced.  The CTA is sized (192 threads, 98 KB of shared memory, 256 tensor-memory
+// columns) so that two of them share an SM and one's start-up and drain overlap the other's work.
 #include "common.cuh"
 #include "tc05.cuh"
 
@@ -18,24 +25,28 @@ namespace hl {
 namespace {
 
 constexpr int FA_BM = 128;   // query rows per CTA
-constexpr int FA_BN = 128;   // keys per tile
+constexpr int FA_BN = 64;    // keys per tile
 constexpr int FA_HD = 64;    // head dimension (one 128-byte swizzle row)
-constexpr int FA_KV_STAGES = 2;
-constexpr int FA_TILE_BYTES = 128 * FA_HD * 2;  // 16 KB
-constexpr int FA_P_BYTES = FA_BM * FA_BN * 2;   // 32 KB
-constexpr int FA_THREADS = 192;                 // warps 0-3 softmax, warp 4 TMA, warp 5 MMA
-constexpr int FA_TMEM_COLS = 256;               // S: 128 columns, O tile: 64 columns
-constexpr int FA_SMEM_DATA = FA_TILE_BYTES * (1 + 2 * FA_KV_STAGES) + FA_P_BYTES;  // 112 KB
-constexpr int FA_SMEM_BYTES = FA_SMEM_DATA + 1024;  // barriers live in the alignment slack
+constexpr int FA_KV_STAGES = 3;
+constexpr int FA_Q_BYTES = FA_BM * FA_HD * 2;   // 16 KB
+constexpr int FA_KV_BYTES = FA_BN * FA_HD * 2;  // 8 KB
+constexpr int FA_P_BYTES = FA_BM * FA_BN * 2;   // 16 KB: 128 rows of 64 keys, one 128-byte line each
+constexpr int FA_SOFTMAX_WARPS = 4;
+constexpr int FA_THREADS = (FA_SOFTMAX_WARPS + 2) * 32;  // + TMA warp + MMA warp
+constexpr int FA_TMEM_COLS = 256;  // S: 2 x 64 columns, O tile: 2 x 64 columns
+constexpr int FA_SMEM_DATA = FA_Q_BYTES + 2 * FA_KV_STAGES * FA_KV_BYTES + 2 * FA_P_BYTES;  // 96 KB
+constexpr int FA_SMEM_BYTES = FA_SMEM_DATA + 2048;  // barriers in front, alignment slack
+static_assert(2 * (FA_SMEM_BYTES + 1024) <= 228 * 1024, "two CTAs per SM");
 
-struct FaBarriers {
+struct FaShared {
   uint64_t q_full;
   uint64_t k_full[FA_KV_STAGES], k_empty[FA_KV_STAGES];
   uint64_t v_full[FA_KV_STAGES], v_empty[FA_KV_STAGES];
-  uint64_t s_full, p_full, o_full;
+  uint64_t s_full[2], p_full[2], o_full[2];
   uint32_t tmem_base;
   int abort_flag;
 };
+static_assert(sizeof(FaShared) + 1023 + FA_SMEM_DATA <= FA_SMEM_BYTES, "front matter must fit the slack");
 
 struct FaParams {
   int B, T, H;
@@ -46,20 +57,19 @@ struct FaParams {
   int* status;
 };
 
-__global__ void __launch_bounds__(FA_THREADS)
+__global__ void __launch_bounds__(FA_THREADS, 2)
 flash_attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                            const __grid_constant__ CUtensorMap map_v, const FaParams p) {
   extern __shared__ uint8_t fa_smem_raw[];
-  // Tiles need 1024-byte alignment for the 128-byte swizzle; barriers use the bytes before them.
   const uintptr_t raw = reinterpret_cast<uintptr_t>(fa_smem_raw);
-  uint8_t* tiles = reinterpret_cast<uint8_t*>((raw + sizeof(FaBarriers) + 1023) & ~uintptr_t(1023));
-  FaBarriers* bars = reinterpret_cast<FaBarriers*>(fa_smem_raw);
+  uint8_t* tiles = reinterpret_cast<uint8_t*>((raw + sizeof(FaShared) + 1023) & ~uintptr_t(1023));
+  FaShared* sh = reinterpret_cast<FaShared*>(fa_smem_raw);
   const bool layout_ok = (tiles + FA_SMEM_DATA) <= (fa_smem_raw + FA_SMEM_BYTES);
   uint8_t* sq = tiles;
-  uint8_t* sk = sq + FA_TILE_BYTES;
-  uint8_t* sv = sk + FA_KV_STAGES * FA_TILE_BYTES;
-  uint8_t* sp = sv + FA_KV_STAGES * FA_TILE_BYTES;
-  volatile int* abort_flag = &bars->abort_flag;
+  uint8_t* sk = sq + FA_Q_BYTES;
+  uint8_t* sv = sk + FA_KV_STAGES * FA_KV_BYTES;
+  uint8_t* sp = sv + FA_KV_STAGES * FA_KV_BYTES;  // two P buffers
+  volatile int* abort_flag = &sh->abort_flag;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int nq = (p.T + FA_BM - 1) / FA_BM;
@@ -67,169 +77,176 @@ flash_attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
   const int qi = nq - 1 - blockIdx.x / (p.B * p.H);  // heavy (late) query tiles are scheduled first
   const int b = bh / p.H, h = bh % p.H;
   const int q0 = qi * FA_BM;
-  const int n_tiles = qi + 1;
+  const int n_tiles = 2 * (qi + 1);  // key tiles of 64 up to and including the diagonal
   const int row_base = b * p.T;  // first row of this batch in the [B*T, *] views
 
   if (threadIdx.x == 0) {
-    tc05::mbar_init(&bars->q_full, 1);
+    tc05::mbar_init(&sh->q_full, 1);
     for (int s = 0; s < FA_KV_STAGES; ++s) {
-      tc05::mbar_init(&bars->k_full[s], 1);
-      tc05::mbar_init(&bars->k_empty[s], 1);
-      tc05::mbar_init(&bars->v_full[s], 1);
-      tc05::mbar_init(&bars->v_empty[s], 1);
+      tc05::mbar_init(&sh->k_full[s], 1);
+      tc05::mbar_init(&sh->k_empty[s], 1);
+      tc05::mbar_init(&sh->v_full[s], 1);
+      tc05::mbar_init(&sh->v_empty[s], 1);
     }
-    tc05::mbar_init(&bars->s_full, 1);
-    tc05::mbar_init(&bars->p_full, 4);
-    tc05::mbar_init(&bars->o_full, 1);
-    bars->abort_flag = layout_ok ? 0 : 1;
+    for (int i = 0; i < 2; ++i) {
+      tc05::mbar_init(&sh->s_full[i], 1);
+      tc05::mbar_init(&sh->p_full[i], FA_SOFTMAX_WARPS);
+      tc05::mbar_init(&sh->o_full[i], 1);
+    }
+    sh->abort_flag = layout_ok ? 0 : 1;
     tc05::fence_barrier_init();
   }
-  if (warp == 5) {
-    tc05::tmem_alloc(&bars->tmem_base, FA_TMEM_COLS);
+  if (warp == FA_SOFTMAX_WARPS + 1) {
+    tc05::tmem_alloc(&sh->tmem_base, FA_TMEM_COLS);
     tc05::tmem_relinquish();
   }
   tc05::tc_fence_before_sync();
   __syncthreads();
   tc05::tc_fence_after_sync();
-  const uint32_t tmem_s = bars->tmem_base;
-  const uint32_t tmem_o = tmem_s + FA_BN;
+  const uint32_t tmem_s0 = sh->tmem_base;         // S buffers at +0 and +64
+  const uint32_t tmem_o0 = tmem_s0 + 2 * FA_BN;   // O tiles at +128 and +192
 
-  if (warp == 4) {
+  if (warp == FA_SOFTMAX_WARPS) {
     // -------------------------------------------------------------------------- TMA producer
     if (tc05::elect_one() && !*abort_flag) {
       tc05::tma_prefetch_desc(&map_q);
       tc05::tma_prefetch_desc(&map_k);
       tc05::tma_prefetch_desc(&map_v);
-      tc05::mbar_arrive_expect_tx(&bars->q_full, FA_TILE_BYTES);
-      tc05::tma_load_2d(sq, &map_q, &bars->q_full, h * FA_HD, row_base + q0);
+      tc05::mbar_arrive_expect_tx(&sh->q_full, FA_Q_BYTES);
+      tc05::tma_load_2d(sq, &map_q, &sh->q_full, h * FA_HD, row_base + q0);
       for (int j = 0; j < n_tiles; ++j) {
         const int s = j % FA_KV_STAGES;
         const uint32_t ph = (uint32_t)(j / FA_KV_STAGES) & 1u;
-        if (!tc05::mbar_wait(&bars->k_empty[s], ph ^ 1u, abort_flag)) break;
-        tc05::mbar_arrive_expect_tx(&bars->k_full[s], FA_TILE_BYTES);
-        tc05::tma_load_2d(sk + s * FA_TILE_BYTES, &map_k, &bars->k_full[s], h * FA_HD, row_base + j * FA_BN);
-        if (!tc05::mbar_wait(&bars->v_empty[s], ph ^ 1u, abort_flag)) break;
-        tc05::mbar_arrive_expect_tx(&bars->v_full[s], FA_TILE_BYTES);
-        tc05::tma_load_2d(sv + s * FA_TILE_BYTES, &map_v, &bars->v_full[s], h * FA_HD, row_base + j * FA_BN);
+        if (!tc05::mbar_wait(&sh->k_empty[s], ph ^ 1u, abort_flag)) break;
+        tc05::mbar_arrive_expect_tx(&sh->k_full[s], FA_KV_BYTES);
+        tc05::tma_load_2d(sk + s * FA_KV_BYTES, &map_k, &sh->k_full[s], h * FA_HD, row_base + j * FA_BN);
+        if (!tc05::mbar_wait(&sh->v_empty[s], ph ^ 1u, abort_flag)) break;
+        tc05::mbar_arrive_expect_tx(&sh->v_full[s], FA_KV_BYTES);
+        tc05::tma_load_2d(sv + s * FA_KV_BYTES, &map_v, &sh->v_full[s], h * FA_HD, row_base + j * FA_BN);
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == FA_SOFTMAX_WARPS + 1) {
     // -------------------------------------------------------------------------- MMA issuer
     if (tc05::elect_one() && !*abort_flag) {
       constexpr uint32_t idesc_qk = tc05::instr_desc_bf16_f32(FA_BM, FA_BN, false, false);
       constexpr uint32_t idesc_pv = tc05::instr_desc_bf16_f32(FA_BM, FA_HD, false, true);
-      const uint32_t aq = tc05::smem_u32(sq), ap = tc05::smem_u32(sp);
-      auto issue_qk = [&](int j) -> bool {
+      const uint32_t aq = tc05::smem_u32(sq);
+      auto issue_qk = [&](int j) -> bool {  // S[j & 1] = Q · K(j)ᵀ
         const int s = j % FA_KV_STAGES;
-        if (!tc05::mbar_wait(&bars->k_full[s], (uint32_t)(j / FA_KV_STAGES) & 1u, abort_flag)) return false;
+        if (!tc05::mbar_wait(&sh->k_full[s], (uint32_t)(j / FA_KV_STAGES) & 1u, abort_flag)) return false;
         tc05::tc_fence_after_sync();
-        const uint32_t ak = tc05::smem_u32(sk + s * FA_TILE_BYTES);
+        const uint32_t ak = tc05::smem_u32(sk + s * FA_KV_BYTES);
 #pragma unroll
         for (int ks = 0; ks < FA_HD / 16; ++ks)
-          tc05::umma_ss(tmem_s, tc05::smem_desc_sw128(aq + ks * 32, 16, 1024),
+          tc05::umma_ss(tmem_s0 + (uint32_t)((j & 1) * FA_BN), tc05::smem_desc_sw128(aq + ks * 32, 16, 1024),
                         tc05::smem_desc_sw128(ak + ks * 32, 16, 1024), idesc_qk, ks > 0 ? 1u : 0u);
-        tc05::umma_commit(&bars->k_empty[s]);
-        tc05::umma_commit(&bars->s_full);
+        tc05::umma_commit(&sh->k_empty[s]);
+        tc05::umma_commit(&sh->s_full[j & 1]);
         return true;
       };
-      bool ok = tc05::mbar_wait(&bars->q_full, 0, abort_flag);
+      bool ok = tc05::mbar_wait(&sh->q_full, 0, abort_flag);
       if (ok) ok = issue_qk(0);
+      if (ok && n_tiles > 1) ok = issue_qk(1);
       for (int j = 0; j < n_tiles && ok; ++j) {
-        // P(j) is in shared memory and S(j) has been read out: S may be overwritten.
-        if (!tc05::mbar_wait(&bars->p_full, (uint32_t)j & 1u, abort_flag)) break;
+        // P(j) is in shared memory, which also means S(j) has been read out of tensor memory
+        if (!tc05::mbar_wait(&sh->p_full[j & 1], (uint32_t)(j >> 1) & 1u, abort_flag)) break;
         tc05::tc_fence_after_sync();
-        if (j + 1 < n_tiles && !issue_qk(j + 1)) break;
         const int s = j % FA_KV_STAGES;
-        if (!tc05::mbar_wait(&bars->v_full[s], (uint32_t)(j / FA_KV_STAGES) & 1u, abort_flag)) break;
+        if (!tc05::mbar_wait(&sh->v_full[s], (uint32_t)(j / FA_KV_STAGES) & 1u, abort_flag)) break;
         tc05::tc_fence_after_sync();
-        const uint32_t av = tc05::smem_u32(sv + s * FA_TILE_BYTES);
+        const uint32_t av = tc05::smem_u32(sv + s * FA_KV_BYTES);
+        const uint32_t ap = tc05::smem_u32(sp + (j & 1) * FA_P_BYTES);
 #pragma unroll
         for (int ks = 0; ks < FA_BN / 16; ++ks) {
-          // A = P: two 64-key blocks of [128 rows x 128 B]; B = V rows are keys (MN-major).
-          const uint64_t da = tc05::smem_desc_sw128(ap + (ks / 4) * (FA_BM * 128) + (ks % 4) * 32, 16, 1024);
+          // A = P: [128 rows x 64 keys], K-major; B = V: rows are keys (MN-major), 16 keys per step
+          const uint64_t da = tc05::smem_desc_sw128(ap + ks * 32, 16, 1024);
           const uint64_t db = tc05::smem_desc_sw128(av + ks * (16 * 128), FA_BN * 128, 1024);
-          tc05::umma_ss(tmem_o, da, db, idesc_pv, ks > 0 ? 1u : 0u);
+          tc05::umma_ss(tmem_o0 + (uint32_t)((j & 1) * FA_HD), da, db, idesc_pv, ks > 0 ? 1u : 0u);
         }
-        tc05::umma_commit(&bars->v_empty[s]);
-        tc05::umma_commit(&bars->o_full);
+        tc05::umma_commit(&sh->v_empty[s]);
+        tc05::umma_commit(&sh->o_full[j & 1]);
+        if (j + 2 < n_tiles && !issue_qk(j + 2)) break;
       }
     }
   } else {
     // -------------------------------------------------------------------------- softmax warps
-    const int r = warp * 32 + lane;            // query row within the tile == tensor-memory lane
-    const int t = q0 + r;                      // query position within the batch
+    const int r = warp * 32 + lane;     // query row within the tile == tensor-memory lane
+    const int t = q0 + r;               // query position within the batch
     const uint32_t lane_sel = (uint32_t)(warp * 32) << 16;
     float o_acc[FA_HD];
 #pragma unroll
     for (int i = 0; i < FA_HD; ++i) o_acc[i] = 0.f;
-    float m_run = -INFINITY, l_run = 0.f;
+    float m_run = -INFINITY;   // running row maximum, in log2 units
+    float m_ref = -INFINITY;   // maximum o_acc is currently scaled to
+    float l_run = 0.f;         // row sum, scaled to m_run
+    float m_hist[2] = {-INFINITY, -INFINITY};  // m_run when tile j (parity j & 1) was exponentiated
     bool ok = !*abort_flag;
-    for (int j = 0; j < n_tiles && ok; ++j) {
-      if (!tc05::mbar_wait(&bars->s_full, (uint32_t)j & 1u, abort_flag)) { ok = false; break; }
+
+    // Fold O_tile of tile `i` (made with maximum m_hist[i & 1]) into o_acc at the current maximum.
+    auto fold = [&](int i) -> bool {
+      if (!tc05::mbar_wait(&sh->o_full[i & 1], (uint32_t)(i >> 1) & 1u, abort_flag)) return false;
       tc05::tc_fence_after_sync();
-      const bool diag = (j == n_tiles - 1);
+      const float a = ex2_fast(m_ref - m_run);          // 0 when nothing has been folded yet
+      const float c = ex2_fast(m_hist[i & 1] - m_run);
+#pragma unroll
+      for (int hb = 0; hb < 2; ++hb) {
+        uint32_t ob[32];
+        tc05::tmem_ld_32x32b_x32(tmem_o0 + (uint32_t)((i & 1) * FA_HD) + lane_sel + hb * 32, ob);
+        tc05::tmem_ld_wait();
+#pragma unroll
+        for (int k = 0; k < 32; ++k) o_acc[hb * 32 + k] = o_acc[hb * 32 + k] * a + __uint_as_float(ob[k]) * c;
+      }
+      m_ref = m_run;
+      return true;
+    };
+
+    for (int j = 0; j < n_tiles && ok; ++j) {
+      // P·V of tile j-2 has finished: take its output, and its P buffer is free for this tile
+      if (j >= 2 && !fold(j - 2)) { ok = false; break; }
+      if (!tc05::mbar_wait(&sh->s_full[j & 1], (uint32_t)(j >> 1) & 1u, abort_flag)) { ok = false; break; }
+      tc05::tc_fence_after_sync();
+      const bool diag = (j >= n_tiles - 2);  // the two tiles that hold keys q0 .. q0+127
       const int key0 = j * FA_BN;
-      // pass 1: row maximum
+      uint32_t sb[FA_BN];
+      tc05::tmem_ld_32x32b_x32(tmem_s0 + (uint32_t)((j & 1) * FA_BN) + lane_sel, *reinterpret_cast<uint32_t(*)[32]>(&sb[0]));
+      tc05::tmem_ld_32x32b_x32(tmem_s0 + (uint32_t)((j & 1) * FA_BN) + lane_sel + 32, *reinterpret_cast<uint32_t(*)[32]>(&sb[32]));
+      tc05::tmem_ld_wait();
+      // maximum of the raw scores (the scale is positive); masked entries become -inf
       float m_tile = -INFINITY;
-#pragma unroll 1
-      for (int c = 0; c < FA_BN / 32; ++c) {
-        uint32_t sb[32];
-        tc05::tmem_ld_32x32b_x32(tmem_s + lane_sel + c * 32, sb);
-        tc05::tmem_ld_wait();
+      if (diag) {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float s = __uint_as_float(sb[i]) * p.scale_log2;
-          if (diag && key0 + c * 32 + i > t) s = -INFINITY;
-          m_tile = fmaxf(m_tile, s);
-        }
+        for (int i = 0; i < FA_BN; ++i)
+          if (key0 + i > t) sb[i] = 0xff800000u;
       }
-      const float m_new = fmaxf(m_run, m_tile);
-      const float alpha = exp2f(m_run - m_new);  // m_run = -inf on the first tile gives 0
-      // pass 2: probabilities, row sum, P -> shared memory (K-major, 128-byte swizzle)
-      float l_tile = 0.f;
-#pragma unroll 1
-      for (int c = 0; c < FA_BN / 32; ++c) {
-        uint32_t sb[32];
-        tc05::tmem_ld_32x32b_x32(tmem_s + lane_sel + c * 32, sb);
-        tc05::tmem_ld_wait();
-        uint32_t packed[16];
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          float s0 = __uint_as_float(sb[i]) * p.scale_log2, s1 = __uint_as_float(sb[i + 1]) * p.scale_log2;
-          if (diag && key0 + c * 32 + i > t) s0 = -INFINITY;
-          if (diag && key0 + c * 32 + i + 1 > t) s1 = -INFINITY;
-          const float p0 = exp2f(s0 - m_new), p1 = exp2f(s1 - m_new);
-          l_tile += p0 + p1;
-          packed[i / 2] = pack_bf16x2(p0, p1);
-        }
-        // 32 keys = four 16-byte chunks of this row's 128-byte line in key block c/2
-        uint8_t* line = sp + (c / 2) * (FA_BM * 128) + r * 128;
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          const int chunk = (c % 2) * 4 + q;
-          *reinterpret_cast<uint4*>(line + ((chunk ^ (r & 7)) << 4)) =
-              make_uint4(packed[q * 4], packed[q * 4 + 1], packed[q * 4 + 2], packed[q * 4 + 3]);
-        }
-      }
-      l_run = l_run * alpha + l_tile;
+      for (int i = 0; i < FA_BN; ++i) m_tile = fmaxf(m_tile, __uint_as_float(sb[i]));
+      const float m_new = fmaxf(m_run, m_tile * p.scale_log2);  // finite: key 0 is in tile 0 and visible to every row
+      l_run *= ex2_fast(m_run - m_new);
       m_run = m_new;
-      // hand P to the tensor cores
+      m_hist[j & 1] = m_new;
+      const float neg_m = -m_new;
+      uint8_t* line = sp + (j & 1) * FA_P_BYTES + r * 128;
+      float l_tile = 0.f;
+#pragma unroll
+      for (int q = 0; q < 8; ++q) {
+        uint32_t w[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float p0 = ex2_fast(fmaf(__uint_as_float(sb[q * 8 + 2 * e]), p.scale_log2, neg_m));
+          const float p1 = ex2_fast(fmaf(__uint_as_float(sb[q * 8 + 2 * e + 1]), p.scale_log2, neg_m));
+          l_tile += p0 + p1;
+          w[e] = pack_bf16x2(p0, p1);
+        }
+        *reinterpret_cast<uint4*>(line + ((q ^ (r & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+      }
+      l_run += l_tile;
       tc05::fence_proxy_async_smem();
       tc05::tc_fence_before_sync();
       __syncwarp();
-      if (lane == 0) tc05::mbar_arrive(&bars->p_full);
-      // fold O_tile = P·V into the running output
-      if (!tc05::mbar_wait(&bars->o_full, (uint32_t)j & 1u, abort_flag)) { ok = false; break; }
-      tc05::tc_fence_after_sync();
-#pragma unroll
-      for (int c = 0; c < FA_HD / 32; ++c) {
-        uint32_t ob[32];
-        tc05::tmem_ld_32x32b_x32(tmem_o + lane_sel + c * 32, ob);
-        tc05::tmem_ld_wait();
-#pragma unroll
-        for (int i = 0; i < 32; ++i) o_acc[c * 32 + i] = o_acc[c * 32 + i] * alpha + __uint_as_float(ob[i]);
-      }
+      if (lane == 0) tc05::mbar_arrive(&sh->p_full[j & 1]);
     }
+    if (ok) ok = fold(n_tiles - 2);
+    if (ok) ok = fold(n_tiles - 1);
     if (ok && t < p.T) {
       const float inv = 1.0f / l_run;
       __nv_bfloat16* dst = p.out + (size_t)(row_base + t) * p.ld_out + (size_t)h * FA_HD;
@@ -253,9 +270,9 @@ flash_attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
     for (int i = 0; i < 2000; ++i) __nanosleep(100);
     if (threadIdx.x == 0) atomicExch(p.status + (layout_ok ? ST_WAIT_EXPIRED : ST_BAD_ARGUMENT), 1);
   }
-  if (warp == 5) {
+  if (warp == FA_SOFTMAX_WARPS + 1) {
     tc05::tc_fence_after_sync();
-    tc05::tmem_dealloc(tmem_s, FA_TMEM_COLS);
+    tc05::tmem_dealloc(tmem_s0, FA_TMEM_COLS);
   }
 }
 

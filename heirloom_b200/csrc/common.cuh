@@ -152,6 +152,13 @@ __device__ __forceinline__ uint32_t pack_rounded_bf16x2(float lo, float hi) {
   return __byte_perm(__float_as_uint(lo), __float_as_uint(hi), 0x7632);
 }
 
+// 2^x in one MUFU op (relative error about 2^-22; results below the normal range flush to zero,
+// 2^-inf = 0).  exp2f() adds a range check and two scalings around the same instruction.
+__device__ __forceinline__ float ex2_fast(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 // Hardware tanh (one MUFU op, relative error about 2^-11): enough for values that are rounded
 // to bf16 right after, as in the GEMM epilogues.
 __device__ __forceinline__ float tanh_fast(float x) {
