@@ -332,20 +332,27 @@ flash_attention_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
   }
 }
 
-// delta[b,h,t] = sum_j dO[b,t,h,j] * O[b,t,h,j]; one warp per (row, head).
-__global__ void attention_delta_kernel(const __nv_bfloat16* __restrict__ out, long long ld_out,
-                                       const __nv_bfloat16* __restrict__ dout, long long ld_dout,
-                                       float* __restrict__ delta, int B, int T, int H) {
-  const int lane = threadIdx.x & 31;
-  const long long w = blockIdx.x * (long long)(blockDim.x >> 5) + (threadIdx.x >> 5);
-  if (w >= (long long)B * T * H) return;
-  const int h = (int)(w % H);
-  const long long row = w / H;  // b*T + t
-  const uint32_t o2 = *reinterpret_cast<const uint32_t*>(out + row * ld_out + h * FB_HD + lane * 2);
-  const uint32_t d2 = *reinterpret_cast<const uint32_t*>(dout + row * ld_dout + h * FB_HD + lane * 2);
-  const float2 of = unpack_bf16x2(o2), df = unpack_bf16x2(d2);
-  const float s = warp_sum(of.x * df.x + of.y * df.y);
-  if (lane == 0) {
+// delta[b,h,t] = sum_j dO[b,t,h,j] * O[b,t,h,j]; eight lanes per (row, head), 16 bytes each.
+__global__ void __launch_bounds__(256)
+attention_delta_kernel(const __nv_bfloat16* __restrict__ out, long long ld_out, const __nv_bfloat16* __restrict__ dout,
+                       long long ld_dout, float* __restrict__ delta, int B, int T, int H) {
+  const long long pair = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 3;  // (row, head)
+  const int part = threadIdx.x & 7;
+  const bool in = pair < (long long)B * T * H;
+  const int h = in ? (int)(pair % H) : 0;
+  const long long row = in ? pair / H : 0;  // b*T + t
+  const uint4 o4 = *reinterpret_cast<const uint4*>(out + row * ld_out + h * FB_HD + part * 8);
+  const uint4 d4 = *reinterpret_cast<const uint4*>(dout + row * ld_dout + h * FB_HD + part * 8);
+  float s = 0.f;
+  {
+    const float2 a0 = unpack_bf16x2(o4.x), a1 = unpack_bf16x2(o4.y), a2 = unpack_bf16x2(o4.z), a3 = unpack_bf16x2(o4.w);
+    const float2 b0 = unpack_bf16x2(d4.x), b1 = unpack_bf16x2(d4.y), b2 = unpack_bf16x2(d4.z), b3 = unpack_bf16x2(d4.w);
+    s = a0.x * b0.x + a0.y * b0.y + a1.x * b1.x + a1.y * b1.y + a2.x * b2.x + a2.y * b2.y + a3.x * b3.x + a3.y * b3.y;
+  }
+  s += __shfl_xor_sync(0xffffffffu, s, 1);
+  s += __shfl_xor_sync(0xffffffffu, s, 2);
+  s += __shfl_xor_sync(0xffffffffu, s, 4);
+  if (in && part == 0) {
     const int b = (int)(row / T), t = (int)(row % T);
     delta[((size_t)b * H + h) * T + t] = s;
   }
@@ -393,8 +400,8 @@ int flash_attention_backward_impl(hl_ctx* ctx, const void* q, const void* k, con
   ProfileScope prof(ctx, HL_PROF_ATTENTION_BWD, 5.0 * batch * n_heads * (double)time * time * head_dim);
   HL_CUDA(cudaMemsetAsync(dq_accum, 0, sizeof(float) * rows * C, ctx->stream));
   {
-    const long long warps = (long long)rows * n_heads;
-    attention_delta_kernel<<<(unsigned)ceil_div_ll(warps, 8), 256, 0, ctx->stream>>>(
+    const long long pairs = (long long)rows * n_heads;
+    attention_delta_kernel<<<(unsigned)ceil_div_ll(pairs * 8, 256), 256, 0, ctx->stream>>>(
         reinterpret_cast<const __nv_bfloat16*>(out), ld_out, reinterpret_cast<const __nv_bfloat16*>(dout), ld_dout,
         delta, batch, time, n_heads);
     HL_LAUNCH_CHECK("attention_delta_kernel");

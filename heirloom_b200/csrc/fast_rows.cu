@@ -30,156 +30,194 @@ __device__ __forceinline__ void store8_f32(float* p, const float (&v)[8]) {
   *reinterpret_cast<float4*>(p + 4) = make_float4(v[4], v[5], v[6], v[7]);
 }
 
-// One warp per row; lane owns columns (j*32 + lane)*8 .. +7 for j < J.
+__device__ __forceinline__ void unpack8_bf16(const uint4& t, float (&v)[8]) {
+  const float2 a = unpack_bf16x2(t.x), b = unpack_bf16x2(t.y), c = unpack_bf16x2(t.z), d = unpack_bf16x2(t.w);
+  v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y; v[4] = c.x; v[5] = c.y; v[6] = d.x; v[7] = d.y;
+}
+
+// One warp per row, rows taken grid-stride; lane owns columns (j*32 + lane)*8 .. +7 for j < J.  The
+// next row of the warp is requested before the current one is reduced.
 template <int J>
 __global__ void __launch_bounds__(ROW_WARPS * 32)
 ln_fwd_bf16_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ gamma, const float* __restrict__ beta,
                    __nv_bfloat16* __restrict__ y, float* __restrict__ mean_out, float* __restrict__ rstd_out, int rows,
                    int features, float eps) {
   const int lane = threadIdx.x & 31;
-  const int row = blockIdx.x * ROW_WARPS + (threadIdx.x >> 5);
-  if (row >= rows) return;
-  const __nv_bfloat16* xr = x + (size_t)row * features;
-  float v[J][8];
-  float sum = 0.f;
+  const int stride = gridDim.x * ROW_WARPS;
+  int row = blockIdx.x * ROW_WARPS + (threadIdx.x >> 5);
+  uint4 raw[J];
+  auto fetch = [&](int r) {
 #pragma unroll
-  for (int j = 0; j < J; ++j) {
-    const int c = (j * 32 + lane) * 8;
-    if (c < features) {
-      load8_bf16(xr + c, v[j]);
-#pragma unroll
-      for (int e = 0; e < 8; ++e) sum += v[j][e];
+    for (int j = 0; j < J; ++j) {
+      const int c = (j * 32 + lane) * 8;
+      raw[j] = (r < rows && c < features) ? *reinterpret_cast<const uint4*>(x + (size_t)r * features + c)
+                                          : make_uint4(0u, 0u, 0u, 0u);
     }
-  }
-  const float mean = warp_sum(sum) / (float)features;
-  float sq = 0.f;
+  };
+  fetch(row);
+  for (; row < rows; row += stride) {
+    float v[J][8];
+    float sum = 0.f;
 #pragma unroll
-  for (int j = 0; j < J; ++j) {
-    const int c = (j * 32 + lane) * 8;
-    if (c < features) {
+    for (int j = 0; j < J; ++j) {
+      unpack8_bf16(raw[j], v[j]);
 #pragma unroll
-      for (int e = 0; e < 8; ++e) { const float d = v[j][e] - mean; sq += d * d; }
+      for (int e = 0; e < 8; ++e) sum += v[j][e];  // columns past the end hold zeros
     }
-  }
-  const float rstd = 1.0f / sqrtf(warp_sum(sq) / (float)features + eps);
-  if (lane == 0) {
-    if (mean_out) mean_out[row] = mean;
-    if (rstd_out) rstd_out[row] = rstd;
-  }
-  __nv_bfloat16* yr = y + (size_t)row * features;
+    fetch(row + stride);
+    const float mean = warp_sum(sum) / (float)features;
+    float sq = 0.f;
 #pragma unroll
-  for (int j = 0; j < J; ++j) {
-    const int c = (j * 32 + lane) * 8;
-    if (c < features) {
-      float g[8], b[8], o[8];
-      load8_f32(gamma + c, g);
-      load8_f32(beta + c, b);
+    for (int j = 0; j < J; ++j) {
+      const int c = (j * 32 + lane) * 8;
+      if (c < features) {
 #pragma unroll
-      for (int e = 0; e < 8; ++e) o[e] = (v[j][e] - mean) * rstd * g[e] + b[e];
-      store8_bf16(yr + c, o);
+        for (int e = 0; e < 8; ++e) { const float d = v[j][e] - mean; sq += d * d; }
+      }
+    }
+    const float rstd = 1.0f / sqrtf(warp_sum(sq) / (float)features + eps);
+    if (lane == 0) {
+      if (mean_out) mean_out[row] = mean;
+      if (rstd_out) rstd_out[row] = rstd;
+    }
+    __nv_bfloat16* yr = y + (size_t)row * features;
+#pragma unroll
+    for (int j = 0; j < J; ++j) {
+      const int c = (j * 32 + lane) * 8;
+      if (c < features) {
+        float g[8], b[8], o[8];
+        load8_f32(gamma + c, g);
+        load8_f32(beta + c, b);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) o[e] = (v[j][e] - mean) * rstd * g[e] + b[e];
+        store8_bf16(yr + c, o);
+      }
     }
   }
 }
 
-// Each warp walks rows of its block's slab; partial[block][3][features] receives the block's
-// sums of dy*xhat, dy and of the dx written (the last only when want_colsum).
-template <int J>
-__global__ void __launch_bounds__(ROW_WARPS * 32, 1)
+// Layer-norm backward.  A row is shared by WPR warps (a thread owns 8 consecutive columns, so its
+// running column sums fit in 24 registers and many warps stay resident); a CTA holds several such
+// row groups, each walking its share of the block's slab.  partial[block][3][features] receives the
+// block's sums of dy*xhat, dy and of the dx written.
+template <int WPR>
+struct LnBwdShape {
+  static constexpr int GROUPS = (WPR >= 3) ? 12 / WPR : 8 / WPR;
+  static constexpr int THREADS = GROUPS * WPR * 32;
+  static_assert(WPR == 1 || GROUPS <= 4, "one hardware barrier per row group");
+};
+
+template <int WPR>
+__global__ void __launch_bounds__(LnBwdShape<WPR>::THREADS, 2)
 ln_bwd_bf16_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ gamma, const float* __restrict__ dy,
                    const float* __restrict__ mean_in, const float* __restrict__ rstd_in,
                    const float* __restrict__ residual, float* __restrict__ dx_f32, __nv_bfloat16* __restrict__ dx_bf16,
                    float* __restrict__ partial, int rows, int features, int rows_per_block) {
-  extern __shared__ float fold_smem[];  // [ROW_WARPS][3][features] then gamma[features]
-  float* gamma_s = fold_smem + (size_t)ROW_WARPS * 3 * features;
+  constexpr int GROUPS = LnBwdShape<WPR>::GROUPS;
+  extern __shared__ float fold_smem[];  // [GROUPS][3][features]
+  __shared__ float2 row_sums[2][GROUPS][WPR];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int group = warp / WPR, wr = warp % WPR;
+  const int c = (wr * 32 + lane) * 8;
+  const bool active = c < features;
   const int r0 = blockIdx.x * rows_per_block, r1 = min(rows, r0 + rows_per_block);
-  for (int c = threadIdx.x; c < features; c += blockDim.x) gamma_s[c] = gamma[c];
-  __syncthreads();
-  float dg[J][8], db[J][8], ds[J][8];
+  float g[8], dg[8], db[8], ds[8];
 #pragma unroll
-  for (int j = 0; j < J; ++j)
-#pragma unroll
-    for (int e = 0; e < 8; ++e) { dg[j][e] = 0.f; db[j][e] = 0.f; ds[j][e] = 0.f; }
+  for (int e = 0; e < 8; ++e) { g[e] = 0.f; dg[e] = 0.f; db[e] = 0.f; ds[e] = 0.f; }
+  if (active) load8_f32(gamma + c, g);
   const float inv_f = 1.0f / (float)features;
-  for (int row = r0 + warp; row < r1; row += ROW_WARPS) {
-    const size_t base = (size_t)row * features;
-    // every global read of the row is issued before anything is consumed
-    float xh[J][8], d[J][8], o[J][8];
+  int parity = 0;
+  for (int row = r0 + group; row < r1; row += GROUPS, parity ^= 1) {
+    const size_t base = (size_t)row * features + c;
+    float xh[8], d[8], o[8];
 #pragma unroll
-    for (int j = 0; j < J; ++j) {
-      const int c = (j * 32 + lane) * 8;
-      if (c < features) {
-        load8_bf16(x + base + c, xh[j]);
-        load8_f32(dy + base + c, d[j]);
-        if (residual) load8_f32(residual + base + c, o[j]);
-      }
+    for (int e = 0; e < 8; ++e) { xh[e] = 0.f; d[e] = 0.f; o[e] = 0.f; }
+    if (active) {  // every global read of the row is issued before anything is consumed
+      load8_bf16(x + base, xh);
+      load8_f32(dy + base, d);
+      if (residual) load8_f32(residual + base, o);
     }
     const float mean = mean_in[row], rstd = rstd_in[row];
     float s1 = 0.f, s2 = 0.f;
+    if (active) {
 #pragma unroll
-    for (int j = 0; j < J; ++j) {
-      const int c = (j * 32 + lane) * 8;
-      if (c < features) {
-        float g[8];
-        load8_f32(gamma_s + c, g);
-#pragma unroll
-        for (int e = 0; e < 8; ++e) {
-          xh[j][e] = (xh[j][e] - mean) * rstd;
-          dg[j][e] += d[j][e] * xh[j][e];
-          db[j][e] += d[j][e];
-          d[j][e] *= g[e];  // dxhat
-          s1 += d[j][e];
-          s2 += d[j][e] * xh[j][e];
-        }
+      for (int e = 0; e < 8; ++e) {
+        xh[e] = (xh[e] - mean) * rstd;
+        dg[e] += d[e] * xh[e];
+        db[e] += d[e];
+        d[e] *= g[e];  // dxhat
+        s1 += d[e];
+        s2 += d[e] * xh[e];
       }
     }
     s1 = warp_sum(s1);
     s2 = warp_sum(s2);
+    if constexpr (WPR > 1) {
+      if (lane == 0) row_sums[parity][group][wr] = make_float2(s1, s2);
+      // hardware barrier 1 + group, immediate ids so that a CTA reserves only GROUPS + 1 of the SM's 16
+      switch (group) {
+        case 0: asm volatile("bar.sync 1, %0;" ::"n"(WPR * 32) : "memory"); break;
+        case 1: asm volatile("bar.sync 2, %0;" ::"n"(WPR * 32) : "memory"); break;
+        case 2: asm volatile("bar.sync 3, %0;" ::"n"(WPR * 32) : "memory"); break;
+        default: asm volatile("bar.sync 4, %0;" ::"n"(WPR * 32) : "memory"); break;
+      }
+      s1 = 0.f;
+      s2 = 0.f;
 #pragma unroll
-    for (int j = 0; j < J; ++j) {
-      const int c = (j * 32 + lane) * 8;
-      if (c < features) {
-#pragma unroll
-        for (int e = 0; e < 8; ++e) {
-          const float dxv = rstd * ((float)features * d[j][e] - s1 - xh[j][e] * s2) * inv_f;
-          o[j][e] = residual ? o[j][e] + dxv : dxv;
-          ds[j][e] += o[j][e];
-        }
-        if (dx_f32) store8_f32(dx_f32 + base + c, o[j]);
-        if (dx_bf16) store8_bf16(dx_bf16 + base + c, o[j]);
+      for (int w = 0; w < WPR; ++w) {
+        const float2 t = row_sums[parity][group][w];
+        s1 += t.x;
+        s2 += t.y;
       }
     }
-  }
-  float* mine = fold_smem + (size_t)warp * 3 * features;
-#pragma unroll
-  for (int j = 0; j < J; ++j) {
-    const int c = (j * 32 + lane) * 8;
-    if (c < features) {
+    if (active) {
 #pragma unroll
       for (int e = 0; e < 8; ++e) {
-        mine[c + e] = dg[j][e];
-        mine[features + c + e] = db[j][e];
-        mine[2 * features + c + e] = ds[j][e];
+        const float dxv = rstd * ((float)features * d[e] - s1 - xh[e] * s2) * inv_f;
+        o[e] = residual ? o[e] + dxv : dxv;
+        ds[e] += o[e];
       }
+      if (dx_f32) store8_f32(dx_f32 + base, o);
+      if (dx_bf16) store8_bf16(dx_bf16 + base, o);
     }
   }
+  if (active) {
+    float* mine = fold_smem + (size_t)group * 3 * features + c;
+    store8_f32(mine, dg);
+    store8_f32(mine + features, db);
+    store8_f32(mine + 2 * features, ds);
+  }
   __syncthreads();
-  for (int c = threadIdx.x; c < 3 * features; c += blockDim.x) {
-    float s = 0.f;
+  for (int i = threadIdx.x; i < 3 * features; i += blockDim.x) {
+    float t = 0.f;
 #pragma unroll
-    for (int w = 0; w < ROW_WARPS; ++w) s += fold_smem[(size_t)w * 3 * features + c];
-    partial[(size_t)blockIdx.x * 3 * features + c] = s;
+    for (int w = 0; w < GROUPS; ++w) t += fold_smem[(size_t)w * 3 * features + i];
+    partial[(size_t)blockIdx.x * 3 * features + i] = t;
   }
 }
 
-__global__ void fold3_kernel(const float* __restrict__ partial, float* __restrict__ o0, float* __restrict__ o1,
-                             float* __restrict__ o2, int features, int blocks) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= 3 * features) return;
+// Sum `blocks` partial rows of `total` columns each, in a fixed order (so the result does not depend
+// on scheduling): a CTA owns 32 columns, its warps take interleaved partial rows and meet in shared
+// memory.  Column c goes to o0/o1/o2 by c / features (null pointers are skipped).
+__global__ void __launch_bounds__(ROW_WARPS * 32)
+fold_partials_kernel(const float* __restrict__ partial, int blocks, int total, float* __restrict__ o0,
+                     float* __restrict__ o1, float* __restrict__ o2, int features) {
+  __shared__ double acc[ROW_WARPS][32];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int c = blockIdx.x * 32 + lane;
   double s = 0.0;
-  for (int b = 0; b < blocks; ++b) s += (double)partial[(size_t)b * 3 * features + c];
-  float* dst = c < features ? o0 : (c < 2 * features ? o1 : o2);
-  if (dst) dst[c % features] = (float)s;
+  if (c < total) {
+#pragma unroll 4
+    for (int b = warp; b < blocks; b += ROW_WARPS) s += (double)partial[(size_t)b * total + c];
+  }
+  acc[warp][lane] = s;
+  __syncthreads();
+  if (warp == 0 && c < total) {
+#pragma unroll
+    for (int w = 1; w < ROW_WARPS; ++w) s += acc[w][lane];
+    float* dst = c < features ? o0 : (c < 2 * features ? o1 : o2);
+    if (dst) dst[c % features] = (float)s;
+  }
 }
 
 // Column sums with 16-byte loads: a warp covers 32*VEC consecutive columns, the block's eight
@@ -221,14 +259,6 @@ colsum_vec_kernel(const T* __restrict__ g, float* __restrict__ partial, int rows
   }
 }
 
-__global__ void colsum_fold_kernel(const float* __restrict__ partial, float* __restrict__ out, int cols, int slabs) {
-  const int col = blockIdx.x * blockDim.x + threadIdx.x;
-  if (col >= cols) return;
-  double s = 0.0;
-  for (int j = 0; j < slabs; ++j) s += (double)partial[(size_t)j * cols + col];
-  out[col] = (float)s;
-}
-
 }  // namespace
 
 bool layer_norm_fast_applicable(int x_dtype, int y_dtype, int features, const void* x, const void* y) {
@@ -238,7 +268,7 @@ bool layer_norm_fast_applicable(int x_dtype, int y_dtype, int features, const vo
 
 int layer_norm_forward_fast(hl_ctx* ctx, const void* x, const float* gamma, const float* beta, void* y, float* mean,
                             float* rstd, int rows, int features, float eps) {
-  const int grid = ceil_div(rows, ROW_WARPS);
+  const int grid = std::min(ceil_div(rows, ROW_WARPS), ctx->sm_count * 8);
   const int J = ceil_div(features, 256);
 #define HL_LAUNCH(JJ)                                                                                          \
   ln_fwd_bf16_kernel<JJ><<<grid, ROW_WARPS * 32, 0, ctx->stream>>>((const __nv_bfloat16*)x, gamma, beta,       \
@@ -258,23 +288,20 @@ int layer_norm_forward_fast(hl_ctx* ctx, const void* x, const float* gamma, cons
 int layer_norm_backward_fast(hl_ctx* ctx, const void* x, const float* gamma, const float* dy, const float* mean,
                              const float* rstd, const float* residual, float* dx_f32, void* dx_bf16, float* dgamma,
                              float* dbeta, float* dx_colsum, int rows, int features) {
-  int blocks = std::min(ctx->sm_count, ceil_div(rows, ROW_WARPS));
+  const int wpr = ceil_div(features, 256);  // 1..4: a warp covers 256 columns
+  const int groups = wpr >= 3 ? 12 / wpr : 8 / wpr;
+  int blocks = std::min(2 * ctx->sm_count, ceil_div(rows, groups));
   const int rows_per_block = ceil_div(rows, blocks);
   blocks = ceil_div(rows, rows_per_block);
   int rc = ensure_workspace(ctx, sizeof(float) * (size_t)blocks * 3 * features);
   if (rc != HL_OK) return rc;
   float* partial = reinterpret_cast<float*>(ctx->workspace);
-  const size_t smem = sizeof(float) * (ROW_WARPS * 3 + 1) * (size_t)features;
-  const int J = ceil_div(features, 256);
-#define HL_LAUNCH(JJ)                                                                                             \
-  do {                                                                                                            \
-    auto k = ln_bwd_bf16_kernel<JJ>;                                                                              \
-    HL_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));                     \
-    k<<<blocks, ROW_WARPS * 32, smem, ctx->stream>>>((const __nv_bfloat16*)x, gamma, dy, mean, rstd, residual,    \
-                                                      dx_f32, (__nv_bfloat16*)dx_bf16, partial, rows, features,   \
-                                                      rows_per_block);                                            \
-  } while (0)
-  switch (J) {
+  const size_t smem = sizeof(float) * (size_t)groups * 3 * features;  // at most 36 KB
+#define HL_LAUNCH(W)                                                                                              \
+  ln_bwd_bf16_kernel<W><<<blocks, LnBwdShape<W>::THREADS, smem, ctx->stream>>>(                                   \
+      (const __nv_bfloat16*)x, gamma, dy, mean, rstd, residual, dx_f32, (__nv_bfloat16*)dx_bf16, partial, rows,   \
+      features, rows_per_block)
+  switch (wpr) {
     case 1: HL_LAUNCH(1); break;
     case 2: HL_LAUNCH(2); break;
     case 3: HL_LAUNCH(3); break;
@@ -282,8 +309,9 @@ int layer_norm_backward_fast(hl_ctx* ctx, const void* x, const float* gamma, con
   }
 #undef HL_LAUNCH
   HL_LAUNCH_CHECK("ln_bwd_bf16_kernel");
-  fold3_kernel<<<ceil_div(3 * features, 256), 256, 0, ctx->stream>>>(partial, dgamma, dbeta, dx_colsum, features, blocks);
-  HL_LAUNCH_CHECK("fold3_kernel");
+  fold_partials_kernel<<<ceil_div(3 * features, 32), ROW_WARPS * 32, 0, ctx->stream>>>(partial, blocks, 3 * features, dgamma,
+                                                                                     dbeta, dx_colsum, features);
+  HL_LAUNCH_CHECK("fold_partials_kernel");
   count_launch(ctx, 2);
   return HL_OK;
 }
@@ -310,8 +338,9 @@ int colsum_fast(hl_ctx* ctx, const void* g, int dtype, float* out, int rows, int
     colsum_vec_kernel<float, 4><<<grid, ROW_WARPS * 32, 0, ctx->stream>>>((const float*)g, partial, rows, cols,
                                                                            rows_per_block);
   HL_LAUNCH_CHECK("colsum_vec_kernel");
-  colsum_fold_kernel<<<ceil_div(cols, 256), 256, 0, ctx->stream>>>(partial, out, cols, slabs);
-  HL_LAUNCH_CHECK("colsum_fold_kernel");
+  fold_partials_kernel<<<ceil_div(cols, 32), ROW_WARPS * 32, 0, ctx->stream>>>(partial, slabs, cols, out, nullptr, nullptr,
+                                                                             cols);
+  HL_LAUNCH_CHECK("fold_partials_kernel");
   count_launch(ctx, 2);
   return HL_OK;
 }
