@@ -60,6 +60,7 @@ struct hl_ctx {
   int* status_host = nullptr;          // pinned mirror
   void* workspace = nullptr;           // grow-only scratch (split-K partials, reductions)
   size_t workspace_bytes = 0;
+  void* gemm_flags = nullptr;          // per-CTA hand-over flags of the GEMM's work split, zeroed once
   hl::Counters counters{};
   void* nccl = nullptr;                // hl::NcclState*
   void* profiler = nullptr;            // hl::Profiler*, present while per-kernel timing is on

@@ -14,6 +14,16 @@
 // thread), warps 2-9 epilogue: two warps per tensor-memory lane group, each taking 128 of the
 // 256 columns.  An epilogue warp moves its 32 rows through two alternating 2 KB swizzled staging
 // tiles and writes them with TMA stores (64-byte row segments, clipped at the tensor edge).
+//
+// Work split: whole waves of output tiles go one tile per CTA; when the tiles left over would fill
+// only part of a wave, their k blocks are dealt out evenly instead (every CTA gets one contiguous
+// range of k blocks).  The CTA that owns the end of a tile's contraction
+// finishes it: the others leave their raw accumulators in a per-CTA slot of a scratch area and
+// raise a per-warp flag, and the finisher adds those slots in ascending CTA order before the
+// normal epilogue, so the result does not depend on timing.  Slots are written before a CTA
+// starts the range it finishes, so no CTA ever waits for one that is itself waiting.
+#include <atomic>
+
 #include "kernels.h"
 #include "tc05.cuh"
 
@@ -42,6 +52,11 @@ struct GemmParams {
   int epilogue;
   int out_dtype;
   int partial_out;  // split-K: raw accumulators go to the [splits][m][n] scratch through map_c
+  int dp_tiles, sk_tiles;   // whole-wave tiles, then tiles whose k blocks are dealt out evenly
+  int panel_w;              // tile columns per panel of the tile order
+  float* sk_slots;          // [grid][BM][BN] raw accumulators of unfinished tile parts
+  unsigned* sk_flags;       // [grid][EPI_WARPS]: launch number once the warp's part of the slot is written
+  unsigned sk_seq;          // this launch's number
   long long ld_aux_in;
   const float* bias;
   const void* aux_in;
@@ -57,6 +72,85 @@ struct SharedTail {
   int abort_flag;
 };
 
+enum { ITEM_FULL = 0, ITEM_PART = 1, ITEM_FINISH = 2 };
+struct WorkItem {
+  int m_tile, n_tile, split, kb0, kb1;
+  int kind;           // ITEM_FULL: whole contraction; ITEM_PART: leave raw sums in this CTA's slot;
+                      // ITEM_FINISH: end of the contraction, add the slots of CTAs first_part .. blockIdx.x-1
+  int first_part;
+};
+
+// Whether CTA `c` owns any k blocks of the evenly dealt region (with few units some CTAs own none).
+__device__ __forceinline__ bool cta_has_units(const GemmParams& p, int c) {
+  const long long units = (long long)p.sk_tiles * p.k_blocks;
+  return c * units / (int)gridDim.x != (c + 1) * units / (int)gridDim.x;
+}
+
+// The `local`-th work item of this CTA, the same sequence for every warp role.
+__device__ __forceinline__ bool get_item(const GemmParams& p, int local, WorkItem& w) {
+  const int grid = (int)gridDim.x, cta = (int)blockIdx.x;
+  const int tiles = p.m_tiles * p.n_tiles;
+  w.split = 0;
+  w.first_part = cta;
+  int tile;
+  if (p.sk_tiles == 0) {  // tiles (times explicit splits) round-robin
+    const int item = cta + local * grid;
+    if (item >= tiles * p.splits) return false;
+    w.split = item / tiles;
+    tile = item - w.split * tiles;
+    w.kb0 = w.split * p.k_blocks_per_split;
+    w.kb1 = min(p.k_blocks, w.kb0 + p.k_blocks_per_split);
+    w.kind = ITEM_FULL;
+  } else {
+    const int n_dp = cta < p.dp_tiles ? (p.dp_tiles - cta + grid - 1) / grid : 0;
+    if (local < n_dp) {
+      tile = cta + local * grid;
+      w.kb0 = 0;
+      w.kb1 = p.k_blocks;
+      w.kind = ITEM_FULL;
+    } else {
+      const int j = local - n_dp;
+      const long long units = (long long)p.sk_tiles * p.k_blocks;
+      const int u0 = (int)(cta * units / grid), u1 = (int)((cta + 1) * units / grid);
+      if (u0 >= u1) return false;
+      // The range covers the tail of one tile, whole tiles, and the head of one more.  Only the last
+      // piece can stop short of its tile's end; it goes first, so that its slot is ready early, and
+      // the piece that may have to wait for other CTAs' slots goes last.
+      const int t_first = u0 / p.k_blocks, t_last = (u1 - 1) / p.k_blocks;
+      const int n = t_last - t_first + 1;
+      if (j >= n) return false;
+      const bool last_is_part = (u1 % p.k_blocks) != 0;
+      int t;
+      if (last_is_part && n > 1) t = (j == 0) ? t_last : (j == n - 1 ? t_first : t_first + j);
+      else t = (j == n - 1) ? t_first : t_first + 1 + j;
+      const int lo = max(u0, t * p.k_blocks), hi = min(u1, (t + 1) * p.k_blocks);
+      w.kb0 = lo - t * p.k_blocks;
+      w.kb1 = hi - t * p.k_blocks;
+      tile = p.dp_tiles + t;
+      if (w.kb1 < p.k_blocks) {
+        w.kind = ITEM_PART;
+      } else if (w.kb0 == 0) {
+        w.kind = ITEM_FULL;
+      } else {
+        w.kind = ITEM_FINISH;
+        int first = cta;  // CTAs whose range reaches into this tile
+        while (first > 0 && (long long)first * units / grid > (long long)t * p.k_blocks) --first;
+        w.first_part = first;
+      }
+    }
+  }
+  // Tile order: panels of `panel_w` tile columns, rows of the panel one after the other.  CTAs that
+  // run at the same time then share a few A row blocks and a few B column blocks, so each operand
+  // byte comes out of DRAM once instead of once per tile column.
+  const int per_panel = p.panel_w * p.m_tiles;
+  const int panel = tile / per_panel;
+  const int r = tile - panel * per_panel;
+  const int width = min(p.panel_w, p.n_tiles - panel * p.panel_w);
+  w.m_tile = r / width;
+  w.n_tile = panel * p.panel_w + (r - w.m_tile * width);
+  return true;
+}
+
 template <bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
@@ -70,8 +164,6 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int total_items = p.m_tiles * p.n_tiles * p.splits;
-
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
       tc05::mbar_init(&tail->full[s], 1);
@@ -101,14 +193,10 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
-        const int split = item / (p.m_tiles * p.n_tiles);
-        const int rem = item - split * (p.m_tiles * p.n_tiles);
-        const int n_tile = rem / p.m_tiles;
-        const int m_tile = rem - n_tile * p.m_tiles;
-        const int kb0 = split * p.k_blocks_per_split;
-        const int kb1 = min(p.k_blocks, kb0 + p.k_blocks_per_split);
-        for (int kb = kb0; kb < kb1; ++kb) {
+      WorkItem w;
+      for (int local = 0; ok && get_item(p, local, w); ++local) {
+        const int m_tile = w.m_tile, n_tile = w.n_tile;
+        for (int kb = w.kb0; kb < w.kb1; ++kb) {
           if (!tc05::mbar_wait(&tail->empty[stage], phase ^ 1u, abort_flag)) { ok = false; break; }
           uint8_t* sa = smem + size_t(stage) * STAGE_BYTES;
           uint8_t* sb = sa + A_STAGE_BYTES;
@@ -137,12 +225,10 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
       constexpr uint32_t idesc = tc05::instr_desc_bf16_f32(BM, BN, A_MN, B_MN);
       int stage = 0;
       uint32_t phase = 0;
-      int local = 0;
       bool ok = true;
-      for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x, ++local) {
-        const int split = item / (p.m_tiles * p.n_tiles);
-        const int kb0 = split * p.k_blocks_per_split;
-        const int kb1 = min(p.k_blocks, kb0 + p.k_blocks_per_split);
+      WorkItem w;
+      for (int local = 0; ok && get_item(p, local, w); ++local) {
+        const int kb0 = w.kb0, kb1 = w.kb1;
         const int buf = local & 1;
         const uint32_t buf_phase = (uint32_t)(local >> 1) & 1u;
         if (!tc05::mbar_wait(&tail->tmem_empty[buf], buf_phase ^ 1u, abort_flag)) { ok = false; break; }
@@ -179,13 +265,10 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
     const bool out_bf16 = !p.partial_out && p.out_dtype == HL_BF16;
     const bool need_aux = !p.partial_out && (p.epilogue == HL_EPI_BIAS_RESIDUAL || p.epilogue == HL_EPI_DGELU);
     const bool need_bias = !p.partial_out && p.bias != nullptr;
-    int local = 0;
     bool ok = true;
-    for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x, ++local) {
-      const int split = item / (p.m_tiles * p.n_tiles);
-      const int rem = item - split * (p.m_tiles * p.n_tiles);
-      const int n_tile = rem / p.m_tiles;
-      const int m_tile = rem - n_tile * p.m_tiles;
+    WorkItem w;
+    for (int local = 0; ok && get_item(p, local, w); ++local) {
+      const int split = w.split, n_tile = w.n_tile, m_tile = w.m_tile;
       const int buf = local & 1;
       const uint32_t buf_phase = (uint32_t)(local >> 1) & 1u;
       const int row0 = m_tile * BM + lane_group * 32;
@@ -213,6 +296,56 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
       if (!tc05::mbar_wait(&tail->tmem_full[buf], buf_phase, abort_flag)) { ok = false; break; }
       tc05::tc_fence_after_sync();
       const uint32_t taddr_row = tmem_base + (uint32_t)(buf * BN) + ((uint32_t)(lane_group * 32) << 16);
+      if (w.kind == ITEM_PART) {
+        // Raw sums of a part of the contraction: this warp's 32 rows x 128 columns go to the CTA's slot.
+        // The slot is laid out [warp][chunk][q][lane] in 16-byte units, i.e. in the order the registers
+        // come out of tensor memory, so that every store (and the finisher's load) covers 512
+        // consecutive bytes.
+        float4* slot = reinterpret_cast<float4*>(p.sk_slots + (size_t)blockIdx.x * (BM * BN)) + (size_t)ew * (4 * 8 * 32) + lane;
+#pragma unroll 1
+        for (int chunk = 0; chunk < 4; ++chunk) {
+          if (half_col0 + chunk * 32 >= p.n) break;
+          uint32_t acc_bits[32];
+          tc05::tmem_ld_32x32b_x32(taddr_row + (uint32_t)(half * 128 + chunk * 32), acc_bits);
+          tc05::tmem_ld_wait();
+#pragma unroll
+          for (int q = 0; q < 8; ++q)
+            __stcg(slot + (chunk * 8 + q) * 32,
+                   make_float4(__uint_as_float(acc_bits[q * 4]), __uint_as_float(acc_bits[q * 4 + 1]),
+                               __uint_as_float(acc_bits[q * 4 + 2]), __uint_as_float(acc_bits[q * 4 + 3])));
+        }
+        __threadfence();
+        __syncwarp();
+        if (lane == 0) {
+          unsigned* flag = p.sk_flags + (size_t)blockIdx.x * EPI_WARPS + ew;
+          asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(flag), "r"(p.sk_seq) : "memory");
+        }
+        tc05::tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) tc05::mbar_arrive(&tail->tmem_empty[buf]);
+        continue;
+      }
+      if (w.kind == ITEM_FINISH) {
+        // The same warp of every earlier CTA on this tile wrote exactly the rows and columns this warp adds.
+        if (lane == 0) {
+          const unsigned long long t0 = tc05::global_timer_ns();
+          for (int c = w.first_part; c < (int)blockIdx.x && ok; ++c) {
+            if (!cta_has_units(p, c)) continue;
+            const unsigned* flag = p.sk_flags + (size_t)c * EPI_WARPS + ew;
+            for (uint32_t spins = 0;; ++spins) {
+              unsigned seen;
+              asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(flag) : "memory");
+              if (seen == p.sk_seq) break;
+              if ((spins & 63u) == 63u) {
+                if (*abort_flag || tc05::global_timer_ns() - t0 > tc05::kWaitLimitNs) { *abort_flag = 1; ok = false; break; }
+                __nanosleep(64);
+              }
+            }
+          }
+        }
+        ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+        if (!ok) break;
+      }
       // Sixteen 32-bit words of this lane's row (32 bf16 or 16 f32) go to the free staging tile
       // and out through one TMA store; at most one earlier store may still be reading.
       auto emit = [&](const CUtensorMap* map, const uint32_t* w, int col) {
@@ -237,6 +370,24 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
         uint32_t acc_bits[32];
         tc05::tmem_ld_32x32b_x32(taddr_row + (uint32_t)(half * 128 + chunk * 32), acc_bits);
         tc05::tmem_ld_wait();
+        if (w.kind == ITEM_FINISH) {
+#pragma unroll 1
+          for (int c = w.first_part; c < (int)blockIdx.x; ++c) {
+            if (!cta_has_units(p, c)) continue;
+            const float4* part = reinterpret_cast<const float4*>(p.sk_slots + (size_t)c * (BM * BN)) +
+                                 (size_t)(ew * 4 + chunk) * (8 * 32) + lane;
+            float4 t[8];  // all eight requests leave before the first sum needs its data
+#pragma unroll
+            for (int q = 0; q < 8; ++q) t[q] = __ldcg(part + q * 32);
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+              acc_bits[q * 4] = __float_as_uint(__uint_as_float(acc_bits[q * 4]) + t[q].x);
+              acc_bits[q * 4 + 1] = __float_as_uint(__uint_as_float(acc_bits[q * 4 + 1]) + t[q].y);
+              acc_bits[q * 4 + 2] = __float_as_uint(__uint_as_float(acc_bits[q * 4 + 2]) + t[q].z);
+              acc_bits[q * 4 + 3] = __float_as_uint(__uint_as_float(acc_bits[q * 4 + 3]) + t[q].w);
+            }
+          }
+        }
         uint32_t packed[16], gelu_packed[16], hi_words[16];  // f32 output: packed = columns 0-15, hi_words = 16-31
 #pragma unroll
         for (int g = 0; g < 4; ++g) {  // groups of 8 columns
@@ -359,34 +510,59 @@ int launch_variant(hl_ctx* ctx, const CUtensorMap& ma, const CUtensorMap& mb, co
 
 }  // namespace
 
-size_t gemm_splitk_workspace_bytes(const hl_gemm_desc* d, int sm_count, int* splits_out) {
+constexpr int kMinDealtKBlocks = 192;  // contraction of 12288 and up
+
+GemmPlan gemm_plan(const hl_gemm_desc* d, int sm_count) {
+  GemmPlan plan{};
   const int m_tiles = ceil_div(d->m, BM), n_tiles = ceil_div(d->n, BN);
   const int k_blocks = ceil_div(d->k, BK);
-  int splits = d->split_k;
-  if (splits <= 0) {
-    splits = 1;
-    if (d->epilogue == HL_EPI_NONE && d->out_dtype == HL_F32) {
-      // Few output tiles and a long contraction: pick the split that fills whole waves best.
-      const int tiles = m_tiles * n_tiles;
-      if (tiles < sm_count && k_blocks >= 16) {
-        double best = (double)tiles / (double)(ceil_div(tiles, sm_count) * sm_count);
-        for (int s = 2; s <= 16 && k_blocks / s >= 8; ++s) {
-          const int items = tiles * s;
-          const double eff = (double)items / (double)(ceil_div(items, sm_count) * sm_count);
-          if (eff > best + 0.02) { best = eff; splits = s; }
-        }
+  const int tiles = m_tiles * n_tiles;
+  plan.splits = 1;
+  plan.dp_tiles = tiles;
+  if (d->split_k > 1) {
+    // explicit request: every tile's contraction cut into equal parts, summed by a second kernel
+    int splits = std::min(d->split_k, k_blocks);
+    const int per = ceil_div(k_blocks, splits);
+    splits = ceil_div(k_blocks, per);  // every split owns at least one k block
+    plan.splits = splits;
+    if (splits > 1) plan.splitk_bytes = (size_t)splits * d->m * (size_t)d->n * sizeof(float);
+  } else if (d->split_k <= 0) {
+    const int rem = tiles % sm_count, waves = tiles / sm_count;
+    const bool plain_f32 = d->epilogue == HL_EPI_NONE && d->out_dtype == HL_F32;
+    if (rem != 0 && rem * 100 < sm_count * 85 && waves < 8 && k_blocks >= kMinDealtKBlocks && tiles * 2 >= sm_count) {
+      // A partly filled last wave of long tiles: deal out its k blocks.  When it is less than half
+      // full, one whole wave joins it, so that a tile is never shared by more than three CTAs.  The
+      // hand-over costs about 15 us per launch, so short contractions keep whole tiles.
+      int sk = rem;
+      if (rem * 2 < sm_count && waves >= 1) sk += sm_count;
+      plan.dp_tiles = tiles - sk;
+      plan.sk_tiles = sk;
+      plan.sk_slot_bytes = (size_t)sm_count * BM * BN * sizeof(float);
+    } else if (plain_f32 && tiles * 2 < sm_count && k_blocks >= 16) {
+      // Few output tiles and a long contraction (weight gradients): equal splits with a second
+      // kernel for the sums; pick the split that fills whole waves best.
+      int splits = 1;
+      double best = (double)tiles / (double)(ceil_div(tiles, sm_count) * sm_count);
+      for (int s = 2; s <= 16 && k_blocks / s >= 8; ++s) {
+        const int items = tiles * s;
+        const double eff = (double)items / (double)(ceil_div(items, sm_count) * sm_count);
+        if (eff > best + 0.02) { best = eff; splits = s; }
       }
+      const int per = ceil_div(k_blocks, splits);
+      splits = ceil_div(k_blocks, per);
+      plan.splits = splits;
+      if (splits > 1) plan.splitk_bytes = (size_t)splits * d->m * (size_t)d->n * sizeof(float);
     }
   }
-  splits = std::max(1, std::min(splits, k_blocks));
-  const int per = ceil_div(k_blocks, splits);
-  splits = ceil_div(k_blocks, per);  // every split owns at least one k block
-  if (splits_out) *splits_out = splits;
-  return splits > 1 ? (size_t)splits * d->m * (size_t)d->n * sizeof(float) : 0;
+  return plan;
 }
 
+size_t gemm_stream_flag_bytes(int sm_count) { return (size_t)sm_count * EPI_WARPS * sizeof(unsigned); }
+
+static std::atomic<unsigned> g_stream_launch_number{0};
+
 int gemm_bf16_run(hl_ctx* ctx, const hl_gemm_desc* d, const void* a, const void* b, void* c, const float* bias,
-                  const void* aux_in, void* aux_out, float* workspace, size_t workspace_bytes) {
+                  const void* aux_in, void* aux_out, float* workspace, size_t workspace_bytes, unsigned* stream_flags) {
   HL_REQUIRE(ctx && d, "hl_gemm_bf16: null argument");
   HL_REQUIRE(d->m > 0 && d->n > 0 && d->k > 0, "hl_gemm_bf16: m, n, k must be positive");
   HL_REQUIRE(a && b && c, "hl_gemm_bf16: null operand pointer");
@@ -425,9 +601,25 @@ int gemm_bf16_run(hl_ctx* ctx, const hl_gemm_desc* d, const void* a, const void*
   p.m_tiles = ceil_div(d->m, BM);
   p.n_tiles = ceil_div(d->n, BN);
   p.k_blocks = ceil_div(d->k, BK);
-  int splits = 1;
-  const size_t need = gemm_splitk_workspace_bytes(d, ctx->sm_count, &splits);
+  // An A operand that stays in L2 anyway keeps the plain order (one tile column after the other);
+  // a larger one is walked in panels of up to eight tile columns so that it streams from DRAM once.
+  p.panel_w = (size_t)d->m * (size_t)d->k * 2 <= (size_t(32) << 20) ? 1 : std::min(p.n_tiles, 8);
+  const GemmPlan plan = gemm_plan(d, ctx->sm_count);
+  const int splits = plan.splits;
+  const size_t need = plan.splitk_bytes;
   p.splits = splits;
+  p.dp_tiles = plan.dp_tiles;
+  p.sk_tiles = plan.sk_tiles;
+  if (plan.sk_tiles > 0) {
+    HL_REQUIRE(workspace != nullptr && workspace_bytes >= plan.sk_slot_bytes && stream_flags != nullptr,
+               "hl_gemm_bf16: scratch for partly finished tiles is too small");
+    HL_REQUIRE((reinterpret_cast<uintptr_t>(workspace) & 15) == 0, "hl_gemm_bf16: scratch must be 16-byte aligned");
+    p.sk_slots = workspace;
+    p.sk_flags = stream_flags;
+    unsigned seq = ++g_stream_launch_number;
+    if (seq == 0) seq = ++g_stream_launch_number;  // 0 means "never written"
+    p.sk_seq = seq;
+  }
   p.k_blocks_per_split = ceil_div(p.k_blocks, splits);
   p.epilogue = d->epilogue;
   p.out_dtype = d->out_dtype;
@@ -473,7 +665,7 @@ int gemm_bf16_run(hl_ctx* ctx, const hl_gemm_desc* d, const void* a, const void*
   }
 
   const int total = p.m_tiles * p.n_tiles * p.splits;
-  const int grid = min(total, ctx->sm_count);
+  const int grid = plan.sk_tiles > 0 ? ctx->sm_count : min(total, ctx->sm_count);
   ProfileScope prof(ctx, HL_PROF_GEMM, 2.0 * (double)d->m * (double)d->n * (double)d->k);
   if (a_mn && b_mn) rc = launch_variant<true, true>(ctx, ma, mb, mc, maux, p, grid);
   else if (a_mn)    rc = launch_variant<true, false>(ctx, ma, mb, mc, maux, p, grid);
@@ -493,16 +685,33 @@ int gemm_bf16_run(hl_ctx* ctx, const hl_gemm_desc* d, const void* a, const void*
 
 }  // namespace hl
 
-extern "C" int hl_gemm_bf16(hl_ctx* ctx, const hl_gemm_desc* desc, const void* a, const void* b, void* c,
-                            const float* bias, const void* aux_in, void* aux_out) {
-  if (!ctx || !desc) return hl::fail("hl_gemm_bf16: null argument");
-  const size_t need = hl::gemm_splitk_workspace_bytes(desc, ctx->sm_count, nullptr);
-  if (need > 0) {
-    int rc = hl::ensure_workspace(ctx, need);
+namespace hl {
+int gemm_bf16_ctx(hl_ctx* ctx, const hl_gemm_desc* desc, const void* a, const void* b, void* c, const float* bias,
+                  const void* aux_in, void* aux_out) {
+  if (!ctx || !desc) return fail("hl_gemm_bf16: null argument");
+  if (desc->m <= 0 || desc->n <= 0 || desc->k <= 0) return fail("hl_gemm_bf16: m, n, k must be positive");
+  const GemmPlan plan = gemm_plan(desc, ctx->sm_count);
+  const size_t need = std::max(plan.splitk_bytes, plan.sk_slot_bytes);
+  if (need > ctx->workspace_bytes) {
+    int rc = ensure_workspace(ctx, need);
     if (rc != HL_OK) return rc;
   }
-  return hl::gemm_bf16_run(ctx, desc, a, b, c, bias, aux_in, aux_out, reinterpret_cast<float*>(ctx->workspace),
-                           ctx->workspace_bytes);
+  if (plan.sk_tiles > 0 && ctx->gemm_flags == nullptr) {
+    // once per context: the flags have to start at zero and must survive growth of the scratch arena
+    const size_t bytes = gemm_stream_flag_bytes(ctx->sm_count);
+    HL_CUDA(cudaMalloc(&ctx->gemm_flags, bytes));
+    HL_CUDA(cudaMemsetAsync(ctx->gemm_flags, 0, bytes, ctx->stream));
+    ctx->counters.allocations += 1;
+    ctx->counters.allocated_bytes += bytes;
+  }
+  return gemm_bf16_run(ctx, desc, a, b, c, bias, aux_in, aux_out, reinterpret_cast<float*>(ctx->workspace),
+                       ctx->workspace_bytes, reinterpret_cast<unsigned*>(ctx->gemm_flags));
+}
+}  // namespace hl
+
+extern "C" int hl_gemm_bf16(hl_ctx* ctx, const hl_gemm_desc* desc, const void* a, const void* b, void* c,
+                            const float* bias, const void* aux_in, void* aux_out) {
+  return hl::gemm_bf16_ctx(ctx, desc, a, b, c, bias, aux_in, aux_out);
 }
 
 // ---- split-K GEMM for callers that must not allocate ----------------------------------------
@@ -519,13 +728,19 @@ namespace {
 
 constexpr size_t kStaticScratchBytes = size_t(32) << 20;
 static __device__ __align__(256) unsigned char g_gemm_static_scratch[kStaticScratchBytes];
+// Flags of the automatic work split (one word per CTA and epilogue warp), apart from the array
+// above so that split-K partial sums never land on them.  Static device memory starts at zero and
+// launch numbers do not repeat within a process, so a stale flag is never mistaken for a fresh one.
+constexpr int kStaticFlagCtas = 256;
+static __device__ __align__(256) unsigned g_gemm_static_flags[kStaticFlagCtas * EPI_WARPS];
 
 constexpr int kMaxDevices = 64;
 void* g_static_scratch_addr[kMaxDevices] = {};  // device address of the array, per device ordinal
+void* g_static_flags_addr[kMaxDevices] = {};
 
 // The array's name is only a host-side handle; the address a kernel can use has to be asked for,
 // once per device, with that device current.
-int static_scratch_address(hl_ctx* ctx, void** out) {
+int static_scratch_address(hl_ctx* ctx, void** out, void** flags_out) {
   HL_REQUIRE(ctx->device >= 0 && ctx->device < kMaxDevices, "hl_gemm_bf16_static_scratch: device ordinal out of range");
   if (g_static_scratch_addr[ctx->device] == nullptr) {
     int current = -1;
@@ -534,9 +749,14 @@ int static_scratch_address(hl_ctx* ctx, void** out) {
     void* ptr = nullptr;
     HL_CUDA(cudaGetSymbolAddress(&ptr, g_gemm_static_scratch));
     HL_REQUIRE(ptr != nullptr, "hl_gemm_bf16_static_scratch: the static scratch array has no device address");
+    void* flags = nullptr;
+    HL_CUDA(cudaGetSymbolAddress(&flags, g_gemm_static_flags));
+    HL_REQUIRE(flags != nullptr, "hl_gemm_bf16_static_scratch: the static flag array has no device address");
+    g_static_flags_addr[ctx->device] = flags;
     g_static_scratch_addr[ctx->device] = ptr;
   }
   *out = g_static_scratch_addr[ctx->device];
+  *flags_out = g_static_flags_addr[ctx->device];
   return HL_OK;
 }
 
@@ -548,16 +768,21 @@ extern "C" int hl_gemm_bf16_static_scratch(hl_ctx* ctx, const hl_gemm_desc* desc
   if (!ctx || !desc) return hl::fail("hl_gemm_bf16_static_scratch: null argument");
   if (ctx->profiler)
     return hl::fail("hl_gemm_bf16_static_scratch: per-kernel timing creates events; turn it off for calls that must not allocate");
-  const size_t need = hl::gemm_splitk_workspace_bytes(desc, ctx->sm_count, nullptr);
+  if (desc->m <= 0 || desc->n <= 0 || desc->k <= 0) return hl::fail("hl_gemm_bf16_static_scratch: m, n, k must be positive");
+  const hl::GemmPlan plan = hl::gemm_plan(desc, ctx->sm_count);
+  const size_t need = std::max(plan.splitk_bytes, plan.sk_slot_bytes);
   if (need > hl::kStaticScratchBytes)
     return hl::fail("hl_gemm_bf16_static_scratch: this shape needs " + std::to_string(need) +
                     " bytes of split-K scratch, more than the fixed " + std::to_string(hl::kStaticScratchBytes) +
                     " bytes; lower split_k or use hl_gemm_bf16");
+  if (ctx->sm_count > hl::kStaticFlagCtas)
+    return hl::fail("hl_gemm_bf16_static_scratch: more SMs than the fixed flag array covers");
   void* scratch = nullptr;
-  int rc = hl::static_scratch_address(ctx, &scratch);
+  void* flags = nullptr;
+  int rc = hl::static_scratch_address(ctx, &scratch, &flags);
   if (rc != HL_OK) return rc;
-  // Nothing in the array has to start at zero: a split-K launch writes every partial sum that
-  // its reduction reads, so the previous call's contents are simply overwritten.
+  // Nothing in the scratch array has to start at zero: a launch writes every partial sum that it
+  // later reads, so the previous call's contents are simply overwritten.
   return hl::gemm_bf16_run(ctx, desc, a, b, c, bias, aux_in, aux_out, reinterpret_cast<float*>(scratch),
-                           hl::kStaticScratchBytes);
+                           hl::kStaticScratchBytes, reinterpret_cast<unsigned*>(flags));
 }

@@ -5,9 +5,20 @@
 
 namespace hl {
 
-size_t gemm_splitk_workspace_bytes(const hl_gemm_desc* d, int sm_count, int* splits_out);
+// How a GEMM's work is cut: explicit split-K (partial sums for a second kernel), or whole waves of
+// tiles followed by tiles whose k blocks are dealt out evenly over the CTAs.
+struct GemmPlan {
+  int splits;
+  int dp_tiles, sk_tiles;
+  size_t splitk_bytes;   // scratch for explicit split-K partial sums
+  size_t sk_slot_bytes;  // scratch for the raw accumulators of partly finished tiles
+};
+GemmPlan gemm_plan(const hl_gemm_desc* d, int sm_count);
 int gemm_bf16_run(hl_ctx* ctx, const hl_gemm_desc* d, const void* a, const void* b, void* c, const float* bias,
-                  const void* aux_in, void* aux_out, float* workspace, size_t workspace_bytes);
+                  const void* aux_in, void* aux_out, float* workspace, size_t workspace_bytes, unsigned* stream_flags);
+// The GEMM with its scratch taken from (and grown in) the context.
+int gemm_bf16_ctx(hl_ctx* ctx, const hl_gemm_desc* d, const void* a, const void* b, void* c, const float* bias,
+                  const void* aux_in, void* aux_out);
 
 int bias_grad_impl(hl_ctx* ctx, const void* grad_out, int dtype, float* grad_bias, int rows, int cols);
 

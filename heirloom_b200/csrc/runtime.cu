@@ -195,6 +195,7 @@ void hl_ctx_destroy(hl_ctx* ctx) {
   cudaStreamSynchronize(ctx->comm_stream);
   if (ctx->profiler) hl_profile_enable(ctx, 0);
   if (ctx->workspace) cudaFree(ctx->workspace);
+  if (ctx->gemm_flags) cudaFree(ctx->gemm_flags);
   if (ctx->status_dev) cudaFree(ctx->status_dev);
   if (ctx->status_host) cudaFreeHost(ctx->status_host);
   cudaStreamDestroy(ctx->stream);

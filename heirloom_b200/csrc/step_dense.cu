@@ -362,13 +362,7 @@ struct Gemm {
     d.lda = lda; d.ldb = ldb; d.ldc = ldc;
     d.epilogue = epi; d.out_dtype = out_dtype; d.split_k = 0;
     d.ld_aux_in = ld_aux_in; d.ld_aux_out = ld_aux_out;
-    const size_t need = gemm_splitk_workspace_bytes(&d, m->ctx->sm_count, nullptr);
-    if (need > m->ctx->workspace_bytes) {
-      int rc = ensure_workspace(m->ctx, need);
-      if (rc != HL_OK) return rc;
-    }
-    return gemm_bf16_run(m->ctx, &d, a, b, c, bias, aux_in, aux_out, reinterpret_cast<float*>(m->ctx->workspace),
-                         m->ctx->workspace_bytes);
+    return gemm_bf16_ctx(m->ctx, &d, a, b, c, bias, aux_in, aux_out);
   }
 };
 

@@ -3,6 +3,7 @@
     python -m heirloom_b200.kernel_bench                      # everything
     python -m heirloom_b200.kernel_bench --only gemm          # cases whose name contains "gemm"
     python -m heirloom_b200.kernel_bench --only fc1_fwd --iters 3 --warmup 1   # small run for a profiler
+    python -m heirloom_b200.kernel_bench --only gemm --split-k 1   # GEMMs without the even deal of the last wave
 
 Cases: the bf16 GEMM shapes of the GPT-124M-shaped step (forward, input gradient, weight gradient),
 causal attention forward/backward (batch 16, 12 heads, head_dim 64, T 1024), layer norm and GELU
@@ -55,6 +56,9 @@ def bf16(*shape):
     return torch.randn(*shape, device="cuda").to(torch.bfloat16)
 
 
+SPLIT_K = 0  # 0: the library's own work split; 1: whole tiles only; >1: that many equal splits
+
+
 def gemm_case(ctx, m, n, k, al, bl, out_dtype=torch.bfloat16, epi=cuda.EPI_NONE):
     a = bf16(*((m, k) if al == K_ else (k, m)))
     b = bf16(*((n, k) if bl == K_ else (k, n)))
@@ -62,7 +66,7 @@ def gemm_case(ctx, m, n, k, al, bl, out_dtype=torch.bfloat16, epi=cuda.EPI_NONE)
     bias = torch.zeros(n, device="cuda") if epi in (cuda.EPI_BIAS, cuda.EPI_BIAS_GELU, cuda.EPI_BIAS_RESIDUAL) else None
     aux = bf16(m, n) if epi in (cuda.EPI_BIAS_RESIDUAL, cuda.EPI_DGELU) else None
     want_aux = epi == cuda.EPI_BIAS_GELU
-    fn = lambda: cuda.gemm_bf16(ctx, a, b, m, n, k, al, bl, epi, out_dtype, bias, aux, want_aux, out=out)
+    fn = lambda: cuda.gemm_bf16(ctx, a, b, m, n, k, al, bl, epi, out_dtype, bias, aux, want_aux, split_k=SPLIT_K, out=out)
     return fn, 2.0 * m * n * k, "flop"
 
 
@@ -140,7 +144,10 @@ def main():
     ap.add_argument("--only", default="")
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--split-k", type=int, default=0, help="split_k passed to the GEMM cases (1 = whole tiles only)")
     args = ap.parse_args()
+    global SPLIT_K
+    SPLIT_K = args.split_k
     torch.manual_seed(0)
     ctx = cuda.Context(0)
     hbm, tf, src = peaks()
