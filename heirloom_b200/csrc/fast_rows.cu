@@ -197,24 +197,34 @@ ln_bwd_bf16_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict_
 }
 
 // Sum `blocks` partial rows of `total` columns each, in a fixed order (so the result does not depend
-// on scheduling): a CTA owns 32 columns, its warps take interleaved partial rows and meet in shared
-// memory.  Column c goes to o0/o1/o2 by c / features (null pointers are skipped).
-__global__ void __launch_bounds__(ROW_WARPS * 32)
+// on scheduling): a CTA owns 32 columns, its 32 warps take interleaved partial rows (all of a warp's
+// loads are in flight together) and meet in shared memory.  Column c goes to o0/o1/o2 by
+// c / features (null pointers are skipped).
+constexpr int FOLD_WARPS = 32;
+__global__ void __launch_bounds__(FOLD_WARPS * 32)
 fold_partials_kernel(const float* __restrict__ partial, int blocks, int total, float* __restrict__ o0,
                      float* __restrict__ o1, float* __restrict__ o2, int features) {
-  __shared__ double acc[ROW_WARPS][32];
+  __shared__ double acc[FOLD_WARPS][33];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int c = blockIdx.x * 32 + lane;
   double s = 0.0;
   if (c < total) {
-#pragma unroll 4
-    for (int b = warp; b < blocks; b += ROW_WARPS) s += (double)partial[(size_t)b * total + c];
+    for (int b0 = warp; b0 < blocks; b0 += FOLD_WARPS * 8) {
+      float v[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const int b = b0 + u * FOLD_WARPS;
+        v[u] = b < blocks ? partial[(size_t)b * total + c] : 0.f;
+      }
+#pragma unroll
+      for (int u = 0; u < 8; ++u) s += (double)v[u];
+    }
   }
   acc[warp][lane] = s;
   __syncthreads();
   if (warp == 0 && c < total) {
-#pragma unroll
-    for (int w = 1; w < ROW_WARPS; ++w) s += acc[w][lane];
+#pragma unroll 8
+    for (int w = 1; w < FOLD_WARPS; ++w) s += acc[w][lane];
     float* dst = c < features ? o0 : (c < 2 * features ? o1 : o2);
     if (dst) dst[c % features] = (float)s;
   }
@@ -309,7 +319,7 @@ int layer_norm_backward_fast(hl_ctx* ctx, const void* x, const float* gamma, con
   }
 #undef HL_LAUNCH
   HL_LAUNCH_CHECK("ln_bwd_bf16_kernel");
-  fold_partials_kernel<<<ceil_div(3 * features, 32), ROW_WARPS * 32, 0, ctx->stream>>>(partial, blocks, 3 * features, dgamma,
+  fold_partials_kernel<<<ceil_div(3 * features, 32), FOLD_WARPS * 32, 0, ctx->stream>>>(partial, blocks, 3 * features, dgamma,
                                                                                      dbeta, dx_colsum, features);
   HL_LAUNCH_CHECK("fold_partials_kernel");
   count_launch(ctx, 2);
@@ -338,7 +348,7 @@ int colsum_fast(hl_ctx* ctx, const void* g, int dtype, float* out, int rows, int
     colsum_vec_kernel<float, 4><<<grid, ROW_WARPS * 32, 0, ctx->stream>>>((const float*)g, partial, rows, cols,
                                                                            rows_per_block);
   HL_LAUNCH_CHECK("colsum_vec_kernel");
-  fold_partials_kernel<<<ceil_div(cols, 32), ROW_WARPS * 32, 0, ctx->stream>>>(partial, slabs, cols, out, nullptr, nullptr,
+  fold_partials_kernel<<<ceil_div(cols, 32), FOLD_WARPS * 32, 0, ctx->stream>>>(partial, slabs, cols, out, nullptr, nullptr,
                                                                              cols);
   HL_LAUNCH_CHECK("fold_partials_kernel");
   count_launch(ctx, 2);

@@ -350,12 +350,14 @@ __global__ void cross_entropy_kernel(const float* __restrict__ logits, long long
 // bf16-gradient route: persistent blocks walk rows, so only a few hundred rows (tens of MB)
 // are in flight and the second read of a row is served by L2.  Pass 1 is an online
 // max / sum-of-exponentials (one read), pass 2 writes dlogits = (softmax - onehot) * scale.
-__global__ void __launch_bounds__(1024)
+constexpr int CE_THREADS = 512;
+__global__ void __launch_bounds__(CE_THREADS, 2)
 cross_entropy_online_kernel(const float* __restrict__ logits, long long ld, const int64_t* __restrict__ targets,
                             int rows, int classes, float scale, float* __restrict__ row_loss,
                             __nv_bfloat16* __restrict__ dlogits, long long ld_d, int* __restrict__ status) {
   __shared__ float sm[32];
   constexpr float kLog2e = 1.4426950408889634f;
+  constexpr int STEP = CE_THREADS * 4;  // columns covered by one 16-byte load per thread
   for (int row = blockIdx.x; row < rows; row += gridDim.x) {
     const float* z = logits + (size_t)row * ld;
     const long long target = targets[row];
@@ -363,27 +365,51 @@ cross_entropy_online_kernel(const float* __restrict__ logits, long long ld, cons
       if (threadIdx.x == 0) { atomicExch(status + ST_BAD_INDEX, 1); if (row_loss) row_loss[row] = 0.f; }
       continue;
     }
-    float m = -INFINITY, s = 0.f;
-    for (int c = threadIdx.x * 4; c < classes; c += blockDim.x * 4) {
-      const float4 v = *reinterpret_cast<const float4*>(z + c);
-      const float mx = fmaxf(fmaxf(v.x, v.y), fmaxf(v.z, v.w));
-      if (mx > m) { s *= exp2f((m - mx) * kLog2e); m = mx; }
-      s += exp2f((v.x - m) * kLog2e) + exp2f((v.y - m) * kLog2e) + exp2f((v.z - m) * kLog2e) + exp2f((v.w - m) * kLog2e);
+    const float z_target = z[target];  // read before pass 2 may overwrite an aliased buffer
+    // pass 1: four independent 16-byte loads per thread and step, one rescale of the running sum per step
+    float m = -INFINITY, s = 0.f;  // m in units of log2(e) * logit
+    for (int c0 = threadIdx.x * 4; c0 < classes; c0 += 4 * STEP) {
+      float4 v[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int c = c0 + u * STEP;
+        v[u] = c < classes ? *reinterpret_cast<const float4*>(z + c) : make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
+      }
+      float mx = -INFINITY;
+#pragma unroll
+      for (int u = 0; u < 4; ++u) mx = fmaxf(mx, fmaxf(fmaxf(v[u].x, v[u].y), fmaxf(v[u].z, v[u].w)));
+      mx *= kLog2e;
+      if (mx > m) { s *= ex2_fast(m - mx); m = mx; }
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+        s += ex2_fast(fmaf(v[u].x, kLog2e, -m)) + ex2_fast(fmaf(v[u].y, kLog2e, -m)) + ex2_fast(fmaf(v[u].z, kLog2e, -m)) +
+             ex2_fast(fmaf(v[u].w, kLog2e, -m));
     }
     const float big = block_max(m, sm, -INFINITY);
-    const float total = block_sum(s * exp2f((m - big) * kLog2e), sm);
-    if (threadIdx.x == 0 && row_loss) row_loss[row] = -z[target] + big + logf(total);
+    const float total = block_sum(s * ex2_fast(m - big), sm);
+    if (threadIdx.x == 0 && row_loss) row_loss[row] = -z_target + big * 0.6931471805599453f + logf(total);
     if (dlogits != nullptr) {
       const float inv = scale / total;
       __nv_bfloat16* d = dlogits + (size_t)row * ld_d;
-      for (int c = threadIdx.x * 4; c < classes; c += blockDim.x * 4) {
-        const float4 v = *reinterpret_cast<const float4*>(z + c);
-        float o[4] = {exp2f((v.x - big) * kLog2e) * inv, exp2f((v.y - big) * kLog2e) * inv,
-                      exp2f((v.z - big) * kLog2e) * inv, exp2f((v.w - big) * kLog2e) * inv};
+      for (int c0 = threadIdx.x * 4; c0 < classes; c0 += 4 * STEP) {
+        float4 v[4];
 #pragma unroll
-        for (int e = 0; e < 4; ++e)
-          if (c + e == target) o[e] -= scale;
-        Vec<__nv_bfloat16>::store(d + c, o);
+        for (int u = 0; u < 4; ++u) {
+          const int c = c0 + u * STEP;
+          v[u] = c < classes ? *reinterpret_cast<const float4*>(z + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int c = c0 + u * STEP;
+          if (c < classes) {
+            float o[4] = {ex2_fast(fmaf(v[u].x, kLog2e, -big)) * inv, ex2_fast(fmaf(v[u].y, kLog2e, -big)) * inv,
+                          ex2_fast(fmaf(v[u].z, kLog2e, -big)) * inv, ex2_fast(fmaf(v[u].w, kLog2e, -big)) * inv};
+#pragma unroll
+            for (int e = 0; e < 4; ++e)
+              if (c + e == target) o[e] -= scale;
+            Vec<__nv_bfloat16>::store(d + c, o);
+          }
+        }
       }
     }
     __syncthreads();  // sm is reused by the next row
@@ -506,7 +532,7 @@ int cross_entropy_impl(hl_ctx* ctx, const float* logits, long long ld, const int
                          (reinterpret_cast<uintptr_t>(logits) & 15) == 0 && (reinterpret_cast<uintptr_t>(dlogits) & 7) == 0 &&
                          classes >= 1024;
   if (online_ok && (dlogits || dlogits_dtype == HL_BF16))
-    cross_entropy_online_kernel<<<std::min(rows, ctx->sm_count * 2), 1024, 0, ctx->stream>>>(
+    cross_entropy_online_kernel<<<std::min(rows, ctx->sm_count * 2), CE_THREADS, 0, ctx->stream>>>(
         logits, ld, targets, rows, classes, scale, rl, (__nv_bfloat16*)dlogits, ld_dlogits, ctx->status_dev);
   else if (dlogits && dlogits_dtype == HL_BF16)
     cross_entropy_kernel<float, __nv_bfloat16><<<rows, threads, 0, ctx->stream>>>(

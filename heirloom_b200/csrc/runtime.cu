@@ -82,7 +82,8 @@ int make_tensor_map(CUtensorMap* out, int dtype, int rank, const void* base, con
                     const uint64_t* strides_bytes, const uint32_t* box, int swizzle_bytes) {
   EncodeTiledFn fn = encode_tiled_fn();
   if (!fn) return fail("cuTensorMapEncodeTiled is not available from this driver");
-  if (swizzle_bytes != 128 && swizzle_bytes != 64) return fail("make_tensor_map: swizzle must be 64 or 128 bytes");
+  if (swizzle_bytes != 128 && swizzle_bytes != 64 && swizzle_bytes != 32)
+    return fail("make_tensor_map: swizzle must be 32, 64 or 128 bytes");
   if (rank < 1 || rank > 5) return fail("make_tensor_map: rank must be in [1, 5]");
   cuuint64_t d[5], s[4];
   cuuint32_t b[5], e[5];
@@ -90,7 +91,7 @@ int make_tensor_map(CUtensorMap* out, int dtype, int rank, const void* base, con
   for (int i = 0; i + 1 < rank; ++i) s[i] = strides_bytes[i];
   const CUtensorMapDataType t = dtype == HL_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
   CUresult r = fn(out, t, (cuuint32_t)rank, const_cast<void*>(base), d, s, b, e, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                  swizzle_bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                  swizzle_bytes == 32 ? CU_TENSOR_MAP_SWIZZLE_32B : (swizzle_bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B), CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) {
     char buf[256];
     snprintf(buf, sizeof buf, "cuTensorMapEncodeTiled failed (%d): rank=%d dims0=%llu dims1=%llu box=%ux%u base=%p", (int)r,
