@@ -58,5 +58,35 @@ def build(verbose: bool = False) -> Path:
     return LIB
 
 
+HOST = PKG / "host"
+HOST_LIB = OUT / "libheirloom_host.so"
+HOST_TESTS = OUT / "host_tests"
+CXX = os.environ.get("CXX", "g++")
+
+
+def build_host() -> Path:
+    """The C++ tensor interface above the C ABI (`host/heirloom_host.cpp`) as a shared library, and its
+    test driver, both linked against the CUDA library next to them."""
+    build()
+    newest = max(p.stat().st_mtime for p in list(HOST.glob("*.cpp")) + list(HOST.glob("*.hpp")) +
+                 list((PKG.parent / "include").glob("*.h")))
+    common = ["-O2", "-std=c++17", "-Wall", "-Wextra", "-fPIC", f"-L{OUT}", "-Wl,-rpath,$ORIGIN"]
+    if not HOST_LIB.exists() or HOST_LIB.stat().st_mtime < newest:
+        cmd = [CXX, *common, "-shared", "-o", str(HOST_LIB), str(HOST / "heirloom_host.cpp"), "-lheirloom_b200"]
+        res = subprocess.run(cmd, capture_output=True, text=True)
+        if res.returncode != 0:
+            raise RuntimeError(f"host library failed to build:\n{res.stdout}\n{res.stderr}")
+    if not HOST_TESTS.exists() or HOST_TESTS.stat().st_mtime < newest:
+        cmd = [CXX, *common, "-o", str(HOST_TESTS), str(HOST / "host_tests.cpp"), "-lheirloom_host", "-lheirloom_b200"]
+        res = subprocess.run(cmd, capture_output=True, text=True)
+        if res.returncode != 0:
+            raise RuntimeError(f"host test driver failed to build:\n{res.stdout}\n{res.stderr}")
+    return HOST_LIB
+
+
+if __name__ == "__main__" and "--host" in sys.argv:
+    print(build_host())
+    sys.exit(0)
+
 if __name__ == "__main__":
     print(build(verbose="-v" in sys.argv))
