@@ -31,6 +31,9 @@ GPT = dict(vocab=50304, d_model=768, n_layers=12, n_heads=12, d_ff=3072, context
 MICRO_BATCH = 16
 METRIC = "train tokens/s (GPT-124M-shaped bf16 step)"
 DATASHEET_BF16_TFLOPS = 2250.0
+# dram__bytes_read.sum + dram__bytes_write.sum per GEMM launch, averaged over the launches of two training steps
+# in a one-pass ncu launch list of this command (summary kept under profiles/)
+GEMM_DRAM_BYTES_PER_LAUNCH = 155.4e6
 
 
 def flops_per_token(cfg) -> float:
@@ -354,7 +357,7 @@ def run_ours(args):
         "gpu_launches": launches * args.steps,
         "roofline": {"bound": "tensor", "kernel": "gemm_bf16_tcgen05_kernel", "achieved": gemm_tflops,
                      "peak": peaks["bf16_sustained"], "unit": "TFLOP/s", "frac": gemm_tflops / peaks["bf16_sustained"],
-                     "traffic": None, "peak_source": peaks["source"] + " sustained bf16 (kernel timed inside a long step)",
+                     "traffic": GEMM_DRAM_BYTES_PER_LAUNCH, "peak_source": peaks["source"] + " sustained bf16 (kernel timed inside a long step)",
                      "launches_per_step": gemm["scopes_per_step"], "ms_per_step": gemm["ms_per_step"]},
         "kernel_breakdown_ms_per_step": {k: round(v["ms_per_step"], 4) for k, v in prof.items()},
         "cpu_baseline": cpu,
