@@ -51,6 +51,9 @@ struct AdamPlan;
 int adam_plan_create(hl_ctx* ctx, const hl_adamw_tensor* tensors, int count, AdamPlan** out);
 void adam_plan_destroy(AdamPlan* plan);
 int adam_plan_step(hl_ctx* ctx, AdamPlan* plan, const hl_adamw_params* hp);
+int adam_plan_step_range(hl_ctx* ctx, AdamPlan* plan, const hl_adamw_params* hp, int first, int count);
+int adam_plan_chunk_elements();
+int adam_plan_chunk_count(const AdamPlan* plan);
 
 extern "C" int hl_memory_copy_indices(hl_ctx* ctx, int64_t* host, const int64_t* dev, long long count);
 

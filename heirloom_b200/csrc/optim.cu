@@ -130,16 +130,26 @@ void adam_plan_destroy(AdamPlan* plan) {
   delete plan;
 }
 
-int adam_plan_step(hl_ctx* ctx, AdamPlan* plan, const hl_adamw_params* hp) {
+int adam_plan_chunk_elements() { return (int)ADAM_CHUNK; }
+int adam_plan_chunk_count(const AdamPlan* plan) { return plan->count; }
+
+// Chunks [first, first + count) of the table: lets a caller update the part of a gradient arena whose
+// all-reduce has finished while the rest is still in flight.
+int adam_plan_step_range(hl_ctx* ctx, AdamPlan* plan, const hl_adamw_params* hp, int first, int count) {
   int rc = validate(hp, "hl_adamw_multi");
   if (rc != HL_OK) return rc;
-  if (plan->count == 0) return HL_OK;
+  HL_REQUIRE(first >= 0 && count >= 0 && first + count <= plan->count, "adamw plan: chunk range out of bounds");
+  if (count == 0) return HL_OK;
   // 28 bytes per parameter (read p, g, m, v; write p, m, v) plus 2 for the bf16 shadow
-  ProfileScope prof(ctx, HL_PROF_OPTIMIZER, 30.0 * (double)plan->elements);
-  adamw_chunks_kernel<<<plan->count, ADAM_THREADS, 0, ctx->stream>>>(plan->chunks_dev, *hp);
+  ProfileScope prof(ctx, HL_PROF_OPTIMIZER, 30.0 * (double)plan->elements * ((double)count / (double)plan->count));
+  adamw_chunks_kernel<<<count, ADAM_THREADS, 0, ctx->stream>>>(plan->chunks_dev + first, *hp);
   HL_LAUNCH_CHECK("adamw_chunks_kernel");
   count_launch(ctx);
   return HL_OK;
+}
+
+int adam_plan_step(hl_ctx* ctx, AdamPlan* plan, const hl_adamw_params* hp) {
+  return adam_plan_step_range(ctx, plan, hp, 0, plan->count);
 }
 
 }  // namespace hl

@@ -91,6 +91,8 @@ struct hl_decoder {
   size_t bucket_elems = 6553600;  // 25 MiB of f32
   size_t next_bucket = 0, n_buckets = 0;
   std::vector<cudaEvent_t> bucket_ready;
+  std::vector<cudaEvent_t> bucket_done;  // recorded on the collective stream after each bucket's all-reduce
+  bool comm_pending = false;             // the compute stream has not yet waited for this step's collectives
   cudaEvent_t comm_done = nullptr;
   unsigned long long launches_last_step = 0;
   // product-key memory (shared tables, MemoryTransformerLm with memory layers)
@@ -472,6 +474,7 @@ int flush_buckets(hl_decoder* m, size_t done_elems) {
     HL_CUDA(cudaEventRecord(m->bucket_ready[m->next_bucket], m->ctx->stream));
     HL_CUDA(cudaStreamWaitEvent(m->ctx->comm_stream, m->bucket_ready[m->next_bucket], 0));
     HL_TRY(nccl_allreduce_sum_f32(m->ctx, m->grads + start, end - start, m->ctx->comm_stream));
+    HL_CUDA(cudaEventRecord(m->bucket_done[m->next_bucket], m->ctx->comm_stream));
     m->next_bucket += 1;
   }
   return HL_OK;
@@ -486,6 +489,10 @@ int backward(hl_decoder* m) {
   const __nv_bfloat16* W = m->shadow;
   float* G = m->grads;
   m->next_bucket = 0;
+  if (m->comm_pending) {  // a previous step's collectives were never consumed: finish them before its gradients are overwritten
+    HL_CUDA(cudaStreamWaitEvent(m->ctx->stream, m->comm_done, 0));
+    m->comm_pending = false;
+  }
   HL_TRY(zero_memory_table_grads(m));
   // loss and dlogits = (softmax - onehot)/N in bf16, the operand precision of the next GEMMs
   HL_TRY(cross_entropy_impl(ctx, m->logits, V, m->targets, N, V, 1.0f, m->loss_dev, nullptr, m->dlogits, HL_BF16, V));
@@ -558,8 +565,10 @@ int backward(hl_decoder* m) {
   HL_TRY(hl_embedding_backward(ctx, dx, m->tokens, G + m->off_tok, V, G + m->off_pos, T, N, d));
   HL_TRY(flush_buckets(m, m->arena));
   if (nccl_active(ctx)) {
+    // The compute stream waits for the collectives only when something reads the averaged gradients:
+    // the optimizer takes them bucket group by bucket group, every other reader waits for all of them.
     HL_CUDA(cudaEventRecord(m->comm_done, ctx->comm_stream));
-    HL_CUDA(cudaStreamWaitEvent(ctx->stream, m->comm_done, 0));
+    m->comm_pending = true;
   }
   return HL_OK;
 }
@@ -632,6 +641,10 @@ int backward_f32(hl_decoder* m) {
   const float* P = m->params;
   float* G = m->grads;
   m->next_bucket = 0;
+  if (m->comm_pending) {  // a previous step's collectives were never consumed: finish them before its gradients are overwritten
+    HL_CUDA(cudaStreamWaitEvent(m->ctx->stream, m->comm_done, 0));
+    m->comm_pending = false;
+  }
   HL_TRY(cross_entropy_impl(ctx, m->logits, V, m->targets, N, V, 1.0f, m->loss_dev, nullptr, m->dlogits_f, HL_F32, V));
   HL_TRY(zero_memory_table_grads(m));
   float* dx = m->d_a;       // gradient of the residual stream
@@ -683,8 +696,19 @@ int backward_f32(hl_decoder* m) {
   HL_TRY(hl_embedding_backward(ctx, dx, m->tokens, G + m->off_tok, V, G + m->off_pos, T, N, d));
   HL_TRY(flush_buckets(m, m->arena));
   if (nccl_active(ctx)) {
+    // The compute stream waits for the collectives only when something reads the averaged gradients:
+    // the optimizer takes them bucket group by bucket group, every other reader waits for all of them.
     HL_CUDA(cudaEventRecord(m->comm_done, ctx->comm_stream));
-    HL_CUDA(cudaStreamWaitEvent(ctx->stream, m->comm_done, 0));
+    m->comm_pending = true;
+  }
+  return HL_OK;
+}
+
+// Make the compute stream wait for every gradient collective of the step.
+int wait_for_collectives(hl_decoder* m) {
+  if (m->comm_pending) {
+    HL_CUDA(cudaStreamWaitEvent(m->ctx->stream, m->comm_done, 0));
+    m->comm_pending = false;
   }
   return HL_OK;
 }
@@ -692,6 +716,7 @@ int backward_f32(hl_decoder* m) {
 int optimizer_step(hl_decoder* m) {
   HL_REQUIRE(m->has_opt, "hl_decoder: no optimizer configured (call hl_decoder_set_optimizer)");
   hl_ctx* ctx = m->ctx;
+  if (m->opt.clip_norm > 0.f) HL_TRY(wait_for_collectives(m));  // the global norm needs every averaged gradient
   const int world = nccl_world(ctx);
   const float inv_world = 1.0f / (float)world;  // sum then scale by 1/world (src/nn.rs:2100-2117)
   double clip = 1.0;
@@ -712,7 +737,26 @@ int optimizer_step(hl_decoder* m) {
   hp.clip_scale = (float)clip * inv_world;
   hp.bias_correction1 = (float)(1.0 - pow((double)m->opt.beta1, (double)m->step));
   hp.bias_correction2 = (float)(1.0 - pow((double)m->opt.beta2, (double)m->step));
-  return adam_plan_step(ctx, m->plan, &hp);
+  if (!m->comm_pending) return adam_plan_step(ctx, m->plan, &hp);
+  // Collectives still in flight: update the arena in groups of buckets, each group as soon as its last
+  // all-reduce has finished, so the update of the early buckets overlaps the reduction of the late ones.
+  const size_t chunk = (size_t)adam_plan_chunk_elements();
+  const int chunks_total = adam_plan_chunk_count(m->plan);
+  constexpr size_t kGroup = 5;  // buckets per launch
+  int first = 0;
+  for (size_t b0 = 0; b0 < m->n_buckets; b0 += kGroup) {
+    const size_t b1 = std::min(b0 + kGroup, m->n_buckets);
+    size_t start, end;
+    bucket_range(m->arena, m->bucket_elems, b1 - 1, &start, &end);
+    // chunks that lie completely inside the buckets reduced so far (a chunk that straddles the boundary waits
+    // for the next group; the last group takes everything that is left)
+    const int upto = b1 == m->n_buckets ? chunks_total : (int)(end / chunk);
+    HL_CUDA(cudaStreamWaitEvent(ctx->stream, m->bucket_done[b1 - 1], 0));
+    HL_TRY(adam_plan_step_range(ctx, m->plan, &hp, first, upto - first));
+    first = upto;
+  }
+  m->comm_pending = false;
+  return HL_OK;
 }
 
 int refresh_shadow(hl_decoder* m, size_t offset, size_t numel) {
@@ -818,6 +862,11 @@ static int decoder_create_impl(hl_ctx* ctx, const hl_decoder_config* cfg, const 
   if (rc != HL_OK) return cleanup(rc);
   m->n_buckets = (m->arena + m->bucket_elems - 1) / m->bucket_elems;
   m->bucket_ready.resize(m->n_buckets);
+  m->bucket_done.resize(m->n_buckets);
+  for (auto& ev : m->bucket_done) {
+    cudaError_t ee = cudaEventCreateWithFlags(&ev, cudaEventDisableTiming);
+    if (ee != cudaSuccess) { ev = nullptr; return fail_cuda(ee, "cudaEventCreate(bucket_done)"); }
+  }
   for (auto& ev : m->bucket_ready) {
     e = cudaEventCreateWithFlags(&ev, cudaEventDisableTiming);
     if (e != cudaSuccess) return cleanup(fail_cuda(e, "cudaEventCreate"));
@@ -839,6 +888,7 @@ void hl_decoder_destroy(hl_decoder* m) {
     cudaStreamSynchronize(m->ctx->comm_stream);
   }
   for (auto ev : m->bucket_ready) if (ev) cudaEventDestroy(ev);
+  for (auto ev : m->bucket_done) if (ev) cudaEventDestroy(ev);
   if (m->comm_done) cudaEventDestroy(m->comm_done);
   adam_plan_destroy(m->plan);
   cudaFree(m->params); cudaFree(m->grads); cudaFree(m->m); cudaFree(m->v); cudaFree(m->shadow); cudaFree(m->act_arena);
@@ -889,6 +939,7 @@ int hl_decoder_get_param(hl_decoder* m, int index, float* host, long long numel)
 int hl_decoder_get_grad(hl_decoder* m, int index, float* host, long long numel) {
   const Slot* s;
   HL_TRY(slot_io(m, index, numel, &s, "hl_decoder_get_grad"));
+  HL_TRY(hl::wait_for_collectives(m));
   return hl_memcpy_d2h(m->ctx, host, m->grads + s->offset, sizeof(float) * s->numel);
 }
 
