@@ -965,6 +965,23 @@ int hl_decoder_set_optimizer(hl_decoder* m, const hl_adamw_config* opt) {
 
 long long hl_decoder_optimizer_steps(hl_decoder* m) { return m ? m->step : 0; }
 
+int hl_decoder_set_moments(hl_decoder* m, int index, const float* m_host, const float* v_host, long long numel) {
+  const Slot* s;
+  HL_TRY(slot_io(m, index, numel, &s, "hl_decoder_set_moments"));
+  HL_REQUIRE(m_host && v_host, "hl_decoder_set_moments: null argument");
+  HL_REQUIRE(m->has_opt, "hl_decoder_set_moments: no optimizer configured (call hl_decoder_set_optimizer)");
+  HL_TRY(hl_memcpy_h2d(m->ctx, m->m + s->offset, m_host, sizeof(float) * s->numel));
+  return hl_memcpy_h2d(m->ctx, m->v + s->offset, v_host, sizeof(float) * s->numel);
+}
+
+int hl_decoder_set_optimizer_steps(hl_decoder* m, long long steps) {
+  HL_REQUIRE(m, "hl_decoder_set_optimizer_steps: null model");
+  HL_REQUIRE(m->has_opt, "hl_decoder_set_optimizer_steps: no optimizer configured (call hl_decoder_set_optimizer)");
+  HL_REQUIRE(steps >= 0, "hl_decoder_set_optimizer_steps: the step counter cannot be negative");
+  m->step = steps;
+  return HL_OK;
+}
+
 int hl_decoder_forward_backward(hl_decoder* m, const int64_t* tokens_dev, const int64_t* targets_dev) {
   HL_REQUIRE(m && tokens_dev && targets_dev, "hl_decoder_forward_backward: null argument");
   const unsigned long long before = m->ctx->counters.launches;

@@ -142,6 +142,19 @@ class DecoderLm:
                                                v.ctypes.data_as(c_void_p), c_longlong(m.size)))
         return m, v
 
+    def set_moments(self, name: str, m: np.ndarray, v: np.ndarray) -> None:
+        """`AdamW::load_state` for one parameter (src/nn.rs:2059-2080); needs `set_optimizer` first."""
+        idx, shape = self._slot(name)
+        m = np.ascontiguousarray(m, np.float32)
+        v = np.ascontiguousarray(v, np.float32)
+        if tuple(m.shape) != shape or tuple(v.shape) != shape:
+            raise HeirloomError(f"AdamW state shape mismatch for {name}: expected {shape}")
+        check(self._lib.hl_decoder_set_moments(self.handle, c_int(idx), m.ctypes.data_as(c_void_p),
+                                               v.ctypes.data_as(c_void_p), c_longlong(m.size)))
+
+    def set_optimizer_steps(self, steps: int) -> None:
+        check(self._lib.hl_decoder_set_optimizer_steps(self.handle, c_longlong(int(steps))))
+
     def state_dict(self) -> Dict[str, np.ndarray]:
         return {n: self.parameter(n) for n in self._index}
 

@@ -401,6 +401,10 @@ int hl_decoder_get_moments(hl_decoder* model, int index, float* m_host, float* v
 /* AdamW::new + with_* (src/nn.rs:1941-2005): resets the step counter and the moments. */
 int hl_decoder_set_optimizer(hl_decoder* model, const hl_adamw_config* opt);
 long long hl_decoder_optimizer_steps(hl_decoder* model);
+/* AdamW::load_state (src/nn.rs:2059-2080): moments of one parameter and the step counter, as a
+ * checkpoint holds them (optimizer.json written by src/checkpoint.rs:124-146). */
+int hl_decoder_set_moments(hl_decoder* model, int index, const float* m_host, const float* v_host, long long numel);
+int hl_decoder_set_optimizer_steps(hl_decoder* model, long long steps);
 /* zero_grad + loss + backward (src/bin/heirloom/commands/training.rs:125-167) on device-resident
  * i64 tokens/targets of shape [batch, context].  With an NCCL communicator on the context,
  * 25 MiB gradient buckets are all-reduced on the collective stream as backward produces them. */
