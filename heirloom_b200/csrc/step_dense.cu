@@ -1065,6 +1065,56 @@ int hl_decoder_train_step(hl_decoder* m, const int64_t* tokens_host, const int64
   return HL_OK;
 }
 
+namespace {
+// Runs the forward pass over `sequences` rows of `time` tokens (both at most what the model was
+// created for), restoring the configured sizes afterwards.
+struct ScopedShape {
+  hl_decoder* m;
+  int batch, context, n;
+  ScopedShape(hl_decoder* model, int sequences, int time) : m(model), batch(model->cfg.batch), context(model->cfg.context), n(model->N) {
+    m->cfg.batch = sequences;
+    m->cfg.context = time;
+    m->N = sequences * time;
+  }
+  ~ScopedShape() {
+    m->cfg.batch = batch;
+    m->cfg.context = context;
+    m->N = n;
+  }
+};
+}  // namespace
+
+int hl_decoder_eval_loss(hl_decoder* m, const int64_t* tokens_dev, const int64_t* targets_dev, int sequences,
+                         float* loss_host) {
+  HL_REQUIRE(m && tokens_dev && targets_dev && loss_host, "hl_decoder_eval_loss: null argument");
+  HL_REQUIRE(sequences > 0 && sequences <= m->cfg.batch,
+             "hl_decoder_eval_loss: sequences must be between 1 and the batch the model was created for");
+  const size_t n = (size_t)sequences * m->cfg.context;
+  HL_CUDA(cudaMemcpyAsync(m->tokens, tokens_dev, sizeof(int64_t) * n, cudaMemcpyDeviceToDevice, m->ctx->stream));
+  HL_CUDA(cudaMemcpyAsync(m->targets, targets_dev, sizeof(int64_t) * n, cudaMemcpyDeviceToDevice, m->ctx->stream));
+  {
+    ScopedShape shape(m, sequences, m->cfg.context);
+    if (m->cfg.precision == HL_PRECISION_AMP_BF16) HL_TRY(forward(m));
+    else HL_TRY(forward_f32(m));
+    HL_TRY(cross_entropy_impl(m->ctx, m->logits, m->cfg.vocab, m->targets, m->N, m->cfg.vocab, 1.0f, m->loss_dev, nullptr,
+                              nullptr, HL_BF16, m->cfg.vocab));
+  }
+  return hl_memcpy_d2h(m->ctx, loss_host, m->loss_dev, sizeof(float));
+}
+
+int hl_decoder_next_token_logits(hl_decoder* m, const int64_t* window_dev, int window_len, float* logits_host) {
+  HL_REQUIRE(m && window_dev && logits_host, "hl_decoder_next_token_logits: null argument");
+  HL_REQUIRE(window_len >= 1, "next_token_logits requires at least one token");
+  HL_REQUIRE(window_len <= m->cfg.context, "hl_decoder_next_token_logits: the window is longer than the model's context");
+  HL_CUDA(cudaMemcpyAsync(m->tokens, window_dev, sizeof(int64_t) * window_len, cudaMemcpyDeviceToDevice, m->ctx->stream));
+  {
+    ScopedShape shape(m, 1, window_len);
+    if (m->cfg.precision == HL_PRECISION_AMP_BF16) HL_TRY(forward(m));
+    else HL_TRY(forward_f32(m));
+  }
+  return hl_memcpy_d2h(m->ctx, logits_host, m->logits + (size_t)(window_len - 1) * m->cfg.vocab, sizeof(float) * m->cfg.vocab);
+}
+
 int hl_decoder_loss(hl_decoder* m, float* loss_host) {
   HL_REQUIRE(m && loss_host, "hl_decoder_loss: null argument");
   return hl_memcpy_d2h(m->ctx, loss_host, m->loss_dev, sizeof(float));

@@ -182,6 +182,22 @@ class DecoderLm:
         forward, no dense update in this call."""
         check(self._lib.hl_decoder_optimizer_step_sparse_rows(self.handle))
 
+    def eval_loss_device(self, tokens: torch.Tensor, targets: torch.Tensor) -> float:
+        """Forward-only mean cross-entropy over int64 CUDA tensors `[sequences, context]`, sequences <= batch."""
+        if tokens.dim() != 2 or tokens.shape[1] != self.cfg.context or tokens.shape != targets.shape:
+            raise HeirloomError(f"expected token input [sequences, {self.cfg.context}], got {tuple(tokens.shape)}")
+        out = c_float()
+        check(self._lib.hl_decoder_eval_loss(self.handle, c_void_p(tokens.contiguous().data_ptr()),
+                                             c_void_p(targets.contiguous().data_ptr()), c_int(tokens.shape[0]), byref(out)))
+        return float(out.value)
+
+    def next_token_logits_device(self, window: torch.Tensor) -> np.ndarray:
+        """Logits after a window of 1..context tokens (int64 CUDA vector), as f32 `[vocab]`."""
+        out = np.empty(self.cfg.vocab, np.float32)
+        check(self._lib.hl_decoder_next_token_logits(self.handle, c_void_p(window.contiguous().data_ptr()),
+                                                     c_int(window.numel()), out.ctypes.data_as(c_void_p)))
+        return out
+
     def train_step_device(self, tokens: torch.Tensor, targets: torch.Tensor) -> None:
         check(self._lib.hl_decoder_train_step_device(self.handle, c_void_p(tokens.data_ptr()),
                                                      c_void_p(targets.data_ptr())))

@@ -405,6 +405,13 @@ long long hl_decoder_optimizer_steps(hl_decoder* model);
  * checkpoint holds them (optimizer.json written by src/checkpoint.rs:124-146). */
 int hl_decoder_set_moments(hl_decoder* model, int index, const float* m_host, const float* v_host, long long numel);
 int hl_decoder_set_optimizer_steps(hl_decoder* model, long long steps);
+/* Forward only, no gradients (the loss inside evaluate_token_loss, src/memory_transformer.rs:1813-1912):
+ * mean cross-entropy over `sequences` (1..batch) rows of `context` tokens; the value is copied to the host. */
+int hl_decoder_eval_loss(hl_decoder* model, const int64_t* tokens_dev, const int64_t* targets_dev, int sequences,
+                         float* loss_host);
+/* next_token_logits (src/memory_transformer.rs:1930-1984): one window of 1..context tokens, full-window
+ * forward, the `vocab` logits of its last position copied to the host. */
+int hl_decoder_next_token_logits(hl_decoder* model, const int64_t* window_dev, int window_len, float* logits_host);
 /* zero_grad + loss + backward (src/bin/heirloom/commands/training.rs:125-167) on device-resident
  * i64 tokens/targets of shape [batch, context].  With an NCCL communicator on the context,
  * 25 MiB gradient buckets are all-reduced on the collective stream as backward produces them. */

@@ -705,6 +705,32 @@ def decoder_loss_and_grads(cfg: DecoderConfig, params: Dict[str, np.ndarray], to
     return loss, grads
 
 
+def decoder_logits(cfg: DecoderConfig, params: Dict[str, np.ndarray], tokens: np.ndarray, amp_bf16: bool = False) -> np.ndarray:
+    """Forward pass only: logits `[B, T, vocab]` for token windows of any length T <= context
+    (`MemoryTransformerLm::forward`, `src/memory_transformer.rs:2069-2081`; the window form is what
+    `next_token_logits` feeds it, `:1930-1984`)."""
+    amp = amp_bf16
+    rt = bf16_round if amp else (lambda a: a)
+    B, T = tokens.shape
+    N, d, H = B * T, cfg.d_model, cfg.n_heads
+    p = params
+    pos_ids = np.tile(np.arange(T, dtype=np.int64), (B, 1))
+    x = rt(add(rt(embedding(p["token_embedding.weight"], tokens)), rt(embedding(p["position_embedding.weight"], pos_ids)))).reshape(N, d)
+    for i in range(cfg.n_layers):
+        b = f"block.{i}."
+        a = rt(layer_norm(x, p[b + "ln1.weight"], p[b + "ln1.bias"]))
+        q, k, v = (rt(_linear(a, p[b + f"attention.{n}.weight"], p[b + f"attention.{n}.bias"], amp)).reshape(B, T, d)
+                   for n in ("q_proj", "k_proj", "v_proj"))
+        o = rt(causal_attention(q, k, v, H, round_probs_bf16=amp)).reshape(N, d)
+        r = rt(add(x, rt(_linear(o, p[b + "attention.out_proj.weight"], p[b + "attention.out_proj.bias"], amp))))
+        c = rt(layer_norm(r, p[b + "ln2.weight"], p[b + "ln2.bias"]))
+        h = rt(_linear(c, p[b + "feed_forward.dense.fc1.weight"], p[b + "feed_forward.dense.fc1.bias"], amp))
+        f = rt(_linear(rt(gelu(h)), p[b + "feed_forward.dense.fc2.weight"], p[b + "feed_forward.dense.fc2.bias"], amp))
+        x = rt(add(r, f))
+    z = rt(layer_norm(x, p["ln_f.weight"], p["ln_f.bias"]))
+    return _linear(z, p["lm_head.weight"], p["lm_head.bias"], amp).reshape(B, T, cfg.vocab)
+
+
 def train_steps(cfg: DecoderConfig, params: Dict[str, np.ndarray], batches, state: AdamWState,
                 amp_bf16: bool = False, grad_f32: bool = False) -> List[float]:
     """Run `zero_grad → loss → backward → AdamW.step` per batch
