@@ -162,6 +162,16 @@ extern "C" {
 
 const char* hl_last_error(void) { return hl::g_last_error.c_str(); }
 
+unsigned long long hl_fnv1a64(const void* data, size_t bytes, unsigned long long seed) {
+  const unsigned char* p = static_cast<const unsigned char*>(data);
+  unsigned long long h = seed;
+  for (size_t i = 0; i < bytes; ++i) {
+    h ^= (unsigned long long)p[i];
+    h *= 0x100000001b3ull;
+  }
+  return h;
+}
+
 int hl_ctx_create(int device_ordinal, hl_ctx** out) {
   if (!out) return hl::fail("hl_ctx_create: null output pointer");
   *out = nullptr;

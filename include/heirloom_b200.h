@@ -44,6 +44,10 @@ int hl_ctx_sync(hl_ctx* ctx);
 /* The compute stream as a cudaStream_t, for callers that time with their own events. */
 void* hl_ctx_stream(hl_ctx* ctx);
 const char* hl_last_error(void);
+/* FNV-1a, 64 bit, continued from `seed` (0xcbf29ce484222325 to start): the hash the reference
+ * records for token shards and their payload files (src/tokenizer.rs:968-975, src/data.rs:1979-2005).
+ * Host function, no device work. */
+unsigned long long hl_fnv1a64(const void* data, size_t bytes, unsigned long long seed);
 
 /* Device facts (reference: device_supports_bf16_tensor_cores, cuda.rs:8290-8296). */
 typedef struct {
