@@ -1,5 +1,7 @@
-// Causal flash attention backward on tcgen05.  One CTA owns 128 keys of one (batch, head) and
-// walks the query tiles at or below the diagonal.  Per query tile five tensor-core products
+// Causal flash attention backward on tcgen05.  A work item is 128 keys of one (batch, head) and
+// walks the query tiles at or below the diagonal; one persistent CTA per SM takes items round-robin
+// (longest walks first) and starts the next item's loads and first products while the current one
+// drains.  Per query tile five tensor-core products
 // run against tensor memory:
 //     S  = Q·Kᵀ          dP = dO·Vᵀ                      (recomputed scores, f32)
 //     dV += Pᵀ·dO        dK += dSᵀ·Q        dQ_tile = dS·K
@@ -11,6 +13,8 @@
 // Replaces the reference's recompute-based backward with scalar f32 atomics
 // (tensor_core.ptx:3111-4407, heirloom-kernels/src/cuda.rs:9256-9294) and, for the values it
 // computes, follows src/tensor/autograd.rs:1626-1914 (bf16 operands, f32 accumulation).
+#include <type_traits>
+
 #include "common.cuh"
 #include "tc05.cuh"
 
@@ -18,19 +22,21 @@ namespace hl {
 namespace {
 
 constexpr int FB_BM = 128;  // queries per tile
-constexpr int FB_BN = 128;  // keys per CTA
+constexpr int FB_BN = 128;  // keys per work item
 constexpr int FB_HD = 64;
 constexpr int FB_Q_STAGES = 2;
+constexpr int FB_KV_BUFFERS = 2;
 constexpr int FB_TILE_BYTES = 128 * FB_HD * 2;  // 16 KB
 constexpr int FB_PS_BYTES = FB_BM * FB_BN * 2;  // 32 KB
 constexpr int FB_SOFTMAX_WARPS = 8;
 constexpr int FB_THREADS = (FB_SOFTMAX_WARPS + 2) * 32;  // + TMA warp + MMA warp
 constexpr int FB_TMEM_COLS = 512;
-constexpr int FB_SMEM_DATA = FB_TILE_BYTES * (2 + 2 * FB_Q_STAGES) + 2 * FB_PS_BYTES;  // 160 KB
+constexpr int FB_SMEM_DATA = FB_TILE_BYTES * (2 * FB_KV_BUFFERS + 2 * FB_Q_STAGES) + 2 * FB_PS_BYTES;  // 192 KB
 constexpr int FB_SMEM_BYTES = FB_SMEM_DATA + 1024;
+static_assert(FB_SMEM_BYTES <= 227 * 1024, "shared memory budget");
 
 struct FbBarriers {
-  uint64_t kv_full;
+  uint64_t kv_full[FB_KV_BUFFERS], kv_empty[FB_KV_BUFFERS];
   uint64_t q_full[FB_Q_STAGES], q_empty[FB_Q_STAGES];
   uint64_t sdp_full, sdp_free, p_full, dq_full;
   uint32_t tmem_base;
@@ -54,6 +60,42 @@ __device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float 
   asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
 }
 
+// A CTA's place in its sequence of query tiles: work item `item` (one key tile of one batch and
+// head; items with the longest walks come first), query tile `it` of its walk.  Every warp role
+// advances an identical copy.
+struct FbCursor {
+  int item;      // global work item, -1 when the sequence is over
+  int local;     // how many items this CTA has started before this one
+  int it;        // query tile within the item's walk
+  int n_tiles;   // length of the walk
+  int kj, b, h;  // key tile, batch, head
+  __device__ __forceinline__ bool valid() const { return item >= 0; }
+};
+// The CTA's `local`-th item.  Items are sorted by decreasing walk length; rounds alternate direction
+// (CTA 0 takes the longest item of even rounds and the shortest of odd ones), which evens out the
+// per-CTA totals of a static assignment.
+__device__ __forceinline__ void fb_load_item(FbCursor& c, int local, const FbParams& p) {
+  const int nq = (p.T + FB_BM - 1) / FB_BM;
+  const int total = nq * p.B * p.H;
+  const int grid = (int)gridDim.x, cta = (int)blockIdx.x;
+  const int item = local * grid + ((local & 1) ? grid - 1 - cta : cta);
+  if (item >= total) { c.item = -1; return; }
+  const int bh = item % (p.B * p.H);
+  c.item = item;
+  c.local = local;
+  c.it = 0;
+  c.kj = item / (p.B * p.H);
+  c.b = bh / p.H;
+  c.h = bh % p.H;
+  c.n_tiles = nq - c.kj;  // query tiles kj .. nq-1
+}
+__device__ __forceinline__ FbCursor fb_next(const FbCursor& c, const FbParams& p) {
+  FbCursor n = c;
+  if (c.it + 1 < c.n_tiles) { n.it = c.it + 1; return n; }
+  fb_load_item(n, c.local + 1, p);
+  return n;
+}
+
 __global__ void __launch_bounds__(FB_THREADS, 1)
 flash_attention_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                            const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do,
@@ -63,25 +105,21 @@ flash_attention_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
   uint8_t* tiles = reinterpret_cast<uint8_t*>((raw + sizeof(FbBarriers) + 1023) & ~uintptr_t(1023));
   FbBarriers* bars = reinterpret_cast<FbBarriers*>(fb_smem_raw);
   const bool layout_ok = (tiles + FB_SMEM_DATA) <= (fb_smem_raw + FB_SMEM_BYTES);
-  uint8_t* sk = tiles;
-  uint8_t* sv = sk + FB_TILE_BYTES;
-  uint8_t* sq = sv + FB_TILE_BYTES;                    // [stage] Q tiles
+  uint8_t* sk = tiles;                                 // [buffer] K tiles
+  uint8_t* sv = sk + FB_KV_BUFFERS * FB_TILE_BYTES;    // [buffer] V tiles
+  uint8_t* sq = sv + FB_KV_BUFFERS * FB_TILE_BYTES;    // [stage] Q tiles
   uint8_t* sdo = sq + FB_Q_STAGES * FB_TILE_BYTES;     // [stage] dO tiles
   uint8_t* sp = sdo + FB_Q_STAGES * FB_TILE_BYTES;     // P  (bf16, [query][key], two 64-key blocks)
   uint8_t* sds = sp + FB_PS_BYTES;                     // dS (same layout)
   volatile int* abort_flag = &bars->abort_flag;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int nq = (p.T + FB_BM - 1) / FB_BM;
-  const int bh = blockIdx.x % (p.B * p.H);
-  const int kj = blockIdx.x / (p.B * p.H);  // key tile; low tiles have the longest walks and start first
-  const int b = bh / p.H, h = bh % p.H;
-  const int row_base = b * p.T;
-  const int key0 = kj * FB_BN;
-  const int n_tiles = nq - kj;  // query tiles kj .. nq-1
 
   if (threadIdx.x == 0) {
-    tc05::mbar_init(&bars->kv_full, 1);
+    for (int s = 0; s < FB_KV_BUFFERS; ++s) {
+      tc05::mbar_init(&bars->kv_full[s], 1);
+      tc05::mbar_init(&bars->kv_empty[s], 1);
+    }
     for (int s = 0; s < FB_Q_STAGES; ++s) {
       tc05::mbar_init(&bars->q_full[s], 1);
       tc05::mbar_init(&bars->q_empty[s], 1);
@@ -106,23 +144,34 @@ flash_attention_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
   const uint32_t tmem_dk = tmem_s + 320;    // 64 columns
   const uint32_t tmem_dq = tmem_s + 384;    // two buffers of 64 columns, alternating by query tile
 
+  FbCursor first;
+  fb_load_item(first, 0, p);
+
   if (warp == FB_SOFTMAX_WARPS) {
     // -------------------------------------------------------------------------- TMA producer
+    // Runs ahead of the other roles: the next item's K and V go into the other buffer pair while the
+    // current item is still being worked on.
     if (tc05::elect_one() && !*abort_flag) {
       tc05::tma_prefetch_desc(&map_q);
       tc05::tma_prefetch_desc(&map_k);
       tc05::tma_prefetch_desc(&map_v);
       tc05::tma_prefetch_desc(&map_do);
-      tc05::mbar_arrive_expect_tx(&bars->kv_full, 2 * FB_TILE_BYTES);
-      tc05::tma_load_2d(sk, &map_k, &bars->kv_full, h * FB_HD, row_base + key0);
-      tc05::tma_load_2d(sv, &map_v, &bars->kv_full, h * FB_HD, row_base + key0);
-      for (int it = 0; it < n_tiles; ++it) {
-        const int s = it % FB_Q_STAGES;
-        if (!tc05::mbar_wait(&bars->q_empty[s], ((uint32_t)(it / FB_Q_STAGES) & 1u) ^ 1u, abort_flag)) break;
-        const int qrow = row_base + (kj + it) * FB_BM;
+      int g = 0;  // query tiles loaded so far
+      for (FbCursor c = first; c.valid(); c = fb_next(c, p), ++g) {
+        const int row_base = c.b * p.T;
+        if (c.it == 0) {
+          const int kb = c.local % FB_KV_BUFFERS;
+          if (!tc05::mbar_wait(&bars->kv_empty[kb], ((uint32_t)(c.local / FB_KV_BUFFERS) & 1u) ^ 1u, abort_flag)) break;
+          tc05::mbar_arrive_expect_tx(&bars->kv_full[kb], 2 * FB_TILE_BYTES);
+          tc05::tma_load_2d(sk + kb * FB_TILE_BYTES, &map_k, &bars->kv_full[kb], c.h * FB_HD, row_base + c.kj * FB_BN);
+          tc05::tma_load_2d(sv + kb * FB_TILE_BYTES, &map_v, &bars->kv_full[kb], c.h * FB_HD, row_base + c.kj * FB_BN);
+        }
+        const int s = g % FB_Q_STAGES;
+        if (!tc05::mbar_wait(&bars->q_empty[s], ((uint32_t)(g / FB_Q_STAGES) & 1u) ^ 1u, abort_flag)) break;
+        const int qrow = row_base + (c.kj + c.it) * FB_BM;
         tc05::mbar_arrive_expect_tx(&bars->q_full[s], 2 * FB_TILE_BYTES);
-        tc05::tma_load_2d(sq + s * FB_TILE_BYTES, &map_q, &bars->q_full[s], h * FB_HD, qrow);
-        tc05::tma_load_2d(sdo + s * FB_TILE_BYTES, &map_do, &bars->q_full[s], h * FB_HD, qrow);
+        tc05::tma_load_2d(sq + s * FB_TILE_BYTES, &map_q, &bars->q_full[s], c.h * FB_HD, qrow);
+        tc05::tma_load_2d(sdo + s * FB_TILE_BYTES, &map_do, &bars->q_full[s], c.h * FB_HD, qrow);
       }
     }
   } else if (warp == FB_SOFTMAX_WARPS + 1) {
@@ -131,12 +180,17 @@ flash_attention_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
       constexpr uint32_t idesc_sdp = tc05::instr_desc_bf16_f32(128, 128, false, false);
       constexpr uint32_t idesc_dkv = tc05::instr_desc_bf16_f32(128, FB_HD, true, true);
       constexpr uint32_t idesc_dq = tc05::instr_desc_bf16_f32(128, FB_HD, false, true);
-      const uint32_t ak = tc05::smem_u32(sk), av = tc05::smem_u32(sv);
       const uint32_t ap = tc05::smem_u32(sp), ads = tc05::smem_u32(sds);
-      auto issue_scores = [&](int it) -> bool {
-        const int s = it % FB_Q_STAGES;
-        if (!tc05::mbar_wait(&bars->q_full[s], (uint32_t)(it / FB_Q_STAGES) & 1u, abort_flag)) return false;
+      // S = Q·Kᵀ and dP = dO·Vᵀ of query tile number `g` (counted over the whole sequence)
+      auto issue_scores = [&](const FbCursor& c, int g) -> bool {
+        const int kb = c.local % FB_KV_BUFFERS;
+        if (c.it == 0) {
+          if (!tc05::mbar_wait(&bars->kv_full[kb], (uint32_t)(c.local / FB_KV_BUFFERS) & 1u, abort_flag)) return false;
+        }
+        const int s = g % FB_Q_STAGES;
+        if (!tc05::mbar_wait(&bars->q_full[s], (uint32_t)(g / FB_Q_STAGES) & 1u, abort_flag)) return false;
         tc05::tc_fence_after_sync();
+        const uint32_t ak = tc05::smem_u32(sk + kb * FB_TILE_BYTES), av = tc05::smem_u32(sv + kb * FB_TILE_BYTES);
         const uint32_t aq = tc05::smem_u32(sq + s * FB_TILE_BYTES), ado = tc05::smem_u32(sdo + s * FB_TILE_BYTES);
 #pragma unroll
         for (int ks = 0; ks < FB_HD / 16; ++ks)
@@ -149,19 +203,22 @@ flash_attention_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
         tc05::umma_commit(&bars->sdp_full);
         return true;
       };
-      bool ok = tc05::mbar_wait(&bars->kv_full, 0, abort_flag);
-      if (ok) ok = issue_scores(0);
-      for (int it = 0; it < n_tiles && ok; ++it) {
-        // S/dP of the next query tile are issued as soon as this tile's have been read out, so the
-        // softmax warps find them ready when they come back
-        if (it + 1 < n_tiles) {
-          if (!tc05::mbar_wait(&bars->sdp_free, (uint32_t)it & 1u, abort_flag)) break;
+      FbCursor c = first;
+      bool ok = c.valid() && issue_scores(c, 0);
+      for (int g = 0; ok && c.valid(); ++g) {
+        // S/dP of the next query tile (of this item or of the next one) are issued as soon as this
+        // tile's have been read out, so the softmax warps find them ready when they come back
+        const FbCursor n = fb_next(c, p);
+        if (n.valid()) {
+          if (!tc05::mbar_wait(&bars->sdp_free, (uint32_t)g & 1u, abort_flag)) break;
           tc05::tc_fence_after_sync();
-          if (!issue_scores(it + 1)) break;
+          if (!issue_scores(n, g + 1)) break;
         }
-        if (!tc05::mbar_wait(&bars->p_full, (uint32_t)it & 1u, abort_flag)) break;
+        if (!tc05::mbar_wait(&bars->p_full, (uint32_t)g & 1u, abort_flag)) break;
         tc05::tc_fence_after_sync();
-        const int s = it % FB_Q_STAGES;
+        const int s = g % FB_Q_STAGES;
+        const int kb = c.local % FB_KV_BUFFERS;
+        const uint32_t ak = tc05::smem_u32(sk + kb * FB_TILE_BYTES);
         const uint32_t aq = tc05::smem_u32(sq + s * FB_TILE_BYTES), ado = tc05::smem_u32(sdo + s * FB_TILE_BYTES);
 #pragma unroll
         for (int ks = 0; ks < FB_BM / 16; ++ks) {
@@ -170,7 +227,7 @@ flash_attention_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
           const uint64_t a_dst = tc05::smem_desc_sw128(ads + ks * 2048, FB_BM * 128, 1024);  // dS^T
           const uint64_t b_do = tc05::smem_desc_sw128(ado + ks * 2048, FB_BM * 128, 1024);
           const uint64_t b_q = tc05::smem_desc_sw128(aq + ks * 2048, FB_BM * 128, 1024);
-          const uint32_t acc = (it > 0 || ks > 0) ? 1u : 0u;
+          const uint32_t acc = (c.it > 0 || ks > 0) ? 1u : 0u;  // a new item starts its dV/dK from zero
           tc05::umma_ss(tmem_dv, a_pt, b_do, idesc_dkv, acc);
           tc05::umma_ss(tmem_dk, a_dst, b_q, idesc_dkv, acc);
         }
@@ -179,66 +236,104 @@ flash_attention_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
           // dQ_tile = dS·K: contraction over the 128 keys; dS is K-major in two 64-key blocks
           const uint64_t a_ds = tc05::smem_desc_sw128(ads + (ks / 4) * (FB_BM * 128) + (ks % 4) * 32, 16, 1024);
           const uint64_t b_k = tc05::smem_desc_sw128(ak + ks * 2048, FB_BN * 128, 1024);
-          tc05::umma_ss(tmem_dq + (uint32_t)((it & 1) * FB_HD), a_ds, b_k, idesc_dq, ks > 0 ? 1u : 0u);
+          tc05::umma_ss(tmem_dq + (uint32_t)((g & 1) * FB_HD), a_ds, b_k, idesc_dq, ks > 0 ? 1u : 0u);
         }
         tc05::umma_commit(&bars->q_empty[s]);
+        if (c.it == c.n_tiles - 1) tc05::umma_commit(&bars->kv_empty[kb]);  // the item's K and V are no longer read
         tc05::umma_commit(&bars->dq_full);
+        c = n;
       }
     }
   } else {
     // -------------------------------------------------------------------------- softmax warps
     // Per query tile: read S and dP, release them, form P and dS in registers while the tensor
-    // cores still work on the previous tile's dV/dK/dQ; then take the previous dQ tile out of
-    // tensor memory, hand P/dS over through shared memory and add the dQ tile to global memory.
+    // cores still work on the previous tile's dV/dK/dQ; then hand P/dS over through shared memory and
+    // add the previous dQ tile to global memory.  At the first tile of a new item the previous item's
+    // dK and dV are taken out of tensor memory before P/dS are released (the new item's products
+    // overwrite them) and stored while those products run.
     const int lg = warp & 3;          // tensor-memory lane group
-    const int half = warp >> 2;       // which 64 key columns / which 32 dQ columns
+    const int half = warp >> 2;       // which 64 key columns / which 32 dQ and dK/dV columns
     const int r = lg * 32 + lane;     // row within the tile
     const uint32_t lane_sel = (uint32_t)(lg * 32) << 16;
     bool ok = !*abort_flag;
-    // dQ tile of query tile `i`: out of tensor memory and into the f32 accumulator in global memory
-    auto add_dq = [&](int i, int t) {
+    // dQ tile number `g` of the sequence, for query position t of (b, h): out of tensor memory and into the f32
+    // accumulator in global memory
+    auto add_dq = [&](int g, const FbCursor& c) {
       uint32_t qb[32];
-      tc05::tmem_ld_32x32b_x32(tmem_dq + (uint32_t)((i & 1) * FB_HD) + lane_sel + half * 32, qb);
+      tc05::tmem_ld_32x32b_x32(tmem_dq + (uint32_t)((g & 1) * FB_HD) + lane_sel + half * 32, qb);
       tc05::tmem_ld_wait();
+      const int t = (c.kj + c.it) * FB_BM + r;
       if (t < p.T) {
-        float* dst = p.dq_accum + (size_t)(row_base + t) * p.ld_dq + (size_t)h * FB_HD + half * 32;
+        float* dst = p.dq_accum + (size_t)(c.b * p.T + t) * p.ld_dq + (size_t)c.h * FB_HD + half * 32;
 #pragma unroll
         for (int i = 0; i < 32; i += 4)
           red_add_v4(dst + i, __uint_as_float(qb[i]), __uint_as_float(qb[i + 1]), __uint_as_float(qb[i + 2]),
                      __uint_as_float(qb[i + 3]));
       }
     };
-    // per-row statistics of the first query tile; later tiles' are fetched one tile ahead
-    auto row_stats = [&](int it, float* neg_lse2, float* dlt) {
-      const int tt = (kj + it) * FB_BM + r;
-      const bool in = it < n_tiles && tt < p.T;
-      const size_t stat = ((size_t)b * p.H + h) * p.T + (in ? tt : 0);
+    // dV and dK of this thread's key row (32 columns each) out of tensor memory, already rounded to bf16 pairs:
+    // words 0-15 hold dV, words 16-31 dK
+    auto load_dkv = [&](uint32_t (&w)[32]) {
+#pragma unroll
+      for (int which = 0; which < 2; ++which) {
+        uint32_t raw[32];
+        tc05::tmem_ld_32x32b_x32((which == 0 ? tmem_dv : tmem_dk) + lane_sel + half * 32, raw);
+        tc05::tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) w[which * 16 + i / 2] = pack_bf16x2(__uint_as_float(raw[i]), __uint_as_float(raw[i + 1]));
+      }
+    };
+    // dK, dV of item c (row r = key)
+    auto store_dkv = [&](const uint32_t (&w)[32], const FbCursor& c) {
+      const int key = c.kj * FB_BN + r;
+      if (key < p.T) {
+        const size_t off = (size_t)(c.b * p.T + key) * p.ld_dkv + (size_t)c.h * FB_HD + half * 32;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          *reinterpret_cast<uint4*>(p.dv + off + i * 8) = make_uint4(w[i * 4], w[i * 4 + 1], w[i * 4 + 2], w[i * 4 + 3]);
+          *reinterpret_cast<uint4*>(p.dk + off + i * 8) = make_uint4(w[16 + i * 4], w[16 + i * 4 + 1], w[16 + i * 4 + 2], w[16 + i * 4 + 3]);
+        }
+      }
+    };
+    // per-row statistics of a query tile, fetched one tile ahead
+    auto row_stats = [&](const FbCursor& c, float* neg_lse2, float* dlt) {
+      const int tt = c.valid() ? (c.kj + c.it) * FB_BM + r : 0;
+      const bool in = c.valid() && tt < p.T;
+      const size_t stat = in ? ((size_t)c.b * p.H + c.h) * p.T + tt : 0;
       *neg_lse2 = in ? -p.lse[stat] * 1.4426950408889634f : 0.f;
       *dlt = in ? p.delta[stat] : 0.f;
     };
+    FbCursor c = first, prev = first;
     float neg_lse2, dlt;
-    row_stats(0, &neg_lse2, &dlt);
-    for (int it = 0; it < n_tiles && ok; ++it) {
-      const int t = (kj + it) * FB_BM + r;  // query position
+    row_stats(c, &neg_lse2, &dlt);
+    int g = 0;
+    // One query tile.  `Boundary` is the first tile of an item that follows another one: only that
+    // instance carries the read-out of the previous item's dK and dV, so the steady-state instance
+    // keeps its registers for the tile itself.
+    auto tile = [&](auto boundary_tag) -> bool {
+      constexpr bool Boundary = decltype(boundary_tag)::value;
+      const FbCursor n = fb_next(c, p);
+      const int t = (c.kj + c.it) * FB_BM + r;  // query position
+      const int key0 = c.kj * FB_BN;
       const bool t_ok = t < p.T;
       float next_neg_lse2, next_dlt;
-      row_stats(it + 1, &next_neg_lse2, &next_dlt);
-      if (!tc05::mbar_wait(&bars->sdp_full, (uint32_t)it & 1u, abort_flag)) { ok = false; break; }
+      row_stats(n, &next_neg_lse2, &next_dlt);
+      if (!tc05::mbar_wait(&bars->sdp_full, (uint32_t)g & 1u, abort_flag)) return false;
       tc05::tc_fence_after_sync();
-      const bool diag = (it == 0);
+      const bool diag = (c.it == 0);
       uint32_t pp[4][8], dd[4][8];  // P and dS of this thread's 64 key columns, bf16 pairs
       uint32_t sb[2][16], db[2][16];
       tc05::tmem_ld_32x32b_x16(tmem_s + lane_sel + half * 64, sb[0]);
       tc05::tmem_ld_32x32b_x16(tmem_dp + lane_sel + half * 64, db[0]);
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        const int col0 = half * 64 + c * 16;  // key column within the tile
+      for (int ch = 0; ch < 4; ++ch) {
+        const int col0 = half * 64 + ch * 16;  // key column within the tile
         tc05::tmem_ld_wait();
-        tc05::tmem_ld_fence(sb[c & 1]);
-        tc05::tmem_ld_fence(db[c & 1]);
-        if (c < 3) {  // the next 16 columns travel while these are worked on
-          tc05::tmem_ld_32x32b_x16(tmem_s + lane_sel + col0 + 16, sb[(c + 1) & 1]);
-          tc05::tmem_ld_32x32b_x16(tmem_dp + lane_sel + col0 + 16, db[(c + 1) & 1]);
+        tc05::tmem_ld_fence(sb[ch & 1]);
+        tc05::tmem_ld_fence(db[ch & 1]);
+        if (ch < 3) {  // the next 16 columns travel while these are worked on
+          tc05::tmem_ld_32x32b_x16(tmem_s + lane_sel + col0 + 16, sb[(ch + 1) & 1]);
+          tc05::tmem_ld_32x32b_x16(tmem_dp + lane_sel + col0 + 16, db[(ch + 1) & 1]);
         } else {  // all of S and dP is in registers: the next tile's may overwrite them
           tc05::tc_fence_before_sync();
           __syncwarp();
@@ -251,71 +346,58 @@ flash_attention_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
           for (int e = 0; e < 2; ++e) {
             const int key = key0 + col0 + i + e;
             const bool live = t_ok && !(diag && key > t);
-            const float pv = live ? ex2_fast(fmaf(__uint_as_float(sb[c & 1][i + e]), p.scale_log2, neg_lse2)) : 0.f;
+            const float pv = live ? ex2_fast(fmaf(__uint_as_float(sb[ch & 1][i + e]), p.scale_log2, neg_lse2)) : 0.f;
             pr[e] = pv;
-            dsv[e] = pv * (__uint_as_float(db[c & 1][i + e]) - dlt) * p.scale;
+            dsv[e] = pv * (__uint_as_float(db[ch & 1][i + e]) - dlt) * p.scale;
           }
-          pp[c][i / 2] = pack_bf16x2(pr[0], pr[1]);
-          dd[c][i / 2] = pack_bf16x2(dsv[0], dsv[1]);
+          pp[ch][i / 2] = pack_bf16x2(pr[0], pr[1]);
+          dd[ch][i / 2] = pack_bf16x2(dsv[0], dsv[1]);
         }
       }
       neg_lse2 = next_neg_lse2;
       dlt = next_dlt;
       // the previous tile's products have finished: its dQ is ready and P/dS may be overwritten
-      if (it > 0) {
-        if (!tc05::mbar_wait(&bars->dq_full, (uint32_t)(it - 1) & 1u, abort_flag)) { ok = false; break; }
+      if (g > 0) {
+        if (!tc05::mbar_wait(&bars->dq_full, (uint32_t)(g - 1) & 1u, abort_flag)) return false;
         tc05::tc_fence_after_sync();
       }
       uint8_t* pline = sp + half * (FB_BM * 128) + r * 128;
       uint8_t* dline = sds + half * (FB_BM * 128) + r * 128;
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
+      for (int ch = 0; ch < 4; ++ch) {
 #pragma unroll
         for (int q = 0; q < 2; ++q) {
-          const int chunk = c * 2 + q;  // 16-byte chunk = 8 keys
+          const int chunk = ch * 2 + q;  // 16-byte chunk = 8 keys
           const int off = (chunk ^ (r & 7)) << 4;
-          *reinterpret_cast<uint4*>(pline + off) = make_uint4(pp[c][q * 4], pp[c][q * 4 + 1], pp[c][q * 4 + 2], pp[c][q * 4 + 3]);
-          *reinterpret_cast<uint4*>(dline + off) = make_uint4(dd[c][q * 4], dd[c][q * 4 + 1], dd[c][q * 4 + 2], dd[c][q * 4 + 3]);
+          *reinterpret_cast<uint4*>(pline + off) = make_uint4(pp[ch][q * 4], pp[ch][q * 4 + 1], pp[ch][q * 4 + 2], pp[ch][q * 4 + 3]);
+          *reinterpret_cast<uint4*>(dline + off) = make_uint4(dd[ch][q * 4], dd[ch][q * 4 + 1], dd[ch][q * 4 + 2], dd[ch][q * 4 + 3]);
         }
       }
+      uint32_t dkv[Boundary ? 32 : 1];
+      if constexpr (Boundary) load_dkv(dkv);  // before the new item's first products may overwrite them
       tc05::fence_proxy_async_smem();
       tc05::tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) tc05::mbar_arrive(&bars->p_full);
       // the other dQ buffer is not written again before this warp's next arrival on p_full
-      if (it > 0) add_dq(it - 1, t - FB_BM);
+      if (g > 0) add_dq(g - 1, prev);
+      if constexpr (Boundary) store_dkv(dkv, prev);
+      prev = c;
+      c = n;
+      ++g;
+      return true;
+    };
+    while (ok && c.valid()) {
+      if (g > 0 && c.it == 0) ok = tile(std::true_type{});
+      else ok = tile(std::false_type{});
     }
-    if (ok) {  // dQ of the last query tile
-      if (tc05::mbar_wait(&bars->dq_full, (uint32_t)(n_tiles - 1) & 1u, abort_flag)) {
+    if (ok && g > 0) {  // dQ of the last query tile and dK, dV of the last item
+      if (tc05::mbar_wait(&bars->dq_full, (uint32_t)(g - 1) & 1u, abort_flag)) {
         tc05::tc_fence_after_sync();
-        add_dq(n_tiles - 1, (kj + n_tiles - 1) * FB_BM + r);
-      } else {
-        ok = false;
-      }
-    }
-    // dK, dV for this key tile (row r = key)
-    if (ok) {
-      const int key = key0 + r;
-      uint32_t vb[32], kb[32];
-      tc05::tmem_ld_32x32b_x32(tmem_dv + lane_sel + half * 32, vb);
-      tc05::tmem_ld_32x32b_x32(tmem_dk + lane_sel + half * 32, kb);
-      tc05::tmem_ld_wait();
-      if (key < p.T) {
-        const size_t off = (size_t)(row_base + key) * p.ld_dkv + (size_t)h * FB_HD + half * 32;
-#pragma unroll
-        for (int i = 0; i < 32; i += 8) {
-          uint4 o;
-          o.x = pack_bf16x2(__uint_as_float(vb[i]), __uint_as_float(vb[i + 1]));
-          o.y = pack_bf16x2(__uint_as_float(vb[i + 2]), __uint_as_float(vb[i + 3]));
-          o.z = pack_bf16x2(__uint_as_float(vb[i + 4]), __uint_as_float(vb[i + 5]));
-          o.w = pack_bf16x2(__uint_as_float(vb[i + 6]), __uint_as_float(vb[i + 7]));
-          *reinterpret_cast<uint4*>(p.dv + off + i) = o;
-          o.x = pack_bf16x2(__uint_as_float(kb[i]), __uint_as_float(kb[i + 1]));
-          o.y = pack_bf16x2(__uint_as_float(kb[i + 2]), __uint_as_float(kb[i + 3]));
-          o.z = pack_bf16x2(__uint_as_float(kb[i + 4]), __uint_as_float(kb[i + 5]));
-          o.w = pack_bf16x2(__uint_as_float(kb[i + 6]), __uint_as_float(kb[i + 7]));
-          *reinterpret_cast<uint4*>(p.dk + off + i) = o;
-        }
+        add_dq(g - 1, prev);
+        uint32_t dkv[32];
+        load_dkv(dkv);
+        store_dkv(dkv, prev);
       }
     }
   }
@@ -428,7 +510,7 @@ int flash_attention_backward_impl(hl_ctx* ctx, const void* q, const void* k, con
     configured = true;
   }
   const int nq = ceil_div(time, FB_BM);
-  flash_attention_bwd_kernel<<<nq * batch * n_heads, FB_THREADS, FB_SMEM_BYTES, ctx->stream>>>(mq, mk, mv, mdo, p);
+  flash_attention_bwd_kernel<<<std::min(nq * batch * n_heads, ctx->sm_count), FB_THREADS, FB_SMEM_BYTES, ctx->stream>>>(mq, mk, mv, mdo, p);
   HL_LAUNCH_CHECK("flash_attention_bwd_kernel");
   {
     const long long quads = (long long)rows * (C / 4);
