@@ -59,6 +59,12 @@ extern "C" int hl_memory_copy_indices(hl_ctx* ctx, int64_t* host, const int64_t*
 
 // NCCL (loaded at run time); see nccl_ddp.cu.
 int nccl_allreduce_sum_f32(hl_ctx* ctx, float* buf, size_t count, cudaStream_t stream);
+int nccl_allreduce_max_u8(hl_ctx* ctx, unsigned char* buf, size_t count, cudaStream_t stream);
+int mark_rows_on(hl_ctx* ctx, cudaStream_t stream, const int64_t* selected_rows, long long n_selected, const unsigned char* row_mask,
+                 unsigned char* flags, int rows);
+int mask_to_indices_on(hl_ctx* ctx, cudaStream_t stream, const unsigned char* mask, int rows, int64_t* out, int* count_dev);
+int move_rows_on(hl_ctx* ctx, cudaStream_t stream, const float* src, const int64_t* idx, const int* count_dev, int n_max, int dim,
+                 float* dst, bool scatter);
 bool nccl_active(const hl_ctx* ctx);
 int nccl_world(const hl_ctx* ctx);
 

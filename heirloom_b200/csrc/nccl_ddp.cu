@@ -15,7 +15,9 @@ namespace {
 typedef struct { char internal[128]; } NcclUniqueId;
 typedef void* NcclComm;
 constexpr int kNcclFloat32 = 7;
+constexpr int kNcclUint8 = 1;
 constexpr int kNcclSum = 0;
+constexpr int kNcclMax = 2;
 
 struct NcclApi {
   void* handle = nullptr;
@@ -76,6 +78,18 @@ int nccl_allreduce_sum_f32(hl_ctx* ctx, float* buf, size_t count, cudaStream_t s
   return HL_OK;
 }
 
+// Element-wise maximum of a byte mask over the ranks: the union of the rows any rank selected
+// (the reference's sparse data-parallel exchange, src/bin/heirloom/runtime.rs:4171-4214).
+int nccl_allreduce_max_u8(hl_ctx* ctx, unsigned char* buf, size_t count, cudaStream_t stream) {
+  NcclState* st = static_cast<NcclState*>(ctx->nccl);
+  HL_REQUIRE(st && st->comm, "NCCL communicator is not initialised");
+  int rc = api()->AllReduce(buf, buf, count, kNcclUint8, kNcclMax, st->comm, stream);
+  if (rc != 0) return fail_nccl(rc, "ncclAllReduce");
+  ctx->counters.nccl_calls += 1;
+  ctx->counters.nccl_bytes += count;
+  return HL_OK;
+}
+
 }  // namespace hl
 
 using namespace hl;
@@ -125,6 +139,12 @@ int hl_nccl_allreduce_f32(hl_ctx* ctx, float* buf_dev, size_t count) {
   // Ordered after the compute stream's queued work and before its later work, like the
   // reference's blocking in-place all-reduce (cuda.rs:8159-8206) but without a host sync.
   return nccl_allreduce_sum_f32(ctx, buf_dev, count, ctx->stream);
+}
+
+int hl_nccl_allreduce_max_u8(hl_ctx* ctx, unsigned char* buf_dev, size_t count) {
+  HL_REQUIRE(ctx && (buf_dev || count == 0), "hl_nccl_allreduce_max_u8: null argument");
+  if (count == 0) return HL_OK;
+  return nccl_allreduce_max_u8(ctx, buf_dev, count, ctx->stream);
 }
 
 int hl_nccl_abort(hl_ctx* ctx) {

@@ -81,6 +81,7 @@ struct hl_decoder {
   float* loss_dev = nullptr;
   float* loss_host = nullptr;  // pinned
   float* norm_dev = nullptr;
+  double* norm_dev64 = nullptr;  // f64 sum of squares over active sparse rows
   float* norm_host = nullptr;  // pinned
   // optimizer
   bool has_opt = false;
@@ -105,6 +106,10 @@ struct hl_decoder {
         *m_dgpre = nullptr, *m_dw = nullptr, *m_dscores = nullptr, *m_dq = nullptr, *m_dc2 = nullptr;
   __nv_bfloat16 *m_dgpre_b = nullptr, *m_dq_b = nullptr;
   unsigned char* m_row_flags = nullptr;
+  int64_t* m_union_rows = nullptr;   // rows of the value table selected by any rank this step
+  int* m_union_count = nullptr;      // device count of them
+  int* m_union_count_host = nullptr; // pinned mirror
+  int union_n = -1;                  // rows in the union after the last exchange, -1 before any
   int64_t *m_sel_all = nullptr, *m_sel_left = nullptr, *m_sel_right = nullptr;  // concatenated selections of all memory blocks
   // f32 route (reference f32 semantics: f32 tensors, f64 accumulation inside every op)
   struct F32Layer {
@@ -256,7 +261,10 @@ void plan_memory_buffers(hl_decoder* m, uint8_t*& cur) {
   m->m_dgpre_b = carve<__nv_bfloat16>(cur, N * vd);
   m->m_dq_b = carve<__nv_bfloat16>(cur, N * kd);
   m->m_row_flags = carve<unsigned char>(cur, (size_t)m->mem.slots);
-  const size_t all = N * k * (size_t)m->mem.n_memory_layers;
+  m->m_union_rows = carve<int64_t>(cur, (size_t)m->mem.slots);
+  m->m_union_count = carve<int>(cur, 4);
+  // room for this rank's selections of every memory block, or for the union of all ranks' (at most every slot)
+  const size_t all = std::max(N * k * (size_t)m->mem.n_memory_layers, (size_t)m->mem.slots);
   m->m_sel_all = carve<int64_t>(cur, all);
   m->m_sel_left = carve<int64_t>(cur, all);
   m->m_sel_right = carve<int64_t>(cur, all);
@@ -302,6 +310,7 @@ int plan_activations(hl_decoder* m, bool measure_only, size_t* bytes_out) {
   m->targets = carve<int64_t>(cur, N);
   m->loss_dev = carve<float>(cur, 4);
   m->norm_dev = carve<float>(cur, 4);
+  m->norm_dev64 = carve<double>(cur, 2);
   *bytes_out = (size_t)(cur - base);
   return HL_OK;
 }
@@ -349,6 +358,7 @@ int plan_activations_f32(hl_decoder* m, bool measure_only, size_t* bytes_out) {
   m->targets = carve<int64_t>(cur, N);
   m->loss_dev = carve<float>(cur, 4);
   m->norm_dev = carve<float>(cur, 4);
+  m->norm_dev64 = carve<double>(cur, 2);
   *bytes_out = (size_t)(cur - base);
   return HL_OK;
 }
@@ -473,10 +483,53 @@ int flush_buckets(hl_decoder* m, size_t done_elems) {
     if (end > done_elems) break;
     HL_CUDA(cudaEventRecord(m->bucket_ready[m->next_bucket], m->ctx->stream));
     HL_CUDA(cudaStreamWaitEvent(m->ctx->comm_stream, m->bucket_ready[m->next_bucket], 0));
-    HL_TRY(nccl_allreduce_sum_f32(m->ctx, m->grads + start, end - start, m->ctx->comm_stream));
+    if (m->has_memory) {
+      // the value table travels as the union of selected rows (exchange_value_rows), not densely
+      const size_t val_lo = m->off_val, val_hi = m->off_val + (size_t)m->mem.slots * m->mem.value_dim;
+      const size_t a_end = std::min(end, val_lo), b_start = std::max(start, val_hi);
+      if (start < a_end) HL_TRY(nccl_allreduce_sum_f32(m->ctx, m->grads + start, a_end - start, m->ctx->comm_stream));
+      if (b_start < end) HL_TRY(nccl_allreduce_sum_f32(m->ctx, m->grads + b_start, end - b_start, m->ctx->comm_stream));
+    } else {
+      HL_TRY(nccl_allreduce_sum_f32(m->ctx, m->grads + start, end - start, m->ctx->comm_stream));
+    }
     HL_CUDA(cudaEventRecord(m->bucket_done[m->next_bucket], m->ctx->comm_stream));
     m->next_bucket += 1;
   }
+  return HL_OK;
+}
+
+// Data-parallel exchange of the value-table gradient: every rank marks the rows its memory blocks selected, the
+// masks are combined with a byte-wise maximum, the union's gradient rows are packed, summed over the ranks and
+// put back (src/bin/heirloom/runtime.rs:4171-4214).  Rows outside the union have zero gradient on every rank.
+// Runs on the collective stream after the dense buckets; the host waits once for the row count.
+int exchange_value_rows(hl_decoder* m) {
+  if (!m->has_memory || !nccl_active(m->ctx)) return HL_OK;
+  hl_ctx* ctx = m->ctx;
+  cudaStream_t cs = ctx->comm_stream;
+  const size_t per_layer = (size_t)m->N * m->mem.top_k;
+  const int slots = m->mem.slots, vd = m->mem.value_dim;
+  HL_CUDA(cudaMemsetAsync(m->m_row_flags, 0, (size_t)slots, cs));
+  for (int l = 0; l < m->cfg.n_layers; ++l)
+    if (m->lo[l].is_memory) HL_TRY(mark_rows_on(ctx, cs, m->ma[l].idx, (long long)per_layer, nullptr, m->m_row_flags, slots));
+  HL_TRY(nccl_allreduce_max_u8(ctx, m->m_row_flags, (size_t)slots, cs));
+  HL_TRY(mask_to_indices_on(ctx, cs, m->m_row_flags, slots, m->m_union_rows, m->m_union_count));
+  HL_CUDA(cudaMemcpyAsync(m->m_union_count_host, m->m_union_count, sizeof(int), cudaMemcpyDeviceToHost, cs));
+  HL_CUDA(cudaStreamSynchronize(cs));
+  const int n = *m->m_union_count_host;
+  HL_REQUIRE(n >= 0 && n <= slots, "hl_decoder: selected-row union out of range");
+  m->union_n = n;
+  if (n > 0) {
+    int rc = ensure_workspace(ctx, sizeof(float) * (size_t)n * vd);
+    if (rc != HL_OK) return rc;
+    float* packed = reinterpret_cast<float*>(ctx->workspace);
+    // the scratch arena belongs to the compute stream: nothing queued there may still use it
+    HL_CUDA(cudaEventRecord(m->comm_done, ctx->stream));
+    HL_CUDA(cudaStreamWaitEvent(cs, m->comm_done, 0));
+    HL_TRY(move_rows_on(ctx, cs, m->grads + m->off_val, m->m_union_rows, nullptr, n, vd, packed, false));
+    HL_TRY(nccl_allreduce_sum_f32(ctx, packed, (size_t)n * vd, cs));
+    HL_TRY(move_rows_on(ctx, cs, packed, m->m_union_rows, nullptr, n, vd, m->grads + m->off_val, true));
+  }
+  HL_CUDA(cudaMemsetAsync(m->m_row_flags, 0, (size_t)slots, cs));
   return HL_OK;
 }
 
@@ -565,6 +618,12 @@ int backward(hl_decoder* m) {
   HL_TRY(hl_embedding_backward(ctx, dx, m->tokens, G + m->off_tok, V, G + m->off_pos, T, N, d));
   HL_TRY(flush_buckets(m, m->arena));
   if (nccl_active(ctx)) {
+    if (m->has_memory) {
+      // the row exchange reads gradients the compute stream is still producing
+      HL_CUDA(cudaEventRecord(m->comm_done, ctx->stream));
+      HL_CUDA(cudaStreamWaitEvent(ctx->comm_stream, m->comm_done, 0));
+      HL_TRY(exchange_value_rows(m));
+    }
     // The compute stream waits for the collectives only when something reads the averaged gradients:
     // the optimizer takes them bucket group by bucket group, every other reader waits for all of them.
     HL_CUDA(cudaEventRecord(m->comm_done, ctx->comm_stream));
@@ -696,6 +755,12 @@ int backward_f32(hl_decoder* m) {
   HL_TRY(hl_embedding_backward(ctx, dx, m->tokens, G + m->off_tok, V, G + m->off_pos, T, N, d));
   HL_TRY(flush_buckets(m, m->arena));
   if (nccl_active(ctx)) {
+    if (m->has_memory) {
+      // the row exchange reads gradients the compute stream is still producing
+      HL_CUDA(cudaEventRecord(m->comm_done, ctx->stream));
+      HL_CUDA(cudaStreamWaitEvent(ctx->comm_stream, m->comm_done, 0));
+      HL_TRY(exchange_value_rows(m));
+    }
     // The compute stream waits for the collectives only when something reads the averaged gradients:
     // the optimizer takes them bucket group by bucket group, every other reader waits for all of them.
     HL_CUDA(cudaEventRecord(m->comm_done, ctx->comm_stream));
@@ -857,6 +922,7 @@ static int decoder_create_impl(hl_ctx* ctx, const hl_decoder_config* cfg, const 
   e = cudaMallocHost(reinterpret_cast<void**>(&m->loss_host), 64);
   if (e != cudaSuccess) return cleanup(fail_cuda(e, "cudaMallocHost"));
   m->norm_host = m->loss_host + 8;
+  m->m_union_count_host = reinterpret_cast<int*>(m->loss_host + 12);
   hl_adamw_tensor whole{m->params, m->grads, m->m, m->v, m->shadow, (uint64_t)m->arena};
   int rc = adam_plan_create(ctx, &whole, 1, &m->plan);
   if (rc != HL_OK) return cleanup(rc);
@@ -1012,30 +1078,54 @@ int hl_decoder_optimizer_step_sparse_rows(hl_decoder* m) {
   HL_REQUIRE(m, "hl_decoder_optimizer_step_sparse_rows: null model");
   HL_REQUIRE(m->has_memory, "hl_decoder_optimizer_step_sparse_rows: the model has no memory layers");
   HL_REQUIRE(m->has_opt, "hl_decoder: no optimizer configured (call hl_decoder_set_optimizer)");
-  HL_REQUIRE(m->opt.clip_norm <= 0.f, "hl_decoder_optimizer_step_sparse_rows: gradient clipping over active rows is not built");
-  HL_REQUIRE(!nccl_active(m->ctx),
-             "hl_decoder_optimizer_step_sparse_rows: with more than one rank the row-union exchange is needed (not built)");
   hl_ctx* ctx = m->ctx;
   const size_t per_layer = (size_t)m->N * m->mem.top_k;
   size_t total = 0;
-  // one list for all memory blocks: a row chosen by several blocks (or tokens) is updated once
-  // (memory_sparse_adamw_updates, src/memory_transformer.rs:1293-1424)
-  for (int l = 0; l < m->cfg.n_layers; ++l) {
-    if (!m->lo[l].is_memory) continue;
-    HL_CUDA(cudaMemcpyAsync(m->m_sel_all + total, m->ma[l].idx, sizeof(int64_t) * per_layer, cudaMemcpyDeviceToDevice,
-                            ctx->stream));
-    total += per_layer;
+  if (nccl_active(ctx)) {
+    // every rank updates the rows any rank selected, with the averaged gradient
+    // (src/bin/heirloom/runtime.rs:4171-4214); the union was formed by the exchange at the end of backward
+    HL_REQUIRE(m->union_n >= 0, "hl_decoder_optimizer_step_sparse_rows: no backward pass has run yet");
+    HL_TRY(hl::wait_for_collectives(m));
+    total = (size_t)m->union_n;
+    HL_CUDA(cudaMemcpyAsync(m->m_sel_all, m->m_union_rows, sizeof(int64_t) * total, cudaMemcpyDeviceToDevice, ctx->stream));
+  } else {
+    // one list for all memory blocks: a row chosen by several blocks (or tokens) is updated once
+    // (memory_sparse_adamw_updates, src/memory_transformer.rs:1293-1424)
+    for (int l = 0; l < m->cfg.n_layers; ++l) {
+      if (!m->lo[l].is_memory) continue;
+      HL_CUDA(cudaMemcpyAsync(m->m_sel_all + total, m->ma[l].idx, sizeof(int64_t) * per_layer, cudaMemcpyDeviceToDevice,
+                              ctx->stream));
+      total += per_layer;
+    }
   }
+  if (total == 0) { m->step += 1; return HL_OK; }
   HL_TRY(hl_product_key_split_rows(ctx, m->m_sel_all, m->m_sel_left, m->m_sel_right, (long long)total, m->side));
   m->step += 1;  // every sparse call advances the step counter (src/nn.rs:2262)
   hl_adamw_params hp{};
   hp.lr = m->opt.lr; hp.beta1 = m->opt.beta1; hp.beta2 = m->opt.beta2; hp.eps = m->opt.eps;
   hp.weight_decay = m->opt.weight_decay;
-  hp.clip_scale = 1.0f;
+  const float inv_world = 1.0f / (float)nccl_world(ctx);  // summed gradients are averaged (src/nn.rs:2100-2117)
+  hp.clip_scale = inv_world;
   hp.bias_correction1 = (float)(1.0 - pow((double)m->opt.beta1, (double)m->step));
   hp.bias_correction2 = (float)(1.0 - pow((double)m->opt.beta2, (double)m->step));
   const int half = m->mem.key_dim / 2;
   HL_CUDA(cudaMemsetAsync(m->m_row_flags, 0, (size_t)m->mem.slots, ctx->stream));
+  if (m->opt.clip_norm > 0.f) {
+    // norm over the active rows of the three tables only (clip_scale_for_sparse_row_updates, src/nn.rs:2667-2774)
+    double* sum_dev = m->norm_dev64;
+    HL_CUDA(cudaMemsetAsync(sum_dev, 0, sizeof(double), ctx->stream));
+    HL_TRY(hl_sparse_rows_sum_squares_f32(ctx, m->grads + m->off_kl, m->m_sel_left, (long long)total, nullptr, m->m_row_flags,
+                                          m->side, half, sum_dev));
+    HL_TRY(hl_sparse_rows_sum_squares_f32(ctx, m->grads + m->off_kr, m->m_sel_right, (long long)total, nullptr, m->m_row_flags,
+                                          m->side, half, sum_dev));
+    HL_TRY(hl_sparse_rows_sum_squares_f32(ctx, m->grads + m->off_val, m->m_sel_all, (long long)total, nullptr, m->m_row_flags,
+                                          m->mem.slots, m->mem.value_dim, sum_dev));
+    double sum_sq = 0.0;
+    HL_TRY(hl_memcpy_d2h(ctx, &sum_sq, sum_dev, sizeof(double)));
+    if (!(sum_sq >= 0.0) || sum_sq > 1e300) return fail("non-finite or negative sparse selected gradient sum-of-squares");
+    const double norm = sqrt(sum_sq) * (double)inv_world;  // norm of the averaged gradient
+    if (norm > (double)m->opt.clip_norm) hp.clip_scale = (float)((double)m->opt.clip_norm / (norm + 1e-12)) * inv_world;
+  }
   HL_TRY(hl_sparse_adamw_rows_f32(ctx, m->params + m->off_kl, m->grads + m->off_kl, m->m + m->off_kl, m->v + m->off_kl,
                                   m->m_sel_left, (long long)total, nullptr, m->m_row_flags, m->side, half, &hp, 0));
   HL_TRY(hl_sparse_adamw_rows_f32(ctx, m->params + m->off_kr, m->grads + m->off_kr, m->m + m->off_kr, m->v + m->off_kr,

@@ -419,3 +419,42 @@ def sparse_adamw_rows(ctx: Context, param, grad, m, v, selected_rows, hp: AdamWP
     check(ctx.lib.hl_sparse_adamw_rows_f32(ctx.handle, _p(param), _p(grad), _p(m), _p(v), _p(selected_rows),
                                            c_longlong(selected_rows.numel()), _p(row_mask), _p(flags), c_int(rows),
                                            c_int(row_dim), byref(hp), c_int(1 if zero_grad_rows else 0)))
+
+
+# ---- row masks and packed rows (sparse data-parallel exchange) ----------------------------------------
+def mark_rows(ctx: Context, selected_rows: torch.Tensor, rows: int, row_mask=None) -> torch.Tensor:
+    """Byte mask with a 1 for every selected row (that the optional mask lets through)."""
+    flags = torch.zeros(rows, dtype=torch.uint8, device=selected_rows.device)
+    check(ctx.lib.hl_mark_rows_u8(ctx.handle, _p(selected_rows), c_longlong(selected_rows.numel()), _p(row_mask), _p(flags),
+                                  c_int(rows)))
+    return flags
+
+
+def mask_to_indices(ctx: Context, mask: torch.Tensor) -> torch.Tensor:
+    """Ascending row numbers of the non-zero bytes of `mask` (int64)."""
+    rows = mask.numel()
+    out = torch.empty(rows, dtype=torch.int64, device=mask.device)
+    count = torch.zeros(1, dtype=torch.int32, device=mask.device)
+    check(ctx.lib.hl_mask_to_indices_u8(ctx.handle, _p(mask), c_int(rows), _p(out), _p(count)))
+    ctx.sync()
+    return out[:int(count.item())]
+
+
+def gather_rows(ctx: Context, src: torch.Tensor, indices: torch.Tensor) -> torch.Tensor:
+    out = torch.empty(indices.numel(), src.shape[1], dtype=torch.float32, device=src.device)
+    check(ctx.lib.hl_gather_rows_f32(ctx.handle, _p(src), _p(indices), c_int(indices.numel()), c_int(src.shape[1]), _p(out)))
+    return out
+
+
+def scatter_rows(ctx: Context, packed: torch.Tensor, indices: torch.Tensor, dst: torch.Tensor) -> None:
+    check(ctx.lib.hl_scatter_rows_f32(ctx.handle, _p(packed), _p(indices), c_int(indices.numel()), c_int(dst.shape[1]), _p(dst)))
+
+
+def sparse_rows_sum_squares(ctx: Context, grad: torch.Tensor, selected_rows: torch.Tensor, row_mask=None) -> float:
+    rows, row_dim = grad.shape
+    flags = torch.zeros(rows, dtype=torch.uint8, device=grad.device)
+    total = torch.zeros(1, dtype=torch.float64, device=grad.device)
+    check(ctx.lib.hl_sparse_rows_sum_squares_f32(ctx.handle, _p(grad), _p(selected_rows), c_longlong(selected_rows.numel()),
+                                                 _p(row_mask), _p(flags), c_int(rows), c_int(row_dim), _p(total)))
+    ctx.sync()
+    return float(total.item())

@@ -321,6 +321,23 @@ int hl_memory_weighted_value_backward(hl_ctx* ctx, const int64_t* indices, const
  * (AdamW::step_sparse_rows_mut, src/nn.rs:2256-2323, :2899-2939; kernels.ptx:537-811).  row_flags is a
  * caller-owned zeroed byte per row; it is left zeroed.  zero_grad_rows != 0 also clears the gradient
  * rows that were consumed.  The caller advances the step counter and passes the bias corrections. */
+/* Row masks and packed rows (reference: cuda_selected_rows_mask, cuda_bool_mask_to_i64_indices,
+ * cuda_memory_gather_selected_grad_rows_f32_i64 and its scatter twin, src/tensor.rs:1312-1353, :2245-2337,
+ * kernels.ptx:673-811), the pieces of the sparse data-parallel exchange:
+ *   hl_mark_rows_u8        flags[r] = 1 for every selected row r (and row_mask[r] != 0 when a mask is given)
+ *   hl_mask_to_indices_u8  ascending row numbers of the non-zero bytes, and their count (int on the device)
+ *   hl_gather_rows_f32     dst[i,:] = src[indices[i],:]      hl_scatter_rows_f32  dst[indices[i],:] = src[i,:] */
+int hl_mark_rows_u8(hl_ctx* ctx, const int64_t* selected_rows, long long n_selected, const unsigned char* row_mask,
+                    unsigned char* flags, int rows);
+int hl_mask_to_indices_u8(hl_ctx* ctx, const unsigned char* mask, int rows, int64_t* out_indices, int* count_dev);
+int hl_gather_rows_f32(hl_ctx* ctx, const float* src, const int64_t* indices, int n, int dim, float* dst);
+int hl_scatter_rows_f32(hl_ctx* ctx, const float* src, const int64_t* indices, int n, int dim, float* dst);
+/* Adds to *sum_dev (f64 on the device, zeroed by the caller) the sum of squares of the gradient rows in the
+ * selected set (same set rule and mask as below): the sparse clip norm is taken over active rows only
+ * (AdamW::clip_scale_for_sparse_row_updates, src/nn.rs:2667-2774).  row_flags as below. */
+int hl_sparse_rows_sum_squares_f32(hl_ctx* ctx, const float* grad, const int64_t* selected_rows, long long n_selected,
+                                   const unsigned char* row_mask, unsigned char* row_flags, int rows, int row_dim,
+                                   double* sum_dev);
 int hl_sparse_adamw_rows_f32(hl_ctx* ctx, float* param, float* grad, float* m, float* v,
                              const int64_t* selected_rows, long long n_selected, const unsigned char* row_mask,
                              unsigned char* row_flags, int rows, int row_dim, const hl_adamw_params* hp,
@@ -334,6 +351,9 @@ int hl_nccl_version(int* out);
 int hl_nccl_unique_id(unsigned char out[128]);
 int hl_nccl_init(hl_ctx* ctx, int rank, int world, const unsigned char id[128]);
 int hl_nccl_allreduce_f32(hl_ctx* ctx, float* buf_dev, size_t count);
+/* Byte-wise maximum over the ranks, in place: the union of per-rank row masks
+ * (src/bin/heirloom/runtime.rs:4171-4214). */
+int hl_nccl_allreduce_max_u8(hl_ctx* ctx, unsigned char* buf_dev, size_t count);
 int hl_nccl_abort(hl_ctx* ctx);
 int hl_nccl_destroy(hl_ctx* ctx);
 

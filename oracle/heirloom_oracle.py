@@ -514,6 +514,19 @@ def adamw_sparse_rows_step(param: np.ndarray, grad: np.ndarray, m: np.ndarray, v
     return f32_round(p)
 
 
+def sparse_rows_clip_scale(updates, clip_norm: Optional[float]) -> float:
+    """`clip_scale_for_sparse_row_updates` (`src/nn.rs:2667-2774`): the norm runs over the active rows of
+    the listed tables only.  `updates` is a sequence of `(grad, selected_rows, row_mask)`."""
+    if clip_norm is None:
+        return 1.0
+    sum_sq = 0.0
+    for grad, selected_rows, row_mask in updates:
+        rows = active_sparse_rows(selected_rows, grad.shape[0], row_mask)
+        sum_sq += float((np.asarray(grad, F64)[rows] ** 2).sum())
+    norm = math.sqrt(sum_sq)
+    return clip_norm / (norm + 1e-12) if norm > clip_norm else 1.0
+
+
 # --------------------------------------------------------------------------------------
 # the dense decoder LM (MemoryTransformerLm with no memory layers) and its training step
 # --------------------------------------------------------------------------------------

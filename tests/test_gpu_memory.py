@@ -166,3 +166,35 @@ def test_bad_memory_index_sets_status():
     cuda.memory_weighted_value_forward(c, dev([[0, 9]], I64), dev([[0.5, 0.5]]), vals)
     with pytest.raises(HeirloomError, match="out-of-range"):
         c.sync()
+
+
+def test_row_masks_compaction_and_packed_rows():
+    from heirloom_b200 import cuda
+    c = ctx()
+    rng = np.random.default_rng(31)
+    rows, dim = 5000, 24
+    selected = rng.integers(0, rows, 700)
+    selected[:50] = selected[50:100]  # duplicates
+    mask_in = (rng.random(rows) < 0.7).astype(np.uint8)
+    sel = torch.tensor(selected, device="cuda")
+    flags = cuda.mark_rows(c, sel, rows)
+    want = np.zeros(rows, np.uint8); want[selected] = 1
+    assert np.array_equal(host(flags), want)
+    flags_m = cuda.mark_rows(c, sel, rows, row_mask=torch.tensor(mask_in, device="cuda"))
+    assert np.array_equal(host(flags_m), want & mask_in)
+    idx = cuda.mask_to_indices(c, flags)
+    assert np.array_equal(host(idx), np.flatnonzero(want))  # ascending, each row once
+    assert cuda.mask_to_indices(c, torch.zeros(rows, dtype=torch.uint8, device="cuda")).numel() == 0
+    table = rng.standard_normal((rows, dim)).astype(np.float32)
+    t = torch.tensor(table, device="cuda")
+    packed = cuda.gather_rows(c, t, idx)
+    assert np.array_equal(host(packed), table[np.flatnonzero(want)])
+    dst = torch.zeros(rows, dim, device="cuda")
+    cuda.scatter_rows(c, packed * 2.0, idx, dst)
+    c.sync()
+    expect = np.zeros_like(table); expect[np.flatnonzero(want)] = 2.0 * table[np.flatnonzero(want)]
+    assert np.array_equal(host(dst), expect)
+    # clip norm over the active rows only: a set, filtered by the mask
+    got = cuda.sparse_rows_sum_squares(c, t, sel, row_mask=torch.tensor(mask_in, device="cuda"))
+    active = np.flatnonzero(want & mask_in)
+    assert got == pytest.approx(float((table[active].astype(np.float64) ** 2).sum()), rel=1e-12)

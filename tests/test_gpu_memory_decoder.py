@@ -125,3 +125,42 @@ def test_sparse_rows_policy_updates_only_the_selected_table_rows():
     for name in ("lm_head.weight", "block.1.feed_forward.memory.query_proj.weight", "token_embedding.weight"):
         assert np.array_equal(model.parameter(name).astype(np.float64), params[name])   # no dense update in this policy
     model.close()
+
+
+def test_sparse_rows_policy_clips_by_the_norm_of_the_active_rows_only():
+    from heirloom_b200 import nn
+    model, ocfg, omem, params = build(nn.PRECISION_F32, 2, seed=3)
+    rng = np.random.default_rng(13)
+    tok = ho.zipf_tokens(rng, ocfg.vocab, (2, 129))
+    x, y = tok[:, :-1].copy(), tok[:, 1:].copy()
+    _, ograds, oidx = ho.memory_decoder_loss_and_grads(ocfg, omem, params, x, y, return_indices=True)
+    selected = np.concatenate([oidx[l].reshape(-1) for l in MEM["memory_layers"]])
+    side = int(np.sqrt(MEM["slots"]))
+    tables = (("shared_memory.product_key_left", selected // side), ("shared_memory.product_key_right", selected % side),
+              ("shared_memory.value", selected))
+    full = ho.sparse_rows_clip_scale([(ograds[n], r, None) for n, r in tables], 1e9)
+    assert full == 1.0
+    norm = np.sqrt(sum(float((ograds[n][np.unique(r)] ** 2).sum()) for n, r in tables))
+    clip_norm = 0.25 * norm  # well below the norm of the active rows, so the step is scaled by about 1/4
+    scale = ho.sparse_rows_clip_scale([(ograds[n], r, None) for n, r in tables], clip_norm)
+    assert scale == pytest.approx(0.25, rel=1e-6)
+    model.set_optimizer(lr=1e-2, weight_decay=0.01, clip_norm=clip_norm)
+    model.forward_backward(torch.tensor(x, device="cuda"), torch.tensor(y, device="cuda"))
+    model.optimizer_step_sparse_rows()
+    state = ho.AdamWState(lr=1e-2, weight_decay=0.01)
+    for name, rows in tables:
+        state.step = 0
+        p = params[name]
+        want = ho.adamw_sparse_rows_step(p, ograds[name], np.zeros_like(p), np.zeros_like(p), rows, state, clip=scale)
+        unclipped = ho.adamw_sparse_rows_step(p, ograds[name], np.zeros_like(p), np.zeros_like(p), rows,
+                                              ho.AdamWState(lr=1e-2, weight_decay=0.01))
+        got = model.parameter(name).astype(np.float64)
+        touched = np.zeros(p.shape[0], bool); touched[rows] = True
+        assert np.array_equal(got[~touched], p[~touched])
+        assert np.abs(got[touched] - want[touched]).max() <= 2e-4
+    # the first Adam step is sign-like, so clipping shows in the moments rather than in the parameters
+    m_got, _ = model.moments("shared_memory.value")
+    rows = np.unique(selected)
+    want_m = 0.1 * (ograds["shared_memory.value"][rows] * scale + 0.01 * params["shared_memory.value"][rows])
+    assert np.abs(m_got[rows] - want_m).max() <= 1e-6 + 1e-3 * np.abs(want_m).max()
+    model.close()
