@@ -60,15 +60,36 @@ side_scores_kernel(const float* __restrict__ query, long long ld_q, int q_off, c
   for (int a = 0; a < 8; ++a)
 #pragma unroll
     for (int b = 0; b < 4; ++b) acc[a][b] = 0.f;
+  // 16-byte loads need four-element granularity everywhere an address is formed
+  const bool vec = (half_dim % 4) == 0 && (ld_q % 4) == 0 && (q_off % 4) == 0 &&
+                   ((reinterpret_cast<uintptr_t>(query) | reinterpret_cast<uintptr_t>(keys)) & 15) == 0;
   for (int j0 = 0; j0 < half_dim; j0 += SS_J) {
-    // stage the slice: consecutive threads read consecutive j of one row (coalesced), and write transposed
-    for (int i = threadIdx.x; i < SS_T * SS_J; i += 256) {
-      const int t = i / SS_J, j = i % SS_J;
-      sq[j][t] = (t0 + t < tokens && j0 + j < half_dim) ? query[(size_t)(t0 + t) * ld_q + q_off + j0 + j] : 0.f;
-    }
-    for (int i = threadIdx.x; i < SS_K * SS_J; i += 256) {
-      const int kk = i / SS_J, j = i % SS_J;
-      sk[j][kk] = (k0 + kk < side && j0 + j < half_dim) ? keys[(size_t)(k0 + kk) * half_dim + j0 + j] : 0.f;
+    // stage the slice transposed.  Consecutive threads take consecutive rows, so the shared-memory stores of a warp
+    // fall into 32 different banks; each thread brings four consecutive j of its row with one 16-byte load.
+    if (vec) {
+      for (int i = threadIdx.x; i < SS_T * (SS_J / 4); i += 256) {
+        const int t = i % SS_T, j = (i / SS_T) * 4;
+        float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (t0 + t < tokens && j0 + j < half_dim)
+          x = *reinterpret_cast<const float4*>(query + (size_t)(t0 + t) * ld_q + q_off + j0 + j);
+        sq[j][t] = x.x; sq[j + 1][t] = x.y; sq[j + 2][t] = x.z; sq[j + 3][t] = x.w;
+      }
+      for (int i = threadIdx.x; i < SS_K * (SS_J / 4); i += 256) {
+        const int kk = i % SS_K, j = (i / SS_K) * 4;
+        float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (k0 + kk < side && j0 + j < half_dim)
+          x = __ldg(reinterpret_cast<const float4*>(keys + (size_t)(k0 + kk) * half_dim + j0 + j));
+        sk[j][kk] = x.x; sk[j + 1][kk] = x.y; sk[j + 2][kk] = x.z; sk[j + 3][kk] = x.w;
+      }
+    } else {
+      for (int i = threadIdx.x; i < SS_T * SS_J; i += 256) {
+        const int t = i % SS_T, j = i / SS_T;
+        sq[j][t] = (t0 + t < tokens && j0 + j < half_dim) ? query[(size_t)(t0 + t) * ld_q + q_off + j0 + j] : 0.f;
+      }
+      for (int i = threadIdx.x; i < SS_K * SS_J; i += 256) {
+        const int kk = i % SS_K, j = i / SS_K;
+        sk[j][kk] = (k0 + kk < side && j0 + j < half_dim) ? keys[(size_t)(k0 + kk) * half_dim + j0 + j] : 0.f;
+      }
     }
     __syncthreads();
     const int jn = min(SS_J, half_dim - j0);
@@ -99,108 +120,168 @@ side_scores_kernel(const float* __restrict__ query, long long ld_q, int q_off, c
 
 // ---- product-key candidates from side scores (src/memory_transformer.rs:847-924; CUDA twin
 // kernels.ptx:2121-2262): top-`beam` per side (desc score, asc index), beam^2 f32 sums, top-k by
-// (desc sum, asc slot).  One warp per token; side <= 2048, beam <= 32, top_k <= beam*beam. ---------
-__device__ __forceinline__ void warp_argmax(float& v, int& idx) {
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) {
-    const float ov = __shfl_xor_sync(0xffffffffu, v, o);
-    const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
-    if (oi != 0x7fffffff && (idx == 0x7fffffff || ov > v || (ov == v && oi < idx))) { v = ov; idx = oi; }
-  }
-}
-
-// Values stay in registers: a lane keeps its strided side scores (up to 64 per side, side <= 2048) and its own
-// current best; a round is one warp arg-max over the lanes' bests, after which only the winning lane rescans.
+// (desc sum, asc slot).  One warp per token; side <= 2048, beam <= 32, top_k <= beam*beam.
+//
+// The selection never walks the side scores one winner at a time.  Scores become order-preserving 32-bit keys held
+// in registers; the beam-th largest key is found by a four-pass radix select over a per-warp histogram; the chosen
+// entries are compacted in index order (which settles ties at the threshold), sorted across the lanes, and the
+// final top-k merges the 32 sorted rows `left[i] + right[.]` with one pointer per lane: a round is two warp
+// reductions, and only the winning lane advances. ---------------------------------------------------------------
 constexpr int PK_MAX_PER_LANE = 64;
-template <int PER_LANE>
-__device__ __forceinline__ void lane_best(const float (&v)[PER_LANE], unsigned long long taken, int n, int lane,
-                                          float* best, int* best_idx) {
-  *best = kNegInf;
-  *best_idx = 0x7fffffff;
-#pragma unroll
-  for (int i = 0; i < PER_LANE; ++i) {
-    if (i < n && !((taken >> i) & 1ull) && (*best_idx == 0x7fffffff || v[i] > *best)) {
-      *best = v[i];
-      *best_idx = i * 32 + lane;  // ascending index within the lane, so the first maximum is the lowest index
-    }
-  }
+
+// a > b as floats  <=>  okey(a) > okey(b); both zeros share a key, a NaN gets the lowest key 1, 0 means "no entry"
+__device__ __forceinline__ unsigned okey(float f) {
+  if (f != f) return 1u;
+  const unsigned u = __float_as_uint(f == 0.f ? 0.f : f);
+  return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+__device__ __forceinline__ float okey_value(unsigned k) {
+  return __uint_as_float((k & 0x80000000u) ? (k & 0x7fffffffu) : ~k);
 }
 
 template <int PER_LANE>
 __global__ void __launch_bounds__(128)
 product_key_topk_kernel(const float* __restrict__ left, const float* __restrict__ right, int64_t* __restrict__ out,
                         int tokens, int side, int top_k, int beam, int* __restrict__ status) {
-  __shared__ float s_score[4][2][32];
-  __shared__ int s_index[4][2][32];
+  __shared__ unsigned s_hist[4][256];
+  __shared__ unsigned s_key[4][32];
+  __shared__ int s_index[4][32];
+  __shared__ float s_rscore[4][32];
   const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
   const int token = blockIdx.x * 4 + w;
   if (token >= tokens) return;
-  const int n_mine = (side - lane + 31) / 32;  // entries lane, lane+32, ... below side
-  // per side: `beam` rounds of warp arg-max (desc score, asc index)
+  const unsigned full = 0xffffffffu, below = (1u << lane) - 1u;
+  unsigned l_key = 0u;  // left beam entry `lane` after the sort
+  int l_idx = 0;
   for (int sd = 0; sd < 2; ++sd) {
     const float* s = (sd == 0 ? left : right) + (size_t)token * side;
-    float v[PER_LANE];
+    unsigned key[PER_LANE];
 #pragma unroll
-    for (int i = 0; i < PER_LANE; ++i) v[i] = (i < n_mine) ? s[i * 32 + lane] : kNegInf;
-    unsigned long long taken = 0ull;
-    float mine;
-    int mine_idx;
-    lane_best<PER_LANE>(v, taken, n_mine, lane, &mine, &mine_idx);
-    for (int r = 0; r < beam; ++r) {
-      float best = mine;
-      int best_idx = mine_idx;
-      warp_argmax(best, best_idx);
-      if (best_idx != 0x7fffffff && (best_idx & 31) == lane) {
-        taken |= 1ull << (best_idx >> 5);
-        lane_best<PER_LANE>(v, taken, n_mine, lane, &mine, &mine_idx);
+    for (int i = 0; i < PER_LANE; ++i) key[i] = (i * 32 + lane < side) ? okey(s[i * 32 + lane]) : 0u;
+    // radix select, 8 bits a pass from the top: afterwards `kstar` is the beam-th largest key and `need` says how
+    // many entries equal to it belong to the beam
+    unsigned kstar = 0u, decided = 0u;
+    int need = beam;
+#pragma unroll 1
+    for (int shift = 24; shift >= 0; shift -= 8) {
+      for (int b = lane; b < 256; b += 32) s_hist[w][b] = 0u;
+      __syncwarp();
+#pragma unroll
+      for (int i = 0; i < PER_LANE; ++i)
+        if (key[i] != 0u && (key[i] & decided) == kstar) atomicAdd(&s_hist[w][(key[i] >> shift) & 255u], 1u);
+      __syncwarp();
+      unsigned c[8], mine = 0u;  // the lane owns digits 8*lane .. 8*lane+7
+#pragma unroll
+      for (int b = 0; b < 8; ++b) { c[b] = s_hist[w][lane * 8 + b]; mine += c[b]; }
+      unsigned from_here = mine;  // entries whose digit is in this lane's range or above
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const unsigned y = __shfl_down_sync(full, from_here, o);
+        if (lane + o < 32) from_here += y;
       }
-      if (lane == 0) { s_score[w][sd][r] = best; s_index[w][sd][r] = best_idx; }
+      const unsigned above = from_here - mine;
+      const bool here = above < (unsigned)need && from_here >= (unsigned)need;
+      int digit = 0;
+      unsigned over = 0u;
+      if (here) {
+        unsigned run = above;
+        bool found = false;
+#pragma unroll
+        for (int b = 7; b >= 0; --b) {
+          if (!found) {
+            if (run + c[b] >= (unsigned)need) { digit = lane * 8 + b; over = run; found = true; }
+            else run += c[b];
+          }
+        }
+      }
+      const unsigned who = __ballot_sync(full, here);
+      const int src = who ? __ffs(who) - 1 : 0;  // who == 0 only with fewer than `beam` entries, which the host rejects
+      digit = __shfl_sync(full, digit, src);
+      over = __shfl_sync(full, over, src);
+      kstar |= (unsigned)digit << shift;
+      decided |= 255u << shift;
+      need -= (int)over;
+      __syncwarp();
     }
-  }
-  __syncwarp();
-  // candidates: lane owns left entry `lane` (if < beam) against every right entry; sums and slots in registers
-  const bool has = lane < beam;
-  const float ls = has ? s_score[w][0][lane] : 0.f;
-  const int li = has ? s_index[w][0][lane] : 0;
-  float cand[32];
-  int cslot[32];
+    // compaction in index order: everything above the threshold, and the first `need` entries equal to it
+    int base = 0, eq_seen = 0;
 #pragma unroll
-  for (int j = 0; j < 32; ++j) {
-    const bool live = has && j < beam;
-    cand[j] = live ? __fadd_rn(ls, s_score[w][1][j]) : kNegInf;
-    cslot[j] = live ? li * side + s_index[w][1][j] : 0x7fffffff;
-  }
-  unsigned int used = 0u;  // bit j: candidate (lane, j) already chosen
-  auto rescan = [&](float* best, int* best_slot) {
-    *best = kNegInf;
-    *best_slot = 0x7fffffff;
+    for (int i = 0; i < PER_LANE; ++i) {
+      const bool eq = key[i] == kstar && kstar != 0u;
+      const unsigned b_eq = __ballot_sync(full, eq);
+      const bool take = (key[i] > kstar && kstar != 0u) || (eq && eq_seen + __popc(b_eq & below) < need);
+      eq_seen += __popc(b_eq);
+      const unsigned b_take = __ballot_sync(full, take);
+      if (take) {
+        const int pos = base + __popc(b_take & below);
+        if (pos < 32) { s_key[w][pos] = key[i]; s_index[w][pos] = i * 32 + lane; }
+      }
+      base += __popc(b_take);
+    }
+    __syncwarp();
+    // sort the beam across the lanes: key descending, index ascending
+    const bool valid = lane < base && lane < 32;
+    unsigned long long c64 = valid ? ((unsigned long long)s_key[w][lane] << 32) | (0xffffffffu - (unsigned)s_index[w][lane]) : 0ull;
 #pragma unroll
-    for (int j = 0; j < 32; ++j) {
-      if (cslot[j] == 0x7fffffff || ((used >> j) & 1u)) continue;
-      if (*best_slot == 0x7fffffff || cand[j] > *best || (cand[j] == *best && cslot[j] < *best_slot)) {
-        *best = cand[j];
-        *best_slot = cslot[j];
+    for (int size = 2; size <= 32; size <<= 1) {
+#pragma unroll
+      for (int stride = size >> 1; stride > 0; stride >>= 1) {
+        const unsigned long long other = __shfl_xor_sync(full, c64, stride);
+        const bool keep_max = ((lane & stride) == 0) == ((lane & size) == 0);
+        c64 = keep_max ? (c64 > other ? c64 : other) : (c64 < other ? c64 : other);
       }
     }
+    const unsigned k_sorted = (unsigned)(c64 >> 32);
+    const int i_sorted = (int)(0xffffffffu - (unsigned)(c64 & 0xffffffffull));
+    __syncwarp();
+    if (sd == 0) {
+      l_key = k_sorted;
+      l_idx = i_sorted;
+    } else {
+      s_key[w][lane] = k_sorted;
+      s_index[w][lane] = i_sorted;
+      s_rscore[w][lane] = okey_value(k_sorted);
+    }
+    __syncwarp();
+  }
+  // row `lane` of the candidate matrix: left[lane] + right[j], non-increasing in j because the right beam is sorted
+  // and f32 addition is monotone.  Equal sums sit next to each other; among them the lowest slot goes first.
+  const bool has = lane < beam && l_key != 0u;
+  const float ls = okey_value(l_key);
+  const unsigned beam_mask = beam >= 32 ? 0xffffffffu : ((1u << beam) - 1u);
+  unsigned used = 0u;
+  unsigned head_key = 0u, head_slot = 0xffffffffu;
+  int head_j = 0;
+  auto advance = [&]() {
+    head_key = 0u;
+    head_slot = 0xffffffffu;
+    const unsigned avail = ~used & beam_mask;
+    if (!has || avail == 0u) return;
+    const int j = __ffs(avail) - 1;
+    if (s_key[w][j] == 0u) return;
+    const float sum = __fadd_rn(ls, s_rscore[w][j]);
+    int best_ri = s_index[w][j], best_j = j;
+    for (int jj = j + 1; jj < beam; ++jj) {
+      if (s_key[w][jj] == 0u || !(__fadd_rn(ls, s_rscore[w][jj]) == sum)) break;
+      if (!((used >> jj) & 1u) && s_index[w][jj] < best_ri) { best_ri = s_index[w][jj]; best_j = jj; }
+    }
+    head_key = okey(sum);
+    head_slot = (unsigned)(l_idx * side + best_ri);
+    head_j = best_j;
   };
-  float mine;
-  int mine_slot;
-  rescan(&mine, &mine_slot);
+  advance();
   for (int r = 0; r < top_k; ++r) {
-    float bv = mine;
-    int bs = mine_slot;
-    warp_argmax(bv, bs);
-    if (bs == 0x7fffffff) {
+    const unsigned m = __reduce_max_sync(full, head_key);
+    if (m == 0u) {
       if (lane == 0) { atomicExch(status + ST_BAD_ARGUMENT, 1); out[(size_t)token * top_k + r] = 0; }
       continue;
     }
-    if (has && bs == mine_slot) {  // the winner is this lane's candidate: retire it and rescan
-#pragma unroll
-      for (int j = 0; j < 32; ++j)
-        if (cslot[j] == bs) used |= 1u << j;
-      rescan(&mine, &mine_slot);
+    const unsigned bs = __reduce_min_sync(full, head_key == m ? head_slot : 0xffffffffu);
+    if (head_key == m && head_slot == bs) {  // slots differ between lanes: exactly one winner
+      used |= 1u << head_j;
+      advance();
     }
-    if (lane == 0) out[(size_t)token * top_k + r] = bs;
+    if (lane == 0) out[(size_t)token * top_k + r] = (long long)bs;
   }
 }
 
@@ -224,6 +305,64 @@ __global__ void selected_scores_fwd_kernel(const int64_t* __restrict__ idx, cons
   if (token >= tokens) return;
   const int half = side > 0 ? key_dim / 2 : key_dim;
   const float* q = query + (size_t)token * ld_q;
+  if (side > 0 && half % 4 == 0 && key_dim <= 1024 && (ld_q % 4) == 0 &&
+      ((reinterpret_cast<uintptr_t>(query) | reinterpret_cast<uintptr_t>(left) | reinterpret_cast<uintptr_t>(right)) & 15) == 0) {
+    // product-key form: the query sits in registers (a lane owns up to 8 four-column groups); slots are split into
+    // their half-table rows once per 32 and handed around by shuffles; 32 per-lane partial dots are then summed
+    // across the warp by a transposing butterfly (31 exchanges instead of 32 five-step reductions).
+    const int groups = key_dim / 4, half_groups = half / 4;
+    float4 qv[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const int gi = u * 32 + lane;
+      qv[u] = gi < groups ? *reinterpret_cast<const float4*>(q + gi * 4) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    for (int k0 = 0; k0 < top_k; k0 += 32) {
+      int my_li = -1, my_ri = 0;
+      if (k0 + lane < top_k) {
+        const long long slot = idx[(size_t)token * top_k + k0 + lane];
+        if (slot >= 0 && slot < slots) {
+          my_li = (int)((unsigned)slot / (unsigned)side);
+          my_ri = (int)((unsigned)slot % (unsigned)side);
+        } else {
+          atomicExch(status + ST_BAD_INDEX, 1);
+        }
+      }
+      double part[32];
+#pragma unroll
+      for (int k = 0; k < 32; ++k) {
+        const int li = __shfl_sync(0xffffffffu, my_li, k);
+        const int ri = __shfl_sync(0xffffffffu, my_ri, k);
+        double acc = 0.0;
+        if (li >= 0) {
+          const float4* lrow = reinterpret_cast<const float4*>(left + (size_t)li * half);
+          const float4* rrow = reinterpret_cast<const float4*>(right + (size_t)ri * half);
+#pragma unroll
+          for (int u = 0; u < 8; ++u) {
+            const int gi = u * 32 + lane;
+            if (gi < groups) {
+              const float4 kv = gi < half_groups ? __ldg(lrow + gi) : __ldg(rrow + (gi - half_groups));
+              acc += (double)qv[u].x * kv.x + (double)qv[u].y * kv.y + (double)qv[u].z * kv.z + (double)qv[u].w * kv.w;
+            }
+          }
+        }
+        part[k] = acc;
+      }
+      // after the step with distance d, a lane keeps the half of its values whose index has the same d-bit as the lane
+#pragma unroll
+      for (int d = 16; d >= 1; d >>= 1) {
+        const bool upper = (lane & d) != 0;
+#pragma unroll
+        for (int i = 0; i < d; ++i) {
+          const double send = upper ? part[i] : part[i + d];
+          const double keep = upper ? part[i + d] : part[i];
+          part[i] = keep + __shfl_xor_sync(0xffffffffu, send, d);
+        }
+      }
+      if (k0 + lane < top_k) scores[(size_t)token * top_k + k0 + lane] = (float)part[0];
+    }
+    return;
+  }
   for (int k = 0; k < top_k; ++k) {
     const long long slot = idx[(size_t)token * top_k + k];
     if (slot < 0 || slot >= slots) {
@@ -232,8 +371,9 @@ __global__ void selected_scores_fwd_kernel(const int64_t* __restrict__ idx, cons
     }
     double acc = 0.0;
     if (side > 0) {
-      const float* kl = left + (size_t)(slot / side) * half;
-      const float* kr = right + (size_t)(slot % side) * half;
+      const unsigned s32 = (unsigned)slot, side32 = (unsigned)side;
+      const float* kl = left + (size_t)(s32 / side32) * half;
+      const float* kr = right + (size_t)(s32 % side32) * half;
       for (int j = lane; j < half; j += 32) acc += (double)q[j] * (double)kl[j] + (double)q[half + j] * (double)kr[j];
     } else {
       const float* kr = left + (size_t)slot * key_dim;
@@ -256,18 +396,65 @@ __global__ void selected_scores_bwd_kernel(const int64_t* __restrict__ idx, cons
   if (token >= tokens) return;
   const int half = side > 0 ? key_dim / 2 : key_dim;
   const float* q = query + (size_t)token * ld_q;
-  for (int j = lane; j < key_dim; j += 32) {
-    double acc = 0.0;
-    for (int k = 0; k < top_k; ++k) {
-      const long long slot = idx[(size_t)token * top_k + k];
-      if (slot < 0 || slot >= slots) continue;
-      const double g = (double)grad_scores[(size_t)token * top_k + k];
-      float kv;
-      if (side > 0) kv = j < half ? left[(size_t)(slot / side) * half + j] : right[(size_t)(slot % side) * half + (j - half)];
-      else kv = left[(size_t)slot * key_dim + j];
-      acc += g * (double)kv;
+  if (dq) {
+    if (side > 0 && half % 4 == 0 && key_dim <= 1024 && (ld_dq % 4) == 0 &&
+        ((reinterpret_cast<uintptr_t>(dq) | reinterpret_cast<uintptr_t>(left) | reinterpret_cast<uintptr_t>(right)) & 15) == 0) {
+      // product-key form: a lane owns up to 8 four-column groups of the query gradient; slots and score gradients are
+      // read once per 32 and handed around by shuffles, table rows come in with 16-byte loads
+      float4 acc[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) acc[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+      const int groups = key_dim / 4, half_groups = half / 4;
+      for (int k0 = 0; k0 < top_k; k0 += 32) {
+        int my_li = -1, my_ri = 0;
+        float my_g = 0.f;
+        if (k0 + lane < top_k) {
+          const long long slot = idx[(size_t)token * top_k + k0 + lane];
+          if (slot >= 0 && slot < slots) {
+            my_li = (int)((unsigned)slot / (unsigned)side);
+            my_ri = (int)((unsigned)slot % (unsigned)side);
+            my_g = grad_scores[(size_t)token * top_k + k0 + lane];
+          }
+        }
+        const int n = min(32, top_k - k0);
+        for (int k = 0; k < n; ++k) {
+          const int li = __shfl_sync(0xffffffffu, my_li, k);
+          const int ri = __shfl_sync(0xffffffffu, my_ri, k);
+          const float g = __shfl_sync(0xffffffffu, my_g, k);
+          if (li < 0) continue;
+          const float4* lrow = reinterpret_cast<const float4*>(left + (size_t)li * half);
+          const float4* rrow = reinterpret_cast<const float4*>(right + (size_t)ri * half);
+#pragma unroll
+          for (int u = 0; u < 8; ++u) {
+            const int gi = u * 32 + lane;
+            if (gi < groups) {
+              const float4 kv = gi < half_groups ? __ldg(lrow + gi) : __ldg(rrow + (gi - half_groups));
+              acc[u].x = fmaf(g, kv.x, acc[u].x); acc[u].y = fmaf(g, kv.y, acc[u].y);
+              acc[u].z = fmaf(g, kv.z, acc[u].z); acc[u].w = fmaf(g, kv.w, acc[u].w);
+            }
+          }
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const int gi = u * 32 + lane;
+        if (gi < groups) *reinterpret_cast<float4*>(dq + (size_t)token * ld_dq + gi * 4) = acc[u];
+      }
+    } else {
+      for (int j = lane; j < key_dim; j += 32) {
+        double acc = 0.0;
+        for (int k = 0; k < top_k; ++k) {
+          const long long slot = idx[(size_t)token * top_k + k];
+          if (slot < 0 || slot >= slots) continue;
+          const double g = (double)grad_scores[(size_t)token * top_k + k];
+          float kv;
+          if (side > 0) kv = j < half ? left[(size_t)(slot / side) * half + j] : right[(size_t)(slot % side) * half + (j - half)];
+          else kv = left[(size_t)slot * key_dim + j];
+          acc += g * (double)kv;
+        }
+        dq[(size_t)token * ld_dq + j] = (float)acc;
+      }
     }
-    if (dq) dq[(size_t)token * ld_dq + j] = (float)acc;
   }
   if (side > 0) return;  // the half-key gradients of the product-key form come from product_key_dkeys_kernel
   for (int k = 0; k < top_k; ++k) {
@@ -319,23 +506,29 @@ product_key_dkeys_kernel(const int64_t* __restrict__ idx, const float* __restric
       const int t = i / DK_COLS, c = i % DK_COLS;
       q_tile[i] = (t0 + t < t_end && c0 + c < half) ? query[(size_t)(t0 + t) * ld_q + (table ? half : 0) + c0 + c] : 0.f;
     }
-    // W rows: warp w builds tokens w, w+8, ...; lane 0 adds the token's gradients in slot order
+    // W rows: warp w builds tokens w, w+8, ...  Each lane takes one selected slot; lanes whose slots share a table
+    // row add their gradients one after the other in slot order (round r = the lane's rank among its duplicates),
+    // so a row's sum is formed in the same order on every run.
     for (int t = warp; t < DK_TOKENS; t += 8) {
       if (t0 + t >= t_end) break;
       for (int k0 = 0; k0 < top_k; k0 += 32) {
-        long long my_slot = -1;
-        float my_g = 0.f;
+        int row = -1;
+        float g = 0.f;
         if (k0 + lane < top_k) {
-          my_slot = idx[(size_t)(t0 + t) * top_k + k0 + lane];
-          my_g = grad_scores[(size_t)(t0 + t) * top_k + k0 + lane];
+          const long long slot = idx[(size_t)(t0 + t) * top_k + k0 + lane];
+          if (slot >= 0 && slot < slots) {
+            const unsigned s32 = (unsigned)slot, side32 = (unsigned)side;
+            row = (int)(table ? s32 % side32 : s32 / side32) - r0;
+            g = grad_scores[(size_t)(t0 + t) * top_k + k0 + lane];
+            if (row < 0 || row >= DK_ROWS) row = -1;
+          }
         }
-        const int n = min(32, top_k - k0);
-        for (int k = 0; k < n; ++k) {
-          const long long slot = __shfl_sync(0xffffffffu, my_slot, k);
-          const float g = __shfl_sync(0xffffffffu, my_g, k);
-          if (slot < 0 || slot >= slots) continue;
-          const int row = (table ? (int)(slot % side) : (int)(slot / side)) - r0;
-          if (lane == 0 && row >= 0 && row < DK_ROWS) w_tile[t * DK_ROWS + row] += g;
+        const unsigned same = __match_any_sync(0xffffffffu, row);
+        const int rank = row < 0 ? -1 : __popc(same & ((1u << lane) - 1u));
+        const int rounds = __reduce_max_sync(0xffffffffu, rank) + 1;
+        for (int r = 0; r < rounds; ++r) {
+          if (rank == r) w_tile[t * DK_ROWS + row] += g;
+          __syncwarp();
         }
       }
     }
@@ -365,7 +558,8 @@ product_key_dkeys_kernel(const int64_t* __restrict__ idx, const float* __restric
       for (int k = lane; k < top_k; k += 32) {
         const long long slot = idx[(size_t)(t0 + t) * top_k + k];
         if (slot < 0 || slot >= slots) continue;
-        const int row = (table ? (int)(slot % side) : (int)(slot / side)) - r0;
+        const unsigned s32 = (unsigned)slot, side32 = (unsigned)side;
+        const int row = (int)(table ? s32 % side32 : s32 / side32) - r0;
         if (row >= 0 && row < DK_ROWS) w_tile[t * DK_ROWS + row] = 0.f;
       }
     }

@@ -7,8 +7,9 @@
 
 Cases: the bf16 GEMM shapes of the GPT-124M-shaped step (forward, input gradient, weight gradient),
 causal attention forward/backward (batch 16, 12 heads, head_dim 64, T 1024), layer norm and GELU
-over 16384 x 768 / 16384 x 3072, fused cross-entropy over 16384 x 50304, bias column sums and the
-fused AdamW over 124 M parameters.  Inputs are N(0,1) from torch's generator with seed 0.
+over 16384 x 768 / 16384 x 3072, fused cross-entropy over 16384 x 50304, bias column sums, the fused
+AdamW over 124 M parameters, and the product-key memory layer's kernels at 16384 tokens, 2 x 512 half
+keys, 262,144 slots, top-k 32.  Inputs are N(0,1) from torch's generator with seed 0.
 Each case reports time from CUDA events on the library's compute stream, the algorithmic work
 (flop or bytes) and the fraction of the measured peak (MEASURED_PEAKS.json when present).
 """
@@ -133,6 +134,57 @@ def build_cases(ctx):
         hp = cuda.adamw_params(1e-3, 0.9, 0.999, 1e-8, 0.01, 1.0, 1)
         return (lambda: cuda.adamw_update_multi(ctx, [p], [g_], [m], [v], hp)), n * 28.0, "bytes"
 
+    # product-key memory layer at the memory-transformer sizes: 16384 tokens, 2 x 512 half keys of dimension 256,
+    # 262,144 slots, value dimension 512, top-k 32 (beam 32)
+    MT, MSIDE, MHALF, MK, MV = 16384, 512, 256, 32, 512
+
+    def mem_inputs():
+        q = torch.randn(MT, 2 * MHALF, device="cuda")
+        kl = torch.randn(MSIDE, MHALF, device="cuda") / 16.0
+        kr = torch.randn(MSIDE, MHALF, device="cuda") / 16.0
+        ls, rs = cuda.product_key_side_scores(ctx, q, kl, kr)
+        idx = cuda.product_key_topk_from_side_scores(ctx, ls, rs, MK, 32)
+        return q, kl, kr, ls, rs, idx
+
+    def mem_side():
+        q, kl, kr, *_ = mem_inputs()
+        return (lambda: cuda.product_key_side_scores(ctx, q, kl, kr)), 2.0 * 2 * MT * MSIDE * MHALF, "flop"
+
+    def mem_topk():
+        _, _, _, ls, rs, _ = mem_inputs()
+        return (lambda: cuda.product_key_topk_from_side_scores(ctx, ls, rs, MK, 32)), 2.0 * MT * MSIDE * 4 + MT * MK * 8.0, "bytes"
+
+    def mem_scores_fwd():
+        q, kl, kr, _, _, idx = mem_inputs()
+        return (lambda: cuda.memory_selected_scores_forward(ctx, idx, q, kl, kr)), MT * MK * 2.0 * MHALF * 4, "bytes"
+
+    def mem_scores_bwd():
+        q, kl, kr, _, _, idx = mem_inputs()
+        g = torch.randn(MT, MK, device="cuda")
+        return (lambda: cuda.memory_selected_scores_backward(ctx, idx, q, kl, kr, g)), MT * MK * 2.0 * MHALF * 4, "bytes"
+
+    def mem_value_fwd():
+        _, _, _, _, _, idx = mem_inputs()
+        vals = torch.randn(MSIDE * MSIDE, MV, device="cuda") * 0.02
+        w = torch.softmax(torch.randn(MT, MK, device="cuda"), dim=1)
+        return (lambda: cuda.memory_weighted_value_forward(ctx, idx, w, vals)), MT * MK * MV * 4.0, "bytes"
+
+    def mem_value_bwd():
+        _, _, _, _, _, idx = mem_inputs()
+        vals = torch.randn(MSIDE * MSIDE, MV, device="cuda") * 0.02
+        w = torch.softmax(torch.randn(MT, MK, device="cuda"), dim=1)
+        go = torch.randn(MT, MV, device="cuda")
+        dv = torch.zeros_like(vals)
+        dw = torch.empty_like(w)
+
+        def run():
+            cuda.check(ctx.lib.hl_memory_weighted_value_backward(ctx.handle, cuda._p(idx), cuda._p(w), cuda._p(vals), cuda._p(go),
+                                                                 cuda._p(dw), cuda._p(dv), MT, MK, MSIDE * MSIDE, MV))
+        return run, MT * MK * MV * 4.0 * 3, "bytes"  # value rows read, gradient rows read and written by the atomics
+
+    cases.update(memory_side_scores=mem_side, memory_topk=mem_topk, memory_selected_scores_fwd=mem_scores_fwd,
+                 memory_selected_scores_bwd=mem_scores_bwd, memory_weighted_value_fwd=mem_value_fwd,
+                 memory_weighted_value_bwd=mem_value_bwd)
     cases.update(attention_fwd_t1024=attn_fwd, attention_bwd_t1024=attn_bwd, layer_norm_fwd=ln_fwd, layer_norm_bwd=ln_bwd,
                  gelu_fwd_16384x3072=gelu_fwd, cross_entropy_16384x50304=ce, bias_colsum_16384x50304=colsum,
                  adamw_124m=adamw)

@@ -86,6 +86,32 @@ def test_side_scores_are_bit_exact_and_indices_equal_the_oracle(tokens, side, ke
     assert np.array_equal(host(idx), ho.product_key_indices_from_side_scores(ql, qr, top_k, beam))
 
 
+@pytest.mark.parametrize("tokens,side,top_k", [(64, 2048, 32), (33, 24, 16), (40, 512, 1), (17, 100, 9)])
+def test_product_key_selection_on_degenerate_scores(tokens, side, top_k):
+    """All-equal scores, signed zeros, a handful of distinct values, -inf entries: the selection must still
+    follow (descending score, ascending index) and (descending sum, ascending slot)."""
+    from heirloom_b200 import cuda
+    c = ctx()
+    rng = np.random.default_rng(side * 7 + top_k)
+    beam = ho.product_key_beam(side, top_k)
+    cases = []
+    zeros = np.zeros((tokens, side), np.float32)
+    cases.append((zeros, zeros))
+    signed = np.where(rng.random((tokens, side)) < 0.5, np.float32(0.0), np.float32(-0.0)).astype(np.float32)
+    cases.append((signed, signed[::-1].copy()))
+    few_l = rng.integers(-2, 3, (tokens, side)).astype(np.float32)
+    few_r = rng.integers(-2, 3, (tokens, side)).astype(np.float32)
+    cases.append((few_l, few_r))
+    holes = rng.standard_normal((tokens, side)).astype(np.float32)
+    holes[rng.random((tokens, side)) < 0.3] = -np.inf
+    cases.append((holes, rng.standard_normal((tokens, side)).astype(np.float32) * 1e-3))
+    wide = (rng.standard_normal((tokens, side)) * 10.0 ** rng.integers(-30, 30, (tokens, side))).astype(np.float32)
+    cases.append((wide, -wide))
+    for left, right in cases:
+        idx = cuda.product_key_topk_from_side_scores(c, dev(left), dev(right), top_k, beam)
+        assert np.array_equal(host(idx), ho.product_key_indices_from_side_scores(left, right, top_k, beam))
+
+
 def test_memory_layer_forward_backward_random():
     from heirloom_b200 import cuda
     c = ctx()
