@@ -672,6 +672,17 @@ __global__ void weighted_value_bwd_kernel(const int64_t* __restrict__ idx, const
   }
 }
 
+// ---- access counts: counts[r] += occurrences of r among the selected rows (kernels.ptx:813-886) ---------------
+__global__ void access_count_rows_kernel(const int64_t* __restrict__ selected, long long n, int rows,
+                                         unsigned long long* __restrict__ counts, int* __restrict__ status) {
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += stride) {
+    const long long r = selected[i];
+    if (r < 0 || r >= rows) { atomicExch(status + ST_BAD_INDEX, 1); continue; }
+    atomicAdd(counts + r, 1ull);
+  }
+}
+
 // ---- row-set AdamW (src/nn.rs:2256-2323, :2899-2939; kernels.ptx:537-811) -----------------------------------
 __global__ void mark_rows_kernel(const int64_t* __restrict__ selected, long long n, unsigned char* __restrict__ flags,
                                  const unsigned char* __restrict__ row_mask, int rows, int* __restrict__ status) {
@@ -955,6 +966,19 @@ int move_rows_on(hl_ctx* ctx, cudaStream_t stream, const float* src, const int64
 }  // namespace hl
 
 extern "C" {
+
+int hl_memory_access_count_rows_i64_u64(hl_ctx* ctx, const int64_t* selected_rows, long long n_selected, int slots,
+                                        unsigned long long* counts) {
+  HL_REQUIRE(ctx && counts, "hl_memory_access_count_rows_i64_u64: null argument");
+  HL_REQUIRE(slots > 0, "memory_access_count_rows_i64_u64 requires non-zero memory_slots");
+  HL_REQUIRE(n_selected >= 0 && (n_selected == 0 || selected_rows), "hl_memory_access_count_rows_i64_u64: null selected rows");
+  if (n_selected == 0) return HL_OK;
+  const unsigned blocks = (unsigned)std::min<long long>(ceil_div_ll(n_selected, 256), (long long)ctx->sm_count * 16);
+  access_count_rows_kernel<<<blocks, 256, 0, ctx->stream>>>(selected_rows, n_selected, slots, counts, ctx->status_dev);
+  HL_LAUNCH_CHECK("access_count_rows_kernel");
+  count_launch(ctx);
+  return HL_OK;
+}
 
 int hl_mark_rows_u8(hl_ctx* ctx, const int64_t* selected_rows, long long n_selected, const unsigned char* row_mask,
                     unsigned char* flags, int rows) {

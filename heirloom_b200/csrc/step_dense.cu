@@ -106,6 +106,8 @@ struct hl_decoder {
         *m_dgpre = nullptr, *m_dw = nullptr, *m_dscores = nullptr, *m_dq = nullptr, *m_dc2 = nullptr;
   __nv_bfloat16 *m_dgpre_b = nullptr, *m_dq_b = nullptr;
   unsigned char* m_row_flags = nullptr;
+  unsigned char *smft_value_mask = nullptr, *smft_left_mask = nullptr, *smft_right_mask = nullptr;  // [slots], [side], [side]
+  bool smft_on = false;  // the sparse-rows step filters its rows through the three masks
   int64_t* m_union_rows = nullptr;   // rows of the value table selected by any rank this step
   int* m_union_count = nullptr;      // device count of them
   int* m_union_count_host = nullptr; // pinned mirror
@@ -261,6 +263,9 @@ void plan_memory_buffers(hl_decoder* m, uint8_t*& cur) {
   m->m_dgpre_b = carve<__nv_bfloat16>(cur, N * vd);
   m->m_dq_b = carve<__nv_bfloat16>(cur, N * kd);
   m->m_row_flags = carve<unsigned char>(cur, (size_t)m->mem.slots);
+  m->smft_value_mask = carve<unsigned char>(cur, (size_t)m->mem.slots);
+  m->smft_left_mask = carve<unsigned char>(cur, (size_t)m->side);
+  m->smft_right_mask = carve<unsigned char>(cur, (size_t)m->side);
   m->m_union_rows = carve<int64_t>(cur, (size_t)m->mem.slots);
   m->m_union_count = carve<int>(cur, 4);
   // room for this rank's selections of every memory block, or for the union of all ranks' (at most every slot)
@@ -1109,16 +1114,21 @@ int hl_decoder_optimizer_step_sparse_rows(hl_decoder* m) {
   hp.bias_correction1 = (float)(1.0 - pow((double)m->opt.beta1, (double)m->step));
   hp.bias_correction2 = (float)(1.0 - pow((double)m->opt.beta2, (double)m->step));
   const int half = m->mem.key_dim / 2;
+  // SMFT: a table row is updated only where its mask allows (memory_sparse_adamw_updates_with_mask,
+  // src/memory_transformer.rs:1426-1468)
+  const unsigned char* mask_l = m->smft_on ? m->smft_left_mask : nullptr;
+  const unsigned char* mask_r = m->smft_on ? m->smft_right_mask : nullptr;
+  const unsigned char* mask_v = m->smft_on ? m->smft_value_mask : nullptr;
   HL_CUDA(cudaMemsetAsync(m->m_row_flags, 0, (size_t)m->mem.slots, ctx->stream));
   if (m->opt.clip_norm > 0.f) {
     // norm over the active rows of the three tables only (clip_scale_for_sparse_row_updates, src/nn.rs:2667-2774)
     double* sum_dev = m->norm_dev64;
     HL_CUDA(cudaMemsetAsync(sum_dev, 0, sizeof(double), ctx->stream));
-    HL_TRY(hl_sparse_rows_sum_squares_f32(ctx, m->grads + m->off_kl, m->m_sel_left, (long long)total, nullptr, m->m_row_flags,
+    HL_TRY(hl_sparse_rows_sum_squares_f32(ctx, m->grads + m->off_kl, m->m_sel_left, (long long)total, mask_l, m->m_row_flags,
                                           m->side, half, sum_dev));
-    HL_TRY(hl_sparse_rows_sum_squares_f32(ctx, m->grads + m->off_kr, m->m_sel_right, (long long)total, nullptr, m->m_row_flags,
+    HL_TRY(hl_sparse_rows_sum_squares_f32(ctx, m->grads + m->off_kr, m->m_sel_right, (long long)total, mask_r, m->m_row_flags,
                                           m->side, half, sum_dev));
-    HL_TRY(hl_sparse_rows_sum_squares_f32(ctx, m->grads + m->off_val, m->m_sel_all, (long long)total, nullptr, m->m_row_flags,
+    HL_TRY(hl_sparse_rows_sum_squares_f32(ctx, m->grads + m->off_val, m->m_sel_all, (long long)total, mask_v, m->m_row_flags,
                                           m->mem.slots, m->mem.value_dim, sum_dev));
     double sum_sq = 0.0;
     HL_TRY(hl_memcpy_d2h(ctx, &sum_sq, sum_dev, sizeof(double)));
@@ -1127,12 +1137,37 @@ int hl_decoder_optimizer_step_sparse_rows(hl_decoder* m) {
     if (norm > (double)m->opt.clip_norm) hp.clip_scale = (float)((double)m->opt.clip_norm / (norm + 1e-12)) * inv_world;
   }
   HL_TRY(hl_sparse_adamw_rows_f32(ctx, m->params + m->off_kl, m->grads + m->off_kl, m->m + m->off_kl, m->v + m->off_kl,
-                                  m->m_sel_left, (long long)total, nullptr, m->m_row_flags, m->side, half, &hp, 0));
+                                  m->m_sel_left, (long long)total, mask_l, m->m_row_flags, m->side, half, &hp, 0));
   HL_TRY(hl_sparse_adamw_rows_f32(ctx, m->params + m->off_kr, m->grads + m->off_kr, m->m + m->off_kr, m->v + m->off_kr,
-                                  m->m_sel_right, (long long)total, nullptr, m->m_row_flags, m->side, half, &hp, 0));
+                                  m->m_sel_right, (long long)total, mask_r, m->m_row_flags, m->side, half, &hp, 0));
   return hl_sparse_adamw_rows_f32(ctx, m->params + m->off_val, m->grads + m->off_val, m->m + m->off_val, m->v + m->off_val,
-                                  m->m_sel_all, (long long)total, nullptr, m->m_row_flags, m->mem.slots, m->mem.value_dim, &hp,
+                                  m->m_sel_all, (long long)total, mask_v, m->m_row_flags, m->mem.slots, m->mem.value_dim, &hp,
                                   0);
+}
+
+int hl_decoder_memory_access_counts(hl_decoder* m, unsigned long long* counts_dev) {
+  HL_REQUIRE(m && counts_dev, "hl_decoder_memory_access_counts: null argument");
+  HL_REQUIRE(m->has_memory, "hl_decoder_memory_access_counts: the model has no memory layers");
+  const long long per_layer = (long long)m->N * m->mem.top_k;
+  for (int l = 0; l < m->cfg.n_layers; ++l)
+    if (m->lo[l].is_memory)
+      HL_TRY(hl_memory_access_count_rows_i64_u64(m->ctx, m->ma[l].idx, per_layer, m->mem.slots, counts_dev));
+  return HL_OK;
+}
+
+int hl_decoder_set_smft_masks(hl_decoder* m, const unsigned char* value_mask_host, const unsigned char* left_mask_host,
+                              const unsigned char* right_mask_host) {
+  HL_REQUIRE(m, "hl_decoder_set_smft_masks: null model");
+  HL_REQUIRE(m->has_memory, "hl_decoder_set_smft_masks: the model has no memory layers");
+  if (!value_mask_host && !left_mask_host && !right_mask_host) { m->smft_on = false; return HL_OK; }
+  HL_REQUIRE(value_mask_host && left_mask_host && right_mask_host, "hl_decoder_set_smft_masks: give all three masks or none");
+  hl_ctx* ctx = m->ctx;
+  HL_CUDA(cudaMemcpyAsync(m->smft_value_mask, value_mask_host, (size_t)m->mem.slots, cudaMemcpyHostToDevice, ctx->stream));
+  HL_CUDA(cudaMemcpyAsync(m->smft_left_mask, left_mask_host, (size_t)m->side, cudaMemcpyHostToDevice, ctx->stream));
+  HL_CUDA(cudaMemcpyAsync(m->smft_right_mask, right_mask_host, (size_t)m->side, cudaMemcpyHostToDevice, ctx->stream));
+  HL_CUDA(cudaStreamSynchronize(ctx->stream));  // the host buffers may be freed on return
+  m->smft_on = true;
+  return HL_OK;
 }
 
 int hl_decoder_train_step_device(hl_decoder* m, const int64_t* tokens_dev, const int64_t* targets_dev) {

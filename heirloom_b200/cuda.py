@@ -458,3 +458,17 @@ def sparse_rows_sum_squares(ctx: Context, grad: torch.Tensor, selected_rows: tor
                                                  _p(row_mask), _p(flags), c_int(rows), c_int(row_dim), _p(total)))
     ctx.sync()
     return float(total.item())
+
+
+def memory_access_count_rows(ctx: Context, selected_rows: torch.Tensor, slots: int, counts: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Row-access histogram of int64 `selected_rows` (`memory_access_count_rows_i64_u64`,
+    heirloom-kernels/src/cuda.rs:2052-2088).  Counts are 64-bit; torch has no unsigned 64-bit arithmetic, so
+    they live in an int64 tensor (same bits below 2^63).  Pass `counts` to keep adding to a histogram."""
+    if slots <= 0:
+        raise HeirloomError("memory_access_count_rows_i64_u64 requires non-zero memory_slots")
+    if counts is None:
+        counts = torch.zeros(slots, dtype=torch.int64, device=selected_rows.device)
+    flat = selected_rows.reshape(-1).contiguous()
+    check(ctx.lib.hl_memory_access_count_rows_i64_u64(ctx.handle, _p(flat), c_longlong(flat.numel()), c_int(slots), _p(counts)))
+    ctx.sync()  # surfaces a bad-index status as an error, like the reference's status check
+    return counts

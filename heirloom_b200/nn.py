@@ -224,6 +224,42 @@ class DecoderLm:
                                                     c_longlong(out.size)))
         return out
 
+    def memory_access_counts(self):
+        """Row-access counts of the last forward pass over every memory block, counted on the device
+        (`MemoryTransformerLm::memory_access_counts`, src/memory_transformer.rs:1561-1583)."""
+        from .smft import MemoryAccessCounts
+        if self.memory is None:
+            raise HeirloomError("memory_access_counts: the model has no memory layers")
+        counts = torch.zeros(self.memory.slots, dtype=torch.int64, device="cuda")
+        check(self._lib.hl_decoder_memory_access_counts(self.handle, c_void_p(counts.data_ptr())))
+        self.ctx.sync()
+        return MemoryAccessCounts.from_row_counts(self.memory.slots, counts.cpu().numpy().view(np.uint64))
+
+    def smft_access_report(self, top_rows: int):
+        """`smft_access_report` (src/memory_transformer.rs:1585-1591)."""
+        from .smft import SmftAccessReport
+        counts = self.memory_access_counts()
+        return SmftAccessReport(counts, counts.top_rows(top_rows))
+
+    def smft_row_mask_against(self, background, trainable_fraction: float, min_rows: int):
+        """`smft_row_mask_against` (src/memory_transformer.rs:1593-1601)."""
+        return self.memory_access_counts().smft_mask_against(background, trainable_fraction, min_rows)
+
+    def set_smft_mask(self, mask) -> None:
+        """Restricts the sparse-rows step to the mask's trainable value rows and to the half-key rows of its
+        conservative projection (`memory_sparse_adamw_updates_with_mask`, src/memory_transformer.rs:1426-1468).
+        `None` lifts the restriction."""
+        if mask is None:
+            check(self._lib.hl_decoder_set_smft_masks(self.handle, None, None, None))
+            return
+        if self.memory is None or mask.memory_slots != self.memory.slots:
+            slots = self.memory.slots if self.memory else 0
+            raise HeirloomError(f"SMFT mask memory_slots {mask.memory_slots} does not match model memory_slots {slots}")
+        projection = mask.product_key_projection()
+        value, left, right = mask.to_mask(), projection.left_mask(), projection.right_mask()
+        check(self._lib.hl_decoder_set_smft_masks(self.handle, value.ctypes.data_as(c_void_p), left.ctypes.data_as(c_void_p),
+                                                  right.ctypes.data_as(c_void_p)))
+
     @property
     def launches_last_step(self) -> int:
         return int(self._lib.hl_decoder_launches_last_step(self.handle))

@@ -409,8 +409,26 @@ int hl_memory_decoder_create(hl_ctx* ctx, const hl_decoder_config* cfg, const hl
  * AdamW::step_sparse_rows_mut, src/nn.rs:2256-2323): row-set AdamW on product_key_left,
  * product_key_right (rows slot/side and slot%side of every selected slot) and the value table
  * (selected slots), rows chosen by several blocks or tokens updated once; nothing else is
- * updated and the step counter advances by one.  Single rank, no clipping. */
+ * updated and the step counter advances by one.  With a clip norm the scale comes from the active
+ * rows only; under data parallelism the rows are the union over the ranks.  When SMFT masks are set
+ * (below), a row is updated only where its table's mask is non-zero. */
 int hl_decoder_optimizer_step_sparse_rows(hl_decoder* model);
+/* SMFT (sparse memory fine-tuning) support.
+ *   hl_memory_access_count_rows_i64_u64: counts[r] += occurrences of r in selected_rows, 64-bit atomic
+ *     adds; counts is caller-owned device memory [slots] (zero it for a fresh histogram); a row outside
+ *     [0, slots) sets the bad-index status (memory_access_count_rows_i64_u64,
+ *     heirloom-kernels/src/cuda.rs:2052-2088, kernels.ptx:813-886).
+ *   hl_decoder_memory_access_counts: adds the selections of the last forward pass of every memory block
+ *     (MemoryTransformerLm::memory_access_counts, src/memory_transformer.rs:1561-1583).
+ *   hl_decoder_set_smft_masks: byte masks (host memory) over the value rows [slots] and the rows of the
+ *     two half-key tables [side] each, used by the sparse-rows step
+ *     (memory_sparse_adamw_updates_with_mask, src/memory_transformer.rs:1426-1468); three null
+ *     pointers switch masking off. */
+int hl_memory_access_count_rows_i64_u64(hl_ctx* ctx, const int64_t* selected_rows, long long n_selected, int slots,
+                                        unsigned long long* counts);
+int hl_decoder_memory_access_counts(hl_decoder* model, unsigned long long* counts_dev);
+int hl_decoder_set_smft_masks(hl_decoder* model, const unsigned char* value_mask_host,
+                              const unsigned char* left_mask_host, const unsigned char* right_mask_host);
 /* Slots chosen by the last forward of one memory block: int64 [batch*context, top_k]. */
 int hl_decoder_selected_indices(hl_decoder* model, int layer, int64_t* host, long long count);
 void hl_decoder_destroy(hl_decoder* model);

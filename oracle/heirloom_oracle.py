@@ -514,6 +514,29 @@ def adamw_sparse_rows_step(param: np.ndarray, grad: np.ndarray, m: np.ndarray, v
     return f32_round(p)
 
 
+def smft_mask_against(foreground_counts, background_counts, trainable_fraction: float, min_rows: int):
+    """TF-IDF ranking of the rows a foreground count set touched against a background set
+    (`src/memory_transformer.rs:273-327`; order `:2045-2055`): score = (fg / max(sum fg, 1)) *
+    ln((max(sum bg, 1) + slots) / (bg + 1)); descending score, then descending fg, ascending bg, ascending
+    row; the first max(ceil(unique * fraction), min(min_rows, unique)) rows are trainable.  Returns
+    `(trainable_rows, [(row, score), ...])` with the scores in rank order."""
+    fg = np.asarray(foreground_counts, np.uint64).astype(F64)
+    bg = np.asarray(background_counts, np.uint64).astype(F64)
+    if fg.shape != bg.shape:
+        raise ValueError("SMFT foreground/background memory_slots mismatch")
+    slots = max(fg.size, 1)
+    touched = np.flatnonzero(fg > 0)
+    tf = fg[touched] / max(fg.sum(), 1.0)
+    idf = np.array([math.log((max(bg.sum(), 1.0) + slots) / (b + 1.0)) for b in bg[touched]], F64)
+    score = tf * idf
+    # lexsort: last key is the primary one
+    order = np.lexsort((touched, bg[touched], -fg[touched], -score))
+    unique = touched.size
+    count = min(max(int(math.ceil(unique * trainable_fraction)), min(min_rows, unique)), unique)
+    ranked = [(int(touched[i]), float(score[i])) for i in order]
+    return [r for r, _ in ranked[:count]], ranked
+
+
 def sparse_rows_clip_scale(updates, clip_norm: Optional[float]) -> float:
     """`clip_scale_for_sparse_row_updates` (`src/nn.rs:2667-2774`): the norm runs over the active rows of
     the listed tables only.  `updates` is a sequence of `(grad, selected_rows, row_mask)`."""
