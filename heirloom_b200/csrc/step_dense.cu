@@ -101,6 +101,8 @@ struct hl_decoder {
   hl_memory_config mem{};
   int side = 0;
   size_t off_kl = 0, off_kr = 0, off_val = 0;
+  size_t tables_end = 0;  // first arena element after the value table
+  AdamPlan *plan_tables = nullptr, *plan_no_values = nullptr;  // the memory tables alone; everything but the value table
   std::vector<MemoryActs> ma;  // indexed by layer; empty entries for dense layers
   float *m_ls = nullptr, *m_rs = nullptr, *m_scores = nullptr, *m_dmv = nullptr, *m_dweighted = nullptr, *m_dgate = nullptr,
         *m_dgpre = nullptr, *m_dw = nullptr, *m_dscores = nullptr, *m_dq = nullptr, *m_dc2 = nullptr;
@@ -190,6 +192,7 @@ void plan_parameters(hl_decoder* m) {
     m->off_kl = add("shared_memory.product_key_left", (size_t)m->side * half, 2, m->side, half);
     m->off_kr = add("shared_memory.product_key_right", (size_t)m->side * half, 2, m->side, half);
     m->off_val = add("shared_memory.value", (size_t)m->mem.slots * m->mem.value_dim, 2, m->mem.slots, m->mem.value_dim);
+    m->tables_end = cur;
   }
   m->off_pos = add("position_embedding.weight", (size_t)T * d, 2, T, d);
   m->off_tok = add("token_embedding.weight", (size_t)V * d, 2, V, d);
@@ -931,6 +934,18 @@ static int decoder_create_impl(hl_ctx* ctx, const hl_decoder_config* cfg, const 
   hl_adamw_tensor whole{m->params, m->grads, m->m, m->v, m->shadow, (uint64_t)m->arena};
   int rc = adam_plan_create(ctx, &whole, 1, &m->plan);
   if (rc != HL_OK) return cleanup(rc);
+  if (m->has_memory) {
+    auto span = [&](size_t begin, size_t end) {
+      return hl_adamw_tensor{m->params + begin, m->grads + begin, m->m + begin, m->v + begin, m->shadow + begin,
+                             (uint64_t)(end - begin)};
+    };
+    hl_adamw_tensor tables = span(m->off_kl, m->tables_end);
+    rc = adam_plan_create(ctx, &tables, 1, &m->plan_tables);
+    if (rc != HL_OK) return cleanup(rc);
+    hl_adamw_tensor rest[2] = {span(0, m->off_val), span(m->tables_end, m->arena)};
+    rc = adam_plan_create(ctx, rest, 2, &m->plan_no_values);
+    if (rc != HL_OK) return cleanup(rc);
+  }
   m->n_buckets = (m->arena + m->bucket_elems - 1) / m->bucket_elems;
   m->bucket_ready.resize(m->n_buckets);
   m->bucket_done.resize(m->n_buckets);
@@ -962,6 +977,8 @@ void hl_decoder_destroy(hl_decoder* m) {
   for (auto ev : m->bucket_done) if (ev) cudaEventDestroy(ev);
   if (m->comm_done) cudaEventDestroy(m->comm_done);
   adam_plan_destroy(m->plan);
+  adam_plan_destroy(m->plan_tables);
+  adam_plan_destroy(m->plan_no_values);
   cudaFree(m->params); cudaFree(m->grads); cudaFree(m->m); cudaFree(m->v); cudaFree(m->shadow); cudaFree(m->act_arena);
   if (m->loss_host) cudaFreeHost(m->loss_host);
   delete m;
@@ -1079,23 +1096,25 @@ int hl_decoder_optimizer_step(hl_decoder* m) {
   return HL_OK;
 }
 
-int hl_decoder_optimizer_step_sparse_rows(hl_decoder* m) {
-  HL_REQUIRE(m, "hl_decoder_optimizer_step_sparse_rows: null model");
-  HL_REQUIRE(m->has_memory, "hl_decoder_optimizer_step_sparse_rows: the model has no memory layers");
-  HL_REQUIRE(m->has_opt, "hl_decoder: no optimizer configured (call hl_decoder_set_optimizer)");
+namespace hl {
+namespace {
+
+constexpr int kTableLeft = 1, kTableRight = 2, kTableValue = 4, kTablesAll = 7;
+
+// The rows the sparse policies work on, as one list for all memory blocks (a row chosen by several blocks or tokens
+// is updated once; memory_sparse_adamw_updates, src/memory_transformer.rs:1293-1424), split into the half-key rows.
+// Under data parallelism the list is the union over the ranks, formed by the exchange at the end of backward:
+// every rank updates the rows any rank selected, with the averaged gradient (src/bin/heirloom/runtime.rs:4171-4214).
+int gather_selection(hl_decoder* m, size_t* total_out) {
   hl_ctx* ctx = m->ctx;
   const size_t per_layer = (size_t)m->N * m->mem.top_k;
   size_t total = 0;
   if (nccl_active(ctx)) {
-    // every rank updates the rows any rank selected, with the averaged gradient
-    // (src/bin/heirloom/runtime.rs:4171-4214); the union was formed by the exchange at the end of backward
-    HL_REQUIRE(m->union_n >= 0, "hl_decoder_optimizer_step_sparse_rows: no backward pass has run yet");
-    HL_TRY(hl::wait_for_collectives(m));
+    HL_REQUIRE(m->union_n >= 0, "hl_decoder: sparse-row update requested, but no backward pass has run yet");
+    HL_TRY(wait_for_collectives(m));
     total = (size_t)m->union_n;
     HL_CUDA(cudaMemcpyAsync(m->m_sel_all, m->m_union_rows, sizeof(int64_t) * total, cudaMemcpyDeviceToDevice, ctx->stream));
   } else {
-    // one list for all memory blocks: a row chosen by several blocks (or tokens) is updated once
-    // (memory_sparse_adamw_updates, src/memory_transformer.rs:1293-1424)
     for (int l = 0; l < m->cfg.n_layers; ++l) {
       if (!m->lo[l].is_memory) continue;
       HL_CUDA(cudaMemcpyAsync(m->m_sel_all + total, m->ma[l].idx, sizeof(int64_t) * per_layer, cudaMemcpyDeviceToDevice,
@@ -1103,46 +1122,160 @@ int hl_decoder_optimizer_step_sparse_rows(hl_decoder* m) {
       total += per_layer;
     }
   }
-  if (total == 0) { m->step += 1; return HL_OK; }
-  HL_TRY(hl_product_key_split_rows(ctx, m->m_sel_all, m->m_sel_left, m->m_sel_right, (long long)total, m->side));
-  m->step += 1;  // every sparse call advances the step counter (src/nn.rs:2262)
+  if (total > 0) HL_TRY(hl_product_key_split_rows(ctx, m->m_sel_all, m->m_sel_left, m->m_sel_right, (long long)total, m->side));
+  *total_out = total;
+  return HL_OK;
+}
+
+struct SparseTable {
+  size_t offset;
+  const int64_t* rows;
+  const unsigned char* mask;
+  int n_rows, row_dim;
+};
+
+// SMFT: a table row is updated only where its mask allows (memory_sparse_adamw_updates_with_mask,
+// src/memory_transformer.rs:1426-1468)
+void sparse_tables(hl_decoder* m, int which, SparseTable out[3], int* count) {
+  const int half = m->mem.key_dim / 2;
+  int n = 0;
+  if (which & kTableLeft) out[n++] = {m->off_kl, m->m_sel_left, m->smft_on ? m->smft_left_mask : nullptr, m->side, half};
+  if (which & kTableRight) out[n++] = {m->off_kr, m->m_sel_right, m->smft_on ? m->smft_right_mask : nullptr, m->side, half};
+  if (which & kTableValue)
+    out[n++] = {m->off_val, m->m_sel_all, m->smft_on ? m->smft_value_mask : nullptr, m->mem.slots, m->mem.value_dim};
+  *count = n;
+}
+
+// adds the sum of squares of the active rows of the chosen tables to *sum_dev (f64, on the device)
+int sparse_sum_squares(hl_decoder* m, size_t total, int which, double* sum_dev) {
+  SparseTable t[3];
+  int n = 0;
+  sparse_tables(m, which, t, &n);
+  for (int i = 0; i < n; ++i)
+    HL_TRY(hl_sparse_rows_sum_squares_f32(m->ctx, m->grads + t[i].offset, t[i].rows, (long long)total, t[i].mask,
+                                          m->m_row_flags, t[i].n_rows, t[i].row_dim, sum_dev));
+  return HL_OK;
+}
+
+int sparse_adamw(hl_decoder* m, size_t total, int which, const hl_adamw_params& hp) {
+  SparseTable t[3];
+  int n = 0;
+  sparse_tables(m, which, t, &n);
+  for (int i = 0; i < n; ++i)
+    HL_TRY(hl_sparse_adamw_rows_f32(m->ctx, m->params + t[i].offset, m->grads + t[i].offset, m->m + t[i].offset,
+                                    m->v + t[i].offset, t[i].rows, (long long)total, t[i].mask, m->m_row_flags, t[i].n_rows,
+                                    t[i].row_dim, &hp, 0));
+  return HL_OK;
+}
+
+hl_adamw_params step_params(hl_decoder* m, double clip) {
   hl_adamw_params hp{};
   hp.lr = m->opt.lr; hp.beta1 = m->opt.beta1; hp.beta2 = m->opt.beta2; hp.eps = m->opt.eps;
   hp.weight_decay = m->opt.weight_decay;
-  const float inv_world = 1.0f / (float)nccl_world(ctx);  // summed gradients are averaged (src/nn.rs:2100-2117)
-  hp.clip_scale = inv_world;
+  hp.clip_scale = (float)clip * (1.0f / (float)nccl_world(m->ctx));  // summed gradients are averaged (src/nn.rs:2100-2117)
   hp.bias_correction1 = (float)(1.0 - pow((double)m->opt.beta1, (double)m->step));
   hp.bias_correction2 = (float)(1.0 - pow((double)m->opt.beta2, (double)m->step));
-  const int half = m->mem.key_dim / 2;
-  // SMFT: a table row is updated only where its mask allows (memory_sparse_adamw_updates_with_mask,
-  // src/memory_transformer.rs:1426-1468)
-  const unsigned char* mask_l = m->smft_on ? m->smft_left_mask : nullptr;
-  const unsigned char* mask_r = m->smft_on ? m->smft_right_mask : nullptr;
-  const unsigned char* mask_v = m->smft_on ? m->smft_value_mask : nullptr;
+  return hp;
+}
+
+// clip factor from a sum of squares of summed (not yet averaged) gradients
+int clip_from_sum(hl_decoder* m, double sum_sq, const char* what, double* clip) {
+  *clip = 1.0;
+  if (!(sum_sq >= 0.0) || sum_sq > 1e300) return fail(std::string("non-finite or negative ") + what + " sum-of-squares");
+  const double norm = sqrt(sum_sq) / (double)nccl_world(m->ctx);  // norm of the averaged gradient
+  if (norm > (double)m->opt.clip_norm) *clip = (double)m->opt.clip_norm / (norm + 1e-12);
+  return HL_OK;
+}
+
+int step_sparse_rows(hl_decoder* m) {
+  hl_ctx* ctx = m->ctx;
+  size_t total = 0;
+  HL_TRY(gather_selection(m, &total));
+  if (total == 0) { m->step += 1; return HL_OK; }
+  m->step += 1;  // every sparse call advances the step counter (src/nn.rs:2262)
   HL_CUDA(cudaMemsetAsync(m->m_row_flags, 0, (size_t)m->mem.slots, ctx->stream));
+  double clip = 1.0;
   if (m->opt.clip_norm > 0.f) {
     // norm over the active rows of the three tables only (clip_scale_for_sparse_row_updates, src/nn.rs:2667-2774)
-    double* sum_dev = m->norm_dev64;
-    HL_CUDA(cudaMemsetAsync(sum_dev, 0, sizeof(double), ctx->stream));
-    HL_TRY(hl_sparse_rows_sum_squares_f32(ctx, m->grads + m->off_kl, m->m_sel_left, (long long)total, mask_l, m->m_row_flags,
-                                          m->side, half, sum_dev));
-    HL_TRY(hl_sparse_rows_sum_squares_f32(ctx, m->grads + m->off_kr, m->m_sel_right, (long long)total, mask_r, m->m_row_flags,
-                                          m->side, half, sum_dev));
-    HL_TRY(hl_sparse_rows_sum_squares_f32(ctx, m->grads + m->off_val, m->m_sel_all, (long long)total, mask_v, m->m_row_flags,
-                                          m->mem.slots, m->mem.value_dim, sum_dev));
+    HL_CUDA(cudaMemsetAsync(m->norm_dev64, 0, sizeof(double), ctx->stream));
+    HL_TRY(sparse_sum_squares(m, total, kTablesAll, m->norm_dev64));
     double sum_sq = 0.0;
-    HL_TRY(hl_memcpy_d2h(ctx, &sum_sq, sum_dev, sizeof(double)));
-    if (!(sum_sq >= 0.0) || sum_sq > 1e300) return fail("non-finite or negative sparse selected gradient sum-of-squares");
-    const double norm = sqrt(sum_sq) * (double)inv_world;  // norm of the averaged gradient
-    if (norm > (double)m->opt.clip_norm) hp.clip_scale = (float)((double)m->opt.clip_norm / (norm + 1e-12)) * inv_world;
+    HL_TRY(hl_memcpy_d2h(ctx, &sum_sq, m->norm_dev64, sizeof(double)));
+    HL_TRY(clip_from_sum(m, sum_sq, "sparse selected gradient", &clip));
   }
-  HL_TRY(hl_sparse_adamw_rows_f32(ctx, m->params + m->off_kl, m->grads + m->off_kl, m->m + m->off_kl, m->v + m->off_kl,
-                                  m->m_sel_left, (long long)total, mask_l, m->m_row_flags, m->side, half, &hp, 0));
-  HL_TRY(hl_sparse_adamw_rows_f32(ctx, m->params + m->off_kr, m->grads + m->off_kr, m->m + m->off_kr, m->v + m->off_kr,
-                                  m->m_sel_right, (long long)total, mask_r, m->m_row_flags, m->side, half, &hp, 0));
-  return hl_sparse_adamw_rows_f32(ctx, m->params + m->off_val, m->grads + m->off_val, m->m + m->off_val, m->v + m->off_val,
-                                  m->m_sel_all, (long long)total, mask_v, m->m_row_flags, m->mem.slots, m->mem.value_dim, &hp,
-                                  0);
+  return sparse_adamw(m, total, kTablesAll, step_params(m, clip));
+}
+
+// `MemoryOnly` (src/bin/heirloom/runtime.rs:2440-2450; AdamW::step_parameter_indices_mut, src/nn.rs:2222-2254):
+// dense AdamW on the memory tables alone, clip norm over those tables.
+int step_memory_only(hl_decoder* m) {
+  hl_ctx* ctx = m->ctx;
+  HL_TRY(wait_for_collectives(m));
+  const size_t begin = m->off_kl, n = m->tables_end - m->off_kl;
+  double clip = 1.0;
+  if (m->opt.clip_norm > 0.f) {
+    HL_TRY(hl_sum_squares_f32(ctx, m->grads + begin, n, m->norm_dev));
+    float sum = 0.f;
+    HL_TRY(hl_memcpy_d2h(ctx, &sum, m->norm_dev, sizeof(float)));
+    HL_TRY(clip_from_sum(m, (double)sum, "memory table gradient", &clip));
+  }
+  m->step += 1;
+  const hl_adamw_params hp = step_params(m, clip);
+  return adam_plan_step(ctx, m->plan_tables, &hp);
+}
+
+// Dense AdamW everywhere except the value table, row-set AdamW on the value rows the step selected: one step count,
+// one clip factor from the dense gradients plus the active value rows.  The value table (slots x value_dim) is by
+// far the largest parameter and only tokens*top_k of its rows carry a gradient, so this skips both the dense pass
+// over it and the decay of rows nobody read.
+int step_dense_plus_sparse_values(hl_decoder* m) {
+  hl_ctx* ctx = m->ctx;
+  size_t total = 0;
+  HL_TRY(gather_selection(m, &total));  // waits for the collectives under data parallelism
+  HL_CUDA(cudaMemsetAsync(m->m_row_flags, 0, (size_t)m->mem.slots, ctx->stream));
+  double clip = 1.0;
+  if (m->opt.clip_norm > 0.f) {
+    const size_t tail = m->tables_end, tail_n = m->arena - m->tables_end;
+    HL_TRY(hl_sum_squares_f32(ctx, m->grads, m->off_val, m->norm_dev));
+    HL_TRY(hl_sum_squares_f32(ctx, m->grads + tail, tail_n, m->norm_dev + 1));
+    HL_CUDA(cudaMemsetAsync(m->norm_dev64, 0, sizeof(double), ctx->stream));
+    if (total > 0) HL_TRY(sparse_sum_squares(m, total, kTableValue, m->norm_dev64));
+    float dense[2] = {0.f, 0.f};
+    double rows = 0.0;
+    HL_TRY(hl_memcpy_d2h(ctx, dense, m->norm_dev, sizeof(dense)));
+    HL_TRY(hl_memcpy_d2h(ctx, &rows, m->norm_dev64, sizeof(double)));
+    HL_TRY(clip_from_sum(m, (double)dense[0] + (double)dense[1] + rows, "gradient", &clip));
+  }
+  m->step += 1;
+  const hl_adamw_params hp = step_params(m, clip);
+  HL_TRY(adam_plan_step(ctx, m->plan_no_values, &hp));
+  if (total > 0) HL_TRY(sparse_adamw(m, total, kTableValue, hp));
+  return HL_OK;
+}
+
+}  // namespace
+}  // namespace hl
+
+int hl_decoder_optimizer_step_sparse_rows(hl_decoder* m) {
+  return hl_decoder_optimizer_step_policy(m, HL_MEMORY_UPDATE_SPARSE_ROWS);
+}
+
+int hl_decoder_optimizer_step_policy(hl_decoder* m, int policy) {
+  HL_REQUIRE(m, "hl_decoder_optimizer_step_policy: null model");
+  if (policy == HL_MEMORY_UPDATE_FROZEN) return HL_OK;  // no optimizer step at all (runtime.rs:2421-2423)
+  HL_REQUIRE(m->has_opt, "hl_decoder: no optimizer configured (call hl_decoder_set_optimizer)");
+  if (policy == HL_MEMORY_UPDATE_FULL) return hl_decoder_optimizer_step(m);
+  HL_REQUIRE(m->has_memory, "hl_decoder_optimizer_step_policy: the model has no memory layers");
+  const unsigned long long before = m->ctx->counters.launches;
+  int rc;
+  switch (policy) {
+    case HL_MEMORY_UPDATE_MEMORY_ONLY: rc = hl::step_memory_only(m); break;
+    case HL_MEMORY_UPDATE_SPARSE_ROWS: rc = hl::step_sparse_rows(m); break;
+    case HL_MEMORY_UPDATE_DENSE_PLUS_SPARSE_VALUES: rc = hl::step_dense_plus_sparse_values(m); break;
+    default: return hl::fail("hl_decoder_optimizer_step_policy: unknown policy " + std::to_string(policy));
+  }
+  m->launches_last_step += m->ctx->counters.launches - before;
+  return rc;
 }
 
 int hl_decoder_memory_access_counts(hl_decoder* m, unsigned long long* counts_dev) {

@@ -32,6 +32,9 @@ def _dt(t: torch.Tensor) -> int:
     return _DT[t.dtype]
 
 
+_OPEN_STREAMS = set()  # raw handles of the compute streams of the contexts that are open
+
+
 class Context:
     """One compute stream + one collective stream on one device (`hl_ctx`)."""
 
@@ -45,10 +48,20 @@ class Context:
         self.stream = torch.cuda.ExternalStream(self.lib.hl_ctx_stream(self.handle), device=self.torch_device)
         # torch allocations, copies and fills issued by this thread now share the compute stream,
         # so buffers handed to the library are always ordered with the kernels that use them.
+        self._previous_stream = torch.cuda.current_stream(self.torch_device)
         torch.cuda.set_stream(self.stream)
+        _OPEN_STREAMS.add(self.stream.cuda_stream)
 
     def close(self) -> None:
         if self.handle:
+            # torch must not be left pointing at a stream that is about to be destroyed: hand it back the stream
+            # that was current before this context (if that one still exists), else the device's default stream
+            _OPEN_STREAMS.discard(self.stream.cuda_stream)
+            if torch.cuda.current_stream(self.torch_device).cuda_stream == self.stream.cuda_stream:
+                previous = self._previous_stream
+                default = torch.cuda.default_stream(self.torch_device)
+                alive = previous.cuda_stream in _OPEN_STREAMS or previous.cuda_stream == default.cuda_stream
+                torch.cuda.set_stream(previous if alive else default)
             self.lib.hl_ctx_destroy(self.handle)
             self.handle = None
 

@@ -1,6 +1,8 @@
 """Throughput of the memory-transformer training step on one GPU, one JSON line.
 
-    python -m heirloom_b200.memory_bench [--steps 10] [--warmup 3] [--policy full|sparse_rows]
+    python -m heirloom_b200.memory_bench [--steps 10] [--warmup 3] [--policy full|memory_only|sparse_rows|dense_plus_sparse_values]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P \
+        -m heirloom_b200.memory_bench --gpus N ...          (one rank per GPU, batch 32 per GPU: weak scaling)
 
 Model: vocab 32000, d_model 512, 8 layers, 8 heads, MLP 2048, context 512, batch 32; product-key
 memory feed-forward in blocks 4 and 6 (2 x 512 half keys of dimension 256 = 262,144 slots, value
@@ -8,7 +10,9 @@ dimension 512, top-k 32, one memory head, one shared table set); bf16 compute wi
 weights and AdamW state; Zipf(1.1) token ids from a seed; weights N(0, 0.02), half keys
 N(0, 1/sqrt(256)).  `full` runs the dense coupled AdamW over every parameter including the tables
 (the reference's `Full` policy); `sparse_rows` runs the row-set AdamW over the selected rows of the
-three tables only (its `SparseRows` policy).  Times come from CUDA events on the library's compute
+three tables only (its `SparseRows` policy); `memory_only` the dense AdamW over the tables alone;
+`dense_plus_sparse_values` the dense AdamW over everything but the value table plus the row-set AdamW over
+the selected value rows.  Times come from CUDA events on the library's compute
 stream, per-kernel-family times from the library's event profile.
 """
 from __future__ import annotations
@@ -17,6 +21,7 @@ import argparse
 import ctypes
 import json
 import math
+import os
 import sys
 from pathlib import Path
 
@@ -52,7 +57,7 @@ def init_weights(model, seed: int) -> None:
             state[name] = np.zeros(shape, np.float32)
         elif ".ln" in name or name.startswith("ln_f"):
             state[name] = np.ones(shape, np.float32)
-        elif "left_keys" in name or "right_keys" in name:
+        elif name.endswith("product_key_left") or name.endswith("product_key_right"):
             state[name] = rng.standard_normal(shape, dtype=np.float32) / np.float32(math.sqrt(shape[-1]))
         else:
             w = rng.standard_normal(shape, dtype=np.float32) * np.float32(0.02)
@@ -66,13 +71,32 @@ def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--policy", default="full", choices=["full", "sparse_rows"])
+    ap.add_argument("--policy", default="full", choices=["full", "memory_only", "sparse_rows", "dense_plus_sparse_values"])
+    ap.add_argument("--gpus", type=int, default=1)
     args = ap.parse_args()
-    ctx = cuda.Context(0)
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torchrun --nproc-per-node {args.gpus}")
+    torch.cuda.set_device(local_rank)
+    ctx = cuda.Context(local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("gloo", rank=rank, world_size=world)
+        ident = (ctypes.c_uint8 * 128)()
+        if rank == 0:
+            cuda.check(ctx.lib.hl_nccl_unique_id(ident))
+        obj = [bytes(ident)]
+        dist.broadcast_object_list(obj, src=0)
+        ident = (ctypes.c_uint8 * 128).from_buffer_copy(obj[0])
+        cuda.check(ctx.lib.hl_nccl_init(ctx.handle, rank, world, ident))
     model = nn.DecoderLm(ctx, nn.DecoderConfig(batch=BATCH, **CFG), nn.MemoryConfig(**MEM))
-    init_weights(model, 0)
+    init_weights(model, 0)  # the same initial weights on every rank
     model.set_optimizer(lr=1e-3, beta1=0.9, beta2=0.999, eps=1e-8, weight_decay=0.01, clip_norm=None)
-    rng = np.random.default_rng(1000)
+    rng = np.random.default_rng(1000 + rank)  # a distinct token stream per rank
     ranks = np.arange(1, CFG["vocab"] + 1, dtype=np.float64)
     cdf = np.cumsum(ranks ** -1.1)
     cdf /= cdf[-1]
@@ -81,24 +105,33 @@ def main() -> None:
         tok = np.minimum(np.searchsorted(cdf, rng.random((BATCH, CFG["context"] + 1)), side="right"), CFG["vocab"] - 1)
         pool.append((torch.from_numpy(tok[:, :-1].copy()).cuda(), torch.from_numpy(tok[:, 1:].copy()).cuda()))
 
+    def barrier():
+        ctx.sync()
+        if dist is not None:
+            dist.barrier()
+
     def step(i):
         x, y = pool[i % len(pool)]
         if args.policy == "full":
             model.train_step_device(x, y)
         else:
             model.forward_backward(x, y)
-            model.optimizer_step_sparse_rows()
+            model.optimizer_step_policy(args.policy)
 
     for i in range(args.warmup):
         step(i)
-    ctx.sync()
+    barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record(ctx.stream)
     for i in range(args.steps):
         step(i)
     e1.record(ctx.stream)
-    ctx.sync()
+    barrier()
     ms = e0.elapsed_time(e1) / args.steps
+    if dist is not None:  # the slowest rank sets the step time
+        t = torch.tensor([ms], dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
     loss = model.loss()
     cuda.check(ctx.lib.hl_profile_enable(ctx.handle, 1))
     prof_steps = min(args.steps, 3)
@@ -108,19 +141,27 @@ def main() -> None:
     p = Profile()
     cuda.check(ctx.lib.hl_profile_read(ctx.handle, ctypes.byref(p)))
     cuda.check(ctx.lib.hl_profile_enable(ctx.handle, 0))
+    barrier()
+    model.close()
+    if dist is not None:
+        cuda.check(ctx.lib.hl_nccl_destroy(ctx.handle))
+        dist.destroy_process_group()
+    if rank != 0:
+        return
     names = ["gemm", "attention_fwd", "attention_bwd", "layer_norm", "loss", "optimizer", "bias_grad", "embedding", "other"]
-    tokens = BATCH * CFG["context"]
+    tokens = BATCH * CFG["context"] * world
     value = tokens / (ms * 1e-3)
     peaks_path = ROOT / "MEASURED_PEAKS.json"
     burst = json.loads(peaks_path.read_text())["bf16_tflops"] if peaks_path.exists() else 1590.0
     print(json.dumps({
-        "metric": "train tokens/s (memory transformer bf16 step)", "value": value, "unit": "tokens/s", "n_gpus": 1,
+        "metric": "train tokens/s (memory transformer bf16 step)", "value": value, "unit": "tokens/s", "n_gpus": world, "scaling": "weak",
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "policy": args.policy, "loss_after": loss,
         "config": {"workload": "memory transformer: vocab 32000, d 512, 8 layers, 8 heads, MLP 2048, context 512, batch 32, "
                                "product-key memory in blocks 4 and 6 (262,144 slots, value dim 512, top-k 32)",
                    "tokens_per_step": tokens, "parameters": sum(int(np.prod(s)) for s in model.parameter_shapes().values())},
-        "mfu_dense_part": {"flops_per_token": flops_per_token(), "vs_measured_burst": value * flops_per_token() / (burst * 1e12),
-                           "vs_datasheet_2250_tflops": value * flops_per_token() / 2250e12},
+        "mfu_dense_part": {"flops_per_token": flops_per_token(),
+                           "vs_measured_burst": value * flops_per_token() / (burst * 1e12 * world),
+                           "vs_datasheet_2250_tflops": value * flops_per_token() / (2250e12 * world)},
         "kernel_breakdown_ms_per_step": {n: round(p.ms[i] / prof_steps, 4) for i, n in enumerate(names)},
         "data": "synthetic"}))
     model.close()

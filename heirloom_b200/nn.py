@@ -182,6 +182,17 @@ class DecoderLm:
         forward, no dense update in this call."""
         check(self._lib.hl_decoder_optimizer_step_sparse_rows(self.handle))
 
+    POLICIES = {"full": 0, "memory_only": 1, "sparse_rows": 2, "frozen": 3, "dense_plus_sparse_values": 4}
+
+    def optimizer_step_policy(self, policy: str) -> None:
+        """The optimizer step under a memory update policy: the reference's `full`, `memory_only`, `sparse_rows`,
+        `frozen` (`MemoryUpdatePolicy`, src/memory_transformer.rs:26-32; runtime.rs:2416-2452), or
+        `dense_plus_sparse_values` (dense AdamW on everything but the value table, row-set AdamW on the value rows
+        the step selected)."""
+        if policy not in self.POLICIES:
+            raise HeirloomError(f"unknown memory update policy {policy!r}; expected one of {sorted(self.POLICIES)}")
+        check(self._lib.hl_decoder_optimizer_step_policy(self.handle, c_int(self.POLICIES[policy])))
+
     def eval_loss_device(self, tokens: torch.Tensor, targets: torch.Tensor) -> float:
         """Forward-only mean cross-entropy over int64 CUDA tensors `[sequences, context]`, sequences <= batch."""
         if tokens.dim() != 2 or tokens.shape[1] != self.cfg.context or tokens.shape != targets.shape:

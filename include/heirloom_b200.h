@@ -413,6 +413,25 @@ int hl_memory_decoder_create(hl_ctx* ctx, const hl_decoder_config* cfg, const hl
  * rows only; under data parallelism the rows are the union over the ranks.  When SMFT masks are set
  * (below), a row is updated only where its table's mask is non-zero. */
 int hl_decoder_optimizer_step_sparse_rows(hl_decoder* model);
+/* The optimizer step under one of the reference's memory update policies (`MemoryUpdatePolicy`,
+ * src/memory_transformer.rs:26-32; dispatch `step_memory_optimizer`, src/bin/heirloom/runtime.rs:2416-2452):
+ *   FULL         dense AdamW on every parameter (= hl_decoder_optimizer_step)
+ *   MEMORY_ONLY  dense AdamW on the memory tables alone, clip norm over those tables
+ *                (AdamW::step_parameter_indices_mut, src/nn.rs:2222-2254)
+ *   SPARSE_ROWS  = hl_decoder_optimizer_step_sparse_rows
+ *   FROZEN       nothing is updated and the step counter stays
+ * and one policy the reference does not have:
+ *   DENSE_PLUS_SPARSE_VALUES  dense AdamW on everything except the value table, row-set AdamW on the
+ *                value rows the step selected (SMFT value mask honoured), one step count, one clip
+ *                factor over the dense gradients plus the active value rows. */
+enum {
+  HL_MEMORY_UPDATE_FULL = 0,
+  HL_MEMORY_UPDATE_MEMORY_ONLY = 1,
+  HL_MEMORY_UPDATE_SPARSE_ROWS = 2,
+  HL_MEMORY_UPDATE_FROZEN = 3,
+  HL_MEMORY_UPDATE_DENSE_PLUS_SPARSE_VALUES = 4
+};
+int hl_decoder_optimizer_step_policy(hl_decoder* model, int policy);
 /* SMFT (sparse memory fine-tuning) support.
  *   hl_memory_access_count_rows_i64_u64: counts[r] += occurrences of r in selected_rows, 64-bit atomic
  *     adds; counts is caller-owned device memory [slots] (zero it for a fresh histogram); a row outside

@@ -164,3 +164,70 @@ def test_sparse_rows_policy_clips_by_the_norm_of_the_active_rows_only():
     want_m = 0.1 * (ograds["shared_memory.value"][rows] * scale + 0.01 * params["shared_memory.value"][rows])
     assert np.abs(m_got[rows] - want_m).max() <= 1e-6 + 1e-3 * np.abs(want_m).max()
     model.close()
+
+
+def test_memory_only_policy_updates_the_tables_and_nothing_else():
+    """`MemoryOnly`: dense AdamW over the three tables, the clip norm taken over them alone
+    (AdamW::step_parameter_indices_mut, src/nn.rs:2222-2254)."""
+    from heirloom_b200 import nn
+    model, ocfg, omem, params = build(nn.PRECISION_F32, 2, seed=3)
+    rng = np.random.default_rng(13)
+    tok = ho.zipf_tokens(rng, ocfg.vocab, (2, 129))
+    x, y = tok[:, :-1].copy(), tok[:, 1:].copy()
+    _, ograds, _ = ho.memory_decoder_loss_and_grads(ocfg, omem, params, x, y, return_indices=True)
+    names = ("shared_memory.product_key_left", "shared_memory.product_key_right", "shared_memory.value")
+    norm = np.sqrt(sum(float((ograds[n].astype(np.float64) ** 2).sum()) for n in names))
+    clip_norm = 0.5 * norm
+    scale = clip_norm / (norm + 1e-12)
+    model.set_optimizer(lr=1e-2, weight_decay=0.01, clip_norm=clip_norm)
+    model.forward_backward(torch.tensor(x, device="cuda"), torch.tensor(y, device="cuda"))
+    model.optimizer_step_policy("memory_only")
+    assert model.optimizer_steps == 1
+    for name in names:
+        p = params[name]
+        state = ho.AdamWState(lr=1e-2, weight_decay=0.01)
+        every_row = np.arange(p.shape[0])
+        want = ho.adamw_sparse_rows_step(p, ograds[name], np.zeros_like(p), np.zeros_like(p), every_row, state, clip=scale)
+        got = model.parameter(name).astype(np.float64)
+        assert np.abs(got - want).max() <= 2e-4
+        assert np.abs(got - p).max() > 1e-3
+    for name in ("lm_head.weight", "block.1.feed_forward.memory.query_proj.weight", "token_embedding.weight", "ln_f.weight"):
+        assert np.array_equal(model.parameter(name).astype(np.float64), params[name])
+    model.optimizer_step_policy("frozen")
+    assert model.optimizer_steps == 1
+    from heirloom_b200._lib import HeirloomError
+    with pytest.raises(HeirloomError, match="unknown memory update policy"):
+        model.optimizer_step_policy("everything")
+    model.close()
+
+
+def test_dense_plus_sparse_values_policy():
+    """Dense AdamW on all parameters but the value table, row-set AdamW on the selected value rows, one step count
+    and one clip factor over the dense gradients plus the active value rows."""
+    from heirloom_b200 import nn
+    model, ocfg, omem, params = build(nn.PRECISION_F32, 2, seed=3)
+    rng = np.random.default_rng(13)
+    tok = ho.zipf_tokens(rng, ocfg.vocab, (2, 129))
+    x, y = tok[:, :-1].copy(), tok[:, 1:].copy()
+    _, ograds, oidx = ho.memory_decoder_loss_and_grads(ocfg, omem, params, x, y, return_indices=True)
+    selected = np.unique(np.concatenate([oidx[l].reshape(-1) for l in MEM["memory_layers"]]))
+    sum_sq = sum(float((g.astype(np.float64) ** 2).sum()) for n, g in ograds.items() if n != "shared_memory.value")
+    sum_sq += float((ograds["shared_memory.value"][selected].astype(np.float64) ** 2).sum())
+    norm = np.sqrt(sum_sq)
+    clip_norm = 0.5 * norm
+    scale = clip_norm / (norm + 1e-12)
+    model.set_optimizer(lr=1e-2, weight_decay=0.01, clip_norm=clip_norm)
+    model.forward_backward(torch.tensor(x, device="cuda"), torch.tensor(y, device="cuda"))
+    model.optimizer_step_policy("dense_plus_sparse_values")
+    assert model.optimizer_steps == 1
+    for name, p in params.items():
+        state = ho.AdamWState(lr=1e-2, weight_decay=0.01)
+        rows = selected if name == "shared_memory.value" else np.arange(p.shape[0])
+        p2 = p.reshape(p.shape[0], -1)
+        g2 = ograds[name].reshape(p2.shape)
+        want = ho.adamw_sparse_rows_step(p2, g2, np.zeros_like(p2), np.zeros_like(p2), rows, state, clip=scale)
+        got = model.parameter(name).astype(np.float64).reshape(p2.shape)
+        active = np.zeros(p2.shape[0], bool); active[rows] = True
+        assert np.array_equal(got[~active], p2[~active]), name
+        assert np.abs(got[active] - want[active]).max() <= 2e-4, name
+    model.close()

@@ -303,3 +303,21 @@ def test_attention_f32_golden_and_random(golden):
     dq, dk, dv = cuda.causal_attention_f32_backward(c, dev(q), dev(k), dev(v), p, dev(go), H)
     for name, got, want in zip("qkv", (dq, dk, dv), ho.causal_attention_backward(q, k, v, H, go, probs=po)):
         assert_close("attn d" + name, host(got), want, atol=1e-5, rtol=1e-4)
+
+
+def test_closing_a_second_context_leaves_torch_and_the_first_context_usable():
+    """A context makes its compute stream torch's current stream; closing it must hand torch a live stream back."""
+    from heirloom_b200 import cuda
+    first = ctx()
+    second = cuda.Context(0)
+    x = torch.arange(8, dtype=torch.float32, device="cuda")
+    flags = cuda.mark_rows(second, torch.tensor([1, 3], device="cuda"), 4)
+    second.sync()
+    assert flags.cpu().tolist() == [0, 1, 0, 1]
+    second.close()
+    y = (x * 2).sum()                     # torch keeps working
+    assert float(y) == 56.0
+    flags = cuda.mark_rows(first, torch.tensor([0], device="cuda"), 4)
+    first.sync()
+    assert flags.cpu().tolist() == [1, 0, 0, 0]
+    assert torch.cuda.current_stream().cuda_stream == first.stream.cuda_stream

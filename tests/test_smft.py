@@ -105,7 +105,8 @@ gpu = pytest.mark.gpu
 def test_device_access_counts_equal_a_host_histogram():
     import torch
     from heirloom_b200 import cuda
-    c = cuda.Context(0)
+    from tests.gpu_util import ctx
+    c = ctx()
     rng = np.random.default_rng(9)
     for slots, n in ((12, 24), (4096, 100_000), (262_144, 1_048_576)):
         rows = (rng.zipf(1.2, n) % slots).astype(np.int64)
@@ -125,7 +126,8 @@ def test_masked_sparse_adamw_rows_known_answer():
     # the reference's cuda_sparse_adamw_rows_respects_smft_row_mask (tests/memory_transformer.rs:1325-1353)
     import torch
     from heirloom_b200 import cuda
-    c = cuda.Context(0)
+    from tests.gpu_util import ctx
+    c = ctx()
     p = torch.tensor([[1.0, 2.0, 0, 0], [3.0, 4.0, 0, 0], [5.0, 6.0, 0, 0]], device="cuda")
     g = torch.tensor([[1.0, -2.0, 0, 0], [3.0, -4.0, 0, 0], [0.5, -0.25, 0, 0]], device="cuda")
     m, v = torch.zeros_like(p), torch.zeros_like(p)
@@ -140,7 +142,7 @@ def test_masked_sparse_adamw_rows_known_answer():
 def test_model_counts_report_and_masked_sparse_step():
     import torch
     from heirloom_b200 import nn
-    from test_gpu_memory_decoder import MEM, build
+    from tests.test_gpu_memory_decoder import MEM, build
     model, ocfg, omem, params = build(nn.PRECISION_F32, 2, seed=3)
     model.set_optimizer(lr=1e-2, weight_decay=0.01)
     rng = np.random.default_rng(13)
