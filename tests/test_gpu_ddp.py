@@ -115,11 +115,9 @@ model.forward_backward(x, y)
 np.save(prefix + f".grad{rank}.npy", model.grad("shared_memory.value"))
 np.save(prefix + f".gradq{rank}.npy", model.grad("block.1.feed_forward.memory.query_proj.weight"))
 np.save(prefix + f".idx{rank}.npy", model.selected_indices(1))
-if sys.argv[6] == "sparse_rows":
-    model.optimizer_step_sparse_rows()
-else:
-    model.optimizer_step()
+model.optimizer_step_policy(sys.argv[6])
 np.save(prefix + f".value{rank}.npy", model.parameter("shared_memory.value"))
+np.save(prefix + f".query{rank}.npy", model.parameter("block.1.feed_forward.memory.query_proj.weight"))
 np.save(prefix + f".left{rank}.npy", model.parameter("shared_memory.product_key_left"))
 model.close()
 cuda.check(ctx.lib.hl_nccl_destroy(ctx.handle))
@@ -128,7 +126,7 @@ print("DONE")
 """
 
 
-@pytest.mark.parametrize("policy", ["full", "sparse_rows"])
+@pytest.mark.parametrize("policy", ["full", "sparse_rows", "dense_plus_sparse_values", "memory_only"])
 def test_memory_model_exchanges_the_union_of_selected_value_rows(tmp_path, policy):
     if not torch.cuda.is_available() or torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
@@ -169,7 +167,11 @@ def test_memory_model_exchanges_the_union_of_selected_value_rows(tmp_path, polic
     v = [np.load(prefix + f".value{r}.npy") for r in range(world)]
     assert np.array_equal(v[0], v[1]) and np.array_equal(np.load(prefix + ".left0.npy"), np.load(prefix + ".left1.npy"))
     moved = np.any(v[0] != params["shared_memory.value"].astype(np.float32), axis=1)
-    if policy == "sparse_rows":
+    if policy in ("sparse_rows", "dense_plus_sparse_values"):
         assert np.array_equal(np.flatnonzero(moved), union)  # exactly the union's rows were updated, on both ranks
     else:
         assert moved[union].all()
+    q = [np.load(prefix + f".query{r}.npy") for r in range(world)]
+    assert np.array_equal(q[0], q[1])
+    dense_moved = np.any(q[0] != params["block.1.feed_forward.memory.query_proj.weight"].astype(np.float32))
+    assert dense_moved == (policy in ("full", "dense_plus_sparse_values"))  # the table-only policies leave dense weights alone
