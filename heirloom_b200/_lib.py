@@ -63,6 +63,8 @@ def load() -> ctypes.CDLL:
         _lib.hl_buffer_ptr.argtypes = [c_void_p]
         _lib.hl_buffer_bytes.restype = c_size_t
         _lib.hl_buffer_bytes.argtypes = [c_void_p]
+        _lib.hl_adamw_plan_destroy.restype = None
+        _lib.hl_adamw_plan_destroy.argtypes = [c_void_p]
         _lib.hl_ctx_destroy.restype = None
         _lib.hl_ctx_destroy.argtypes = [c_void_p]
     return _lib

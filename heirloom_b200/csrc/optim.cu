@@ -183,4 +183,20 @@ int hl_adamw_multi(hl_ctx* ctx, const hl_adamw_tensor* tensors_host, int count, 
   return rc;
 }
 
+int hl_adamw_plan_create(hl_ctx* ctx, const hl_adamw_tensor* tensors_host, int count, hl_adamw_plan** out) {
+  HL_REQUIRE(out, "hl_adamw_plan_create: null output pointer");
+  *out = nullptr;
+  AdamPlan* plan = nullptr;
+  int rc = adam_plan_create(ctx, tensors_host, count, &plan);
+  if (rc == HL_OK) *out = reinterpret_cast<hl_adamw_plan*>(plan);
+  return rc;
+}
+
+int hl_adamw_plan_step(hl_ctx* ctx, hl_adamw_plan* plan, const hl_adamw_params* hp) {
+  HL_REQUIRE(ctx && plan, "hl_adamw_plan_step: null argument");
+  return adam_plan_step(ctx, reinterpret_cast<AdamPlan*>(plan), hp);
+}
+
+void hl_adamw_plan_destroy(hl_adamw_plan* plan) { adam_plan_destroy(reinterpret_cast<AdamPlan*>(plan)); }
+
 }  // extern "C"

@@ -247,6 +247,36 @@ def adamw_update_multi(ctx: Context, params, grads, ms, vs, hp: AdamWParams, sha
     check(ctx.lib.hl_adamw_multi(ctx.handle, arr, c_int(len(params)), byref(hp)))
 
 
+class AdamWPlan:
+    """The tensor table of `adamw_update_multi`, built once and stepped every iteration (`hl_adamw_plan_*`)."""
+
+    def __init__(self, ctx: Context, params, grads, ms, vs, shadows=None):
+        self.ctx = ctx
+        self._keep = (params, grads, ms, vs, shadows)  # the plan holds raw pointers
+        arr = (AdamWTensor * len(params))()
+        for i, (p, g, m, v) in enumerate(zip(params, grads, ms, vs)):
+            arr[i] = AdamWTensor(p.data_ptr(), g.data_ptr(), m.data_ptr(), v.data_ptr(),
+                                 shadows[i].data_ptr() if shadows is not None else 0, p.numel())
+        h = c_void_p()
+        check(ctx.lib.hl_adamw_plan_create(ctx.handle, arr, c_int(len(params)), byref(h)))
+        self.handle = h
+
+    def step(self, hp: AdamWParams) -> None:
+        check(self.ctx.lib.hl_adamw_plan_step(self.ctx.handle, self.handle, byref(hp)))
+
+    def close(self) -> None:
+        if self.handle:
+            self.ctx.sync()
+            self.ctx.lib.hl_adamw_plan_destroy(self.handle)
+            self.handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
 # ---- matmul ------------------------------------------------------------------------------------------
 def _layout(t: torch.Tensor) -> MatrixLayout:
     return MatrixLayout(t.shape[0], t.shape[1], t.stride(0), t.stride(1), 0)

@@ -6,9 +6,9 @@
     python -m heirloom_b200.kernel_bench --only gemm --split-k 1   # GEMMs without the even deal of the last wave
 
 Cases: the bf16 GEMM shapes of the GPT-124M-shaped step (forward, input gradient, weight gradient),
-causal attention forward/backward (batch 16, 12 heads, head_dim 64, T 1024), layer norm and GELU
-over 16384 x 768 / 16384 x 3072, fused cross-entropy over 16384 x 50304, bias column sums, the fused
-AdamW over 124 M parameters, and the product-key memory layer's kernels at 16384 tokens, 2 x 512 half
+causal attention forward/backward (12 heads, head_dim 64; batch 16 x T 1024 and batch 4 x T 4096), layer norm and
+GELU over 16384 x 768 / 16384 x 3072, fused cross-entropy over 16384 x 50304, bias column sums, the fused
+AdamW over 124 M and 1.3 G parameters, and the product-key memory layer's kernels at 16384 tokens, 2 x 512 half
 keys, 262,144 slots, top-k 32.  Inputs are N(0,1) from torch's generator with seed 0.
 Each case reports time from CUDA events on the library's compute stream, the algorithmic work
 (flop or bytes) and the fraction of the measured peak (MEASURED_PEAKS.json when present).
@@ -103,6 +103,33 @@ def build_cases(ctx):
         do = bf16(N, D)
         return (lambda: cuda.flash_attention_backward(ctx, q, k, v, out, do, lse, B, T, H)), 5.0 * B * H * T * T * 64, "flop"
 
+    def attn_long(backward):
+        # the sweep's long-sequence point: batch 16 x T 4096 would be 64 Ki tokens; batch 4 keeps the token count
+        # (and the qkv buffer) of the step, the work per (batch, head) is what changes
+        b4, t4 = 4, 4096
+        def make():
+            qkv = bf16(b4 * t4, 3 * D)
+            q, k, v = qkv[:, :D], qkv[:, D:2 * D], qkv[:, 2 * D:]
+            if not backward:
+                return (lambda: cuda.flash_attention_forward(ctx, q, k, v, b4, t4, H)), 2.0 * b4 * H * t4 * t4 * 64, "flop"
+            out, lse = cuda.flash_attention_forward(ctx, q, k, v, b4, t4, H)
+            do = bf16(b4 * t4, D)
+            return (lambda: cuda.flash_attention_backward(ctx, q, k, v, out, do, lse, b4, t4, H)), \
+                5.0 * b4 * H * t4 * t4 * 64, "flop"
+        return make
+
+    def ln_wide_fwd():
+        x, w, b = bf16(N, F), torch.ones(F, device="cuda"), torch.zeros(F, device="cuda")
+        return (lambda: cuda.layer_norm_forward(ctx, x, w, b)), N * F * 4.0, "bytes"
+
+    def adamw_big():
+        n = 1_300_000_000
+        p, g_, m, v = (torch.empty(n, device="cuda").normal_() for _ in range(4))
+        v.abs_()
+        hp = cuda.adamw_params(1e-3, 0.9, 0.999, 1e-8, 0.01, 1.0, 1)
+        plan = cuda.AdamWPlan(ctx, [p], [g_], [m], [v])  # built once, as an optimizer does
+        return (lambda: plan.step(hp)), n * 28.0, "bytes"
+
     def ln_fwd():
         x, w, b = bf16(N, D), torch.ones(D, device="cuda"), torch.zeros(D, device="cuda")
         return (lambda: cuda.layer_norm_forward(ctx, x, w, b)), N * D * 4.0, "bytes"
@@ -132,7 +159,8 @@ def build_cases(ctx):
         p, g_, m, v = (torch.randn(n, device="cuda") for _ in range(4))
         v.abs_()
         hp = cuda.adamw_params(1e-3, 0.9, 0.999, 1e-8, 0.01, 1.0, 1)
-        return (lambda: cuda.adamw_update_multi(ctx, [p], [g_], [m], [v], hp)), n * 28.0, "bytes"
+        plan = cuda.AdamWPlan(ctx, [p], [g_], [m], [v])  # built once, as an optimizer does
+        return (lambda: plan.step(hp)), n * 28.0, "bytes"
 
     # product-key memory layer at the memory-transformer sizes: 16384 tokens, 2 x 512 half keys of dimension 256,
     # 262,144 slots, value dimension 512, top-k 32 (beam 32)
@@ -187,7 +215,8 @@ def build_cases(ctx):
                  memory_weighted_value_bwd=mem_value_bwd)
     cases.update(attention_fwd_t1024=attn_fwd, attention_bwd_t1024=attn_bwd, layer_norm_fwd=ln_fwd, layer_norm_bwd=ln_bwd,
                  gelu_fwd_16384x3072=gelu_fwd, cross_entropy_16384x50304=ce, bias_colsum_16384x50304=colsum,
-                 adamw_124m=adamw)
+                 adamw_124m=adamw, attention_fwd_t4096=attn_long(False), attention_bwd_t4096=attn_long(True),
+                 layer_norm_fwd_16384x3072=ln_wide_fwd, adamw_1300m=adamw_big)
     return cases
 
 

@@ -181,6 +181,13 @@ typedef struct {
   uint64_t n;
 } hl_adamw_tensor;
 int hl_adamw_multi(hl_ctx* ctx, const hl_adamw_tensor* tensors_host, int count, const hl_adamw_params* hp);
+/* The same update with the tensor table built once: an optimizer owns a plan for its parameter set and
+ * steps it every iteration with that iteration's hyper-parameters (hl_adamw_multi builds and frees a table
+ * on every call, which costs a device allocation).  The plan keeps pointers, not data. */
+typedef struct hl_adamw_plan hl_adamw_plan;
+int hl_adamw_plan_create(hl_ctx* ctx, const hl_adamw_tensor* tensors_host, int count, hl_adamw_plan** out);
+int hl_adamw_plan_step(hl_ctx* ctx, hl_adamw_plan* plan, const hl_adamw_params* hp);
+void hl_adamw_plan_destroy(hl_adamw_plan* plan);
 
 /* ---- GEMM ----------------------------------------------------------------------------------
  * f32 strided matmul with f64 accumulation: out[i,j] = sum_k A[i,k]*B[k,j] with arbitrary

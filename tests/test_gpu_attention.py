@@ -20,7 +20,7 @@ def reference_lse(q, k, n_heads):
     return m + np.log(np.exp(s - m[..., None]).sum(-1))
 
 
-@pytest.mark.parametrize("B,T,H", [(1, 128, 1), (2, 256, 3), (1, 200, 2), (2, 1024, 2), (1, 72, 4)])
+@pytest.mark.parametrize("B,T,H", [(1, 128, 1), (2, 256, 3), (1, 200, 2), (2, 1024, 2), (1, 72, 4), (1, 4096, 1), (1, 2100, 2)])
 def test_flash_forward_matches_oracle(B, T, H):
     from heirloom_b200 import cuda
     c = ctx()
@@ -47,7 +47,7 @@ def test_flash_forward_rejects_unsupported_shapes():
         cuda.flash_attention_forward(c, x, x, x, 1, 128, 3)
 
 
-@pytest.mark.parametrize("B,T,H", [(1, 128, 1), (2, 256, 2), (1, 200, 2), (1, 1024, 2), (2, 72, 3)])
+@pytest.mark.parametrize("B,T,H", [(1, 128, 1), (2, 256, 2), (1, 200, 2), (1, 1024, 2), (2, 72, 3), (1, 4096, 1), (1, 2100, 2)])
 def test_flash_backward_matches_oracle(B, T, H):
     from heirloom_b200 import cuda
     c = ctx()

@@ -321,3 +321,25 @@ def test_closing_a_second_context_leaves_torch_and_the_first_context_usable():
     first.sync()
     assert flags.cpu().tolist() == [1, 0, 0, 0]
     assert torch.cuda.current_stream().cuda_stream == first.stream.cuda_stream
+
+
+def test_adamw_plan_steps_like_the_multi_tensor_call():
+    """A plan built once and stepped three times gives the bits of three `adamw_update_multi` calls."""
+    from heirloom_b200 import cuda
+    c = ctx()
+    rng = np.random.default_rng(16)
+    sizes = [3, 4096, 50001]
+    make = lambda: [dev(rng.standard_normal(n).astype(np.float32)) for n in sizes]
+    ps, gs = make(), make()
+    ps2 = [p.clone() for p in ps]
+    zeros = lambda: [c.zeros(n) for n in sizes]
+    ms, vs, ms2, vs2 = zeros(), zeros(), zeros(), zeros()
+    sh, sh2 = [c.empty(n, torch.bfloat16) for n in sizes], [c.empty(n, torch.bfloat16) for n in sizes]
+    plan = cuda.AdamWPlan(c, ps, gs, ms, vs, sh)
+    for step in (1, 2, 3):
+        hp = cuda.adamw_params(0.02, 0.9, 0.999, 1e-8, 0.01, 1.0, step)
+        plan.step(hp)
+        cuda.adamw_update_multi(c, ps2, gs, ms2, vs2, hp, sh2)
+    for a, b in zip(ps + ms + vs + sh, ps2 + ms2 + vs2 + sh2):
+        assert np.array_equal(host(a), host(b))
+    plan.close()
