@@ -8,7 +8,7 @@
 // P = exp(S·scale − lse) and dS = P∘(dP − D)·scale are formed in registers by eight warps (two
 // per tensor-memory lane group, each taking half of the key columns) and handed back through
 // swizzled shared memory as bf16 operands.  dK and dV stay in tensor memory for the whole
-// walk; dQ tiles are added into an f32 accumulator with 128-bit reductions.
+// walk; dQ tiles are staged in shared memory and added into an f32 accumulator by TMA reductions.
 //
 // Replaces the reference's recompute-based backward with scalar f32 atomics
 // (tensor_core.ptx:3111-4407, heirloom-kernels/src/cuda.rs:9256-9294) and, for the values it
@@ -31,7 +31,8 @@ constexpr int FB_PS_BYTES = FB_BM * FB_BN * 2;  // 32 KB
 constexpr int FB_SOFTMAX_WARPS = 8;
 constexpr int FB_THREADS = (FB_SOFTMAX_WARPS + 2) * 32;  // + TMA warp + MMA warp
 constexpr int FB_TMEM_COLS = 512;
-constexpr int FB_SMEM_DATA = FB_TILE_BYTES * (2 * FB_KV_BUFFERS + 2 * FB_Q_STAGES) + 2 * FB_PS_BYTES;  // 192 KB
+constexpr int FB_DQ_BYTES = FB_BM * FB_HD * 4;     // 32 KB: one dQ tile in f32, staged for the TMA reduction
+constexpr int FB_SMEM_DATA = FB_TILE_BYTES * (2 * FB_KV_BUFFERS + 2 * FB_Q_STAGES) + 2 * FB_PS_BYTES + FB_DQ_BYTES;  // 224 KB
 constexpr int FB_SMEM_BYTES = FB_SMEM_DATA + 1024;
 static_assert(FB_SMEM_BYTES <= 227 * 1024, "shared memory budget");
 
@@ -39,6 +40,7 @@ struct FbBarriers {
   uint64_t kv_full[FB_KV_BUFFERS], kv_empty[FB_KV_BUFFERS];
   uint64_t q_full[FB_Q_STAGES], q_empty[FB_Q_STAGES];
   uint64_t sdp_full, sdp_free, p_full, dq_full;
+  uint64_t stage_free, stage_full;  // dQ staging buffer: read by the previous reduction / written by all softmax warps
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -55,10 +57,6 @@ struct FbParams {
   float scale, scale_log2;
   int* status;
 };
-
-__device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
-  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
-}
 
 // A CTA's place in its sequence of query tiles: work item `item` (one key tile of one batch and
 // head; items with the longest walks come first), query tile `it` of its walk.  Every warp role
@@ -99,7 +97,7 @@ __device__ __forceinline__ FbCursor fb_next(const FbCursor& c, const FbParams& p
 __global__ void __launch_bounds__(FB_THREADS, 1)
 flash_attention_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                            const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do,
-                           const FbParams p) {
+                           const __grid_constant__ CUtensorMap map_dq, const FbParams p) {
   extern __shared__ uint8_t fb_smem_raw[];
   const uintptr_t raw = reinterpret_cast<uintptr_t>(fb_smem_raw);
   uint8_t* tiles = reinterpret_cast<uint8_t*>((raw + sizeof(FbBarriers) + 1023) & ~uintptr_t(1023));
@@ -111,6 +109,7 @@ flash_attention_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
   uint8_t* sdo = sq + FB_Q_STAGES * FB_TILE_BYTES;     // [stage] dO tiles
   uint8_t* sp = sdo + FB_Q_STAGES * FB_TILE_BYTES;     // P  (bf16, [query][key], two 64-key blocks)
   uint8_t* sds = sp + FB_PS_BYTES;                     // dS (same layout)
+  uint8_t* sdq = sds + FB_PS_BYTES;                    // dQ tile, f32: two blocks of [query][32 columns], 128-byte swizzle
   volatile int* abort_flag = &bars->abort_flag;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -128,6 +127,8 @@ flash_attention_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
     tc05::mbar_init(&bars->sdp_free, FB_SOFTMAX_WARPS);
     tc05::mbar_init(&bars->p_full, FB_SOFTMAX_WARPS);
     tc05::mbar_init(&bars->dq_full, 1);
+    tc05::mbar_init(&bars->stage_free, 1);
+    tc05::mbar_init(&bars->stage_full, FB_SOFTMAX_WARPS);
     bars->abort_flag = layout_ok ? 0 : 1;
     tc05::fence_barrier_init();
   }
@@ -167,8 +168,11 @@ flash_attention_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
           tc05::tma_load_2d(sv + kb * FB_TILE_BYTES, &map_v, &bars->kv_full[kb], c.h * FB_HD, row_base + c.kj * FB_BN);
         }
         const int s = g % FB_Q_STAGES;
-        if (!tc05::mbar_wait(&bars->q_empty[s], ((uint32_t)(g / FB_Q_STAGES) & 1u) ^ 1u, abort_flag)) break;
         const int qrow = row_base + (c.kj + c.it) * FB_BM;
+        // the stage frees only when the tile two back has been consumed: have L2 fetch the tile in the meantime
+        tc05::tma_prefetch_l2_2d(&map_q, c.h * FB_HD, qrow);
+        tc05::tma_prefetch_l2_2d(&map_do, c.h * FB_HD, qrow);
+        if (!tc05::mbar_wait(&bars->q_empty[s], ((uint32_t)(g / FB_Q_STAGES) & 1u) ^ 1u, abort_flag)) break;
         tc05::mbar_arrive_expect_tx(&bars->q_full[s], 2 * FB_TILE_BYTES);
         tc05::tma_load_2d(sq + s * FB_TILE_BYTES, &map_q, &bars->q_full[s], c.h * FB_HD, qrow);
         tc05::tma_load_2d(sdo + s * FB_TILE_BYTES, &map_do, &bars->q_full[s], c.h * FB_HD, qrow);
@@ -258,18 +262,42 @@ flash_attention_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
     bool ok = !*abort_flag;
     // dQ tile number `g` of the sequence, for query position t of (b, h): out of tensor memory and into the f32
     // accumulator in global memory
-    auto add_dq = [&](int g, const FbCursor& c) {
-      uint32_t qb[32];
-      tc05::tmem_ld_32x32b_x32(tmem_dq + (uint32_t)((g & 1) * FB_HD) + lane_sel + half * 32, qb);
-      tc05::tmem_ld_wait();
-      const int t = (c.kj + c.it) * FB_BM + r;
-      if (t < p.T) {
-        float* dst = p.dq_accum + (size_t)(c.b * p.T + t) * p.ld_dq + (size_t)c.h * FB_HD + half * 32;
-#pragma unroll
-        for (int i = 0; i < 32; i += 4)
-          red_add_v4(dst + i, __uint_as_float(qb[i]), __uint_as_float(qb[i + 1]), __uint_as_float(qb[i + 2]),
-                     __uint_as_float(qb[i + 3]));
+    // The tile is staged in shared memory and added by one TMA reduction per 32-column block: 32 KB of f32 per query
+    // tile would otherwise leave as 16-byte reductions issued by these warps, which then wait behind them.
+    // `drain` counts the calls; rows past T are clipped by the tensor map.
+    int drain = 0;
+    // the previous reduction has read the staging buffer: checked by its issuer well before the buffer is needed again
+    auto release_stage = [&]() {
+      if (warp == 0 && lane == 0) {
+        tc05::tma_store_wait_read();
+        tc05::mbar_arrive(&bars->stage_free);
       }
+    };
+    auto add_dq_begin = [&](int g, uint32_t (&qb)[32]) {  // the tile starts to travel out of tensor memory
+      tc05::tmem_ld_32x32b_x32(tmem_dq + (uint32_t)((g & 1) * FB_HD) + lane_sel + half * 32, qb);
+    };
+    auto add_dq_finish = [&](const FbCursor& c, uint32_t (&qb)[32]) -> bool {
+      tc05::tmem_ld_wait();
+      tc05::tmem_ld_fence(qb);
+      if (!tc05::mbar_wait(&bars->stage_free, (uint32_t)drain & 1u, abort_flag)) return false;
+      uint8_t* line = sdq + half * (FB_BM * 128) + r * 128;
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+        *reinterpret_cast<uint4*>(line + ((i ^ (r & 7)) << 4)) = make_uint4(qb[i * 4], qb[i * 4 + 1], qb[i * 4 + 2], qb[i * 4 + 3]);
+      tc05::fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) tc05::mbar_arrive(&bars->stage_full);
+      if (warp == 0) {
+        if (!tc05::mbar_wait(&bars->stage_full, (uint32_t)drain & 1u, abort_flag)) return false;
+        if (lane == 0) {
+          const int t0 = (c.kj + c.it) * FB_BM;
+          tc05::tma_reduce_add_3d(&map_dq, sdq, c.h * FB_HD, t0, c.b);
+          tc05::tma_reduce_add_3d(&map_dq, sdq + FB_BM * 128, c.h * FB_HD + 32, t0, c.b);
+          tc05::tma_store_commit();
+        }
+      }
+      ++drain;
+      return true;
     };
     // dV and dK of this thread's key row (32 columns each) out of tensor memory, already rounded to bf16 pairs:
     // words 0-15 hold dV, words 16-31 dK
@@ -296,66 +324,67 @@ flash_attention_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
       }
     };
     // per-row statistics of a query tile, fetched one tile ahead
-    auto row_stats = [&](const FbCursor& c, float* neg_lse2, float* dlt) {
+    auto row_stats = [&](const FbCursor& c, float* neg_lse2, float* neg_dlt_scaled) {
       const int tt = c.valid() ? (c.kj + c.it) * FB_BM + r : 0;
       const bool in = c.valid() && tt < p.T;
       const size_t stat = in ? ((size_t)c.b * p.H + c.h) * p.T + tt : 0;
-      *neg_lse2 = in ? -p.lse[stat] * 1.4426950408889634f : 0.f;
-      *dlt = in ? p.delta[stat] : 0.f;
+      *neg_lse2 = in ? -p.lse[stat] * 1.4426950408889634f : -INFINITY;  // rows past T: every P becomes 0
+      *neg_dlt_scaled = in ? -p.delta[stat] * p.scale : 0.f;
     };
     FbCursor c = first, prev = first;
-    float neg_lse2, dlt;
-    row_stats(c, &neg_lse2, &dlt);
+    float neg_lse2, neg_dlt_scaled;
+    row_stats(c, &neg_lse2, &neg_dlt_scaled);
     int g = 0;
     // One query tile.  `Boundary` is the first tile of an item that follows another one: only that
     // instance carries the read-out of the previous item's dK and dV, so the steady-state instance
     // keeps its registers for the tile itself.
-    auto tile = [&](auto boundary_tag) -> bool {
+    auto tile = [&](auto boundary_tag, auto diag_tag) -> bool {
       constexpr bool Boundary = decltype(boundary_tag)::value;
+      constexpr bool Diag = decltype(diag_tag)::value;
       const FbCursor n = fb_next(c, p);
       const int t = (c.kj + c.it) * FB_BM + r;  // query position
       const int key0 = c.kj * FB_BN;
-      const bool t_ok = t < p.T;
-      float next_neg_lse2, next_dlt;
-      row_stats(n, &next_neg_lse2, &next_dlt);
+      float next_neg_lse2, next_neg_dlt_scaled;
+      row_stats(n, &next_neg_lse2, &next_neg_dlt_scaled);
       if (!tc05::mbar_wait(&bars->sdp_full, (uint32_t)g & 1u, abort_flag)) return false;
       tc05::tc_fence_after_sync();
-      const bool diag = (c.it == 0);
       uint32_t pp[4][8], dd[4][8];  // P and dS of this thread's 64 key columns, bf16 pairs
-      uint32_t sb[2][16], db[2][16];
-      tc05::tmem_ld_32x32b_x16(tmem_s + lane_sel + half * 64, sb[0]);
-      tc05::tmem_ld_32x32b_x16(tmem_dp + lane_sel + half * 64, db[0]);
+      uint32_t sb[2][8], db[2][8];  // eight columns at a time, the next eight on their way
+      tc05::tmem_ld_32x32b_x8(tmem_s + lane_sel + half * 64, sb[0]);
+      tc05::tmem_ld_32x32b_x8(tmem_dp + lane_sel + half * 64, db[0]);
 #pragma unroll
-      for (int ch = 0; ch < 4; ++ch) {
-        const int col0 = half * 64 + ch * 16;  // key column within the tile
+      for (int ch = 0; ch < 8; ++ch) {
+        const int col0 = half * 64 + ch * 8;  // key column within the tile
         tc05::tmem_ld_wait();
         tc05::tmem_ld_fence(sb[ch & 1]);
         tc05::tmem_ld_fence(db[ch & 1]);
-        if (ch < 3) {  // the next 16 columns travel while these are worked on
-          tc05::tmem_ld_32x32b_x16(tmem_s + lane_sel + col0 + 16, sb[(ch + 1) & 1]);
-          tc05::tmem_ld_32x32b_x16(tmem_dp + lane_sel + col0 + 16, db[(ch + 1) & 1]);
+        if (ch < 7) {  // the next columns travel while these are worked on
+          tc05::tmem_ld_32x32b_x8(tmem_s + lane_sel + col0 + 8, sb[(ch + 1) & 1]);
+          tc05::tmem_ld_32x32b_x8(tmem_dp + lane_sel + col0 + 8, db[(ch + 1) & 1]);
         } else {  // all of S and dP is in registers: the next tile's may overwrite them
           tc05::tc_fence_before_sync();
           __syncwarp();
           if (lane == 0) tc05::mbar_arrive(&bars->sdp_free);
+          if (g > 0) release_stage();  // one release per drain: tile g drains the dQ of tile g - 1
         }
+        // P = 2^(S*scale*log2e - lse*log2e); rows past T carry lse = +inf, so their P is 0.  dS = P * (dP - D) * scale
+        // with the scale folded into both terms.  Only the diagonal tile has keys above the query to mask.
 #pragma unroll
-        for (int i = 0; i < 16; i += 2) {
+        for (int i = 0; i < 8; i += 2) {
           float pr[2], dsv[2];
 #pragma unroll
           for (int e = 0; e < 2; ++e) {
-            const int key = key0 + col0 + i + e;
-            const bool live = t_ok && !(diag && key > t);
-            const float pv = live ? ex2_fast(fmaf(__uint_as_float(sb[ch & 1][i + e]), p.scale_log2, neg_lse2)) : 0.f;
+            float pv = ex2_fast(fmaf(__uint_as_float(sb[ch & 1][i + e]), p.scale_log2, neg_lse2));
+            if constexpr (Diag) pv = (key0 + col0 + i + e > t) ? 0.f : pv;
             pr[e] = pv;
-            dsv[e] = pv * (__uint_as_float(db[ch & 1][i + e]) - dlt) * p.scale;
+            dsv[e] = pv * fmaf(__uint_as_float(db[ch & 1][i + e]), p.scale, neg_dlt_scaled);
           }
-          pp[ch][i / 2] = pack_bf16x2(pr[0], pr[1]);
-          dd[ch][i / 2] = pack_bf16x2(dsv[0], dsv[1]);
+          pp[ch / 2][(ch & 1) * 4 + i / 2] = pack_bf16x2(pr[0], pr[1]);
+          dd[ch / 2][(ch & 1) * 4 + i / 2] = pack_bf16x2(dsv[0], dsv[1]);
         }
       }
       neg_lse2 = next_neg_lse2;
-      dlt = next_dlt;
+      neg_dlt_scaled = next_neg_dlt_scaled;
       // the previous tile's products have finished: its dQ is ready and P/dS may be overwritten
       if (g > 0) {
         if (!tc05::mbar_wait(&bars->dq_full, (uint32_t)(g - 1) & 1u, abort_flag)) return false;
@@ -380,7 +409,11 @@ flash_attention_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
       __syncwarp();
       if (lane == 0) tc05::mbar_arrive(&bars->p_full);
       // the other dQ buffer is not written again before this warp's next arrival on p_full
-      if (g > 0) add_dq(g - 1, prev);
+      if (g > 0) {
+        uint32_t qb[32];
+        add_dq_begin(g - 1, qb);
+        if (!add_dq_finish(prev, qb)) return false;
+      }
       if constexpr (Boundary) store_dkv(dkv, prev);
       prev = c;
       c = n;
@@ -388,13 +421,17 @@ flash_attention_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
       return true;
     };
     while (ok && c.valid()) {
-      if (g > 0 && c.it == 0) ok = tile(std::true_type{});
-      else ok = tile(std::false_type{});
+      if (c.it == 0) ok = g > 0 ? tile(std::true_type{}, std::true_type{}) : tile(std::false_type{}, std::true_type{});
+      else ok = tile(std::false_type{}, std::false_type{});
     }
     if (ok && g > 0) {  // dQ of the last query tile and dK, dV of the last item
       if (tc05::mbar_wait(&bars->dq_full, (uint32_t)(g - 1) & 1u, abort_flag)) {
         tc05::tc_fence_after_sync();
-        add_dq(g - 1, prev);
+        uint32_t qb[32];
+        release_stage();
+        add_dq_begin(g - 1, qb);
+        add_dq_finish(prev, qb);
+        if (warp == 0 && lane == 0) tc05::tma_store_wait_all();  // the last reduction has left shared memory and landed
         uint32_t dkv[32];
         load_dkv(dkv);
         store_dkv(dkv, prev);
@@ -510,7 +547,16 @@ int flash_attention_backward_impl(hl_ctx* ctx, const void* q, const void* k, con
     configured = true;
   }
   const int nq = ceil_div(time, FB_BM);
-  flash_attention_bwd_kernel<<<std::min(nq * batch * n_heads, ctx->sm_count), FB_THREADS, FB_SMEM_BYTES, ctx->stream>>>(mq, mk, mv, mdo, p);
+  // dQ accumulator as [batch][time][channels] f32, so that a tile's rows past `time` are clipped instead of landing in
+  // the next batch entry; boxes of 32 columns (128 bytes) by 128 rows
+  CUtensorMap mdq;
+  {
+    const uint64_t dims[3] = {(uint64_t)C, (uint64_t)time, (uint64_t)batch};
+    const uint64_t strides[2] = {(uint64_t)C * sizeof(float), (uint64_t)time * (uint64_t)C * sizeof(float)};
+    const uint32_t box[3] = {32, (uint32_t)FB_BM, 1};
+    if ((rc = make_tensor_map(&mdq, HL_F32, 3, dq_accum, dims, strides, box, 128)) != HL_OK) return rc;
+  }
+  flash_attention_bwd_kernel<<<std::min(nq * batch * n_heads, ctx->sm_count), FB_THREADS, FB_SMEM_BYTES, ctx->stream>>>(mq, mk, mv, mdo, mdq, p);
   HL_LAUNCH_CHECK("flash_attention_bwd_kernel");
   {
     const long long quads = (long long)rows * (C / 4);
@@ -539,3 +585,4 @@ extern "C" int hl_flash_attention_backward(hl_ctx* ctx, const void* q, const voi
   return hl::flash_attention_backward_impl(ctx, q, k, v, ld_qkv, out, ld_out, dout, ld_dout, lse, dq, dk, dv, ld_dqkv,
                                            batch, time, n_heads, head_dim, ctx->workspace, ctx->workspace_bytes);
 }
+
