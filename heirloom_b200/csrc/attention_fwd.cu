@@ -1,4 +1,4 @@
-// Causal flash attention forward on tcgen05: S = Q·Kᵀ and O_tile = P·V are tensor-memory
+// Causal flash attention forward on tcgen05: S = Q·Kᵀ and O += P·V are tensor-memory
 // accumulators, K/V tiles stream in by TMA, the online softmax runs in registers and P goes
 // back to the tensor cores through swizzled shared memory.
 //
@@ -12,12 +12,13 @@
 // dimension (column h*hd + j, as src/tensor.rs:5156-5177), so they may live side by side in
 // one fused [B*T, 3C] projection buffer.  One CTA owns 128 query rows of one (batch, head).
 //
-// Pipeline: key tiles of 64; two S buffers and two O_tile buffers in tensor memory and two P
-// buffers in shared memory.  Four softmax warps (one per tensor-memory lane group, a thread per
-// query row) work on tile j while the tensor cores run P·V of tile j-1 and Q·Kᵀ of tile j+1; an
-// O_tile is folded into the running output two tiles later, rescaled by the maximum recorded when
-// it was produced.  The CTA is sized (192 threads, 98 KB of shared memory, 256 tensor-memory
-// columns) so that two of them share an SM and one's start-up and drain overlap the other's work.
+// Pipeline: key tiles of 64; two S buffers and the O accumulator in tensor memory and two P buffers in
+// shared memory.  Four softmax warps (one per tensor-memory lane group, a thread per query row) work
+// on tile j while the tensor cores run P·V of tile j-1 and Q·Kᵀ of tile j+1.  P is formed against a
+// reference maximum that a row raises only when its maximum has grown by more than 2^8; the row then
+// rescales its O in place (tensor-memory load, multiply, store) between two P·V products.  The CTA
+// is sized (192 threads, 98 KB of shared memory, 256 tensor-memory columns) so that two of them share
+// an SM and one's start-up and drain overlap the other's work.
 #include "common.cuh"
 #include "tc05.cuh"
 
@@ -33,7 +34,7 @@ constexpr int FA_KV_BYTES = FA_BN * FA_HD * 2;  // 8 KB
 constexpr int FA_P_BYTES = FA_BM * FA_BN * 2;   // 16 KB: 128 rows of 64 keys, one 128-byte line each
 constexpr int FA_SOFTMAX_WARPS = 4;
 constexpr int FA_THREADS = (FA_SOFTMAX_WARPS + 2) * 32;  // + TMA warp + MMA warp
-constexpr int FA_TMEM_COLS = 256;  // S: 2 x 64 columns, O tile: 2 x 64 columns
+constexpr int FA_TMEM_COLS = 256;  // S: 2 x 64 columns, O: 64 columns (allocations are powers of two)
 constexpr int FA_SMEM_DATA = FA_Q_BYTES + 2 * FA_KV_STAGES * FA_KV_BYTES + 2 * FA_P_BYTES;  // 96 KB
 constexpr int FA_SMEM_BYTES = FA_SMEM_DATA + 2048;  // barriers in front, alignment slack
 static_assert(2 * (FA_SMEM_BYTES + 1024) <= 228 * 1024, "two CTAs per SM");
@@ -104,7 +105,7 @@ flash_attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
   __syncthreads();
   tc05::tc_fence_after_sync();
   const uint32_t tmem_s0 = sh->tmem_base;         // S buffers at +0 and +64
-  const uint32_t tmem_o0 = tmem_s0 + 2 * FA_BN;   // O tiles at +128 and +192
+  const uint32_t tmem_o0 = tmem_s0 + 2 * FA_BN;   // O at +128
 
   if (warp == FA_SOFTMAX_WARPS) {
     // -------------------------------------------------------------------------- TMA producer
@@ -161,7 +162,7 @@ flash_attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
           // A = P: [128 rows x 64 keys], K-major; B = V: rows are keys (MN-major), 16 keys per step
           const uint64_t da = tc05::smem_desc_sw128(ap + ks * 32, 16, 1024);
           const uint64_t db = tc05::smem_desc_sw128(av + ks * (16 * 128), FA_BN * 128, 1024);
-          tc05::umma_ss(tmem_o0 + (uint32_t)((j & 1) * FA_HD), da, db, idesc_pv, ks > 0 ? 1u : 0u);
+          tc05::umma_ss(tmem_o0, da, db, idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);  // O accumulates over the key tiles
         }
         tc05::umma_commit(&sh->v_empty[s]);
         tc05::umma_commit(&sh->o_full[j & 1]);
@@ -173,36 +174,19 @@ flash_attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
     const int r = warp * 32 + lane;     // query row within the tile == tensor-memory lane
     const int t = q0 + r;               // query position within the batch
     const uint32_t lane_sel = (uint32_t)(warp * 32) << 16;
-    float o_acc[FA_HD];
-#pragma unroll
-    for (int i = 0; i < FA_HD; ++i) o_acc[i] = 0.f;
-    float m_run = -INFINITY;   // running row maximum, in log2 units
-    float m_ref = -INFINITY;   // maximum o_acc is currently scaled to
-    float l_run = 0.f;         // row sum, scaled to m_run
-    float m_hist[2] = {-INFINITY, -INFINITY};  // m_run when tile j (parity j & 1) was exponentiated
+    // O accumulates in tensor memory against a reference maximum m_ref that is only raised when a row's maximum has
+    // grown by more than 2^8 since: P = 2^(s - m_ref) then stays below 256, which costs bf16 nothing (same relative
+    // precision) and f32 sums nothing, and O is rescaled in place a few times per row instead of once per tile.
+    constexpr float kRaise = 8.0f;
+    float m_ref = -INFINITY;   // reference maximum, in log2 units
+    float l_run = 0.f;         // row sum, scaled to m_ref
     bool ok = !*abort_flag;
 
-    // Fold O_tile of tile `i` (made with maximum m_hist[i & 1]) into o_acc at the current maximum.
-    auto fold = [&](int i) -> bool {
-      if (!tc05::mbar_wait(&sh->o_full[i & 1], (uint32_t)(i >> 1) & 1u, abort_flag)) return false;
-      tc05::tc_fence_after_sync();
-      const float a = ex2_fast(m_ref - m_run);          // 0 when nothing has been folded yet
-      const float c = ex2_fast(m_hist[i & 1] - m_run);
-#pragma unroll
-      for (int hb = 0; hb < 2; ++hb) {
-        uint32_t ob[32];
-        tc05::tmem_ld_32x32b_x32(tmem_o0 + (uint32_t)((i & 1) * FA_HD) + lane_sel + hb * 32, ob);
-        tc05::tmem_ld_wait();
-#pragma unroll
-        for (int k = 0; k < 32; ++k) o_acc[hb * 32 + k] = o_acc[hb * 32 + k] * a + __uint_as_float(ob[k]) * c;
-      }
-      m_ref = m_run;
-      return true;
-    };
-
     for (int j = 0; j < n_tiles && ok; ++j) {
-      // P·V of tile j-2 has finished: take its output, and its P buffer is free for this tile
-      if (j >= 2 && !fold(j - 2)) { ok = false; break; }
+      // P·V of tile j-2 has finished: its P buffer is free for this tile
+      if (j >= 2) {
+        if (!tc05::mbar_wait(&sh->o_full[j & 1], (uint32_t)((j - 2) >> 1) & 1u, abort_flag)) { ok = false; break; }
+      }
       if (!tc05::mbar_wait(&sh->s_full[j & 1], (uint32_t)(j >> 1) & 1u, abort_flag)) { ok = false; break; }
       tc05::tc_fence_after_sync();
       const bool diag = (j >= n_tiles - 2);  // the two tiles that hold keys q0 .. q0+127
@@ -220,11 +204,30 @@ flash_attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
       }
 #pragma unroll
       for (int i = 0; i < FA_BN; ++i) m_tile = fmaxf(m_tile, __uint_as_float(sb[i]));
-      const float m_new = fmaxf(m_run, m_tile * p.scale_log2);  // finite: key 0 is in tile 0 and visible to every row
-      l_run *= ex2_fast(m_run - m_new);
-      m_run = m_new;
-      m_hist[j & 1] = m_new;
-      const float neg_m = -m_new;
+      const float m_new = m_tile * p.scale_log2;  // finite in tile 0: key 0 is visible to every row
+      const bool raise = m_new > m_ref + kRaise;  // always true in tile 0 (m_ref = -inf)
+      if (j == 0) {
+        m_ref = m_new;
+      } else if (__any_sync(0xffffffffu, raise)) {
+        // rows of this warp rescale their O in place; P·V of tile j-1 must have landed, and P·V of tile j is not
+        // issued before this warp has handed over P(j)
+        if (!tc05::mbar_wait(&sh->o_full[(j - 1) & 1], (uint32_t)((j - 1) >> 1) & 1u, abort_flag)) { ok = false; break; }
+        tc05::tc_fence_after_sync();
+        const float a = raise ? ex2_fast(m_ref - m_new) : 1.0f;
+        if (raise) m_ref = m_new;
+        l_run *= a;
+#pragma unroll
+        for (int hb = 0; hb < 2; ++hb) {
+          uint32_t ob[32];
+          tc05::tmem_ld_32x32b_x32(tmem_o0 + lane_sel + hb * 32, ob);
+          tc05::tmem_ld_wait();
+#pragma unroll
+          for (int k = 0; k < 32; ++k) ob[k] = __float_as_uint(__uint_as_float(ob[k]) * a);
+          tc05::tmem_st_32x32b_x32(tmem_o0 + lane_sel + hb * 32, ob);
+        }
+        tc05::tmem_st_wait();
+      }
+      const float neg_m = -m_ref;
       uint8_t* line = sp + (j & 1) * FA_P_BYTES + r * 128;
       float l_tile = 0.f;
 #pragma unroll
@@ -245,22 +248,34 @@ flash_attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
       __syncwarp();
       if (lane == 0) tc05::mbar_arrive(&sh->p_full[j & 1]);
     }
-    if (ok) ok = fold(n_tiles - 2);
-    if (ok) ok = fold(n_tiles - 1);
-    if (ok && t < p.T) {
+    if (ok) {  // the last P·V has landed
+      ok = tc05::mbar_wait(&sh->o_full[(n_tiles - 1) & 1], (uint32_t)((n_tiles - 1) >> 1) & 1u, abort_flag);
+      tc05::tc_fence_after_sync();
+    }
+    if (ok) {
       const float inv = 1.0f / l_run;
       __nv_bfloat16* dst = p.out + (size_t)(row_base + t) * p.ld_out + (size_t)h * FA_HD;
 #pragma unroll
-      for (int i = 0; i < FA_HD; i += 8) {
-        uint4 o;
-        o.x = pack_bf16x2(o_acc[i] * inv, o_acc[i + 1] * inv);
-        o.y = pack_bf16x2(o_acc[i + 2] * inv, o_acc[i + 3] * inv);
-        o.z = pack_bf16x2(o_acc[i + 4] * inv, o_acc[i + 5] * inv);
-        o.w = pack_bf16x2(o_acc[i + 6] * inv, o_acc[i + 7] * inv);
-        *reinterpret_cast<uint4*>(dst + i) = o;
+      for (int hb = 0; hb < 2; ++hb) {
+        uint32_t ob[32];
+        tc05::tmem_ld_32x32b_x32(tmem_o0 + lane_sel + hb * 32, ob);
+        tc05::tmem_ld_wait();
+        if (t < p.T) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 8) {
+            uint4 o;
+            o.x = pack_bf16x2(__uint_as_float(ob[i]) * inv, __uint_as_float(ob[i + 1]) * inv);
+            o.y = pack_bf16x2(__uint_as_float(ob[i + 2]) * inv, __uint_as_float(ob[i + 3]) * inv);
+            o.z = pack_bf16x2(__uint_as_float(ob[i + 4]) * inv, __uint_as_float(ob[i + 5]) * inv);
+            o.w = pack_bf16x2(__uint_as_float(ob[i + 6]) * inv, __uint_as_float(ob[i + 7]) * inv);
+            *reinterpret_cast<uint4*>(dst + hb * 32 + i) = o;
+          }
+        }
       }
+    }
+    if (ok && t < p.T) {
       // natural-log log-sum-exp of the scaled scores
-      p.lse[((size_t)b * p.H + h) * p.T + t] = (m_run + log2f(l_run)) * 0.6931471805599453f;
+      p.lse[((size_t)b * p.H + h) * p.T + t] = (m_ref + log2f(l_run)) * 0.6931471805599453f;
     }
   }
 
