@@ -4,6 +4,8 @@
 // reference's one-thread-per-token serial selection (heirloom-kernels/src/ptx/kernels.ptx:1780-2262)
 // and its one-thread-per-element gathers (:2317-3259); the O(selected^2) duplicate scan of the
 // sparse AdamW kernels (:537-811) becomes a row flag pass.
+#include <cub/device/device_radix_sort.cuh>
+
 #include "kernels.h"
 
 namespace hl {
@@ -672,6 +674,88 @@ __global__ void weighted_value_bwd_kernel(const int64_t* __restrict__ idx, const
   }
 }
 
+// ---- weighted value backward in row order ---------------------------------------------------------------------
+// With many more (token, slot) events than distinct rows (about 26 events per row at the memory-transformer size),
+// per-event 16-byte atomics pile onto hot rows in L2.  Events are therefore sorted by row (radix sort over as many key
+// bits as the row count needs); a warp takes 32 consecutive sorted events, keeps the value row of the current run and
+// the run's gradient sum in registers, and issues one set of atomics per run (and per chunk boundary).  The weight
+// gradients, dot(grad_out[token], values[row]), come from the same pass: one 2 KB read of grad_out per event is all
+// the traffic that does not stay in registers.
+__global__ void value_event_keys_kernel(const int64_t* __restrict__ idx, long long n, int rows, int* __restrict__ keys,
+                                        int* __restrict__ events) {
+  const long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const long long r = idx[i];
+  keys[i] = (r < 0 || r >= rows) ? rows : (int)r;  // out-of-range slots sort behind every row and are skipped
+  events[i] = (int)i;
+}
+
+template <int VPL>  // 16-byte pieces of a row per lane: dim <= VPL * 128
+__global__ void __launch_bounds__(128)
+weighted_value_bwd_sorted_kernel(const int* __restrict__ keys, const int* __restrict__ events,
+                                 const float* __restrict__ weights, const float* __restrict__ values,
+                                 const float* __restrict__ grad_out, float* __restrict__ dweights,
+                                 float* __restrict__ dvalues, long long n, int top_k, int rows, int dim) {
+  const int lane = threadIdx.x & 31;
+  const long long base = ((long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)) * 32;
+  if (base >= n) return;
+  const int groups = dim / 4;
+  int my_key = rows, my_event = 0;
+  float my_w = 0.f;
+  if (base + lane < n) {
+    my_key = keys[base + lane];
+    my_event = events[base + lane];
+    if (my_key < rows) my_w = weights[my_event];
+  }
+  float4 acc[VPL], vrow[VPL];
+#pragma unroll
+  for (int u = 0; u < VPL; ++u) acc[u] = vrow[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+  int cur = -1;
+  auto flush = [&]() {
+    if (cur < 0 || !dvalues) return;
+#pragma unroll
+    for (int u = 0; u < VPL; ++u) {
+      const int gi = u * 32 + lane;
+      if (gi < groups) atomicAdd(reinterpret_cast<float4*>(dvalues + (size_t)cur * dim) + gi, acc[u]);
+      acc[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+  };
+  for (int i = 0; i < 32; ++i) {
+    const int key = __shfl_sync(0xffffffffu, my_key, i);
+    if (key >= rows) break;  // sorted: nothing valid follows
+    const int event = __shfl_sync(0xffffffffu, my_event, i);
+    const float w = __shfl_sync(0xffffffffu, my_w, i);
+    if (key != cur) {
+      flush();
+      cur = key;
+      if (dweights) {
+#pragma unroll
+        for (int u = 0; u < VPL; ++u) {
+          const int gi = u * 32 + lane;
+          if (gi < groups) vrow[u] = __ldg(reinterpret_cast<const float4*>(values + (size_t)key * dim) + gi);
+        }
+      }
+    }
+    const float4* go = reinterpret_cast<const float4*>(grad_out + (size_t)(event / top_k) * dim);
+    double dot = 0.0;
+#pragma unroll
+    for (int u = 0; u < VPL; ++u) {
+      const int gi = u * 32 + lane;
+      if (gi < groups) {
+        const float4 g = __ldg(go + gi);
+        dot += (double)g.x * vrow[u].x + (double)g.y * vrow[u].y + (double)g.z * vrow[u].z + (double)g.w * vrow[u].w;
+        acc[u].x = fmaf(w, g.x, acc[u].x); acc[u].y = fmaf(w, g.y, acc[u].y);
+        acc[u].z = fmaf(w, g.z, acc[u].z); acc[u].w = fmaf(w, g.w, acc[u].w);
+      }
+    }
+    if (dweights) {
+      dot = warp_sum(dot);
+      if (lane == 0) dweights[event] = (float)dot;
+    }
+  }
+  flush();
+}
+
 // ---- access counts: counts[r] += occurrences of r among the selected rows (kernels.ptx:813-886) ---------------
 __global__ void access_count_rows_kernel(const int64_t* __restrict__ selected, long long n, int rows,
                                          unsigned long long* __restrict__ counts, int* __restrict__ status) {
@@ -928,6 +1012,34 @@ int hl_memory_weighted_value_backward(hl_ctx* ctx, const int64_t* indices, const
   int rc = check_memory_dims(tokens, top_k, dim, "hl_memory_weighted_value_backward");
   if (rc != HL_OK) return rc;
   HL_REQUIRE(rows > 0 && dim % 4 == 0, "hl_memory_weighted_value_backward: non-zero rows/row_dim, row_dim a multiple of 4");
+  const long long n = (long long)tokens * top_k;
+  if (grad_values && n >= 32768 && dim <= 1024 && rows < (1 << 30)) {
+    // row order (see weighted_value_bwd_sorted_kernel).  Scratch: keys and events in and out, and the sort's own space.
+    int end_bit = 1;
+    while ((1ll << end_bit) <= rows) ++end_bit;  // the sentinel key `rows` must sort last
+    size_t sort_bytes = 0;
+    HL_CUDA(cub::DeviceRadixSort::SortPairs(nullptr, sort_bytes, (const int*)nullptr, (int*)nullptr, (const int*)nullptr,
+                                            (int*)nullptr, (int)n, 0, end_bit, ctx->stream));
+    const size_t arr = ((size_t)n * sizeof(int) + 255) & ~size_t(255);
+    rc = ensure_workspace(ctx, 4 * arr + sort_bytes);
+    if (rc != HL_OK) return rc;
+    uint8_t* ws = reinterpret_cast<uint8_t*>(ctx->workspace);
+    int *keys_in = reinterpret_cast<int*>(ws), *ev_in = reinterpret_cast<int*>(ws + arr);
+    int *keys = reinterpret_cast<int*>(ws + 2 * arr), *ev = reinterpret_cast<int*>(ws + 3 * arr);
+    value_event_keys_kernel<<<(unsigned)ceil_div_ll(n, 256), 256, 0, ctx->stream>>>(indices, n, rows, keys_in, ev_in);
+    HL_LAUNCH_CHECK("value_event_keys_kernel");
+    HL_CUDA(cub::DeviceRadixSort::SortPairs(ws + 4 * arr, sort_bytes, keys_in, keys, ev_in, ev, (int)n, 0, end_bit, ctx->stream));
+    const unsigned blocks = (unsigned)ceil_div_ll(ceil_div_ll(n, 32), 4);
+    if (dim <= 512)
+      weighted_value_bwd_sorted_kernel<4><<<blocks, 128, 0, ctx->stream>>>(keys, ev, weights, values, grad_out, grad_weights,
+                                                                           grad_values, n, top_k, rows, dim);
+    else
+      weighted_value_bwd_sorted_kernel<8><<<blocks, 128, 0, ctx->stream>>>(keys, ev, weights, values, grad_out, grad_weights,
+                                                                           grad_values, n, top_k, rows, dim);
+    HL_LAUNCH_CHECK("weighted_value_bwd_sorted_kernel");
+    count_launch(ctx, 3);
+    return HL_OK;
+  }
   weighted_value_bwd_kernel<<<ceil_div(tokens, 4), 128, 0, ctx->stream>>>(indices, weights, values, grad_out, grad_weights,
                                                                           grad_values, tokens, top_k, rows, dim);
   HL_LAUNCH_CHECK("weighted_value_bwd_kernel");

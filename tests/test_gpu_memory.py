@@ -224,3 +224,27 @@ def test_row_masks_compaction_and_packed_rows():
     got = cuda.sparse_rows_sum_squares(c, t, sel, row_mask=torch.tensor(mask_in, device="cuda"))
     active = np.flatnonzero(want & mask_in)
     assert got == pytest.approx(float((table[active].astype(np.float64) ** 2).sum()), rel=1e-12)
+
+
+@pytest.mark.parametrize("tokens,top_k,rows,dim", [(4096, 16, 1024, 256), (2048, 32, 300, 512), (4100, 8, 70000, 64),
+                                                   (1030, 32, 4096, 640)])
+def test_weighted_value_backward_in_row_order_matches_a_host_sum(tokens, top_k, rows, dim):
+    """Event counts from 32768 up take the row-ordered path (sort by row, one set of atomics per run): many events per
+    row, rows nobody selected, chunk boundaries inside a run, a row count that is not a power of two."""
+    from heirloom_b200 import cuda
+    c = ctx()
+    rng = np.random.default_rng(tokens + rows)
+    idx = (rng.zipf(1.3, (tokens, top_k)) % rows).astype(np.int64)
+    idx[0, :] = rows - 1                      # the last row, a whole token's worth
+    w = rng.standard_normal((tokens, top_k)).astype(np.float32)
+    vals = rng.standard_normal((rows, dim)).astype(np.float32)
+    go = rng.standard_normal((tokens, dim)).astype(np.float32)
+    dw, dv = cuda.memory_weighted_value_backward(c, dev(idx, I64), dev(w), dev(vals), dev(go))
+    want_dw = np.einsum("td,tkd->tk", go.astype(np.float64), vals[idx].astype(np.float64))
+    want_dv = np.zeros((rows, dim), np.float64)
+    np.add.at(want_dv, idx.reshape(-1), (w[..., None].astype(np.float64) * go[:, None, :]).reshape(-1, dim))
+    assert_close("dw", host(dw), want_dw, atol=1e-5, rtol=1e-6)
+    scale = np.abs(want_dv).max()
+    assert np.abs(host(dv) - want_dv).max() <= 2e-6 * scale * np.sqrt(tokens * top_k / max(np.unique(idx).size, 1)) + 1e-5
+    untouched = np.ones(rows, bool); untouched[np.unique(idx)] = False
+    assert not np.any(host(dv)[untouched])
