@@ -473,15 +473,15 @@ __global__ void selected_scores_bwd_kernel(const int64_t* __restrict__ idx, cons
 // Half-key gradients of the product-key form: dK_L[li,:] += g[t,k] q_L[t,:], dK_R[ri,:] += g[t,k] q_R[t,:] over the
 // selected slots.  With only `side` rows per table every row collects about tokens*top_k/side terms, so atomics
 // (global or shared) would pile onto a few addresses.  The sum is therefore run as a dense product
-// dK = Wᵀ·Q with W[t, row] = sum of the g[t,k] whose slot maps to `row`: a CTA owns a block of tokens, 512 rows
+// dK = Wᵀ·Q with W[t, row] = sum of the g[t,k] whose slot maps to `row`: a CTA owns a block of tokens, 256 rows
 // and 64 columns of one table; per slice of 32 tokens it builds W in shared memory (one warp per token, its
-// duplicates added in slot order), multiplies with a 16 x 8 register tile per thread, and clears the entries it
+// duplicates added in slot order), multiplies with an 8 x 8 register tile per thread (two CTAs per SM), and clears the entries it
 // set.  The CTA's tile goes out as a partial result that fold_key_partials_kernel adds up in block order, so the
 // result does not depend on scheduling.
 constexpr int DK_COLS = 64;    // columns per CTA
-constexpr int DK_ROWS = 512;   // table rows per CTA
+constexpr int DK_ROWS = 256;   // table rows per CTA
 constexpr int DK_TOKENS = 32;  // tokens per slice
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, 2)
 product_key_dkeys_kernel(const int64_t* __restrict__ idx, const float* __restrict__ query, long long ld_q,
                          const float* __restrict__ grad_scores, float* __restrict__ partial, int tokens, int top_k,
                          int side, int half, int slots, int tokens_per_block, int col_blocks) {
@@ -492,11 +492,11 @@ product_key_dkeys_kernel(const int64_t* __restrict__ idx, const float* __restric
   const int c0 = (blockIdx.y % col_blocks) * DK_COLS;
   const int r0 = (blockIdx.y / col_blocks) * DK_ROWS;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int tr = threadIdx.x >> 3;  // 32 row groups of 16 rows
+  const int tr = threadIdx.x >> 3;  // 32 row groups of 8 rows
   const int tc = threadIdx.x & 7;   // 8 column groups of 8 columns
-  float acc[16][8];
+  float acc[8][8];
 #pragma unroll
-  for (int a = 0; a < 16; ++a)
+  for (int a = 0; a < 8; ++a)
 #pragma unroll
     for (int b = 0; b < 8; ++b) acc[a][b] = 0.f;
   for (int i = threadIdx.x; i < DK_TOKENS * DK_ROWS; i += 256) w_tile[i] = 0.f;
@@ -537,10 +537,10 @@ product_key_dkeys_kernel(const int64_t* __restrict__ idx, const float* __restric
     __syncthreads();
     const int tn = min(DK_TOKENS, t_end - t0);
     for (int t = 0; t < tn; ++t) {
-      float wv[16], qv[8];
+      float wv[8], qv[8];
 #pragma unroll
-      for (int a = 0; a < 16; a += 4) {
-        const float4 x = *reinterpret_cast<const float4*>(&w_tile[t * DK_ROWS + tr * 16 + a]);
+      for (int a = 0; a < 8; a += 4) {
+        const float4 x = *reinterpret_cast<const float4*>(&w_tile[t * DK_ROWS + tr * 8 + a]);
         wv[a] = x.x; wv[a + 1] = x.y; wv[a + 2] = x.z; wv[a + 3] = x.w;
       }
 #pragma unroll
@@ -549,7 +549,7 @@ product_key_dkeys_kernel(const int64_t* __restrict__ idx, const float* __restric
         qv[b] = x.x; qv[b + 1] = x.y; qv[b + 2] = x.z; qv[b + 3] = x.w;
       }
 #pragma unroll
-      for (int a = 0; a < 16; ++a)
+      for (int a = 0; a < 8; ++a)
 #pragma unroll
         for (int b = 0; b < 8; ++b) acc[a][b] = fmaf(wv[a], qv[b], acc[a][b]);
     }
@@ -569,8 +569,8 @@ product_key_dkeys_kernel(const int64_t* __restrict__ idx, const float* __restric
   // partial[block][table][side][half]
   float* dst = partial + ((size_t)blockIdx.x * 2 + table) * side * half;
 #pragma unroll
-  for (int a = 0; a < 16; ++a) {
-    const int row = r0 + tr * 16 + a;
+  for (int a = 0; a < 8; ++a) {
+    const int row = r0 + tr * 8 + a;
     if (row >= side) continue;
 #pragma unroll
     for (int b = 0; b < 8; ++b) {
