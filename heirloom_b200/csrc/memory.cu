@@ -1013,7 +1013,7 @@ int hl_memory_weighted_value_backward(hl_ctx* ctx, const int64_t* indices, const
   if (rc != HL_OK) return rc;
   HL_REQUIRE(rows > 0 && dim % 4 == 0, "hl_memory_weighted_value_backward: non-zero rows/row_dim, row_dim a multiple of 4");
   const long long n = (long long)tokens * top_k;
-  if (grad_values && n >= 32768 && dim <= 1024 && rows < (1 << 30)) {
+  if (grad_values && n >= 32768 && n < (1ll << 31) - 64 && dim <= 1024 && rows < (1 << 30)) {
     // row order (see weighted_value_bwd_sorted_kernel).  Scratch: keys and events in and out, and the sort's own space.
     int end_bit = 1;
     while ((1ll << end_bit) <= rows) ++end_bit;  // the sentinel key `rows` must sort last
