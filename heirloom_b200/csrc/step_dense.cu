@@ -76,6 +76,10 @@ struct hl_decoder {
   std::vector<__nv_bfloat16*> x;  // x[l] is the input of block l; x[L] the final residual stream
   std::vector<LayerActs> la;
   __nv_bfloat16 *z = nullptr, *dlogits = nullptr, *dxb = nullptr, *dh = nullptr, *dob = nullptr, *dqkv = nullptr;
+  // head sizes other than 64 on the bf16 route: attention runs through the f32 kernels on these shared buffers
+  bool flash_ok = true;
+  float *fa_q = nullptr, *fa_k = nullptr, *fa_v = nullptr, *fa_o = nullptr, *fa_probs = nullptr, *fa_dq = nullptr,
+        *fa_dk = nullptr, *fa_dv = nullptr, *fa_do = nullptr;
   float *logits = nullptr, *meanf = nullptr, *rstdf = nullptr, *dx0 = nullptr, *dx1 = nullptr, *dtmp = nullptr;
   int64_t *tokens = nullptr, *targets = nullptr;
   float* loss_dev = nullptr;
@@ -313,6 +317,12 @@ int plan_activations(hl_decoder* m, bool measure_only, size_t* bytes_out) {
   m->dh = carve<__nv_bfloat16>(cur, N * F);
   m->dob = carve<__nv_bfloat16>(cur, N * d);
   m->dqkv = carve<__nv_bfloat16>(cur, N * 3 * d);
+  if (!m->flash_ok) {
+    m->fa_q = carve<float>(cur, N * d); m->fa_k = carve<float>(cur, N * d); m->fa_v = carve<float>(cur, N * d);
+    m->fa_o = carve<float>(cur, N * d); m->fa_do = carve<float>(cur, N * d);
+    m->fa_dq = carve<float>(cur, N * d); m->fa_dk = carve<float>(cur, N * d); m->fa_dv = carve<float>(cur, N * d);
+    m->fa_probs = carve<float>(cur, (size_t)c.batch * c.n_heads * c.context * c.context);
+  }
   plan_memory_buffers(m, cur);
   m->tokens = carve<int64_t>(cur, N);
   m->targets = carve<int64_t>(cur, N);
@@ -431,6 +441,66 @@ int zero_memory_table_grads(hl_decoder* m) {
   return HL_OK;
 }
 
+// ---- attention for head sizes the tcgen05 kernels are not built for (they take head_dim 64) ----------------------
+// The bf16 q, k, v are widened to f32 (exact), the f32 attention kernels run on them and their results are rounded to
+// bf16 where the flash route stores bf16 (attention output, dQ/dK/dV).  Probabilities are not kept per layer: the
+// backward pass runs the forward kernel again into the shared probability buffer.
+__global__ void rows_bf16_to_f32_kernel(const __nv_bfloat16* __restrict__ src, long long ld_src, float* __restrict__ dst,
+                                        long long rows, int cols) {
+  const long long n = rows * cols;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
+    dst[i] = __bfloat162float(src[(i / cols) * ld_src + (i % cols)]);
+}
+__global__ void rows_f32_to_bf16_kernel(const float* __restrict__ src, __nv_bfloat16* __restrict__ dst, long long ld_dst,
+                                        long long rows, int cols) {
+  const long long n = rows * cols;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
+    dst[(i / cols) * ld_dst + (i % cols)] = __float2bfloat16_rn(src[i]);
+}
+
+int widen_rows(hl_ctx* ctx, const __nv_bfloat16* src, long long ld_src, float* dst, long long rows, int cols) {
+  const long long want = ceil_div_ll(rows * cols, 256);
+  rows_bf16_to_f32_kernel<<<(unsigned)std::min<long long>(want, (long long)ctx->sm_count * 16), 256, 0, ctx->stream>>>(
+      src, ld_src, dst, rows, cols);
+  HL_LAUNCH_CHECK("rows_bf16_to_f32_kernel");
+  count_launch(ctx);
+  return HL_OK;
+}
+int narrow_rows(hl_ctx* ctx, const float* src, __nv_bfloat16* dst, long long ld_dst, long long rows, int cols) {
+  const long long want = ceil_div_ll(rows * cols, 256);
+  rows_f32_to_bf16_kernel<<<(unsigned)std::min<long long>(want, (long long)ctx->sm_count * 16), 256, 0, ctx->stream>>>(
+      src, dst, ld_dst, rows, cols);
+  HL_LAUNCH_CHECK("rows_f32_to_bf16_kernel");
+  count_launch(ctx);
+  return HL_OK;
+}
+
+int attention_forward_wide(hl_decoder* m, const __nv_bfloat16* qkv, __nv_bfloat16* out) {
+  hl_ctx* ctx = m->ctx;
+  const hl_decoder_config& c = m->cfg;
+  const int N = m->N, d = c.d_model;
+  HL_TRY(widen_rows(ctx, qkv, 3 * d, m->fa_q, N, d));
+  HL_TRY(widen_rows(ctx, qkv + d, 3 * d, m->fa_k, N, d));
+  HL_TRY(widen_rows(ctx, qkv + 2 * d, 3 * d, m->fa_v, N, d));
+  HL_TRY(hl_causal_attention_f32_forward(ctx, m->fa_q, m->fa_k, m->fa_v, m->fa_o, m->fa_probs, c.batch, c.context, d, c.n_heads));
+  if (out) HL_TRY(narrow_rows(ctx, m->fa_o, out, d, N, d));
+  return HL_OK;
+}
+
+int attention_backward_wide(hl_decoder* m, const __nv_bfloat16* qkv, const __nv_bfloat16* dout, __nv_bfloat16* dqkv) {
+  hl_ctx* ctx = m->ctx;
+  const hl_decoder_config& c = m->cfg;
+  const int N = m->N, d = c.d_model;
+  HL_TRY(attention_forward_wide(m, qkv, nullptr));  // q, k, v and the probabilities again
+  HL_TRY(widen_rows(ctx, dout, d, m->fa_do, N, d));
+  HL_TRY(hl_causal_attention_f32_backward(ctx, m->fa_q, m->fa_k, m->fa_v, m->fa_probs, m->fa_do, m->fa_dq, m->fa_dk, m->fa_dv,
+                                          c.batch, c.context, d, c.n_heads));
+  HL_TRY(narrow_rows(ctx, m->fa_dq, dqkv, 3 * d, N, d));
+  HL_TRY(narrow_rows(ctx, m->fa_dk, dqkv + d, 3 * d, N, d));
+  HL_TRY(narrow_rows(ctx, m->fa_dv, dqkv + 2 * d, 3 * d, N, d));
+  return HL_OK;
+}
+
 int forward(hl_decoder* m) {
   hl_ctx* ctx = m->ctx;
   const hl_decoder_config& c = m->cfg;
@@ -444,7 +514,8 @@ int forward(hl_decoder* m) {
     LayerActs& a = m->la[l];
     HL_TRY(layer_norm_forward_impl(ctx, m->x[l], HL_BF16, P + o.ln1g, P + o.ln1b, a.a, HL_BF16, a.mean1, a.rstd1, N, d, 1e-5f));
     HL_TRY(g.run(N, 3 * d, d, a.a, d, HL_K_MAJOR, W + o.wqkv, d, HL_K_MAJOR, a.qkv, 3 * d, HL_BF16, HL_EPI_BIAS, P + o.bqkv));
-    HL_TRY(flash_attention_forward_impl(ctx, a.qkv, a.qkv + d, a.qkv + 2 * d, 3 * d, a.o, d, a.lse, B, T, H, d / H));
+    if (m->flash_ok) HL_TRY(flash_attention_forward_impl(ctx, a.qkv, a.qkv + d, a.qkv + 2 * d, 3 * d, a.o, d, a.lse, B, T, H, d / H));
+    else HL_TRY(attention_forward_wide(m, a.qkv, a.o));
     HL_TRY(g.run(N, d, d, a.o, d, HL_K_MAJOR, W + o.wo, d, HL_K_MAJOR, a.r, d, HL_BF16, HL_EPI_BIAS_RESIDUAL, P + o.bo,
                  m->x[l], d));
     HL_TRY(layer_norm_forward_impl(ctx, a.r, HL_BF16, P + o.ln2g, P + o.ln2b, a.c, HL_BF16, a.mean2, a.rstd2, N, d, 1e-5f));
@@ -605,12 +676,14 @@ int backward(hl_decoder* m) {
     std::swap(dx, dx_next);  // dx is now dL/dr
     HL_TRY(g.run(d, d, N, m->dxb, d, HL_MN_MAJOR, a.o, d, HL_MN_MAJOR, G + o.wo, d, HL_F32));
     HL_TRY(g.run(N, d, d, m->dxb, d, HL_K_MAJOR, W + o.wo, d, HL_MN_MAJOR, m->dob, d, HL_BF16));
-    {
+    if (m->flash_ok) {
       const size_t need = flash_attention_backward_scratch_bytes(B, T, H, d / H);
       if (need > ctx->workspace_bytes) HL_TRY(ensure_workspace(ctx, need));
       HL_TRY(flash_attention_backward_impl(ctx, a.qkv, a.qkv + d, a.qkv + 2 * d, 3 * d, a.o, d, m->dob, d, a.lse, m->dqkv,
                                            m->dqkv + d, m->dqkv + 2 * d, 3 * d, B, T, H, d / H, ctx->workspace,
                                            ctx->workspace_bytes));
+    } else {
+      HL_TRY(attention_backward_wide(m, a.qkv, m->dob, m->dqkv));
     }
     HL_TRY(g.run(3 * d, d, N, m->dqkv, 3 * d, HL_MN_MAJOR, a.a, d, HL_MN_MAJOR, G + o.wqkv, d, HL_F32));
     HL_TRY(bias_grad_impl(ctx, m->dqkv, HL_BF16, G + o.bqkv, N, 3 * d));
@@ -888,7 +961,6 @@ static int decoder_create_impl(hl_ctx* ctx, const hl_decoder_config* cfg, const 
              "hl_decoder_create: precision must be HL_PRECISION_F32 or HL_PRECISION_AMP_BF16");
   const bool amp = cfg->precision == HL_PRECISION_AMP_BF16;
   if (amp) {
-    HL_REQUIRE(cfg->d_model / cfg->n_heads == 64, "hl_decoder_create: the bf16 route needs head_dim 64");
     HL_REQUIRE(cfg->d_model % 8 == 0 && cfg->d_ff % 8 == 0 && cfg->vocab % 8 == 0 && cfg->d_model <= 1024,
                "hl_decoder_create: d_model (<= 1024), d_ff and vocab must be multiples of 8");
   } else {
@@ -899,6 +971,7 @@ static int decoder_create_impl(hl_ctx* ctx, const hl_decoder_config* cfg, const 
   m->ctx = ctx;
   m->cfg = *cfg;
   m->N = cfg->batch * cfg->context;
+  m->flash_ok = cfg->d_model / cfg->n_heads == 64;
   if (mem && mem->n_memory_layers > 0) {
     m->has_memory = true;
     m->mem = *mem;

@@ -32,8 +32,9 @@ def test_parameter_names_follow_state_dict_order():
     model.close()
 
 
-def test_one_step_loss_and_gradients_match_the_amp_oracle():
-    kw = dict(vocab=512, d_model=128, n_layers=2, n_heads=2, d_ff=256, context=128)
+@pytest.mark.parametrize("n_heads", [2, 4, 1])  # head_dim 64 (tcgen05 flash kernels), 32 and 128 (f32 attention kernels)
+def test_one_step_loss_and_gradients_match_the_amp_oracle(n_heads):
+    kw = dict(vocab=512, d_model=128, n_layers=2, n_heads=n_heads, d_ff=256, context=128)
     c, model, ocfg, params = make(kw, 2)
     rng = np.random.default_rng(3)
     tok = ho.zipf_tokens(rng, ocfg.vocab, (2, 129))
