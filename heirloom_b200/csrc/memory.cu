@@ -685,3 +685,511 @@ __global__ void weighted_value_fwd_kernel(const int64_t* __restrict__ idx, const
     *reinterpret_cast<float4*>(out + (size_t)token * dim + c) = make_float4((float)a0, (float)a1, (float)a2, (float)a3);
   }
 }
+
+// dw[t,k] = dout[t] . V[idx[t,k]];  dV[idx[t,k],:] += w[t,k] dout[t,:] (f32 atomics, repeats accumulate)
+// (src/tensor/autograd.rs:2263-2323).
+__global__ void weighted_value_bwd_kernel(const int64_t* __restrict__ idx, const float* __restrict__ weights,
+                                          const float* __restrict__ values, const float* __restrict__ grad_out,
+                                          float* __restrict__ dweights, float* __restrict__ dvalues, int tokens, int top_k,
+                                          int rows, int dim) {
+  const int lane = threadIdx.x & 31;
+  const int token = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (token >= tokens) return;
+  const float* go = grad_out + (size_t)token * dim;
+  for (int k = 0; k < top_k; ++k) {
+    const long long r = idx[(size_t)token * top_k + k];
+    if (r < 0 || r >= rows) continue;
+    const float w = weights[(size_t)token * top_k + k];
+    double dot = 0.0;
+    for (int c = lane * 4; c < dim; c += 128) {
+      const float4 g = *reinterpret_cast<const float4*>(go + c);
+      if (dweights) {
+        const float4 v = __ldg(reinterpret_cast<const float4*>(values + (size_t)r * dim + c));
+        dot += (double)g.x * v.x + (double)g.y * v.y + (double)g.z * v.z + (double)g.w * v.w;
+      }
+      if (dvalues) atomicAdd(reinterpret_cast<float4*>(dvalues + (size_t)r * dim + c), make_float4(w * g.x, w * g.y, w * g.z, w * g.w));
+    }
+    if (dweights) {
+      dot = warp_sum(dot);
+      if (lane == 0) dweights[(size_t)token * top_k + k] = (float)dot;
+    }
+  }
+}
+
+// ---- weighted value backward in row order ---------------------------------------------------------------------
+// With many more (token, slot) events than distinct rows (about 26 events per row at the memory-transformer size),
+// per-event 16-byte atomics pile onto hot rows in L2.  Events are therefore sorted by row (radix sort over as many key
+// bits as the row count needs); a warp takes 32 consecutive sorted events, keeps the value row of the current run and
+// the run's gradient sum in registers, and issues one set of atomics per run (and per chunk boundary).  The weight
+// gradients, dot(grad_out[token], values[row]), come from the same pass: one 2 KB read of grad_out per event is all
+// the traffic that does not stay in registers.
+__global__ void value_event_keys_kernel(const int64_t* __restrict__ idx, long long n, int rows, int* __restrict__ keys,
+                                        int* __restrict__ events) {
+  const long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const long long r = idx[i];
+  keys[i] = (r < 0 || r >= rows) ? rows : (int)r;  // out-of-range slots sort behind every row and are skipped
+  events[i] = (int)i;
+}
+
+template <int VPL>  // 16-byte pieces of a row per lane: dim <= VPL * 128
+__global__ void __launch_bounds__(128)
+weighted_value_bwd_sorted_kernel(const int* __restrict__ keys, const int* __restrict__ events,
+                                 const float* __restrict__ weights, const float* __restrict__ values,
+                                 const float* __restrict__ grad_out, float* __restrict__ dweights,
+                                 float* __restrict__ dvalues, long long n, int top_k, int rows, int dim) {
+  const int lane = threadIdx.x & 31;
+  const long long base = ((long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)) * 32;
+  if (base >= n) return;
+  const int groups = dim / 4;
+  int my_key = rows, my_event = 0;
+  float my_w = 0.f;
+  if (base + lane < n) {
+    my_key = keys[base + lane];
+    my_event = events[base + lane];
+    if (my_key < rows) my_w = weights[my_event];
+  }
+  float4 acc[VPL], vrow[VPL];
+#pragma unroll
+  for (int u = 0; u < VPL; ++u) acc[u] = vrow[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+  int cur = -1;
+  auto flush = [&]() {
+    if (cur < 0 || !dvalues) return;
+#pragma unroll
+    for (int u = 0; u < VPL; ++u) {
+      const int gi = u * 32 + lane;
+      if (gi < groups) atomicAdd(reinterpret_cast<float4*>(dvalues + (size_t)cur * dim) + gi, acc[u]);
+      acc[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+  };
+  for (int i = 0; i < 32; ++i) {
+    const int key = __shfl_sync(0xffffffffu, my_key, i);
+    if (key >= rows) break;  // sorted: nothing valid follows
+    const int event = __shfl_sync(0xffffffffu, my_event, i);
+    const float w = __shfl_sync(0xffffffffu, my_w, i);
+    if (key != cur) {
+      flush();
+      cur = key;
+      if (dweights) {
+#pragma unroll
+        for (int u = 0; u < VPL; ++u) {
+          const int gi = u * 32 + lane;
+          if (gi < groups) vrow[u] = __ldg(reinterpret_cast<const float4*>(values + (size_t)key * dim) + gi);
+        }
+      }
+    }
+    const float4* go = reinterpret_cast<const float4*>(grad_out + (size_t)(event / top_k) * dim);
+    float share = 0.f;  // this lane's part of the dot product in f32, the 32 parts are summed in f64
+#pragma unroll
+    for (int u = 0; u < VPL; ++u) {
+      const int gi = u * 32 + lane;
+      if (gi < groups) {
+        const float4 g = __ldg(go + gi);
+        share = fmaf(g.x, vrow[u].x, share); share = fmaf(g.y, vrow[u].y, share);
+        share = fmaf(g.z, vrow[u].z, share); share = fmaf(g.w, vrow[u].w, share);
+        acc[u].x = fmaf(w, g.x, acc[u].x); acc[u].y = fmaf(w, g.y, acc[u].y);
+        acc[u].z = fmaf(w, g.z, acc[u].z); acc[u].w = fmaf(w, g.w, acc[u].w);
+      }
+    }
+    if (dweights) {
+      const double dot = warp_sum((double)share);
+      if (lane == 0) dweights[event] = (float)dot;
+    }
+  }
+  flush();
+}
+
+// ---- access counts: counts[r] += occurrences of r among the selected rows (kernels.ptx:813-886) ---------------
+__global__ void access_count_rows_kernel(const int64_t* __restrict__ selected, long long n, int rows,
+                                         unsigned long long* __restrict__ counts, int* __restrict__ status) {
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += stride) {
+    const long long r = selected[i];
+    if (r < 0 || r >= rows) { atomicExch(status + ST_BAD_INDEX, 1); continue; }
+    atomicAdd(counts + r, 1ull);
+  }
+}
+
+// ---- row-set AdamW (src/nn.rs:2256-2323, :2899-2939; kernels.ptx:537-811) -----------------------------------
+__global__ void mark_rows_kernel(const int64_t* __restrict__ selected, long long n, unsigned char* __restrict__ flags,
+                                 const unsigned char* __restrict__ row_mask, int rows, int* __restrict__ status) {
+  const long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const long long r = selected[i];
+  if (r < 0 || r >= rows) { atomicExch(status + ST_BAD_INDEX, 1); return; }
+  if (row_mask == nullptr || row_mask[r]) flags[r] = 1;
+}
+
+__device__ __forceinline__ void adamw_one(float& p, float g, float& m, float& v, const hl_adamw_params& hp) {
+  const float gd = __fadd_rn(__fmul_rn(g, hp.clip_scale), __fmul_rn(p, hp.weight_decay));
+  m = __fadd_rn(__fmul_rn(hp.beta1, m), __fmul_rn(__fsub_rn(1.0f, hp.beta1), gd));
+  v = __fadd_rn(__fmul_rn(hp.beta2, v), __fmul_rn(__fsub_rn(1.0f, hp.beta2), __fmul_rn(gd, gd)));
+  const float upd = __fdiv_rn(__fdiv_rn(m, hp.bias_correction1), __fadd_rn(__fsqrt_rn(__fdiv_rn(v, hp.bias_correction2)), hp.eps));
+  p = __fsub_rn(p, __fmul_rn(hp.lr, upd));
+}
+
+// One warp per flagged row; clears the flag and (optionally) the gradient row it consumed.
+__global__ void sparse_adamw_rows_kernel(float* __restrict__ param, float* __restrict__ grad, float* __restrict__ m,
+                                         float* __restrict__ v, unsigned char* __restrict__ flags, int rows, int row_dim,
+                                         const hl_adamw_params hp, int zero_grad_rows) {
+  const int lane = threadIdx.x & 31;
+  const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= rows || !flags[row]) return;
+  const size_t base = (size_t)row * row_dim;
+  for (int c = lane; c < row_dim; c += 32) {
+    float p = param[base + c], mm = m[base + c], vv = v[base + c];
+    adamw_one(p, grad[base + c], mm, vv, hp);
+    param[base + c] = p; m[base + c] = mm; v[base + c] = vv;
+    if (zero_grad_rows) grad[base + c] = 0.f;
+  }
+  __syncwarp();
+  if (lane == 0) flags[row] = 0;
+}
+
+// Sum of squares of the flagged gradient rows (a set: a row counts once however often it was selected); one
+// warp per flagged row, f64 partial per warp, flags cleared on the way out.
+__global__ void flagged_rows_sum_squares_kernel(const float* __restrict__ grad, unsigned char* __restrict__ flags, int rows,
+                                                int row_dim, double* __restrict__ out) {
+  const int lane = threadIdx.x & 31;
+  const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= rows || !flags[row]) return;
+  const float* g = grad + (size_t)row * row_dim;
+  double s = 0.0;
+  for (int c = lane; c < row_dim; c += 32) s += (double)g[c] * (double)g[c];
+  s = warp_sum(s);
+  __syncwarp();
+  if (lane == 0) {
+    atomicAdd(out, s);
+    flags[row] = 0;
+  }
+}
+
+// Ascending indices of the non-zero bytes of a mask, and their count.  One CTA: every thread counts a contiguous
+// span, an exclusive scan over the spans gives its write position.
+__global__ void __launch_bounds__(1024)
+mask_to_indices_kernel(const unsigned char* __restrict__ mask, int rows, int64_t* __restrict__ out, int* __restrict__ count) {
+  __shared__ int span_start[1025];
+  const int per = (rows + 1023) / 1024;
+  const int lo = min(rows, (int)threadIdx.x * per), hi = min(rows, lo + per);
+  int mine = 0;
+  for (int r = lo; r < hi; ++r) mine += mask[r] != 0;
+  span_start[threadIdx.x + 1] = mine;
+  if (threadIdx.x == 0) span_start[0] = 0;
+  __syncthreads();
+  if (threadIdx.x == 0)
+    for (int i = 1; i <= 1024; ++i) span_start[i] += span_start[i - 1];
+  __syncthreads();
+  int at = span_start[threadIdx.x];
+  for (int r = lo; r < hi; ++r)
+    if (mask[r]) out[at++] = r;
+  if (threadIdx.x == 0) *count = span_start[1024];
+}
+
+// dst[i,:] = src[idx[i],:] (gather) or dst[idx[i],:] = src[i,:] (scatter); one warp per row, 16-byte accesses.
+__global__ void move_rows_kernel(const float* __restrict__ src, const int64_t* __restrict__ idx, const int* __restrict__ count_dev,
+                                 int n_max, int dim, float* __restrict__ dst, int scatter) {
+  const int lane = threadIdx.x & 31;
+  const int n = count_dev ? min(*count_dev, n_max) : n_max;
+  for (int i = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); i < n; i += gridDim.x * (blockDim.x >> 5)) {
+    const size_t row = (size_t)idx[i];
+    const float4* s4 = reinterpret_cast<const float4*>(src + (scatter ? (size_t)i : row) * dim);
+    float4* d4 = reinterpret_cast<float4*>(dst + (scatter ? row : (size_t)i) * dim);
+    for (int c = lane; c < dim / 4; c += 32) d4[c] = s4[c];
+  }
+}
+
+int check_memory_dims(int tokens, int top_k, int dim, const char* who) {
+  HL_REQUIRE(tokens > 0 && top_k > 0 && dim > 0, std::string(who) + ": requires non-zero tokens/top_k/dim");
+  return HL_OK;
+}
+
+}  // namespace
+}  // namespace hl
+
+using namespace hl;
+
+extern "C" {
+
+int hl_topk_rows_f32(hl_ctx* ctx, const float* scores, int64_t* out, int rows, int cols, int k) {
+  HL_REQUIRE(ctx && scores && out, "hl_topk_rows_f32: null argument");
+  HL_REQUIRE(rows > 0 && cols > 0, "hl_topk_rows_f32: requires non-zero rows/cols");
+  HL_REQUIRE(k > 0 && k <= cols, "hl_topk_rows_f32: k must be in [1, cols]");
+  HL_REQUIRE(cols <= 2048, "hl_topk_rows_f32: at most 2048 columns");
+  topk_rows_kernel<<<ceil_div(rows, 4), 128, 0, ctx->stream>>>(scores, out, rows, cols, k);
+  HL_LAUNCH_CHECK("topk_rows_kernel");
+  count_launch(ctx);
+  return HL_OK;
+}
+
+int hl_product_key_side_scores_f32(hl_ctx* ctx, const float* query, long long ld_query, const float* left_keys,
+                                   const float* right_keys, float* left_scores, float* right_scores, int tokens, int side,
+                                   int key_dim) {
+  HL_REQUIRE(ctx && query && left_keys && right_keys && left_scores && right_scores, "hl_product_key_side_scores_f32: null argument");
+  HL_REQUIRE(tokens > 0 && side > 0 && key_dim > 0, "hl_product_key_side_scores_f32: requires non-zero sizes");
+  HL_REQUIRE(key_dim % 2 == 0, "product-key memory lookup requires even memory_key_dim, got " + std::to_string(key_dim));
+  HL_REQUIRE(ld_query >= key_dim, "hl_product_key_side_scores_f32: query row stride smaller than key_dim");
+  const int half = key_dim / 2;
+  dim3 grid(ceil_div(side, SS_K), ceil_div(tokens, SS_T));
+  side_scores_kernel<<<grid, 256, 0, ctx->stream>>>(query, ld_query, 0, left_keys, left_scores, tokens, side, half);
+  HL_LAUNCH_CHECK("side_scores_kernel");
+  side_scores_kernel<<<grid, 256, 0, ctx->stream>>>(query, ld_query, half, right_keys, right_scores, tokens, side, half);
+  HL_LAUNCH_CHECK("side_scores_kernel");
+  count_launch(ctx, 2);
+  return HL_OK;
+}
+
+int hl_product_key_topk_from_side_scores(hl_ctx* ctx, const float* left_scores, const float* right_scores, int64_t* out,
+                                         int tokens, int side, int top_k, int beam) {
+  HL_REQUIRE(ctx && left_scores && right_scores && out, "hl_product_key_topk_from_side_scores: null argument");
+  HL_REQUIRE(tokens > 0 && side > 0, "hl_product_key_topk_from_side_scores: requires non-zero tokens/side");
+  HL_REQUIRE(side <= 2048, "hl_product_key_topk_from_side_scores: side must be at most 2048");
+  HL_REQUIRE(beam > 0 && beam <= 32 && beam <= side, "hl_product_key_topk_from_side_scores: beam must be in [1, min(32, side)]");
+  HL_REQUIRE(top_k > 0 && top_k <= beam * beam, "hl_product_key_topk_from_side_scores: top_k must be in [1, beam^2]");
+  if (side <= 512)
+    product_key_topk_kernel<16><<<ceil_div(tokens, 4), 128, 0, ctx->stream>>>(left_scores, right_scores, out, tokens, side,
+                                                                              top_k, beam, ctx->status_dev);
+  else
+    product_key_topk_kernel<PK_MAX_PER_LANE><<<ceil_div(tokens, 4), 128, 0, ctx->stream>>>(
+        left_scores, right_scores, out, tokens, side, top_k, beam, ctx->status_dev);
+  HL_LAUNCH_CHECK("product_key_topk_kernel");
+  count_launch(ctx);
+  return HL_OK;
+}
+
+int hl_product_key_split_rows(hl_ctx* ctx, const int64_t* rows, int64_t* left, int64_t* right, long long n, int side) {
+  HL_REQUIRE(ctx && rows && left && right, "hl_product_key_split_rows: null argument");
+  HL_REQUIRE(n > 0 && side > 0, "hl_product_key_split_rows: requires non-zero rows/side");
+  split_rows_kernel<<<(unsigned)ceil_div_ll(n, 256), 256, 0, ctx->stream>>>(rows, left, right, n, side);
+  HL_LAUNCH_CHECK("split_rows_kernel");
+  count_launch(ctx);
+  return HL_OK;
+}
+
+int hl_memory_selected_scores_forward(hl_ctx* ctx, const int64_t* indices, const float* query, long long ld_query,
+                                      const float* left_or_keys, const float* right_keys, float* scores, int tokens,
+                                      int top_k, int side, int key_dim, int slots) {
+  HL_REQUIRE(ctx && indices && query && left_or_keys && scores, "hl_memory_selected_scores_forward: null argument");
+  int rc = check_memory_dims(tokens, top_k, key_dim, "hl_memory_selected_scores_forward");
+  if (rc != HL_OK) return rc;
+  HL_REQUIRE(side == 0 || (right_keys && key_dim % 2 == 0 && (long long)side * side == slots),
+             "hl_memory_selected_scores_forward: product-key mode needs both half tables, even key_dim and square slots");
+  selected_scores_fwd_kernel<<<ceil_div(tokens, 4), 128, 0, ctx->stream>>>(indices, query, ld_query, left_or_keys, right_keys,
+                                                                           scores, tokens, top_k, side, key_dim, slots,
+                                                                           ctx->status_dev);
+  HL_LAUNCH_CHECK("selected_scores_fwd_kernel");
+  count_launch(ctx);
+  return HL_OK;
+}
+
+int hl_memory_selected_scores_backward(hl_ctx* ctx, const int64_t* indices, const float* query, long long ld_query,
+                                       const float* left_or_keys, const float* right_keys, const float* grad_scores,
+                                       float* grad_query, long long ld_grad_query, float* grad_left_or_keys,
+                                       float* grad_right_keys, int tokens, int top_k, int side, int key_dim, int slots) {
+  HL_REQUIRE(ctx && indices && query && left_or_keys && grad_scores, "hl_memory_selected_scores_backward: null argument");
+  int rc = check_memory_dims(tokens, top_k, key_dim, "hl_memory_selected_scores_backward");
+  if (rc != HL_OK) return rc;
+  HL_REQUIRE(side == 0 || (right_keys && key_dim % 2 == 0), "hl_memory_selected_scores_backward: product-key mode needs both half tables");
+  selected_scores_bwd_kernel<<<ceil_div(tokens, 4), 128, 0, ctx->stream>>>(
+      indices, query, ld_query, left_or_keys, right_keys, grad_scores, grad_query, ld_grad_query, grad_left_or_keys,
+      grad_right_keys, tokens, top_k, side, key_dim, slots);
+  HL_LAUNCH_CHECK("selected_scores_bwd_kernel");
+  count_launch(ctx);
+  if (side > 0 && (grad_left_or_keys || grad_right_keys)) {
+    const int half = key_dim / 2;
+    const size_t smem = sizeof(float) * (size_t)DK_TOKENS * (DK_ROWS + DK_COLS);
+    const int col_blocks = ceil_div(half, DK_COLS), row_blocks = ceil_div(side, DK_ROWS);
+    const int token_blocks =
+        std::max(1, std::min(ceil_div(tokens, 64), std::max(1, (2 * ctx->sm_count) / (2 * col_blocks * row_blocks))));
+    const int tokens_per_block = ceil_div(tokens, token_blocks);
+    rc = ensure_workspace(ctx, sizeof(float) * (size_t)token_blocks * 2 * side * half);
+    if (rc != HL_OK) return rc;
+    float* partial = reinterpret_cast<float*>(ctx->workspace);
+    HL_CUDA(cudaFuncSetAttribute(product_key_dkeys_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    product_key_dkeys_kernel<<<dim3(token_blocks, col_blocks * row_blocks, 2), 256, smem, ctx->stream>>>(
+        indices, query, ld_query, grad_scores, partial, tokens, top_k, side, half, slots, tokens_per_block, col_blocks);
+    HL_LAUNCH_CHECK("product_key_dkeys_kernel");
+    const size_t total = 2 * (size_t)side * half;
+    fold_key_partials_kernel<<<(unsigned)((total + 255) / 256), 256, 0, ctx->stream>>>(partial, grad_left_or_keys, grad_right_keys,
+                                                                                       token_blocks, side, half);
+    HL_LAUNCH_CHECK("fold_key_partials_kernel");
+    count_launch(ctx, 2);
+  }
+  return HL_OK;
+}
+
+int hl_softmax_rows_f32(hl_ctx* ctx, const float* x, float* y, int rows, int cols) {
+  HL_REQUIRE(ctx && x && y, "hl_softmax_rows_f32: null argument");
+  HL_REQUIRE(rows > 0 && cols > 0, "hl_softmax_rows_f32: requires non-zero rows/cols");
+  softmax_rows_kernel<<<ceil_div(rows, 4), 128, 0, ctx->stream>>>(x, y, rows, cols);
+  HL_LAUNCH_CHECK("softmax_rows_kernel");
+  count_launch(ctx);
+  return HL_OK;
+}
+
+int hl_softmax_rows_backward_f32(hl_ctx* ctx, const float* y, const float* grad_y, float* grad_x, int rows, int cols) {
+  HL_REQUIRE(ctx && y && grad_y && grad_x, "hl_softmax_rows_backward_f32: null argument");
+  HL_REQUIRE(rows > 0 && cols > 0, "hl_softmax_rows_backward_f32: requires non-zero rows/cols");
+  softmax_rows_bwd_kernel<<<ceil_div(rows, 4), 128, 0, ctx->stream>>>(y, grad_y, grad_x, rows, cols);
+  HL_LAUNCH_CHECK("softmax_rows_bwd_kernel");
+  count_launch(ctx);
+  return HL_OK;
+}
+
+int hl_memory_weighted_value_forward(hl_ctx* ctx, const int64_t* indices, const float* weights, const float* values,
+                                     float* out, int tokens, int top_k, int rows, int dim) {
+  HL_REQUIRE(ctx && indices && weights && values && out, "hl_memory_weighted_value_forward: null argument");
+  int rc = check_memory_dims(tokens, top_k, dim, "hl_memory_weighted_value_forward");
+  if (rc != HL_OK) return rc;
+  HL_REQUIRE(rows > 0 && dim % 4 == 0, "hl_memory_weighted_value_forward: non-zero rows/row_dim, row_dim a multiple of 4");
+  weighted_value_fwd_kernel<<<ceil_div(tokens, 4), 128, 0, ctx->stream>>>(indices, weights, values, out, tokens, top_k, rows,
+                                                                          dim, ctx->status_dev);
+  HL_LAUNCH_CHECK("weighted_value_fwd_kernel");
+  count_launch(ctx);
+  return HL_OK;
+}
+
+int hl_memory_weighted_value_backward(hl_ctx* ctx, const int64_t* indices, const float* weights, const float* values,
+                                      const float* grad_out, float* grad_weights, float* grad_values, int tokens,
+                                      int top_k, int rows, int dim) {
+  HL_REQUIRE(ctx && indices && weights && values && grad_out, "hl_memory_weighted_value_backward: null argument");
+  int rc = check_memory_dims(tokens, top_k, dim, "hl_memory_weighted_value_backward");
+  if (rc != HL_OK) return rc;
+  HL_REQUIRE(rows > 0 && dim % 4 == 0, "hl_memory_weighted_value_backward: non-zero rows/row_dim, row_dim a multiple of 4");
+  const long long n = (long long)tokens * top_k;
+  if (grad_values && n >= 32768 && n < (1ll << 31) - 64 && dim <= 1024 && rows < (1 << 30)) {
+    // row order (see weighted_value_bwd_sorted_kernel).  Scratch: keys and events in and out, and the sort's own space.
+    int end_bit = 1;
+    while ((1ll << end_bit) <= rows) ++end_bit;  // the sentinel key `rows` must sort last
+    size_t sort_bytes = 0;
+    HL_CUDA(cub::DeviceRadixSort::SortPairs(nullptr, sort_bytes, (const int*)nullptr, (int*)nullptr, (const int*)nullptr,
+                                            (int*)nullptr, (int)n, 0, end_bit, ctx->stream));
+    const size_t arr = ((size_t)n * sizeof(int) + 255) & ~size_t(255);
+    rc = ensure_workspace(ctx, 4 * arr + sort_bytes);
+    if (rc != HL_OK) return rc;
+    uint8_t* ws = reinterpret_cast<uint8_t*>(ctx->workspace);
+    int *keys_in = reinterpret_cast<int*>(ws), *ev_in = reinterpret_cast<int*>(ws + arr);
+    int *keys = reinterpret_cast<int*>(ws + 2 * arr), *ev = reinterpret_cast<int*>(ws + 3 * arr);
+    value_event_keys_kernel<<<(unsigned)ceil_div_ll(n, 256), 256, 0, ctx->stream>>>(indices, n, rows, keys_in, ev_in);
+    HL_LAUNCH_CHECK("value_event_keys_kernel");
+    HL_CUDA(cub::DeviceRadixSort::SortPairs(ws + 4 * arr, sort_bytes, keys_in, keys, ev_in, ev, (int)n, 0, end_bit, ctx->stream));
+    const unsigned blocks = (unsigned)ceil_div_ll(ceil_div_ll(n, 32), 4);
+    if (dim <= 512)
+      weighted_value_bwd_sorted_kernel<4><<<blocks, 128, 0, ctx->stream>>>(keys, ev, weights, values, grad_out, grad_weights,
+                                                                           grad_values, n, top_k, rows, dim);
+    else
+      weighted_value_bwd_sorted_kernel<8><<<blocks, 128, 0, ctx->stream>>>(keys, ev, weights, values, grad_out, grad_weights,
+                                                                           grad_values, n, top_k, rows, dim);
+    HL_LAUNCH_CHECK("weighted_value_bwd_sorted_kernel");
+    count_launch(ctx, 3);
+    return HL_OK;
+  }
+  weighted_value_bwd_kernel<<<ceil_div(tokens, 4), 128, 0, ctx->stream>>>(indices, weights, values, grad_out, grad_weights,
+                                                                          grad_values, tokens, top_k, rows, dim);
+  HL_LAUNCH_CHECK("weighted_value_bwd_kernel");
+  count_launch(ctx);
+  return HL_OK;
+}
+
+}  // extern "C" (reopened below)
+
+namespace hl {
+// Stream-explicit forms, used by the data-parallel row exchange on the collective stream.
+int mark_rows_on(hl_ctx* ctx, cudaStream_t stream, const int64_t* selected_rows, long long n_selected, const unsigned char* row_mask,
+                 unsigned char* flags, int rows) {
+  if (n_selected <= 0) return HL_OK;
+  mark_rows_kernel<<<(unsigned)ceil_div_ll(n_selected, 256), 256, 0, stream>>>(selected_rows, n_selected, flags, row_mask, rows,
+                                                                             ctx->status_dev);
+  HL_LAUNCH_CHECK("mark_rows_kernel");
+  count_launch(ctx);
+  return HL_OK;
+}
+int mask_to_indices_on(hl_ctx* ctx, cudaStream_t stream, const unsigned char* mask, int rows, int64_t* out, int* count_dev) {
+  mask_to_indices_kernel<<<1, 1024, 0, stream>>>(mask, rows, out, count_dev);
+  HL_LAUNCH_CHECK("mask_to_indices_kernel");
+  count_launch(ctx);
+  return HL_OK;
+}
+int move_rows_on(hl_ctx* ctx, cudaStream_t stream, const float* src, const int64_t* idx, const int* count_dev, int n_max, int dim,
+                 float* dst, bool scatter) {
+  if (n_max <= 0) return HL_OK;
+  const int blocks = std::min(ceil_div(n_max, 8), ctx->sm_count * 8);
+  move_rows_kernel<<<blocks, 256, 0, stream>>>(src, idx, count_dev, n_max, dim, dst, scatter ? 1 : 0);
+  HL_LAUNCH_CHECK("move_rows_kernel");
+  count_launch(ctx);
+  return HL_OK;
+}
+}  // namespace hl
+
+extern "C" {
+
+int hl_memory_access_count_rows_i64_u64(hl_ctx* ctx, const int64_t* selected_rows, long long n_selected, int slots,
+                                        unsigned long long* counts) {
+  HL_REQUIRE(ctx && counts, "hl_memory_access_count_rows_i64_u64: null argument");
+  HL_REQUIRE(slots > 0, "memory_access_count_rows_i64_u64 requires non-zero memory_slots");
+  HL_REQUIRE(n_selected >= 0 && (n_selected == 0 || selected_rows), "hl_memory_access_count_rows_i64_u64: null selected rows");
+  if (n_selected == 0) return HL_OK;
+  const unsigned blocks = (unsigned)std::min<long long>(ceil_div_ll(n_selected, 256), (long long)ctx->sm_count * 16);
+  access_count_rows_kernel<<<blocks, 256, 0, ctx->stream>>>(selected_rows, n_selected, slots, counts, ctx->status_dev);
+  HL_LAUNCH_CHECK("access_count_rows_kernel");
+  count_launch(ctx);
+  return HL_OK;
+}
+
+int hl_mark_rows_u8(hl_ctx* ctx, const int64_t* selected_rows, long long n_selected, const unsigned char* row_mask,
+                    unsigned char* flags, int rows) {
+  HL_REQUIRE(ctx && selected_rows && flags, "hl_mark_rows_u8: null argument");
+  HL_REQUIRE(rows > 0, "hl_mark_rows_u8: requires non-zero rows");
+  return mark_rows_on(ctx, ctx->stream, selected_rows, n_selected, row_mask, flags, rows);
+}
+
+int hl_mask_to_indices_u8(hl_ctx* ctx, const unsigned char* mask, int rows, int64_t* out_indices, int* count_dev) {
+  HL_REQUIRE(ctx && mask && out_indices && count_dev, "hl_mask_to_indices_u8: null argument");
+  HL_REQUIRE(rows > 0, "hl_mask_to_indices_u8: requires non-zero rows");
+  return mask_to_indices_on(ctx, ctx->stream, mask, rows, out_indices, count_dev);
+}
+
+int hl_gather_rows_f32(hl_ctx* ctx, const float* src, const int64_t* indices, int n, int dim, float* dst) {
+  HL_REQUIRE(ctx && src && indices && dst, "hl_gather_rows_f32: null argument");
+  HL_REQUIRE(n >= 0 && dim > 0 && dim % 4 == 0, "hl_gather_rows_f32: row_dim must be a positive multiple of 4");
+  return move_rows_on(ctx, ctx->stream, src, indices, nullptr, n, dim, dst, false);
+}
+
+int hl_scatter_rows_f32(hl_ctx* ctx, const float* src, const int64_t* indices, int n, int dim, float* dst) {
+  HL_REQUIRE(ctx && src && indices && dst, "hl_scatter_rows_f32: null argument");
+  HL_REQUIRE(n >= 0 && dim > 0 && dim % 4 == 0, "hl_scatter_rows_f32: row_dim must be a positive multiple of 4");
+  return move_rows_on(ctx, ctx->stream, src, indices, nullptr, n, dim, dst, true);
+}
+
+int hl_sparse_rows_sum_squares_f32(hl_ctx* ctx, const float* grad, const int64_t* selected_rows, long long n_selected,
+                                   const unsigned char* row_mask, unsigned char* row_flags, int rows, int row_dim,
+                                   double* sum_dev) {
+  HL_REQUIRE(ctx && grad && selected_rows && row_flags && sum_dev, "hl_sparse_rows_sum_squares_f32: null argument");
+  HL_REQUIRE(rows > 0 && row_dim > 0, "hl_sparse_rows_sum_squares_f32: requires non-zero rows/row_dim");
+  if (n_selected <= 0) return HL_OK;
+  mark_rows_kernel<<<(unsigned)ceil_div_ll(n_selected, 256), 256, 0, ctx->stream>>>(selected_rows, n_selected, row_flags,
+                                                                                  row_mask, rows, ctx->status_dev);
+  HL_LAUNCH_CHECK("mark_rows_kernel");
+  flagged_rows_sum_squares_kernel<<<ceil_div(rows, 8), 256, 0, ctx->stream>>>(grad, row_flags, rows, row_dim, sum_dev);
+  HL_LAUNCH_CHECK("flagged_rows_sum_squares_kernel");
+  count_launch(ctx, 2);
+  return HL_OK;
+}
+
+int hl_sparse_adamw_rows_f32(hl_ctx* ctx, float* param, float* grad, float* m, float* v, const int64_t* selected_rows,
+                             long long n_selected, const unsigned char* row_mask, unsigned char* row_flags, int rows,
+                             int row_dim, const hl_adamw_params* hp, int zero_grad_rows) {
+  HL_REQUIRE(ctx && param && grad && m && v && selected_rows && row_flags && hp, "hl_sparse_adamw_rows_f32: null argument");
+  HL_REQUIRE(rows > 0 && row_dim > 0, "hl_sparse_adamw_rows_f32: requires non-zero rows/row_dim");
+  HL_REQUIRE(hp->bias_correction1 > 0.f && hp->bias_correction2 > 0.f, "hl_sparse_adamw_rows_f32: bias corrections must be positive");
+  if (n_selected <= 0) return HL_OK;
+  mark_rows_kernel<<<(unsigned)ceil_div_ll(n_selected, 256), 256, 0, ctx->stream>>>(selected_rows, n_selected, row_flags,
+                                                                                  row_mask, rows, ctx->status_dev);
+  HL_LAUNCH_CHECK("mark_rows_kernel");
+  sparse_adamw_rows_kernel<<<ceil_div(rows, 8), 256, 0, ctx->stream>>>(param, grad, m, v, row_flags, rows, row_dim, *hp,
+                                                                       zero_grad_rows);
+  HL_LAUNCH_CHECK("sparse_adamw_rows_kernel");
+  count_launch(ctx, 2);
+  return HL_OK;
+}
+
+}  // extern "C"
