@@ -312,6 +312,38 @@ int hl_cast(hl_ctx* ctx, const void* src, int src_dtype, void* dst, int dst_dtyp
   return HL_OK;
 }
 
+// One f32 value as a sum of bf16 pieces: hi = bf16(x), mid = bf16(x - hi), lo = bf16(x - hi - mid).  The
+// differences are exact in f32, so hi + mid + lo == x whenever the three 8-bit mantissas reach the last bit of x.
+static __global__ void split_bf16_kernel(const float* __restrict__ src, __nv_bfloat16* __restrict__ dst, long long rows, int cols,
+                                  int mode) {
+  const int pieces = mode == HL_SPLIT_HI_LO ? 2 : 3;
+  const long long n = rows * cols;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    const long long r = i / cols;
+    const int c = (int)(i - r * cols);
+    const float x = src[i];
+    const __nv_bfloat16 hi = __float2bfloat16_rn(x);
+    const float r1 = x - __bfloat162float(hi);
+    const __nv_bfloat16 mid = __float2bfloat16_rn(r1);
+    const __nv_bfloat16 lo = __float2bfloat16_rn(r1 - __bfloat162float(mid));
+    __nv_bfloat16* out = dst + r * (long long)pieces * cols + c;
+    out[0] = hi;
+    if (mode == HL_SPLIT_HI_MID_LO) { out[cols] = mid; out[2 * cols] = lo; }
+    else if (mode == HL_SPLIT_HI_HI_LO) { out[cols] = hi; out[2 * cols] = mid; }
+    else out[cols] = mid;
+  }
+}
+
+int hl_split_bf16_f32(hl_ctx* ctx, const float* src, void* dst, long long rows, int cols, int mode) {
+  HL_REQUIRE(ctx && src && dst, "hl_split_bf16_f32: null argument");
+  HL_REQUIRE(rows > 0 && cols > 0, "hl_split_bf16_f32: requires non-zero rows/cols");
+  HL_REQUIRE(mode == HL_SPLIT_HI_MID_LO || mode == HL_SPLIT_HI_HI_LO || mode == HL_SPLIT_HI_LO, "hl_split_bf16_f32: unknown mode");
+  split_bf16_kernel<<<ew_grid(ctx, (size_t)rows * cols), EW_THREADS, 0, ctx->stream>>>(src, (__nv_bfloat16*)dst, rows, cols, mode);
+  HL_LAUNCH_CHECK("split_bf16_kernel");
+  count_launch(ctx);
+  return HL_OK;
+}
+
 int hl_gelu(hl_ctx* ctx, const void* x, void* out, int dtype, size_t n) {
   HL_REQUIRE(ctx && ((x && out) || n == 0), "hl_gelu: null argument");
   if (n == 0) return HL_OK;

@@ -54,6 +54,7 @@ struct GemmParams {
   int partial_out;  // split-K: raw accumulators go to the [splits][m][n] scratch through map_c
   int dp_tiles, sk_tiles;   // whole-wave tiles, then tiles whose k blocks are dealt out evenly
   int panel_w;              // tile columns per panel of the tile order
+  int a_kb_wrap;            // > 0: A holds this many k blocks and is read again from its start after them
   float* sk_slots;          // [grid][BM][BN] raw accumulators of unfinished tile parts
   unsigned* sk_flags;       // [grid][EPI_WARPS]: launch number once the warp's part of the slot is written
   unsigned sk_seq;          // this launch's number
@@ -201,12 +202,13 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
           uint8_t* sa = smem + size_t(stage) * STAGE_BYTES;
           uint8_t* sb = sa + A_STAGE_BYTES;
           tc05::mbar_arrive_expect_tx(&tail->full[stage], STAGE_BYTES);
+          const int ka = p.a_kb_wrap > 0 ? kb % p.a_kb_wrap : kb;
           if (A_MN) {
 #pragma unroll
             for (int j = 0; j < BM / 64; ++j)
-              tc05::tma_load_2d(sa + j * (BK * 128), &map_a, &tail->full[stage], m_tile * BM + j * 64, kb * BK);
+              tc05::tma_load_2d(sa + j * (BK * 128), &map_a, &tail->full[stage], m_tile * BM + j * 64, ka * BK);
           } else {
-            tc05::tma_load_2d(sa, &map_a, &tail->full[stage], kb * BK, m_tile * BM);
+            tc05::tma_load_2d(sa, &map_a, &tail->full[stage], ka * BK, m_tile * BM);
           }
           if (B_MN) {
 #pragma unroll
@@ -573,7 +575,10 @@ int gemm_bf16_run(hl_ctx* ctx, const hl_gemm_desc* d, const void* a, const void*
                  (reinterpret_cast<uintptr_t>(c) & 15) == 0,
              "hl_gemm_bf16: operands must be 16-byte aligned");
   const bool a_mn = d->a_layout == HL_MN_MAJOR, b_mn = d->b_layout == HL_MN_MAJOR;
-  HL_REQUIRE(d->lda >= (a_mn ? d->m : d->k) && d->ldb >= (b_mn ? d->n : d->k) && d->ldc >= d->n,
+  HL_REQUIRE(d->a_k_period >= 0 && d->a_k_period % BK == 0 && d->a_k_period <= d->k,
+             "hl_gemm_bf16: a_k_period must be a multiple of 64 and at most k");
+  const int a_k = d->a_k_period > 0 ? d->a_k_period : d->k;  // contraction extent that A really holds
+  HL_REQUIRE(d->lda >= (a_mn ? d->m : a_k) && d->ldb >= (b_mn ? d->n : d->k) && d->ldc >= d->n,
              "hl_gemm_bf16: leading dimension smaller than the row length");
   const long long ld_aux_in = d->ld_aux_in > 0 ? d->ld_aux_in : d->ldc;
   const long long ld_aux_out = d->ld_aux_out > 0 ? d->ld_aux_out : d->ldc;
@@ -603,6 +608,7 @@ int gemm_bf16_run(hl_ctx* ctx, const hl_gemm_desc* d, const void* a, const void*
   p.k_blocks = ceil_div(d->k, BK);
   // An A operand that stays in L2 anyway keeps the plain order (one tile column after the other);
   // a larger one is walked in panels of up to eight tile columns so that it streams from DRAM once.
+  p.a_kb_wrap = d->a_k_period > 0 ? d->a_k_period / BK : 0;
   p.panel_w = (size_t)d->m * (size_t)d->k * 2 <= (size_t(32) << 20) ? 1 : std::min(p.n_tiles, 8);
   const GemmPlan plan = gemm_plan(d, ctx->sm_count);
   const int splits = plan.splits;
@@ -636,8 +642,8 @@ int gemm_bf16_run(hl_ctx* ctx, const hl_gemm_desc* d, const void* a, const void*
 
   CUtensorMap ma, mb, mc, maux;
   int rc;
-  if (a_mn) rc = make_tensor_map_bf16_2d(&ma, a, (uint64_t)d->m, (uint64_t)d->k, (uint64_t)d->lda, 64, BK);
-  else      rc = make_tensor_map_bf16_2d(&ma, a, (uint64_t)d->k, (uint64_t)d->m, (uint64_t)d->lda, BK, BM);
+  if (a_mn) rc = make_tensor_map_bf16_2d(&ma, a, (uint64_t)d->m, (uint64_t)a_k, (uint64_t)d->lda, 64, BK);
+  else      rc = make_tensor_map_bf16_2d(&ma, a, (uint64_t)a_k, (uint64_t)d->m, (uint64_t)d->lda, BK, BM);
   if (rc != HL_OK) return rc;
   if (b_mn) rc = make_tensor_map_bf16_2d(&mb, b, (uint64_t)d->n, (uint64_t)d->k, (uint64_t)d->ldb, 64, BK);
   else      rc = make_tensor_map_bf16_2d(&mb, b, (uint64_t)d->k, (uint64_t)d->n, (uint64_t)d->ldb, BK, BN);
@@ -714,6 +720,16 @@ extern "C" int hl_gemm_bf16(hl_ctx* ctx, const hl_gemm_desc* desc, const void* a
   return hl::gemm_bf16_ctx(ctx, desc, a, b, c, bias, aux_in, aux_out);
 }
 
+extern "C" int hl_gemm_bf16_plan(hl_ctx* ctx, const hl_gemm_desc* desc, int* splits, int* dealt_tiles, size_t* scratch_bytes) {
+  if (!ctx || !desc) return hl::fail("hl_gemm_bf16_plan: null argument");
+  if (desc->m <= 0 || desc->n <= 0 || desc->k <= 0) return hl::fail("hl_gemm_bf16_plan: m, n, k must be positive");
+  const hl::GemmPlan plan = hl::gemm_plan(desc, ctx->sm_count);
+  if (splits) *splits = plan.splits;
+  if (dealt_tiles) *dealt_tiles = plan.sk_tiles;
+  if (scratch_bytes) *scratch_bytes = std::max(plan.splitk_bytes, plan.sk_slot_bytes);
+  return HL_OK;
+}
+
 // ---- split-K GEMM for callers that must not allocate ----------------------------------------
 // hl_gemm_bf16 takes its split-K partial sums from the context's scratch arena and grows that
 // arena with the CUDA allocator when a call needs more.  Two kinds of callers of this library
@@ -747,10 +763,14 @@ int static_scratch_address(hl_ctx* ctx, void** out, void** flags_out) {
     HL_CUDA(cudaGetDevice(&current));
     if (current != ctx->device) HL_CUDA(cudaSetDevice(ctx->device));
     void* ptr = nullptr;
-    HL_CUDA(cudaGetSymbolAddress(&ptr, g_gemm_static_scratch));
-    HL_REQUIRE(ptr != nullptr, "hl_gemm_bf16_static_scratch: the static scratch array has no device address");
     void* flags = nullptr;
-    HL_CUDA(cudaGetSymbolAddress(&flags, g_gemm_static_flags));
+    const cudaError_t e1 = cudaGetSymbolAddress(&ptr, g_gemm_static_scratch);
+    const cudaError_t e2 = cudaGetSymbolAddress(&flags, g_gemm_static_flags);
+    // the caller's current device is put back before anything is reported
+    if (current != ctx->device && current >= 0) HL_CUDA(cudaSetDevice(current));
+    HL_CUDA(e1);
+    HL_CUDA(e2);
+    HL_REQUIRE(ptr != nullptr, "hl_gemm_bf16_static_scratch: the static scratch array has no device address");
     HL_REQUIRE(flags != nullptr, "hl_gemm_bf16_static_scratch: the static flag array has no device address");
     g_static_flags_addr[ctx->device] = flags;
     g_static_scratch_addr[ctx->device] = ptr;

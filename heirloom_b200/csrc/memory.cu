@@ -724,12 +724,17 @@ __global__ void weighted_value_bwd_kernel(const int64_t* __restrict__ idx, const
 // gradients, dot(grad_out[token], values[row]), come from the same pass: one 2 KB read of grad_out per event is all
 // the traffic that does not stay in registers.
 __global__ void value_event_keys_kernel(const int64_t* __restrict__ idx, long long n, int rows, int* __restrict__ keys,
-                                        int* __restrict__ events) {
+                                        int* __restrict__ events, float* __restrict__ dweights, int* __restrict__ status) {
   const long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x;
   if (i >= n) return;
   const long long r = idx[i];
-  keys[i] = (r < 0 || r >= rows) ? rows : (int)r;  // out-of-range slots sort behind every row and are skipped
+  const bool bad = r < 0 || r >= rows;
+  keys[i] = bad ? rows : (int)r;  // out-of-range slots sort behind every row and are skipped by the row walk,
   events[i] = (int)i;
+  if (bad) {                      // so they are reported and their weight gradient is written here
+    atomicExch(status + ST_BAD_INDEX, 1);
+    if (dweights) dweights[i] = 0.f;
+  }
 }
 
 template <int VPL>  // 16-byte pieces of a row per lane: dim <= VPL * 128
@@ -1069,7 +1074,8 @@ int hl_memory_weighted_value_backward(hl_ctx* ctx, const int64_t* indices, const
     uint8_t* ws = reinterpret_cast<uint8_t*>(ctx->workspace);
     int *keys_in = reinterpret_cast<int*>(ws), *ev_in = reinterpret_cast<int*>(ws + arr);
     int *keys = reinterpret_cast<int*>(ws + 2 * arr), *ev = reinterpret_cast<int*>(ws + 3 * arr);
-    value_event_keys_kernel<<<(unsigned)ceil_div_ll(n, 256), 256, 0, ctx->stream>>>(indices, n, rows, keys_in, ev_in);
+    value_event_keys_kernel<<<(unsigned)ceil_div_ll(n, 256), 256, 0, ctx->stream>>>(indices, n, rows, keys_in, ev_in, grad_weights,
+                                                                                     ctx->status_dev);
     HL_LAUNCH_CHECK("value_event_keys_kernel");
     HL_CUDA(cub::DeviceRadixSort::SortPairs(ws + 4 * arr, sort_bytes, keys_in, keys, ev_in, ev, (int)n, 0, end_bit, ctx->stream));
     const unsigned blocks = (unsigned)ceil_div_ll(ceil_div_ll(n, 32), 4);

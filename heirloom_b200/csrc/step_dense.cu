@@ -46,7 +46,10 @@ struct LayerOffsets {
 struct MemoryActs {
   float *query = nullptr, *weights = nullptr, *weighted = nullptr, *gpre = nullptr, *gate = nullptr, *mv = nullptr;
   int64_t* idx = nullptr;
-  __nv_bfloat16* mv_b = nullptr;
+  __nv_bfloat16* mv_b = nullptr;  // amp route: [N, 2*value_dim] = [hi | lo] pieces of mv
+  // amp route: the three projection weights as bf16 pieces along the contraction (hl_split_bf16_f32),
+  // rebuilt from the f32 parameters at the start of every forward pass
+  __nv_bfloat16 *wq3 = nullptr, *wg3 = nullptr, *wout3 = nullptr;
 };
 
 struct LayerActs {
@@ -114,6 +117,8 @@ struct hl_decoder {
   unsigned char* m_row_flags = nullptr;
   unsigned char *smft_value_mask = nullptr, *smft_left_mask = nullptr, *smft_right_mask = nullptr;  // [slots], [side], [side]
   bool smft_on = false;  // the sparse-rows step filters its rows through the three masks
+  float* m_packed = nullptr;         // gradient rows of the union, packed for the all-reduce (own allocation)
+  size_t packed_rows_cap = 0;        // rows it holds
   int64_t* m_union_rows = nullptr;   // rows of the value table selected by any rank this step
   int* m_union_count = nullptr;      // device count of them
   int* m_union_count_host = nullptr; // pinned mirror
@@ -254,7 +259,10 @@ void plan_memory_buffers(hl_decoder* m, uint8_t*& cur) {
     a.gate = carve<float>(cur, N * vd);
     a.mv = carve<float>(cur, N * vd);
     a.idx = carve<int64_t>(cur, N * k);
-    a.mv_b = carve<__nv_bfloat16>(cur, N * vd);
+    a.mv_b = carve<__nv_bfloat16>(cur, N * 2 * vd);
+    a.wq3 = carve<__nv_bfloat16>(cur, kd * 3 * d);
+    a.wg3 = carve<__nv_bfloat16>(cur, vd * 3 * d);
+    a.wout3 = carve<__nv_bfloat16>(cur, d * 3 * vd);
   }
   m->m_ls = carve<float>(cur, N * m->side);
   m->m_rs = carve<float>(cur, N * m->side);
@@ -385,9 +393,10 @@ struct Gemm {
   hl_decoder* m;
   int run(int M, int N, int K, const void* a, long long lda, int al, const void* b, long long ldb, int bl, void* c,
           long long ldc, int out_dtype, int epi = HL_EPI_NONE, const float* bias = nullptr, const void* aux_in = nullptr,
-          long long ld_aux_in = 0, void* aux_out = nullptr, long long ld_aux_out = 0) const {
+          long long ld_aux_in = 0, void* aux_out = nullptr, long long ld_aux_out = 0, int a_k_period = 0) const {
     hl_gemm_desc d{};
     d.m = M; d.n = N; d.k = K;
+    d.a_k_period = a_k_period;
     d.a_layout = al; d.b_layout = bl;
     d.lda = lda; d.ldb = ldb; d.ldc = ldc;
     d.epilogue = epi; d.out_dtype = out_dtype; d.split_k = 0;
@@ -520,18 +529,27 @@ int forward(hl_decoder* m) {
                  m->x[l], d));
     HL_TRY(layer_norm_forward_impl(ctx, a.r, HL_BF16, P + o.ln2g, P + o.ln2b, a.c, HL_BF16, a.mean2, a.rstd2, N, d, 1e-5f));
     if (o.is_memory) {
-      // The three projections run on the tensor cores with bf16 operands and f32 results; the
-      // lookup, scores, softmax, gather and gate stay in f32.
+      // The reference keeps the memory feed-forward in f32 under AMP (src/memory_transformer.rs:787-789).  Its three
+      // projections still run on the tensor cores here, at f32 accuracy: the block input is bf16-exact, so
+      // x*W = x*W_hi + x*W_mid + x*W_lo with exact products and one f32 accumulation (a contraction of 3*d against
+      // the weight's three bf16 pieces, the input read three times); out_proj takes the f32 mv as hi + lo pieces and
+      // drops only the lo*lo term (2^-16 relative, far below the bf16 rounding of the block output that follows).
+      // The query decides the routing, so it has to be this accurate; lookup, scores, softmax, gather and gate are f32.
       MemoryActs& ma = m->ma[l];
       const int kd = m->mem.key_dim, vd = m->mem.value_dim;
-      HL_TRY(g.run(N, kd, d, a.c, d, HL_K_MAJOR, W + o.wq_m, d, HL_K_MAJOR, ma.query, kd, HL_F32, HL_EPI_BIAS, P + o.bq_m));
+      HL_TRY(hl_split_bf16_f32(ctx, P + o.wq_m, ma.wq3, kd, d, HL_SPLIT_HI_MID_LO));
+      HL_TRY(hl_split_bf16_f32(ctx, P + o.wg_m, ma.wg3, vd, d, HL_SPLIT_HI_MID_LO));
+      HL_TRY(hl_split_bf16_f32(ctx, P + o.wout_m, ma.wout3, d, vd, HL_SPLIT_HI_HI_LO));
+      HL_TRY(g.run(N, kd, 3 * d, a.c, d, HL_K_MAJOR, ma.wq3, 3 * d, HL_K_MAJOR, ma.query, kd, HL_F32, HL_EPI_BIAS, P + o.bq_m,
+                   nullptr, 0, nullptr, 0, d));
       HL_TRY(memory_core_forward(m, l));
-      HL_TRY(g.run(N, vd, d, a.c, d, HL_K_MAJOR, W + o.wg_m, d, HL_K_MAJOR, ma.gpre, vd, HL_F32, HL_EPI_BIAS, P + o.bg_m));
+      HL_TRY(g.run(N, vd, 3 * d, a.c, d, HL_K_MAJOR, ma.wg3, 3 * d, HL_K_MAJOR, ma.gpre, vd, HL_F32, HL_EPI_BIAS, P + o.bg_m,
+                   nullptr, 0, nullptr, 0, d));
       HL_TRY(hl_gelu(ctx, ma.gpre, ma.gate, HL_F32, (size_t)N * vd));
       HL_TRY(hl_binary_f32(ctx, HL_MUL, ma.weighted, ma.gate, ma.mv, (size_t)N * vd));
-      HL_TRY(hl_cast(ctx, ma.mv, HL_F32, ma.mv_b, HL_BF16, (size_t)N * vd));
-      HL_TRY(g.run(N, d, vd, ma.mv_b, vd, HL_K_MAJOR, W + o.wout_m, vd, HL_K_MAJOR, m->x[l + 1], d, HL_BF16,
-                   HL_EPI_BIAS_RESIDUAL, P + o.bout_m, a.r, d));
+      HL_TRY(hl_split_bf16_f32(ctx, ma.mv, ma.mv_b, N, vd, HL_SPLIT_HI_LO));
+      HL_TRY(g.run(N, d, 3 * vd, ma.mv_b, 2 * vd, HL_K_MAJOR, ma.wout3, 3 * vd, HL_K_MAJOR, m->x[l + 1], d, HL_BF16,
+                   HL_EPI_BIAS_RESIDUAL, P + o.bout_m, a.r, d, nullptr, 0, 2 * vd));
       continue;
     }
     HL_TRY(g.run(N, F, d, a.c, d, HL_K_MAJOR, W + o.w1, d, HL_K_MAJOR, a.h, F, HL_BF16, HL_EPI_BIAS_GELU, P + o.b1, nullptr,
@@ -598,12 +616,23 @@ int exchange_value_rows(hl_decoder* m) {
   HL_REQUIRE(n >= 0 && n <= slots, "hl_decoder: selected-row union out of range");
   m->union_n = n;
   if (n > 0) {
-    int rc = ensure_workspace(ctx, sizeof(float) * (size_t)n * vd);
-    if (rc != HL_OK) return rc;
-    float* packed = reinterpret_cast<float*>(ctx->workspace);
-    // the scratch arena belongs to the compute stream: nothing queued there may still use it
-    HL_CUDA(cudaEventRecord(m->comm_done, ctx->stream));
-    HL_CUDA(cudaStreamWaitEvent(cs, m->comm_done, 0));
+    // The packed rows live in a buffer of their own: the context's scratch arena belongs to the compute stream,
+    // which keeps running (and may regrow the arena) while this exchange is in flight on the collective stream.
+    if ((size_t)n > m->packed_rows_cap) {
+      const size_t events = (size_t)nccl_world(ctx) * per_layer * (size_t)m->mem.n_memory_layers;
+      const size_t cap = std::max((size_t)n, std::min((size_t)slots, events));
+      if (m->m_packed) {
+        HL_CUDA(cudaStreamSynchronize(cs));
+        HL_CUDA(cudaFree(m->m_packed));
+        m->m_packed = nullptr;
+        m->packed_rows_cap = 0;
+      }
+      HL_CUDA(cudaMalloc(reinterpret_cast<void**>(&m->m_packed), sizeof(float) * cap * vd));
+      m->packed_rows_cap = cap;
+      ctx->counters.allocations += 1;
+      ctx->counters.allocated_bytes += sizeof(float) * cap * vd;
+    }
+    float* packed = m->m_packed;
     HL_TRY(move_rows_on(ctx, cs, m->grads + m->off_val, m->m_union_rows, nullptr, n, vd, packed, false));
     HL_TRY(nccl_allreduce_sum_f32(ctx, packed, (size_t)n * vd, cs));
     HL_TRY(move_rows_on(ctx, cs, packed, m->m_union_rows, nullptr, n, vd, m->grads + m->off_val, true));
@@ -647,7 +676,7 @@ int backward(hl_decoder* m) {
       MemoryActs& ma = m->ma[l];
       const int kd = m->mem.key_dim, vd = m->mem.value_dim;
       const size_t nv = (size_t)N * vd;
-      HL_TRY(g.run(d, vd, N, m->dxb, d, HL_MN_MAJOR, ma.mv_b, vd, HL_MN_MAJOR, G + o.wout_m, vd, HL_F32));
+      HL_TRY(g.run(d, vd, N, m->dxb, d, HL_MN_MAJOR, ma.mv_b, 2 * vd, HL_MN_MAJOR, G + o.wout_m, vd, HL_F32));  // hi piece of mv
       HL_TRY(g.run(N, vd, d, m->dxb, d, HL_K_MAJOR, W + o.wout_m, vd, HL_MN_MAJOR, m->m_dmv, vd, HL_F32));
       HL_TRY(hl_binary_f32(ctx, HL_MUL, m->m_dmv, ma.gate, m->m_dweighted, nv));
       HL_TRY(hl_binary_f32(ctx, HL_MUL, m->m_dmv, ma.weighted, m->m_dgate, nv));
@@ -897,7 +926,11 @@ int optimizer_step(hl_decoder* m) {
     // chunks that lie completely inside the buckets reduced so far (a chunk that straddles the boundary waits
     // for the next group; the last group takes everything that is left)
     const int upto = b1 == m->n_buckets ? chunks_total : (int)(end / chunk);
-    HL_CUDA(cudaStreamWaitEvent(ctx->stream, m->bucket_done[b1 - 1], 0));
+    // The value table's gradient is not final when its buckets are: its rows are summed over the ranks by the row
+    // exchange that follows the last bucket on the collective stream.  A group that reaches into the table waits for
+    // the end of that stream's work (which covers every bucket as well).
+    const bool reaches_values = m->has_memory && (b1 == m->n_buckets || (size_t)upto * chunk > m->off_val);
+    HL_CUDA(cudaStreamWaitEvent(ctx->stream, reaches_values ? m->comm_done : m->bucket_done[b1 - 1], 0));
     HL_TRY(adam_plan_step_range(ctx, m->plan, &hp, first, upto - first));
     first = upto;
   }
@@ -963,6 +996,9 @@ static int decoder_create_impl(hl_ctx* ctx, const hl_decoder_config* cfg, const 
   if (amp) {
     HL_REQUIRE(cfg->d_model % 8 == 0 && cfg->d_ff % 8 == 0 && cfg->vocab % 8 == 0 && cfg->d_model <= 1024,
                "hl_decoder_create: d_model (<= 1024), d_ff and vocab must be multiples of 8");
+    if (mem && mem->n_memory_layers > 0)  // the projections' contraction is read piecewise in whole 64-element blocks
+      HL_REQUIRE(cfg->d_model % 64 == 0 && mem->value_dim % 32 == 0,
+                 "hl_memory_decoder_create: the bf16 route needs d_model to be a multiple of 64 and value_dim of 32");
   } else {
     HL_REQUIRE(cfg->d_model % 4 == 0 && cfg->d_model <= 1024,
                "hl_decoder_create: the f32 route needs d_model to be a multiple of 4 and at most 1024");
@@ -1052,6 +1088,7 @@ void hl_decoder_destroy(hl_decoder* m) {
   adam_plan_destroy(m->plan);
   adam_plan_destroy(m->plan_tables);
   adam_plan_destroy(m->plan_no_values);
+  if (m->m_packed) cudaFree(m->m_packed);
   cudaFree(m->params); cudaFree(m->grads); cudaFree(m->m); cudaFree(m->v); cudaFree(m->shadow); cudaFree(m->act_arena);
   if (m->loss_host) cudaFreeHost(m->loss_host);
   delete m;

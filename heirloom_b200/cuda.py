@@ -293,17 +293,28 @@ def matmul_f32_strided(ctx: Context, a: torch.Tensor, b: torch.Tensor, out: Opti
     return out
 
 
+SPLIT_HI_MID_LO, SPLIT_HI_HI_LO, SPLIT_HI_LO = 0, 1, 2
+
+
 def gemm_bf16(ctx: Context, a: torch.Tensor, b: torch.Tensor, m: int, n: int, k: int, a_layout=K_MAJOR,
               b_layout=K_MAJOR, epilogue=EPI_NONE, out_dtype=torch.bfloat16, bias=None, aux_in=None,
-              want_aux_out=False, split_k=0, out=None):
+              want_aux_out=False, split_k=0, out=None, a_k_period=0):
     """C[m,n] = A·B with per-operand storage order; see `hl_gemm_bf16` in the C header."""
     if out is None:
         out = torch.empty(m, n, dtype=out_dtype, device=a.device)
     aux_out = torch.empty(m, n, dtype=torch.bfloat16, device=a.device) if want_aux_out else None
     desc = GemmDesc(m, n, k, a_layout, b_layout, a.stride(0), b.stride(0), out.stride(0), epilogue, _DT[out.dtype],
-                    split_k, aux_in.stride(0) if aux_in is not None else 0, n if want_aux_out else 0)
+                    split_k, aux_in.stride(0) if aux_in is not None else 0, n if want_aux_out else 0, a_k_period)
     check(ctx.lib.hl_gemm_bf16(ctx.handle, byref(desc), _p(a), _p(b), _p(out), _p(bias), _p(aux_in), _p(aux_out)))
     return (out, aux_out) if want_aux_out else out
+
+
+def gemm_bf16_plan(ctx: Context, m: int, n: int, k: int, epilogue=EPI_NONE, out_dtype=torch.float32, split_k=0):
+    """`hl_gemm_bf16_plan`: (splits, dealt tiles, scratch bytes) of the work split for this shape."""
+    desc = GemmDesc(m, n, k, K_MAJOR, K_MAJOR, k, k, n, epilogue, _DT[out_dtype], split_k, 0, 0)
+    splits, dealt, need = c_int(), c_int(), c_size_t()
+    check(ctx.lib.hl_gemm_bf16_plan(ctx.handle, byref(desc), byref(splits), byref(dealt), byref(need)))
+    return splits.value, dealt.value, need.value
 
 
 def gemm_bf16_static_scratch(ctx: Context, a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, m: int, n: int,

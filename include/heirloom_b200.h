@@ -106,6 +106,16 @@ int hl_relu_backward_f32(hl_ctx* ctx, const float* x, const float* grad_out, flo
 /* Casts with round-to-nearest-even (kernels.ptx:174, :208, :238; src/storage.rs:440-449).
  * src_dtype/dst_dtype in {HL_F32, HL_BF16}; equal f32 types perform the bf16 round trip. */
 int hl_cast(hl_ctx* ctx, const void* src, int src_dtype, void* dst, int dst_dtype, size_t n);
+/* An f32 matrix [rows, cols] as bf16 pieces laid side by side along the columns, dst [rows, pieces*cols]:
+ * hi = bf16(x), mid = bf16(x - hi), lo = bf16(x - hi - mid) (the differences are exact).  With them a product
+ * with an f32 operand runs on the bf16 tensor cores at f32 accuracy (hl_gemm_desc.a_k_period): this is how the
+ * memory feed-forward keeps its projections in f32 under AMP, as the reference does
+ * (src/memory_transformer.rs:787-789), without leaving the tensor cores.
+ *   HL_SPLIT_HI_MID_LO  [hi | mid | lo]   exact three-piece form of a weight, against a bf16-exact input
+ *   HL_SPLIT_HI_HI_LO   [hi | hi | mid]   weight side of hi*hi + lo*hi + hi*lo
+ *   HL_SPLIT_HI_LO      [hi | mid]        input side of the same, read with a_k_period = 2*cols */
+enum { HL_SPLIT_HI_MID_LO = 0, HL_SPLIT_HI_HI_LO = 1, HL_SPLIT_HI_LO = 2 };
+int hl_split_bf16_f32(hl_ctx* ctx, const float* src, void* dst, long long rows, int cols, int mode);
 /* tanh-GELU and its gradient (kernels.ptx:4791, :4842; src/tensor.rs:5152-5154,
  * src/tensor/autograd.rs:2891-2897).  dtype in {HL_F32, HL_BF16} applies to x/out/grads. */
 int hl_gelu(hl_ctx* ctx, const void* x, void* out, int dtype, size_t n);
@@ -239,9 +249,18 @@ typedef struct {
   int out_dtype; /* HL_BF16 or HL_F32 */
   int split_k;
   long long ld_aux_in, ld_aux_out; /* 0 = same as ldc */
+  int a_k_period; /* 0, or a multiple of 64: A holds only this many contraction elements and is read again
+                     from its start after them (B supplies all k), so that one f32 accumulation can take
+                     C = A*B1 + A*B2 + ... with B = [B1 | B2 | ...] along the contraction */
 } hl_gemm_desc;
 int hl_gemm_bf16(hl_ctx* ctx, const hl_gemm_desc* desc, const void* a, const void* b, void* c,
                  const float* bias, const void* aux_in, void* aux_out);
+
+/* How hl_gemm_bf16 would cut this shape on this context's GPU: the number of equal splits of the contraction
+ * (1 = none), the number of output tiles whose k blocks are dealt out over the CTAs (0 = none), and the scratch
+ * bytes the launch needs.  Pure host arithmetic; lets a caller check a shape against a scratch budget before the
+ * step starts (the reference's shape-support predicates play this role, heirloom-kernels/src/cuda.rs:3761-3900). */
+int hl_gemm_bf16_plan(hl_ctx* ctx, const hl_gemm_desc* desc, int* splits, int* dealt_tiles, size_t* scratch_bytes);
 
 /* The same GEMM for callers that must not allocate.  It has no counterpart in the reference.
  * hl_gemm_bf16 keeps split-K partial sums in the context's scratch arena and grows that arena

@@ -907,7 +907,8 @@ def memory_feed_forward_backward(saved, p, prefix: str, mem: MemoryConfig, gout,
 
 
 def memory_decoder_loss_and_grads(cfg: DecoderConfig, mem: MemoryConfig, params, tokens, targets,
-                                  amp_bf16: bool = False, grad_f32: bool = False, return_indices: bool = False):
+                                  amp_bf16: bool = False, grad_f32: bool = False, return_indices: bool = False,
+                                  return_queries: bool = False):
     """The decoder of `decoder_loss_and_grads` with memory feed-forward blocks at `mem.memory_layers`
     (`MemoryTransformerBlock`, `src/memory_transformer.rs:1092-1183`)."""
     amp = amp_bf16
@@ -922,6 +923,7 @@ def memory_decoder_loss_and_grads(cfg: DecoderConfig, mem: MemoryConfig, params,
     x = rt(add(tok, pos)).reshape(N, d)
     saved = []
     all_indices = {}
+    all_queries = {}
     for i in range(cfg.n_layers):
         b = f"block.{i}."
         a = rt(layer_norm(x, p[b + "ln1.weight"], p[b + "ln1.bias"]))
@@ -937,6 +939,7 @@ def memory_decoder_loss_and_grads(cfg: DecoderConfig, mem: MemoryConfig, params,
         if i in mem.memory_layers:
             f_raw, ff_saved = memory_feed_forward(c, p, b + "feed_forward.memory.", mem)
             all_indices[i] = ff_saved[2]
+            all_queries[i] = ff_saved[1]
             f = rt(f_raw)
             saved.append((x, a, q, k, v, probs, o, r, c, None, None, ff_saved))
         else:
@@ -984,6 +987,8 @@ def memory_decoder_loss_and_grads(cfg: DecoderConfig, mem: MemoryConfig, params,
     grads["position_embedding.weight"] = embedding_backward(p["position_embedding.weight"].shape, pos_ids, dx3)
     if grad_f32 or amp:
         grads = {n: f32_round(g_) for n, g_ in grads.items()}
+    if return_queries:
+        return loss, grads, all_indices, all_queries
     if return_indices:
         return loss, grads, all_indices
     return loss, grads

@@ -92,3 +92,52 @@ def test_gemm_rejects_bad_arguments_before_launch():
         cuda.gemm_bf16(c, a, a, 16, 16, 12)
     with pytest.raises(HeirloomError, match="positive"):
         cuda.gemm_bf16(c, a, a, 0, 16, 8)
+
+
+def split_bf16(ctx_, x, mode):
+    """`hl_split_bf16_f32` on an f32 matrix; returns the bf16 pieces laid side by side."""
+    from heirloom_b200 import cuda
+    rows, cols = x.shape
+    pieces = 2 if mode == cuda.SPLIT_HI_LO else 3
+    out = torch.empty(rows, pieces * cols, dtype=torch.bfloat16, device="cuda")
+    cuda.check(ctx_.lib.hl_split_bf16_f32(ctx_.handle, cuda._p(x), cuda._p(out), cuda.c_longlong(rows), cuda.c_int(cols),
+                                          cuda.c_int(mode)))
+    return out
+
+
+def test_split_pieces_rebuild_the_f32_value_exactly():
+    from heirloom_b200 import cuda
+    c = ctx()
+    rng = np.random.default_rng(31)
+    x = (rng.standard_normal((50, 72)) * np.exp(rng.uniform(-6, 6, (50, 72)))).astype(np.float32)
+    x[0, :4] = [0.0, -0.0, 1.0, -3.5]
+    p = host(split_bf16(c, dev(x), cuda.SPLIT_HI_MID_LO))
+    assert np.array_equal(p[:, :72], ho.bf16_round(x))
+    assert np.array_equal((p[:, :72] + p[:, 72:144] + p[:, 144:]).astype(np.float32), x)
+    q = host(split_bf16(c, dev(x), cuda.SPLIT_HI_HI_LO))
+    assert np.array_equal(q[:, :72], p[:, :72]) and np.array_equal(q[:, 72:144], p[:, :72]) and np.array_equal(q[:, 144:], p[:, 72:144])
+    r = host(split_bf16(c, dev(x), cuda.SPLIT_HI_LO))
+    assert np.array_equal(r[:, :72], p[:, :72]) and np.array_equal(r[:, 72:], p[:, 72:144])
+
+
+@pytest.mark.parametrize("m,n,k", [(300, 264, 128), (1024, 512, 512)])
+def test_gemm_with_a_repeated_operand_reaches_f32_accuracy(m, n, k):
+    """x [m,k] bf16-exact against an f32 weight [n,k]: one accumulation over the weight's three bf16 pieces, the input
+    read three times (a_k_period), equals the f64 product of the f32 operands to f32 rounding."""
+    from heirloom_b200 import cuda
+    c = ctx()
+    rng = np.random.default_rng(m + n + k)
+    x = ho.bf16_round(rng.standard_normal((m, k)))
+    w = rng.standard_normal((n, k)).astype(np.float32)
+    w3 = split_bf16(c, dev(w), cuda.SPLIT_HI_MID_LO)
+    out = cuda.gemm_bf16(c, dev(x, torch.bfloat16), w3, m, n, 3 * k, out_dtype=torch.float32, a_k_period=k)
+    want = x @ w.astype(np.float64).T
+    scale = np.abs(want).max()
+    assert np.abs(host(out) - want).max() <= 2e-6 * scale   # plain bf16 operands would be off by ~4e-3 of scale
+    # both operands f32: hi*hi + lo*hi + hi*lo, the dropped lo*lo term is 2^-16 relative
+    a = rng.standard_normal((m, k)).astype(np.float32)
+    a2 = split_bf16(c, dev(a), cuda.SPLIT_HI_LO)
+    wb = split_bf16(c, dev(w), cuda.SPLIT_HI_HI_LO)
+    out = cuda.gemm_bf16(c, a2, wb, m, n, 3 * k, out_dtype=torch.float32, a_k_period=2 * k)
+    want = a.astype(np.float64) @ w.astype(np.float64).T
+    assert np.abs(host(out) - want).max() <= 6e-5 * np.abs(want).max()

@@ -50,39 +50,60 @@ def test_f32_route_matches_the_oracle_with_identical_indices():
     model.close()
 
 
+def _slot_scores(q, kl, kr, slots, side):
+    """Full product-key score of each slot in `slots` [tokens, k] for the queries q [tokens, key_dim] (f64)."""
+    half = q.shape[1] // 2
+    left, right = slots // side, slots % side
+    return np.einsum("tkd,td->tk", kl[left], q[:, :half]) + np.einsum("tkd,td->tk", kr[right], q[:, half:])
+
+
 def test_amp_route_tracks_the_oracle_and_routes_almost_identically():
     from heirloom_b200 import nn
     model, ocfg, omem, params = build(nn.PRECISION_AMP_BF16, 2, seed=1)
     model.set_optimizer(lr=1e-3, weight_decay=0.01)
     state = ho.AdamWState(lr=1e-3, weight_decay=0.01)
     rng = np.random.default_rng(12)
-    agree = []
+    side = int(np.sqrt(MEM["slots"]))
+    agree, gaps = [], []
     for step in range(5):
         tok = ho.zipf_tokens(rng, ocfg.vocab, (2, 129))
         x, y = tok[:, :-1].copy(), tok[:, 1:].copy()
         loss = model.train_step(torch.tensor(x).pin_memory(), torch.tensor(y).pin_memory())
-        oloss, ograds, oidx = ho.memory_decoder_loss_and_grads(ocfg, omem, params, x, y, amp_bf16=True, return_indices=True)
-        ho.adamw_step(params, ograds, state)
+        oloss, ograds, oidx, oq = ho.memory_decoder_loss_and_grads(ocfg, omem, params, x, y, amp_bf16=True, return_indices=True,
+                                                                   return_queries=True)
         assert abs(loss - oloss) <= 1e-2 * abs(oloss), (step, loss, oloss)
         for layer in MEM["memory_layers"]:
             got = model.selected_indices(layer)
             agree.append(np.mean([len(set(a) & set(b)) / len(a) for a, b in zip(got, oidx[layer])]))
-    # projections run with bf16 operands here and in f32 in the reference: a few near-tie slots differ
-    assert min(agree) >= 0.9, agree
+            # every slot that differs must be a near-tie under the oracle's own queries: its score lies within the
+            # bf16 noise of the block input (the layer norm output both sides round to bf16) below the oracle's k-th
+            q = oq[layer].astype(np.float64)
+            kl, kr = params["shared_memory.product_key_left"], params["shared_memory.product_key_right"]
+            s_ref, s_got = _slot_scores(q, kl, kr, oidx[layer], side), _slot_scores(q, kl, kr, got, side)
+            spread = s_ref.max(axis=1) - s_ref.min(axis=1) + 1e-30
+            gaps.append(float(np.max((s_ref.min(axis=1) - s_got.min(axis=1)) / spread)))
+        ho.adamw_step(params, ograds, state)
+    print("amp memory routing agreement per (step, block):", [round(a, 4) for a in agree])
+    print("amp memory worst score gap of a differing slot, relative to the selected scores' spread:", max(gaps))
+    # the query projection runs at f32 accuracy (bf16 pieces of the weight), as the reference keeps it in f32; what is
+    # left are slots whose scores tie within the bf16 rounding of the activations that feed the block
+    assert min(agree) >= 0.97, agree
+    assert max(gaps) <= 0.05, gaps
     floor = 5 * 1e-3
-    report = {}
+    report, measured = {}, {}
     for name in ho.memory_parameter_names(ocfg, omem):
         if name.endswith("attention.k_proj.bias"):
             continue
         got, want = model.parameter(name).astype(np.float64), params[name]
         bad = np.abs(got - want) > 2e-2 * np.maximum(np.abs(want), floor)
         # Small vectors that start at zero (biases) move by about lr per step whatever the gradient's
-        # size, so a handful of sign flips already is several per cent of their elements.  Parameters
-        # of the memory blocks also see the few slots that are routed differently (bf16 projections
-        # here, f32 in the reference).
-        limit = 0.25 if "memory" in name else (0.03 if got.size >= 1024 else 0.10)
+        # size, so a handful of sign flips already is several per cent of their elements.
+        cls = "memory" if "memory" in name else ("large" if got.size >= 1024 else "small")
+        measured[cls] = max(measured.get(cls, 0.0), float(bad.mean()))
+        limit = {"memory": 0.25, "large": 0.03, "small": 0.10}[cls]
         if bad.mean() > limit:
             report[name] = float(bad.mean())
+    print("amp memory model, worst fraction of elements outside 2e-2 after 5 steps, by class:", measured)
     assert not report, report
     model.close()
 

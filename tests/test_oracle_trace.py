@@ -30,3 +30,16 @@ def test_amp_and_f32_oracle_modes_agree_within_bf16_tolerance():
     assert abs(l32 - l16) <= 1e-2 * l32
     for n in ("lm_head.weight", "block.0.feed_forward.dense.fc1.weight"):
         assert np.abs(g32[n] - g16[n]).max() <= 0.1 * np.abs(g32[n]).max()
+
+
+def test_first_steps_of_the_committed_amp_trace_reproduce():
+    from tests.golden import make_amp_trace as mt
+    trace = json.loads((Path(__file__).parent / "golden" / "amp_decoder_trace.json").read_text())
+    assert trace["config"] == mt.CONFIG and trace["steps"] == mt.STEPS == len(trace["losses"]) and trace["batch"] == mt.BATCH
+    cfg = ho.DecoderConfig(**mt.CONFIG)
+    params = ho.init_parameters(cfg, mt.WEIGHT_SEED)
+    state = ho.AdamWState(lr=1e-3, beta1=0.9, beta2=0.999, eps=1e-8, weight_decay=0.01)
+    losses = ho.train_steps(cfg, params, mt.batches(3), state, amp_bf16=True)
+    assert np.allclose(losses, trace["losses"][:3], rtol=1e-6, atol=0)
+    # Zipf(1.1) streams: the loss falls by well over a nat within the 200 steps, so the trace discriminates
+    assert trace["losses"][0] > 6.0 and trace["losses"][-1] < 4.6

@@ -32,9 +32,37 @@ def test_static_scratch_gemm_matches_the_allocating_entry_point_twice_in_a_row()
         a, b, da, db = _case(rng, m, n, k)
         want = cuda.gemm_bf16(c, da, db, m, n, k, cuda.MN_MAJOR, cuda.MN_MAJOR, out_dtype=torch.float32, split_k=split)
         out = torch.full((m, n), float("nan"), dtype=torch.float32, device="cuda")
+        c.sync()
+        before = c.counters()
         got = cuda.gemm_bf16_static_scratch(c, da, db, out, m, n, k, cuda.MN_MAJOR, cuda.MN_MAJOR, split_k=split)
+        after = c.counters()
+        # the one promise of the entry point: the library allocated nothing on the way
+        assert (after.allocations, after.allocated_bytes) == (before.allocations, before.allocated_bytes)
         assert_close("static scratch vs regular", host(got), host(want), atol=1e-2, rtol=1e-5)
         assert_close("static scratch vs oracle", host(got), a @ b, atol=1e-2, rtol=1e-5)
+
+
+def test_static_scratch_gemm_with_dealt_k_blocks_twice_in_a_row():
+    """80 output tiles with a contraction of 12288 on 148 SMs: the automatic work split deals the tiles' k blocks out
+    over the CTAs, the only path that uses the per-CTA slots and the flag array of the fixed scratch.  The second call
+    finds the first one's slots and flags in place."""
+    from heirloom_b200 import cuda
+    c = ctx()
+    rng = np.random.default_rng(22)
+    m, n, k = 1280, 2048, 12288
+    splits, dealt, need = cuda.gemm_bf16_plan(c, m, n, k)
+    assert dealt > 0 and 0 < need <= (32 << 20)
+    for _ in range(2):
+        a, b, da, db = _case(rng, m, n, k)
+        want = cuda.gemm_bf16(c, da, db, m, n, k, cuda.MN_MAJOR, cuda.MN_MAJOR, out_dtype=torch.float32, split_k=0)
+        out = torch.full((m, n), float("nan"), dtype=torch.float32, device="cuda")
+        c.sync()
+        before = c.counters()
+        got = cuda.gemm_bf16_static_scratch(c, da, db, out, m, n, k, cuda.MN_MAJOR, cuda.MN_MAJOR, split_k=0)
+        after = c.counters()
+        assert (after.allocations, after.allocated_bytes) == (before.allocations, before.allocated_bytes)
+        assert np.array_equal(host(got), host(want))  # same kernel, same split, same summation order
+        assert_close("static scratch vs oracle", host(got), a @ b, atol=2e-2, rtol=1e-5)
 
 
 def test_static_scratch_gemm_rejects_shapes_beyond_its_fixed_array():
