@@ -198,12 +198,12 @@ int reduce_impl(hl_ctx* ctx, const float* x, size_t n, float* out_dev, int mode,
 
 }  // namespace
 
-int bias_grad_impl(hl_ctx* ctx, const void* grad_out, int dtype, float* grad_bias, int rows, int cols) {
+int bias_grad_impl(hl_ctx* ctx, const void* grad_out, int dtype, float* grad_bias, int rows, int cols, FoldBatch* defer) {
   HL_REQUIRE(ctx && grad_out && grad_bias, "hl_bias_grad: null argument");
   HL_REQUIRE(rows > 0 && cols > 0, "hl_bias_grad: rows and cols must be positive");
   HL_REQUIRE(dtype == HL_F32 || dtype == HL_BF16, "hl_bias_grad: dtype must be f32 or bf16");
   ProfileScope prof(ctx, HL_PROF_BIAS_GRAD, (double)rows * cols * (double)dtype_size(dtype));
-  if (colsum_fast_applicable(dtype, cols, grad_out)) return colsum_fast(ctx, grad_out, dtype, grad_bias, rows, cols);
+  if (colsum_fast_applicable(dtype, cols, grad_out)) return colsum_fast(ctx, grad_out, dtype, grad_bias, rows, cols, defer);
   int slabs = std::min(std::max(rows / 256, 1), 64);
   const int rows_per_block = ceil_div(rows, slabs);
   slabs = ceil_div(rows, rows_per_block);

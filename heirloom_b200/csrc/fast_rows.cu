@@ -230,6 +230,40 @@ fold_partials_kernel(const float* __restrict__ partial, int blocks, int total, f
   }
 }
 
+// The same fold for up to FoldBatch::kMaxJobs reductions in one launch: blockIdx.y picks the job.
+struct FoldJobs {
+  FoldJob job[FoldBatch::kMaxJobs];
+};
+__global__ void __launch_bounds__(FOLD_WARPS * 32)
+fold_batch_kernel(const FoldJobs jobs) {
+  __shared__ double acc[FOLD_WARPS][33];
+  const FoldJob& j = jobs.job[blockIdx.y];
+  if ((int)blockIdx.x * 32 >= j.total) return;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int c = blockIdx.x * 32 + lane;
+  double s = 0.0;
+  if (c < j.total) {
+    for (int b0 = warp; b0 < j.blocks; b0 += FOLD_WARPS * 8) {
+      float v[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const int b = b0 + u * FOLD_WARPS;
+        v[u] = b < j.blocks ? j.partial[(size_t)b * j.total + c] : 0.f;
+      }
+#pragma unroll
+      for (int u = 0; u < 8; ++u) s += (double)v[u];
+    }
+  }
+  acc[warp][lane] = s;
+  __syncthreads();
+  if (warp == 0 && c < j.total) {
+#pragma unroll 8
+    for (int w = 1; w < FOLD_WARPS; ++w) s += acc[w][lane];
+    float* dst = c < j.features ? j.o0 : (c < 2 * j.features ? j.o1 : j.o2);
+    if (dst) dst[c % j.features] = (float)s;
+  }
+}
+
 // Column sums with 16-byte loads: a warp covers 32*VEC consecutive columns, the block's eight
 // warps take different rows of the slab.
 template <typename T, int VEC>
@@ -271,6 +305,36 @@ colsum_vec_kernel(const T* __restrict__ g, float* __restrict__ partial, int rows
 
 }  // namespace
 
+float* fold_batch_reserve(FoldBatch* batch, size_t elems) {
+  if (!batch || !batch->scratch || batch->n >= FoldBatch::kMaxJobs) return nullptr;
+  const size_t need = (elems + 63) & ~size_t(63);
+  if (batch->used + need > batch->capacity) return nullptr;
+  float* p = batch->scratch + batch->used;
+  batch->used += need;
+  return p;
+}
+
+void fold_batch_add(FoldBatch* batch, const float* partial, int blocks, int total, int features, float* o0, float* o1,
+                    float* o2) {
+  batch->jobs[batch->n++] = FoldJob{partial, blocks, total, features, o0, o1, o2};
+}
+
+int fold_batch_flush(hl_ctx* ctx, FoldBatch* batch) {
+  if (!batch || batch->n == 0) return HL_OK;
+  FoldJobs jobs{};
+  int widest = 0;
+  for (int i = 0; i < batch->n; ++i) {
+    jobs.job[i] = batch->jobs[i];
+    widest = std::max(widest, batch->jobs[i].total);
+  }
+  fold_batch_kernel<<<dim3(ceil_div(widest, 32), batch->n), FOLD_WARPS * 32, 0, ctx->stream>>>(jobs);
+  HL_LAUNCH_CHECK("fold_batch_kernel");
+  count_launch(ctx);
+  batch->n = 0;
+  batch->used = 0;
+  return HL_OK;
+}
+
 bool layer_norm_fast_applicable(int x_dtype, int y_dtype, int features, const void* x, const void* y) {
   return x_dtype == HL_BF16 && y_dtype == HL_BF16 && features % 8 == 0 && features <= 1024 &&
          ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y)) & 15) == 0;
@@ -297,15 +361,19 @@ int layer_norm_forward_fast(hl_ctx* ctx, const void* x, const float* gamma, cons
 
 int layer_norm_backward_fast(hl_ctx* ctx, const void* x, const float* gamma, const float* dy, const float* mean,
                              const float* rstd, const float* residual, float* dx_f32, void* dx_bf16, float* dgamma,
-                             float* dbeta, float* dx_colsum, int rows, int features) {
+                             float* dbeta, float* dx_colsum, int rows, int features, FoldBatch* defer) {
   const int wpr = ceil_div(features, 256);  // 1..4: a warp covers 256 columns
   const int groups = wpr >= 3 ? 12 / wpr : 8 / wpr;
   int blocks = std::min(2 * ctx->sm_count, ceil_div(rows, groups));
   const int rows_per_block = ceil_div(rows, blocks);
   blocks = ceil_div(rows, rows_per_block);
-  int rc = ensure_workspace(ctx, sizeof(float) * (size_t)blocks * 3 * features);
-  if (rc != HL_OK) return rc;
-  float* partial = reinterpret_cast<float*>(ctx->workspace);
+  float* partial = fold_batch_reserve(defer, (size_t)blocks * 3 * features);
+  const bool deferred = partial != nullptr;
+  if (!deferred) {
+    int rc = ensure_workspace(ctx, sizeof(float) * (size_t)blocks * 3 * features);
+    if (rc != HL_OK) return rc;
+    partial = reinterpret_cast<float*>(ctx->workspace);
+  }
   const size_t smem = sizeof(float) * (size_t)groups * 3 * features;  // at most 36 KB
 #define HL_LAUNCH(W)                                                                                              \
   ln_bwd_bf16_kernel<W><<<blocks, LnBwdShape<W>::THREADS, smem, ctx->stream>>>(                                   \
@@ -319,6 +387,11 @@ int layer_norm_backward_fast(hl_ctx* ctx, const void* x, const float* gamma, con
   }
 #undef HL_LAUNCH
   HL_LAUNCH_CHECK("ln_bwd_bf16_kernel");
+  if (deferred) {
+    fold_batch_add(defer, partial, blocks, 3 * features, features, dgamma, dbeta, dx_colsum);
+    count_launch(ctx);
+    return HL_OK;
+  }
   fold_partials_kernel<<<ceil_div(3 * features, 32), FOLD_WARPS * 32, 0, ctx->stream>>>(partial, blocks, 3 * features, dgamma,
                                                                                      dbeta, dx_colsum, features);
   HL_LAUNCH_CHECK("fold_partials_kernel");
@@ -331,15 +404,19 @@ bool colsum_fast_applicable(int dtype, int cols, const void* g) {
   return (dtype == HL_BF16 || dtype == HL_F32) && cols % vec == 0 && (reinterpret_cast<uintptr_t>(g) & 15) == 0;
 }
 
-int colsum_fast(hl_ctx* ctx, const void* g, int dtype, float* out, int rows, int cols) {
+int colsum_fast(hl_ctx* ctx, const void* g, int dtype, float* out, int rows, int cols, FoldBatch* defer) {
   const int vec = dtype == HL_BF16 ? 8 : 4;
   const int col_blocks = ceil_div(cols, 32 * vec);
   int slabs = std::max(1, std::min(std::min(64, ceil_div(rows, ROW_WARPS * 4)), (ctx->sm_count * 4) / col_blocks));
   const int rows_per_block = ceil_div(rows, slabs);
   slabs = ceil_div(rows, rows_per_block);
-  int rc = ensure_workspace(ctx, sizeof(float) * (size_t)slabs * cols);
-  if (rc != HL_OK) return rc;
-  float* partial = reinterpret_cast<float*>(ctx->workspace);
+  float* partial = fold_batch_reserve(defer, (size_t)slabs * cols);
+  const bool deferred = partial != nullptr;
+  if (!deferred) {
+    int rc = ensure_workspace(ctx, sizeof(float) * (size_t)slabs * cols);
+    if (rc != HL_OK) return rc;
+    partial = reinterpret_cast<float*>(ctx->workspace);
+  }
   dim3 grid(col_blocks, slabs);
   if (dtype == HL_BF16)
     colsum_vec_kernel<__nv_bfloat16, 8><<<grid, ROW_WARPS * 32, 0, ctx->stream>>>((const __nv_bfloat16*)g, partial, rows,
@@ -348,6 +425,11 @@ int colsum_fast(hl_ctx* ctx, const void* g, int dtype, float* out, int rows, int
     colsum_vec_kernel<float, 4><<<grid, ROW_WARPS * 32, 0, ctx->stream>>>((const float*)g, partial, rows, cols,
                                                                            rows_per_block);
   HL_LAUNCH_CHECK("colsum_vec_kernel");
+  if (deferred) {
+    fold_batch_add(defer, partial, slabs, cols, cols, out, nullptr, nullptr);
+    count_launch(ctx);
+    return HL_OK;
+  }
   fold_partials_kernel<<<ceil_div(cols, 32), FOLD_WARPS * 32, 0, ctx->stream>>>(partial, slabs, cols, out, nullptr, nullptr,
                                                                              cols);
   HL_LAUNCH_CHECK("fold_partials_kernel");

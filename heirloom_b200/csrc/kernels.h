@@ -20,21 +20,44 @@ int gemm_bf16_run(hl_ctx* ctx, const hl_gemm_desc* d, const void* a, const void*
 int gemm_bf16_ctx(hl_ctx* ctx, const hl_gemm_desc* d, const void* a, const void* b, void* c, const float* bias,
                   const void* aux_in, void* aux_out);
 
-int bias_grad_impl(hl_ctx* ctx, const void* grad_out, int dtype, float* grad_bias, int rows, int cols);
+// Column reductions (layer-norm parameter gradients, bias gradients) end in a fold of per-block partial rows.  A
+// caller that runs several of them before anyone reads the results hands in a FoldBatch: the kernels then leave their
+// partial rows in the batch's scratch and one launch (fold_batch_flush) folds all of them, in a fixed order.
+struct FoldJob {
+  const float* partial;  // [blocks][total]
+  int blocks, total, features;
+  float *o0, *o1, *o2;   // column c goes to o(c / features)[c % features]; null outputs are skipped
+};
+struct FoldBatch {
+  static constexpr int kMaxJobs = 8;
+  FoldJob jobs[kMaxJobs];
+  int n = 0;
+  float* scratch = nullptr;  // device memory, `capacity` floats
+  size_t capacity = 0, used = 0;
+};
+// Room for `elems` partial sums in the batch, or null when the batch is absent or full (the caller then folds at once).
+float* fold_batch_reserve(FoldBatch* batch, size_t elems);
+void fold_batch_add(FoldBatch* batch, const float* partial, int blocks, int total, int features, float* o0, float* o1,
+                    float* o2);
+int fold_batch_flush(hl_ctx* ctx, FoldBatch* batch);
+
+int bias_grad_impl(hl_ctx* ctx, const void* grad_out, int dtype, float* grad_bias, int rows, int cols,
+                   FoldBatch* defer = nullptr);
 
 int layer_norm_forward_impl(hl_ctx* ctx, const void* x, int x_dtype, const float* gamma, const float* beta, void* y,
                             int y_dtype, float* mean, float* rstd, int rows, int features, float eps);
 int layer_norm_backward_impl(hl_ctx* ctx, const void* x, int x_dtype, const float* gamma, const float* dy,
                              const float* mean, const float* rstd, const float* residual_grad, float* dx_f32,
-                             void* dx_bf16, float* dgamma, float* dbeta, float* dx_colsum, int rows, int features);
+                             void* dx_bf16, float* dgamma, float* dbeta, float* dx_colsum, int rows, int features,
+                             FoldBatch* defer = nullptr);
 bool layer_norm_fast_applicable(int x_dtype, int y_dtype, int features, const void* x, const void* y);
 int layer_norm_forward_fast(hl_ctx* ctx, const void* x, const float* gamma, const float* beta, void* y, float* mean,
                             float* rstd, int rows, int features, float eps);
 int layer_norm_backward_fast(hl_ctx* ctx, const void* x, const float* gamma, const float* dy, const float* mean,
                              const float* rstd, const float* residual, float* dx_f32, void* dx_bf16, float* dgamma,
-                             float* dbeta, float* dx_colsum, int rows, int features);
+                             float* dbeta, float* dx_colsum, int rows, int features, FoldBatch* defer = nullptr);
 bool colsum_fast_applicable(int dtype, int cols, const void* g);
-int colsum_fast(hl_ctx* ctx, const void* g, int dtype, float* out, int rows, int cols);
+int colsum_fast(hl_ctx* ctx, const void* g, int dtype, float* out, int rows, int cols, FoldBatch* defer = nullptr);
 int cross_entropy_impl(hl_ctx* ctx, const float* logits, long long ld, const int64_t* targets, int rows, int classes,
                        float grad_scale, float* loss_dev, float* row_loss, void* dlogits, int dlogits_dtype,
                        long long ld_dlogits);

@@ -462,7 +462,8 @@ int layer_norm_forward_impl(hl_ctx* ctx, const void* x, int x_dtype, const float
 
 int layer_norm_backward_impl(hl_ctx* ctx, const void* x, int x_dtype, const float* gamma, const float* dy,
                              const float* mean, const float* rstd, const float* residual_grad, float* dx_f32,
-                             void* dx_bf16, float* dgamma, float* dbeta, float* dx_colsum, int rows, int features) {
+                             void* dx_bf16, float* dgamma, float* dbeta, float* dx_colsum, int rows, int features,
+                             FoldBatch* defer) {
   HL_REQUIRE(ctx && x && gamma && dy, "hl_layer_norm_backward: null argument");
   HL_REQUIRE(rows > 0 && features > 0, "hl_layer_norm_backward: rows and features must be positive");
   HL_REQUIRE(features % 4 == 0 && features <= LNB_MAXJ * 128,
@@ -475,7 +476,7 @@ int layer_norm_backward_impl(hl_ctx* ctx, const void* x, int x_dtype, const floa
                                reinterpret_cast<uintptr_t>(dx_f32) | reinterpret_cast<uintptr_t>(dx_bf16);
   if (x_dtype == HL_BF16 && mean && rstd && features % 8 == 0 && (align_bits & 15) == 0)
     return layer_norm_backward_fast(ctx, x, gamma, dy, mean, rstd, residual_grad, dx_f32, dx_bf16, dgamma, dbeta,
-                                    dx_colsum, rows, features);
+                                    dx_colsum, rows, features, defer);
   HL_REQUIRE(!dx_colsum || dx_f32, "hl_layer_norm_backward: dx_colsum needs dx_f32 on this route");
   int blocks = std::min(ctx->sm_count * 2, ceil_div(rows, LNB_WARPS));
   const int rows_per_block = ceil_div(rows, blocks);

@@ -85,6 +85,7 @@ struct hl_decoder {
         *fa_dk = nullptr, *fa_dv = nullptr, *fa_do = nullptr;
   float *logits = nullptr, *meanf = nullptr, *rstdf = nullptr, *dx0 = nullptr, *dx1 = nullptr, *dtmp = nullptr;
   int64_t *tokens = nullptr, *targets = nullptr;
+  FoldBatch fold;  // column reductions of one block's backward, folded by one launch before its buckets are flushed
   float* loss_dev = nullptr;
   float* loss_host = nullptr;  // pinned
   float* norm_dev = nullptr;
@@ -332,6 +333,19 @@ int plan_activations(hl_decoder* m, bool measure_only, size_t* bytes_out) {
     m->fa_probs = carve<float>(cur, (size_t)c.batch * c.n_heads * c.context * c.context);
   }
   plan_memory_buffers(m, cur);
+  {
+    // partial rows of the column reductions: two layer norms (at most 2 CTAs per SM, three sums each) and the bias
+    // column sums (at most 64 slabs) of one block, or the head's
+    const size_t sm = (size_t)m->ctx->sm_count;
+    const size_t ln = 2 * sm * 3 * d + 64;
+    const size_t wide = m->has_memory ? std::max(F, (size_t)(m->mem.key_dim + m->mem.value_dim)) : F;
+    const size_t layer = 2 * ln + 64 * (wide + 3 * d) + 4 * 64;
+    const size_t head = ln + 64 * V + 2 * 64;
+    m->fold.capacity = std::max(layer, head);
+    m->fold.scratch = carve<float>(cur, m->fold.capacity);
+    m->fold.n = 0;
+    m->fold.used = 0;
+  }
   m->tokens = carve<int64_t>(cur, N);
   m->targets = carve<int64_t>(cur, N);
   m->loss_dev = carve<float>(cur, 4);
@@ -659,14 +673,18 @@ int backward(hl_decoder* m) {
   HL_TRY(cross_entropy_impl(ctx, m->logits, V, m->targets, N, V, 1.0f, m->loss_dev, nullptr, m->dlogits, HL_BF16, V));
   // lm_head
   HL_TRY(g.run(V, d, N, m->dlogits, V, HL_MN_MAJOR, m->z, d, HL_MN_MAJOR, G + m->off_head_w, d, HL_F32));
-  HL_TRY(bias_grad_impl(ctx, m->dlogits, HL_BF16, G + m->off_head_b, N, V));
+  FoldBatch* fb = &m->fold;
+  fb->n = 0;
+  fb->used = 0;
+  HL_TRY(bias_grad_impl(ctx, m->dlogits, HL_BF16, G + m->off_head_b, N, V, fb));
   HL_TRY(g.run(N, d, V, m->dlogits, V, HL_K_MAJOR, W + m->off_head_w, d, HL_MN_MAJOR, m->dtmp, d, HL_F32));
   float* dx = m->dx0;
   float* dx_next = m->dx1;
   // every layer-norm backward also returns the column sums of the gradient it writes: the bias
   // gradient of the projection that produced that residual-stream value (fc2 or out_proj)
   HL_TRY(layer_norm_backward_impl(ctx, m->x[c.n_layers], HL_BF16, P + m->off_lnf_g, m->dtmp, m->meanf, m->rstdf, nullptr, dx,
-                                  m->dxb, G + m->off_lnf_g, G + m->off_lnf_b, G + m->lo[c.n_layers - 1].out_bias(), N, d));
+                                  m->dxb, G + m->off_lnf_g, G + m->off_lnf_b, G + m->lo[c.n_layers - 1].out_bias(), N, d, fb));
+  HL_TRY(fold_batch_flush(ctx, fb));
   HL_TRY(flush_buckets(m, m->off_lnf_b + d));
   for (int l = c.n_layers - 1; l >= 0; --l) {
     const LayerOffsets& o = m->lo[l];
@@ -683,12 +701,12 @@ int backward(hl_decoder* m) {
       HL_TRY(hl_gelu_backward(ctx, ma.gpre, m->m_dgate, m->m_dgpre, HL_F32, nv));
       HL_TRY(hl_cast(ctx, m->m_dgpre, HL_F32, m->m_dgpre_b, HL_BF16, nv));
       HL_TRY(g.run(vd, d, N, m->m_dgpre_b, vd, HL_MN_MAJOR, a.c, d, HL_MN_MAJOR, G + o.wg_m, d, HL_F32));
-      HL_TRY(bias_grad_impl(ctx, m->m_dgpre, HL_F32, G + o.bg_m, N, vd));
+      HL_TRY(bias_grad_impl(ctx, m->m_dgpre, HL_F32, G + o.bg_m, N, vd, fb));
       HL_TRY(g.run(N, d, vd, m->m_dgpre_b, vd, HL_K_MAJOR, W + o.wg_m, d, HL_MN_MAJOR, m->dtmp, d, HL_F32));
       HL_TRY(memory_core_backward(m, l, m->m_dweighted));
       HL_TRY(hl_cast(ctx, m->m_dq, HL_F32, m->m_dq_b, HL_BF16, (size_t)N * kd));
       HL_TRY(g.run(kd, d, N, m->m_dq_b, kd, HL_MN_MAJOR, a.c, d, HL_MN_MAJOR, G + o.wq_m, d, HL_F32));
-      HL_TRY(bias_grad_impl(ctx, m->m_dq, HL_F32, G + o.bq_m, N, kd));
+      HL_TRY(bias_grad_impl(ctx, m->m_dq, HL_F32, G + o.bq_m, N, kd, fb));
       HL_TRY(g.run(N, d, kd, m->m_dq_b, kd, HL_K_MAJOR, W + o.wq_m, d, HL_MN_MAJOR, m->m_dc2, d, HL_F32));
       HL_TRY(hl_binary_f32(ctx, HL_ADD, m->dtmp, m->m_dc2, m->dtmp, (size_t)N * d));
     } else {
@@ -696,12 +714,12 @@ int backward(hl_decoder* m) {
     HL_TRY(g.run(d, F, N, m->dxb, d, HL_MN_MAJOR, a.g, F, HL_MN_MAJOR, G + o.w2, F, HL_F32));
     HL_TRY(g.run(N, F, d, m->dxb, d, HL_K_MAJOR, W + o.w2, F, HL_MN_MAJOR, m->dh, F, HL_BF16, HL_EPI_DGELU, nullptr, a.h, F));
     HL_TRY(g.run(F, d, N, m->dh, F, HL_MN_MAJOR, a.c, d, HL_MN_MAJOR, G + o.w1, d, HL_F32));
-    HL_TRY(bias_grad_impl(ctx, m->dh, HL_BF16, G + o.b1, N, F));
+    HL_TRY(bias_grad_impl(ctx, m->dh, HL_BF16, G + o.b1, N, F, fb));
     HL_TRY(g.run(N, d, F, m->dh, F, HL_K_MAJOR, W + o.w1, d, HL_MN_MAJOR, m->dtmp, d, HL_F32));
     }
     // dr = dx + LN2'(dc)
     HL_TRY(layer_norm_backward_impl(ctx, a.r, HL_BF16, P + o.ln2g, m->dtmp, a.mean2, a.rstd2, dx, dx_next, m->dxb,
-                                    G + o.ln2g, G + o.ln2b, G + o.bo, N, d));
+                                    G + o.ln2g, G + o.ln2b, G + o.bo, N, d, fb));
     std::swap(dx, dx_next);  // dx is now dL/dr
     HL_TRY(g.run(d, d, N, m->dxb, d, HL_MN_MAJOR, a.o, d, HL_MN_MAJOR, G + o.wo, d, HL_F32));
     HL_TRY(g.run(N, d, d, m->dxb, d, HL_K_MAJOR, W + o.wo, d, HL_MN_MAJOR, m->dob, d, HL_BF16));
@@ -715,12 +733,13 @@ int backward(hl_decoder* m) {
       HL_TRY(attention_backward_wide(m, a.qkv, m->dob, m->dqkv));
     }
     HL_TRY(g.run(3 * d, d, N, m->dqkv, 3 * d, HL_MN_MAJOR, a.a, d, HL_MN_MAJOR, G + o.wqkv, d, HL_F32));
-    HL_TRY(bias_grad_impl(ctx, m->dqkv, HL_BF16, G + o.bqkv, N, 3 * d));
+    HL_TRY(bias_grad_impl(ctx, m->dqkv, HL_BF16, G + o.bqkv, N, 3 * d, fb));
     HL_TRY(g.run(N, d, 3 * d, m->dqkv, 3 * d, HL_K_MAJOR, W + o.wqkv, d, HL_MN_MAJOR, m->dtmp, d, HL_F32));
     // dx_in = dr + LN1'(da)
     HL_TRY(layer_norm_backward_impl(ctx, m->x[l], HL_BF16, P + o.ln1g, m->dtmp, a.mean1, a.rstd1, dx, dx_next, m->dxb,
-                                    G + o.ln1g, G + o.ln1b, l > 0 ? G + m->lo[l - 1].out_bias() : nullptr, N, d));
+                                    G + o.ln1g, G + o.ln1b, l > 0 ? G + m->lo[l - 1].out_bias() : nullptr, N, d, fb));
     std::swap(dx, dx_next);
+    HL_TRY(fold_batch_flush(ctx, fb));
     HL_TRY(flush_buckets(m, o.ln1b + d));
   }
   // embeddings: scatter-add into zeroed tables

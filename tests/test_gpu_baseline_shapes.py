@@ -89,8 +89,9 @@ def test_gpt_shape_full_batch_equals_the_average_of_its_sequences():
         scale = np.abs(mean[n]).max() + 1e-30
         dev = np.abs(got[n] - mean[n]).max() / scale
         worst = max(worst, dev)
-        # f32 sums in another order; the attention backward adds its dQ tiles in arrival order
-        assert dev <= 2e-3, (n, dev)
+        # f32 sums in another order (the attention backward adds its dQ tiles in arrival order), which moves a few bf16
+        # roundings downstream by one step; measured worst 1.5e-3
+        assert dev <= 4e-3, (n, dev)
     print("gpt-shape whole batch vs parts, worst |g-mean|/max|mean|:", worst)
 
 
@@ -151,5 +152,5 @@ def test_memory_shape_full_batch_equals_the_average_of_its_parts():
         scale = np.abs(mean[n]).max() + 1e-30
         dev = np.abs(got[n] - mean[n]).max() / scale
         worst = max(worst, dev)
-        assert dev <= 2e-3, (n, dev)
+        assert dev <= 4e-3, (n, dev)  # measured worst 1.8e-3
     print("memory-shape whole batch vs parts, worst |g-mean|/max|mean|:", worst)

@@ -80,7 +80,7 @@ def test_ten_steps_parameters_and_losses_track_the_amp_oracle():
         viol = np.abs(got - want) / np.maximum(np.abs(want), floor)
         frac_bad = np.mean(viol > 2e-2)
         worst = max(worst, frac_bad)
-        assert frac_bad <= 0.02, (name, frac_bad, viol.max())
+        assert frac_bad <= 0.015, (name, frac_bad, viol.max())  # measured worst: 0.011 (a 1024-element bias)
     print("amp dense model, worst fraction of elements outside 2e-2 after 10 steps:", worst)
     model.close()
 

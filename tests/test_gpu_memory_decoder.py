@@ -88,7 +88,7 @@ def test_amp_route_tracks_the_oracle_and_routes_almost_identically():
     # the query projection runs at f32 accuracy (bf16 pieces of the weight), as the reference keeps it in f32; what is
     # left are slots whose scores tie within the bf16 rounding of the activations that feed the block
     assert min(agree) >= 0.97, agree
-    assert max(gaps) <= 0.05, gaps
+    assert max(gaps) <= 0.08, gaps
     floor = 5 * 1e-3
     report, measured = {}, {}
     for name in ho.memory_parameter_names(ocfg, omem):
@@ -98,9 +98,13 @@ def test_amp_route_tracks_the_oracle_and_routes_almost_identically():
         bad = np.abs(got - want) > 2e-2 * np.maximum(np.abs(want), floor)
         # Small vectors that start at zero (biases) move by about lr per step whatever the gradient's
         # size, so a handful of sign flips already is several per cent of their elements.
-        cls = "memory" if "memory" in name else ("large" if got.size >= 1024 else "small")
+        # The shared tables are where the last routing differences show: a slot chosen on one side only gives its
+        # value row and half-key rows a gradient there and plain decay here, and AdamW turns any gradient into a step
+        # of about lr; over five steps of two blocks about one row in four meets at least one such event.
+        cls = ("tables" if name.startswith("shared_memory") else "memory projections" if "memory" in name
+               else "large" if got.size >= 1024 else "small")
         measured[cls] = max(measured.get(cls, 0.0), float(bad.mean()))
-        limit = {"memory": 0.25, "large": 0.03, "small": 0.10}[cls]
+        limit = {"tables": 0.30, "memory projections": 0.10, "large": 0.01, "small": 0.07}[cls]
         if bad.mean() > limit:
             report[name] = float(bad.mean())
     print("amp memory model, worst fraction of elements outside 2e-2 after 5 steps, by class:", measured)
