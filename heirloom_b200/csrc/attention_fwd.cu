@@ -202,8 +202,14 @@ flash_attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
         for (int i = 0; i < FA_BN; ++i)
           if (key0 + i > t) sb[i] = 0xff800000u;
       }
+      {  // eight independent running maxima, so that the 64 comparisons are not one dependent chain
+        float mx[8];
 #pragma unroll
-      for (int i = 0; i < FA_BN; ++i) m_tile = fmaxf(m_tile, __uint_as_float(sb[i]));
+        for (int u = 0; u < 8; ++u) mx[u] = __uint_as_float(sb[u]);
+#pragma unroll
+        for (int i = 8; i < FA_BN; ++i) mx[i & 7] = fmaxf(mx[i & 7], __uint_as_float(sb[i]));
+        m_tile = fmaxf(fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])), fmaxf(fmaxf(mx[4], mx[5]), fmaxf(mx[6], mx[7])));
+      }
       const float m_new = m_tile * p.scale_log2;  // finite in tile 0: key 0 is visible to every row
       const bool raise = m_new > m_ref + kRaise;  // always true in tile 0 (m_ref = -inf)
       if (j == 0) {
