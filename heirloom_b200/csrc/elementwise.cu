@@ -269,6 +269,63 @@ int hl_fill_f32(hl_ctx* ctx, float* out, float value, size_t n) {
   return HL_OK;
 }
 
+// ---- plain SGD, index ranges and index concatenation ---------------------------------------------------------
+static __global__ void sgd_update_kernel(float* __restrict__ param, const float* __restrict__ grad, float lr, size_t n) {
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+    param[i] = __fsub_rn(param[i], __fmul_rn(lr, grad[i]));  // two roundings, as the reference's mul then sub
+}
+static __global__ void arange_i64_kernel(int64_t* __restrict__ out, size_t n) {
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+    out[i] = (int64_t)i;
+}
+static __global__ void copy_i64_kernel(const int64_t* __restrict__ src, int64_t* __restrict__ dst, size_t n) {
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+    dst[i] = src[i];
+}
+
+int hl_sgd_update_f32(hl_ctx* ctx, float* param, const float* grad, float lr, size_t n) {
+  HL_REQUIRE(ctx && ((param && grad) || n == 0), "hl_sgd_update_f32: null argument");
+  HL_REQUIRE(lr > 0.f, "sgd_update_f32_buffer learning rate must be positive, got " + std::to_string(lr));
+  if (n == 0) return HL_OK;
+  sgd_update_kernel<<<ew_grid(ctx, n), EW_THREADS, 0, ctx->stream>>>(param, grad, lr, n);
+  HL_LAUNCH_CHECK("sgd_update_kernel");
+  count_launch(ctx);
+  return HL_OK;
+}
+
+int hl_arange_i64(hl_ctx* ctx, int64_t* out, size_t n) {
+  HL_REQUIRE(ctx && (out || n == 0), "hl_arange_i64: null argument");
+  HL_REQUIRE(n <= 0xffffffffull, "i64_arange len exceeds the u32 launch limit");
+  if (n == 0) return HL_OK;
+  arange_i64_kernel<<<ew_grid(ctx, n), EW_THREADS, 0, ctx->stream>>>(out, n);
+  HL_LAUNCH_CHECK("arange_i64_kernel");
+  count_launch(ctx);
+  return HL_OK;
+}
+
+int hl_concat_i64(hl_ctx* ctx, const int64_t* const* inputs, const size_t* lengths, int count, int64_t* out, size_t out_capacity) {
+  HL_REQUIRE(ctx && inputs && lengths, "hl_concat_i64: null argument");
+  HL_REQUIRE(count >= 1, "concat_i64_buffers requires at least one input buffer");
+  size_t total = 0;
+  for (int i = 0; i < count; ++i) {
+    HL_REQUIRE(lengths[i] == 0 || inputs[i], "hl_concat_i64: null input buffer");
+    HL_REQUIRE(total + lengths[i] >= total, "concat_i64_buffers total length overflow");
+    total += lengths[i];
+  }
+  HL_REQUIRE(total <= out_capacity, "hl_concat_i64: the output holds " + std::to_string(out_capacity) + " elements, the inputs " +
+                                        std::to_string(total));
+  HL_REQUIRE(out || total == 0, "hl_concat_i64: null output");
+  size_t offset = 0;
+  for (int i = 0; i < count; ++i) {
+    if (lengths[i] == 0) continue;
+    copy_i64_kernel<<<ew_grid(ctx, lengths[i]), EW_THREADS, 0, ctx->stream>>>(inputs[i], out + offset, lengths[i]);
+    HL_LAUNCH_CHECK("copy_i64_kernel");
+    count_launch(ctx);
+    offset += lengths[i];
+  }
+  return HL_OK;
+}
+
 int hl_relu_f32(hl_ctx* ctx, const float* x, float* out, size_t n) {
   HL_REQUIRE(ctx && ((x && out) || n == 0), "hl_relu_f32: null argument");
   if (n == 0) return HL_OK;

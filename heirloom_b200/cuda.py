@@ -94,6 +94,31 @@ class Context:
         return torch.zeros(shape, dtype=dtype, device=self.torch_device)
 
 
+# ---- plain SGD, index ranges, index concatenation ---------------------------------------------------
+def sgd_update_f32(ctx: Context, param: torch.Tensor, grad: torch.Tensor, lr: float) -> None:
+    """`hl_sgd_update_f32`: param -= lr * grad in place."""
+    check(ctx.lib.hl_sgd_update_f32(ctx.handle, _p(param), _p(grad), c_float(lr), c_size_t(param.numel())))
+
+
+def arange_i64(ctx: Context, n: int) -> torch.Tensor:
+    out = torch.empty(n, dtype=torch.int64, device=ctx.torch_device)
+    check(ctx.lib.hl_arange_i64(ctx.handle, _p(out), c_size_t(n)))
+    return out
+
+
+def concat_i64(ctx: Context, inputs) -> torch.Tensor:
+    """`hl_concat_i64`: the int64 device vectors one after the other."""
+    if not inputs:
+        ptrs, lens = (c_void_p * 1)(), (c_size_t * 1)()
+        check(ctx.lib.hl_concat_i64(ctx.handle, ptrs, lens, c_int(0), None, c_size_t(0)))
+    total = sum(int(t.numel()) for t in inputs)
+    out = torch.empty(total, dtype=torch.int64, device=ctx.torch_device)
+    ptrs = (c_void_p * len(inputs))(*[t.data_ptr() if t.numel() else None for t in inputs])
+    lens = (c_size_t * len(inputs))(*[int(t.numel()) for t in inputs])
+    check(ctx.lib.hl_concat_i64(ctx.handle, ptrs, lens, c_int(len(inputs)), _p(out), c_size_t(total)))
+    return out
+
+
 # ---- elementwise ------------------------------------------------------------------------------
 def binary_f32(ctx: Context, op: int, a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
     out = torch.empty_like(a)

@@ -100,6 +100,17 @@ int hl_binary_f32(hl_ctx* ctx, int op, const float* a, const float* b, float* ou
 int hl_scale_f32(hl_ctx* ctx, const float* a, float s, float* out, size_t n);
 /* kernels.ptx:1131. */
 int hl_fill_f32(hl_ctx* ctx, float* out, float value, size_t n);
+/* Plain SGD, param -= lr * grad with the product and the difference rounded separately; lr must be positive
+ * (sgd_update_f32_buffer, heirloom-kernels/src/cuda.rs:6280-6303; heirloom_sgd_update_f32, kernels.ptx:356). */
+int hl_sgd_update_f32(hl_ctx* ctx, float* param, const float* grad, float lr, size_t n);
+/* out[i] = i (i64_arange_buffer, cuda.rs:2090-2103; heirloom_i64_arange, kernels.ptx:861): the position ids of the
+ * learned position embedding. */
+int hl_arange_i64(hl_ctx* ctx, int64_t* out, size_t n);
+/* The inputs one after the other in `out` (concat_i64_buffers, cuda.rs:6437-6490; heirloom_copy_i64_with_offset,
+ * kernels.ptx:1066): how the selected rows of several memory blocks become one row list for the row-set AdamW.
+ * Empty inputs are skipped; `out_capacity` is checked against the summed lengths before anything is launched. */
+int hl_concat_i64(hl_ctx* ctx, const int64_t* const* inputs, const size_t* lengths, int count, int64_t* out,
+                  size_t out_capacity);
 /* ReLU and its gradient (kernels.ptx:4724, :4755). */
 int hl_relu_f32(hl_ctx* ctx, const float* x, float* out, size_t n);
 int hl_relu_backward_f32(hl_ctx* ctx, const float* x, const float* grad_out, float* grad_in, size_t n);

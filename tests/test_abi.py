@@ -49,3 +49,20 @@ def test_missing_library_is_a_loud_error(monkeypatch, tmp_path):
     monkeypatch.setattr(_lib, "LIB_PATH", tmp_path / "absent.so")
     with pytest.raises(_lib.HeirloomError):
         _lib.load()
+
+
+def test_rust_shim_is_current_and_binds_every_entry_point():
+    """`include/heirloom_b200.rs` is generated from the header: regenerating gives the committed file, and its
+    `extern "C"` block names every declared entry point (the reference drives this path from Rust)."""
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("make_rust_shim", ROOT / "include" / "make_rust_shim.py")
+    gen = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(gen)
+    text = (ROOT / "include" / "heirloom_b200.rs").read_text()
+    assert gen.generate() == text
+    bound = set(re.findall(r"pub fn (hl_[a-z0-9_]+)\(", text))
+    assert bound == set(declared_symbols())
+    # the safe layer keeps the names of the reference's wrappers for the ops of the step
+    for name in ("layer_norm_forward_f32_buffers", "adamw_update_f32_buffers", "sgd_update_f32_buffer", "concat_i64_buffers",
+                 "i64_arange_buffer", "matmul_bf16_tensor_core_rhs_transposed_f32_buffers"):
+        assert f"pub fn {name}(" in text

@@ -343,3 +343,30 @@ def test_adamw_plan_steps_like_the_multi_tensor_call():
     for a, b in zip(ps + ms + vs + sh, ps2 + ms2 + vs2 + sh2):
         assert np.array_equal(host(a), host(b))
     plan.close()
+
+
+def test_sgd_update_rounds_product_and_difference_separately():
+    from heirloom_b200 import cuda
+    from heirloom_b200._lib import HeirloomError
+    c = ctx()
+    rng = np.random.default_rng(41)
+    p, g = rng.standard_normal(10007).astype(np.float32), rng.standard_normal(10007).astype(np.float32)
+    dp = dev(p)
+    cuda.sgd_update_f32(c, dp, dev(g), 0.05)
+    want = (p - (np.float32(0.05) * g).astype(np.float32)).astype(np.float32)   # mul.f32 then sub.f32 (kernels.ptx:383-384)
+    assert np.array_equal(host(dp).astype(np.float32), want)
+    with pytest.raises(HeirloomError, match="learning rate must be positive"):
+        cuda.sgd_update_f32(c, dp, dev(g), 0.0)
+
+
+def test_arange_and_concat_of_index_vectors():
+    from heirloom_b200 import cuda
+    from heirloom_b200._lib import HeirloomError
+    c = ctx()
+    a = cuda.arange_i64(c, 1025)
+    assert np.array_equal(host(a), np.arange(1025))
+    parts = [torch.tensor([5, -3, 2 ** 40], dtype=torch.int64, device="cuda"), torch.empty(0, dtype=torch.int64, device="cuda"), a]
+    got = cuda.concat_i64(c, parts)
+    assert np.array_equal(host(got), np.concatenate([host(t) for t in parts]))
+    with pytest.raises(HeirloomError, match="at least one input"):
+        cuda.concat_i64(c, [])
