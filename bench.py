@@ -185,7 +185,9 @@ def cpu_port_run(sample_tokens=(8, 24)):
                 sample=f"C++ f64 restatement, 1 thread: forward+backward of 1 sequence of {sample_tokens[0]} and of "
                        f"{sample_tokens[1]} tokens through the full 12-layer model and head ({seconds[0]:.1f} s, "
                        f"{seconds[1]:.1f} s: {per_token:.3f} s per token + {fixed:.1f} s per step) and one AdamW step over "
-                       f"all {total} parameters ({t_opt:.1f} s), scaled to the {tokens}-token step")
+                       f"all {total} parameters ({t_opt:.1f} s), scaled to the {tokens}-token step; the two-point fit is "
+                       f"linear in the tokens, so the attention term that grows with the square of the sequence length "
+                       f"(about 8 % of the flops at 1024 tokens) is left out and the CPU time is understated by that much")
 
 
 def cpu_blas_run(steps, warmup, sample_tokens=256):
@@ -305,7 +307,7 @@ def run_ours(args):
 
     # ---- per-kernel timing of one more pass, for the roofline of the dominant kernel --------------
     # Every rank runs these steps (the gradient exchange needs all of them); only rank 0 times them.
-    prof = None
+    prof, comm = None, None
     prof_steps = min(args.steps, 5)
     if rank == 0:
         cuda.check(ctx.lib.hl_profile_enable(ctx.handle, 1))
@@ -321,14 +323,49 @@ def run_ours(args):
                  "other"]
         prof = {n: {"ms_per_step": p.ms[i] / prof_steps, "work_per_step": p.work[i] / prof_steps,
                     "scopes_per_step": p.scopes[i] / prof_steps} for i, n in enumerate(names)}
+        exposed_ms, waits = model.comm_exposed_ms()
+        comm = {"exposed_ms_per_step": exposed_ms / prof_steps, "waits_per_step": waits / prof_steps,
+                "how": "CUDA events around every wait of the compute stream for the collective stream, profiled pass"}
     barrier()
+
+    # ---- replicas stay identical: (sum, sum of squares) of every parameter, compared across the ranks ------------
+    # (the reference's drift evidence, src/bin/heirloom/runtime.rs:3403-3416)
+    total, total_sq = 0.0, 0.0
+    for name in model.parameter_names():
+        w = model.parameter(name).astype(np.float64)
+        total += float(w.sum())
+        total_sq += float((w * w).sum())
+    sums = [(total, total_sq)]
+    if world > 1:
+        gathered = [None] * world
+        dist.all_gather_object(gathered, (total, total_sq))
+        sums = gathered
+    checksum = {"sum": sums[0][0], "sum_of_squares": sums[0][1], "ranks": len(sums),
+                "equal_across_ranks": all(s == sums[0] for s in sums)}
     model.close()
+
+    # ---- the memory-transformer configuration at the same number of GPUs (its own JSON object in the line) --------
+    from heirloom_b200 import memory_bench
+    memory_line = memory_bench.run(ctx, dist if world > 1 else None, world, rank, steps=min(args.steps, 10), warmup=3,
+                                   policy="full")
     if world > 1:
         cuda.check(ctx.lib.hl_nccl_destroy(ctx.handle))
         dist.destroy_process_group()
 
     if rank != 0:
         return
+    memory_step = {"ms_per_step": memory_line["ms_per_step"], "tokens_per_s": memory_line["value"], "policy": "full",
+                   "n_gpus": world, "memory_kernel_share": memory_line["memory_kernel_share"],
+                   "loss_after": memory_line["loss_after"], "config": memory_line["config"]["workload"],
+                   "kernel_breakdown_ms_per_step": memory_line["kernel_breakdown_ms_per_step"]}
+    kernel_sweep = None
+    if world == 1 and not args.no_kernel_sweep:
+        # the kernel-level configuration: one figure per piece of the step (all of heirloom_b200.kernel_bench's cases
+        # but the 1.3 G-parameter AdamW, which holds 21 GB)
+        from heirloom_b200 import kernel_bench
+        wanted = [n for n in kernel_bench.build_cases(ctx) if n != "adamw_1300m"]
+        kernel_sweep = {r["case"]: {"us": r["us"], "frac": r["frac"], "unit": r["unit"]}
+                        for r in kernel_bench.sweep(ctx, wanted, iters=10, warmup=2)}
     peaks = measured_peaks()
     ms_per_step = ms_total / args.steps
     value = tokens_per_step / (ms_per_step * 1e-3)
@@ -360,6 +397,10 @@ def run_ours(args):
                      "traffic": GEMM_DRAM_BYTES_PER_LAUNCH, "peak_source": peaks["source"] + " sustained bf16 (kernel timed inside a long step)",
                      "launches_per_step": gemm["scopes_per_step"], "ms_per_step": gemm["ms_per_step"]},
         "kernel_breakdown_ms_per_step": {k: round(v["ms_per_step"], 4) for k, v in prof.items()},
+        "comm": comm,
+        "replica_checksum": checksum,
+        "memory_step": memory_step,
+        "kernel_sweep": kernel_sweep,
         "cpu_baseline": cpu,
     }
     print(json.dumps(line))
@@ -374,6 +415,7 @@ if __name__ == "__main__":
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-kernel-sweep", action="store_true")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

@@ -103,6 +103,10 @@ struct hl_decoder {
   std::vector<cudaEvent_t> bucket_done;  // recorded on the collective stream after each bucket's all-reduce
   bool comm_pending = false;             // the compute stream has not yet waited for this step's collectives
   cudaEvent_t comm_done = nullptr;
+  // while per-kernel timing is on: events around every wait of the compute stream for the collective stream, so that
+  // the time the step spends exposed to the gradient exchange can be read back (hl_decoder_comm_exposed_ms)
+  std::vector<cudaEvent_t> wait_begin, wait_end;
+  size_t waits_recorded = 0;
   unsigned long long launches_last_step = 0;
   // product-key memory (shared tables, MemoryTransformerLm with memory layers)
   bool has_memory = false;
@@ -434,6 +438,8 @@ int memory_core_forward(hl_decoder* m, int l) {
   const float* P = m->params;
   const int N = m->N, kd = m->mem.key_dim, vd = m->mem.value_dim, k = m->mem.top_k, side = m->side;
   const int beam = std::min(side, std::max(k, (int)ceil(sqrt((double)k))));  // product_key_beam, :2014-2016
+  // timed as one family ("other" in the per-kernel profile); work = table rows gathered, in bytes
+  ProfileScope prof(ctx, HL_PROF_OTHER, (double)N * k * (double)(kd + vd) * 4.0 + 2.0 * (double)N * side * 4.0);
   HL_TRY(hl_product_key_side_scores_f32(ctx, a.query, kd, P + m->off_kl, P + m->off_kr, m->m_ls, m->m_rs, N, side, kd));
   HL_TRY(hl_product_key_topk_from_side_scores(ctx, m->m_ls, m->m_rs, a.idx, N, side, k, beam));
   HL_TRY(hl_memory_selected_scores_forward(ctx, a.idx, a.query, kd, P + m->off_kl, P + m->off_kr, m->m_scores, N, k, side, kd,
@@ -449,6 +455,7 @@ int memory_core_backward(hl_decoder* m, int l, const float* dweighted) {
   const float* P = m->params;
   float* G = m->grads;
   const int N = m->N, kd = m->mem.key_dim, vd = m->mem.value_dim, k = m->mem.top_k, side = m->side;
+  ProfileScope prof(ctx, HL_PROF_OTHER, (double)N * k * (double)(kd + 3 * vd) * 4.0);
   HL_TRY(hl_memory_weighted_value_backward(ctx, a.idx, a.weights, P + m->off_val, dweighted, m->m_dw, G + m->off_val, N, k,
                                            m->mem.slots, vd));
   HL_TRY(hl_softmax_rows_backward_f32(ctx, a.weights, m->m_dw, m->m_dscores, N, k));
@@ -898,10 +905,34 @@ int backward_f32(hl_decoder* m) {
   return HL_OK;
 }
 
+// The compute stream waits for `ev` of the collective stream.  With per-kernel timing on, the wait is bracketed by two
+// timing events: the first completes when the compute stream has run dry, the second when the collective has arrived,
+// so their distance is the time this wait left the GPU's compute stream idle.
+int wait_on_collective(hl_decoder* m, cudaEvent_t ev) {
+  cudaStream_t s = m->ctx->stream;
+  const bool timed = m->ctx->profiler != nullptr;
+  if (timed) {
+    if (m->waits_recorded == m->wait_begin.size()) {
+      cudaEvent_t a = nullptr, b = nullptr;
+      HL_CUDA(cudaEventCreate(&a));
+      HL_CUDA(cudaEventCreate(&b));
+      m->wait_begin.push_back(a);
+      m->wait_end.push_back(b);
+    }
+    HL_CUDA(cudaEventRecord(m->wait_begin[m->waits_recorded], s));
+  }
+  HL_CUDA(cudaStreamWaitEvent(s, ev, 0));
+  if (timed) {
+    HL_CUDA(cudaEventRecord(m->wait_end[m->waits_recorded], s));
+    m->waits_recorded += 1;
+  }
+  return HL_OK;
+}
+
 // Make the compute stream wait for every gradient collective of the step.
 int wait_for_collectives(hl_decoder* m) {
   if (m->comm_pending) {
-    HL_CUDA(cudaStreamWaitEvent(m->ctx->stream, m->comm_done, 0));
+    HL_TRY(wait_on_collective(m, m->comm_done));
     m->comm_pending = false;
   }
   return HL_OK;
@@ -949,7 +980,7 @@ int optimizer_step(hl_decoder* m) {
     // exchange that follows the last bucket on the collective stream.  A group that reaches into the table waits for
     // the end of that stream's work (which covers every bucket as well).
     const bool reaches_values = m->has_memory && (b1 == m->n_buckets || (size_t)upto * chunk > m->off_val);
-    HL_CUDA(cudaStreamWaitEvent(ctx->stream, reaches_values ? m->comm_done : m->bucket_done[b1 - 1], 0));
+    HL_TRY(wait_on_collective(m, reaches_values ? m->comm_done : m->bucket_done[b1 - 1]));
     HL_TRY(adam_plan_step_range(ctx, m->plan, &hp, first, upto - first));
     first = upto;
   }
@@ -1104,6 +1135,8 @@ void hl_decoder_destroy(hl_decoder* m) {
   for (auto ev : m->bucket_ready) if (ev) cudaEventDestroy(ev);
   for (auto ev : m->bucket_done) if (ev) cudaEventDestroy(ev);
   if (m->comm_done) cudaEventDestroy(m->comm_done);
+  for (auto ev : m->wait_begin) cudaEventDestroy(ev);
+  for (auto ev : m->wait_end) cudaEventDestroy(ev);
   adam_plan_destroy(m->plan);
   adam_plan_destroy(m->plan_tables);
   adam_plan_destroy(m->plan_no_values);
@@ -1508,6 +1541,21 @@ int hl_decoder_loss(hl_decoder* m, float* loss_host) {
 }
 
 unsigned long long hl_decoder_launches_last_step(hl_decoder* m) { return m ? m->launches_last_step : 0; }
+
+int hl_decoder_comm_exposed_ms(hl_decoder* m, float* total_ms, int* waits) {
+  HL_REQUIRE(m && total_ms, "hl_decoder_comm_exposed_ms: null argument");
+  HL_CUDA(cudaStreamSynchronize(m->ctx->stream));
+  float sum = 0.f;
+  for (size_t i = 0; i < m->waits_recorded; ++i) {
+    float ms = 0.f;
+    HL_CUDA(cudaEventElapsedTime(&ms, m->wait_begin[i], m->wait_end[i]));
+    sum += ms;
+  }
+  *total_ms = sum;
+  if (waits) *waits = (int)m->waits_recorded;
+  m->waits_recorded = 0;
+  return HL_OK;
+}
 
 long long hl_ddp_bucket_count(long long arena_elems, long long bucket_elems) {
   if (arena_elems <= 0 || bucket_elems <= 0) return 0;

@@ -220,6 +220,24 @@ def build_cases(ctx):
     return cases
 
 
+def sweep(ctx, names=None, iters=20, warmup=3):
+    """Runs the named cases (all when None) and yields one result dict per case."""
+    hbm, tf, src = peaks()
+    for name, make in build_cases(ctx).items():
+        if names is not None and name not in names:
+            continue
+        fn, work, unit = make()
+        ms = timed(ctx, fn, iters, warmup)
+        if unit == "flop":
+            rate, peak, runit = work / ms / 1e9, tf, "TFLOP/s"
+        else:
+            rate, peak, runit = work / ms / 1e6, hbm, "GB/s"
+        yield {"case": name, "us": round(ms * 1e3, 2), "achieved": round(rate, 1), "unit": runit, "peak": peak,
+               "frac": round(rate / peak, 4), "peak_source": src}
+        del fn
+        torch.cuda.empty_cache()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--only", default="")
@@ -231,20 +249,9 @@ def main():
     SPLIT_K = args.split_k
     torch.manual_seed(0)
     ctx = cuda.Context(0)
-    hbm, tf, src = peaks()
-    for name, make in build_cases(ctx).items():
-        if args.only and args.only not in name:
-            continue
-        fn, work, unit = make()
-        ms = timed(ctx, fn, args.iters, args.warmup)
-        if unit == "flop":
-            rate, peak, runit = work / ms / 1e9, tf, "TFLOP/s"
-        else:
-            rate, peak, runit = work / ms / 1e6, hbm, "GB/s"
-        print(json.dumps({"case": name, "us": round(ms * 1e3, 2), "achieved": round(rate, 1), "unit": runit,
-                          "peak": peak, "frac": round(rate / peak, 4), "peak_source": src}), flush=True)
-        del fn
-        torch.cuda.empty_cache()
+    names = [n for n in build_cases(ctx) if not args.only or args.only in n]
+    for row in sweep(ctx, names, args.iters, args.warmup):
+        print(json.dumps(row), flush=True)
 
 
 if __name__ == "__main__":

@@ -67,32 +67,10 @@ def init_weights(model, seed: int) -> None:
     model.load_state_dict(state)
 
 
-def main() -> None:
-    ap = argparse.ArgumentParser()
-    ap.add_argument("--steps", type=int, default=10)
-    ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--policy", default="full", choices=["full", "memory_only", "sparse_rows", "dense_plus_sparse_values"])
-    ap.add_argument("--gpus", type=int, default=1)
-    args = ap.parse_args()
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    if world != args.gpus:
-        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torchrun --nproc-per-node {args.gpus}")
-    torch.cuda.set_device(local_rank)
-    ctx = cuda.Context(local_rank)
-    dist = None
-    if world > 1:
-        import torch.distributed as dist
-        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        dist.init_process_group("gloo", rank=rank, world_size=world)
-        ident = (ctypes.c_uint8 * 128)()
-        if rank == 0:
-            cuda.check(ctx.lib.hl_nccl_unique_id(ident))
-        obj = [bytes(ident)]
-        dist.broadcast_object_list(obj, src=0)
-        ident = (ctypes.c_uint8 * 128).from_buffer_copy(obj[0])
-        cuda.check(ctx.lib.hl_nccl_init(ctx.handle, rank, world, ident))
+def run(ctx, dist, world: int, rank: int, steps: int, warmup: int, policy: str):
+    """The memory-transformer step on a context whose communicator (if any) is already set up.  Every rank calls it;
+    returns the result line as a dict (the same on every rank up to the per-kernel profile, which is this rank's)."""
+    args = argparse.Namespace(steps=steps, warmup=warmup, policy=policy)
     model = nn.DecoderLm(ctx, nn.DecoderConfig(batch=BATCH, **CFG), nn.MemoryConfig(**MEM))
     init_weights(model, 0)  # the same initial weights on every rank
     model.set_optimizer(lr=1e-3, beta1=0.9, beta2=0.999, eps=1e-8, weight_decay=0.01, clip_norm=None)
@@ -142,29 +120,60 @@ def main() -> None:
     cuda.check(ctx.lib.hl_profile_read(ctx.handle, ctypes.byref(p)))
     cuda.check(ctx.lib.hl_profile_enable(ctx.handle, 0))
     barrier()
+    shapes = model.parameter_shapes()
     model.close()
-    if dist is not None:
-        cuda.check(ctx.lib.hl_nccl_destroy(ctx.handle))
-        dist.destroy_process_group()
-    if rank != 0:
-        return
     names = ["gemm", "attention_fwd", "attention_bwd", "layer_norm", "loss", "optimizer", "bias_grad", "embedding", "other"]
     tokens = BATCH * CFG["context"] * world
     value = tokens / (ms * 1e-3)
     peaks_path = ROOT / "MEASURED_PEAKS.json"
     burst = json.loads(peaks_path.read_text())["bf16_tflops"] if peaks_path.exists() else 1590.0
-    print(json.dumps({
+    memory_kernels = p.ms[8] / prof_steps  # the lookup, scoring, gather and table-gradient kernels carry no category of their own
+    return ({
         "metric": "train tokens/s (memory transformer bf16 step)", "value": value, "unit": "tokens/s", "n_gpus": world, "scaling": "weak",
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "policy": args.policy, "loss_after": loss,
         "config": {"workload": "memory transformer: vocab 32000, d 512, 8 layers, 8 heads, MLP 2048, context 512, batch 32, "
                                "product-key memory in blocks 4 and 6 (262,144 slots, value dim 512, top-k 32)",
-                   "tokens_per_step": tokens, "parameters": sum(int(np.prod(s)) for s in model.parameter_shapes().values())},
+                   "tokens_per_step": tokens, "parameters": sum(int(np.prod(s)) for s in shapes.values())},
         "mfu_dense_part": {"flops_per_token": flops_per_token(),
                            "vs_measured_burst": value * flops_per_token() / (burst * 1e12 * world),
                            "vs_datasheet_2250_tflops": value * flops_per_token() / (2250e12 * world)},
         "kernel_breakdown_ms_per_step": {n: round(p.ms[i] / prof_steps, 4) for i, n in enumerate(names)},
-        "data": "synthetic"}))
-    model.close()
+        "memory_kernel_share": memory_kernels / max(sum(p.ms[i] for i in range(len(names))) / prof_steps, 1e-9),
+        "data": "synthetic"})
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--policy", default="full", choices=["full", "memory_only", "sparse_rows", "dense_plus_sparse_values"])
+    ap.add_argument("--gpus", type=int, default=1)
+    args = ap.parse_args()
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torchrun --nproc-per-node {args.gpus}")
+    torch.cuda.set_device(local_rank)
+    ctx = cuda.Context(local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("gloo", rank=rank, world_size=world)
+        ident = (ctypes.c_uint8 * 128)()
+        if rank == 0:
+            cuda.check(ctx.lib.hl_nccl_unique_id(ident))
+        obj = [bytes(ident)]
+        dist.broadcast_object_list(obj, src=0)
+        ident = (ctypes.c_uint8 * 128).from_buffer_copy(obj[0])
+        cuda.check(ctx.lib.hl_nccl_init(ctx.handle, rank, world, ident))
+    line = run(ctx, dist, world, rank, args.steps, args.warmup, args.policy)
+    if dist is not None:
+        cuda.check(ctx.lib.hl_nccl_destroy(ctx.handle))
+        dist.destroy_process_group()
+    if rank == 0:
+        print(json.dumps(line))
 
 
 if __name__ == "__main__":

@@ -271,6 +271,13 @@ class DecoderLm:
         check(self._lib.hl_decoder_set_smft_masks(self.handle, value.ctypes.data_as(c_void_p), left.ctypes.data_as(c_void_p),
                                                   right.ctypes.data_as(c_void_p)))
 
+    def comm_exposed_ms(self):
+        """(milliseconds, waits): how long the compute stream sat idle waiting for gradient collectives since the
+        last call; measured only while the context's per-kernel timing is on."""
+        ms, waits = c_float(), c_int()
+        check(self._lib.hl_decoder_comm_exposed_ms(self.handle, byref(ms), byref(waits)))
+        return float(ms.value), int(waits.value)
+
     @property
     def launches_last_step(self) -> int:
         return int(self._lib.hl_decoder_launches_last_step(self.handle))

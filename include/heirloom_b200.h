@@ -527,6 +527,11 @@ int hl_decoder_train_step(hl_decoder* model, const int64_t* tokens_host, const i
 int hl_decoder_loss(hl_decoder* model, float* loss_host);
 /* Kernels launched by the last forward_backward + optimizer_step. */
 unsigned long long hl_decoder_launches_last_step(hl_decoder* model);
+/* Data parallelism: how long the compute stream sat idle in its waits for the collective stream since the last call
+ * (sum over the waits, and their number), measured with timing events while hl_profile_enable is on; 0 otherwise.
+ * Synchronises the compute stream.  The reference times its exchange the same way, as the all-reduce's own event
+ * timer (NcclCommunicator::start_event_timer, heirloom-kernels/src/cuda.rs:8049-8233). */
+int hl_decoder_comm_exposed_ms(hl_decoder* model, float* total_ms, int* waits);
 
 #ifdef __cplusplus
 }
