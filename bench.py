@@ -345,16 +345,18 @@ def run_ours(args):
     model.close()
 
     # ---- the memory-transformer configuration at the same number of GPUs (its own JSON object in the line) --------
-    from heirloom_b200 import memory_bench
-    memory_line = memory_bench.run(ctx, dist if world > 1 else None, world, rank, steps=min(args.steps, 10), warmup=3,
-                                   policy="full")
+    memory_line = None
+    if not args.no_memory_step:
+        from heirloom_b200 import memory_bench
+        memory_line = memory_bench.run(ctx, dist if world > 1 else None, world, rank, steps=min(args.steps, 10), warmup=3,
+                                       policy="full")
     if world > 1:
         cuda.check(ctx.lib.hl_nccl_destroy(ctx.handle))
         dist.destroy_process_group()
 
     if rank != 0:
         return
-    memory_step = {"ms_per_step": memory_line["ms_per_step"], "tokens_per_s": memory_line["value"], "policy": "full",
+    memory_step = None if memory_line is None else {"ms_per_step": memory_line["ms_per_step"], "tokens_per_s": memory_line["value"], "policy": "full",
                    "n_gpus": world, "memory_kernel_share": memory_line["memory_kernel_share"],
                    "loss_after": memory_line["loss_after"], "config": memory_line["config"]["workload"],
                    "kernel_breakdown_ms_per_step": memory_line["kernel_breakdown_ms_per_step"]}
@@ -416,6 +418,7 @@ if __name__ == "__main__":
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-kernel-sweep", action="store_true")
+    ap.add_argument("--no-memory-step", action="store_true")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

@@ -556,7 +556,7 @@ int flash_attention_backward_impl(hl_ctx* ctx, const void* q, const void* k, con
     const uint32_t box[3] = {32, (uint32_t)FB_BM, 1};
     if ((rc = make_tensor_map(&mdq, HL_F32, 3, dq_accum, dims, strides, box, 128)) != HL_OK) return rc;
   }
-  flash_attention_bwd_kernel<<<std::min(nq * batch * n_heads, ctx->sm_count), FB_THREADS, FB_SMEM_BYTES, ctx->stream>>>(mq, mk, mv, mdo, mdq, p);
+  flash_attention_bwd_kernel<<<std::min(nq * batch * n_heads, persistent_sms(ctx)), FB_THREADS, FB_SMEM_BYTES, ctx->stream>>>(mq, mk, mv, mdo, mdq, p);
   HL_LAUNCH_CHECK("flash_attention_bwd_kernel");
   {
     const long long quads = (long long)rows * (C / 4);

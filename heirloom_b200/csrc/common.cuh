@@ -7,6 +7,7 @@
 #include <stdint.h>
 #include <stddef.h>
 #include <string>
+#include <algorithm>
 #include "../../include/heirloom_b200.h"
 
 namespace hl {
@@ -54,6 +55,8 @@ struct Counters {
 struct hl_ctx {
   int device = 0;
   int sm_count = 0;
+  int reserve_sms = 0;                 // SMs the persistent kernels leave free while gradient collectives are in flight
+  int comm_sms = 0;                    // how many they leave when asked to (0 = none); set when the communicator is made
   cudaStream_t stream = nullptr;       // compute stream
   cudaStream_t comm_stream = nullptr;  // collective stream
   int* status_dev = nullptr;           // hl::ST_SLOTS ints
@@ -69,6 +72,10 @@ struct hl_ctx {
 namespace hl {
 int ensure_workspace(hl_ctx* ctx, size_t bytes);
 inline void count_launch(hl_ctx* ctx, unsigned long long n = 1) { ctx->counters.launches += n; }
+// SMs a persistent one-CTA-per-SM kernel should fill: all of them, minus those left to the collective kernels.  A CTA of
+// those kernels takes a whole SM's registers or shared memory, so it cannot start on an SM a collective kernel sits
+// on, and a grid of one CTA per SM would wait for that SM with its share of the tiles.
+inline int persistent_sms(const hl_ctx* ctx) { return std::max(1, ctx->sm_count - ctx->reserve_sms); }
 
 // Opt-in per-kernel timing: a scope brackets the launches of one op with two events on the
 // compute stream; hl_profile_read folds them by category after a stream sync (the reference's

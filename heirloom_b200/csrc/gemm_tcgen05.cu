@@ -610,7 +610,8 @@ int gemm_bf16_run(hl_ctx* ctx, const hl_gemm_desc* d, const void* a, const void*
   // a larger one is walked in panels of up to eight tile columns so that it streams from DRAM once.
   p.a_kb_wrap = d->a_k_period > 0 ? d->a_k_period / BK : 0;
   p.panel_w = (size_t)d->m * (size_t)d->k * 2 <= (size_t(32) << 20) ? 1 : std::min(p.n_tiles, 8);
-  const GemmPlan plan = gemm_plan(d, ctx->sm_count);
+  const int sms = persistent_sms(ctx);
+  const GemmPlan plan = gemm_plan(d, sms);
   const int splits = plan.splits;
   const size_t need = plan.splitk_bytes;
   p.splits = splits;
@@ -671,7 +672,7 @@ int gemm_bf16_run(hl_ctx* ctx, const hl_gemm_desc* d, const void* a, const void*
   }
 
   const int total = p.m_tiles * p.n_tiles * p.splits;
-  const int grid = plan.sk_tiles > 0 ? ctx->sm_count : min(total, ctx->sm_count);
+  const int grid = plan.sk_tiles > 0 ? sms : min(total, sms);
   ProfileScope prof(ctx, HL_PROF_GEMM, 2.0 * (double)d->m * (double)d->n * (double)d->k);
   if (a_mn && b_mn) rc = launch_variant<true, true>(ctx, ma, mb, mc, maux, p, grid);
   else if (a_mn)    rc = launch_variant<true, false>(ctx, ma, mb, mc, maux, p, grid);
@@ -696,7 +697,7 @@ int gemm_bf16_ctx(hl_ctx* ctx, const hl_gemm_desc* desc, const void* a, const vo
                   const void* aux_in, void* aux_out) {
   if (!ctx || !desc) return fail("hl_gemm_bf16: null argument");
   if (desc->m <= 0 || desc->n <= 0 || desc->k <= 0) return fail("hl_gemm_bf16: m, n, k must be positive");
-  const GemmPlan plan = gemm_plan(desc, ctx->sm_count);
+  const GemmPlan plan = gemm_plan(desc, persistent_sms(ctx));
   const size_t need = std::max(plan.splitk_bytes, plan.sk_slot_bytes);
   if (need > ctx->workspace_bytes) {
     int rc = ensure_workspace(ctx, need);

@@ -6,6 +6,8 @@
 
 #include <cstdlib>
 #include <cstring>
+#include <string>
+#include <algorithm>
 
 #include "kernels.h"
 
@@ -127,6 +129,16 @@ int hl_nccl_init(hl_ctx* ctx, int rank, int world, const unsigned char id_bytes[
   NcclState* st = new NcclState();
   st->rank = rank;
   st->world = world;
+  // The collective kernels get a bounded number of SMs and the persistent GEMM / attention kernels leave exactly those
+  // free while collectives are in flight (HEIRLOOM_COMM_SMS, default 8, 0 = no reservation and NCCL's own choice).
+  // NCCL reads its bound from the environment when the communicator is made; a value the user set is kept.
+  int comm_sms = 8;
+  if (const char* e = getenv("HEIRLOOM_COMM_SMS")) comm_sms = std::max(0, std::min(atoi(e), ctx->sm_count / 2));
+  if (world > 1 && comm_sms > 0) {
+    const std::string v = std::to_string(comm_sms);
+    setenv("NCCL_MAX_CTAS", v.c_str(), 0);
+    ctx->comm_sms = comm_sms;
+  }
   int rc = a->CommInitRank(&st->comm, world, id, rank);
   if (rc != 0) { delete st; return fail_nccl(rc, "ncclCommInitRank"); }
   ctx->nccl = st;
@@ -154,6 +166,7 @@ int hl_nccl_abort(hl_ctx* ctx) {
   if (st->comm) api()->CommAbort(st->comm);
   delete st;
   ctx->nccl = nullptr;
+  ctx->comm_sms = ctx->reserve_sms = 0;
   return HL_OK;
 }
 
@@ -164,6 +177,7 @@ int hl_nccl_destroy(hl_ctx* ctx) {
   if (st->comm) api()->CommDestroy(st->comm);
   delete st;
   ctx->nccl = nullptr;
+  ctx->comm_sms = ctx->reserve_sms = 0;
   return HL_OK;
 }
 

@@ -124,6 +124,14 @@ struct hl_decoder {
   bool smft_on = false;  // the sparse-rows step filters its rows through the three masks
   float* m_packed = nullptr;         // gradient rows of the union, packed for the all-reduce (own allocation)
   size_t packed_rows_cap = 0;        // rows it holds
+  // data-parallel exchange of the token-embedding gradient as the union of the rows any rank's batch touched
+  bool sparse_tok_exchange = true;
+  unsigned char* tok_flags = nullptr;  // [vocab]
+  int64_t* tok_union_rows = nullptr;   // [vocab]
+  int* tok_union_count = nullptr;
+  int* tok_union_count_host = nullptr;  // pinned
+  float* tok_packed = nullptr;
+  size_t tok_packed_cap = 0;
   int64_t* m_union_rows = nullptr;   // rows of the value table selected by any rank this step
   int* m_union_count = nullptr;      // device count of them
   int* m_union_count_host = nullptr; // pinned mirror
@@ -251,6 +259,9 @@ T* carve(uint8_t*& cursor, size_t count) {
 
 // Buffers of the memory feed-forward blocks; appended to either route's arena.
 void plan_memory_buffers(hl_decoder* m, uint8_t*& cur) {
+  m->tok_flags = carve<unsigned char>(cur, (size_t)m->cfg.vocab);
+  m->tok_union_rows = carve<int64_t>(cur, (size_t)m->cfg.vocab);
+  m->tok_union_count = carve<int>(cur, 4);
   if (!m->has_memory) return;
   const size_t N = (size_t)m->N, kd = m->mem.key_dim, vd = m->mem.value_dim, k = m->mem.top_k, d = m->cfg.d_model;
   m->ma.assign(m->cfg.n_layers, MemoryActs{});
@@ -538,6 +549,7 @@ int forward(hl_decoder* m) {
   const Gemm g{m};
   const float* P = m->params;
   const __nv_bfloat16* W = m->shadow;
+  if (!m->comm_pending) ctx->reserve_sms = 0;  // nothing of the gradient exchange is in flight during a forward pass
   HL_TRY(hl_embedding_forward(ctx, P + m->off_tok, V, m->tokens, P + m->off_pos, T, m->x[0], HL_BF16, N, d));
   for (int l = 0; l < c.n_layers; ++l) {
     const LayerOffsets& o = m->lo[l];
@@ -601,65 +613,104 @@ int flush_buckets(hl_decoder* m, size_t done_elems) {
     if (end > done_elems) break;
     HL_CUDA(cudaEventRecord(m->bucket_ready[m->next_bucket], m->ctx->stream));
     HL_CUDA(cudaStreamWaitEvent(m->ctx->comm_stream, m->bucket_ready[m->next_bucket], 0));
-    if (m->has_memory) {
-      // the value table travels as the union of selected rows (exchange_value_rows), not densely
-      const size_t val_lo = m->off_val, val_hi = m->off_val + (size_t)m->mem.slots * m->mem.value_dim;
-      const size_t a_end = std::min(end, val_lo), b_start = std::max(start, val_hi);
-      if (start < a_end) HL_TRY(nccl_allreduce_sum_f32(m->ctx, m->grads + start, a_end - start, m->ctx->comm_stream));
-      if (b_start < end) HL_TRY(nccl_allreduce_sum_f32(m->ctx, m->grads + b_start, end - b_start, m->ctx->comm_stream));
-    } else {
-      HL_TRY(nccl_allreduce_sum_f32(m->ctx, m->grads + start, end - start, m->ctx->comm_stream));
+    // The value table and the token-embedding table travel as the union of the rows that carry a gradient
+    // (exchange_rows), not densely: their ranges are cut out of the bucket (value table first, token table last).
+    size_t cut_lo[2], cut_hi[2];
+    int cuts = 0;
+    if (m->has_memory) { cut_lo[cuts] = m->off_val; cut_hi[cuts] = m->off_val + (size_t)m->mem.slots * m->mem.value_dim; ++cuts; }
+    if (m->sparse_tok_exchange) { cut_lo[cuts] = m->off_tok; cut_hi[cuts] = m->off_tok + (size_t)m->cfg.vocab * m->cfg.d_model; ++cuts; }
+    size_t at = start;
+    for (int c = 0; c <= cuts && at < end; ++c) {
+      const size_t stop = c < cuts ? std::min(end, std::max(at, cut_lo[c])) : end;
+      if (at < stop) HL_TRY(nccl_allreduce_sum_f32(m->ctx, m->grads + at, stop - at, m->ctx->comm_stream));
+      at = c < cuts ? std::max(stop, std::min(end, cut_hi[c])) : end;
     }
     HL_CUDA(cudaEventRecord(m->bucket_done[m->next_bucket], m->ctx->comm_stream));
     m->next_bucket += 1;
+    m->ctx->reserve_sms = m->ctx->comm_sms;  // collectives are in flight from here to the optimizer's last wait
   }
   return HL_OK;
 }
 
-// Data-parallel exchange of the value-table gradient: every rank marks the rows its memory blocks selected, the
-// masks are combined with a byte-wise maximum, the union's gradient rows are packed, summed over the ranks and
-// put back (src/bin/heirloom/runtime.rs:4171-4214).  Rows outside the union have zero gradient on every rank.
-// Runs on the collective stream after the dense buckets; the host waits once for the row count.
+// Data-parallel exchange of a table gradient of which only some rows are non-zero: every rank marks the rows it
+// touched, the masks are combined with a byte-wise maximum, the union's gradient rows are packed, summed over the
+// ranks and put back (src/bin/heirloom/runtime.rs:4171-4214).  Rows outside the union have zero gradient on every
+// rank.  Runs on the collective stream after the dense buckets; the host waits once for the row count.
+struct RowExchange {
+  float* grad;            // [rows, dim] in the gradient arena
+  int rows, dim;
+  unsigned char* flags;   // [rows], zero on entry and on return
+  int64_t* union_rows;    // [rows]
+  int* count_dev;
+  int* count_host;        // pinned
+  float** packed;         // own allocation, grown on demand
+  size_t* packed_cap;     // rows it holds
+  size_t max_events;      // rows all ranks together can touch at most
+};
+
+int exchange_rows(hl_decoder* m, const RowExchange& x, int* union_n) {
+  hl_ctx* ctx = m->ctx;
+  cudaStream_t cs = ctx->comm_stream;
+  HL_TRY(nccl_allreduce_max_u8(ctx, x.flags, (size_t)x.rows, cs));
+  HL_TRY(mask_to_indices_on(ctx, cs, x.flags, x.rows, x.union_rows, x.count_dev));
+  HL_CUDA(cudaMemcpyAsync(x.count_host, x.count_dev, sizeof(int), cudaMemcpyDeviceToHost, cs));
+  HL_CUDA(cudaStreamSynchronize(cs));
+  const int n = *x.count_host;
+  HL_REQUIRE(n >= 0 && n <= x.rows, "hl_decoder: row union out of range");
+  *union_n = n;
+  if (n > 0) {
+    // The packed rows live in a buffer of their own: the context's scratch arena belongs to the compute stream,
+    // which keeps running (and may regrow the arena) while this exchange is in flight on the collective stream.
+    if ((size_t)n > *x.packed_cap) {
+      const size_t cap = std::max((size_t)n, std::min((size_t)x.rows, x.max_events));
+      if (*x.packed) {
+        HL_CUDA(cudaFree(*x.packed));  // the stream was synchronised just above
+        *x.packed = nullptr;
+        *x.packed_cap = 0;
+      }
+      HL_CUDA(cudaMalloc(reinterpret_cast<void**>(x.packed), sizeof(float) * cap * x.dim));
+      *x.packed_cap = cap;
+      ctx->counters.allocations += 1;
+      ctx->counters.allocated_bytes += sizeof(float) * cap * x.dim;
+    }
+    HL_TRY(move_rows_on(ctx, cs, x.grad, x.union_rows, nullptr, n, x.dim, *x.packed, false));
+    HL_TRY(nccl_allreduce_sum_f32(ctx, *x.packed, (size_t)n * x.dim, cs));
+    HL_TRY(move_rows_on(ctx, cs, *x.packed, x.union_rows, nullptr, n, x.dim, x.grad, true));
+  }
+  HL_CUDA(cudaMemsetAsync(x.flags, 0, (size_t)x.rows, cs));
+  return HL_OK;
+}
+
+// The value table: rows = the slots the memory blocks selected.
 int exchange_value_rows(hl_decoder* m) {
   if (!m->has_memory || !nccl_active(m->ctx)) return HL_OK;
   hl_ctx* ctx = m->ctx;
   cudaStream_t cs = ctx->comm_stream;
   const size_t per_layer = (size_t)m->N * m->mem.top_k;
-  const int slots = m->mem.slots, vd = m->mem.value_dim;
+  const int slots = m->mem.slots;
   HL_CUDA(cudaMemsetAsync(m->m_row_flags, 0, (size_t)slots, cs));
   for (int l = 0; l < m->cfg.n_layers; ++l)
     if (m->lo[l].is_memory) HL_TRY(mark_rows_on(ctx, cs, m->ma[l].idx, (long long)per_layer, nullptr, m->m_row_flags, slots));
-  HL_TRY(nccl_allreduce_max_u8(ctx, m->m_row_flags, (size_t)slots, cs));
-  HL_TRY(mask_to_indices_on(ctx, cs, m->m_row_flags, slots, m->m_union_rows, m->m_union_count));
-  HL_CUDA(cudaMemcpyAsync(m->m_union_count_host, m->m_union_count, sizeof(int), cudaMemcpyDeviceToHost, cs));
-  HL_CUDA(cudaStreamSynchronize(cs));
-  const int n = *m->m_union_count_host;
-  HL_REQUIRE(n >= 0 && n <= slots, "hl_decoder: selected-row union out of range");
-  m->union_n = n;
-  if (n > 0) {
-    // The packed rows live in a buffer of their own: the context's scratch arena belongs to the compute stream,
-    // which keeps running (and may regrow the arena) while this exchange is in flight on the collective stream.
-    if ((size_t)n > m->packed_rows_cap) {
-      const size_t events = (size_t)nccl_world(ctx) * per_layer * (size_t)m->mem.n_memory_layers;
-      const size_t cap = std::max((size_t)n, std::min((size_t)slots, events));
-      if (m->m_packed) {
-        HL_CUDA(cudaStreamSynchronize(cs));
-        HL_CUDA(cudaFree(m->m_packed));
-        m->m_packed = nullptr;
-        m->packed_rows_cap = 0;
-      }
-      HL_CUDA(cudaMalloc(reinterpret_cast<void**>(&m->m_packed), sizeof(float) * cap * vd));
-      m->packed_rows_cap = cap;
-      ctx->counters.allocations += 1;
-      ctx->counters.allocated_bytes += sizeof(float) * cap * vd;
-    }
-    float* packed = m->m_packed;
-    HL_TRY(move_rows_on(ctx, cs, m->grads + m->off_val, m->m_union_rows, nullptr, n, vd, packed, false));
-    HL_TRY(nccl_allreduce_sum_f32(ctx, packed, (size_t)n * vd, cs));
-    HL_TRY(move_rows_on(ctx, cs, packed, m->m_union_rows, nullptr, n, vd, m->grads + m->off_val, true));
-  }
-  HL_CUDA(cudaMemsetAsync(m->m_row_flags, 0, (size_t)slots, cs));
-  return HL_OK;
+  const RowExchange x{m->grads + m->off_val, slots, m->mem.value_dim, m->m_row_flags, m->m_union_rows, m->m_union_count,
+                      m->m_union_count_host, &m->m_packed, &m->packed_rows_cap,
+                      (size_t)nccl_world(ctx) * per_layer * (size_t)m->mem.n_memory_layers};
+  return exchange_rows(m, x, &m->union_n);
+}
+
+// The token-embedding table: rows = the token ids of the batch.  At a Zipf-distributed batch of 16 Ki tokens over a
+// vocabulary of 50 Ki this is a small share of the 154 MB table, and it is the gradient that becomes final last in
+// backward, i.e. the exchange nothing is left to hide behind.
+int exchange_token_rows(hl_decoder* m) {
+  if (!m->sparse_tok_exchange || !nccl_active(m->ctx)) return HL_OK;
+  hl_ctx* ctx = m->ctx;
+  cudaStream_t cs = ctx->comm_stream;
+  const int V = m->cfg.vocab;
+  HL_CUDA(cudaMemsetAsync(m->tok_flags, 0, (size_t)V, cs));
+  HL_TRY(mark_rows_on(ctx, cs, m->tokens, (long long)m->N, nullptr, m->tok_flags, V));
+  const RowExchange x{m->grads + m->off_tok, V, m->cfg.d_model, m->tok_flags, m->tok_union_rows, m->tok_union_count,
+                      m->tok_union_count_host, &m->tok_packed, &m->tok_packed_cap, (size_t)nccl_world(ctx) * (size_t)m->N};
+  int n = 0;
+  return exchange_rows(m, x, &n);
 }
 
 int backward(hl_decoder* m) {
@@ -754,10 +805,11 @@ int backward(hl_decoder* m) {
   HL_TRY(hl_embedding_backward(ctx, dx, m->tokens, G + m->off_tok, V, G + m->off_pos, T, N, d));
   HL_TRY(flush_buckets(m, m->arena));
   if (nccl_active(ctx)) {
-    if (m->has_memory) {
-      // the row exchange reads gradients the compute stream is still producing
+    if (m->has_memory || m->sparse_tok_exchange) {
+      // the row exchanges read gradients the compute stream is still producing
       HL_CUDA(cudaEventRecord(m->comm_done, ctx->stream));
       HL_CUDA(cudaStreamWaitEvent(ctx->comm_stream, m->comm_done, 0));
+      HL_TRY(exchange_token_rows(m));
       HL_TRY(exchange_value_rows(m));
     }
     // The compute stream waits for the collectives only when something reads the averaged gradients:
@@ -891,10 +943,11 @@ int backward_f32(hl_decoder* m) {
   HL_TRY(hl_embedding_backward(ctx, dx, m->tokens, G + m->off_tok, V, G + m->off_pos, T, N, d));
   HL_TRY(flush_buckets(m, m->arena));
   if (nccl_active(ctx)) {
-    if (m->has_memory) {
-      // the row exchange reads gradients the compute stream is still producing
+    if (m->has_memory || m->sparse_tok_exchange) {
+      // the row exchanges read gradients the compute stream is still producing
       HL_CUDA(cudaEventRecord(m->comm_done, ctx->stream));
       HL_CUDA(cudaStreamWaitEvent(ctx->comm_stream, m->comm_done, 0));
+      HL_TRY(exchange_token_rows(m));
       HL_TRY(exchange_value_rows(m));
     }
     // The compute stream waits for the collectives only when something reads the averaged gradients:
@@ -935,6 +988,7 @@ int wait_for_collectives(hl_decoder* m) {
     HL_TRY(wait_on_collective(m, m->comm_done));
     m->comm_pending = false;
   }
+  m->ctx->reserve_sms = 0;
   return HL_OK;
 }
 
@@ -976,15 +1030,17 @@ int optimizer_step(hl_decoder* m) {
     // chunks that lie completely inside the buckets reduced so far (a chunk that straddles the boundary waits
     // for the next group; the last group takes everything that is left)
     const int upto = b1 == m->n_buckets ? chunks_total : (int)(end / chunk);
-    // The value table's gradient is not final when its buckets are: its rows are summed over the ranks by the row
-    // exchange that follows the last bucket on the collective stream.  A group that reaches into the table waits for
-    // the end of that stream's work (which covers every bucket as well).
-    const bool reaches_values = m->has_memory && (b1 == m->n_buckets || (size_t)upto * chunk > m->off_val);
+    // The gradients of the value table and of the token-embedding table are not final when their buckets are: their
+    // rows are summed over the ranks by the row exchanges that follow the last bucket on the collective stream.  A
+    // group that reaches into such a table waits for the end of that stream's work (which covers every bucket too).
+    const size_t range_end = b1 == m->n_buckets ? m->arena : (size_t)upto * chunk;
+    const bool reaches_values = (m->has_memory && range_end > m->off_val) || (m->sparse_tok_exchange && range_end > m->off_tok);
     HL_TRY(wait_on_collective(m, reaches_values ? m->comm_done : m->bucket_done[b1 - 1]));
     HL_TRY(adam_plan_step_range(ctx, m->plan, &hp, first, upto - first));
     first = upto;
   }
   m->comm_pending = false;
+  ctx->reserve_sms = 0;
   return HL_OK;
 }
 
@@ -1090,6 +1146,8 @@ static int decoder_create_impl(hl_ctx* ctx, const hl_decoder_config* cfg, const 
   if (e != cudaSuccess) return cleanup(fail_cuda(e, "cudaMallocHost"));
   m->norm_host = m->loss_host + 8;
   m->m_union_count_host = reinterpret_cast<int*>(m->loss_host + 12);
+  m->tok_union_count_host = reinterpret_cast<int*>(m->loss_host + 13);
+  if (const char* e = getenv("HEIRLOOM_SPARSE_EMBEDDING_EXCHANGE")) m->sparse_tok_exchange = atoi(e) != 0;
   hl_adamw_tensor whole{m->params, m->grads, m->m, m->v, m->shadow, (uint64_t)m->arena};
   int rc = adam_plan_create(ctx, &whole, 1, &m->plan);
   if (rc != HL_OK) return cleanup(rc);
@@ -1141,6 +1199,7 @@ void hl_decoder_destroy(hl_decoder* m) {
   adam_plan_destroy(m->plan_tables);
   adam_plan_destroy(m->plan_no_values);
   if (m->m_packed) cudaFree(m->m_packed);
+  if (m->tok_packed) cudaFree(m->tok_packed);
   cudaFree(m->params); cudaFree(m->grads); cudaFree(m->m); cudaFree(m->v); cudaFree(m->shadow); cudaFree(m->act_arena);
   if (m->loss_host) cudaFreeHost(m->loss_host);
   delete m;
