@@ -55,6 +55,8 @@ struct Counters {
 struct hl_ctx {
   int device = 0;
   int sm_count = 0;
+  unsigned long long wait_limit_ns = 0;  // bound of the pipeline waits in the GEMM kernel (0 = the two-second default)
+  int gemm_skip_kblock = -1;           // test hook of hl_ctx_set_test_hooks
   int reserve_sms = 0;                 // SMs the persistent kernels leave free while gradient collectives are in flight
   int comm_sms = 0;                    // how many they leave when asked to (0 = none); set when the communicator is made
   cudaStream_t stream = nullptr;       // compute stream

@@ -55,6 +55,8 @@ struct GemmParams {
   int dp_tiles, sk_tiles;   // whole-wave tiles, then tiles whose k blocks are dealt out evenly
   int panel_w;              // tile columns per panel of the tile order
   int a_kb_wrap;            // > 0: A holds this many k blocks and is read again from its start after them
+  unsigned long long wait_limit_ns;  // bound of every pipeline wait
+  int skip_kblock;          // test hook: the producer leaves out this k block of its first tile (-1: none)
   float* sk_slots;          // [grid][BM][BN] raw accumulators of unfinished tile parts
   unsigned* sk_flags;       // [grid][EPI_WARPS]: launch number once the warp's part of the slot is written
   unsigned sk_seq;          // this launch's number
@@ -198,7 +200,11 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
       for (int local = 0; ok && get_item(p, local, w); ++local) {
         const int m_tile = w.m_tile, n_tile = w.n_tile;
         for (int kb = w.kb0; kb < w.kb1; ++kb) {
-          if (!tc05::mbar_wait(&tail->empty[stage], phase ^ 1u, abort_flag)) { ok = false; break; }
+          if (!tc05::mbar_wait(&tail->empty[stage], phase ^ 1u, abort_flag, p.wait_limit_ns)) { ok = false; break; }
+          if (local == 0 && kb == p.skip_kblock) {  // test hook: this stage is never filled, the MMA issuer's wait runs out
+            if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+            continue;
+          }
           uint8_t* sa = smem + size_t(stage) * STAGE_BYTES;
           uint8_t* sb = sa + A_STAGE_BYTES;
           tc05::mbar_arrive_expect_tx(&tail->full[stage], STAGE_BYTES);
@@ -233,11 +239,11 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
         const int kb0 = w.kb0, kb1 = w.kb1;
         const int buf = local & 1;
         const uint32_t buf_phase = (uint32_t)(local >> 1) & 1u;
-        if (!tc05::mbar_wait(&tail->tmem_empty[buf], buf_phase ^ 1u, abort_flag)) { ok = false; break; }
+        if (!tc05::mbar_wait(&tail->tmem_empty[buf], buf_phase ^ 1u, abort_flag, p.wait_limit_ns)) { ok = false; break; }
         tc05::tc_fence_after_sync();
         const uint32_t tmem_d = tmem_base + (uint32_t)(buf * BN);
         for (int kb = kb0; kb < kb1; ++kb) {
-          if (!tc05::mbar_wait(&tail->full[stage], phase, abort_flag)) { ok = false; break; }
+          if (!tc05::mbar_wait(&tail->full[stage], phase, abort_flag, p.wait_limit_ns)) { ok = false; break; }
           tc05::tc_fence_after_sync();
           const uint32_t sa = tc05::smem_u32(smem + size_t(stage) * STAGE_BYTES);
           const uint32_t sb = sa + A_STAGE_BYTES;
@@ -295,7 +301,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
       };
       uint4 aux_a[4], aux_b[4];
       fetch_aux(0, aux_a);
-      if (!tc05::mbar_wait(&tail->tmem_full[buf], buf_phase, abort_flag)) { ok = false; break; }
+      if (!tc05::mbar_wait(&tail->tmem_full[buf], buf_phase, abort_flag, p.wait_limit_ns)) { ok = false; break; }
       tc05::tc_fence_after_sync();
       const uint32_t taddr_row = tmem_base + (uint32_t)(buf * BN) + ((uint32_t)(lane_group * 32) << 16);
       if (w.kind == ITEM_PART) {
@@ -339,7 +345,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
               asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(flag) : "memory");
               if (seen == p.sk_seq) break;
               if ((spins & 63u) == 63u) {
-                if (*abort_flag || tc05::global_timer_ns() - t0 > tc05::kWaitLimitNs) { *abort_flag = 1; ok = false; break; }
+                if (*abort_flag || tc05::global_timer_ns() - t0 > p.wait_limit_ns) { *abort_flag = 1; ok = false; break; }
                 __nanosleep(64);
               }
             }
@@ -609,6 +615,8 @@ int gemm_bf16_run(hl_ctx* ctx, const hl_gemm_desc* d, const void* a, const void*
   // An A operand that stays in L2 anyway keeps the plain order (one tile column after the other);
   // a larger one is walked in panels of up to eight tile columns so that it streams from DRAM once.
   p.a_kb_wrap = d->a_k_period > 0 ? d->a_k_period / BK : 0;
+  p.wait_limit_ns = ctx->wait_limit_ns ? ctx->wait_limit_ns : tc05::kWaitLimitNs;
+  p.skip_kblock = ctx->gemm_skip_kblock;
   p.panel_w = (size_t)d->m * (size_t)d->k * 2 <= (size_t(32) << 20) ? 1 : std::min(p.n_tiles, 8);
   const int sms = persistent_sms(ctx);
   const GemmPlan plan = gemm_plan(d, sms);

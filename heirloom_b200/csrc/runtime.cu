@@ -214,6 +214,13 @@ void hl_ctx_destroy(hl_ctx* ctx) {
   delete ctx;
 }
 
+int hl_ctx_set_test_hooks(hl_ctx* ctx, unsigned long long wait_limit_ns, int gemm_skip_kblock) {
+  HL_REQUIRE(ctx, "hl_ctx_set_test_hooks: null context");
+  ctx->wait_limit_ns = wait_limit_ns;
+  ctx->gemm_skip_kblock = gemm_skip_kblock;
+  return HL_OK;
+}
+
 int hl_ctx_sync(hl_ctx* ctx) {
   if (!ctx) return hl::fail("hl_ctx_sync: null context");
   HL_CUDA(cudaMemcpyAsync(ctx->status_host, ctx->status_dev, sizeof(int) * hl::ST_SLOTS, cudaMemcpyDeviceToHost,

@@ -53,14 +53,15 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 }
 // Bounded wait.  Returns false (and raises *abort_flag) when the time budget runs out or
 // when another role already aborted.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                          unsigned long long limit_ns = kWaitLimitNs) {
   if (mbar_try_wait(bar, parity)) return true;
   const unsigned long long t0 = global_timer_ns();
   for (uint32_t i = 1;; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((i & 127u) == 0u) {
       if (*abort_flag) return false;
-      if (global_timer_ns() - t0 > kWaitLimitNs) break;
+      if (global_timer_ns() - t0 > limit_ns) break;
     }
   }
   *abort_flag = 1;

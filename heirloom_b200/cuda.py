@@ -84,6 +84,11 @@ class Context:
         check(self.lib.hl_counters_get(self.handle, byref(c)))
         return c
 
+    def set_test_hooks(self, wait_limit_ns: int = 0, gemm_skip_kblock: int = -1) -> None:
+        """`hl_ctx_set_test_hooks`: shorten the bound of the GEMM's pipeline waits and/or make its producer leave
+        out one k block, so that the failure path (status word, clean return) can be exercised."""
+        check(self.lib.hl_ctx_set_test_hooks(self.handle, ctypes.c_ulonglong(wait_limit_ns), c_int(gemm_skip_kblock)))
+
     def reset_counters(self) -> None:
         check(self.lib.hl_counters_reset(self.handle))
 

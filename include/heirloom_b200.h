@@ -41,6 +41,13 @@ int hl_ctx_create(int device_ordinal, hl_ctx** out);
 void hl_ctx_destroy(hl_ctx* ctx);
 /* Waits for the compute stream, then reports any device status word as an error. */
 int hl_ctx_sync(hl_ctx* ctx);
+/* Test hooks of the failure path.  Every wait inside the tcgen05 kernels is bounded (two seconds by default): when a
+ * wait runs out the kernel leaves its loops, frees its tensor memory, returns, and sets a status word that the next
+ * hl_ctx_sync reports as HL_ERR_DEVICE; the context stays usable.  `wait_limit_ns` shortens the bound for hl_gemm_bf16
+ * (0 = default) and `gemm_skip_kblock` >= 0 makes the GEMM's TMA producer leave out that k block of its first tile,
+ * so that the wait for it runs out; -1 switches the hook off.  The reference has no such path: its kernels have no
+ * device-side waits (single-role kernels, heirloom-kernels/src/ptx/tensor_core.ptx). */
+int hl_ctx_set_test_hooks(hl_ctx* ctx, unsigned long long wait_limit_ns, int gemm_skip_kblock);
 /* The compute stream as a cudaStream_t, for callers that time with their own events. */
 void* hl_ctx_stream(hl_ctx* ctx);
 const char* hl_last_error(void);

@@ -141,3 +141,27 @@ def test_gemm_with_a_repeated_operand_reaches_f32_accuracy(m, n, k):
     out = cuda.gemm_bf16(c, a2, wb, m, n, 3 * k, out_dtype=torch.float32, a_k_period=2 * k)
     want = a.astype(np.float64) @ w.astype(np.float64).T
     assert np.abs(host(out) - want).max() <= 6e-5 * np.abs(want).max()
+
+
+def test_an_expired_pipeline_wait_ends_the_kernel_with_a_status_and_leaves_the_context_usable():
+    """Failure detection without a fault: the producer is told to leave one k block of the first tile out, so the MMA
+    issuer's wait for that stage can never be satisfied; with the bound set to 200 microseconds the wait gives up, every
+    role leaves its loop, the kernel frees its tensor memory and returns, and the next sync reports the status word.
+    Nothing traps and nothing spins: the next GEMM on the same context is correct."""
+    from heirloom_b200 import cuda
+    from heirloom_b200._lib import HeirloomError
+    c = ctx()
+    rng = np.random.default_rng(51)
+    m, n, k = 128, 256, 256
+    a, b, da, db = operands(rng, m, n, k, False, False)
+    c.sync()
+    c.set_test_hooks(wait_limit_ns=200_000, gemm_skip_kblock=1)
+    try:
+        cuda.gemm_bf16(c, da, db, m, n, k, out_dtype=torch.float32)
+        with pytest.raises(HeirloomError, match="bounded pipeline wait expired"):
+            c.sync()
+    finally:
+        c.set_test_hooks(0, -1)
+    c.sync()  # the status was reported once and cleared
+    out = cuda.gemm_bf16(c, da, db, m, n, k, out_dtype=torch.float32)
+    assert_close("gemm after an expired wait", host(out), a @ b, atol=2e-3, rtol=1e-5)
