@@ -27,17 +27,28 @@ namespace {
 
 constexpr int FA_BM = 128;   // query rows per CTA
 constexpr int FA_BN = 64;    // keys per tile
-constexpr int FA_HD = 64;    // head dimension (one 128-byte swizzle row)
 constexpr int FA_KV_STAGES = 3;
-constexpr int FA_Q_BYTES = FA_BM * FA_HD * 2;   // 16 KB
-constexpr int FA_KV_BYTES = FA_BN * FA_HD * 2;  // 8 KB
 constexpr int FA_P_BYTES = FA_BM * FA_BN * 2;   // 16 KB: 128 rows of 64 keys, one 128-byte line each
 constexpr int FA_SOFTMAX_WARPS = 4;
 constexpr int FA_THREADS = (FA_SOFTMAX_WARPS + 2) * 32;  // + TMA warp + MMA warp
-constexpr int FA_TMEM_COLS = 256;  // S: 2 x 64 columns, O: 64 columns (allocations are powers of two)
-constexpr int FA_SMEM_DATA = FA_Q_BYTES + 2 * FA_KV_STAGES * FA_KV_BYTES + 2 * FA_P_BYTES;  // 96 KB
-constexpr int FA_SMEM_BYTES = FA_SMEM_DATA + 2048;  // barriers in front, alignment slack
-static_assert(2 * (FA_SMEM_BYTES + 1024) <= 228 * 1024, "two CTAs per SM");
+constexpr int FA_TMEM_COLS = 256;  // S: 2 x 64 columns, O: head_dim columns (allocations are powers of two)
+
+// Sizes that depend on the head dimension (64 or 128).  Operands wider than one 128-byte swizzle row are kept as
+// blocks of 64 channels side by side: a Q block is [128 rows x 128 bytes], a K or V block [64 keys x 128 bytes].
+template <int HD>
+struct FaSizes {
+  static_assert(HD == 64 || HD == 128, "head_dim 64 or 128");
+  static constexpr int BLOCKS = HD / 64;
+  static constexpr int Q_BLOCK = FA_BM * 128;            // 16 KB
+  static constexpr int KV_BLOCK = FA_BN * 128;           // 8 KB
+  static constexpr int Q_BYTES = BLOCKS * Q_BLOCK;
+  static constexpr int KV_BYTES = BLOCKS * KV_BLOCK;
+  static constexpr int SMEM_DATA = Q_BYTES + 2 * FA_KV_STAGES * KV_BYTES + 2 * FA_P_BYTES;  // 96 KB / 160 KB
+  static constexpr int SMEM_BYTES = SMEM_DATA + 2048;    // barriers in front, alignment slack
+  static constexpr int CTAS_PER_SM = HD == 64 ? 2 : 1;
+  static_assert(CTAS_PER_SM * (SMEM_BYTES + 1024) <= 228 * 1024, "shared memory per SM");
+  static_assert(2 * FA_BN + HD <= FA_TMEM_COLS, "tensor memory columns");
+};
 
 struct FaShared {
   uint64_t q_full;
@@ -47,7 +58,7 @@ struct FaShared {
   uint32_t tmem_base;
   int abort_flag;
 };
-static_assert(sizeof(FaShared) + 1023 + FA_SMEM_DATA <= FA_SMEM_BYTES, "front matter must fit the slack");
+static_assert(sizeof(FaShared) + 1023 <= 2048, "front matter must fit the slack");
 
 struct FaParams {
   int B, T, H;
@@ -58,9 +69,13 @@ struct FaParams {
   int* status;
 };
 
-__global__ void __launch_bounds__(FA_THREADS, 2)
+template <int HD>
+__global__ void __launch_bounds__(FA_THREADS, FaSizes<HD>::CTAS_PER_SM)
 flash_attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                            const __grid_constant__ CUtensorMap map_v, const FaParams p) {
+  using Z = FaSizes<HD>;
+  constexpr int FA_HD = HD;
+  constexpr int FA_Q_BYTES = Z::Q_BYTES, FA_KV_BYTES = Z::KV_BYTES, FA_SMEM_DATA = Z::SMEM_DATA, FA_SMEM_BYTES = Z::SMEM_BYTES;
   extern __shared__ uint8_t fa_smem_raw[];
   const uintptr_t raw = reinterpret_cast<uintptr_t>(fa_smem_raw);
   uint8_t* tiles = reinterpret_cast<uint8_t*>((raw + sizeof(FaShared) + 1023) & ~uintptr_t(1023));
@@ -114,16 +129,24 @@ flash_attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
       tc05::tma_prefetch_desc(&map_k);
       tc05::tma_prefetch_desc(&map_v);
       tc05::mbar_arrive_expect_tx(&sh->q_full, FA_Q_BYTES);
-      tc05::tma_load_2d(sq, &map_q, &sh->q_full, h * FA_HD, row_base + q0);
+#pragma unroll
+      for (int blk = 0; blk < Z::BLOCKS; ++blk)
+        tc05::tma_load_2d(sq + blk * Z::Q_BLOCK, &map_q, &sh->q_full, h * FA_HD + blk * 64, row_base + q0);
       for (int j = 0; j < n_tiles; ++j) {
         const int s = j % FA_KV_STAGES;
         const uint32_t ph = (uint32_t)(j / FA_KV_STAGES) & 1u;
         if (!tc05::mbar_wait(&sh->k_empty[s], ph ^ 1u, abort_flag)) break;
         tc05::mbar_arrive_expect_tx(&sh->k_full[s], FA_KV_BYTES);
-        tc05::tma_load_2d(sk + s * FA_KV_BYTES, &map_k, &sh->k_full[s], h * FA_HD, row_base + j * FA_BN);
+#pragma unroll
+        for (int blk = 0; blk < Z::BLOCKS; ++blk)
+          tc05::tma_load_2d(sk + s * FA_KV_BYTES + blk * Z::KV_BLOCK, &map_k, &sh->k_full[s], h * FA_HD + blk * 64,
+                            row_base + j * FA_BN);
         if (!tc05::mbar_wait(&sh->v_empty[s], ph ^ 1u, abort_flag)) break;
         tc05::mbar_arrive_expect_tx(&sh->v_full[s], FA_KV_BYTES);
-        tc05::tma_load_2d(sv + s * FA_KV_BYTES, &map_v, &sh->v_full[s], h * FA_HD, row_base + j * FA_BN);
+#pragma unroll
+        for (int blk = 0; blk < Z::BLOCKS; ++blk)
+          tc05::tma_load_2d(sv + s * FA_KV_BYTES + blk * Z::KV_BLOCK, &map_v, &sh->v_full[s], h * FA_HD + blk * 64,
+                            row_base + j * FA_BN);
       }
     }
   } else if (warp == FA_SOFTMAX_WARPS + 1) {
@@ -138,9 +161,11 @@ flash_attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
         tc05::tc_fence_after_sync();
         const uint32_t ak = tc05::smem_u32(sk + s * FA_KV_BYTES);
 #pragma unroll
-        for (int ks = 0; ks < FA_HD / 16; ++ks)
-          tc05::umma_ss(tmem_s0 + (uint32_t)((j & 1) * FA_BN), tc05::smem_desc_sw128(aq + ks * 32, 16, 1024),
-                        tc05::smem_desc_sw128(ak + ks * 32, 16, 1024), idesc_qk, ks > 0 ? 1u : 0u);
+        for (int ks = 0; ks < FA_HD / 16; ++ks)  // 16 channels a step; four steps per 64-channel block
+          tc05::umma_ss(tmem_s0 + (uint32_t)((j & 1) * FA_BN),
+                        tc05::smem_desc_sw128(aq + (ks / 4) * Z::Q_BLOCK + (ks % 4) * 32, 16, 1024),
+                        tc05::smem_desc_sw128(ak + (ks / 4) * Z::KV_BLOCK + (ks % 4) * 32, 16, 1024), idesc_qk,
+                        ks > 0 ? 1u : 0u);
         tc05::umma_commit(&sh->k_empty[s]);
         tc05::umma_commit(&sh->s_full[j & 1]);
         return true;
@@ -161,7 +186,7 @@ flash_attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
         for (int ks = 0; ks < FA_BN / 16; ++ks) {
           // A = P: [128 rows x 64 keys], K-major; B = V: rows are keys (MN-major), 16 keys per step
           const uint64_t da = tc05::smem_desc_sw128(ap + ks * 32, 16, 1024);
-          const uint64_t db = tc05::smem_desc_sw128(av + ks * (16 * 128), FA_BN * 128, 1024);
+          const uint64_t db = tc05::smem_desc_sw128(av + ks * (16 * 128), Z::KV_BLOCK, 1024);  // channel blocks KV_BLOCK apart
           tc05::umma_ss(tmem_o0, da, db, idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);  // O accumulates over the key tiles
         }
         tc05::umma_commit(&sh->v_empty[s]);
@@ -223,7 +248,7 @@ flash_attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
         if (raise) m_ref = m_new;
         l_run *= a;
 #pragma unroll
-        for (int hb = 0; hb < 2; ++hb) {
+        for (int hb = 0; hb < FA_HD / 32; ++hb) {
           uint32_t ob[32];
           tc05::tmem_ld_32x32b_x32(tmem_o0 + lane_sel + hb * 32, ob);
           tc05::tmem_ld_wait();
@@ -262,7 +287,7 @@ flash_attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
       const float inv = 1.0f / l_run;
       __nv_bfloat16* dst = p.out + (size_t)(row_base + t) * p.ld_out + (size_t)h * FA_HD;
 #pragma unroll
-      for (int hb = 0; hb < 2; ++hb) {
+      for (int hb = 0; hb < FA_HD / 32; ++hb) {
         uint32_t ob[32];
         tc05::tmem_ld_32x32b_x32(tmem_o0 + lane_sel + hb * 32, ob);
         tc05::tmem_ld_wait();
@@ -304,7 +329,7 @@ int flash_attention_forward_impl(hl_ctx* ctx, const void* q, const void* k, cons
   HL_REQUIRE(ctx && q && k && v && out && lse, "hl_flash_attention_forward: null argument");
   HL_REQUIRE(n_heads > 0, "hl_flash_attention_forward: causal_self_attention requires n_heads > 0");
   HL_REQUIRE(batch > 0 && time > 0, "hl_flash_attention_forward: batch and time must be positive");
-  HL_REQUIRE(head_dim == FA_HD, "hl_flash_attention_forward: head_dim must be 64");
+  HL_REQUIRE(head_dim == 64 || head_dim == 128, "hl_flash_attention_forward: head_dim must be 64 or 128");
   HL_REQUIRE(ld_qkv % 8 == 0 && ld_out % 8 == 0 && ld_qkv >= (long long)n_heads * head_dim &&
                  ld_out >= (long long)n_heads * head_dim,
              "hl_flash_attention_forward: row strides must be multiples of 8 and cover all heads");
@@ -314,9 +339,10 @@ int flash_attention_forward_impl(hl_ctx* ctx, const void* q, const void* k, cons
   const uint64_t rows = (uint64_t)batch * time, cols = (uint64_t)n_heads * head_dim;
   CUtensorMap mq, mk, mv;
   int rc;
-  if ((rc = make_tensor_map_bf16_2d(&mq, q, cols, rows, (uint64_t)ld_qkv, FA_HD, FA_BM)) != HL_OK) return rc;
-  if ((rc = make_tensor_map_bf16_2d(&mk, k, cols, rows, (uint64_t)ld_qkv, FA_HD, FA_BN)) != HL_OK) return rc;
-  if ((rc = make_tensor_map_bf16_2d(&mv, v, cols, rows, (uint64_t)ld_qkv, FA_HD, FA_BN)) != HL_OK) return rc;
+  // boxes of 64 channels (one 128-byte swizzle row); wider heads take several boxes per tile
+  if ((rc = make_tensor_map_bf16_2d(&mq, q, cols, rows, (uint64_t)ld_qkv, 64, FA_BM)) != HL_OK) return rc;
+  if ((rc = make_tensor_map_bf16_2d(&mk, k, cols, rows, (uint64_t)ld_qkv, 64, FA_BN)) != HL_OK) return rc;
+  if ((rc = make_tensor_map_bf16_2d(&mv, v, cols, rows, (uint64_t)ld_qkv, 64, FA_BN)) != HL_OK) return rc;
   FaParams p{};
   p.B = batch; p.T = time; p.H = n_heads;
   p.ld_out = ld_out;
@@ -324,15 +350,24 @@ int flash_attention_forward_impl(hl_ctx* ctx, const void* q, const void* k, cons
   p.lse = lse;
   p.scale_log2 = (1.0f / sqrtf((float)head_dim)) * 1.4426950408889634f;
   p.status = ctx->status_dev;
-  static bool configured = false;
-  if (!configured) {
-    HL_CUDA(cudaFuncSetAttribute(flash_attention_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, FA_SMEM_BYTES));
-    configured = true;
-  }
   const int nq = ceil_div(time, FA_BM);
   // causal algorithmic work: QK^T and PV over the lower triangle
   ProfileScope prof(ctx, HL_PROF_ATTENTION_FWD, 2.0 * batch * n_heads * (double)time * time * head_dim);
-  flash_attention_fwd_kernel<<<nq * batch * n_heads, FA_THREADS, FA_SMEM_BYTES, ctx->stream>>>(mq, mk, mv, p);
+  if (head_dim == 64) {
+    static bool configured = false;
+    if (!configured) {
+      HL_CUDA(cudaFuncSetAttribute(flash_attention_fwd_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, FaSizes<64>::SMEM_BYTES));
+      configured = true;
+    }
+    flash_attention_fwd_kernel<64><<<nq * batch * n_heads, FA_THREADS, FaSizes<64>::SMEM_BYTES, ctx->stream>>>(mq, mk, mv, p);
+  } else {
+    static bool configured = false;
+    if (!configured) {
+      HL_CUDA(cudaFuncSetAttribute(flash_attention_fwd_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, FaSizes<128>::SMEM_BYTES));
+      configured = true;
+    }
+    flash_attention_fwd_kernel<128><<<nq * batch * n_heads, FA_THREADS, FaSizes<128>::SMEM_BYTES, ctx->stream>>>(mq, mk, mv, p);
+  }
   HL_LAUNCH_CHECK("flash_attention_fwd_kernel");
   count_launch(ctx);
   ctx->counters.attention_launches += 1;

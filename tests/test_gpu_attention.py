@@ -20,16 +20,18 @@ def reference_lse(q, k, n_heads):
     return m + np.log(np.exp(s - m[..., None]).sum(-1))
 
 
+@pytest.mark.parametrize("hd", [64, 128])
 @pytest.mark.parametrize("B,T,H", [(1, 128, 1), (2, 256, 3), (1, 200, 2), (2, 1024, 2), (1, 72, 4), (1, 4096, 1), (1, 2100, 2)])
-def test_flash_forward_matches_oracle(B, T, H):
+def test_flash_forward_matches_oracle(B, T, H, hd):
     from heirloom_b200 import cuda
     c = ctx()
-    hd, C = 64, 64 * H
+    C = hd * H
     rng = np.random.default_rng(B * 1000 + T + H)
     qkv = ho.bf16_round(rng.standard_normal((B * T, 3 * C)) * 1.2)
     fused = dev(qkv, torch.bfloat16)
     q, k, v = fused[:, :C], fused[:, C:2 * C], fused[:, 2 * C:]
     out, lse = cuda.flash_attention_forward(c, q, k, v, B, T, H)
+    assert out.shape == (B * T, C)
     qn, kn, vn = (qkv[:, i * C:(i + 1) * C].reshape(B, T, C) for i in range(3))
     want = ho.causal_attention(qn, kn, vn, H, round_probs_bf16=True)
     # P is rounded to bf16 before the PV product (as the reference's tensor-core route does) and
@@ -43,7 +45,7 @@ def test_flash_forward_rejects_unsupported_shapes():
     from heirloom_b200._lib import HeirloomError
     c = ctx()
     x = c.zeros((128, 96), torch.bfloat16)
-    with pytest.raises(HeirloomError, match="head_dim must be 64"):
+    with pytest.raises(HeirloomError, match="head_dim must be 64 or 128"):
         cuda.flash_attention_forward(c, x, x, x, 1, 128, 3)
 
 
