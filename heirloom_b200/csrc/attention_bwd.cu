@@ -23,22 +23,34 @@ namespace {
 
 constexpr int FB_BM = 128;  // queries per tile
 constexpr int FB_BN = 128;  // keys per work item
-constexpr int FB_HD = 64;
-constexpr int FB_Q_STAGES = 2;
-constexpr int FB_KV_BUFFERS = 2;
-constexpr int FB_TILE_BYTES = 128 * FB_HD * 2;  // 16 KB
+constexpr int FB_BLOCK = 128 * 128;  // one 64-channel block of a 128-row operand tile: 16 KB
 constexpr int FB_PS_BYTES = FB_BM * FB_BN * 2;  // 32 KB
 constexpr int FB_SOFTMAX_WARPS = 8;
 constexpr int FB_THREADS = (FB_SOFTMAX_WARPS + 2) * 32;  // + TMA warp + MMA warp
 constexpr int FB_TMEM_COLS = 512;
-constexpr int FB_DQ_BYTES = FB_BM * FB_HD * 4;     // 32 KB: one dQ tile in f32, staged for the TMA reduction
-constexpr int FB_SMEM_DATA = FB_TILE_BYTES * (2 * FB_KV_BUFFERS + 2 * FB_Q_STAGES) + 2 * FB_PS_BYTES + FB_DQ_BYTES;  // 224 KB
-constexpr int FB_SMEM_BYTES = FB_SMEM_DATA + 1024;
-static_assert(FB_SMEM_BYTES <= 227 * 1024, "shared memory budget");
+constexpr int FB_DQ_BYTES = FB_BM * 64 * 4;     // 32 KB: 64 columns of a dQ tile in f32, staged for the TMA reduction
+constexpr int FB_MAX_STAGES = 2;
+
+// Sizes that depend on the head dimension.  A head of 128 channels is worked on as two halves of 64: S and dP use the
+// whole head (their operand tiles are two 64-channel blocks side by side), while dV, dK and dQ of a work item cover
+// one 64-channel block, so that the tensor-memory budget (S 128 + dP 128 + dV 64 + dK 64 + dQ 2 x 64 columns) is the
+// same for both sizes; the two halves are separate work items.  The wider tiles leave room for one K/V buffer and
+// one Q/dO stage only.
+template <int HD>
+struct FbSizes {
+  static_assert(HD == 64 || HD == 128, "head_dim 64 or 128");
+  static constexpr int BLOCKS = HD / 64;
+  static constexpr int TILE_BYTES = BLOCKS * FB_BLOCK;  // 16 KB / 32 KB
+  static constexpr int KV_BUFFERS = HD == 64 ? 2 : 1;
+  static constexpr int Q_STAGES = HD == 64 ? 2 : 1;
+  static constexpr int SMEM_DATA = TILE_BYTES * (2 * KV_BUFFERS + 2 * Q_STAGES) + 2 * FB_PS_BYTES + FB_DQ_BYTES;  // 224 KB
+  static constexpr int SMEM_BYTES = SMEM_DATA + 1024;
+  static_assert(SMEM_BYTES <= 227 * 1024, "shared memory budget");
+};
 
 struct FbBarriers {
-  uint64_t kv_full[FB_KV_BUFFERS], kv_empty[FB_KV_BUFFERS];
-  uint64_t q_full[FB_Q_STAGES], q_empty[FB_Q_STAGES];
+  uint64_t kv_full[FB_MAX_STAGES], kv_empty[FB_MAX_STAGES];
+  uint64_t q_full[FB_MAX_STAGES], q_empty[FB_MAX_STAGES];
   uint64_t sdp_full, sdp_free, p_full, dq_full;
   uint64_t stage_free, stage_full;  // dQ staging buffer: read by the previous reduction / written by all softmax warps
   uint32_t tmem_base;
@@ -47,6 +59,7 @@ struct FbBarriers {
 
 struct FbParams {
   int B, T, H;
+  int blocks;          // 64-channel blocks per head: 1 or 2
   const float* lse;    // [B,H,T]
   const float* delta;  // [B,H,T] rowsum(dO * O)
   float* dq_accum;     // f32 [B*T, H*hd], zeroed by the caller
@@ -67,6 +80,7 @@ struct FbCursor {
   int it;        // query tile within the item's walk
   int n_tiles;   // length of the walk
   int kj, b, h;  // key tile, batch, head
+  int cb;        // which 64-channel block of the head this item's dV, dK and dQ cover
   __device__ __forceinline__ bool valid() const { return item >= 0; }
 };
 // The CTA's `local`-th item.  Items are sorted by decreasing walk length; rounds alternate direction
@@ -74,15 +88,18 @@ struct FbCursor {
 // per-CTA totals of a static assignment.
 __device__ __forceinline__ void fb_load_item(FbCursor& c, int local, const FbParams& p) {
   const int nq = (p.T + FB_BM - 1) / FB_BM;
-  const int total = nq * p.B * p.H;
+  const int per_kj = p.B * p.H * p.blocks;
+  const int total = nq * per_kj;
   const int grid = (int)gridDim.x, cta = (int)blockIdx.x;
   const int item = local * grid + ((local & 1) ? grid - 1 - cta : cta);
   if (item >= total) { c.item = -1; return; }
-  const int bh = item % (p.B * p.H);
+  const int rest = item % per_kj;
+  const int bh = rest / p.blocks;
   c.item = item;
   c.local = local;
   c.it = 0;
-  c.kj = item / (p.B * p.H);
+  c.kj = item / per_kj;
+  c.cb = rest % p.blocks;
   c.b = bh / p.H;
   c.h = bh % p.H;
   c.n_tiles = nq - c.kj;  // query tiles kj .. nq-1
@@ -94,10 +111,15 @@ __device__ __forceinline__ FbCursor fb_next(const FbCursor& c, const FbParams& p
   return n;
 }
 
+template <int HD>
 __global__ void __launch_bounds__(FB_THREADS, 1)
 flash_attention_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                            const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do,
                            const __grid_constant__ CUtensorMap map_dq, const FbParams p) {
+  using Z = FbSizes<HD>;
+  constexpr int FB_HD = HD;
+  constexpr int FB_TILE_BYTES = Z::TILE_BYTES, FB_KV_BUFFERS = Z::KV_BUFFERS, FB_Q_STAGES = Z::Q_STAGES;
+  constexpr int FB_SMEM_DATA = Z::SMEM_DATA, FB_SMEM_BYTES = Z::SMEM_BYTES;
   extern __shared__ uint8_t fb_smem_raw[];
   const uintptr_t raw = reinterpret_cast<uintptr_t>(fb_smem_raw);
   uint8_t* tiles = reinterpret_cast<uint8_t*>((raw + sizeof(FbBarriers) + 1023) & ~uintptr_t(1023));
@@ -141,7 +163,7 @@ flash_attention_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
   tc05::tc_fence_after_sync();
   const uint32_t tmem_s = bars->tmem_base;  // 128 columns
   const uint32_t tmem_dp = tmem_s + 128;    // 128 columns
-  const uint32_t tmem_dv = tmem_s + 256;    // 64 columns
+  const uint32_t tmem_dv = tmem_s + 256;    // 64 columns (one channel block of the head)
   const uint32_t tmem_dk = tmem_s + 320;    // 64 columns
   const uint32_t tmem_dq = tmem_s + 384;    // two buffers of 64 columns, alternating by query tile
 
@@ -164,26 +186,37 @@ flash_attention_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
           const int kb = c.local % FB_KV_BUFFERS;
           if (!tc05::mbar_wait(&bars->kv_empty[kb], ((uint32_t)(c.local / FB_KV_BUFFERS) & 1u) ^ 1u, abort_flag)) break;
           tc05::mbar_arrive_expect_tx(&bars->kv_full[kb], 2 * FB_TILE_BYTES);
-          tc05::tma_load_2d(sk + kb * FB_TILE_BYTES, &map_k, &bars->kv_full[kb], c.h * FB_HD, row_base + c.kj * FB_BN);
-          tc05::tma_load_2d(sv + kb * FB_TILE_BYTES, &map_v, &bars->kv_full[kb], c.h * FB_HD, row_base + c.kj * FB_BN);
+#pragma unroll
+          for (int blk = 0; blk < Z::BLOCKS; ++blk) {
+            tc05::tma_load_2d(sk + kb * FB_TILE_BYTES + blk * FB_BLOCK, &map_k, &bars->kv_full[kb], c.h * FB_HD + blk * 64,
+                              row_base + c.kj * FB_BN);
+            tc05::tma_load_2d(sv + kb * FB_TILE_BYTES + blk * FB_BLOCK, &map_v, &bars->kv_full[kb], c.h * FB_HD + blk * 64,
+                              row_base + c.kj * FB_BN);
+          }
         }
         const int s = g % FB_Q_STAGES;
         const int qrow = row_base + (c.kj + c.it) * FB_BM;
         // the stage frees only when the tile two back has been consumed: have L2 fetch the tile in the meantime
-        tc05::tma_prefetch_l2_2d(&map_q, c.h * FB_HD, qrow);
-        tc05::tma_prefetch_l2_2d(&map_do, c.h * FB_HD, qrow);
+#pragma unroll
+        for (int blk = 0; blk < Z::BLOCKS; ++blk) {
+          tc05::tma_prefetch_l2_2d(&map_q, c.h * FB_HD + blk * 64, qrow);
+          tc05::tma_prefetch_l2_2d(&map_do, c.h * FB_HD + blk * 64, qrow);
+        }
         if (!tc05::mbar_wait(&bars->q_empty[s], ((uint32_t)(g / FB_Q_STAGES) & 1u) ^ 1u, abort_flag)) break;
         tc05::mbar_arrive_expect_tx(&bars->q_full[s], 2 * FB_TILE_BYTES);
-        tc05::tma_load_2d(sq + s * FB_TILE_BYTES, &map_q, &bars->q_full[s], c.h * FB_HD, qrow);
-        tc05::tma_load_2d(sdo + s * FB_TILE_BYTES, &map_do, &bars->q_full[s], c.h * FB_HD, qrow);
+#pragma unroll
+        for (int blk = 0; blk < Z::BLOCKS; ++blk) {
+          tc05::tma_load_2d(sq + s * FB_TILE_BYTES + blk * FB_BLOCK, &map_q, &bars->q_full[s], c.h * FB_HD + blk * 64, qrow);
+          tc05::tma_load_2d(sdo + s * FB_TILE_BYTES + blk * FB_BLOCK, &map_do, &bars->q_full[s], c.h * FB_HD + blk * 64, qrow);
+        }
       }
     }
   } else if (warp == FB_SOFTMAX_WARPS + 1) {
     // -------------------------------------------------------------------------- MMA issuer
     if (tc05::elect_one() && !*abort_flag) {
       constexpr uint32_t idesc_sdp = tc05::instr_desc_bf16_f32(128, 128, false, false);
-      constexpr uint32_t idesc_dkv = tc05::instr_desc_bf16_f32(128, FB_HD, true, true);
-      constexpr uint32_t idesc_dq = tc05::instr_desc_bf16_f32(128, FB_HD, false, true);
+      constexpr uint32_t idesc_dkv = tc05::instr_desc_bf16_f32(128, 64, true, true);   // one channel block of dV / dK
+      constexpr uint32_t idesc_dq = tc05::instr_desc_bf16_f32(128, 64, false, true);
       const uint32_t ap = tc05::smem_u32(sp), ads = tc05::smem_u32(sds);
       // S = Q·Kᵀ and dP = dO·Vᵀ of query tile number `g` (counted over the whole sequence)
       auto issue_scores = [&](const FbCursor& c, int g) -> bool {
@@ -197,13 +230,13 @@ flash_attention_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
         const uint32_t ak = tc05::smem_u32(sk + kb * FB_TILE_BYTES), av = tc05::smem_u32(sv + kb * FB_TILE_BYTES);
         const uint32_t aq = tc05::smem_u32(sq + s * FB_TILE_BYTES), ado = tc05::smem_u32(sdo + s * FB_TILE_BYTES);
 #pragma unroll
-        for (int ks = 0; ks < FB_HD / 16; ++ks)
-          tc05::umma_ss(tmem_s, tc05::smem_desc_sw128(aq + ks * 32, 16, 1024),
-                        tc05::smem_desc_sw128(ak + ks * 32, 16, 1024), idesc_sdp, ks > 0 ? 1u : 0u);
+        for (int ks = 0; ks < FB_HD / 16; ++ks)  // the whole head: four 16-channel steps per 64-channel block
+          tc05::umma_ss(tmem_s, tc05::smem_desc_sw128(aq + (ks / 4) * FB_BLOCK + (ks % 4) * 32, 16, 1024),
+                        tc05::smem_desc_sw128(ak + (ks / 4) * FB_BLOCK + (ks % 4) * 32, 16, 1024), idesc_sdp, ks > 0 ? 1u : 0u);
 #pragma unroll
         for (int ks = 0; ks < FB_HD / 16; ++ks)
-          tc05::umma_ss(tmem_dp, tc05::smem_desc_sw128(ado + ks * 32, 16, 1024),
-                        tc05::smem_desc_sw128(av + ks * 32, 16, 1024), idesc_sdp, ks > 0 ? 1u : 0u);
+          tc05::umma_ss(tmem_dp, tc05::smem_desc_sw128(ado + (ks / 4) * FB_BLOCK + (ks % 4) * 32, 16, 1024),
+                        tc05::smem_desc_sw128(av + (ks / 4) * FB_BLOCK + (ks % 4) * 32, 16, 1024), idesc_sdp, ks > 0 ? 1u : 0u);
         tc05::umma_commit(&bars->sdp_full);
         return true;
       };
@@ -213,7 +246,7 @@ flash_attention_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
         // S/dP of the next query tile (of this item or of the next one) are issued as soon as this
         // tile's have been read out, so the softmax warps find them ready when they come back
         const FbCursor n = fb_next(c, p);
-        if (n.valid()) {
+        if (FB_Q_STAGES > 1 && n.valid()) {
           if (!tc05::mbar_wait(&bars->sdp_free, (uint32_t)g & 1u, abort_flag)) break;
           tc05::tc_fence_after_sync();
           if (!issue_scores(n, g + 1)) break;
@@ -222,8 +255,10 @@ flash_attention_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
         tc05::tc_fence_after_sync();
         const int s = g % FB_Q_STAGES;
         const int kb = c.local % FB_KV_BUFFERS;
-        const uint32_t ak = tc05::smem_u32(sk + kb * FB_TILE_BYTES);
-        const uint32_t aq = tc05::smem_u32(sq + s * FB_TILE_BYTES), ado = tc05::smem_u32(sdo + s * FB_TILE_BYTES);
+        // dV, dK and dQ of this item cover channel block c.cb of the head
+        const uint32_t ak = tc05::smem_u32(sk + kb * FB_TILE_BYTES) + (uint32_t)(c.cb * FB_BLOCK);
+        const uint32_t aq = tc05::smem_u32(sq + s * FB_TILE_BYTES) + (uint32_t)(c.cb * FB_BLOCK);
+        const uint32_t ado = tc05::smem_u32(sdo + s * FB_TILE_BYTES) + (uint32_t)(c.cb * FB_BLOCK);
 #pragma unroll
         for (int ks = 0; ks < FB_BM / 16; ++ks) {
           // contraction over the 128 queries of this tile: 16 query rows = 2048 bytes per step
@@ -240,11 +275,18 @@ flash_attention_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
           // dQ_tile = dS·K: contraction over the 128 keys; dS is K-major in two 64-key blocks
           const uint64_t a_ds = tc05::smem_desc_sw128(ads + (ks / 4) * (FB_BM * 128) + (ks % 4) * 32, 16, 1024);
           const uint64_t b_k = tc05::smem_desc_sw128(ak + ks * 2048, FB_BN * 128, 1024);
-          tc05::umma_ss(tmem_dq + (uint32_t)((g & 1) * FB_HD), a_ds, b_k, idesc_dq, ks > 0 ? 1u : 0u);
+          tc05::umma_ss(tmem_dq + (uint32_t)((g & 1) * 64), a_ds, b_k, idesc_dq, ks > 0 ? 1u : 0u);
         }
         tc05::umma_commit(&bars->q_empty[s]);
         if (c.it == c.n_tiles - 1) tc05::umma_commit(&bars->kv_empty[kb]);  // the item's K and V are no longer read
         tc05::umma_commit(&bars->dq_full);
+        if (FB_Q_STAGES == 1 && n.valid()) {
+          // one Q/dO stage: the next tile's loads could only start once this tile's products were committed, so its
+          // scores are issued after them (S and dP were read out before P and dS were handed over)
+          if (!tc05::mbar_wait(&bars->sdp_free, (uint32_t)g & 1u, abort_flag)) break;
+          tc05::tc_fence_after_sync();
+          if (!issue_scores(n, g + 1)) break;
+        }
         c = n;
       }
     }
@@ -274,7 +316,7 @@ flash_attention_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
       }
     };
     auto add_dq_begin = [&](int g, uint32_t (&qb)[32]) {  // the tile starts to travel out of tensor memory
-      tc05::tmem_ld_32x32b_x32(tmem_dq + (uint32_t)((g & 1) * FB_HD) + lane_sel + half * 32, qb);
+      tc05::tmem_ld_32x32b_x32(tmem_dq + (uint32_t)((g & 1) * 64) + lane_sel + half * 32, qb);
     };
     auto add_dq_finish = [&](const FbCursor& c, uint32_t (&qb)[32]) -> bool {
       tc05::tmem_ld_wait();
@@ -291,8 +333,8 @@ flash_attention_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
         if (!tc05::mbar_wait(&bars->stage_full, (uint32_t)drain & 1u, abort_flag)) return false;
         if (lane == 0) {
           const int t0 = (c.kj + c.it) * FB_BM;
-          tc05::tma_reduce_add_3d(&map_dq, sdq, c.h * FB_HD, t0, c.b);
-          tc05::tma_reduce_add_3d(&map_dq, sdq + FB_BM * 128, c.h * FB_HD + 32, t0, c.b);
+          tc05::tma_reduce_add_3d(&map_dq, sdq, c.h * FB_HD + c.cb * 64, t0, c.b);
+          tc05::tma_reduce_add_3d(&map_dq, sdq + FB_BM * 128, c.h * FB_HD + c.cb * 64 + 32, t0, c.b);
           tc05::tma_store_commit();
         }
       }
@@ -315,7 +357,7 @@ flash_attention_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
     auto store_dkv = [&](const uint32_t (&w)[32], const FbCursor& c) {
       const int key = c.kj * FB_BN + r;
       if (key < p.T) {
-        const size_t off = (size_t)(c.b * p.T + key) * p.ld_dkv + (size_t)c.h * FB_HD + half * 32;
+        const size_t off = (size_t)(c.b * p.T + key) * p.ld_dkv + (size_t)c.h * FB_HD + c.cb * 64 + half * 32;
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
           *reinterpret_cast<uint4*>(p.dv + off + i * 8) = make_uint4(w[i * 4], w[i * 4 + 1], w[i * 4 + 2], w[i * 4 + 3]);
@@ -451,22 +493,22 @@ flash_attention_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
   }
 }
 
-// delta[b,h,t] = sum_j dO[b,t,h,j] * O[b,t,h,j]; eight lanes per (row, head), 16 bytes each.
+// delta[b,h,t] = sum_j dO[b,t,h,j] * O[b,t,h,j]; eight lanes per (row, head), 16 bytes at a time.
 __global__ void __launch_bounds__(256)
 attention_delta_kernel(const __nv_bfloat16* __restrict__ out, long long ld_out, const __nv_bfloat16* __restrict__ dout,
-                       long long ld_dout, float* __restrict__ delta, int B, int T, int H) {
+                       long long ld_dout, float* __restrict__ delta, int B, int T, int H, int hd) {
   const long long pair = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 3;  // (row, head)
   const int part = threadIdx.x & 7;
   const bool in = pair < (long long)B * T * H;
   const int h = in ? (int)(pair % H) : 0;
   const long long row = in ? pair / H : 0;  // b*T + t
-  const uint4 o4 = *reinterpret_cast<const uint4*>(out + row * ld_out + h * FB_HD + part * 8);
-  const uint4 d4 = *reinterpret_cast<const uint4*>(dout + row * ld_dout + h * FB_HD + part * 8);
   float s = 0.f;
-  {
+  for (int c = part * 8; c < hd; c += 64) {
+    const uint4 o4 = *reinterpret_cast<const uint4*>(out + row * ld_out + h * hd + c);
+    const uint4 d4 = *reinterpret_cast<const uint4*>(dout + row * ld_dout + h * hd + c);
     const float2 a0 = unpack_bf16x2(o4.x), a1 = unpack_bf16x2(o4.y), a2 = unpack_bf16x2(o4.z), a3 = unpack_bf16x2(o4.w);
     const float2 b0 = unpack_bf16x2(d4.x), b1 = unpack_bf16x2(d4.y), b2 = unpack_bf16x2(d4.z), b3 = unpack_bf16x2(d4.w);
-    s = a0.x * b0.x + a0.y * b0.y + a1.x * b1.x + a1.y * b1.y + a2.x * b2.x + a2.y * b2.y + a3.x * b3.x + a3.y * b3.y;
+    s += a0.x * b0.x + a0.y * b0.y + a1.x * b1.x + a1.y * b1.y + a2.x * b2.x + a2.y * b2.y + a3.x * b3.x + a3.y * b3.y;
   }
   s += __shfl_xor_sync(0xffffffffu, s, 1);
   s += __shfl_xor_sync(0xffffffffu, s, 2);
@@ -501,7 +543,7 @@ int flash_attention_backward_impl(hl_ctx* ctx, const void* q, const void* k, con
                                   int n_heads, int head_dim, void* scratch, size_t scratch_bytes) {
   HL_REQUIRE(ctx && q && k && v && out && dout && lse && dq && dk && dv, "hl_flash_attention_backward: null argument");
   HL_REQUIRE(n_heads > 0 && batch > 0 && time > 0, "hl_flash_attention_backward: sizes must be positive");
-  HL_REQUIRE(head_dim == FB_HD, "hl_flash_attention_backward: head_dim must be 64");
+  HL_REQUIRE(head_dim == 64 || head_dim == 128, "hl_flash_attention_backward: head_dim must be 64 or 128");
   const long long C = (long long)n_heads * head_dim;
   HL_REQUIRE(ld_qkv % 8 == 0 && ld_out % 8 == 0 && ld_dout % 8 == 0 && ld_dqkv % 8 == 0 && ld_qkv >= C && ld_out >= C &&
                  ld_dout >= C && ld_dqkv >= C,
@@ -522,17 +564,19 @@ int flash_attention_backward_impl(hl_ctx* ctx, const void* q, const void* k, con
     const long long pairs = (long long)rows * n_heads;
     attention_delta_kernel<<<(unsigned)ceil_div_ll(pairs * 8, 256), 256, 0, ctx->stream>>>(
         reinterpret_cast<const __nv_bfloat16*>(out), ld_out, reinterpret_cast<const __nv_bfloat16*>(dout), ld_dout,
-        delta, batch, time, n_heads);
+        delta, batch, time, n_heads, head_dim);
     HL_LAUNCH_CHECK("attention_delta_kernel");
   }
   CUtensorMap mq, mk, mv, mdo;
   int rc;
-  if ((rc = make_tensor_map_bf16_2d(&mq, q, (uint64_t)C, rows, (uint64_t)ld_qkv, FB_HD, FB_BM)) != HL_OK) return rc;
-  if ((rc = make_tensor_map_bf16_2d(&mk, k, (uint64_t)C, rows, (uint64_t)ld_qkv, FB_HD, FB_BN)) != HL_OK) return rc;
-  if ((rc = make_tensor_map_bf16_2d(&mv, v, (uint64_t)C, rows, (uint64_t)ld_qkv, FB_HD, FB_BN)) != HL_OK) return rc;
-  if ((rc = make_tensor_map_bf16_2d(&mdo, dout, (uint64_t)C, rows, (uint64_t)ld_dout, FB_HD, FB_BM)) != HL_OK) return rc;
+  // boxes of 64 channels (one 128-byte swizzle row); a head of 128 channels takes two boxes per tile
+  if ((rc = make_tensor_map_bf16_2d(&mq, q, (uint64_t)C, rows, (uint64_t)ld_qkv, 64, FB_BM)) != HL_OK) return rc;
+  if ((rc = make_tensor_map_bf16_2d(&mk, k, (uint64_t)C, rows, (uint64_t)ld_qkv, 64, FB_BN)) != HL_OK) return rc;
+  if ((rc = make_tensor_map_bf16_2d(&mv, v, (uint64_t)C, rows, (uint64_t)ld_qkv, 64, FB_BN)) != HL_OK) return rc;
+  if ((rc = make_tensor_map_bf16_2d(&mdo, dout, (uint64_t)C, rows, (uint64_t)ld_dout, 64, FB_BM)) != HL_OK) return rc;
   FbParams p{};
   p.B = batch; p.T = time; p.H = n_heads;
+  p.blocks = head_dim / 64;
   p.lse = lse; p.delta = delta;
   p.dq_accum = dq_accum; p.ld_dq = C;
   p.dk = reinterpret_cast<__nv_bfloat16*>(dk);
@@ -541,11 +585,6 @@ int flash_attention_backward_impl(hl_ctx* ctx, const void* q, const void* k, con
   p.scale = 1.0f / sqrtf((float)head_dim);
   p.scale_log2 = p.scale * 1.4426950408889634f;
   p.status = ctx->status_dev;
-  static bool configured = false;
-  if (!configured) {
-    HL_CUDA(cudaFuncSetAttribute(flash_attention_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, FB_SMEM_BYTES));
-    configured = true;
-  }
   const int nq = ceil_div(time, FB_BM);
   // dQ accumulator as [batch][time][channels] f32, so that a tile's rows past `time` are clipped instead of landing in
   // the next batch entry; boxes of 32 columns (128 bytes) by 128 rows
@@ -556,7 +595,22 @@ int flash_attention_backward_impl(hl_ctx* ctx, const void* q, const void* k, con
     const uint32_t box[3] = {32, (uint32_t)FB_BM, 1};
     if ((rc = make_tensor_map(&mdq, HL_F32, 3, dq_accum, dims, strides, box, 128)) != HL_OK) return rc;
   }
-  flash_attention_bwd_kernel<<<std::min(nq * batch * n_heads, persistent_sms(ctx)), FB_THREADS, FB_SMEM_BYTES, ctx->stream>>>(mq, mk, mv, mdo, mdq, p);
+  const int grid = std::min(nq * batch * n_heads * p.blocks, persistent_sms(ctx));
+  if (head_dim == 64) {
+    static bool configured = false;
+    if (!configured) {
+      HL_CUDA(cudaFuncSetAttribute(flash_attention_bwd_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, FbSizes<64>::SMEM_BYTES));
+      configured = true;
+    }
+    flash_attention_bwd_kernel<64><<<grid, FB_THREADS, FbSizes<64>::SMEM_BYTES, ctx->stream>>>(mq, mk, mv, mdo, mdq, p);
+  } else {
+    static bool configured = false;
+    if (!configured) {
+      HL_CUDA(cudaFuncSetAttribute(flash_attention_bwd_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, FbSizes<128>::SMEM_BYTES));
+      configured = true;
+    }
+    flash_attention_bwd_kernel<128><<<grid, FB_THREADS, FbSizes<128>::SMEM_BYTES, ctx->stream>>>(mq, mk, mv, mdo, mdq, p);
+  }
   HL_LAUNCH_CHECK("flash_attention_bwd_kernel");
   {
     const long long quads = (long long)rows * (C / 4);

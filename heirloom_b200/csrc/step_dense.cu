@@ -79,7 +79,7 @@ struct hl_decoder {
   std::vector<__nv_bfloat16*> x;  // x[l] is the input of block l; x[L] the final residual stream
   std::vector<LayerActs> la;
   __nv_bfloat16 *z = nullptr, *dlogits = nullptr, *dxb = nullptr, *dh = nullptr, *dob = nullptr, *dqkv = nullptr;
-  // head sizes other than 64 on the bf16 route: attention runs through the f32 kernels on these shared buffers
+  // head sizes other than 64 and 128 on the bf16 route: attention runs through the f32 kernels on these shared buffers
   bool flash_ok = true;
   float *fa_q = nullptr, *fa_k = nullptr, *fa_v = nullptr, *fa_o = nullptr, *fa_probs = nullptr, *fa_dq = nullptr,
         *fa_dk = nullptr, *fa_dv = nullptr, *fa_do = nullptr;
@@ -482,7 +482,7 @@ int zero_memory_table_grads(hl_decoder* m) {
   return HL_OK;
 }
 
-// ---- attention for head sizes the tcgen05 kernels are not built for (they take head_dim 64) ----------------------
+// ---- attention for head sizes the tcgen05 kernels are not built for (they take head_dim 64 and 128) -------------
 // The bf16 q, k, v are widened to f32 (exact), the f32 attention kernels run on them and their results are rounded to
 // bf16 where the flash route stores bf16 (attention output, dQ/dK/dV).  Probabilities are not kept per layer: the
 // backward pass runs the forward kernel again into the shared probability buffer.
@@ -1113,7 +1113,7 @@ static int decoder_create_impl(hl_ctx* ctx, const hl_decoder_config* cfg, const 
   m->ctx = ctx;
   m->cfg = *cfg;
   m->N = cfg->batch * cfg->context;
-  m->flash_ok = cfg->d_model / cfg->n_heads == 64;
+  m->flash_ok = cfg->d_model / cfg->n_heads == 64 || cfg->d_model / cfg->n_heads == 128;
   if (mem && mem->n_memory_layers > 0) {
     m->has_memory = true;
     m->mem = *mem;

@@ -6,7 +6,7 @@
     python -m heirloom_b200.kernel_bench --only gemm --split-k 1   # GEMMs without the even deal of the last wave
 
 Cases: the bf16 GEMM shapes of the GPT-124M-shaped step (forward, input gradient, weight gradient),
-causal attention forward/backward (12 heads, head_dim 64; batch 16 x T 1024 and batch 4 x T 4096), layer norm and
+causal attention forward/backward (12 heads, head_dim 64 and 128; batch 16 x T 1024 and batch 4 x T 4096), layer norm and
 GELU over 16384 x 768 / 16384 x 3072, fused cross-entropy over 16384 x 50304, bias column sums, the fused
 AdamW over 124 M and 1.3 G parameters, and the product-key memory layer's kernels at 16384 tokens, 2 x 512 half
 keys, 262,144 slots, top-k 32.  Inputs are N(0,1) from torch's generator with seed 0.
@@ -118,6 +118,20 @@ def build_cases(ctx):
                 5.0 * b4 * H * t4 * t4 * 64, "flop"
         return make
 
+    def attn_wide(backward, b_, t_):
+        # head_dim 128: the same 12 heads, 1536 channels
+        hd, C = 128, 12 * 128
+        def make():
+            qkv = bf16(b_ * t_, 3 * C)
+            q, k, v = qkv[:, :C], qkv[:, C:2 * C], qkv[:, 2 * C:]
+            if not backward:
+                return (lambda: cuda.flash_attention_forward(ctx, q, k, v, b_, t_, H)), 2.0 * b_ * H * t_ * t_ * hd, "flop"
+            out, lse = cuda.flash_attention_forward(ctx, q, k, v, b_, t_, H)
+            do = bf16(b_ * t_, C)
+            return (lambda: cuda.flash_attention_backward(ctx, q, k, v, out, do, lse, b_, t_, H)), \
+                5.0 * b_ * H * t_ * t_ * hd, "flop"
+        return make
+
     def ln_wide_fwd():
         x, w, b = bf16(N, F), torch.ones(F, device="cuda"), torch.zeros(F, device="cuda")
         return (lambda: cuda.layer_norm_forward(ctx, x, w, b)), N * F * 4.0, "bytes"
@@ -216,7 +230,9 @@ def build_cases(ctx):
     cases.update(attention_fwd_t1024=attn_fwd, attention_bwd_t1024=attn_bwd, layer_norm_fwd=ln_fwd, layer_norm_bwd=ln_bwd,
                  gelu_fwd_16384x3072=gelu_fwd, cross_entropy_16384x50304=ce, bias_colsum_16384x50304=colsum,
                  adamw_124m=adamw, attention_fwd_t4096=attn_long(False), attention_bwd_t4096=attn_long(True),
-                 layer_norm_fwd_16384x3072=ln_wide_fwd, adamw_1300m=adamw_big)
+                 layer_norm_fwd_16384x3072=ln_wide_fwd, adamw_1300m=adamw_big,
+                 attention_fwd_t1024_hd128=attn_wide(False, B, T), attention_bwd_t1024_hd128=attn_wide(True, B, T),
+                 attention_fwd_t4096_hd128=attn_wide(False, 4, 4096), attention_bwd_t4096_hd128=attn_wide(True, 4, 4096))
     return cases
 
 

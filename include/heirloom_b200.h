@@ -304,7 +304,8 @@ int hl_gemm_bf16_static_scratch(hl_ctx* ctx, const hl_gemm_desc* desc, const voi
  * scores, saved for the backward (the reference saves row_max and row_denom instead,
  * src/tensor.rs:4164-4358).  P enters the PV product rounded to bf16, accumulation is f32.
  * Replaces causal_attention_bf16_flash_tensor_core_forward_f32_buffers (cuda.rs:5283-5420,
- * tensor_core.ptx:2284-2981).  head_dim must be 64. */
+ * tensor_core.ptx:2284-2981, which takes any head_dim that is a multiple of 16).  head_dim must be 64 or 128;
+ * wider heads are handled as 64-channel blocks side by side. */
 int hl_flash_attention_forward(hl_ctx* ctx, const void* q, const void* k, const void* v, long long ld_qkv,
                                void* out, long long ld_out, float* lse, int batch, int time, int n_heads,
                                int head_dim);

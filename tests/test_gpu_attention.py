@@ -49,11 +49,12 @@ def test_flash_forward_rejects_unsupported_shapes():
         cuda.flash_attention_forward(c, x, x, x, 1, 128, 3)
 
 
+@pytest.mark.parametrize("hd", [64, 128])
 @pytest.mark.parametrize("B,T,H", [(1, 128, 1), (2, 256, 2), (1, 200, 2), (1, 1024, 2), (2, 72, 3), (1, 4096, 1), (1, 2100, 2)])
-def test_flash_backward_matches_oracle(B, T, H):
+def test_flash_backward_matches_oracle(B, T, H, hd):
     from heirloom_b200 import cuda
     c = ctx()
-    C = 64 * H
+    C = hd * H
     rng = np.random.default_rng(B * 77 + T + H)
     qkv = ho.bf16_round(rng.standard_normal((B * T, 3 * C)))
     go = ho.bf16_round(rng.standard_normal((B * T, C)))
