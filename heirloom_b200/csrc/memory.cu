@@ -4,7 +4,6 @@
 // reference's one-thread-per-token serial selection (heirloom-kernels/src/ptx/kernels.ptx:1780-2262)
 // and its one-thread-per-element gathers (:2317-3259); the O(selected^2) duplicate scan of the
 // sparse AdamW kernels (:537-811) becomes a row flag pass.
-#include <cub/device/device_radix_sort.cuh>
 
 #include "kernels.h"
 
@@ -737,6 +736,137 @@ __global__ void value_event_keys_kernel(const int64_t* __restrict__ idx, long lo
   }
 }
 
+// ---- stable radix sort of (row key, event) pairs, eight bits a pass --------------------------------------------
+// The row-ordered value backward needs the step's (token, slot) events grouped by table row, events of a row in
+// ascending order (that order fixes the f32 summation order of a row's gradient).  Three kernels a pass:
+// digit histograms per tile of 2048 keys, an exclusive scan of every digit's row of the digit-major histogram array
+// (one block per digit; the scatter adds the scan over the 256 digit totals itself), and a scatter in which every
+// warp walks its 256 keys in order, ranking equal digits with warp matches, so the sort is stable.
+constexpr int RS_BITS = 8, RS_DIGITS = 1 << RS_BITS, RS_WARPS = 8, RS_THREADS = RS_WARPS * 32;
+constexpr int RS_PER_WARP = 256, RS_TILE = RS_WARPS * RS_PER_WARP;
+
+// Digit counts of each warp's keys in shared memory: lanes with equal digits are found with a warp match, the
+// lowest of them adds the group's size.
+__device__ __forceinline__ void rs_count_tile(const int* __restrict__ keys, long long n, int shift,
+                                              int (*wc)[RS_DIGITS]) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  for (int i = threadIdx.x; i < RS_WARPS * RS_DIGITS; i += RS_THREADS) (&wc[0][0])[i] = 0;
+  __syncthreads();
+  const long long base = (long long)blockIdx.x * RS_TILE + (long long)warp * RS_PER_WARP;
+  for (int r = 0; r < RS_PER_WARP / 32; ++r) {
+    const long long i = base + r * 32 + lane;
+    const bool in = i < n;
+    const unsigned alive = __ballot_sync(0xffffffffu, in);
+    if (in) {
+      const int d = (keys[i] >> shift) & (RS_DIGITS - 1);
+      const unsigned peers = __match_any_sync(alive, d);
+      if (lane == __ffs(peers) - 1) wc[warp][d] += __popc(peers);
+    }
+    __syncwarp();
+  }
+  __syncthreads();
+}
+
+__global__ void __launch_bounds__(RS_THREADS)
+radix_hist_kernel(const int* __restrict__ keys, long long n, int shift, int* __restrict__ hist, int n_tiles) {
+  __shared__ int wc[RS_WARPS][RS_DIGITS];
+  rs_count_tile(keys, n, shift, wc);
+  for (int d = threadIdx.x; d < RS_DIGITS; d += RS_THREADS) {
+    int t = 0;
+#pragma unroll
+    for (int w = 0; w < RS_WARPS; ++w) t += wc[w][d];
+    hist[(size_t)d * n_tiles + blockIdx.x] = t;  // digit-major: a scan over the array gives every (digit, tile) its start
+  }
+}
+
+// Block d scans row d of the digit-major histogram in place (exclusive) and writes the row's total.
+__global__ void __launch_bounds__(RS_THREADS)
+radix_scan_rows_kernel(int* __restrict__ hist, int n_tiles, int* __restrict__ totals) {
+  __shared__ int warp_sums[RS_WARPS];
+  __shared__ int carry;
+  int* row = hist + (size_t)blockIdx.x * n_tiles;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (threadIdx.x == 0) carry = 0;
+  __syncthreads();
+  for (int base = 0; base < n_tiles; base += RS_THREADS) {
+    const int i = base + threadIdx.x;
+    const int v = i < n_tiles ? row[i] : 0;
+    int inc = v;  // inclusive scan within the warp
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+      const int t = __shfl_up_sync(0xffffffffu, inc, off);
+      if (lane >= off) inc += t;
+    }
+    if (lane == 31) warp_sums[warp] = inc;
+    __syncthreads();
+    int before = carry;
+    for (int w = 0; w < warp; ++w) before += warp_sums[w];
+    if (i < n_tiles) row[i] = before + inc - v;
+    __syncthreads();
+    if (threadIdx.x == RS_THREADS - 1) carry = before + inc;
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) totals[blockIdx.x] = carry;
+}
+
+__global__ void __launch_bounds__(RS_THREADS)
+radix_scatter_kernel(const int* __restrict__ keys, const int* __restrict__ vals, int* __restrict__ keys_out,
+                     int* __restrict__ vals_out, long long n, int shift, const int* __restrict__ starts,
+                     const int* __restrict__ totals, int n_tiles) {
+  __shared__ int wc[RS_WARPS][RS_DIGITS];  // counts, then the running output position of each (warp, digit)
+  __shared__ int dbase[RS_DIGITS];         // keys with a smaller digit, over all tiles
+  __shared__ int wsum[RS_WARPS];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  static_assert(RS_DIGITS == RS_THREADS, "one thread per digit");
+  {
+    const int v = totals[threadIdx.x];
+    int inc = v;
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+      const int t = __shfl_up_sync(0xffffffffu, inc, off);
+      if (lane >= off) inc += t;
+    }
+    if (lane == 31) wsum[warp] = inc;
+    __syncthreads();
+    int before = 0;
+    for (int w = 0; w < warp; ++w) before += wsum[w];
+    dbase[threadIdx.x] = before + inc - v;
+  }
+  rs_count_tile(keys, n, shift, wc);
+  for (int d = threadIdx.x; d < RS_DIGITS; d += RS_THREADS) {
+    int run = dbase[d] + starts[(size_t)d * n_tiles + blockIdx.x];
+#pragma unroll
+    for (int w = 0; w < RS_WARPS; ++w) {
+      const int c = wc[w][d];
+      wc[w][d] = run;
+      run += c;
+    }
+  }
+  __syncthreads();
+  const long long base = (long long)blockIdx.x * RS_TILE + (long long)warp * RS_PER_WARP;
+  for (int r = 0; r < RS_PER_WARP / 32; ++r) {
+    const long long i = base + r * 32 + lane;
+    const bool in = i < n;
+    const unsigned alive = __ballot_sync(0xffffffffu, in);
+    if (in) {
+      const int key = keys[i];
+      const int d = (key >> shift) & (RS_DIGITS - 1);
+      const unsigned peers = __match_any_sync(alive, d);
+      const int leader = __ffs(peers) - 1;
+      int first = 0;
+      if (lane == leader) {
+        first = wc[warp][d];
+        wc[warp][d] = first + __popc(peers);
+      }
+      first = __shfl_sync(peers, first, leader);
+      const int pos = first + __popc(peers & ((1u << lane) - 1u));  // earlier lanes hold earlier keys
+      keys_out[pos] = key;
+      vals_out[pos] = vals[i];
+    }
+    __syncwarp();
+  }
+}
+
 template <int VPL>  // 16-byte pieces of a row per lane: dim <= VPL * 128
 __global__ void __launch_bounds__(128)
 weighted_value_bwd_sorted_kernel(const int* __restrict__ keys, const int* __restrict__ events,
@@ -1065,19 +1195,32 @@ int hl_memory_weighted_value_backward(hl_ctx* ctx, const int64_t* indices, const
     // row order (see weighted_value_bwd_sorted_kernel).  Scratch: keys and events in and out, and the sort's own space.
     int end_bit = 1;
     while ((1ll << end_bit) <= rows) ++end_bit;  // the sentinel key `rows` must sort last
-    size_t sort_bytes = 0;
-    HL_CUDA(cub::DeviceRadixSort::SortPairs(nullptr, sort_bytes, (const int*)nullptr, (int*)nullptr, (const int*)nullptr,
-                                            (int*)nullptr, (int)n, 0, end_bit, ctx->stream));
+    const int n_tiles = (int)ceil_div_ll(n, RS_TILE);
     const size_t arr = ((size_t)n * sizeof(int) + 255) & ~size_t(255);
-    rc = ensure_workspace(ctx, 4 * arr + sort_bytes);
+    const size_t hist_bytes = ((size_t)RS_DIGITS * (n_tiles + 1) * sizeof(int) + 255) & ~size_t(255);  // rows, then totals
+    rc = ensure_workspace(ctx, 4 * arr + hist_bytes);
     if (rc != HL_OK) return rc;
     uint8_t* ws = reinterpret_cast<uint8_t*>(ctx->workspace);
-    int *keys_in = reinterpret_cast<int*>(ws), *ev_in = reinterpret_cast<int*>(ws + arr);
-    int *keys = reinterpret_cast<int*>(ws + 2 * arr), *ev = reinterpret_cast<int*>(ws + 3 * arr);
-    value_event_keys_kernel<<<(unsigned)ceil_div_ll(n, 256), 256, 0, ctx->stream>>>(indices, n, rows, keys_in, ev_in, grad_weights,
+    int *keys_a = reinterpret_cast<int*>(ws), *ev_a = reinterpret_cast<int*>(ws + arr);
+    int *keys_b = reinterpret_cast<int*>(ws + 2 * arr), *ev_b = reinterpret_cast<int*>(ws + 3 * arr);
+    int* hist = reinterpret_cast<int*>(ws + 4 * arr);
+    value_event_keys_kernel<<<(unsigned)ceil_div_ll(n, 256), 256, 0, ctx->stream>>>(indices, n, rows, keys_a, ev_a, grad_weights,
                                                                                      ctx->status_dev);
     HL_LAUNCH_CHECK("value_event_keys_kernel");
-    HL_CUDA(cub::DeviceRadixSort::SortPairs(ws + 4 * arr, sort_bytes, keys_in, keys, ev_in, ev, (int)n, 0, end_bit, ctx->stream));
+    int passes = 0;
+    for (int shift = 0; shift < end_bit; shift += RS_BITS, ++passes) {
+      radix_hist_kernel<<<n_tiles, RS_THREADS, 0, ctx->stream>>>(keys_a, n, shift, hist, n_tiles);
+      HL_LAUNCH_CHECK("radix_hist_kernel");
+      int* totals = hist + (size_t)RS_DIGITS * n_tiles;
+      radix_scan_rows_kernel<<<RS_DIGITS, RS_THREADS, 0, ctx->stream>>>(hist, n_tiles, totals);
+      HL_LAUNCH_CHECK("radix_scan_rows_kernel");
+      radix_scatter_kernel<<<n_tiles, RS_THREADS, 0, ctx->stream>>>(keys_a, ev_a, keys_b, ev_b, n, shift, hist, totals, n_tiles);
+      HL_LAUNCH_CHECK("radix_scatter_kernel");
+      std::swap(keys_a, keys_b);
+      std::swap(ev_a, ev_b);
+    }
+    const int *keys = keys_a, *ev = ev_a;  // the last pass's output
+    count_launch(ctx, 3 * passes);
     const unsigned blocks = (unsigned)ceil_div_ll(ceil_div_ll(n, 32), 4);
     if (dim <= 512)
       weighted_value_bwd_sorted_kernel<4><<<blocks, 128, 0, ctx->stream>>>(keys, ev, weights, values, grad_out, grad_weights,
@@ -1086,7 +1229,7 @@ int hl_memory_weighted_value_backward(hl_ctx* ctx, const int64_t* indices, const
       weighted_value_bwd_sorted_kernel<8><<<blocks, 128, 0, ctx->stream>>>(keys, ev, weights, values, grad_out, grad_weights,
                                                                            grad_values, n, top_k, rows, dim);
     HL_LAUNCH_CHECK("weighted_value_bwd_sorted_kernel");
-    count_launch(ctx, 3);
+    count_launch(ctx, 2);
     return HL_OK;
   }
   weighted_value_bwd_kernel<<<ceil_div(tokens, 4), 128, 0, ctx->stream>>>(indices, weights, values, grad_out, grad_weights,

@@ -248,3 +248,28 @@ def test_weighted_value_backward_in_row_order_matches_a_host_sum(tokens, top_k, 
     assert np.abs(host(dv) - want_dv).max() <= 2e-6 * scale * np.sqrt(tokens * top_k / max(np.unique(idx).size, 1)) + 1e-5
     untouched = np.ones(rows, bool); untouched[np.unique(idx)] = False
     assert not np.any(host(dv)[untouched])
+
+
+def test_row_ordered_value_backward_reports_a_bad_index_and_zeroes_its_weight_gradient():
+    """An index past the table in the row-ordered path: the event is left out of the row sums, its weight gradient is
+    written as zero (not left as stale scratch), and the next sync reports the status word; nothing faults."""
+    from heirloom_b200 import cuda
+    from heirloom_b200._lib import HeirloomError
+    c = ctx()
+    rng = np.random.default_rng(77)
+    tokens, top_k, rows, dim = 2048, 32, 500, 64
+    idx = rng.integers(0, rows, (tokens, top_k)).astype(np.int64)
+    idx[5, 3], idx[100, 0] = rows, -1
+    w = rng.standard_normal((tokens, top_k)).astype(np.float32)
+    vals = rng.standard_normal((rows, dim)).astype(np.float32)
+    go = rng.standard_normal((tokens, dim)).astype(np.float32)
+    c.sync()
+    dw, dv = cuda.memory_weighted_value_backward(c, dev(idx, I64), dev(w), dev(vals), dev(go))
+    with pytest.raises(HeirloomError, match="out-of-range index"):
+        c.sync()
+    c.sync()
+    got = dw.cpu().numpy()
+    assert got[5, 3] == 0.0 and got[100, 0] == 0.0
+    good = np.ones_like(idx, bool); good[5, 3] = good[100, 0] = False
+    want_dw = np.einsum("td,tkd->tk", go.astype(np.float64), vals[np.clip(idx, 0, rows - 1)].astype(np.float64))
+    assert np.allclose(got[good], want_dw[good], rtol=1e-5, atol=1e-5)

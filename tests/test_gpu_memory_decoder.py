@@ -104,7 +104,7 @@ def test_amp_route_tracks_the_oracle_and_routes_almost_identically():
         cls = ("tables" if name.startswith("shared_memory") else "memory projections" if "memory" in name
                else "large" if got.size >= 1024 else "small")
         measured[cls] = max(measured.get(cls, 0.0), float(bad.mean()))
-        limit = {"tables": 0.30, "memory projections": 0.10, "large": 0.01, "small": 0.07}[cls]
+        limit = {"tables": 0.30, "memory projections": 0.25, "large": 0.01, "small": 0.07}[cls]
         if bad.mean() > limit:
             report[name] = float(bad.mean())
     print("amp memory model, worst fraction of elements outside 2e-2 after 5 steps, by class:", measured)
