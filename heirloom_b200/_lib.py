@@ -44,7 +44,7 @@ class GemmDesc(Structure):
     _fields_ = [("m", c_int), ("n", c_int), ("k", c_int), ("a_layout", c_int), ("b_layout", c_int),
                 ("lda", c_longlong), ("ldb", c_longlong), ("ldc", c_longlong), ("epilogue", c_int),
                 ("out_dtype", c_int), ("split_k", c_int), ("ld_aux_in", c_longlong), ("ld_aux_out", c_longlong),
-                ("a_k_period", c_int)]
+                ("a_k_period", c_int), ("b_k_period", c_int)]
 
 
 _lib = None

@@ -372,9 +372,13 @@ int hl_cast(hl_ctx* ctx, const void* src, int src_dtype, void* dst, int dst_dtyp
 // One f32 value as a sum of bf16 pieces: hi = bf16(x), mid = bf16(x - hi), lo = bf16(x - hi - mid).  The
 // differences are exact in f32, so hi + mid + lo == x whenever the three 8-bit mantissas reach the last bit of x.
 static __global__ void split_bf16_kernel(const float* __restrict__ src, __nv_bfloat16* __restrict__ dst, long long rows, int cols,
-                                  int mode) {
+                                  int mode_bits) {
+  const int mode = mode_bits & 3;
+  const bool stacked = (mode_bits & HL_SPLIT_STACK_ROWS) != 0;
   const int pieces = mode == HL_SPLIT_HI_LO ? 2 : 3;
   const long long n = rows * cols;
+  const long long piece_stride = stacked ? n : cols;            // distance between the pieces of one element
+  const long long ld = stacked ? cols : (long long)pieces * cols;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
     const long long r = i / cols;
     const int c = (int)(i - r * cols);
@@ -383,18 +387,18 @@ static __global__ void split_bf16_kernel(const float* __restrict__ src, __nv_bfl
     const float r1 = x - __bfloat162float(hi);
     const __nv_bfloat16 mid = __float2bfloat16_rn(r1);
     const __nv_bfloat16 lo = __float2bfloat16_rn(r1 - __bfloat162float(mid));
-    __nv_bfloat16* out = dst + r * (long long)pieces * cols + c;
+    __nv_bfloat16* out = dst + r * ld + c;
     out[0] = hi;
-    if (mode == HL_SPLIT_HI_MID_LO) { out[cols] = mid; out[2 * cols] = lo; }
-    else if (mode == HL_SPLIT_HI_HI_LO) { out[cols] = hi; out[2 * cols] = mid; }
-    else out[cols] = mid;
+    if (mode == HL_SPLIT_HI_MID_LO) { out[piece_stride] = mid; out[2 * piece_stride] = lo; }
+    else if (mode == HL_SPLIT_HI_HI_LO) { out[piece_stride] = hi; out[2 * piece_stride] = mid; }
+    else out[piece_stride] = mid;
   }
 }
 
 int hl_split_bf16_f32(hl_ctx* ctx, const float* src, void* dst, long long rows, int cols, int mode) {
   HL_REQUIRE(ctx && src && dst, "hl_split_bf16_f32: null argument");
   HL_REQUIRE(rows > 0 && cols > 0, "hl_split_bf16_f32: requires non-zero rows/cols");
-  HL_REQUIRE(mode == HL_SPLIT_HI_MID_LO || mode == HL_SPLIT_HI_HI_LO || mode == HL_SPLIT_HI_LO, "hl_split_bf16_f32: unknown mode");
+  HL_REQUIRE((mode & ~(3 | HL_SPLIT_STACK_ROWS)) == 0 && (mode & 3) != 3, "hl_split_bf16_f32: unknown mode");
   split_bf16_kernel<<<ew_grid(ctx, (size_t)rows * cols), EW_THREADS, 0, ctx->stream>>>(src, (__nv_bfloat16*)dst, rows, cols, mode);
   HL_LAUNCH_CHECK("split_bf16_kernel");
   count_launch(ctx);

@@ -55,6 +55,7 @@ struct GemmParams {
   int dp_tiles, sk_tiles;   // whole-wave tiles, then tiles whose k blocks are dealt out evenly
   int panel_w;              // tile columns per panel of the tile order
   int a_kb_wrap;            // > 0: A holds this many k blocks and is read again from its start after them
+  int b_kb_wrap;            // the same for B
   unsigned long long wait_limit_ns;  // bound of every pipeline wait
   int skip_kblock;          // test hook: the producer leaves out this k block of its first tile (-1: none)
   float* sk_slots;          // [grid][BM][BN] raw accumulators of unfinished tile parts
@@ -216,12 +217,13 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
           } else {
             tc05::tma_load_2d(sa, &map_a, &tail->full[stage], ka * BK, m_tile * BM);
           }
+          const int kbb = p.b_kb_wrap > 0 ? kb % p.b_kb_wrap : kb;
           if (B_MN) {
 #pragma unroll
             for (int j = 0; j < BN / 64; ++j)
-              tc05::tma_load_2d(sb + j * (BK * 128), &map_b, &tail->full[stage], n_tile * BN + j * 64, kb * BK);
+              tc05::tma_load_2d(sb + j * (BK * 128), &map_b, &tail->full[stage], n_tile * BN + j * 64, kbb * BK);
           } else {
-            tc05::tma_load_2d(sb, &map_b, &tail->full[stage], kb * BK, n_tile * BN);
+            tc05::tma_load_2d(sb, &map_b, &tail->full[stage], kbb * BK, n_tile * BN);
           }
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
@@ -583,8 +585,11 @@ int gemm_bf16_run(hl_ctx* ctx, const hl_gemm_desc* d, const void* a, const void*
   const bool a_mn = d->a_layout == HL_MN_MAJOR, b_mn = d->b_layout == HL_MN_MAJOR;
   HL_REQUIRE(d->a_k_period >= 0 && d->a_k_period % BK == 0 && d->a_k_period <= d->k,
              "hl_gemm_bf16: a_k_period must be a multiple of 64 and at most k");
+  HL_REQUIRE(d->b_k_period >= 0 && d->b_k_period % BK == 0 && d->b_k_period <= d->k,
+             "hl_gemm_bf16: b_k_period must be a multiple of 64 and at most k");
   const int a_k = d->a_k_period > 0 ? d->a_k_period : d->k;  // contraction extent that A really holds
-  HL_REQUIRE(d->lda >= (a_mn ? d->m : a_k) && d->ldb >= (b_mn ? d->n : d->k) && d->ldc >= d->n,
+  const int b_k = d->b_k_period > 0 ? d->b_k_period : d->k;
+  HL_REQUIRE(d->lda >= (a_mn ? d->m : a_k) && d->ldb >= (b_mn ? d->n : b_k) && d->ldc >= d->n,
              "hl_gemm_bf16: leading dimension smaller than the row length");
   const long long ld_aux_in = d->ld_aux_in > 0 ? d->ld_aux_in : d->ldc;
   const long long ld_aux_out = d->ld_aux_out > 0 ? d->ld_aux_out : d->ldc;
@@ -615,6 +620,7 @@ int gemm_bf16_run(hl_ctx* ctx, const hl_gemm_desc* d, const void* a, const void*
   // An A operand that stays in L2 anyway keeps the plain order (one tile column after the other);
   // a larger one is walked in panels of up to eight tile columns so that it streams from DRAM once.
   p.a_kb_wrap = d->a_k_period > 0 ? d->a_k_period / BK : 0;
+  p.b_kb_wrap = d->b_k_period > 0 ? d->b_k_period / BK : 0;
   p.wait_limit_ns = ctx->wait_limit_ns ? ctx->wait_limit_ns : tc05::kWaitLimitNs;
   p.skip_kblock = ctx->gemm_skip_kblock;
   p.panel_w = (size_t)d->m * (size_t)d->k * 2 <= (size_t(32) << 20) ? 1 : std::min(p.n_tiles, 8);
@@ -654,8 +660,8 @@ int gemm_bf16_run(hl_ctx* ctx, const hl_gemm_desc* d, const void* a, const void*
   if (a_mn) rc = make_tensor_map_bf16_2d(&ma, a, (uint64_t)d->m, (uint64_t)a_k, (uint64_t)d->lda, 64, BK);
   else      rc = make_tensor_map_bf16_2d(&ma, a, (uint64_t)a_k, (uint64_t)d->m, (uint64_t)d->lda, BK, BM);
   if (rc != HL_OK) return rc;
-  if (b_mn) rc = make_tensor_map_bf16_2d(&mb, b, (uint64_t)d->n, (uint64_t)d->k, (uint64_t)d->ldb, 64, BK);
-  else      rc = make_tensor_map_bf16_2d(&mb, b, (uint64_t)d->k, (uint64_t)d->n, (uint64_t)d->ldb, BK, BN);
+  if (b_mn) rc = make_tensor_map_bf16_2d(&mb, b, (uint64_t)d->n, (uint64_t)b_k, (uint64_t)d->ldb, 64, BK);
+  else      rc = make_tensor_map_bf16_2d(&mb, b, (uint64_t)b_k, (uint64_t)d->n, (uint64_t)d->ldb, BK, BN);
   if (rc != HL_OK) return rc;
   if (p.partial_out) {
     const uint64_t dims[3] = {(uint64_t)d->n, (uint64_t)d->m, (uint64_t)splits};

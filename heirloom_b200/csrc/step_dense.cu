@@ -119,6 +119,10 @@ struct hl_decoder {
   float *m_ls = nullptr, *m_rs = nullptr, *m_scores = nullptr, *m_dmv = nullptr, *m_dweighted = nullptr, *m_dgate = nullptr,
         *m_dgpre = nullptr, *m_dw = nullptr, *m_dscores = nullptr, *m_dq = nullptr, *m_dc2 = nullptr;
   __nv_bfloat16 *m_dgpre_b = nullptr, *m_dq_b = nullptr;
+  // amp route, backward of the three memory projections at f32 accuracy: bf16 pieces of the f32 operands, side by
+  // side along the columns where the contraction runs along a row, one below the other where it runs down the rows
+  __nv_bfloat16 *p_dx_side = nullptr, *p_dx_rows = nullptr, *p_mv_rows = nullptr, *p_dg_side = nullptr, *p_dg_rows = nullptr,
+                *p_dq_side = nullptr, *p_dq_rows = nullptr, *p_wout_rows = nullptr, *p_wg_rows = nullptr, *p_wq_rows = nullptr;
   unsigned char* m_row_flags = nullptr;
   unsigned char *smft_value_mask = nullptr, *smft_left_mask = nullptr, *smft_right_mask = nullptr;  // [slots], [side], [side]
   bool smft_on = false;  // the sparse-rows step filters its rows through the three masks
@@ -293,6 +297,18 @@ void plan_memory_buffers(hl_decoder* m, uint8_t*& cur) {
   m->m_dc2 = carve<float>(cur, N * d);
   m->m_dgpre_b = carve<__nv_bfloat16>(cur, N * vd);
   m->m_dq_b = carve<__nv_bfloat16>(cur, N * kd);
+  if (m->cfg.precision == HL_PRECISION_AMP_BF16) {
+    m->p_dx_side = carve<__nv_bfloat16>(cur, N * 2 * d);
+    m->p_dx_rows = carve<__nv_bfloat16>(cur, 2 * N * d);
+    m->p_mv_rows = carve<__nv_bfloat16>(cur, 3 * N * vd);
+    m->p_dg_side = carve<__nv_bfloat16>(cur, N * 2 * vd);
+    m->p_dg_rows = carve<__nv_bfloat16>(cur, 3 * N * vd);
+    m->p_dq_side = carve<__nv_bfloat16>(cur, N * 2 * kd);
+    m->p_dq_rows = carve<__nv_bfloat16>(cur, 3 * N * kd);
+    m->p_wout_rows = carve<__nv_bfloat16>(cur, 3 * d * vd);
+    m->p_wg_rows = carve<__nv_bfloat16>(cur, 3 * vd * d);
+    m->p_wq_rows = carve<__nv_bfloat16>(cur, 3 * kd * d);
+  }
   m->m_row_flags = carve<unsigned char>(cur, (size_t)m->mem.slots);
   m->smft_value_mask = carve<unsigned char>(cur, (size_t)m->mem.slots);
   m->smft_left_mask = carve<unsigned char>(cur, (size_t)m->side);
@@ -422,10 +438,12 @@ struct Gemm {
   hl_decoder* m;
   int run(int M, int N, int K, const void* a, long long lda, int al, const void* b, long long ldb, int bl, void* c,
           long long ldc, int out_dtype, int epi = HL_EPI_NONE, const float* bias = nullptr, const void* aux_in = nullptr,
-          long long ld_aux_in = 0, void* aux_out = nullptr, long long ld_aux_out = 0, int a_k_period = 0) const {
+          long long ld_aux_in = 0, void* aux_out = nullptr, long long ld_aux_out = 0, int a_k_period = 0,
+          int b_k_period = 0) const {
     hl_gemm_desc d{};
     d.m = M; d.n = N; d.k = K;
     d.a_k_period = a_k_period;
+    d.b_k_period = b_k_period;
     d.a_layout = al; d.b_layout = bl;
     d.lda = lda; d.ldb = ldb; d.ldc = ldc;
     d.epilogue = epi; d.out_dtype = out_dtype; d.split_k = 0;
@@ -752,20 +770,44 @@ int backward(hl_decoder* m) {
       MemoryActs& ma = m->ma[l];
       const int kd = m->mem.key_dim, vd = m->mem.value_dim;
       const size_t nv = (size_t)N * vd;
-      HL_TRY(g.run(d, vd, N, m->dxb, d, HL_MN_MAJOR, ma.mv_b, 2 * vd, HL_MN_MAJOR, G + o.wout_m, vd, HL_F32));  // hi piece of mv
-      HL_TRY(g.run(N, vd, d, m->dxb, d, HL_K_MAJOR, W + o.wout_m, vd, HL_MN_MAJOR, m->m_dmv, vd, HL_F32));
+      // The reference runs these three projections in f32 also backward (src/memory_transformer.rs:787-789).  Here
+      // every product stays on the tensor cores with its f32 operands as bf16 pieces: hi*hi + lo*hi + hi*lo in one
+      // f32 accumulation (the dropped lo*lo term is 2^-16 relative), or hi + mid + lo (exact) against the block input,
+      // which is bf16-exact.  `side`: pieces along the columns, for operands contracted along their rows' direction;
+      // `rows`: pieces one below the other, for operands contracted down their rows.
+      const int ROWS = HL_SPLIT_STACK_ROWS;
+      const float* dy = dx;  // dL/dy of this block, f32
+      // out_proj: dW = dy^T mv, dmv = dy W
+      HL_TRY(hl_split_bf16_f32(ctx, dy, m->p_dx_rows, N, d, HL_SPLIT_HI_LO | ROWS));
+      HL_TRY(hl_split_bf16_f32(ctx, ma.mv, m->p_mv_rows, N, vd, HL_SPLIT_HI_HI_LO | ROWS));
+      HL_TRY(g.run(d, vd, 3 * N, m->p_dx_rows, d, HL_MN_MAJOR, m->p_mv_rows, vd, HL_MN_MAJOR, G + o.wout_m, vd, HL_F32,
+                   HL_EPI_NONE, nullptr, nullptr, 0, nullptr, 0, 2 * N));
+      HL_TRY(hl_split_bf16_f32(ctx, dy, m->p_dx_side, N, d, HL_SPLIT_HI_LO));
+      HL_TRY(hl_split_bf16_f32(ctx, P + o.wout_m, m->p_wout_rows, d, vd, HL_SPLIT_HI_HI_LO | ROWS));
+      HL_TRY(g.run(N, vd, 3 * d, m->p_dx_side, 2 * d, HL_K_MAJOR, m->p_wout_rows, vd, HL_MN_MAJOR, m->m_dmv, vd, HL_F32,
+                   HL_EPI_NONE, nullptr, nullptr, 0, nullptr, 0, 2 * d));
       HL_TRY(hl_binary_f32(ctx, HL_MUL, m->m_dmv, ma.gate, m->m_dweighted, nv));
       HL_TRY(hl_binary_f32(ctx, HL_MUL, m->m_dmv, ma.weighted, m->m_dgate, nv));
       HL_TRY(hl_gelu_backward(ctx, ma.gpre, m->m_dgate, m->m_dgpre, HL_F32, nv));
-      HL_TRY(hl_cast(ctx, m->m_dgpre, HL_F32, m->m_dgpre_b, HL_BF16, nv));
-      HL_TRY(g.run(vd, d, N, m->m_dgpre_b, vd, HL_MN_MAJOR, a.c, d, HL_MN_MAJOR, G + o.wg_m, d, HL_F32));
+      // gate_proj: dW = dgpre^T c (c is bf16-exact: three exact pieces of dgpre, c read three times), dc = dgpre W
+      HL_TRY(hl_split_bf16_f32(ctx, m->m_dgpre, m->p_dg_rows, N, vd, HL_SPLIT_HI_MID_LO | ROWS));
+      HL_TRY(g.run(vd, d, 3 * N, m->p_dg_rows, vd, HL_MN_MAJOR, a.c, d, HL_MN_MAJOR, G + o.wg_m, d, HL_F32, HL_EPI_NONE,
+                   nullptr, nullptr, 0, nullptr, 0, 0, N));
       HL_TRY(bias_grad_impl(ctx, m->m_dgpre, HL_F32, G + o.bg_m, N, vd, fb));
-      HL_TRY(g.run(N, d, vd, m->m_dgpre_b, vd, HL_K_MAJOR, W + o.wg_m, d, HL_MN_MAJOR, m->dtmp, d, HL_F32));
+      HL_TRY(hl_split_bf16_f32(ctx, m->m_dgpre, m->p_dg_side, N, vd, HL_SPLIT_HI_LO));
+      HL_TRY(hl_split_bf16_f32(ctx, P + o.wg_m, m->p_wg_rows, vd, d, HL_SPLIT_HI_HI_LO | ROWS));
+      HL_TRY(g.run(N, d, 3 * vd, m->p_dg_side, 2 * vd, HL_K_MAJOR, m->p_wg_rows, d, HL_MN_MAJOR, m->dtmp, d, HL_F32,
+                   HL_EPI_NONE, nullptr, nullptr, 0, nullptr, 0, 2 * vd));
       HL_TRY(memory_core_backward(m, l, m->m_dweighted));
-      HL_TRY(hl_cast(ctx, m->m_dq, HL_F32, m->m_dq_b, HL_BF16, (size_t)N * kd));
-      HL_TRY(g.run(kd, d, N, m->m_dq_b, kd, HL_MN_MAJOR, a.c, d, HL_MN_MAJOR, G + o.wq_m, d, HL_F32));
+      // query_proj: dW = dq^T c, dc += dq W
+      HL_TRY(hl_split_bf16_f32(ctx, m->m_dq, m->p_dq_rows, N, kd, HL_SPLIT_HI_MID_LO | ROWS));
+      HL_TRY(g.run(kd, d, 3 * N, m->p_dq_rows, kd, HL_MN_MAJOR, a.c, d, HL_MN_MAJOR, G + o.wq_m, d, HL_F32, HL_EPI_NONE,
+                   nullptr, nullptr, 0, nullptr, 0, 0, N));
       HL_TRY(bias_grad_impl(ctx, m->m_dq, HL_F32, G + o.bq_m, N, kd, fb));
-      HL_TRY(g.run(N, d, kd, m->m_dq_b, kd, HL_K_MAJOR, W + o.wq_m, d, HL_MN_MAJOR, m->m_dc2, d, HL_F32));
+      HL_TRY(hl_split_bf16_f32(ctx, m->m_dq, m->p_dq_side, N, kd, HL_SPLIT_HI_LO));
+      HL_TRY(hl_split_bf16_f32(ctx, P + o.wq_m, m->p_wq_rows, kd, d, HL_SPLIT_HI_HI_LO | ROWS));
+      HL_TRY(g.run(N, d, 3 * kd, m->p_dq_side, 2 * kd, HL_K_MAJOR, m->p_wq_rows, d, HL_MN_MAJOR, m->m_dc2, d, HL_F32,
+                   HL_EPI_NONE, nullptr, nullptr, 0, nullptr, 0, 2 * kd));
       HL_TRY(hl_binary_f32(ctx, HL_ADD, m->dtmp, m->m_dc2, m->dtmp, (size_t)N * d));
     } else {
     // y = r + fc2(gelu(fc1(c)));   dx is dL/dy (f32), dxb its bf16 operand copy
@@ -1103,8 +1145,10 @@ static int decoder_create_impl(hl_ctx* ctx, const hl_decoder_config* cfg, const 
     HL_REQUIRE(cfg->d_model % 8 == 0 && cfg->d_ff % 8 == 0 && cfg->vocab % 8 == 0 && cfg->d_model <= 1024,
                "hl_decoder_create: d_model (<= 1024), d_ff and vocab must be multiples of 8");
     if (mem && mem->n_memory_layers > 0)  // the projections' contraction is read piecewise in whole 64-element blocks
-      HL_REQUIRE(cfg->d_model % 64 == 0 && mem->value_dim % 32 == 0,
-                 "hl_memory_decoder_create: the bf16 route needs d_model to be a multiple of 64 and value_dim of 32");
+      HL_REQUIRE(cfg->d_model % 64 == 0 && mem->value_dim % 32 == 0 && mem->key_dim % 32 == 0 &&
+                     (cfg->batch * cfg->context) % 64 == 0,
+                 "hl_memory_decoder_create: the bf16 route needs d_model and batch*context to be multiples of 64, "
+                 "key_dim and value_dim of 32");
   } else {
     HL_REQUIRE(cfg->d_model % 4 == 0 && cfg->d_model <= 1024,
                "hl_decoder_create: the f32 route needs d_model to be a multiple of 4 and at most 1024");

@@ -323,18 +323,18 @@ def matmul_f32_strided(ctx: Context, a: torch.Tensor, b: torch.Tensor, out: Opti
     return out
 
 
-SPLIT_HI_MID_LO, SPLIT_HI_HI_LO, SPLIT_HI_LO = 0, 1, 2
+SPLIT_HI_MID_LO, SPLIT_HI_HI_LO, SPLIT_HI_LO, SPLIT_STACK_ROWS = 0, 1, 2, 4
 
 
 def gemm_bf16(ctx: Context, a: torch.Tensor, b: torch.Tensor, m: int, n: int, k: int, a_layout=K_MAJOR,
               b_layout=K_MAJOR, epilogue=EPI_NONE, out_dtype=torch.bfloat16, bias=None, aux_in=None,
-              want_aux_out=False, split_k=0, out=None, a_k_period=0):
+              want_aux_out=False, split_k=0, out=None, a_k_period=0, b_k_period=0):
     """C[m,n] = A·B with per-operand storage order; see `hl_gemm_bf16` in the C header."""
     if out is None:
         out = torch.empty(m, n, dtype=out_dtype, device=a.device)
     aux_out = torch.empty(m, n, dtype=torch.bfloat16, device=a.device) if want_aux_out else None
     desc = GemmDesc(m, n, k, a_layout, b_layout, a.stride(0), b.stride(0), out.stride(0), epilogue, _DT[out.dtype],
-                    split_k, aux_in.stride(0) if aux_in is not None else 0, n if want_aux_out else 0, a_k_period)
+                    split_k, aux_in.stride(0) if aux_in is not None else 0, n if want_aux_out else 0, a_k_period, b_k_period)
     check(ctx.lib.hl_gemm_bf16(ctx.handle, byref(desc), _p(a), _p(b), _p(out), _p(bias), _p(aux_in), _p(aux_out)))
     return (out, aux_out) if want_aux_out else out
 

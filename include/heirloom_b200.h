@@ -132,7 +132,9 @@ int hl_cast(hl_ctx* ctx, const void* src, int src_dtype, void* dst, int dst_dtyp
  *   HL_SPLIT_HI_MID_LO  [hi | mid | lo]   exact three-piece form of a weight, against a bf16-exact input
  *   HL_SPLIT_HI_HI_LO   [hi | hi | mid]   weight side of hi*hi + lo*hi + hi*lo
  *   HL_SPLIT_HI_LO      [hi | mid]        input side of the same, read with a_k_period = 2*cols */
-enum { HL_SPLIT_HI_MID_LO = 0, HL_SPLIT_HI_HI_LO = 1, HL_SPLIT_HI_LO = 2 };
+enum { HL_SPLIT_HI_MID_LO = 0, HL_SPLIT_HI_HI_LO = 1, HL_SPLIT_HI_LO = 2,
+       HL_SPLIT_STACK_ROWS = 4 /* or-ed in: the pieces one below the other, dst [pieces*rows, cols], for operands whose
+                                  rows are the contraction index */ };
 int hl_split_bf16_f32(hl_ctx* ctx, const float* src, void* dst, long long rows, int cols, int mode);
 /* tanh-GELU and its gradient (kernels.ptx:4791, :4842; src/tensor.rs:5152-5154,
  * src/tensor/autograd.rs:2891-2897).  dtype in {HL_F32, HL_BF16} applies to x/out/grads. */
@@ -270,6 +272,7 @@ typedef struct {
   int a_k_period; /* 0, or a multiple of 64: A holds only this many contraction elements and is read again
                      from its start after them (B supplies all k), so that one f32 accumulation can take
                      C = A*B1 + A*B2 + ... with B = [B1 | B2 | ...] along the contraction */
+  int b_k_period; /* the same for B */
 } hl_gemm_desc;
 int hl_gemm_bf16(hl_ctx* ctx, const hl_gemm_desc* desc, const void* a, const void* b, void* c,
                  const float* bias, const void* aux_in, void* aux_out);

@@ -316,7 +316,7 @@ pub fn matmul_bf16_tensor_core_rhs_transposed_f32_buffers(lhs_bf16: &CudaBuffer,
     let out = CudaBuffer::uninit_bytes(lhs_bf16.device_ordinal(), m * n, 4)?;
     let desc = HlGemmDesc { m: dim(m, "m")?, n: dim(n, "n")?, k: dim(k, "k")?, a_layout: HL_K_MAJOR, b_layout: HL_K_MAJOR,
                             lda: k as i64, ldb: k as i64, ldc: n as i64, epilogue: HL_EPI_NONE, out_dtype: HL_F32,
-                            split_k: 0, ld_aux_in: 0, ld_aux_out: 0, a_k_period: 0 };
+                            split_k: 0, ld_aux_in: 0, ld_aux_out: 0, a_k_period: 0, b_k_period: 0 };
     check(unsafe {
         hl_gemm_bf16(ctx_for(lhs_bf16.device_ordinal())?, &desc, lhs_bf16.ptr(), rhs_bf16.ptr(), out.ptr(),
                      std::ptr::null(), std::ptr::null(), std::ptr::null_mut())

@@ -143,6 +143,47 @@ def test_gemm_with_a_repeated_operand_reaches_f32_accuracy(m, n, k):
     assert np.abs(host(out) - want).max() <= 6e-5 * np.abs(want).max()
 
 
+def split_bf16_rows(ctx_, x, mode):
+    """The pieces one below the other: `[pieces*rows, cols]`."""
+    from heirloom_b200 import cuda
+    rows, cols = x.shape
+    pieces = 2 if mode == cuda.SPLIT_HI_LO else 3
+    out = torch.empty(pieces * rows, cols, dtype=torch.bfloat16, device="cuda")
+    cuda.check(ctx_.lib.hl_split_bf16_f32(ctx_.handle, cuda._p(x), cuda._p(out), cuda.c_longlong(rows), cuda.c_int(cols),
+                                          cuda.c_int(mode | cuda.SPLIT_STACK_ROWS)))
+    return out
+
+
+def test_weight_gradient_shaped_products_of_f32_operands_reach_f32_accuracy():
+    """dW[p,q] = sum_t dy[t,p] x[t,q]: both operands stored row-per-token, contracted down their rows.  The pieces lie
+    one below the other; x bf16-exact is read three times (b_k_period), or both operands f32 with dy's two pieces read
+    as hi, lo, hi (a_k_period) against x's hi, hi, lo."""
+    from heirloom_b200 import cuda
+    c = ctx()
+    rng = np.random.default_rng(77)
+    t, p, q = 1024, 256, 384
+    dy = (rng.standard_normal((t, p)) * np.exp(rng.uniform(-3, 3, (t, 1)))).astype(np.float32)
+    xb = ho.bf16_round(rng.standard_normal((t, q)))
+    dy3 = split_bf16_rows(c, dev(dy), cuda.SPLIT_HI_MID_LO)
+    assert np.array_equal(host(dy3)[:t], ho.bf16_round(dy))
+    assert np.array_equal((host(dy3)[:t] + host(dy3)[t:2 * t] + host(dy3)[2 * t:]).astype(np.float32), dy)
+    out = cuda.gemm_bf16(c, dy3, dev(xb, torch.bfloat16), p, q, 3 * t, a_layout=cuda.MN_MAJOR, b_layout=cuda.MN_MAJOR,
+                         out_dtype=torch.float32, b_k_period=t)
+    want = dy.astype(np.float64).T @ xb
+    assert np.abs(host(out) - want).max() <= 2e-6 * np.abs(want).max()
+    x = rng.standard_normal((t, q)).astype(np.float32)
+    dy2 = split_bf16_rows(c, dev(dy), cuda.SPLIT_HI_LO)
+    x3 = split_bf16_rows(c, dev(x), cuda.SPLIT_HI_HI_LO)
+    out = cuda.gemm_bf16(c, dy2, x3, p, q, 3 * t, a_layout=cuda.MN_MAJOR, b_layout=cuda.MN_MAJOR,
+                         out_dtype=torch.float32, a_k_period=2 * t)
+    want = dy.astype(np.float64).T @ x.astype(np.float64)
+    assert np.abs(host(out) - want).max() <= 6e-5 * np.abs(want).max()
+    # the split-K route (k blocks dealt over CTAs) wraps the same way
+    out2 = cuda.gemm_bf16(c, dy2, x3, p, q, 3 * t, a_layout=cuda.MN_MAJOR, b_layout=cuda.MN_MAJOR,
+                          out_dtype=torch.float32, a_k_period=2 * t, split_k=4)
+    assert np.abs(host(out2) - want).max() <= 6e-5 * np.abs(want).max()
+
+
 def test_an_expired_pipeline_wait_ends_the_kernel_with_a_status_and_leaves_the_context_usable():
     """Failure detection without a fault: the producer is told to leave one k block of the first tile out, so the MMA
     issuer's wait for that stage can never be satisfied; with the bound set to 200 microseconds the wait gives up, every
