@@ -19,7 +19,8 @@ class DeviceInfo(Structure):
 
 class Counters(Structure):
     _fields_ = [(n, c_uint64) for n in ("launches", "gemm_tcgen05_launches", "attention_launches", "h2d_bytes",
-                                        "d2h_bytes", "allocations", "allocated_bytes", "nccl_calls", "nccl_bytes")]
+                                        "d2h_bytes", "allocations", "allocated_bytes", "nccl_calls", "nccl_bytes",
+                                        "gemm_pair_launches")]
 
 
 class Profile(Structure):

@@ -51,10 +51,13 @@ def build(verbose: bool = False) -> Path:
         objs = list(pool.map(lambda s: _compile(s, verbose), sources))
     if LIB.exists() and all(LIB.stat().st_mtime >= o.stat().st_mtime for o in objs):
         return LIB
-    cmd = [NVCC, "-shared", "-o", str(LIB), *map(str, objs), "-lcudart", "-ldl"]
+    # linked under another name and renamed, so that a process that opens the library never sees half a file
+    tmp = LIB.with_suffix(".so.linking")
+    cmd = [NVCC, "-shared", "-o", str(tmp), *map(str, objs), "-lcudart", "-ldl"]
     res = subprocess.run(cmd, capture_output=True, text=True)
     if res.returncode != 0:
         raise RuntimeError(f"link failed:\n{res.stdout}\n{res.stderr}")
+    os.replace(tmp, LIB)
     return LIB
 
 

@@ -47,7 +47,7 @@ enum StatusSlot : int {
 
 struct Counters {
   unsigned long long launches, gemm_tcgen05_launches, attention_launches, h2d_bytes, d2h_bytes,
-      allocations, allocated_bytes, nccl_calls, nccl_bytes;
+      allocations, allocated_bytes, nccl_calls, nccl_bytes, gemm_pair_launches;
 };
 
 }  // namespace hl

@@ -266,6 +266,7 @@ int hl_counters_get(hl_ctx* ctx, hl_counters_t* out) {
   out->allocated_bytes = ctx->counters.allocated_bytes;
   out->nccl_calls = ctx->counters.nccl_calls;
   out->nccl_bytes = ctx->counters.nccl_bytes;
+  out->gemm_pair_launches = ctx->counters.gemm_pair_launches;
   return HL_OK;
 }
 

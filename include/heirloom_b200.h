@@ -67,7 +67,8 @@ int hl_device_info(hl_ctx* ctx, hl_device_info_t* out);
 /* Counters (reference: cuda_runtime_counters / tensor_core_counters, cuda.rs:1589-2014). */
 typedef struct {
   uint64_t launches, gemm_tcgen05_launches, attention_launches, h2d_bytes, d2h_bytes, allocations,
-      allocated_bytes, nccl_calls, nccl_bytes;
+      allocated_bytes, nccl_calls, nccl_bytes,
+      gemm_pair_launches; /* those of gemm_tcgen05_launches that ran on pairs of CTAs (256-row tiles) */
 } hl_counters_t;
 int hl_counters_get(hl_ctx* ctx, hl_counters_t* out);
 int hl_counters_reset(hl_ctx* ctx);

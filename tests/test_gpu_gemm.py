@@ -206,3 +206,53 @@ def test_an_expired_pipeline_wait_ends_the_kernel_with_a_status_and_leaves_the_c
     c.sync()  # the status was reported once and cleared
     out = cuda.gemm_bf16(c, da, db, m, n, k, out_dtype=torch.float32)
     assert_close("gemm after an expired wait", host(out), a @ b, atol=2e-3, rtol=1e-5)
+
+
+PAIR_SCRIPT = r"""
+import numpy as np, torch
+from oracle import heirloom_oracle as ho
+from tests.gpu_util import ctx, dev, host
+from heirloom_b200 import cuda
+c = ctx()
+rng = np.random.default_rng(5)
+for (m, n, k, a_mn, b_mn) in [(256, 256, 64, False, False), (1000, 264, 1032, False, False), (384, 768, 768, True, True),
+                              (2048, 512, 320, False, True), (640, 1024, 192, True, False)]:
+    a = ho.bf16_round(rng.standard_normal((m, k))); b = ho.bf16_round(rng.standard_normal((k, n)))
+    a_store = a.T.copy() if a_mn else a
+    b_store = b.copy() if b_mn else b.T.copy()
+    out = cuda.gemm_bf16(c, dev(a_store, torch.bfloat16), dev(b_store, torch.bfloat16), m, n, k,
+                         cuda.MN_MAJOR if a_mn else cuda.K_MAJOR, cuda.MN_MAJOR if b_mn else cuda.K_MAJOR,
+                         out_dtype=torch.float32, split_k=1)  # whole tiles: the only work split that runs on pairs
+    want = a.astype(np.float64) @ b.astype(np.float64)
+    assert np.abs(host(out) - want).max() <= 2e-6 * np.abs(want).max() * np.sqrt(k), (m, n, k)
+# bias + residual epilogue into bf16, ragged rows
+m, n, k = 1500, 768, 768
+a = ho.bf16_round(rng.standard_normal((m, k))); w = ho.bf16_round(rng.standard_normal((n, k)) * 0.05)
+bias = rng.standard_normal(n).astype(np.float32); res = ho.bf16_round(rng.standard_normal((m, n)))
+out = cuda.gemm_bf16(c, dev(a, torch.bfloat16), dev(w, torch.bfloat16), m, n, k, epilogue=cuda.EPI_BIAS_RESIDUAL,
+                     bias=dev(bias), aux_in=dev(res, torch.bfloat16))
+want = ho.bf16_round(res + ho.bf16_round(a.astype(np.float64) @ w.T.astype(np.float64) + bias))
+assert np.abs(host(out) - want).max() <= 2.0 ** -7 * np.abs(want).max()
+# a weight-gradient shape: few tiles, the contraction in four equal splits summed by the second kernel
+m, n, k = 512, 768, 4096
+a = ho.bf16_round(rng.standard_normal((k, m))); b = ho.bf16_round(rng.standard_normal((k, n)))
+out = cuda.gemm_bf16(c, dev(a, torch.bfloat16), dev(b, torch.bfloat16), m, n, k, cuda.MN_MAJOR, cuda.MN_MAJOR,
+                     out_dtype=torch.float32, split_k=4)
+want = a.T.astype(np.float64) @ b.astype(np.float64)
+assert np.abs(host(out) - want).max() <= 2e-6 * np.abs(want).max() * np.sqrt(k)
+c.sync()
+n_pair, n_all = c.counters().gemm_pair_launches, c.counters().gemm_tcgen05_launches
+assert n_pair == n_all == 7, (n_pair, n_all)
+print("pairs ok")
+"""
+
+
+def test_gemm_on_cta_pairs_matches_in_a_process_that_opts_in():
+    """HEIRLOOM_GEMM_PAIRS=1 (read once per process) runs whole-tile products on clusters of two CTAs: 256-row tiles,
+    one MMA issuer for both SMs, each CTA staging half of B.  Same results, all operand majors, ragged edges."""
+    import os, subprocess, sys
+    from pathlib import Path
+    env = dict(os.environ, HEIRLOOM_GEMM_PAIRS="1")
+    res = subprocess.run([sys.executable, "-c", PAIR_SCRIPT], env=env, cwd=str(Path(__file__).resolve().parents[1]),
+                         capture_output=True, text=True, timeout=300)
+    assert res.returncode == 0 and "pairs ok" in res.stdout, res.stdout[-2000:] + res.stderr[-2000:]

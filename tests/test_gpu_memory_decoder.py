@@ -102,14 +102,14 @@ def test_amp_route_tracks_the_oracle_and_routes_almost_identically():
         # size, so a handful of sign flips already is several per cent of their elements.
         # The shared tables are where the last routing differences show: a slot chosen on one side only gives its
         # value row and half-key rows a gradient there and plain decay here, and AdamW turns any gradient into a step
-        # of about lr; over five steps of two blocks about one row in four meets at least one such event.
+        # of about lr; with 1 % of the slots differing, 0.2 % of the table elements end outside the gate.
         # The memory projections' gradients are 1e-5 of the dense ones at this initialisation (the looked-up values are
         # small) and every token with one differing slot moves them by several per cent of their scale: measured 8-19 %
         # of the tensor scale at the worst element, 1-2 % on average, with the projections themselves f32-accurate.
         cls = ("tables" if name.startswith("shared_memory") else "memory projections" if "memory" in name
                else "large" if got.size >= 1024 else "small")
         measured[cls] = max(measured.get(cls, 0.0), float(bad.mean()))
-        limit = {"tables": 0.30, "memory projections": 0.25, "large": 0.01, "small": 0.07}[cls]
+        limit = {"tables": 0.03, "memory projections": 0.25, "large": 0.01, "small": 0.07}[cls]
         if bad.mean() > limit:
             report[name] = float(bad.mean())
     print("amp memory model, worst fraction of elements outside 2e-2 after 5 steps, by class:", measured)
