@@ -32,8 +32,23 @@ MICRO_BATCH = 16
 METRIC = "train tokens/s (GPT-124M-shaped bf16 step)"
 DATASHEET_BF16_TFLOPS = 2250.0
 # dram__bytes_read.sum + dram__bytes_write.sum per GEMM launch, averaged over the launches of two training steps
-# in a one-pass ncu launch list of this command (summary kept under profiles/)
+# in a one-pass ncu launch list of this command (summary kept under profiles/), and the first 16 hex digits of the
+# SHA-256 of the GEMM source the capture ran with: a kernel changed since then gets no traffic figure, not a stale one.
 GEMM_DRAM_BYTES_PER_LAUNCH = 155.4e6
+GEMM_SOURCE_AT_CAPTURE = "50bd6e325b6a3bbe"
+
+
+def gemm_traffic():
+    """(bytes per launch or None, note)."""
+    import hashlib
+    src = ROOT / "heirloom_b200" / "csrc" / "gemm_tcgen05.cu"
+    try:
+        now = hashlib.sha256(src.read_bytes()).hexdigest()[:16]
+    except OSError:
+        return None, "GEMM source not found beside the library: capture cannot be matched to it"
+    if now != GEMM_SOURCE_AT_CAPTURE:
+        return None, "gemm_tcgen05.cu changed since the ncu capture (" + GEMM_SOURCE_AT_CAPTURE + " -> " + now + "): re-capture"
+    return GEMM_DRAM_BYTES_PER_LAUNCH, "ncu launch list of this command, profiles/bench_step_launch_list.md"
 
 
 def flops_per_token(cfg) -> float:
@@ -396,7 +411,7 @@ def run_ours(args):
         "gpu_launches": launches * args.steps,
         "roofline": {"bound": "tensor", "kernel": "gemm_bf16_tcgen05_kernel", "achieved": gemm_tflops,
                      "peak": peaks["bf16_sustained"], "unit": "TFLOP/s", "frac": gemm_tflops / peaks["bf16_sustained"],
-                     "traffic": GEMM_DRAM_BYTES_PER_LAUNCH, "peak_source": peaks["source"] + " sustained bf16 (kernel timed inside a long step)",
+                     "traffic": gemm_traffic()[0], "traffic_source": gemm_traffic()[1], "peak_source": peaks["source"] + " sustained bf16 (kernel timed inside a long step)",
                      "launches_per_step": gemm["scopes_per_step"], "ms_per_step": gemm["ms_per_step"]},
         "kernel_breakdown_ms_per_step": {k: round(v["ms_per_step"], 4) for k, v in prof.items()},
         "comm": comm,
