@@ -15,6 +15,12 @@
 // 256 columns.  An epilogue warp moves its 32 rows through two alternating 2 KB swizzled staging
 // tiles and writes them with TMA stores (64-byte row segments, clipped at the tensor edge).
 //
+// Contractions of 2048 and up whose tiles are whole (or equal splits) run on pairs of CTAs instead: a cluster of two
+// neighbouring SMs works on a 256 x 256 tile, the even CTA's MMA warp issues tcgen05.mma.cta_group::2 for both, each CTA
+// stages its own 128 rows of A and 128 of B's 256 columns (six 32 KB stages in the same shared memory) and keeps its 128
+// accumulator rows in its own tensor memory, so each SM reads half as much of B per MMA.  The even CTA's `full` barriers
+// count both CTAs' TMA bytes, its `tmem_empty` barriers both CTAs' epilogue warps; MMA commits arrive in both CTAs.
+//
 // Work split: whole waves of output tiles go one tile per CTA; when the tiles left over would fill
 // only part of a wave, their k blocks are dealt out evenly instead (every CTA gets one contiguous
 // range of k blocks).  The CTA that owns the end of a tile's contraction

@@ -103,6 +103,11 @@ struct hl_decoder {
   std::vector<cudaEvent_t> bucket_done;  // recorded on the collective stream after each bucket's all-reduce
   bool comm_pending = false;             // the compute stream has not yet waited for this step's collectives
   cudaEvent_t comm_done = nullptr;
+  // row-union exchanges: which rows the ranks touched is known long before their gradients are (the token ids when the
+  // step starts, the selected slots when forward ends), so the union and its size are formed then, on the collective
+  // stream, and the host finds the size ready when it queues the exchange itself at the end of backward
+  cudaEvent_t rows_known = nullptr, tok_count_ready = nullptr, val_count_ready = nullptr;
+  bool tok_prepared = false, val_prepared = false;
   // while per-kernel timing is on: events around every wait of the compute stream for the collective stream, so that
   // the time the step spends exposed to the gradient exchange can be read back (hl_decoder_comm_exposed_ms)
   std::vector<cudaEvent_t> wait_begin, wait_end;
@@ -653,7 +658,8 @@ int flush_buckets(hl_decoder* m, size_t done_elems) {
 // Data-parallel exchange of a table gradient of which only some rows are non-zero: every rank marks the rows it
 // touched, the masks are combined with a byte-wise maximum, the union's gradient rows are packed, summed over the
 // ranks and put back (src/bin/heirloom/runtime.rs:4171-4214).  Rows outside the union have zero gradient on every
-// rank.  Runs on the collective stream after the dense buckets; the host waits once for the row count.
+// rank.  Runs on the collective stream in two halves: the union of the rows when they are known, the exchange of the
+// gradient rows after the dense buckets; the host reads the union's size between the two, long after it was written.
 struct RowExchange {
   float* grad;            // [rows, dim] in the gradient arena
   int rows, dim;
@@ -666,13 +672,25 @@ struct RowExchange {
   size_t max_events;      // rows all ranks together can touch at most
 };
 
-int exchange_rows(hl_decoder* m, const RowExchange& x, int* union_n) {
+// First half, queued as soon as the touched rows are known: x.flags holds this rank's marks; the union over the ranks, its
+// row list and its size (copied to pinned host memory) follow on the collective stream, `ready` after them.
+int prepare_rows(hl_decoder* m, const RowExchange& x, cudaEvent_t ready) {
   hl_ctx* ctx = m->ctx;
   cudaStream_t cs = ctx->comm_stream;
   HL_TRY(nccl_allreduce_max_u8(ctx, x.flags, (size_t)x.rows, cs));
   HL_TRY(mask_to_indices_on(ctx, cs, x.flags, x.rows, x.union_rows, x.count_dev));
   HL_CUDA(cudaMemcpyAsync(x.count_host, x.count_dev, sizeof(int), cudaMemcpyDeviceToHost, cs));
-  HL_CUDA(cudaStreamSynchronize(cs));
+  HL_CUDA(cudaMemsetAsync(x.flags, 0, (size_t)x.rows, cs));
+  HL_CUDA(cudaEventRecord(ready, cs));
+  return HL_OK;
+}
+
+// Second half, once the gradient rows are final: pack the union's rows, sum them over the ranks, put them back.  The
+// host reads the size here; the device passed `ready` long ago unless the caller queued both halves back to back.
+int finish_rows(hl_decoder* m, const RowExchange& x, cudaEvent_t ready, int* union_n) {
+  hl_ctx* ctx = m->ctx;
+  cudaStream_t cs = ctx->comm_stream;
+  HL_CUDA(cudaEventSynchronize(ready));
   const int n = *x.count_host;
   HL_REQUIRE(n >= 0 && n <= x.rows, "hl_decoder: row union out of range");
   *union_n = n;
@@ -682,7 +700,8 @@ int exchange_rows(hl_decoder* m, const RowExchange& x, int* union_n) {
     if ((size_t)n > *x.packed_cap) {
       const size_t cap = std::max((size_t)n, std::min((size_t)x.rows, x.max_events));
       if (*x.packed) {
-        HL_CUDA(cudaFree(*x.packed));  // the stream was synchronised just above
+        HL_CUDA(cudaStreamSynchronize(cs));  // an earlier step's exchange may still be reading the old buffer
+        HL_CUDA(cudaFree(*x.packed));
         *x.packed = nullptr;
         *x.packed_cap = 0;
       }
@@ -695,40 +714,70 @@ int exchange_rows(hl_decoder* m, const RowExchange& x, int* union_n) {
     HL_TRY(nccl_allreduce_sum_f32(ctx, *x.packed, (size_t)n * x.dim, cs));
     HL_TRY(move_rows_on(ctx, cs, *x.packed, x.union_rows, nullptr, n, x.dim, x.grad, true));
   }
-  HL_CUDA(cudaMemsetAsync(x.flags, 0, (size_t)x.rows, cs));
   return HL_OK;
 }
 
 // The value table: rows = the slots the memory blocks selected.
-int exchange_value_rows(hl_decoder* m) {
+RowExchange value_rows(hl_decoder* m) {
+  const size_t per_layer = (size_t)m->N * m->mem.top_k;
+  return RowExchange{m->grads + m->off_val, m->mem.slots, m->mem.value_dim, m->m_row_flags, m->m_union_rows, m->m_union_count,
+                     m->m_union_count_host, &m->m_packed, &m->packed_rows_cap,
+                     (size_t)nccl_world(m->ctx) * per_layer * (size_t)m->mem.n_memory_layers};
+}
+
+// Queued after forward: the selections of every memory block are on the device.
+int prepare_value_rows(hl_decoder* m) {
   if (!m->has_memory || !nccl_active(m->ctx)) return HL_OK;
   hl_ctx* ctx = m->ctx;
   cudaStream_t cs = ctx->comm_stream;
   const size_t per_layer = (size_t)m->N * m->mem.top_k;
   const int slots = m->mem.slots;
+  HL_CUDA(cudaEventRecord(m->rows_known, ctx->stream));
+  HL_CUDA(cudaStreamWaitEvent(cs, m->rows_known, 0));
   HL_CUDA(cudaMemsetAsync(m->m_row_flags, 0, (size_t)slots, cs));
   for (int l = 0; l < m->cfg.n_layers; ++l)
     if (m->lo[l].is_memory) HL_TRY(mark_rows_on(ctx, cs, m->ma[l].idx, (long long)per_layer, nullptr, m->m_row_flags, slots));
-  const RowExchange x{m->grads + m->off_val, slots, m->mem.value_dim, m->m_row_flags, m->m_union_rows, m->m_union_count,
-                      m->m_union_count_host, &m->m_packed, &m->packed_rows_cap,
-                      (size_t)nccl_world(ctx) * per_layer * (size_t)m->mem.n_memory_layers};
-  return exchange_rows(m, x, &m->union_n);
+  HL_TRY(prepare_rows(m, value_rows(m), m->val_count_ready));
+  m->val_prepared = true;
+  return HL_OK;
+}
+
+int exchange_value_rows(hl_decoder* m) {
+  if (!m->has_memory || !nccl_active(m->ctx)) return HL_OK;
+  if (!m->val_prepared) HL_TRY(prepare_value_rows(m));
+  m->val_prepared = false;
+  return finish_rows(m, value_rows(m), m->val_count_ready, &m->union_n);
 }
 
 // The token-embedding table: rows = the token ids of the batch.  At a Zipf-distributed batch of 16 Ki tokens over a
 // vocabulary of 50 Ki this is a small share of the 154 MB table, and it is the gradient that becomes final last in
 // backward, i.e. the exchange nothing is left to hide behind.
-int exchange_token_rows(hl_decoder* m) {
+RowExchange token_rows(hl_decoder* m) {
+  return RowExchange{m->grads + m->off_tok, m->cfg.vocab, m->cfg.d_model, m->tok_flags, m->tok_union_rows, m->tok_union_count,
+                     m->tok_union_count_host, &m->tok_packed, &m->tok_packed_cap, (size_t)nccl_world(m->ctx) * (size_t)m->N};
+}
+
+// Queued as soon as the step's token ids are on the device.
+int prepare_token_rows(hl_decoder* m) {
   if (!m->sparse_tok_exchange || !nccl_active(m->ctx)) return HL_OK;
   hl_ctx* ctx = m->ctx;
   cudaStream_t cs = ctx->comm_stream;
   const int V = m->cfg.vocab;
+  HL_CUDA(cudaEventRecord(m->rows_known, ctx->stream));
+  HL_CUDA(cudaStreamWaitEvent(cs, m->rows_known, 0));
   HL_CUDA(cudaMemsetAsync(m->tok_flags, 0, (size_t)V, cs));
   HL_TRY(mark_rows_on(ctx, cs, m->tokens, (long long)m->N, nullptr, m->tok_flags, V));
-  const RowExchange x{m->grads + m->off_tok, V, m->cfg.d_model, m->tok_flags, m->tok_union_rows, m->tok_union_count,
-                      m->tok_union_count_host, &m->tok_packed, &m->tok_packed_cap, (size_t)nccl_world(ctx) * (size_t)m->N};
+  HL_TRY(prepare_rows(m, token_rows(m), m->tok_count_ready));
+  m->tok_prepared = true;
+  return HL_OK;
+}
+
+int exchange_token_rows(hl_decoder* m) {
+  if (!m->sparse_tok_exchange || !nccl_active(m->ctx)) return HL_OK;
+  if (!m->tok_prepared) HL_TRY(prepare_token_rows(m));
+  m->tok_prepared = false;
   int n = 0;
-  return exchange_rows(m, x, &n);
+  return finish_rows(m, token_rows(m), m->tok_count_ready, &n);
 }
 
 int backward(hl_decoder* m) {
@@ -1218,6 +1267,10 @@ static int decoder_create_impl(hl_ctx* ctx, const hl_decoder_config* cfg, const 
     e = cudaEventCreateWithFlags(&ev, cudaEventDisableTiming);
     if (e != cudaSuccess) return cleanup(fail_cuda(e, "cudaEventCreate"));
   }
+  for (cudaEvent_t* ev : {&m->rows_known, &m->tok_count_ready, &m->val_count_ready}) {
+    e = cudaEventCreateWithFlags(ev, cudaEventDisableTiming);
+    if (e != cudaSuccess) { *ev = nullptr; return fail_cuda(e, "cudaEventCreate(row exchange)"); }
+  }
   e = cudaEventCreateWithFlags(&m->comm_done, cudaEventDisableTiming);
   if (e != cudaSuccess) return cleanup(fail_cuda(e, "cudaEventCreate"));
   e = cudaStreamSynchronize(ctx->stream);
@@ -1237,6 +1290,7 @@ void hl_decoder_destroy(hl_decoder* m) {
   for (auto ev : m->bucket_ready) if (ev) cudaEventDestroy(ev);
   for (auto ev : m->bucket_done) if (ev) cudaEventDestroy(ev);
   if (m->comm_done) cudaEventDestroy(m->comm_done);
+  for (cudaEvent_t ev : {m->rows_known, m->tok_count_ready, m->val_count_ready}) if (ev) cudaEventDestroy(ev);
   for (auto ev : m->wait_begin) cudaEventDestroy(ev);
   for (auto ev : m->wait_end) cudaEventDestroy(ev);
   adam_plan_destroy(m->plan);
@@ -1342,11 +1396,14 @@ int hl_decoder_forward_backward(hl_decoder* m, const int64_t* tokens_dev, const 
     HL_CUDA(cudaMemcpyAsync(m->tokens, tokens_dev, sizeof(int64_t) * m->N, cudaMemcpyDeviceToDevice, m->ctx->stream));
   if (targets_dev != m->targets)
     HL_CUDA(cudaMemcpyAsync(m->targets, targets_dev, sizeof(int64_t) * m->N, cudaMemcpyDeviceToDevice, m->ctx->stream));
+  HL_TRY(prepare_token_rows(m));  // data parallel: the union of the ranks' token rows forms while forward runs
   if (m->cfg.precision == HL_PRECISION_AMP_BF16) {
     HL_TRY(forward(m));
+    HL_TRY(prepare_value_rows(m));
     HL_TRY(backward(m));
   } else {
     HL_TRY(forward_f32(m));
+    HL_TRY(prepare_value_rows(m));
     HL_TRY(backward_f32(m));
   }
   m->launches_last_step = m->ctx->counters.launches - before;
