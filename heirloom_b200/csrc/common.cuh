@@ -65,6 +65,8 @@ struct hl_ctx {
   int* status_host = nullptr;          // pinned mirror
   void* workspace = nullptr;           // grow-only scratch (split-K partials, reductions)
   size_t workspace_bytes = 0;
+  unsigned* gemm_sched = nullptr;      // counter of the GEMM's dynamic tile order: every processed tile adds one
+  unsigned gemm_sched_base = 0;        // its value once every launch queued so far has finished
   void* gemm_flags = nullptr;          // per-CTA hand-over flags of the GEMM's work split, zeroed once
   hl::Counters counters{};
   void* nccl = nullptr;                // hl::NcclState*

@@ -21,6 +21,9 @@
 // accumulator rows in its own tensor memory, so each SM reads half as much of B per MMA.  The even CTA's `full` barriers
 // count both CTAs' TMA bytes, its `tmem_empty` barriers both CTAs' epilogue warps; MMA commits arrive in both CTAs.
 //
+// Tile order: round-robin over the CTAs; beside another stream's kernels (collectives in flight) the whole tiles of
+// single CTAs are drawn from a counter instead, so a CTA that starts late takes fewer tiles (see `dyn` in the kernel).
+//
 // Work split: whole waves of output tiles go one tile per CTA; when the tiles left over would fill
 // only part of a wave, their k blocks are dealt out evenly instead (every CTA gets one contiguous
 // range of k blocks).  The CTA that owns the end of a tile's contraction
@@ -53,6 +56,7 @@ constexpr int PAIR_B_STAGE_BYTES = B_STAGE_BYTES / 2;
 constexpr int PAIR_STAGE_BYTES = A_STAGE_BYTES + PAIR_B_STAGE_BYTES;
 static_assert(PAIR_STAGES * PAIR_STAGE_BYTES <= STAGES * (A_STAGE_BYTES + B_STAGE_BYTES), "pair stages must fit the same shared memory");
 constexpr int EPI_WARPS = 8;
+constexpr int SCHED_SLOTS = 4;
 constexpr int GEMM_THREADS = (2 + EPI_WARPS) * 32;
 constexpr int TMEM_COLS = 512;
 constexpr int STAGING_BYTES = 4096;  // per epilogue warp: two tiles of 32 rows x 64 bytes
@@ -74,6 +78,8 @@ struct GemmParams {
   float* sk_slots;          // [grid][BM][BN] raw accumulators of unfinished tile parts
   unsigned* sk_flags;       // [grid][EPI_WARPS]: launch number once the warp's part of the slot is written
   unsigned sk_seq;          // this launch's number
+  unsigned* sched;          // dynamic tile order: a counter that every processed tile advances by one; null: round-robin
+  unsigned sched_base;      // the counter's value when this launch starts (the host adds each launch's tile count)
   long long ld_aux_in;
   const float* bias;
   const void* aux_in;
@@ -85,6 +91,9 @@ struct SharedTail {
   uint64_t empty[MAX_STAGES];
   uint64_t tmem_full[2];
   uint64_t tmem_empty[2];
+  uint64_t sched_full[SCHED_SLOTS];   // dynamic tile order: the producer warp's thread hands the items to the other roles
+  uint64_t sched_empty[SCHED_SLOTS];
+  int sched_item[SCHED_SLOTS];
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -117,8 +126,8 @@ __device__ __forceinline__ bool get_item(const GemmParams& p, int local, WorkIte
   w.split = 0;
   w.first_part = cta;
   int tile;
-  if (p.sk_tiles == 0) {  // tiles (times explicit splits) round-robin
-    const int item = cta + local * grid;
+  if (p.sk_tiles == 0) {  // tiles (times explicit splits) round-robin, or handed out by a counter (item < 0: local is the item)
+    const int item = local < 0 ? -local - 1 : cta + local * grid;
     if (item >= tiles * p.splits) return false;
     w.split = item / tiles;
     tile = item - w.split * tiles;
@@ -204,6 +213,10 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
       tc05::mbar_init(&tail->tmem_full[b], 1);
       tc05::mbar_init(&tail->tmem_empty[b], PAIR ? 2 * EPI_WARPS : EPI_WARPS);
     }
+    for (int q = 0; q < SCHED_SLOTS; ++q) {
+      tc05::mbar_init(&tail->sched_full[q], 1);
+      tc05::mbar_init(&tail->sched_empty[q], 1 + EPI_WARPS);  // the MMA issuer and every epilogue warp read an item
+    }
     tail->abort_flag = 0;
     tc05::fence_barrier_init();
   }
@@ -215,6 +228,21 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
   if (PAIR) tc05::cluster_sync_all(); else __syncthreads();
   tc05::tc_fence_after_sync();
   const uint32_t tmem_base = tail->tmem_base;
+  // Dynamic tile order: the first item of a CTA is its own index, every further one comes from a counter, so a CTA that
+  // starts late (its SM was busy with another stream's kernel) simply takes fewer tiles and nobody waits for it.  The
+  // producer warp's thread draws the items and hands them to the other roles through a small ring in shared memory.
+  const bool dyn = !PAIR && p.sched != nullptr;
+  const int items_total = p.m_tiles * p.n_tiles * p.splits;
+  // (MMA issuer and epilogue warps) the `local`-th item of this CTA, -1 at the end, -2 when the wait ran out
+  auto fetch_item = [&](int local, bool whole_warp) -> int {
+    const int slot = local % SCHED_SLOTS;
+    const uint32_t sphase = (uint32_t)(local / SCHED_SLOTS) & 1u;
+    if (!tc05::mbar_wait(&tail->sched_full[slot], sphase, abort_flag, p.wait_limit_ns)) return -2;
+    const int item = tail->sched_item[slot];
+    if (whole_warp) __syncwarp();
+    if (!whole_warp || lane == 0) tc05::mbar_arrive(&tail->sched_empty[slot]);
+    return item;
+  };
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
@@ -225,7 +253,23 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
       uint32_t phase = 0;
       bool ok = true;
       WorkItem w;
-      for (int local = 0; ok && get_item<PAIR>(p, local, w); ++local) {
+      int item = worker_index<PAIR>();
+      for (int local = 0; ok; ++local) {
+        unsigned next_item = 0;
+        if (dyn) {
+          const int slot = local % SCHED_SLOTS;
+          const uint32_t sphase = (uint32_t)(local / SCHED_SLOTS) & 1u;
+          if (!tc05::mbar_wait(&tail->sched_empty[slot], sphase ^ 1u, abort_flag, p.wait_limit_ns)) { ok = false; break; }
+          const bool more = item < items_total;
+          tail->sched_item[slot] = more ? item : -1;
+          tc05::mbar_arrive(&tail->sched_full[slot]);
+          if (!more) break;
+          get_item<false>(p, -item - 1, w);
+          // asked for now, needed when this tile's loads are queued; unsigned arithmetic, the counter may wrap
+          next_item = atomicAdd(p.sched, 1u) - p.sched_base + gridDim.x;
+        } else if (!get_item<PAIR>(p, local, w)) {
+          break;
+        }
         const int m_row = w.m_tile * TILE_M + (int)rank * BM;      // this CTA's 128 rows of A
         const int n_row = w.n_tile * BN + (int)rank * B_ROWS;      // this CTA's columns of B
         for (int kb = w.kb0; kb < w.kb1; ++kb) {
@@ -275,6 +319,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
           }
           if (++stage == NSTAGES) { stage = 0; phase ^= 1u; }
         }
+        item = (int)next_item;
       }
     }
   } else if (warp == 1) {
@@ -285,7 +330,14 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
       uint32_t phase = 0;
       bool ok = true;
       WorkItem w;
-      for (int local = 0; ok && get_item<PAIR>(p, local, w); ++local) {
+      for (int local = 0; ok; ++local) {
+        if (dyn) {
+          const int item = fetch_item(local, false);
+          if (item < 0) { ok = item == -1; break; }
+          get_item<false>(p, -item - 1, w);
+        } else if (!get_item<PAIR>(p, local, w)) {
+          break;
+        }
         const int kb0 = w.kb0, kb1 = w.kb1;
         const int buf = local & 1;
         const uint32_t buf_phase = (uint32_t)(local >> 1) & 1u;
@@ -344,7 +396,14 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
       if (PAIR) tc05::mbar_arrive_cluster(tc05::cluster_map_shared(&tail->tmem_empty[buf], 0));
       else tc05::mbar_arrive(&tail->tmem_empty[buf]);
     };
-    for (int local = 0; ok && get_item<PAIR>(p, local, w); ++local) {
+    for (int local = 0; ok; ++local) {
+      if (dyn) {
+        const int item = fetch_item(local, true);
+        if (item < 0) { ok = item == -1; break; }
+        get_item<false>(p, -item - 1, w);
+      } else if (!get_item<PAIR>(p, local, w)) {
+        break;
+      }
       const int split = w.split, n_tile = w.n_tile, m_tile = w.m_tile;
       const int buf = local & 1;
       const uint32_t buf_phase = (uint32_t)(local >> 1) & 1u;
@@ -749,6 +808,19 @@ int gemm_bf16_run(hl_ctx* ctx, const hl_gemm_desc* d, const void* a, const void*
     unsigned seq = ++g_stream_launch_number;
     if (seq == 0) seq = ++g_stream_launch_number;  // 0 means "never written"
     p.sk_seq = seq;
+  }
+  // Beside another stream's kernels (collectives in flight) whole tiles and equal splits are handed out by a counter
+  // instead of round-robin: per launch it costs about a microsecond, and it keeps a CTA that starts late from holding
+  // up its share of the tiles.  HEIRLOOM_GEMM_DYNAMIC=1 / 0 forces it on / off.  Every tile advances the counter by
+  // one, so the host knows its value at the start of the next launch without touching the device.
+  {
+    const char* e = getenv("HEIRLOOM_GEMM_DYNAMIC");
+    const bool dynamic = e && (e[0] == '0' || e[0] == '1') ? e[0] == '1' : nccl_active(ctx);
+    p.sched = (dynamic && !pair && plan.sk_tiles == 0 && ctx->gemm_skip_kblock < 0) ? ctx->gemm_sched : nullptr;
+    if (p.sched) {
+      p.sched_base = ctx->gemm_sched_base;
+      ctx->gemm_sched_base += (unsigned)(p.m_tiles * p.n_tiles * splits);
+    }
   }
   p.k_blocks_per_split = ceil_div(p.k_blocks, splits);
   p.epilogue = d->epilogue;

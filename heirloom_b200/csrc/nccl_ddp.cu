@@ -129,10 +129,12 @@ int hl_nccl_init(hl_ctx* ctx, int rank, int world, const unsigned char id_bytes[
   NcclState* st = new NcclState();
   st->rank = rank;
   st->world = world;
-  // The collective kernels get a bounded number of SMs and the persistent GEMM / attention kernels leave exactly those
-  // free while collectives are in flight (HEIRLOOM_COMM_SMS, default 8, 0 = no reservation and NCCL's own choice).
-  // NCCL reads its bound from the environment when the communicator is made; a value the user set is kept.
-  int comm_sms = 8;
+  // HEIRLOOM_COMM_SMS=R gives the collective kernels at most R SMs and makes the persistent GEMM / attention kernels
+  // leave exactly those free while collectives are in flight; the default, 0, leaves NCCL its own choice and reserves
+  // nothing (at 8 GPUs: 21.84 ms a step against 22.07 with R = 8 and 21.97 with R = 16, where the capped collectives
+  // finish later than the backward pass they hide behind).  NCCL reads its bound from the environment when the
+  // communicator is made; a value the user set is kept.
+  int comm_sms = 0;
   if (const char* e = getenv("HEIRLOOM_COMM_SMS")) comm_sms = std::max(0, std::min(atoi(e), ctx->sm_count / 2));
   if (world > 1 && comm_sms > 0) {
     const std::string v = std::to_string(comm_sms);

@@ -193,6 +193,8 @@ int hl_ctx_create(int device_ordinal, hl_ctx** out) {
   HL_CUDA(cudaStreamCreateWithFlags(&ctx->comm_stream, cudaStreamNonBlocking));
   HL_CUDA(cudaMalloc(&ctx->status_dev, sizeof(int) * hl::ST_SLOTS));
   HL_CUDA(cudaMemset(ctx->status_dev, 0, sizeof(int) * hl::ST_SLOTS));
+  HL_CUDA(cudaMalloc(&ctx->gemm_sched, 64));
+  HL_CUDA(cudaMemset(ctx->gemm_sched, 0, 64));
   HL_CUDA(cudaMallocHost(&ctx->status_host, sizeof(int) * hl::ST_SLOTS));
   memset(ctx->status_host, 0, sizeof(int) * hl::ST_SLOTS);
   *out = ctx;
@@ -208,6 +210,7 @@ void hl_ctx_destroy(hl_ctx* ctx) {
   if (ctx->workspace) cudaFree(ctx->workspace);
   if (ctx->gemm_flags) cudaFree(ctx->gemm_flags);
   if (ctx->status_dev) cudaFree(ctx->status_dev);
+  if (ctx->gemm_sched) cudaFree(ctx->gemm_sched);
   if (ctx->status_host) cudaFreeHost(ctx->status_host);
   cudaStreamDestroy(ctx->stream);
   cudaStreamDestroy(ctx->comm_stream);
@@ -234,6 +237,11 @@ int hl_ctx_sync(hl_ctx* ctx) {
     if (ctx->status_host[hl::ST_WAIT_EXPIRED]) msg += " a bounded pipeline wait expired;";
     if (ctx->status_host[hl::ST_BAD_ARGUMENT]) msg += " kernel argument rejected on device;";
     HL_CUDA(cudaMemsetAsync(ctx->status_dev, 0, sizeof(int) * hl::ST_SLOTS, ctx->stream));
+    if (ctx->status_host[hl::ST_WAIT_EXPIRED]) {
+      // a kernel that gave up did not hand out all of its tiles: the tile counter starts over with the host's copy
+      HL_CUDA(cudaMemsetAsync(ctx->gemm_sched, 0, 64, ctx->stream));
+      ctx->gemm_sched_base = 0;
+    }
     HL_CUDA(cudaStreamSynchronize(ctx->stream));
     hl::set_error(msg);
     return HL_ERR_DEVICE;

@@ -208,6 +208,27 @@ def test_an_expired_pipeline_wait_ends_the_kernel_with_a_status_and_leaves_the_c
     assert_close("gemm after an expired wait", host(out), a @ b, atol=2e-3, rtol=1e-5)
 
 
+def test_tiles_handed_out_by_a_counter_give_the_same_bits_as_round_robin(monkeypatch):
+    """HEIRLOOM_GEMM_DYNAMIC (read at every call; on by default only beside a communicator) changes which CTA computes
+    which tile, never a tile's arithmetic: outputs are bit-identical, launch after launch (the counter is never reset,
+    the host tracks its value), for whole tiles, equal splits and a bf16 epilogue."""
+    from heirloom_b200 import cuda
+    c = ctx()
+    rng = np.random.default_rng(91)
+    monkeypatch.setenv("HEIRLOOM_GEMM_PAIRS", "0")
+    cases = [(4096, 2048, 320, 0, torch.float32), (1000, 520, 1032, 4, torch.float32), (2304, 1024, 128, 1, torch.bfloat16)]
+    for m, n, k, split, dt in cases:
+        a = dev(ho.bf16_round(rng.standard_normal((m, k))), torch.bfloat16)
+        b = dev(ho.bf16_round(rng.standard_normal((n, k))), torch.bfloat16)
+        monkeypatch.setenv("HEIRLOOM_GEMM_DYNAMIC", "0")
+        want = cuda.gemm_bf16(c, a, b, m, n, k, out_dtype=dt, split_k=split).clone()
+        monkeypatch.setenv("HEIRLOOM_GEMM_DYNAMIC", "1")
+        for _ in range(3):
+            got = cuda.gemm_bf16(c, a, b, m, n, k, out_dtype=dt, split_k=split)
+            assert torch.equal(got, want), (m, n, k, split)
+    c.sync()
+
+
 PAIR_SCRIPT = r"""
 import numpy as np, torch
 from oracle import heirloom_oracle as ho
