@@ -52,7 +52,6 @@ struct FbBarriers {
   uint64_t kv_full[FB_MAX_STAGES], kv_empty[FB_MAX_STAGES];
   uint64_t q_full[FB_MAX_STAGES], q_empty[FB_MAX_STAGES];
   uint64_t sdp_full, sdp_free, p_full, dq_full;
-  uint64_t stage_free, stage_full;  // dQ staging buffer: read by the previous reduction / written by all softmax warps
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -115,7 +114,8 @@ template <int HD>
 __global__ void __launch_bounds__(FB_THREADS, 1)
 flash_attention_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                            const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do,
-                           const __grid_constant__ CUtensorMap map_dq, const FbParams p) {
+                           const __grid_constant__ CUtensorMap map_dq, const __grid_constant__ CUtensorMap map_dk,
+                           const __grid_constant__ CUtensorMap map_dv, const FbParams p) {
   using Z = FbSizes<HD>;
   constexpr int FB_HD = HD;
   constexpr int FB_TILE_BYTES = Z::TILE_BYTES, FB_KV_BUFFERS = Z::KV_BUFFERS, FB_Q_STAGES = Z::Q_STAGES;
@@ -149,8 +149,6 @@ flash_attention_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
     tc05::mbar_init(&bars->sdp_free, FB_SOFTMAX_WARPS);
     tc05::mbar_init(&bars->p_full, FB_SOFTMAX_WARPS);
     tc05::mbar_init(&bars->dq_full, 1);
-    tc05::mbar_init(&bars->stage_free, 1);
-    tc05::mbar_init(&bars->stage_full, FB_SOFTMAX_WARPS);
     bars->abort_flag = layout_ok ? 0 : 1;
     tc05::fence_barrier_init();
   }
@@ -304,41 +302,31 @@ flash_attention_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
     bool ok = !*abort_flag;
     // dQ tile number `g` of the sequence, for query position t of (b, h): out of tensor memory and into the f32
     // accumulator in global memory
-    // The tile is staged in shared memory and added by one TMA reduction per 32-column block: 32 KB of f32 per query
-    // tile would otherwise leave as 16-byte reductions issued by these warps, which then wait behind them.
-    // `drain` counts the calls; rows past T are clipped by the tensor map.
-    int drain = 0;
-    // the previous reduction has read the staging buffer: checked by its issuer well before the buffer is needed again
-    auto release_stage = [&]() {
-      if (warp == 0 && lane == 0) {
-        tc05::tma_store_wait_read();
-        tc05::mbar_arrive(&bars->stage_free);
-      }
-    };
+    // The tile is staged in shared memory and added by TMA reductions: 32 KB of f32 per query tile would otherwise
+    // leave as 16-byte reductions issued by these warps, which then wait behind them.  Rows past T are clipped by the
+    // tensor map.  Every warp stages its own 32 rows x 32 columns (4 KB, rows of 128 bytes, 128-byte swizzle) and its lane 0 adds
+    // them with one TMA reduction of its own: no warp waits for another one, and the only wait is the lane's own, for
+    // its previous reduction to have read the 4 KB, a whole tile earlier.
+    uint8_t* my_stage = sdq + half * (FB_BM * 128) + lg * (32 * 128);
     auto add_dq_begin = [&](int g, uint32_t (&qb)[32]) {  // the tile starts to travel out of tensor memory
       tc05::tmem_ld_32x32b_x32(tmem_dq + (uint32_t)((g & 1) * 64) + lane_sel + half * 32, qb);
     };
     auto add_dq_finish = [&](const FbCursor& c, uint32_t (&qb)[32]) -> bool {
+      if (lane == 0) tc05::tma_store_wait_read();  // this warp's previous reduction has read the staging rows
       tc05::tmem_ld_wait();
       tc05::tmem_ld_fence(qb);
-      if (!tc05::mbar_wait(&bars->stage_free, (uint32_t)drain & 1u, abort_flag)) return false;
-      uint8_t* line = sdq + half * (FB_BM * 128) + r * 128;
+      __syncwarp();
+      uint8_t* line = my_stage + lane * 128;
 #pragma unroll
       for (int i = 0; i < 8; ++i)
-        *reinterpret_cast<uint4*>(line + ((i ^ (r & 7)) << 4)) = make_uint4(qb[i * 4], qb[i * 4 + 1], qb[i * 4 + 2], qb[i * 4 + 3]);
+        *reinterpret_cast<uint4*>(line + ((i ^ (lane & 7)) << 4)) = make_uint4(qb[i * 4], qb[i * 4 + 1], qb[i * 4 + 2], qb[i * 4 + 3]);
       tc05::fence_proxy_async_smem();
       __syncwarp();
-      if (lane == 0) tc05::mbar_arrive(&bars->stage_full);
-      if (warp == 0) {
-        if (!tc05::mbar_wait(&bars->stage_full, (uint32_t)drain & 1u, abort_flag)) return false;
-        if (lane == 0) {
-          const int t0 = (c.kj + c.it) * FB_BM;
-          tc05::tma_reduce_add_3d(&map_dq, sdq, c.h * FB_HD + c.cb * 64, t0, c.b);
-          tc05::tma_reduce_add_3d(&map_dq, sdq + FB_BM * 128, c.h * FB_HD + c.cb * 64 + 32, t0, c.b);
-          tc05::tma_store_commit();
-        }
+      if (lane == 0) {
+        const int t0 = (c.kj + c.it) * FB_BM + lg * 32;
+        tc05::tma_reduce_add_3d(&map_dq, my_stage, c.h * FB_HD + c.cb * 64 + half * 32, t0, c.b);
+        tc05::tma_store_commit();
       }
-      ++drain;
       return true;
     };
     // dV and dK of this thread's key row (32 columns each) out of tensor memory, already rounded to bf16 pairs:
@@ -353,16 +341,27 @@ flash_attention_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
         for (int i = 0; i < 32; i += 2) w[which * 16 + i / 2] = pack_bf16x2(__uint_as_float(raw[i]), __uint_as_float(raw[i + 1]));
       }
     };
-    // dK, dV of item c (row r = key)
+    // dK, dV of item c (row r = key): through the warp's staging rows (two tiles of 32 rows x 64 bytes, 64-byte
+    // swizzle) and out with one TMA store each, 128-byte row segments together with the other half's warp, instead of
+    // sixteen 16-byte stores a thread that each touch 32 different lines.  Keys past T are clipped by the tensor map.
     auto store_dkv = [&](const uint32_t (&w)[32], const FbCursor& c) {
-      const int key = c.kj * FB_BN + r;
-      if (key < p.T) {
-        const size_t off = (size_t)(c.b * p.T + key) * p.ld_dkv + (size_t)c.h * FB_HD + c.cb * 64 + half * 32;
+      if (lane == 0) tc05::tma_store_wait_read();  // the dQ reduction queued just before has read the staging rows
+      __syncwarp();
+      uint8_t* tv = my_stage + lane * 64;
+      uint8_t* tk = my_stage + 2048 + lane * 64;
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          *reinterpret_cast<uint4*>(p.dv + off + i * 8) = make_uint4(w[i * 4], w[i * 4 + 1], w[i * 4 + 2], w[i * 4 + 3]);
-          *reinterpret_cast<uint4*>(p.dk + off + i * 8) = make_uint4(w[16 + i * 4], w[16 + i * 4 + 1], w[16 + i * 4 + 2], w[16 + i * 4 + 3]);
-        }
+      for (int i = 0; i < 4; ++i) {
+        const int off = (i ^ ((lane >> 1) & 3)) << 4;
+        *reinterpret_cast<uint4*>(tv + off) = make_uint4(w[i * 4], w[i * 4 + 1], w[i * 4 + 2], w[i * 4 + 3]);
+        *reinterpret_cast<uint4*>(tk + off) = make_uint4(w[16 + i * 4], w[16 + i * 4 + 1], w[16 + i * 4 + 2], w[16 + i * 4 + 3]);
+      }
+      tc05::fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) {
+        const int col = c.h * FB_HD + c.cb * 64 + half * 32, key0 = c.kj * FB_BN + lg * 32;
+        tc05::tma_store_3d(&map_dv, my_stage, col, key0, c.b);
+        tc05::tma_store_3d(&map_dk, my_stage + 2048, col, key0, c.b);
+        tc05::tma_store_commit();
       }
     };
     // per-row statistics of a query tile, fetched one tile ahead
@@ -407,7 +406,6 @@ flash_attention_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
           tc05::tc_fence_before_sync();
           __syncwarp();
           if (lane == 0) tc05::mbar_arrive(&bars->sdp_free);
-          if (g > 0) release_stage();  // one release per drain: tile g drains the dQ of tile g - 1
         }
         // P = 2^(S*scale*log2e - lse*log2e); rows past T carry lse = +inf, so their P is 0.  dS = P * (dP - D) * scale
         // with the scale folded into both terms.  Only the diagonal tile has keys above the query to mask.
@@ -470,13 +468,12 @@ flash_attention_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
       if (tc05::mbar_wait(&bars->dq_full, (uint32_t)(g - 1) & 1u, abort_flag)) {
         tc05::tc_fence_after_sync();
         uint32_t qb[32];
-        release_stage();
         add_dq_begin(g - 1, qb);
         add_dq_finish(prev, qb);
-        if (warp == 0 && lane == 0) tc05::tma_store_wait_all();  // the last reduction has left shared memory and landed
         uint32_t dkv[32];
         load_dkv(dkv);
         store_dkv(dkv, prev);
+        if (lane == 0) tc05::tma_store_wait_all();  // the last reduction and stores have left shared memory and landed
       }
     }
   }
@@ -587,13 +584,22 @@ int flash_attention_backward_impl(hl_ctx* ctx, const void* q, const void* k, con
   p.status = ctx->status_dev;
   const int nq = ceil_div(time, FB_BM);
   // dQ accumulator as [batch][time][channels] f32, so that a tile's rows past `time` are clipped instead of landing in
-  // the next batch entry; boxes of 32 columns (128 bytes) by 128 rows
+  // the next batch entry; boxes of 32 columns (128 bytes) by 32 rows
   CUtensorMap mdq;
   {
     const uint64_t dims[3] = {(uint64_t)C, (uint64_t)time, (uint64_t)batch};
     const uint64_t strides[2] = {(uint64_t)C * sizeof(float), (uint64_t)time * (uint64_t)C * sizeof(float)};
-    const uint32_t box[3] = {32, (uint32_t)FB_BM, 1};
+    const uint32_t box[3] = {32, 32, 1};  // one softmax warp's share of a dQ tile
     if ((rc = make_tensor_map(&mdq, HL_F32, 3, dq_accum, dims, strides, box, 128)) != HL_OK) return rc;
+  }
+  // dK and dV as [batch][time][channels] bf16 with the caller's row stride; boxes of 32 channels (64 bytes) by 32 keys
+  CUtensorMap mdk, mdv;
+  {
+    const uint64_t dims[3] = {(uint64_t)C, (uint64_t)time, (uint64_t)batch};
+    const uint64_t strides[2] = {(uint64_t)ld_dqkv * 2, (uint64_t)time * (uint64_t)ld_dqkv * 2};
+    const uint32_t box[3] = {32, 32, 1};
+    if ((rc = make_tensor_map(&mdk, HL_BF16, 3, dk, dims, strides, box, 64)) != HL_OK) return rc;
+    if ((rc = make_tensor_map(&mdv, HL_BF16, 3, dv, dims, strides, box, 64)) != HL_OK) return rc;
   }
   const int grid = std::min(nq * batch * n_heads * p.blocks, persistent_sms(ctx));
   if (head_dim == 64) {
@@ -602,14 +608,14 @@ int flash_attention_backward_impl(hl_ctx* ctx, const void* q, const void* k, con
       HL_CUDA(cudaFuncSetAttribute(flash_attention_bwd_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, FbSizes<64>::SMEM_BYTES));
       configured = true;
     }
-    flash_attention_bwd_kernel<64><<<grid, FB_THREADS, FbSizes<64>::SMEM_BYTES, ctx->stream>>>(mq, mk, mv, mdo, mdq, p);
+    flash_attention_bwd_kernel<64><<<grid, FB_THREADS, FbSizes<64>::SMEM_BYTES, ctx->stream>>>(mq, mk, mv, mdo, mdq, mdk, mdv, p);
   } else {
     static bool configured = false;
     if (!configured) {
       HL_CUDA(cudaFuncSetAttribute(flash_attention_bwd_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, FbSizes<128>::SMEM_BYTES));
       configured = true;
     }
-    flash_attention_bwd_kernel<128><<<grid, FB_THREADS, FbSizes<128>::SMEM_BYTES, ctx->stream>>>(mq, mk, mv, mdo, mdq, p);
+    flash_attention_bwd_kernel<128><<<grid, FB_THREADS, FbSizes<128>::SMEM_BYTES, ctx->stream>>>(mq, mk, mv, mdo, mdq, mdk, mdv, p);
   }
   HL_LAUNCH_CHECK("flash_attention_bwd_kernel");
   {
