@@ -365,16 +365,26 @@ flash_attention_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
       }
     };
     // per-row statistics of a query tile, fetched one tile ahead
-    auto row_stats = [&](const FbCursor& c, float* neg_lse2, float* neg_dlt_scaled) {
+    // The two loads are requested here and their values first touched where the caller pins them (after the tile's
+    // arithmetic), so that nothing waits for them on the way.
+    auto row_stats = [&](const FbCursor& c, float* lse_raw, float* dlt_raw) {
       const int tt = c.valid() ? (c.kj + c.it) * FB_BM + r : 0;
       const bool in = c.valid() && tt < p.T;
       const size_t stat = in ? ((size_t)c.b * p.H + c.h) * p.T + tt : 0;
-      *neg_lse2 = in ? -p.lse[stat] * 1.4426950408889634f : -INFINITY;  // rows past T: every P becomes 0
-      *neg_dlt_scaled = in ? -p.delta[stat] * p.scale : 0.f;
+      *lse_raw = in ? __ldg(p.lse + stat) : INFINITY;  // rows past T: every P becomes 0
+      *dlt_raw = in ? __ldg(p.delta + stat) : 0.f;
+    };
+    auto scale_stats = [&](float lse_raw, float dlt_raw, float* neg_lse2, float* neg_dlt_scaled) {
+      *neg_lse2 = -lse_raw * 1.4426950408889634f;
+      *neg_dlt_scaled = -dlt_raw * p.scale;
     };
     FbCursor c = first, prev = first;
     float neg_lse2, neg_dlt_scaled;
-    row_stats(c, &neg_lse2, &neg_dlt_scaled);
+    {
+      float l0, d0;
+      row_stats(c, &l0, &d0);
+      scale_stats(l0, d0, &neg_lse2, &neg_dlt_scaled);
+    }
     int g = 0;
     // One query tile.  `Boundary` is the first tile of an item that follows another one: only that
     // instance carries the read-out of the previous item's dK and dV, so the steady-state instance
@@ -385,8 +395,8 @@ flash_attention_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
       const FbCursor n = fb_next(c, p);
       const int t = (c.kj + c.it) * FB_BM + r;  // query position
       const int key0 = c.kj * FB_BN;
-      float next_neg_lse2, next_neg_dlt_scaled;
-      row_stats(n, &next_neg_lse2, &next_neg_dlt_scaled);
+      float next_lse_raw, next_dlt_raw;
+      row_stats(n, &next_lse_raw, &next_dlt_raw);
       if (!tc05::mbar_wait(&bars->sdp_full, (uint32_t)g & 1u, abort_flag)) return false;
       tc05::tc_fence_after_sync();
       uint32_t pp[4][8], dd[4][8];  // P and dS of this thread's 64 key columns, bf16 pairs
@@ -423,8 +433,8 @@ flash_attention_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
           dd[ch / 2][(ch & 1) * 4 + i / 2] = pack_bf16x2(dsv[0], dsv[1]);
         }
       }
-      neg_lse2 = next_neg_lse2;
-      neg_dlt_scaled = next_neg_dlt_scaled;
+      asm volatile("" : "+f"(next_lse_raw), "+f"(next_dlt_raw));  // first use of the loaded values: not before here
+      scale_stats(next_lse_raw, next_dlt_raw, &neg_lse2, &neg_dlt_scaled);
       // the previous tile's products have finished: its dQ is ready and P/dS may be overwritten
       if (g > 0) {
         if (!tc05::mbar_wait(&bars->dq_full, (uint32_t)(g - 1) & 1u, abort_flag)) return false;
