@@ -459,12 +459,14 @@ flash_attention_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
       __syncwarp();
       if (lane == 0) tc05::mbar_arrive(&bars->p_full);
       // the other dQ buffer is not written again before this warp's next arrival on p_full
+      // dK and dV first: the staging rows were last read a whole tile ago, so nothing waits; the dQ share that follows
+      // waits only for these two plain stores to have read them
+      if constexpr (Boundary) store_dkv(dkv, prev);
       if (g > 0) {
         uint32_t qb[32];
         add_dq_begin(g - 1, qb);
         if (!add_dq_finish(prev, qb)) return false;
       }
-      if constexpr (Boundary) store_dkv(dkv, prev);
       prev = c;
       c = n;
       ++g;
