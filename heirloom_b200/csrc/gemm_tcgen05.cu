@@ -184,7 +184,10 @@ __device__ __forceinline__ bool get_item(const GemmParams& p, int local, WorkIte
   return true;
 }
 
-template <bool A_MN, bool B_MN, bool PAIR>
+// SPEC < 0: epilogue, output type and work split are read from the parameters at run time.  SPEC >= 0: a product of whole
+// tiles whose epilogue (SPEC / 2) and output type (SPEC & 1: bf16) are fixed at compile time, so that an epilogue warp
+// runs straight-line code of its own variant only (the step's short-contraction products are bound by their epilogue).
+template <bool A_MN, bool B_MN, bool PAIR, int SPEC>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                          const __grid_constant__ CUtensorMap map_c, const __grid_constant__ CUtensorMap map_aux,
@@ -386,9 +389,11 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
     // a TMA store is still reading one tile while the next columns are written into the other.
     uint8_t* staging = staging_base + size_t(ew) * STAGING_BYTES;
     int stage_sel = 0;
-    const bool out_bf16 = !p.partial_out && p.out_dtype == HL_BF16;
-    const bool need_aux = !p.partial_out && (p.epilogue == HL_EPI_BIAS_RESIDUAL || p.epilogue == HL_EPI_DGELU);
-    const bool need_bias = !p.partial_out && p.bias != nullptr;
+    const int epi = SPEC >= 0 ? SPEC / 2 : p.epilogue;
+    const bool partial = SPEC >= 0 ? false : p.partial_out != 0;
+    const bool out_bf16 = SPEC >= 0 ? (SPEC & 1) != 0 : (!partial && p.out_dtype == HL_BF16);
+    const bool need_aux = !partial && (epi == HL_EPI_BIAS_RESIDUAL || epi == HL_EPI_DGELU);
+    const bool need_bias = !partial && p.bias != nullptr;
     bool ok = true;
     WorkItem w;
     // the accumulator buffer goes back to the MMA issuer, which in a pair sits in the even CTA
@@ -432,7 +437,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
       if (!tc05::mbar_wait(&tail->tmem_full[buf], buf_phase, abort_flag, p.wait_limit_ns)) { ok = false; break; }
       tc05::tc_fence_after_sync();
       const uint32_t taddr_row = tmem_base + (uint32_t)(buf * BN) + ((uint32_t)(lane_group * 32) << 16);
-      if (w.kind == ITEM_PART) {
+      if (SPEC < 0 && w.kind == ITEM_PART) {
         // Raw sums of a part of the contraction: this warp's 32 rows x 128 columns go to the CTA's slot.
         // The slot is laid out [warp][chunk][q][lane] in 16-byte units, i.e. in the order the registers
         // come out of tensor memory, so that every store (and the finisher's load) covers 512
@@ -461,7 +466,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
         if (lane == 0) release_buffer(buf);
         continue;
       }
-      if (w.kind == ITEM_FINISH) {
+      if (SPEC < 0 && w.kind == ITEM_FINISH) {
         // The same warp of every earlier CTA on this tile wrote exactly the rows and columns this warp adds.
         if (lane == 0) {
           const unsigned long long t0 = tc05::global_timer_ns();
@@ -495,7 +500,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
         tc05::fence_proxy_async_smem();
         __syncwarp();
         if (lane == 0) {
-          if (p.partial_out) tc05::tma_store_3d(map, tile, col, row0, split);
+          if (partial) tc05::tma_store_3d(map, tile, col, row0, split);
           else tc05::tma_store_2d(map, tile, col, row0);
           tc05::tma_store_commit();
         }
@@ -506,7 +511,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
         uint32_t acc_bits[32];
         tc05::tmem_ld_32x32b_x32(taddr_row + (uint32_t)(half * 128 + chunk * 32), acc_bits);
         tc05::tmem_ld_wait();
-        if (w.kind == ITEM_FINISH) {
+        if (SPEC < 0 && w.kind == ITEM_FINISH) {
 #pragma unroll 1
           for (int c = w.first_part; c < (int)blockIdx.x; ++c) {
             if (!cta_has_units(p, c)) continue;
@@ -530,7 +535,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
           float v[8];
 #pragma unroll
           for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(acc_bits[g * 8 + i]);
-          if (!p.partial_out) {
+          if (!partial) {
             if (need_bias) {
               // columns chunk*32 + g*8 + i of this half live in lane chunk*8 + g*2 + i/4
               const int src = chunk * 8 + g * 2;
@@ -539,18 +544,18 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
               v[4] += __shfl_sync(0xffffffffu, bias_reg.x, src + 1); v[5] += __shfl_sync(0xffffffffu, bias_reg.y, src + 1);
               v[6] += __shfl_sync(0xffffffffu, bias_reg.z, src + 1); v[7] += __shfl_sync(0xffffffffu, bias_reg.w, src + 1);
             }
-            if (p.epilogue == HL_EPI_BIAS_GELU) {
+            if (epi == HL_EPI_BIAS_GELU) {
               // h = bf16(acc + bias) is the main output; g = bf16(gelu(h)) the second one
               float gl[8];
 #pragma unroll
               for (int i = 0; i < 8; ++i) { v[i] = bf16_round_alu(v[i]); gl[i] = gelu_fwd_fast(v[i]); }
               gelu_packed[g * 4] = pack_bf16x2(gl[0], gl[1]); gelu_packed[g * 4 + 1] = pack_bf16x2(gl[2], gl[3]);
               gelu_packed[g * 4 + 2] = pack_bf16x2(gl[4], gl[5]); gelu_packed[g * 4 + 3] = pack_bf16x2(gl[6], gl[7]);
-            } else if (p.epilogue == HL_EPI_BIAS_RESIDUAL || p.epilogue == HL_EPI_DGELU) {
+            } else if (epi == HL_EPI_BIAS_RESIDUAL || epi == HL_EPI_DGELU) {
               const uint4 r = aux[g];
               const float2 r0 = unpack_bf16x2(r.x), r1 = unpack_bf16x2(r.y), r2 = unpack_bf16x2(r.z), r3 = unpack_bf16x2(r.w);
               const float rr[8] = {r0.x, r0.y, r1.x, r1.y, r2.x, r2.y, r3.x, r3.y};
-              if (p.epilogue == HL_EPI_BIAS_RESIDUAL) {
+              if (epi == HL_EPI_BIAS_RESIDUAL) {
                 // out = bf16(residual + bf16(acc + bias)): the two round trips of the block
 #pragma unroll
                 for (int i = 0; i < 8; ++i) v[i] = rr[i] + bf16_round_alu(v[i]);
@@ -561,7 +566,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
               }
             }
           }
-          if (out_bf16 && p.epilogue == HL_EPI_BIAS_GELU) {  // h is already rounded
+          if (out_bf16 && epi == HL_EPI_BIAS_GELU) {  // h is already rounded
             packed[g * 4] = pack_rounded_bf16x2(v[0], v[1]); packed[g * 4 + 1] = pack_rounded_bf16x2(v[2], v[3]);
             packed[g * 4 + 2] = pack_rounded_bf16x2(v[4], v[5]); packed[g * 4 + 3] = pack_rounded_bf16x2(v[6], v[7]);
           } else if (out_bf16) {
@@ -577,7 +582,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
         }
         if (out_bf16) {
           emit(&map_c, packed, col0);
-          if (p.epilogue == HL_EPI_BIAS_GELU) emit(&map_aux, gelu_packed, col0);
+          if (epi == HL_EPI_BIAS_GELU) emit(&map_aux, gelu_packed, col0);
         } else {
           emit(&map_c, packed, col0);
           if (col0 + 16 < p.n) emit(&map_c, hi_words, col0 + 16);
@@ -631,10 +636,10 @@ __global__ void splitk_reduce_kernel(const float* __restrict__ partials, float* 
   }
 }
 
-template <bool A_MN, bool B_MN, bool PAIR>
+template <bool A_MN, bool B_MN, bool PAIR, int SPEC = -1>
 int launch_variant(hl_ctx* ctx, const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc,
                    const CUtensorMap& maux, const GemmParams& p, int grid) {
-  auto kern = gemm_bf16_tcgen05_kernel<A_MN, B_MN, PAIR>;
+  auto kern = gemm_bf16_tcgen05_kernel<A_MN, B_MN, PAIR, SPEC>;
   static bool configured = false;
   if (!configured) {
     HL_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GEMM_SMEM_BYTES));
@@ -869,7 +874,23 @@ int gemm_bf16_run(hl_ctx* ctx, const hl_gemm_desc* d, const void* a, const void*
   const int total = p.m_tiles * p.n_tiles * p.splits;
   const int grid = pair ? 2 * min(total, sms / 2) : plan.sk_tiles > 0 ? sms : min(total, sms);
   ProfileScope prof(ctx, HL_PROF_GEMM, 2.0 * (double)d->m * (double)d->n * (double)d->k);
-  if (pair) {
+  // The training step's products with whole tiles have kernels of their own, compiled for one epilogue and output type.
+  const bool simple = splits == 1 && plan.sk_tiles == 0;
+  const int spec = simple ? d->epilogue * 2 + (d->out_dtype == HL_BF16 ? 1 : 0) : -1;
+  constexpr int kBias = HL_EPI_BIAS * 2, kGelu = HL_EPI_BIAS_GELU * 2, kResidual = HL_EPI_BIAS_RESIDUAL * 2,
+                kDgelu = HL_EPI_DGELU * 2, kNone = HL_EPI_NONE * 2;
+  bool launched = true;
+  if (!a_mn && !b_mn && !pair && spec == kBias + 1) rc = launch_variant<false, false, false, kBias + 1>(ctx, ma, mb, mc, maux, p, grid);
+  else if (!a_mn && !b_mn && !pair && spec == kBias) rc = launch_variant<false, false, false, kBias>(ctx, ma, mb, mc, maux, p, grid);
+  else if (!a_mn && !b_mn && !pair && spec == kGelu + 1) rc = launch_variant<false, false, false, kGelu + 1>(ctx, ma, mb, mc, maux, p, grid);
+  else if (!a_mn && !b_mn && !pair && spec == kResidual + 1) rc = launch_variant<false, false, false, kResidual + 1>(ctx, ma, mb, mc, maux, p, grid);
+  else if (!a_mn && !b_mn && pair && spec == kResidual + 1) rc = launch_variant<false, false, true, kResidual + 1>(ctx, ma, mb, mc, maux, p, grid);
+  else if (!a_mn && b_mn && !pair && spec == kDgelu + 1) rc = launch_variant<false, true, false, kDgelu + 1>(ctx, ma, mb, mc, maux, p, grid);
+  else if (!a_mn && b_mn && !pair && spec == kNone + 1) rc = launch_variant<false, true, false, kNone + 1>(ctx, ma, mb, mc, maux, p, grid);
+  else if (!a_mn && b_mn && pair && spec == kNone) rc = launch_variant<false, true, true, kNone>(ctx, ma, mb, mc, maux, p, grid);
+  else launched = false;
+  if (launched) {
+  } else if (pair) {
     if (a_mn && b_mn) rc = launch_variant<true, true, true>(ctx, ma, mb, mc, maux, p, grid);
     else if (a_mn)    rc = launch_variant<true, false, true>(ctx, ma, mb, mc, maux, p, grid);
     else if (b_mn)    rc = launch_variant<false, true, true>(ctx, ma, mb, mc, maux, p, grid);
