@@ -186,7 +186,9 @@ __device__ __forceinline__ bool get_item(const GemmParams& p, int local, WorkIte
 
 // SPEC < 0: epilogue, output type and work split are read from the parameters at run time.  SPEC >= 0: a product of whole
 // tiles whose epilogue (SPEC / 2) and output type (SPEC & 1: bf16) are fixed at compile time, so that an epilogue warp
-// runs straight-line code of its own variant only (the step's short-contraction products are bound by their epilogue).
+// runs straight-line code of its own variant only (the step's short-contraction products are bound by their epilogue);
+// SPEC_PARTIAL: equal splits of the contraction whose raw f32 sums go to the scratch of the second kernel.
+constexpr int SPEC_PARTIAL = 16;
 template <bool A_MN, bool B_MN, bool PAIR, int SPEC>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
@@ -389,9 +391,9 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
     // a TMA store is still reading one tile while the next columns are written into the other.
     uint8_t* staging = staging_base + size_t(ew) * STAGING_BYTES;
     int stage_sel = 0;
-    const int epi = SPEC >= 0 ? SPEC / 2 : p.epilogue;
-    const bool partial = SPEC >= 0 ? false : p.partial_out != 0;
-    const bool out_bf16 = SPEC >= 0 ? (SPEC & 1) != 0 : (!partial && p.out_dtype == HL_BF16);
+    const int epi = SPEC == SPEC_PARTIAL ? HL_EPI_NONE : SPEC >= 0 ? SPEC / 2 : p.epilogue;
+    const bool partial = SPEC == SPEC_PARTIAL ? true : SPEC >= 0 ? false : p.partial_out != 0;
+    const bool out_bf16 = SPEC == SPEC_PARTIAL ? false : SPEC >= 0 ? (SPEC & 1) != 0 : (!partial && p.out_dtype == HL_BF16);
     const bool need_aux = !partial && (epi == HL_EPI_BIAS_RESIDUAL || epi == HL_EPI_DGELU);
     const bool need_bias = !partial && p.bias != nullptr;
     bool ok = true;
@@ -876,7 +878,8 @@ int gemm_bf16_run(hl_ctx* ctx, const hl_gemm_desc* d, const void* a, const void*
   ProfileScope prof(ctx, HL_PROF_GEMM, 2.0 * (double)d->m * (double)d->n * (double)d->k);
   // The training step's products with whole tiles have kernels of their own, compiled for one epilogue and output type.
   const bool simple = splits == 1 && plan.sk_tiles == 0;
-  const int spec = simple ? d->epilogue * 2 + (d->out_dtype == HL_BF16 ? 1 : 0) : -1;
+  const int spec = simple ? d->epilogue * 2 + (d->out_dtype == HL_BF16 ? 1 : 0)
+                          : (splits > 1 && plan.sk_tiles == 0) ? SPEC_PARTIAL : -1;
   constexpr int kBias = HL_EPI_BIAS * 2, kGelu = HL_EPI_BIAS_GELU * 2, kResidual = HL_EPI_BIAS_RESIDUAL * 2,
                 kDgelu = HL_EPI_DGELU * 2, kNone = HL_EPI_NONE * 2;
   bool launched = true;
@@ -888,6 +891,8 @@ int gemm_bf16_run(hl_ctx* ctx, const hl_gemm_desc* d, const void* a, const void*
   else if (!a_mn && b_mn && !pair && spec == kDgelu + 1) rc = launch_variant<false, true, false, kDgelu + 1>(ctx, ma, mb, mc, maux, p, grid);
   else if (!a_mn && b_mn && !pair && spec == kNone + 1) rc = launch_variant<false, true, false, kNone + 1>(ctx, ma, mb, mc, maux, p, grid);
   else if (!a_mn && b_mn && pair && spec == kNone) rc = launch_variant<false, true, true, kNone>(ctx, ma, mb, mc, maux, p, grid);
+  else if (a_mn && b_mn && pair && spec == kNone) rc = launch_variant<true, true, true, kNone>(ctx, ma, mb, mc, maux, p, grid);
+  else if (a_mn && b_mn && pair && spec == SPEC_PARTIAL) rc = launch_variant<true, true, true, SPEC_PARTIAL>(ctx, ma, mb, mc, maux, p, grid);
   else launched = false;
   if (launched) {
   } else if (pair) {
