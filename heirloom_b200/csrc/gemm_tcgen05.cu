@@ -403,14 +403,56 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
       if (PAIR) tc05::mbar_arrive_cluster(tc05::cluster_map_shared(&tail->tmem_empty[buf], 0));
       else tc05::mbar_arrive(&tail->tmem_empty[buf]);
     };
-    for (int local = 0; ok; ++local) {
+    // The `local`-th item of this CTA into `dst`: 1 = there is one, 0 = the sequence is over, -1 = a wait ran out.
+    auto take_item = [&](int local, WorkItem& dst) -> int {
       if (dyn) {
         const int item = fetch_item(local, true);
-        if (item < 0) { ok = item == -1; break; }
-        get_item<false>(p, -item - 1, w);
-      } else if (!get_item<PAIR>(p, local, w)) {
-        break;
+        if (item < 0) return item == -1 ? 0 : -1;
+        get_item<false>(p, -item - 1, dst);
+        return 1;
       }
+      return get_item<PAIR>(p, local, dst) ? 1 : 0;
+    };
+    // Global reads of the epilogue are issued ahead of their use so that their latency hides behind the previous
+    // tile's last chunk, the wait for the accumulator and the previous chunk's arithmetic: the warp's 128 bias values
+    // sit four per lane and are handed around by shuffles, and the residual / pre-activation rows are fetched one
+    // 32-column chunk ahead.  The next tile's item, bias and first rows are asked for before the current tile's last
+    // chunk is worked on.
+    auto fetch_aux_of = [&](const WorkItem& x, int chunk, uint4 (&dst)[4]) {
+      const int xrow = x.m_tile * TILE_M + (int)rank * BM + lane_group * 32 + lane;
+      const int xcol0 = x.n_tile * BN + half * 128;
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const int col = xcol0 + chunk * 32 + q * 8;
+        dst[q] = make_uint4(0, 0, 0, 0);
+        if (need_aux && xrow < p.m && col < p.n)
+          dst[q] = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(p.aux_in) +
+                                                        (size_t)xrow * p.ld_aux_in + col));
+      }
+    };
+    auto fetch_bias_of = [&](const WorkItem& x) -> float4 {
+      const int xcol0 = x.n_tile * BN + half * 128;
+      float4 b = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (need_bias && xcol0 + lane * 4 < p.n) b = __ldg(reinterpret_cast<const float4*>(p.bias + xcol0 + lane * 4));
+      return b;
+    };
+    WorkItem wn;
+    uint4 aux_a[4], aux_b[4];
+    float4 bias_reg = make_float4(0.f, 0.f, 0.f, 0.f), bias_next = bias_reg;
+    int have = take_item(0, w);
+    if (have == 1) {
+      bias_reg = fetch_bias_of(w);
+      fetch_aux_of(w, 0, aux_a);
+    }
+    for (int local = 0; ok && have == 1; ++local) {
+      int have_next = -2;  // not asked for yet
+      auto ask_next = [&]() {  // the next item, its bias and its first rows (into the buffer the chunk loop is done with)
+        have_next = take_item(local + 1, wn);
+        if (have_next == 1) {
+          bias_next = fetch_bias_of(wn);
+          fetch_aux_of(wn, 0, aux_b);
+        }
+      };
       const int split = w.split, n_tile = w.n_tile, m_tile = w.m_tile;
       const int buf = local & 1;
       const uint32_t buf_phase = (uint32_t)(local >> 1) & 1u;
@@ -418,24 +460,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
       const int row = row0 + lane;
       const bool row_ok = row < p.m;
       const int half_col0 = n_tile * BN + half * 128;
-      // Global reads of the epilogue are issued ahead of their use so that their latency hides
-      // behind the wait for the accumulator and behind the previous chunk's arithmetic:
-      // the warp's 128 bias values sit four per lane and are handed around by shuffles, and the
-      // residual / pre-activation rows are fetched one 32-column chunk ahead.
-      float4 bias_reg = make_float4(0.f, 0.f, 0.f, 0.f);
-      if (need_bias && half_col0 + lane * 4 < p.n) bias_reg = __ldg(reinterpret_cast<const float4*>(p.bias + half_col0 + lane * 4));
-      auto fetch_aux = [&](int chunk, uint4 (&dst)[4]) {
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          const int col = half_col0 + chunk * 32 + q * 8;
-          dst[q] = make_uint4(0, 0, 0, 0);
-          if (need_aux && row_ok && col < p.n)
-            dst[q] = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(p.aux_in) +
-                                                          (size_t)row * p.ld_aux_in + col));
-        }
-      };
-      uint4 aux_a[4], aux_b[4];
-      fetch_aux(0, aux_a);
+      auto fetch_aux = [&](int chunk, uint4 (&dst)[4]) { fetch_aux_of(w, chunk, dst); };
       if (!tc05::mbar_wait(&tail->tmem_full[buf], buf_phase, abort_flag, p.wait_limit_ns)) { ok = false; break; }
       tc05::tc_fence_after_sync();
       const uint32_t taddr_row = tmem_base + (uint32_t)(buf * BN) + ((uint32_t)(lane_group * 32) << 16);
@@ -466,6 +491,13 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
         tc05::tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) release_buffer(buf);
+        ask_next();
+        if (have_next < 0) ok = false;
+        have = have_next;
+        w = wn;
+        bias_reg = bias_next;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) aux_a[q] = aux_b[q];
         continue;
       }
       if (SPEC < 0 && w.kind == ITEM_FINISH) {
@@ -594,7 +626,9 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
 #pragma unroll 1
       for (int chunk = 0; chunk < 4; ++chunk) {
         if (half_col0 + chunk * 32 >= p.n) break;
-        if (chunk < 3) fetch_aux(chunk + 1, aux_b);
+        const bool last = chunk == 3 || half_col0 + (chunk + 1) * 32 >= p.n;
+        if (!last) fetch_aux(chunk + 1, aux_b);
+        else ask_next();
         process(chunk, aux_a);
 #pragma unroll
         for (int q = 0; q < 4; ++q) aux_a[q] = aux_b[q];
@@ -602,6 +636,15 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
       tc05::tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) release_buffer(buf);
+      if (have_next == -2) {  // no chunk of this half lies inside the matrix
+        ask_next();
+#pragma unroll
+        for (int q = 0; q < 4; ++q) aux_a[q] = aux_b[q];
+      }
+      if (have_next < 0) ok = false;
+      have = have_next;
+      w = wn;
+      bias_reg = bias_next;
     }
     if (lane == 0) tc05::tma_store_wait_all();  // global writes are complete before the kernel ends
   }
