@@ -72,7 +72,8 @@ struct FaParams {
 template <int HD>
 __global__ void __launch_bounds__(FA_THREADS, FaSizes<HD>::CTAS_PER_SM)
 flash_attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
-                           const __grid_constant__ CUtensorMap map_v, const FaParams p) {
+                           const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_o,
+                           const FaParams p) {
   using Z = FaSizes<HD>;
   constexpr int FA_HD = HD;
   constexpr int FA_Q_BYTES = Z::Q_BYTES, FA_KV_BYTES = Z::KV_BYTES, FA_SMEM_DATA = Z::SMEM_DATA, FA_SMEM_BYTES = Z::SMEM_BYTES;
@@ -284,24 +285,36 @@ flash_attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
       tc05::tc_fence_after_sync();
     }
     if (ok) {
+      // O leaves through the Q tile's shared memory (every product that read Q has finished): a warp stages its 32
+      // rows per 64-channel block (128-byte rows, 128-byte swizzle) and its lane 0 sends them with one TMA store, whole
+      // 128-byte row segments instead of 16-byte stores that each touch 32 different lines.  Rows past T are clipped by
+      // the tensor map.
       const float inv = 1.0f / l_run;
-      __nv_bfloat16* dst = p.out + (size_t)(row_base + t) * p.ld_out + (size_t)h * FA_HD;
 #pragma unroll
       for (int hb = 0; hb < FA_HD / 32; ++hb) {
         uint32_t ob[32];
         tc05::tmem_ld_32x32b_x32(tmem_o0 + lane_sel + hb * 32, ob);
         tc05::tmem_ld_wait();
-        if (t < p.T) {
+        uint8_t* line = sq + (hb / 2) * Z::Q_BLOCK + r * 128;
 #pragma unroll
-          for (int i = 0; i < 32; i += 8) {
-            uint4 o;
-            o.x = pack_bf16x2(__uint_as_float(ob[i]) * inv, __uint_as_float(ob[i + 1]) * inv);
-            o.y = pack_bf16x2(__uint_as_float(ob[i + 2]) * inv, __uint_as_float(ob[i + 3]) * inv);
-            o.z = pack_bf16x2(__uint_as_float(ob[i + 4]) * inv, __uint_as_float(ob[i + 5]) * inv);
-            o.w = pack_bf16x2(__uint_as_float(ob[i + 6]) * inv, __uint_as_float(ob[i + 7]) * inv);
-            *reinterpret_cast<uint4*>(dst + hb * 32 + i) = o;
-          }
+        for (int i = 0; i < 32; i += 8) {
+          uint4 o;
+          o.x = pack_bf16x2(__uint_as_float(ob[i]) * inv, __uint_as_float(ob[i + 1]) * inv);
+          o.y = pack_bf16x2(__uint_as_float(ob[i + 2]) * inv, __uint_as_float(ob[i + 3]) * inv);
+          o.z = pack_bf16x2(__uint_as_float(ob[i + 4]) * inv, __uint_as_float(ob[i + 5]) * inv);
+          o.w = pack_bf16x2(__uint_as_float(ob[i + 6]) * inv, __uint_as_float(ob[i + 7]) * inv);
+          const int chunk = (hb & 1) * 4 + i / 8;  // 16-byte chunk of the 128-byte row
+          *reinterpret_cast<uint4*>(line + ((chunk ^ (r & 7)) << 4)) = o;
         }
+      }
+      tc05::fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) {
+#pragma unroll
+        for (int blk = 0; blk < Z::BLOCKS; ++blk)
+          tc05::tma_store_3d(&map_o, sq + blk * Z::Q_BLOCK + warp * (32 * 128), h * FA_HD + blk * 64, q0 + warp * 32, b);
+        tc05::tma_store_commit();
+        tc05::tma_store_wait_all();
       }
     }
     if (ok && t < p.T) {
@@ -343,6 +356,14 @@ int flash_attention_forward_impl(hl_ctx* ctx, const void* q, const void* k, cons
   if ((rc = make_tensor_map_bf16_2d(&mq, q, cols, rows, (uint64_t)ld_qkv, 64, FA_BM)) != HL_OK) return rc;
   if ((rc = make_tensor_map_bf16_2d(&mk, k, cols, rows, (uint64_t)ld_qkv, 64, FA_BN)) != HL_OK) return rc;
   if ((rc = make_tensor_map_bf16_2d(&mv, v, cols, rows, (uint64_t)ld_qkv, 64, FA_BN)) != HL_OK) return rc;
+  // the output as [batch][time][channels], so that a tile's rows past `time` are clipped; boxes of 64 channels by 32 rows
+  CUtensorMap mo;
+  {
+    const uint64_t dims[3] = {(uint64_t)cols, (uint64_t)time, (uint64_t)batch};
+    const uint64_t strides[2] = {(uint64_t)ld_out * 2, (uint64_t)time * (uint64_t)ld_out * 2};
+    const uint32_t box[3] = {64, 32, 1};
+    if ((rc = make_tensor_map(&mo, HL_BF16, 3, out, dims, strides, box, 128)) != HL_OK) return rc;
+  }
   FaParams p{};
   p.B = batch; p.T = time; p.H = n_heads;
   p.ld_out = ld_out;
@@ -359,14 +380,14 @@ int flash_attention_forward_impl(hl_ctx* ctx, const void* q, const void* k, cons
       HL_CUDA(cudaFuncSetAttribute(flash_attention_fwd_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, FaSizes<64>::SMEM_BYTES));
       configured = true;
     }
-    flash_attention_fwd_kernel<64><<<nq * batch * n_heads, FA_THREADS, FaSizes<64>::SMEM_BYTES, ctx->stream>>>(mq, mk, mv, p);
+    flash_attention_fwd_kernel<64><<<nq * batch * n_heads, FA_THREADS, FaSizes<64>::SMEM_BYTES, ctx->stream>>>(mq, mk, mv, mo, p);
   } else {
     static bool configured = false;
     if (!configured) {
       HL_CUDA(cudaFuncSetAttribute(flash_attention_fwd_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, FaSizes<128>::SMEM_BYTES));
       configured = true;
     }
-    flash_attention_fwd_kernel<128><<<nq * batch * n_heads, FA_THREADS, FaSizes<128>::SMEM_BYTES, ctx->stream>>>(mq, mk, mv, p);
+    flash_attention_fwd_kernel<128><<<nq * batch * n_heads, FA_THREADS, FaSizes<128>::SMEM_BYTES, ctx->stream>>>(mq, mk, mv, mo, p);
   }
   HL_LAUNCH_CHECK("flash_attention_fwd_kernel");
   count_launch(ctx);
