@@ -5,8 +5,8 @@
 // run against tensor memory:
 //     S  = Q·Kᵀ          dP = dO·Vᵀ                      (recomputed scores, f32)
 //     dV += Pᵀ·dO        dK += dSᵀ·Q        dQ_tile = dS·K
-// P = exp(S·scale − lse) and dS = P∘(dP − D)·scale are formed in registers by sixteen warps (four
-// per tensor-memory lane group, each taking a quarter of the key columns) and handed back through
+// P = exp(S·scale − lse) and dS = P∘(dP − D)·scale are formed in registers by eight warps (two
+// per tensor-memory lane group, each taking half of the key columns) and handed back through
 // swizzled shared memory as bf16 operands.  dK and dV stay in tensor memory for the whole
 // walk; dQ tiles are staged in shared memory and added into an f32 accumulator by TMA reductions.
 //
@@ -25,11 +25,7 @@ constexpr int FB_BM = 128;  // queries per tile
 constexpr int FB_BN = 128;  // keys per work item
 constexpr int FB_BLOCK = 128 * 128;  // one 64-channel block of a 128-row operand tile: 16 KB
 constexpr int FB_PS_BYTES = FB_BM * FB_BN * 2;  // 32 KB
-constexpr int FB_SOFTMAX_WARPS = 16;
-constexpr int FB_COL_GROUPS = FB_SOFTMAX_WARPS / 4;       // warps per tensor-memory lane group
-constexpr int FB_KEYS_PER_WARP = FB_BN / FB_COL_GROUPS;   // key columns of S, dP, P, dS a warp works on
-constexpr int FB_OUT_PER_WARP = 64 / FB_COL_GROUPS;       // columns of a dQ tile, of dK and of dV a warp moves
-static_assert(FB_SOFTMAX_WARPS == 8 || FB_SOFTMAX_WARPS == 16, "two or four warps per lane group");
+constexpr int FB_SOFTMAX_WARPS = 8;
 constexpr int FB_THREADS = (FB_SOFTMAX_WARPS + 2) * 32;  // + TMA warp + MMA warp
 constexpr int FB_TMEM_COLS = 512;
 constexpr int FB_DQ_BYTES = FB_BM * 64 * 4;     // 32 KB: 64 columns of a dQ tile in f32, staged for the TMA reduction
@@ -308,11 +304,7 @@ flash_attention_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
     // dK and dV are taken out of tensor memory before P/dS are released (the new item's products
     // overwrite them) and stored while those products run.
     const int lg = warp & 3;          // tensor-memory lane group
-    const int cg = warp >> 2;         // column group: which key columns / which dQ and dK/dV columns
-    constexpr int KEYS = FB_KEYS_PER_WARP, OUT = FB_OUT_PER_WARP;
-    // a warp's staging rows: 32 rows of OUT f32 columns (dQ), or of OUT bf16 columns twice (dV, dK)
-    constexpr int ROW_BYTES = OUT * 4;                 // 128 or 64: one swizzle row of the dQ share
-    constexpr int STAGE_BYTES_PER_WARP = 32 * ROW_BYTES;
+    const int half = warp >> 2;       // which 64 key columns / which 32 dQ and dK/dV columns
     const int r = lg * 32 + lane;     // row within the tile
     const uint32_t lane_sel = (uint32_t)(lg * 32) << 16;
     bool ok = !*abort_flag;
@@ -323,68 +315,60 @@ flash_attention_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
     // tensor map.  Every warp stages its own 32 rows x 32 columns (4 KB, rows of 128 bytes, 128-byte swizzle) and its lane 0 adds
     // them with one TMA reduction of its own: no warp waits for another one, and the only wait is the lane's own, for
     // its previous reduction to have read the 4 KB, a whole tile earlier.
-    uint8_t* my_stage = sdq + (cg * 4 + lg) * STAGE_BYTES_PER_WARP;
-    // 16-byte chunk `i` of this lane's row in a tile of 32 rows of `row_bytes` (128, 64 or 32), swizzled as the tensor
-    // map of that row width expects
-    auto swz = [&](int i, int row_bytes) -> int {
-      const int x = row_bytes == 128 ? (lane & 7) : row_bytes == 64 ? ((lane >> 1) & 3) : ((lane >> 2) & 1);
-      return (i ^ x) << 4;
+    uint8_t* my_stage = sdq + half * (FB_BM * 128) + lg * (32 * 128);
+    auto add_dq_begin = [&](int g, uint32_t (&qb)[32]) {  // the tile starts to travel out of tensor memory
+      tc05::tmem_ld_32x32b_x32(tmem_dq + (uint32_t)((g & 1) * 64) + lane_sel + half * 32, qb);
     };
-    auto add_dq_begin = [&](int g, uint32_t (&qb)[OUT]) {  // the tile starts to travel out of tensor memory
-      tc05::tmem_ld_32x32b(tmem_dq + (uint32_t)((g & 1) * 64) + lane_sel + cg * OUT, qb);
-    };
-    auto add_dq_finish = [&](const FbCursor& c, uint32_t (&qb)[OUT]) -> bool {
+    auto add_dq_finish = [&](const FbCursor& c, uint32_t (&qb)[32]) -> bool {
       if (lane == 0) tc05::tma_store_wait_read();  // this warp's previous reduction has read the staging rows
       tc05::tmem_ld_wait();
       tc05::tmem_ld_fence(qb);
       __syncwarp();
-      uint8_t* line = my_stage + lane * ROW_BYTES;
+      uint8_t* line = my_stage + lane * 128;
 #pragma unroll
-      for (int i = 0; i < OUT / 4; ++i)
-        *reinterpret_cast<uint4*>(line + swz(i, ROW_BYTES)) = make_uint4(qb[i * 4], qb[i * 4 + 1], qb[i * 4 + 2], qb[i * 4 + 3]);
+      for (int i = 0; i < 8; ++i)
+        *reinterpret_cast<uint4*>(line + ((i ^ (lane & 7)) << 4)) = make_uint4(qb[i * 4], qb[i * 4 + 1], qb[i * 4 + 2], qb[i * 4 + 3]);
       tc05::fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) {
         const int t0 = (c.kj + c.it) * FB_BM + lg * 32;
-        tc05::tma_reduce_add_3d(&map_dq, my_stage, c.h * FB_HD + c.cb * 64 + cg * OUT, t0, c.b);
+        tc05::tma_reduce_add_3d(&map_dq, my_stage, c.h * FB_HD + c.cb * 64 + half * 32, t0, c.b);
         tc05::tma_store_commit();
       }
       return true;
     };
-    // dV and dK of this thread's key row (OUT columns each) out of tensor memory, already rounded to bf16 pairs: the
-    // first OUT/2 words hold dV, the rest dK
-    auto load_dkv = [&](uint32_t (&w)[OUT]) {
+    // dV and dK of this thread's key row (32 columns each) out of tensor memory, already rounded to bf16 pairs:
+    // words 0-15 hold dV, words 16-31 dK
+    auto load_dkv = [&](uint32_t (&w)[32]) {
 #pragma unroll
       for (int which = 0; which < 2; ++which) {
-        uint32_t raw[OUT];
-        tc05::tmem_ld_32x32b((which == 0 ? tmem_dv : tmem_dk) + lane_sel + cg * OUT, raw);
+        uint32_t raw[32];
+        tc05::tmem_ld_32x32b_x32((which == 0 ? tmem_dv : tmem_dk) + lane_sel + half * 32, raw);
         tc05::tmem_ld_wait();
 #pragma unroll
-        for (int i = 0; i < OUT; i += 2) w[which * (OUT / 2) + i / 2] = pack_bf16x2(__uint_as_float(raw[i]), __uint_as_float(raw[i + 1]));
+        for (int i = 0; i < 32; i += 2) w[which * 16 + i / 2] = pack_bf16x2(__uint_as_float(raw[i]), __uint_as_float(raw[i + 1]));
       }
     };
-    // dK, dV of item c (row r = key): through the warp's staging rows (two tiles of 32 rows of OUT bf16 columns) and out
-    // with one TMA store each, whole row segments together with the neighbouring warps, instead of 16-byte stores that
-    // each touch 32 different lines.  Keys past T are clipped by the tensor map.
-    auto store_dkv = [&](const uint32_t (&w)[OUT], const FbCursor& c) {
-      constexpr int KV_ROW = OUT * 2;  // 64 or 32 bytes
-      if (lane == 0) tc05::tma_store_wait_read();  // whatever was queued from the staging rows before has read them
+    // dK, dV of item c (row r = key): through the warp's staging rows (two tiles of 32 rows x 64 bytes, 64-byte
+    // swizzle) and out with one TMA store each, 128-byte row segments together with the other half's warp, instead of
+    // sixteen 16-byte stores a thread that each touch 32 different lines.  Keys past T are clipped by the tensor map.
+    auto store_dkv = [&](const uint32_t (&w)[32], const FbCursor& c) {
+      if (lane == 0) tc05::tma_store_wait_read();  // the dQ reduction queued just before has read the staging rows
       __syncwarp();
-      uint8_t* tv = my_stage + lane * KV_ROW;
-      uint8_t* tk = my_stage + 32 * KV_ROW + lane * KV_ROW;
+      uint8_t* tv = my_stage + lane * 64;
+      uint8_t* tk = my_stage + 2048 + lane * 64;
 #pragma unroll
-      for (int i = 0; i < OUT / 8; ++i) {
-        const int off = swz(i, KV_ROW);
+      for (int i = 0; i < 4; ++i) {
+        const int off = (i ^ ((lane >> 1) & 3)) << 4;
         *reinterpret_cast<uint4*>(tv + off) = make_uint4(w[i * 4], w[i * 4 + 1], w[i * 4 + 2], w[i * 4 + 3]);
-        *reinterpret_cast<uint4*>(tk + off) =
-            make_uint4(w[OUT / 2 + i * 4], w[OUT / 2 + i * 4 + 1], w[OUT / 2 + i * 4 + 2], w[OUT / 2 + i * 4 + 3]);
+        *reinterpret_cast<uint4*>(tk + off) = make_uint4(w[16 + i * 4], w[16 + i * 4 + 1], w[16 + i * 4 + 2], w[16 + i * 4 + 3]);
       }
       tc05::fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) {
-        const int col = c.h * FB_HD + c.cb * 64 + cg * OUT, key0 = c.kj * FB_BN + lg * 32;
+        const int col = c.h * FB_HD + c.cb * 64 + half * 32, key0 = c.kj * FB_BN + lg * 32;
         tc05::tma_store_3d(&map_dv, my_stage, col, key0, c.b);
-        tc05::tma_store_3d(&map_dk, my_stage + 32 * KV_ROW, col, key0, c.b);
+        tc05::tma_store_3d(&map_dk, my_stage + 2048, col, key0, c.b);
         tc05::tma_store_commit();
       }
     };
@@ -423,17 +407,17 @@ flash_attention_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
       row_stats(n, &next_lse_raw, &next_dlt_raw);
       if (!tc05::mbar_wait(&bars->sdp_full, (uint32_t)g & 1u, abort_flag)) return false;
       tc05::tc_fence_after_sync();
-      uint32_t pp[KEYS / 16][8], dd[KEYS / 16][8];  // P and dS of this thread's key columns, bf16 pairs
+      uint32_t pp[4][8], dd[4][8];  // P and dS of this thread's 64 key columns, bf16 pairs
       uint32_t sb[2][8], db[2][8];  // eight columns at a time, the next eight on their way
-      tc05::tmem_ld_32x32b_x8(tmem_s + lane_sel + cg * KEYS, sb[0]);
-      tc05::tmem_ld_32x32b_x8(tmem_dp + lane_sel + cg * KEYS, db[0]);
+      tc05::tmem_ld_32x32b_x8(tmem_s + lane_sel + half * 64, sb[0]);
+      tc05::tmem_ld_32x32b_x8(tmem_dp + lane_sel + half * 64, db[0]);
 #pragma unroll
-      for (int ch = 0; ch < KEYS / 8; ++ch) {
-        const int col0 = cg * KEYS + ch * 8;  // key column within the tile
+      for (int ch = 0; ch < 8; ++ch) {
+        const int col0 = half * 64 + ch * 8;  // key column within the tile
         tc05::tmem_ld_wait();
         tc05::tmem_ld_fence(sb[ch & 1]);
         tc05::tmem_ld_fence(db[ch & 1]);
-        if (ch < KEYS / 8 - 1) {  // the next columns travel while these are worked on
+        if (ch < 7) {  // the next columns travel while these are worked on
           tc05::tmem_ld_32x32b_x8(tmem_s + lane_sel + col0 + 8, sb[(ch + 1) & 1]);
           tc05::tmem_ld_32x32b_x8(tmem_dp + lane_sel + col0 + 8, db[(ch + 1) & 1]);
         } else {  // all of S and dP is in registers: the next tile's may overwrite them
@@ -464,21 +448,19 @@ flash_attention_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
         if (!tc05::mbar_wait(&bars->dq_full, (uint32_t)(g - 1) & 1u, abort_flag)) return false;
         tc05::tc_fence_after_sync();
       }
-      // P and dS are two 64-key blocks of [query][128 bytes]; this warp's keys are 16-byte chunks chunk0.. of one of them
-      uint8_t* pline = sp + ((cg * KEYS) / 64) * (FB_BM * 128) + r * 128;
-      uint8_t* dline = sds + ((cg * KEYS) / 64) * (FB_BM * 128) + r * 128;
-      const int chunk0 = ((cg * KEYS) % 64) / 8;
+      uint8_t* pline = sp + half * (FB_BM * 128) + r * 128;
+      uint8_t* dline = sds + half * (FB_BM * 128) + r * 128;
 #pragma unroll
-      for (int ch = 0; ch < KEYS / 16; ++ch) {
+      for (int ch = 0; ch < 4; ++ch) {
 #pragma unroll
         for (int q = 0; q < 2; ++q) {
-          const int chunk = chunk0 + ch * 2 + q;  // 16-byte chunk = 8 keys
+          const int chunk = ch * 2 + q;  // 16-byte chunk = 8 keys
           const int off = (chunk ^ (r & 7)) << 4;
           *reinterpret_cast<uint4*>(pline + off) = make_uint4(pp[ch][q * 4], pp[ch][q * 4 + 1], pp[ch][q * 4 + 2], pp[ch][q * 4 + 3]);
           *reinterpret_cast<uint4*>(dline + off) = make_uint4(dd[ch][q * 4], dd[ch][q * 4 + 1], dd[ch][q * 4 + 2], dd[ch][q * 4 + 3]);
         }
       }
-      uint32_t dkv[Boundary ? OUT : 1];
+      uint32_t dkv[Boundary ? 32 : 1];
       if constexpr (Boundary) load_dkv(dkv);  // before the new item's first products may overwrite them
       tc05::fence_proxy_async_smem();
       tc05::tc_fence_before_sync();
@@ -489,7 +471,7 @@ flash_attention_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
       // waits only for these two plain stores to have read them
       if constexpr (Boundary) store_dkv(dkv, prev);
       if (g > 0) {
-        uint32_t qb[OUT];
+        uint32_t qb[32];
         add_dq_begin(g - 1, qb);
         if (!add_dq_finish(prev, qb)) return false;
       }
@@ -505,10 +487,10 @@ flash_attention_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
     if (ok && g > 0) {  // dQ of the last query tile and dK, dV of the last item
       if (tc05::mbar_wait(&bars->dq_full, (uint32_t)(g - 1) & 1u, abort_flag)) {
         tc05::tc_fence_after_sync();
-        uint32_t qb[OUT];
+        uint32_t qb[32];
         add_dq_begin(g - 1, qb);
         add_dq_finish(prev, qb);
-        uint32_t dkv[OUT];
+        uint32_t dkv[32];
         load_dkv(dkv);
         store_dkv(dkv, prev);
         if (lane == 0) tc05::tma_store_wait_all();  // the last reduction and stores have left shared memory and landed
@@ -627,17 +609,17 @@ int flash_attention_backward_impl(hl_ctx* ctx, const void* q, const void* k, con
   {
     const uint64_t dims[3] = {(uint64_t)C, (uint64_t)time, (uint64_t)batch};
     const uint64_t strides[2] = {(uint64_t)C * sizeof(float), (uint64_t)time * (uint64_t)C * sizeof(float)};
-    const uint32_t box[3] = {(uint32_t)FB_OUT_PER_WARP, 32, 1};  // one softmax warp's share of a dQ tile
-    if ((rc = make_tensor_map(&mdq, HL_F32, 3, dq_accum, dims, strides, box, FB_OUT_PER_WARP * 4)) != HL_OK) return rc;
+    const uint32_t box[3] = {32, 32, 1};  // one softmax warp's share of a dQ tile
+    if ((rc = make_tensor_map(&mdq, HL_F32, 3, dq_accum, dims, strides, box, 128)) != HL_OK) return rc;
   }
   // dK and dV as [batch][time][channels] bf16 with the caller's row stride; boxes of 32 channels (64 bytes) by 32 keys
   CUtensorMap mdk, mdv;
   {
     const uint64_t dims[3] = {(uint64_t)C, (uint64_t)time, (uint64_t)batch};
     const uint64_t strides[2] = {(uint64_t)ld_dqkv * 2, (uint64_t)time * (uint64_t)ld_dqkv * 2};
-    const uint32_t box[3] = {(uint32_t)FB_OUT_PER_WARP, 32, 1};
-    if ((rc = make_tensor_map(&mdk, HL_BF16, 3, dk, dims, strides, box, FB_OUT_PER_WARP * 2)) != HL_OK) return rc;
-    if ((rc = make_tensor_map(&mdv, HL_BF16, 3, dv, dims, strides, box, FB_OUT_PER_WARP * 2)) != HL_OK) return rc;
+    const uint32_t box[3] = {32, 32, 1};
+    if ((rc = make_tensor_map(&mdk, HL_BF16, 3, dk, dims, strides, box, 64)) != HL_OK) return rc;
+    if ((rc = make_tensor_map(&mdv, HL_BF16, 3, dv, dims, strides, box, 64)) != HL_OK) return rc;
   }
   const int grid = std::min(nq * batch * n_heads * p.blocks, persistent_sms(ctx));
   if (head_dim == 64) {

@@ -5,7 +5,6 @@
 // f32 bias gradients of the step cost no extra pass over memory.
 // Arithmetic: src/tensor.rs:3175-3256 (forward), src/tensor/autograd.rs:2158-2232 (backward),
 // kernels.ptx:312 (bias gradient), in f32 as the reference's CUDA route.
-#include <cstdlib>
 #include "kernels.h"
 
 namespace hl {
@@ -128,28 +127,17 @@ ln_bwd_bf16_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict_
   if (active) load8_f32(gamma + c, g);
   const float inv_f = 1.0f / (float)features;
   int parity = 0;
-  // x and dy of the group's next row are requested while the current row is reduced; the residual row, needed only for
-  // the last step, is requested after the row sums, so that its latency hides behind the group's barrier.
-  uint4 nx = make_uint4(0u, 0u, 0u, 0u);
-  float4 nd0 = make_float4(0.f, 0.f, 0.f, 0.f), nd1 = nd0;
-  auto fetch = [&](int row) {
-    if (active && row < r1) {
-      const size_t b = (size_t)row * features + c;
-      nx = *reinterpret_cast<const uint4*>(x + b);
-      nd0 = *reinterpret_cast<const float4*>(dy + b);
-      nd1 = *reinterpret_cast<const float4*>(dy + b + 4);
-    }
-  };
-  fetch(r0 + group);
   for (int row = r0 + group; row < r1; row += GROUPS, parity ^= 1) {
     const size_t base = (size_t)row * features + c;
     float xh[8], d[8], o[8];
-    unpack8_bf16(nx, xh);
-    d[0] = nd0.x; d[1] = nd0.y; d[2] = nd0.z; d[3] = nd0.w; d[4] = nd1.x; d[5] = nd1.y; d[6] = nd1.z; d[7] = nd1.w;
 #pragma unroll
-    for (int e = 0; e < 8; ++e) o[e] = 0.f;
+    for (int e = 0; e < 8; ++e) { xh[e] = 0.f; d[e] = 0.f; o[e] = 0.f; }
+    if (active) {  // every global read of the row is issued before anything is consumed
+      load8_bf16(x + base, xh);
+      load8_f32(dy + base, d);
+      if (residual) load8_f32(residual + base, o);
+    }
     const float mean = mean_in[row], rstd = rstd_in[row];
-    fetch(row + GROUPS);
     float s1 = 0.f, s2 = 0.f;
     if (active) {
 #pragma unroll
@@ -164,7 +152,6 @@ ln_bwd_bf16_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict_
     }
     s1 = warp_sum(s1);
     s2 = warp_sum(s2);
-    if (active && residual) load8_f32(residual + base, o);
     if constexpr (WPR > 1) {
       if (lane == 0) row_sums[parity][group][wr] = make_float2(s1, s2);
       // hardware barrier 1 + group, immediate ids so that a CTA reserves only GROUPS + 1 of the SM's 16
@@ -355,8 +342,7 @@ bool layer_norm_fast_applicable(int x_dtype, int y_dtype, int features, const vo
 
 int layer_norm_forward_fast(hl_ctx* ctx, const void* x, const float* gamma, const float* beta, void* y, float* mean,
                             float* rstd, int rows, int features, float eps) {
-  static const int per_sm = [] { const char* e = getenv("HEIRLOOM_LN_FWD_CTAS"); return e ? atoi(e) : 8; }();  // EXPERIMENT
-  const int grid = std::min(ceil_div(rows, ROW_WARPS), ctx->sm_count * per_sm);
+  const int grid = std::min(ceil_div(rows, ROW_WARPS), ctx->sm_count * 8);
   const int J = ceil_div(features, 256);
 #define HL_LAUNCH(JJ)                                                                                          \
   ln_fwd_bf16_kernel<JJ><<<grid, ROW_WARPS * 32, 0, ctx->stream>>>((const __nv_bfloat16*)x, gamma, beta,       \
