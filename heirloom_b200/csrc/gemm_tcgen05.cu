@@ -580,9 +580,18 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
             }
             if (epi == HL_EPI_BIAS_GELU) {
               // h = bf16(acc + bias) is the main output; g = bf16(gelu(h)) the second one
+              // rounded two at a time by the packing conversion (the packed word is the output word as well) and widened
+              // again with one integer op each: a quarter of the instructions of rounding on integer ops
               float gl[8];
 #pragma unroll
-              for (int i = 0; i < 8; ++i) { v[i] = bf16_round_alu(v[i]); gl[i] = gelu_fwd_fast(v[i]); }
+              for (int i = 0; i < 8; i += 2) {
+                const uint32_t hw = pack_bf16x2(v[i], v[i + 1]);
+                packed[g * 4 + i / 2] = hw;
+                v[i] = __uint_as_float(hw << 16);
+                v[i + 1] = __uint_as_float(hw & 0xFFFF0000u);
+              }
+#pragma unroll
+              for (int i = 0; i < 8; ++i) gl[i] = gelu_fwd_fast(v[i]);
               gelu_packed[g * 4] = pack_bf16x2(gl[0], gl[1]); gelu_packed[g * 4 + 1] = pack_bf16x2(gl[2], gl[3]);
               gelu_packed[g * 4 + 2] = pack_bf16x2(gl[4], gl[5]); gelu_packed[g * 4 + 3] = pack_bf16x2(gl[6], gl[7]);
             } else if (epi == HL_EPI_BIAS_RESIDUAL || epi == HL_EPI_DGELU) {
@@ -592,7 +601,11 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
               if (epi == HL_EPI_BIAS_RESIDUAL) {
                 // out = bf16(residual + bf16(acc + bias)): the two round trips of the block
 #pragma unroll
-                for (int i = 0; i < 8; ++i) v[i] = rr[i] + bf16_round_alu(v[i]);
+                for (int i = 0; i < 8; i += 2) {
+                  const uint32_t hw = pack_bf16x2(v[i], v[i + 1]);
+                  v[i] = rr[i] + __uint_as_float(hw << 16);
+                  v[i + 1] = rr[i + 1] + __uint_as_float(hw & 0xFFFF0000u);
+                }
               } else {
                 // out = acc * gelu'(h), h read from aux_in
 #pragma unroll
@@ -600,9 +613,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
               }
             }
           }
-          if (out_bf16 && epi == HL_EPI_BIAS_GELU) {  // h is already rounded
-            packed[g * 4] = pack_rounded_bf16x2(v[0], v[1]); packed[g * 4 + 1] = pack_rounded_bf16x2(v[2], v[3]);
-            packed[g * 4 + 2] = pack_rounded_bf16x2(v[4], v[5]); packed[g * 4 + 3] = pack_rounded_bf16x2(v[6], v[7]);
+          if (out_bf16 && epi == HL_EPI_BIAS_GELU) {  // h was packed when it was rounded
           } else if (out_bf16) {
             packed[g * 4] = pack_bf16x2(v[0], v[1]); packed[g * 4 + 1] = pack_bf16x2(v[2], v[3]);
             packed[g * 4 + 2] = pack_bf16x2(v[4], v[5]); packed[g * 4 + 3] = pack_bf16x2(v[6], v[7]);
