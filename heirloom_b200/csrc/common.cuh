@@ -178,15 +178,23 @@ __device__ __forceinline__ float tanh_fast(float x) {
   asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
+// The tanh form of GELU and its derivative, written as the shortest chains of fused multiply-adds (the epilogues that use
+// them are bound by their instruction count): gelu(x) = hx + hx*t with hx = x/2, t = tanh(x*(k0 + k1*x^2)).
 __device__ __forceinline__ float gelu_fwd_fast(float x) {
-  const float inner = 0.7978845608028654f * (x + 0.044715f * x * x * x);
-  return 0.5f * x * (1.0f + tanh_fast(inner));
-}
-__device__ __forceinline__ float gelu_grad_fast(float x) {
+  constexpr float k0 = 0.7978845608028654f, k1 = 0.7978845608028654f * 0.044715f;
   const float x2 = x * x;
-  const float t = tanh_fast(0.7978845608028654f * (x + 0.044715f * x * x2));
-  const float dinner = 0.7978845608028654f * (1.0f + 3.0f * 0.044715f * x2);
-  return 0.5f * (1.0f + t) + 0.5f * x * (1.0f - t * t) * dinner;
+  const float t = tanh_fast(x * fmaf(x2, k1, k0));
+  const float hx = 0.5f * x;
+  return fmaf(hx, t, hx);
+}
+// gelu'(x) = (1 + t)/2 + hx*(1 - t^2)*(k0 + 3*k1*x^2)
+__device__ __forceinline__ float gelu_grad_fast(float x) {
+  constexpr float k0 = 0.7978845608028654f, k1 = 0.7978845608028654f * 0.044715f;
+  const float x2 = x * x;
+  const float t = tanh_fast(x * fmaf(x2, k1, k0));
+  const float dinner = fmaf(x2, 3.0f * k1, k0);
+  const float sech2 = fmaf(-t, t, 1.0f);
+  return fmaf(0.5f * x * sech2, dinner, fmaf(0.5f, t, 0.5f));
 }
 
 template <typename T>
