@@ -734,13 +734,19 @@ int launch_variant(hl_ctx* ctx, const CUtensorMap& ma, const CUtensorMap& mb, co
 }
 
 // Which products run on CTA pairs: HEIRLOOM_GEMM_PAIRS=1 every whole-tile product, 0 none; unset, those with a contraction
-// of kPairMinK and up, where the main loop and not the epilogue bounds the tile.  Read at every call.
+// of kPairMinK and up and the wide forward products.  Read at every call.
 constexpr int kPairMinK = 2048;
-bool pairs_enabled(int k) {
+bool pairs_enabled(const hl_gemm_desc* d) {
   const char* e = getenv("HEIRLOOM_GEMM_PAIRS");
   if (e && e[0] == '1') return true;
   if (e && e[0] == '0') return false;
-  return k >= kPairMinK;
+  if (d->k >= kPairMinK) return true;
+  // Short contractions are bound by what the SMs can pull out of L2 (every tile reads its operands again: the MMA issuer
+  // of the qkv forward product spends three quarters of a tile waiting for operand stages, not for the epilogue), and a
+  // pair reads a third less per output.  It pays where the output is wide: qkv forward 51.3 -> 47.8 us, fc1 forward
+  // 84.5 -> 81.5, lm_head forward 1290 -> 1230; the 768-wide outputs and the input gradients lose a few per cent.
+  return d->a_layout == HL_K_MAJOR && d->b_layout == HL_K_MAJOR && d->n >= 2048 &&
+         (d->epilogue == HL_EPI_BIAS || d->epilogue == HL_EPI_BIAS_GELU);
 }
 
 }  // namespace
@@ -842,7 +848,7 @@ int gemm_bf16_run(hl_ctx* ctx, const hl_gemm_desc* d, const void* a, const void*
   // Whole tiles (of the whole contraction or of equal splits of it; not the dealt-out k blocks) can run on CTA pairs
   // with 256-row tiles.  Measured on alternating calls: 6-7 % faster where the main loop bounds the tile (contractions
   // of 2304 and up), 6-10 % slower at 768, where the epilogue does and the leader waits for both CTAs' epilogue warps.
-  const bool pair = pairs_enabled(d->k) && plan.sk_tiles == 0 && d->m > BM && sms >= 2 && ctx->gemm_skip_kblock < 0;
+  const bool pair = pairs_enabled(d) && plan.sk_tiles == 0 && d->m > BM && sms >= 2 && ctx->gemm_skip_kblock < 0;
   GemmParams p{};
   p.m = d->m; p.n = d->n; p.k = d->k;
   p.m_tiles = ceil_div(d->m, pair ? 2 * BM : BM);
@@ -942,6 +948,11 @@ int gemm_bf16_run(hl_ctx* ctx, const hl_gemm_desc* d, const void* a, const void*
   else if (!a_mn && !b_mn && !pair && spec == kGelu + 1) rc = launch_variant<false, false, false, kGelu + 1>(ctx, ma, mb, mc, maux, p, grid);
   else if (!a_mn && !b_mn && !pair && spec == kResidual + 1) rc = launch_variant<false, false, false, kResidual + 1>(ctx, ma, mb, mc, maux, p, grid);
   else if (!a_mn && !b_mn && pair && spec == kResidual + 1) rc = launch_variant<false, false, true, kResidual + 1>(ctx, ma, mb, mc, maux, p, grid);
+  else if (!a_mn && !b_mn && pair && spec == kBias + 1) rc = launch_variant<false, false, true, kBias + 1>(ctx, ma, mb, mc, maux, p, grid);
+  else if (!a_mn && !b_mn && pair && spec == kGelu + 1) rc = launch_variant<false, false, true, kGelu + 1>(ctx, ma, mb, mc, maux, p, grid);
+  else if (!a_mn && !b_mn && pair && spec == kBias) rc = launch_variant<false, false, true, kBias>(ctx, ma, mb, mc, maux, p, grid);
+  else if (!a_mn && b_mn && pair && spec == kDgelu + 1) rc = launch_variant<false, true, true, kDgelu + 1>(ctx, ma, mb, mc, maux, p, grid);
+  else if (!a_mn && b_mn && pair && spec == kNone + 1) rc = launch_variant<false, true, true, kNone + 1>(ctx, ma, mb, mc, maux, p, grid);
   else if (!a_mn && b_mn && !pair && spec == kDgelu + 1) rc = launch_variant<false, true, false, kDgelu + 1>(ctx, ma, mb, mc, maux, p, grid);
   else if (!a_mn && b_mn && !pair && spec == kNone + 1) rc = launch_variant<false, true, false, kNone + 1>(ctx, ma, mb, mc, maux, p, grid);
   else if (!a_mn && b_mn && pair && spec == kNone) rc = launch_variant<false, true, true, kNone>(ctx, ma, mb, mc, maux, p, grid);
