@@ -15,7 +15,12 @@
 // 256 columns.  An epilogue warp moves its 32 rows through two alternating 2 KB swizzled staging
 // tiles and writes them with TMA stores (64-byte row segments, clipped at the tensor edge).
 //
-// Contractions of 2048 and up whose tiles are whole (or equal splits) run on pairs of CTAs instead: a cluster of two
+// Kernels: the generic one reads epilogue, output type and work split from its parameters; the training step's
+// whole-tile products also have kernels compiled for their one epilogue and output type (template parameter SPEC), whose
+// epilogue warps run straight-line code.
+//
+// Contractions of 2048 and up and the wide forward products, with whole tiles (or equal splits), run on pairs of CTAs: a
+// cluster of two
 // neighbouring SMs works on a 256 x 256 tile, the even CTA's MMA warp issues tcgen05.mma.cta_group::2 for both, each CTA
 // stages its own 128 rows of A and 128 of B's 256 columns (six 32 KB stages in the same shared memory) and keeps its 128
 // accumulator rows in its own tensor memory, so each SM reads half as much of B per MMA.  The even CTA's `full` barriers
