@@ -35,7 +35,7 @@ DATASHEET_BF16_TFLOPS = 2250.0
 # in a one-pass ncu launch list of this command (summary kept under profiles/), and the first 16 hex digits of the
 # SHA-256 of the GEMM source the capture ran with: a kernel changed since then gets no traffic figure, not a stale one.
 GEMM_DRAM_BYTES_PER_LAUNCH = 155.1e6
-GEMM_SOURCE_AT_CAPTURE = "d1f5424ef7d2e22d"
+GEMM_SOURCE_AT_CAPTURE = "6a10afcb74c80bde"
 
 
 def gemm_traffic():

@@ -890,8 +890,7 @@ int gemm_bf16_run(hl_ctx* ctx, const hl_gemm_desc* d, const void* a, const void*
     const bool dynamic = e && (e[0] == '0' || e[0] == '1') ? e[0] == '1' : nccl_active(ctx);
     p.sched = (dynamic && !pair && plan.sk_tiles == 0 && ctx->gemm_skip_kblock < 0) ? ctx->gemm_sched : nullptr;
     if (p.sched) {
-      p.sched_base = ctx->gemm_sched_base;
-      ctx->gemm_sched_base += (unsigned)(p.m_tiles * p.n_tiles * splits);
+      p.sched_base = ctx->gemm_sched_base;  // advanced below, once the launch has been queued
     }
   }
   p.k_blocks_per_split = ceil_div(p.k_blocks, splits);
@@ -977,6 +976,7 @@ int gemm_bf16_run(hl_ctx* ctx, const hl_gemm_desc* d, const void* a, const void*
     else              rc = launch_variant<false, false, false>(ctx, ma, mb, mc, maux, p, grid);
   }
   if (rc != HL_OK) return rc;
+  if (p.sched) ctx->gemm_sched_base += (unsigned)total;  // every tile of the launch draws from the counter once
   if (splits > 1) {
     const long long quads = (long long)d->m * (d->n / 4);
     const long long want_blocks = ceil_div_ll(quads, 256), cap_blocks = (long long)ctx->sm_count * 8;
